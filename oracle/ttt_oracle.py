@@ -1,0 +1,411 @@
+"""CPU oracle for the fused TTT inner loop (TEST INFRASTRUCTURE, not product code).
+
+This file restates, in plain torch tensor arithmetic on the CPU, what the
+reference computes on the `fused-tile-multi` path, so that the CUDA kernels can
+be checked against it.  Only tests, the smoke check and the benchmark's CPU
+baseline leg may import it; the product package never does.
+
+Parity status: PINNED.  `tests/test_oracle_golden.py` checks every function here
+against fixtures produced by running the reference's own PyTorch module
+(`reference/ttt.py`, `TTTLinear.ttt` / `TTTMLP.ttt` plus autograd) and its
+`reference/validate.py` cases; the generating script is
+`tests/golden/make_golden.py`.
+
+Reference lines each function follows (paths relative to the reference repo):
+
+* `ln_stats`, `ln_fwd`, `ln_l2_grad`      reference/ttt.py:461-505,
+                                          rust/core/src/util.rs:141-182
+* `ttt_linear_forward`                    rust/core/src/linear.rs:91-149 (one stage),
+                                          rust/fused/src/linear_fused_tile/forward/kernel.rs:116-175
+                                          (stage loop, checkpoints *before* the update of
+                                          stage s when s % K == 0, token_eta read at [0, CS)
+                                          in every stage)
+* `ttt_linear_backward`                   rust/fused/src/linear_fused_tile/backward/stage.rs:42-1006
+                                          (analytic per-stage backward),
+                                          backward/kernel.rs:254-429 (reverse stage loop; final-state
+                                          gradients are taken as zero, launch.rs:188-194),
+                                          backward/launch.rs:351-392 (gradient shapes: per-batch
+                                          dW/db, [T] token_eta gradient, [H,F] LN gradients)
+* `ttt_mlp_forward`                       rust/core/src/mlp.rs:127-208, reference/ttt.py:1107-1229
+* `gelu_tanh`, `gelu_tanh_grad`           rust/thundercube/src/unary_ops.rs:147-173,
+                                          reference/ttt.py:509-512
+
+All functions take tensors laid out as the reference's operator does:
+xq/xk/xv/out `[B,H,T,F]`, state weight `[B,H,F,F]`, bias `[B,H,F]`,
+token_eta `[T]`, ttt_lr_eta `[B,H,T]`, LN weight/bias `[H,F]`.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional, Tuple
+
+import torch
+
+GELU_C0 = 0.7978845608028654  # sqrt(2/pi)
+GELU_C1 = 0.044715
+
+
+# --------------------------------------------------------------------------
+# LayerNorm pieces
+# --------------------------------------------------------------------------
+
+def ln_stats(x: torch.Tensor, eps: float):
+    """Row statistics over the last dim: biased variance, eps inside the sqrt."""
+    mu = x.mean(dim=-1, keepdim=True)
+    xc = x - mu
+    var = (xc * xc).mean(dim=-1, keepdim=True)
+    sigma = torch.sqrt(var + eps)
+    return xc / sigma, sigma
+
+
+def ln_fwd(x, gamma, beta, eps: float):
+    x_hat, _ = ln_stats(x, eps)
+    return gamma * x_hat + beta
+
+
+def ln_l2_grad(x, target, gamma, beta, eps: float):
+    """Gradient of 0.5*||LN(x) - target||^2 w.r.t. x (summed loss, per row)."""
+    F = x.shape[-1]
+    x_hat, sigma = ln_stats(x, eps)
+    gy = gamma * x_hat + beta - target
+    gxh = gy * gamma
+    g = (F * gxh - gxh.sum(-1, keepdim=True) - x_hat * (gxh * x_hat).sum(-1, keepdim=True)) / (sigma * F)
+    return g
+
+
+def gelu_tanh(x):
+    return 0.5 * x * (1.0 + torch.tanh(GELU_C0 * x * (1.0 + GELU_C1 * x * x)))
+
+
+def gelu_tanh_grad(x):
+    t = torch.tanh(GELU_C0 * x * (1.0 + GELU_C1 * x * x))
+    return 0.5 * x * ((1.0 - t * t) * (GELU_C0 + 3.0 * GELU_C0 * GELU_C1 * x * x)) + 0.5 * (1.0 + t)
+
+
+# --------------------------------------------------------------------------
+# TTT-Linear forward
+# --------------------------------------------------------------------------
+
+def _stage_views(x: torch.Tensor, cs: int):
+    B, H, T = x.shape[:3]
+    return x.reshape(B, H, T // cs, cs, *x.shape[3:])
+
+
+def _eta_matrices(token_eta_cs: torch.Tensor, lr_stage: torch.Tensor):
+    """eta[i,j] = token_eta[i] * lr[j] for j <= i (diagonal included), else 0."""
+    eta = token_eta_cs.view(1, 1, -1, 1) * lr_stage.unsqueeze(-2)  # [B,H,CS,CS]
+    return torch.tril(eta)
+
+
+def ttt_linear_forward(
+    xq, xk, xv, weight, bias, token_eta, ttt_lr_eta, ln_weight, ln_bias,
+    mini_batch: int = 16, eps: float = 1e-6, checkpoint_interval: int = 1,
+) -> Dict[str, torch.Tensor]:
+    """Whole-sequence forward scan.
+
+    Returns dict(output [B,H,T,F], weight [B,H,F,F], bias [B,H,F],
+    weight_checkpoints [B*H*ceil(NS/K),F,F], bias_checkpoints [B*H*ceil(NS/K),F]).
+    """
+    B, H, T, F = xq.shape
+    cs = mini_batch
+    if T % cs != 0:
+        raise ValueError(f"seq_len ({T}) must be divisible by mini_batch_len ({cs})")
+    ns = T // cs
+    K = checkpoint_interval
+    nck = (ns + K - 1) // K
+    W = weight.clone()
+    b = bias.clone()
+    g_ = ln_weight.view(1, H, 1, F)
+    be_ = ln_bias.view(1, H, 1, F)
+    te = token_eta[:cs]
+    q_s, k_s, v_s = (_stage_views(t, cs) for t in (xq, xk, xv))
+    lr_s = _stage_views(ttt_lr_eta, cs)
+    out = torch.empty_like(xq).reshape(B, H, ns, cs, F)
+    w_ck = torch.empty(B, H, nck, F, F, dtype=W.dtype)
+    b_ck = torch.empty(B, H, nck, F, dtype=W.dtype)
+    for s in range(ns):
+        if s % K == 0:
+            w_ck[:, :, s // K] = W
+            b_ck[:, :, s // K] = b
+        Q, Kk, V, lr = q_s[:, :, s], k_s[:, :, s], v_s[:, :, s], lr_s[:, :, s]
+        z1 = Kk @ W + b.unsqueeze(-2)
+        G = ln_l2_grad(z1, V - Kk, g_, be_, eps)
+        eta = _eta_matrices(te, lr)
+        attn = torch.tril(Q @ Kk.transpose(-1, -2))
+        zbar = Q @ W + b.unsqueeze(-2) - (eta * (1.0 + attn)) @ G
+        out[:, :, s] = Q + ln_fwd(zbar, g_, be_, eps)
+        last = (te[cs - 1] * lr).unsqueeze(-1)  # [B,H,CS,1]
+        W = W - (last * Kk).transpose(-1, -2) @ G
+        b = b - (last * G).sum(dim=-2)
+    return {
+        "output": out.reshape(B, H, T, F),
+        "weight": W,
+        "bias": b,
+        "weight_checkpoints": w_ck.reshape(B * H * nck, F, F),
+        "bias_checkpoints": b_ck.reshape(B * H * nck, F),
+    }
+
+
+# --------------------------------------------------------------------------
+# TTT-Linear analytic backward
+# --------------------------------------------------------------------------
+
+def _stage_states(xk, xv, weight, bias, te, lr_s, g_, be_, cs, eps):
+    """Re-simulate the state (W_s, b_s) seen at the start of every stage."""
+    B, H, T, F = xk.shape
+    ns = T // cs
+    k_s, v_s = _stage_views(xk, cs), _stage_views(xv, cs)
+    W, b = weight.clone(), bias.clone()
+    Ws, bs = [], []
+    for s in range(ns):
+        Ws.append(W)
+        bs.append(b)
+        Kk, V, lr = k_s[:, :, s], v_s[:, :, s], lr_s[:, :, s]
+        G = ln_l2_grad(Kk @ W + b.unsqueeze(-2), V - Kk, g_, be_, eps)
+        last = (te[cs - 1] * lr).unsqueeze(-1)
+        W = W - (last * Kk).transpose(-1, -2) @ G
+        b = b - (last * G).sum(dim=-2)
+    return Ws, bs
+
+
+def ttt_linear_backward(
+    xq, xk, xv, weight, bias, token_eta, ttt_lr_eta, ln_weight, ln_bias, grad_output,
+    mini_batch: int = 16, eps: float = 1e-6,
+) -> Dict[str, torch.Tensor]:
+    """Analytic backward of `ttt_linear_forward` for loss = <grad_output, output>.
+
+    Gradients w.r.t. the returned final state are taken as zero, as the
+    reference's backward does.  Returns dict with
+    grad_xq/xk/xv [B,H,T,F], grad_weight [B,H,F,F] (per batch element),
+    grad_bias [B,H,F], grad_ttt_lr_eta [B,H,T], grad_token_eta [T]
+    (written per stage at stage*CS+i, summed over B and H),
+    grad_ln_weight / grad_ln_bias [H,F] (summed over B).
+    """
+    B, H, T, F = xq.shape
+    cs = mini_batch
+    ns = T // cs
+    g_ = ln_weight.view(1, H, 1, F)
+    be_ = ln_bias.view(1, H, 1, F)
+    te = token_eta[:cs]
+    te_col = te.view(1, 1, cs, 1)
+    q_s, k_s, v_s, do_s = (_stage_views(t, cs) for t in (xq, xk, xv, grad_output))
+    lr_s = _stage_views(ttt_lr_eta, cs)
+    Ws, bs = _stage_states(xk, xv, weight, bias, te, lr_s, g_, be_, cs, eps)
+
+    dq = torch.empty_like(xq).reshape(B, H, ns, cs, F)
+    dk = torch.empty_like(dq)
+    dv = torch.empty_like(dq)
+    dlr = torch.empty_like(ttt_lr_eta).reshape(B, H, ns, cs)
+    dte = torch.zeros(T, dtype=xq.dtype)
+    dgam = torch.zeros(B, H, F, dtype=xq.dtype)
+    dbet = torch.zeros(B, H, F, dtype=xq.dtype)
+    dW = torch.zeros_like(weight)
+    db = torch.zeros_like(bias)
+
+    for s in reversed(range(ns)):
+        Q, Kk, V, lr, dO = q_s[:, :, s], k_s[:, :, s], v_s[:, :, s], lr_s[:, :, s], do_s[:, :, s]
+        W, b = Ws[s], bs[s]
+        # ---- recompute forward intermediates
+        z1 = Kk @ W + b.unsqueeze(-2)
+        xh, sig = ln_stats(z1, eps)
+        gy = g_ * xh + be_ - (V - Kk)
+        gxh = gy * g_
+        sum_gxh = gxh.sum(-1, keepdim=True)
+        sum_gxh_xh = (gxh * xh).sum(-1, keepdim=True)
+        G = (F * gxh - sum_gxh - xh * sum_gxh_xh) / (sig * F)
+        eta = _eta_matrices(te, lr)
+        attn = torch.tril(Q @ Kk.transpose(-1, -2))
+        M = eta * (1.0 + attn)
+        zbar = Q @ W + b.unsqueeze(-2) - M @ G
+        xhz, sigz = ln_stats(zbar, eps)
+        ell = te[cs - 1] * lr  # [B,H,CS]
+        ell_c = ell.unsqueeze(-1)
+        # ---- 1. LN backward of the output
+        dgam += (dO * xhz).sum(-2)
+        dbet += dO.sum(-2)
+        t = dO * g_
+        dzbar = (F * t - t.sum(-1, keepdim=True) - xhz * (t * xhz).sum(-1, keepdim=True)) / (sigz * F)
+        # ---- 2. direct W/b terms from Q@W + b
+        dW_acc = dW + Q.transpose(-1, -2) @ dzbar
+        db_acc = db + dzbar.sum(-2)
+        # ---- 3. eta / attention terms
+        P = dzbar @ G.transpose(-1, -2)
+        dM = -torch.tril(P)
+        dA = dM * eta
+        deta = dM * (1.0 + attn)
+        dq_inner = dzbar @ W.transpose(-1, -2) + dA @ Kk
+        dk_attn = dA.transpose(-1, -2) @ Q
+        # ---- 4. gradient reaching G
+        dG = -(M.transpose(-1, -2) @ dzbar) - (ell_c * Kk) @ dW - ell_c * db.unsqueeze(-2)
+        # ---- 5. last-eta-row terms of the state update
+        Gl = G @ dW.transpose(-1, -2)
+        dell = -((Gl * Kk).sum(-1) + (G * db.unsqueeze(-2)).sum(-1))  # [B,H,CS]
+        dk_upd = -ell_c * Gl
+        # ---- 6. eta factor gradients
+        dte_stage = (deta * lr.unsqueeze(-2)).sum(-1)  # [B,H,CS] (row i)
+        dte_stage[..., cs - 1] += (dell * lr).sum(-1)
+        dlr_stage = (deta * te_col).sum(-2) + dell * te[cs - 1]
+        dte[s * cs:(s + 1) * cs] = dte_stage.sum(dim=(0, 1))
+        dlr[:, :, s] = dlr_stage
+        # ---- 7. second derivative through the LN + L2 gradient
+        u = dG
+        v = -u / sig
+        s1 = v.sum(-1, keepdim=True)
+        s2 = (v * xh).sum(-1, keepdim=True)
+        dgxh = u / sig + s1 / F + xh * s2 / F
+        dy = g_ * dgxh
+        dgam += (gy * dgxh + dy * xh).sum(-2)
+        dbet += dy.sum(-2)
+        dxh = dy * g_ + gxh * s2 / F + v * sum_gxh_xh / F
+        S = (-(dxh * xh + u * G) / sig).sum(-1, keepdim=True)
+        dz1 = dxh / sig - dxh.sum(-1, keepdim=True) / (sig * F) + xh * S / F
+        dT = -g_ * dgxh
+        # ---- 8. assemble
+        dq[:, :, s] = dO + dq_inner
+        dv[:, :, s] = dT
+        dk[:, :, s] = -dT + dk_attn + dk_upd + dz1 @ W.transpose(-1, -2)
+        dW = dW_acc + Kk.transpose(-1, -2) @ dz1
+        db = db_acc + dz1.sum(-2)
+
+    return {
+        "grad_xq": dq.reshape(B, H, T, F),
+        "grad_xk": dk.reshape(B, H, T, F),
+        "grad_xv": dv.reshape(B, H, T, F),
+        "grad_weight": dW,
+        "grad_bias": db,
+        "grad_ttt_lr_eta": dlr.reshape(B, H, T),
+        "grad_token_eta": dte,
+        "grad_ln_weight": dgam.sum(0),
+        "grad_ln_bias": dbet.sum(0),
+    }
+
+
+def ttt_linear_backward_autograd(
+    xq, xk, xv, weight, bias, token_eta, ttt_lr_eta, ln_weight, ln_bias, grad_output,
+    mini_batch: int = 16, eps: float = 1e-6,
+) -> Dict[str, torch.Tensor]:
+    """Same contract as `ttt_linear_backward`, via torch autograd over the forward
+    restatement.  Used to cross-check the analytic backward.
+
+    `token_eta` is treated the way the layer builds it (one `[CS]` base vector
+    tiled to `[T]`, rust/layer/src/ttt.rs:253-256), so its gradient is reported
+    per stage position like the fused kernel writes it.
+    """
+    cs = mini_batch
+    T = xq.shape[2]
+    ns = T // cs
+    leaves = [t.detach().clone().requires_grad_(True)
+              for t in (xq, xk, xv, weight, bias, ttt_lr_eta, ln_weight, ln_bias)]
+    q, k, v, w, b, lr, g, be = leaves
+    te_full = token_eta[:cs].detach().repeat(ns).clone().requires_grad_(True)
+    B, H, _, F = q.shape
+    g_ = g.view(1, H, 1, F)
+    be_ = be.view(1, H, 1, F)
+    W, bb = w, b
+    outs = []
+    for s in range(ns):
+        sl = slice(s * cs, (s + 1) * cs)
+        Q, Kk, V, lrs, te = q[:, :, sl], k[:, :, sl], v[:, :, sl], lr[:, :, sl], te_full[sl]
+        z1 = Kk @ W + bb.unsqueeze(-2)
+        G = ln_l2_grad(z1, V - Kk, g_, be_, eps)
+        eta = torch.tril(te.view(1, 1, cs, 1) * lrs.unsqueeze(-2))
+        attn = torch.tril(Q @ Kk.transpose(-1, -2))
+        zbar = Q @ W + bb.unsqueeze(-2) - (eta * (1.0 + attn)) @ G
+        outs.append(Q + ln_fwd(zbar, g_, be_, eps))
+        last = eta[:, :, cs - 1, :].unsqueeze(-1)
+        W = W - (last * Kk).transpose(-1, -2) @ G
+        bb = bb - (last * G).sum(dim=-2)
+    out = torch.cat(outs, dim=2)
+    grads = torch.autograd.grad(out, leaves + [te_full], grad_outputs=grad_output)
+    names = ["grad_xq", "grad_xk", "grad_xv", "grad_weight", "grad_bias",
+             "grad_ttt_lr_eta", "grad_ln_weight", "grad_ln_bias", "grad_token_eta"]
+    return dict(zip(names, grads))
+
+
+# --------------------------------------------------------------------------
+# TTT-MLP forward (2-layer inner model, GELU tanh)
+# --------------------------------------------------------------------------
+
+def ttt_mlp_forward(
+    xq, xk, xv, w1, b1, w2, b2, token_eta, ttt_lr_eta, ln_weight, ln_bias,
+    mini_batch: int = 16, eps: float = 1e-6,
+) -> Dict[str, torch.Tensor]:
+    """Whole-sequence TTT-MLP forward scan.  w1 [B,H,F,E], b1 [B,H,E],
+    w2 [B,H,E,F], b2 [B,H,F]; differentiable w.r.t. every floating input."""
+    B, H, T, F = xq.shape
+    cs = mini_batch
+    if T % cs != 0:
+        raise ValueError(f"seq_len ({T}) must be divisible by mini_batch_len ({cs})")
+    ns = T // cs
+    g_ = ln_weight.view(1, H, 1, F)
+    be_ = ln_bias.view(1, H, 1, F)
+    W1, B1, W2, B2 = w1, b1, w2, b2
+    outs = []
+    for s in range(ns):
+        sl = slice(s * cs, (s + 1) * cs)
+        Q, Kk, V, lr = xq[:, :, sl], xk[:, :, sl], xv[:, :, sl], ttt_lr_eta[:, :, sl]
+        te = token_eta[:cs]
+        z1 = Kk @ W1 + B1.unsqueeze(-2)
+        x2 = gelu_tanh(z1)
+        z2 = x2 @ W2 + B2.unsqueeze(-2)
+        g2 = ln_l2_grad(z2, V - Kk, g_, be_, eps)
+        g1 = (g2 @ W2.transpose(-1, -2)) * gelu_tanh_grad(z1)
+        eta = torch.tril(te.view(1, 1, cs, 1) * lr.unsqueeze(-2))
+        attn1 = torch.tril(Q @ Kk.transpose(-1, -2))
+        z1b = Q @ W1 + B1.unsqueeze(-2) - (eta * (1.0 + attn1)) @ g1
+        x2b = gelu_tanh(z1b)
+        attn2 = torch.tril(x2b @ x2.transpose(-1, -2))
+        z2b = x2b @ W2 + B2.unsqueeze(-2) - (eta * (1.0 + attn2)) @ g2
+        outs.append(Q + ln_fwd(z2b, g_, be_, eps))
+        last = eta[:, :, cs - 1, :].unsqueeze(-1)
+        W1 = W1 - (last * Kk).transpose(-1, -2) @ g1
+        B1 = B1 - (last * g1).sum(dim=-2)
+        W2 = W2 - (last * x2).transpose(-1, -2) @ g2
+        B2 = B2 - (last * g2).sum(dim=-2)
+    return {"output": torch.cat(outs, dim=2), "w1": W1, "b1": B1, "w2": W2, "b2": B2}
+
+
+# --------------------------------------------------------------------------
+# Synthetic inputs (the benchmark / parity workload generator)
+# --------------------------------------------------------------------------
+
+def make_inputs(B: int, H: int, T: int, F: int = 64, mini_batch: int = 16, seed: int = 0,
+                dtype: torch.dtype = torch.float32, inner: str = "linear",
+                with_grad_output: bool = True) -> Dict[str, torch.Tensor]:
+    """Seeded synthetic operands with the benchmark's shapes and distributions.
+
+    One CPU generator, f32, drawn in this fixed order: XQ, XK, XV ~ N(0,1)/sqrt(F);
+    W0 ~ N(0,0.02) [H,F,F] repeated over B (MLP: W1 [H,F,4F], W2 [H,4F,F]); biases 0;
+    LN gamma = 1, beta = 0; logits ~ N(0,1) [B,H,T], lr = (1/F)*sigmoid(logits);
+    token_eta[t] = 1/((t mod CS)+1) (rust/layer/src/ttt.rs:106-110,
+    rust/core/src/test_utils.rs:133-142); upstream grad ~ N(0, 1e-2).
+    Values are rounded to `dtype` once and returned in `dtype`.
+    """
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    shp = (B, H, T, F)
+    scale = 1.0 / math.sqrt(F)
+    d: Dict[str, torch.Tensor] = {}
+    d["xq"] = torch.randn(shp, generator=g) * scale
+    d["xk"] = torch.randn(shp, generator=g) * scale
+    d["xv"] = torch.randn(shp, generator=g) * scale
+    if inner == "linear":
+        w0 = torch.randn(H, F, F, generator=g) * 0.02
+        d["weight"] = w0.unsqueeze(0).repeat(B, 1, 1, 1)
+        d["bias"] = torch.zeros(B, H, F)
+    else:
+        E = 4 * F
+        w1 = torch.randn(H, F, E, generator=g) * 0.02
+        w2 = torch.randn(H, E, F, generator=g) * 0.02
+        d["w1"] = w1.unsqueeze(0).repeat(B, 1, 1, 1)
+        d["b1"] = torch.zeros(B, H, E)
+        d["w2"] = w2.unsqueeze(0).repeat(B, 1, 1, 1)
+        d["b2"] = torch.zeros(B, H, F)
+    d["ln_weight"] = torch.ones(H, F)
+    d["ln_bias"] = torch.zeros(H, F)
+    logits = torch.randn(B, H, T, generator=g)
+    d["ttt_lr_eta"] = (1.0 / F) * torch.sigmoid(logits)
+    d["token_eta"] = 1.0 / ((torch.arange(T) % mini_batch) + 1).to(torch.float32)
+    if with_grad_output:
+        d["grad_output"] = torch.randn(shp, generator=g) * 1e-2
+    return {k: v.to(dtype).contiguous() for k, v in d.items()}
