@@ -1,0 +1,122 @@
+/*
+ * ttt_b200.h - C ABI of the B200 (sm_100a) fused TTT inner loop.
+ *
+ * This library replaces the *inside* of the reference's `fused-tile-multi` operator: the two host
+ * functions that build launch arguments and dispatch the device kernels,
+ *     forward_multi  / launch_tile_forward_multi   rust/fused/src/linear_fused_tile/forward/launch.rs:199-257,128-190
+ *     backward_multi / launch_tile_backward_multi  rust/fused/src/linear_fused_tile/backward/launch.rs:332-438,234-325
+ * which sit behind `TttTileMultiKernel: FusedKernel::{forward_launch, backward_launch}`
+ * (rust/fused/src/linear_fused_tile/launch.rs:117-208).  Everything above that boundary (tensor bundles,
+ * autodiff registration, the TTTInnerModel impl) is unchanged.
+ *
+ * Conventions
+ *  - Every tensor pointer is a DEVICE pointer to a contiguous row-major buffer, 16-byte aligned.
+ *  - The caller owns and allocates every buffer (as the reference's host wrappers do with `empty_like`);
+ *    the library allocates nothing and keeps no state between calls, so calls are re-entrant and may be
+ *    issued from any thread.  Calls enqueue work on `stream` and never synchronise.
+ *  - `dtype` selects the element type of all tensors marked T below: TTT_F32 or TTT_BF16.  Arithmetic is
+ *    float32 (bf16 tensor-core operands with float32 accumulation; three-plane split operands for TTT_F32).
+ *  - Return value: TTT_OK or an error code; ttt_b200_last_error() gives a thread-local message.  Where the
+ *    reference panics (unsupported tile config, seq_len not a multiple of the mini-batch:
+ *    linear_fused_tile/mod.rs:143, forward/launch.rs:209-213) these functions return an error and launch
+ *    nothing.
+ *  - `status`, when non-null, points to 4 zero-initialised device uint32 words; a kernel whose bounded wait on
+ *    a TMA completion barrier expires writes {TTT_ERR_TIMEOUT, where, block, stage} there and returns early.
+ */
+#ifndef TTT_B200_H
+#define TTT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TTT_B200_ABI_VERSION 1
+
+enum ttt_status {
+  TTT_OK = 0,
+  TTT_ERR_NULL = 1,        /* a required pointer is null */
+  TTT_ERR_SHAPE = 2,       /* non-positive dim, seq_len % mini_batch != 0, checkpoint_interval < 1 */
+  TTT_ERR_UNSUPPORTED = 3, /* (mini_batch, head_dim) other than (16, 64); unknown dtype */
+  TTT_ERR_ALIGN = 4,       /* a tensor base is not 16-byte aligned */
+  TTT_ERR_CUDA = 5,        /* a CUDA runtime/driver call failed (message in ttt_b200_last_error) */
+  TTT_ERR_TIMEOUT = 6,     /* written by kernels into `status`, never returned by a launch call */
+  TTT_ERR_WORKSPACE = 7    /* workspace too small */
+};
+
+enum ttt_dtype { TTT_F32 = 0, TTT_BF16 = 1 };
+
+/* Problem description.  Mirrors what the reference derives from tensor shapes plus `FusedTttConfig`
+ * {mini_batch_len, head_dim, epsilon, checkpoint_interval} (rust/fused/src/lib.rs:285-328). */
+typedef struct ttt_dims {
+  int32_t batch;               /* B */
+  int32_t heads;               /* H */
+  int32_t seq_len;             /* T, multiple of mini_batch */
+  int32_t head_dim;            /* F (64) */
+  int32_t mini_batch;          /* CS (16) */
+  int32_t checkpoint_interval; /* K >= 1, in stages */
+  float epsilon;               /* LayerNorm epsilon */
+  int32_t dtype;               /* enum ttt_dtype */
+} ttt_dims;
+
+int ttt_b200_abi_version(void);
+const char* ttt_b200_status_string(int status);
+const char* ttt_b200_last_error(void);
+
+/* Number of checkpoints per (batch, head) stream: ceil((T / CS) / K)  (forward/launch.rs:221-223). */
+int64_t ttt_linear_num_checkpoints(const ttt_dims* d);
+/* Bytes of the two checkpoint buffers.  They are opaque saved state handed from forward to backward; this
+ * library keeps them in float32 whatever `dtype` is: [B*H*NCK, F, F] and [B*H*NCK, F]. */
+size_t ttt_linear_weight_ckpt_bytes(const ttt_dims* d);
+size_t ttt_linear_bias_ckpt_bytes(const ttt_dims* d);
+
+/* Forward of the whole sequence.  Replaces launch_tile_forward_multi (forward/launch.rs:128-190).
+ *   xq, xk, xv      T [B,H,T,F]
+ *   weight          T [B,H,F,F]   initial state W (per batch element), W[k][n]: z = x @ W
+ *   bias            T [B,H,F]
+ *   token_eta       T [T]         only entries [0, CS) are read, in every stage (forward/kernel.rs:152-165)
+ *   ttt_lr_eta      T [B,H,T]
+ *   ln_weight/bias  T [H,F]
+ *   output          T [B,H,T,F]   (out)
+ *   weight_out      T [B,H,F,F]   (out) final state
+ *   bias_out        T [B,H,F]     (out)
+ *   weight_ckpt, bias_ckpt        (out) see ttt_linear_*_ckpt_bytes
+ */
+int ttt_linear_forward(const ttt_dims* d, const void* xq, const void* xk, const void* xv, const void* weight,
+                       const void* bias, const void* token_eta, const void* ttt_lr_eta, const void* ln_weight,
+                       const void* ln_bias, void* output, void* weight_out, void* bias_out, void* weight_ckpt,
+                       void* bias_ckpt, void* status, void* stream);
+
+/* Scratch the backward needs (per-stream partial sums that a second, deterministic pass reduces). */
+size_t ttt_linear_backward_workspace_bytes(const ttt_dims* d);
+
+/* Backward of the whole sequence for upstream gradient `grad_output` of `output` only (gradients of the
+ * returned final state are taken as zero, as launch.rs:188-194 does).  Replaces launch_tile_backward_multi
+ * (backward/launch.rs:234-325).
+ *   saved inputs as in forward, plus weight_ckpt / bias_ckpt written by ttt_linear_forward
+ *   grad_output     T [B,H,T,F]
+ *   grad_xq/xk/xv   T [B,H,T,F]   (out)
+ *   grad_weight     T [B,H,F,F]   (out) per batch element (backward/launch.rs:355-362)
+ *   grad_bias       T [B,H,F]     (out)
+ *   grad_ttt_lr_eta T [B,H,T]     (out)
+ *   grad_token_eta  float32 [T]   (out) stage s writes positions s*CS+i, summed over B and H
+ *   grad_ln_weight, grad_ln_bias  float32 [H,F] (out) summed over B   (backward/launch.rs:368-385)
+ *   outer_grad_packed  float32 [H*F*F + 3*H*F + CS] or null: {dW0 [H,F,F], db0 [H,F], d ln_weight, d ln_bias,
+ *                   d token_eta folded to [CS]} summed over this call's batch: one buffer for one all-reduce
+ *   workspace       at least ttt_linear_backward_workspace_bytes(d) bytes
+ * The three float32 outputs are written (not accumulated into); the caller need not zero them.
+ */
+int ttt_linear_backward(const ttt_dims* d, const void* xq, const void* xk, const void* xv, const void* weight,
+                        const void* bias, const void* token_eta, const void* ttt_lr_eta, const void* ln_weight,
+                        const void* ln_bias, const void* weight_ckpt, const void* bias_ckpt,
+                        const void* grad_output, void* grad_xq, void* grad_xk, void* grad_xv, void* grad_weight,
+                        void* grad_bias, void* grad_ttt_lr_eta, float* grad_token_eta, float* grad_ln_weight,
+                        float* grad_ln_bias, float* outer_grad_packed, void* workspace, size_t workspace_bytes,
+                        void* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TTT_B200_H */

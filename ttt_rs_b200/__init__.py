@@ -1,0 +1,17 @@
+"""B200 (sm_100a) fused TTT inner loop behind the reference's `fused-tile-multi` operator interface."""
+
+from ._lib import TttDims, TttError, load as load_library  # noqa: F401
+from .fused import (  # noqa: F401
+    FusedTileMultiTTTLinear,
+    FusedTttConfig,
+    Qkv,
+    TTTInputsInner,
+    TTTLinear,
+    TTTLinearState,
+    TttInputs,
+    TttOutputs,
+    TttSavedStateMulti,
+    TttTileMultiKernel,
+    fused_ttt_tile_forward_multi,
+    packed_outer_grad_len,
+)

@@ -1,0 +1,282 @@
+// C ABI of the fused TTT inner loop: argument validation, TMA descriptor set-up and kernel launches.
+// Signatures and their reference counterparts are documented in include/ttt_b200.h.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/ttt_b200.h"
+#include "ttt_kernels.h"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode_fn() {
+  static EncodeFn fn = nullptr;  // benign race: every thread resolves the same pointer
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(p);
+  }
+  return fn;
+}
+
+// 2-D view [rows, 64] of a [B,H,T,64] tensor, box = one 16-token tile (or half of it for float32),
+// 128-byte swizzle so that ldmatrix / element-wise shared-memory reads are bank-conflict free.
+int make_tile_map(CUtensorMap* m, const void* base, int64_t rows, int dtype) {
+  EncodeFn enc = get_encode_fn();
+  if (enc == nullptr) return fail(TTT_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  const bool bf = dtype == TTT_BF16;
+  const cuuint64_t dims[2] = {64, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)(64 * (bf ? 2 : 4))};
+  const cuuint32_t box[2] = {(cuuint32_t)(bf ? 64 : 32), 16};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(TTT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return TTT_OK;
+}
+
+int check_dims(const ttt_dims* d) {
+  if (d == nullptr) return fail(TTT_ERR_NULL, "dims is null");
+  if (d->batch <= 0 || d->heads <= 0 || d->seq_len <= 0 || d->head_dim <= 0 || d->mini_batch <= 0)
+    return fail(TTT_ERR_SHAPE, "batch, heads, seq_len, head_dim and mini_batch must be positive");
+  if (d->checkpoint_interval < 1) return fail(TTT_ERR_SHAPE, "checkpoint_interval must be >= 1");
+  if (d->dtype != TTT_F32 && d->dtype != TTT_BF16) return fail(TTT_ERR_UNSUPPORTED, "unknown dtype %d", d->dtype);
+  if (d->mini_batch != 16 || d->head_dim != 64)
+    return fail(TTT_ERR_UNSUPPORTED, "Unsupported tile config: mini_batch_len=%d, head_dim=%d (supported: 16x64)",
+                d->mini_batch, d->head_dim);
+  if (d->seq_len % d->mini_batch != 0)
+    return fail(TTT_ERR_SHAPE, "seq_len (%d) must be divisible by mini_batch_len (%d)", d->seq_len, d->mini_batch);
+  if ((int64_t)d->batch * d->heads * d->seq_len >= (int64_t)1 << 31)
+    return fail(TTT_ERR_SHAPE, "batch*heads*seq_len must be below 2^31");
+  if (!(d->epsilon >= 0.f)) return fail(TTT_ERR_SHAPE, "epsilon must be >= 0");
+  return TTT_OK;
+}
+
+struct NamedPtr {
+  const char* name;
+  const void* p;
+};
+
+int check_ptrs(const NamedPtr* ptrs, int n) {
+  for (int i = 0; i < n; ++i) {
+    if (ptrs[i].p == nullptr) return fail(TTT_ERR_NULL, "%s is null", ptrs[i].name);
+    if ((reinterpret_cast<uintptr_t>(ptrs[i].p) & 15u) != 0)
+      return fail(TTT_ERR_ALIGN, "%s is not 16-byte aligned", ptrs[i].name);
+  }
+  return TTT_OK;
+}
+
+int64_t num_ckpt(const ttt_dims* d) {
+  const int64_t ns = d->seq_len / d->mini_batch;
+  return (ns + d->checkpoint_interval - 1) / d->checkpoint_interval;
+}
+
+// workspace layout of the backward (float32 words)
+struct WsLayout {
+  size_t off_ln, off_te, off_w, total_bytes;
+};
+WsLayout ws_layout(const ttt_dims* d) {
+  const size_t streams = (size_t)d->batch * d->heads;
+  WsLayout w;
+  w.off_ln = 0;
+  w.off_te = w.off_ln + streams * 2 * 64;
+  w.off_w = w.off_te + streams * (size_t)d->seq_len;
+  const size_t words = w.off_w + streams * (64 * 64 + 64);
+  w.total_bytes = words * sizeof(float);
+  return w;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ttt_b200_abi_version(void) { return TTT_B200_ABI_VERSION; }
+
+const char* ttt_b200_status_string(int s) {
+  switch (s) {
+    case TTT_OK: return "ok";
+    case TTT_ERR_NULL: return "null pointer";
+    case TTT_ERR_SHAPE: return "bad shape";
+    case TTT_ERR_UNSUPPORTED: return "unsupported configuration";
+    case TTT_ERR_ALIGN: return "misaligned pointer";
+    case TTT_ERR_CUDA: return "CUDA error";
+    case TTT_ERR_TIMEOUT: return "device-side wait timed out";
+    case TTT_ERR_WORKSPACE: return "workspace too small";
+    default: return "unknown status";
+  }
+}
+
+const char* ttt_b200_last_error(void) { return g_err; }
+
+int64_t ttt_linear_num_checkpoints(const ttt_dims* d) {
+  if (check_dims(d) != TTT_OK) return -1;
+  return num_ckpt(d);
+}
+size_t ttt_linear_weight_ckpt_bytes(const ttt_dims* d) {
+  if (check_dims(d) != TTT_OK) return 0;
+  return (size_t)d->batch * d->heads * num_ckpt(d) * 64 * 64 * sizeof(float);
+}
+size_t ttt_linear_bias_ckpt_bytes(const ttt_dims* d) {
+  if (check_dims(d) != TTT_OK) return 0;
+  return (size_t)d->batch * d->heads * num_ckpt(d) * 64 * sizeof(float);
+}
+
+int ttt_linear_forward(const ttt_dims* d, const void* xq, const void* xk, const void* xv, const void* weight,
+                       const void* bias, const void* token_eta, const void* ttt_lr_eta, const void* ln_weight,
+                       const void* ln_bias, void* output, void* weight_out, void* bias_out, void* weight_ckpt,
+                       void* bias_ckpt, void* status, void* stream) {
+  int rc = check_dims(d);
+  if (rc != TTT_OK) return rc;
+  const NamedPtr ptrs[] = {{"xq", xq},           {"xk", xk},
+                           {"xv", xv},           {"weight", weight},
+                           {"bias", bias},       {"token_eta", token_eta},
+                           {"ttt_lr_eta", ttt_lr_eta}, {"ln_weight", ln_weight},
+                           {"ln_bias", ln_bias}, {"output", output},
+                           {"weight_out", weight_out}, {"bias_out", bias_out},
+                           {"weight_ckpt", weight_ckpt}, {"bias_ckpt", bias_ckpt}};
+  rc = check_ptrs(ptrs, sizeof(ptrs) / sizeof(ptrs[0]));
+  if (rc != TTT_OK) return rc;
+  if (status != nullptr && (reinterpret_cast<uintptr_t>(status) & 3u) != 0)
+    return fail(TTT_ERR_ALIGN, "status is not 4-byte aligned");
+
+  const int64_t rows = (int64_t)d->batch * d->heads * d->seq_len;
+  CUtensorMap maps[4];
+  const void* bases[4] = {xq, xk, xv, output};
+  for (int i = 0; i < 4; ++i) {
+    rc = make_tile_map(&maps[i], bases[i], rows, d->dtype);
+    if (rc != TTT_OK) return rc;
+  }
+  ttt::LinFwdParams p;
+  p.w0 = weight;
+  p.b0 = bias;
+  p.token_eta = token_eta;
+  p.lr = ttt_lr_eta;
+  p.ln_g = ln_weight;
+  p.ln_b = ln_bias;
+  p.w_out = weight_out;
+  p.b_out = bias_out;
+  p.w_ckpt = static_cast<float*>(weight_ckpt);
+  p.b_ckpt = static_cast<float*>(bias_ckpt);
+  p.status = static_cast<uint32_t*>(status);
+  p.H = d->heads;
+  p.T = d->seq_len;
+  p.NS = d->seq_len / d->mini_batch;
+  p.K = d->checkpoint_interval;
+  p.NCK = (int)num_ckpt(d);
+  p.eps = d->epsilon;
+  cudaError_t e = ttt::launch_linear_fwd(d->dtype, maps, p, d->batch * d->heads, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(e));
+  return TTT_OK;
+}
+
+size_t ttt_linear_backward_workspace_bytes(const ttt_dims* d) {
+  if (check_dims(d) != TTT_OK) return 0;
+  return ws_layout(d).total_bytes;
+}
+
+int ttt_linear_backward(const ttt_dims* d, const void* xq, const void* xk, const void* xv, const void* weight,
+                        const void* bias, const void* token_eta, const void* ttt_lr_eta, const void* ln_weight,
+                        const void* ln_bias, const void* weight_ckpt, const void* bias_ckpt,
+                        const void* grad_output, void* grad_xq, void* grad_xk, void* grad_xv, void* grad_weight,
+                        void* grad_bias, void* grad_ttt_lr_eta, float* grad_token_eta, float* grad_ln_weight,
+                        float* grad_ln_bias, float* outer_grad_packed, void* workspace, size_t workspace_bytes,
+                        void* status, void* stream) {
+  int rc = check_dims(d);
+  if (rc != TTT_OK) return rc;
+  const NamedPtr ptrs[] = {{"xq", xq},
+                           {"xk", xk},
+                           {"xv", xv},
+                           {"weight", weight},
+                           {"bias", bias},
+                           {"token_eta", token_eta},
+                           {"ttt_lr_eta", ttt_lr_eta},
+                           {"ln_weight", ln_weight},
+                           {"ln_bias", ln_bias},
+                           {"weight_ckpt", weight_ckpt},
+                           {"bias_ckpt", bias_ckpt},
+                           {"grad_output", grad_output},
+                           {"grad_xq", grad_xq},
+                           {"grad_xk", grad_xk},
+                           {"grad_xv", grad_xv},
+                           {"grad_weight", grad_weight},
+                           {"grad_bias", grad_bias},
+                           {"grad_ttt_lr_eta", grad_ttt_lr_eta},
+                           {"grad_token_eta", grad_token_eta},
+                           {"grad_ln_weight", grad_ln_weight},
+                           {"grad_ln_bias", grad_ln_bias},
+                           {"workspace", workspace}};
+  rc = check_ptrs(ptrs, sizeof(ptrs) / sizeof(ptrs[0]));
+  if (rc != TTT_OK) return rc;
+  if (outer_grad_packed != nullptr && (reinterpret_cast<uintptr_t>(outer_grad_packed) & 15u) != 0)
+    return fail(TTT_ERR_ALIGN, "outer_grad_packed is not 16-byte aligned");
+  const WsLayout wl = ws_layout(d);
+  if (workspace_bytes < wl.total_bytes)
+    return fail(TTT_ERR_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes, wl.total_bytes);
+
+  const int64_t rows = (int64_t)d->batch * d->heads * d->seq_len;
+  CUtensorMap maps[7];
+  const void* bases[7] = {xq, xk, xv, grad_output, grad_xq, grad_xk, grad_xv};
+  for (int i = 0; i < 7; ++i) {
+    rc = make_tile_map(&maps[i], bases[i], rows, d->dtype);
+    if (rc != TTT_OK) return rc;
+  }
+  float* ws = static_cast<float*>(workspace);
+  ttt::LinBwdParams p;
+  p.w0 = weight;
+  p.b0 = bias;
+  p.token_eta = token_eta;
+  p.lr = ttt_lr_eta;
+  p.ln_g = ln_weight;
+  p.ln_b = ln_bias;
+  p.w_ckpt = static_cast<const float*>(weight_ckpt);
+  p.b_ckpt = static_cast<const float*>(bias_ckpt);
+  p.d_w = grad_weight;
+  p.d_b = grad_bias;
+  p.d_lr = grad_ttt_lr_eta;
+  p.part_ln = ws + wl.off_ln;
+  p.part_te = ws + wl.off_te;
+  p.part_w = ws + wl.off_w;
+  p.status = static_cast<uint32_t*>(status);
+  p.H = d->heads;
+  p.T = d->seq_len;
+  p.NS = d->seq_len / d->mini_batch;
+  p.K = d->checkpoint_interval;
+  p.NCK = (int)num_ckpt(d);
+  p.eps = d->epsilon;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = ttt::launch_linear_bwd(d->dtype, maps, p, d->batch * d->heads, st);
+  if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "backward launch failed: %s", cudaGetErrorString(e));
+  ttt::ReduceParams r;
+  r.part_ln = p.part_ln;
+  r.part_te = p.part_te;
+  r.part_w = p.part_w;
+  r.d_token_eta = grad_token_eta;
+  r.d_ln_g = grad_ln_weight;
+  r.d_ln_b = grad_ln_bias;
+  r.packed = outer_grad_packed;
+  r.B = d->batch;
+  r.H = d->heads;
+  r.T = d->seq_len;
+  e = ttt::launch_linear_bwd_reduce(r, st);
+  if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "backward reduction launch failed: %s", cudaGetErrorString(e));
+  return TTT_OK;
+}
+
+}  // extern "C"

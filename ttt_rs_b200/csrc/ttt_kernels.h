@@ -1,0 +1,65 @@
+// Internal interface between the C-ABI layer (ttt_abi.cu) and the kernel translation units.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ttt {
+
+struct LinFwdParams {
+  const void* w0;         // [B,H,F,F] element type T
+  const void* b0;         // [B,H,F]
+  const void* token_eta;  // [T], first 16 entries read
+  const void* lr;         // [B,H,T]
+  const void* ln_g;       // [H,F]
+  const void* ln_b;       // [H,F]
+  void* w_out;            // [B,H,F,F]
+  void* b_out;            // [B,H,F]
+  float* w_ckpt;          // [B*H*NCK, F, F] float32
+  float* b_ckpt;          // [B*H*NCK, F]    float32
+  uint32_t* status;       // device uint32[4] or null
+  int H, T, NS, K, NCK;
+  float eps;
+};
+
+struct LinBwdParams {
+  const void* w0;
+  const void* b0;
+  const void* token_eta;
+  const void* lr;
+  const void* ln_g;
+  const void* ln_b;
+  const float* w_ckpt;
+  const float* b_ckpt;
+  void* d_w;        // [B,H,F,F] element type T (per batch element), nullable
+  void* d_b;        // [B,H,F], nullable
+  void* d_lr;       // [B,H,T]
+  float* part_ln;   // workspace: [B*H][2][F] per-stream partial LN gradients (weight, bias)
+  float* part_te;   // workspace: [B*H][T] per-stream token_eta gradient terms
+  float* part_w;    // workspace: [B*H][F*F + F] float32 dW, db per stream (for the packed reduction)
+  uint32_t* status;
+  int H, T, NS, K, NCK;
+  float eps;
+};
+
+struct ReduceParams {
+  const float* part_ln;
+  const float* part_te;
+  const float* part_w;
+  float* d_token_eta;  // [T] f32
+  float* d_ln_g;       // [H,F] f32
+  float* d_ln_b;       // [H,F] f32
+  float* packed;       // nullable: [H*F*F + 3*H*F + CS] f32
+  int B, H, T;
+};
+
+// dtype: 0 = float32, 1 = bfloat16.  maps: q, k, v, out.
+cudaError_t launch_linear_fwd(int dtype, const CUtensorMap* maps, const LinFwdParams& p, int nstreams,
+                              cudaStream_t st);
+// maps: q, k, v, d_out, d_q, d_k, d_v.
+cudaError_t launch_linear_bwd(int dtype, const CUtensorMap* maps, const LinBwdParams& p, int nstreams,
+                              cudaStream_t st);
+cudaError_t launch_linear_bwd_reduce(const ReduceParams& p, cudaStream_t st);
+
+}  // namespace ttt

@@ -1,0 +1,405 @@
+// Fused TTT-Linear forward scan for sm_100a: one 4-warp CTA per (batch, head) stream walks all mini-batches.
+//
+// What it computes is the reference's multi-stage forward kernel
+// (rust/fused/src/linear_fused_tile/forward/kernel.rs:92-176, stage body forward/stage.rs:29-208, semantics
+// rust/core/src/linear.rs:91-149): per 16-token stage
+//     Z1 = K W + b;  G = d/dZ1 of 0.5|LN(Z1) - (V-K)|^2;  M = eta o (1 + tril(Q K^T)),  eta[i,j] = te[i] lr[j] (j<=i)
+//     out = Q + LN(Q W + b - M G);   W -= (te[15] lr o K)^T G;   b -= sum_j te[15] lr[j] G[j,:]
+// with (W, b) checkpointed before the update of every K-th stage.
+//
+// How it is laid out here (none of this follows the reference's design):
+//   * The state is held transposed, W^T[n][k], as float32 mma accumulators: warp w owns output features
+//     n in [16w,16w+16) and all 64 k (32 registers per thread).  In that layout the same registers are,
+//     after one cvt to bf16, the B operand of K.W / Q.W, and the rank-16 update W^T += (-te15 lr G)^T K
+//     accumulates straight into them, so W never leaves registers between stages.
+//   * Q/K/V tiles of the next three stages are in flight as TMA loads (128B swizzle) on mbarriers.
+//   * Row statistics for the two LayerNorms are warp-shuffle reduced and exchanged across the 4 warps through
+//     512 bytes of shared memory; G reaches the tensor cores as an A/B operand through movmatrix.
+//   * Output tiles leave through a double-buffered staging tile and a TMA store.
+#include "ttt_kernels.h"
+#include "ttt_tiles.cuh"
+
+namespace ttt {
+
+constexpr int FWD_NST = 3;  // TMA pipeline depth (stages in flight)
+
+template <typename T>
+struct FwdSmem {
+  using TF = TileFmt<T>;
+  static constexpr uint32_t SLOT = 3 * TF::BYTES;                  // q, k, v
+  static constexpr uint32_t OFF_OUT = FWD_NST * SLOT;              // 2 staging tiles (raw format)
+  static constexpr uint32_t OFF_LR = OFF_OUT + 2 * TF::RAW_BYTES;  // FWD_NST x 64 bytes
+  static constexpr uint32_t OFF_XCH = OFF_LR + FWD_NST * 64;       // 2 x XchBuf
+  static constexpr uint32_t OFF_BAR = OFF_XCH + 2 * sizeof(XchBuf);
+  static constexpr uint32_t TOTAL = OFF_BAR + FWD_NST * 8;
+  static constexpr uint32_t DYN_BYTES = TOTAL + 1024;  // slack for manual 1024-byte alignment
+};
+
+__device__ __forceinline__ void report_timeout(uint32_t* status, uint32_t where, uint32_t stage) {
+  if (status != nullptr && atomicCAS(status, 0u, (uint32_t)KST_TIMEOUT) == 0u) {
+    status[1] = where;
+    status[2] = blockIdx.x;
+    status[3] = stage;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
+    ttt_linear_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                          const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                          const LinFwdParams p) {
+  using TF = TileFmt<T>;
+  using SM = FwdSmem<T>;
+  constexpr int NP = TF::NP;
+  constexpr bool TWO_PASS = (sizeof(T) == 4);
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_u32 = smem_u32(smem_raw);
+  const uint32_t base = (raw_u32 + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - raw_u32);
+  XchBuf* xch = reinterpret_cast<XchBuf*>(gbase + SM::OFF_XCH);
+  const uint32_t bar0 = base + SM::OFF_BAR;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int nb = warp * 16;
+  const int stream = blockIdx.x;
+  const int head = stream % p.H;
+  const int NS = p.NS;
+  const int row_base = stream * p.T;  // first row of this stream in the [B*H*T, 64] view
+
+  if (tid == 0) {
+    prefetch_tmap(&tm_q);
+    prefetch_tmap(&tm_k);
+    prefetch_tmap(&tm_v);
+    prefetch_tmap(&tm_o);
+    for (int i = 0; i < FWD_NST; ++i) mbar_init(bar0 + 8 * i, 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  auto issue_loads = [&](int s) {
+    const int slot = s % FWD_NST;
+    const uint32_t bar = bar0 + 8 * slot;
+    const uint32_t tq = base + slot * SM::SLOT;
+    mbar_expect_tx(bar, 3 * TF::RAW_BYTES + CS * TF::ELT);
+    const int r0 = row_base + s * CS;
+    tma_load_tile<T>(tq, &tm_q, r0, bar);
+    tma_load_tile<T>(tq + TF::BYTES, &tm_k, r0, bar);
+    tma_load_tile<T>(tq + 2 * TF::BYTES, &tm_v, r0, bar);
+    bulk_load_1d(base + SM::OFF_LR + slot * 64,
+                 static_cast<const uint8_t*>(p.lr) + (size_t)(row_base + s * CS) * TF::ELT, CS * TF::ELT, bar);
+  };
+  if (tid == 0) {
+    for (int s = 0; s < FWD_NST && s < NS; ++s) issue_loads(s);
+  }
+
+  // ---- per-thread constants: 4 owned columns c(nt,e) = nb + 8nt + 2t + e, rows g and g+8
+  float gam[4], bet[4], bias[4];
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int c = nb + 8 * nt + 2 * t + e;
+      gam[2 * nt + e] = ld_as_float<T>(p.ln_g, (size_t)head * HD + c);
+      bet[2 * nt + e] = ld_as_float<T>(p.ln_b, (size_t)head * HD + c);
+      bias[2 * nt + e] = ld_as_float<T>(p.b0, (size_t)stream * HD + c);
+    }
+  const float te_row[2] = {ld_as_float<T>(p.token_eta, g), ld_as_float<T>(p.token_eta, g + 8)};
+  const float te15 = ld_as_float<T>(p.token_eta, CS - 1);
+
+  // ---- state W^T[n][k], n in {nb+g, nb+g+8}: wt[kt][2*rn + e] = W[k = 8kt+2t+e][n = nb+g+8rn]
+  float wt[8][4];
+#pragma unroll
+  for (int kt = 0; kt < 8; ++kt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int k = 8 * kt + 2 * t + (i & 1), n = nb + g + 8 * (i >> 1);
+      wt[kt][i] = ld_as_float<T>(p.w0, (size_t)stream * HD * HD + k * HD + n);
+    }
+
+  int xsel = 0;
+  bool failed = false;
+
+  for (int s = 0; s < NS; ++s) {
+    const int slot = s % FWD_NST;
+    const uint32_t tq = base + slot * SM::SLOT, tk = tq + TF::BYTES, tv = tk + TF::BYTES;
+    const uint32_t pq = tq + TF::PLANE_OFF, pk = tk + TF::PLANE_OFF;
+    int fail = mbar_wait_bounded(bar0 + 8 * slot, (s / FWD_NST) & 1) ? 0 : 1;
+    if constexpr (NP == 3) {
+      if (!fail) {
+        split_tile_f32(tq, tid);
+        split_tile_f32(tk, tid);
+      }
+      fail = __syncthreads_or(fail);
+      if (fail) {
+        failed = true;
+        if (tid == 0) report_timeout(p.status, 1, s);
+        break;
+      }
+    }
+
+    // ---- checkpoint (state before this stage's update)
+    if (s % p.K == 0) {
+      const size_t ck = (size_t)stream * p.NCK + s / p.K;
+      float* wc = p.w_ckpt + ck * HD * HD;
+#pragma unroll
+      for (int kt = 0; kt < 8; ++kt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) wc[(8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1)] = wt[kt][i];
+      if (g == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) p.b_ckpt[ck * HD + nb + 8 * (j >> 1) + 2 * t + (j & 1)] = bias[j];
+      }
+    }
+
+    const float lr_row[2] = {ld_as_float<T>(gbase + SM::OFF_LR + slot * 64, g),
+                             ld_as_float<T>(gbase + SM::OFF_LR + slot * 64, g + 8)};
+
+    // ---- Z1 = K W + b, Zq = Q W + b (columns nb..nb+15), Attn = Q K^T (full 16x16, every warp)
+    float z1[2][4], zq[2][4], at[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        z1[nt][i] = bias[2 * nt + (i & 1)];
+        zq[nt][i] = bias[2 * nt + (i & 1)];
+        at[nt][i] = 0.f;
+      }
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      Pk<NP> bw[2][2];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        bw[nt][0] = split_pack<NP>(wt[2 * ks][2 * nt], wt[2 * ks][2 * nt + 1]);
+        bw[nt][1] = split_pack<NP>(wt[2 * ks + 1][2 * nt], wt[2 * ks + 1][2 * nt + 1]);
+      }
+      Pk<NP> ak[4], aq[4], bk[4];
+      ldsm_np<NP>(ak, pk + lane_off_A(lane, 16 * ks), TILE_BF16_BYTES, false);
+      ldsm_np<NP>(aq, pq + lane_off_A(lane, 16 * ks), TILE_BF16_BYTES, false);
+      ldsm_np<NP>(bk, pk + lane_off_B_nk(lane, 16 * ks), TILE_BF16_BYTES, false);
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        mma_np<NP>(z1[nt], ak, bw[nt]);
+        mma_np<NP>(zq[nt], aq, bw[nt]);
+      }
+      const Pk<NP> bj0[2] = {bk[0], bk[1]}, bj1[2] = {bk[2], bk[3]};
+      mma_np<NP>(at[0], aq, bj0);
+      mma_np<NP>(at[1], aq, bj1);
+    }
+
+    // ---- LN statistics of Z1 (rows g, g+8)
+    float mean[2], rstd[2];
+    auto row_stats = [&](const float (&z)[2][4], int& fl) {
+      float s1[2], s2[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        s1[r] = (z[0][2 * r] + z[0][2 * r + 1]) + (z[1][2 * r] + z[1][2 * r + 1]);
+        s2[r] = 0.f;
+        if constexpr (!TWO_PASS) {
+          s2[r] = (z[0][2 * r] * z[0][2 * r] + z[0][2 * r + 1] * z[0][2 * r + 1]) +
+                  (z[1][2 * r] * z[1][2 * r] + z[1][2 * r + 1] * z[1][2 * r + 1]);
+        }
+        s1[r] = quad_sum(s1[r]);
+        if constexpr (!TWO_PASS) s2[r] = quad_sum(s2[r]);
+      }
+      XchBuf* xb = &xch[xsel];
+      xsel ^= 1;
+      if (t == 0) {
+        xch_put(xb, g, warp, s1[0], s2[0]);
+        xch_put(xb, g + 8, warp, s1[1], s2[1]);
+      }
+      fl = __syncthreads_or(fl);
+      const float2 a0 = xch_get(xb, g), a1 = xch_get(xb, g + 8);
+      mean[0] = a0.x * (1.f / HD);
+      mean[1] = a1.x * (1.f / HD);
+      float var[2];
+      if constexpr (!TWO_PASS) {
+        var[0] = fmaxf(a0.y * (1.f / HD) - mean[0] * mean[0], 0.f);
+        var[1] = fmaxf(a1.y * (1.f / HD) - mean[1] * mean[1], 0.f);
+        rstd[0] = rsqrtf(var[0] + p.eps);
+        rstd[1] = rsqrtf(var[1] + p.eps);
+      } else {
+        float q2[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          float acc = 0.f;
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const float d = z[nt][2 * r + e] - mean[r];
+              acc += d * d;
+            }
+          q2[r] = quad_sum(acc);
+        }
+        XchBuf* xb2 = &xch[xsel];
+        xsel ^= 1;
+        if (t == 0) {
+          xch_put(xb2, g, warp, q2[0], 0.f);
+          xch_put(xb2, g + 8, warp, q2[1], 0.f);
+        }
+        __syncthreads();
+        var[0] = xch_get(xb2, g).x * (1.f / HD);
+        var[1] = xch_get(xb2, g + 8).x * (1.f / HD);
+        rstd[0] = 1.0f / sqrtf(var[0] + p.eps);
+        rstd[1] = 1.0f / sqrtf(var[1] + p.eps);
+      }
+    };
+
+    row_stats(z1, fail);
+    if (fail) {
+      failed = true;
+      if (tid == 0) report_timeout(p.status, 2, s);
+      break;
+    }
+
+    // ---- G = dL/dZ1 ; gp = lr[row] * G
+    float xh[2][4], gx[2][4];
+    {
+      float sa[2] = {0.f, 0.f}, sb[2] = {0.f, 0.f};
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const int row = g + 8 * r, col = nb + 8 * nt + 2 * t;
+          const float2 kv = ld_pair<T>(tk, row, col), vv = ld_pair<T>(tv, row, col);
+          const float tg[2] = {vv.x - kv.x, vv.y - kv.y};
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int i = 2 * r + e, j = 2 * nt + e;
+            const float x = (z1[nt][i] - mean[r]) * rstd[r];
+            const float gy = gam[j] * x + bet[j] - tg[e];
+            const float gg = gy * gam[j];
+            xh[nt][i] = x;
+            gx[nt][i] = gg;
+            sa[r] += gg;
+            sb[r] += gg * x;
+          }
+        }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        sa[r] = quad_sum(sa[r]);
+        sb[r] = quad_sum(sb[r]);
+      }
+      XchBuf* xb = &xch[xsel];
+      xsel ^= 1;
+      if (t == 0) {
+        xch_put(xb, g, warp, sa[0], sb[0]);
+        xch_put(xb, g + 8, warp, sa[1], sb[1]);
+      }
+      __syncthreads();
+      const float2 a0 = xch_get(xb, g), a1 = xch_get(xb, g + 8);
+      const float A[2] = {a0.x * (1.f / HD), a1.x * (1.f / HD)}, Bv[2] = {a0.y * (1.f / HD), a1.y * (1.f / HD)};
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int r = i >> 1;
+          // reuse gx as G' = lr * G
+          gx[nt][i] = (gx[nt][i] - A[r] - xh[nt][i] * Bv[r]) * (rstd[r] * lr_row[r]);
+        }
+    }
+
+    // ---- G' as tensor-core operands (transposed through movmatrix): plain for M.G, scaled by -te15 for the update
+    Pk<NP> gt[2][2], gu[2][2];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        gt[nt][r] = movm_t_np<NP>(split_pack<NP>(gx[nt][2 * r], gx[nt][2 * r + 1]));
+        gu[nt][r] = movm_t_np<NP>(split_pack<NP>(-te15 * gx[nt][2 * r], -te15 * gx[nt][2 * r + 1]));
+      }
+
+    // ---- Zbar = Zq - M G',  M[i][j] = te[i] (1 + Attn[i][j]) for j <= i
+    {
+      Pk<NP> am[4];
+#pragma unroll
+      for (int jt = 0; jt < 2; ++jt)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const int i = g + 8 * r, j = 8 * jt + 2 * t;
+          const float m0 = (j <= i) ? -te_row[r] * (1.f + at[jt][2 * r]) : 0.f;
+          const float m1 = (j + 1 <= i) ? -te_row[r] * (1.f + at[jt][2 * r + 1]) : 0.f;
+          am[2 * jt + r] = split_pack<NP>(m0, m1);
+        }
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const Pk<NP> bg[2] = {gt[nt][0], gt[nt][1]};
+        mma_np<NP>(zq[nt], am, bg);
+      }
+    }
+
+    // ---- state update: W^T[nb.., :] += (-te15 G')^T K ; b -= te15 * colsum(G')
+    {
+      const Pk<NP> au[4] = {gu[0][0], gu[1][0], gu[0][1], gu[1][1]};
+#pragma unroll
+      for (int kp = 0; kp < 4; ++kp) {
+        Pk<NP> bk[4];
+        ldsm_np<NP>(bk, pk + lane_off_B_kn(lane, 16 * kp), TILE_BF16_BYTES, true);
+        const Pk<NP> b0[2] = {bk[0], bk[1]}, b1[2] = {bk[2], bk[3]};
+        mma_np<NP>(wt[2 * kp], au, b0);
+        mma_np<NP>(wt[2 * kp + 1], au, b1);
+      }
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) bias[2 * nt + e] -= te15 * col_sum(gx[nt][e] + gx[nt][2 + e]);
+    }
+
+    // ---- out = Q + LN(Zbar)
+    int fl2 = 0;
+    row_stats(zq, fl2);
+    const uint32_t so = base + SM::OFF_OUT + (s & 1) * TF::RAW_BYTES;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int row = g + 8 * r, col = nb + 8 * nt + 2 * t;
+        const float2 qv = ld_pair<T>(tq, row, col);
+        const float o0 = qv.x + gam[2 * nt] * ((zq[nt][2 * r] - mean[r]) * rstd[r]) + bet[2 * nt];
+        const float o1 = qv.y + gam[2 * nt + 1] * ((zq[nt][2 * r + 1] - mean[r]) * rstd[r]) + bet[2 * nt + 1];
+        st_pair<T>(so, row, col, o0, o1);
+      }
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      tma_store_tile<T>(&tm_o, row_base + s * CS, so);
+      bulk_commit();
+      bulk_wait_read<1>();
+      if (s + FWD_NST < NS) issue_loads(s + FWD_NST);
+    }
+  }
+
+  if (!failed) {
+    // ---- final state
+#pragma unroll
+    for (int kt = 0; kt < 8; ++kt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        st_from_float<T>(p.w_out, (size_t)stream * HD * HD + (8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1),
+                         wt[kt][i]);
+    if (g == 0) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        st_from_float<T>(p.b_out, (size_t)stream * HD + nb + 8 * (j >> 1) + 2 * t + (j & 1), bias[j]);
+    }
+  }
+  if (tid == 0) bulk_wait_all<0>();
+}
+
+template <typename T>
+static cudaError_t launch_fwd_t(const CUtensorMap* m, const LinFwdParams& p, int nstreams, cudaStream_t st) {
+  auto kfn = ttt_linear_fwd_kernel<T>;
+  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FwdSmem<T>::DYN_BYTES);
+  if (e != cudaSuccess) return e;
+  kfn<<<nstreams, NTHREADS, FwdSmem<T>::DYN_BYTES, st>>>(m[0], m[1], m[2], m[3], p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_linear_fwd(int dtype, const CUtensorMap* maps, const LinFwdParams& p, int nstreams,
+                              cudaStream_t st) {
+  if (dtype == 1) return launch_fwd_t<__nv_bfloat16>(maps, p, nstreams, st);
+  return launch_fwd_t<float>(maps, p, nstreams, st);
+}
+
+}  // namespace ttt

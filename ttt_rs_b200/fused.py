@@ -1,0 +1,359 @@
+"""Host-side mirror of the reference's `fused-tile-multi` operator, over the C ABI.
+
+Names, argument meaning and error behaviour follow the reference so that tests read like its own:
+
+* `FusedTttConfig`                       rust/fused/src/lib.rs:285-328
+* `TttInputs` / `TttOutputs`             rust/fused/src/ttt/types.rs:3-13
+* `TttSavedStateMulti`                   rust/fused/src/linear_fused_tile/launch.rs:30-41
+* `TttTileMultiKernel.forward_launch / backward_launch`
+                                         rust/fused/src/linear_fused_tile/launch.rs:117-208 (FusedKernel trait,
+                                         rust/kernels/src/kernel.rs:32-54)
+* `fused_ttt_tile_forward_multi`         rust/fused/src/linear_fused_tile/api.rs:52-83 (autodiff-registered entry,
+                                         rust/kernels/src/impls/autodiff.rs:107-200)
+* `TTTLinear`, `TTTLinearState`, `TTTInputsInner`, `Qkv`
+                                         rust/core/src/linear.rs:18-33,84-89, rust/core/src/inner.rs:61-68,108-130
+* `FusedTileMultiTTTLinear`              rust/fused/src/linear_fused_tile/wrapper.rs:81-211 (TTTInnerModel impl)
+
+torch is used for device memory and streams only; all arithmetic happens in libttt_b200.so.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, fields
+from typing import Optional, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import TttDims, TttError
+
+_DTYPES = {torch.float32: _lib.TTT_F32, torch.bfloat16: _lib.TTT_BF16}
+
+
+# --------------------------------------------------------------------------------------------
+# config and tensor bundles
+# --------------------------------------------------------------------------------------------
+
+@dataclass(frozen=True)
+class FusedTttConfig:
+    """Kernel configuration key.  `epsilon` travels as an integer multiple of 1e-9 like the reference's
+    hashable config; `threads` is accepted for signature compatibility (the sm_100a kernels always run
+    4 warps per stream)."""
+    mini_batch_len: int
+    head_dim: int
+    epsilon_scaled: int
+    threads: int = 128
+    checkpoint_interval: int = 1
+
+    @staticmethod
+    def new(mini_batch_len: int, head_dim: int, epsilon: float, threads: int = 128,
+            checkpoint_interval: int = 1) -> "FusedTttConfig":
+        # float32 arithmetic like the reference: (1e-6f32 / 1e-9f32) as u32 == 1000
+        scaled = int(np.float32(epsilon) / np.float32(1e-9))
+        return FusedTttConfig(mini_batch_len, head_dim, scaled, threads, checkpoint_interval)
+
+    def epsilon(self) -> float:
+        return float(np.float32(self.epsilon_scaled) * np.float32(1e-9))
+
+    def with_checkpoint_interval(self, k: int) -> "FusedTttConfig":
+        return FusedTttConfig(self.mini_batch_len, self.head_dim, self.epsilon_scaled, self.threads, k)
+
+
+@dataclass
+class TttInputs:
+    xq: torch.Tensor
+    xk: torch.Tensor
+    xv: torch.Tensor
+    weight: torch.Tensor
+    bias: torch.Tensor
+    token_eta: torch.Tensor
+    ttt_lr_eta: torch.Tensor
+    ln_weight: torch.Tensor
+    ln_bias: torch.Tensor
+
+    def map(self, fn):
+        return TttInputs(*[fn(getattr(self, f.name)) for f in fields(self)])
+
+
+@dataclass
+class TttOutputs:
+    output: torch.Tensor
+    weight: torch.Tensor
+    bias: torch.Tensor
+
+
+@dataclass
+class TttSavedStateMulti:
+    xq: torch.Tensor
+    xk: torch.Tensor
+    xv: torch.Tensor
+    weight_init: torch.Tensor
+    bias: torch.Tensor
+    token_eta: torch.Tensor
+    ttt_lr_eta: torch.Tensor
+    ln_weight: torch.Tensor
+    ln_bias: torch.Tensor
+    weight_checkpoints: torch.Tensor
+    bias_checkpoints: torch.Tensor
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream_ptr(device) -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _dims(xq: torch.Tensor, config: FusedTttConfig) -> TttDims:
+    if xq.dim() != 4:
+        raise TttError(_lib.TTT_ERR_SHAPE, f"xq must be [batch, heads, seq_len, head_dim], got {tuple(xq.shape)}")
+    if xq.dtype not in _DTYPES:
+        raise TttError(_lib.TTT_ERR_UNSUPPORTED, f"unsupported dtype {xq.dtype}")
+    B, H, T, F = xq.shape
+    if F != config.head_dim:
+        raise TttError(_lib.TTT_ERR_SHAPE, f"head_dim of xq ({F}) differs from config.head_dim ({config.head_dim})")
+    return TttDims(B, H, T, F, config.mini_batch_len, config.checkpoint_interval,
+                   float(config.epsilon()), _DTYPES[xq.dtype])
+
+
+def _expect(name: str, t: torch.Tensor, shape, dtype, device):
+    if tuple(t.shape) != tuple(shape):
+        raise TttError(_lib.TTT_ERR_SHAPE, f"{name} has shape {tuple(t.shape)}, expected {tuple(shape)}")
+    if t.dtype != dtype:
+        raise TttError(_lib.TTT_ERR_SHAPE, f"{name} has dtype {t.dtype}, expected {dtype}")
+    if t.device != device:
+        raise TttError(_lib.TTT_ERR_SHAPE, f"{name} is on {t.device}, expected {device}")
+
+
+def _check_inputs(i, wname="weight"):
+    xq = i.xq
+    if not xq.is_cuda:
+        raise TttError(_lib.TTT_ERR_CUDA, "inputs must be CUDA tensors: this operator has no CPU path")
+    B, H, T, F = xq.shape
+    dt, dev = xq.dtype, xq.device
+    _expect("xk", i.xk, (B, H, T, F), dt, dev)
+    _expect("xv", i.xv, (B, H, T, F), dt, dev)
+    _expect(wname, getattr(i, wname), (B, H, F, F), dt, dev)
+    _expect("bias", i.bias, (B, H, F), dt, dev)
+    if i.token_eta.dim() != 1 or i.token_eta.shape[0] < 1:
+        raise TttError(_lib.TTT_ERR_SHAPE, "token_eta must be [seq_len]")
+    _expect("token_eta", i.token_eta, (i.token_eta.shape[0],), dt, dev)
+    _expect("ttt_lr_eta", i.ttt_lr_eta, (B, H, T), dt, dev)
+    _expect("ln_weight", i.ln_weight, (H, F), dt, dev)
+    _expect("ln_bias", i.ln_bias, (H, F), dt, dev)
+
+
+class TttTileMultiKernel:
+    """The multi-stage tiled TTT-Linear operator: one launch walks every mini-batch of the sequence."""
+
+    #: when set, every launch allocates a 4-word device status buffer and the last one is kept here; call
+    #: `check_status()` after synchronising to surface device-side wait timeouts
+    last_status: Optional[torch.Tensor] = None
+
+    @staticmethod
+    def forward_launch(inputs: TttInputs, config: FusedTttConfig) -> Tuple[TttOutputs, TttSavedStateMulti]:
+        if config.mini_batch_len <= 0:
+            raise TttError(_lib.TTT_ERR_SHAPE, "mini_batch_len must be set for TttTileMultiKernel")
+        lib = _lib.load()
+        inputs = inputs.map(lambda t: t.contiguous())
+        d = _dims(inputs.xq, config)
+        _check_inputs(inputs)
+        if inputs.token_eta.shape[0] < config.mini_batch_len:
+            raise TttError(_lib.TTT_ERR_SHAPE, "token_eta must hold at least mini_batch_len entries")
+        dev = inputs.xq.device
+        nck = lib.ttt_linear_num_checkpoints(C.byref(d))
+        if nck < 0:
+            raise TttError(_lib.TTT_ERR_SHAPE, _lib.last_error())
+        B, H, T, F = inputs.xq.shape
+        output = torch.empty_like(inputs.xq)
+        weight_out = torch.empty_like(inputs.weight)
+        bias_out = torch.empty_like(inputs.bias)
+        w_ck = torch.empty((B * H * nck, F, F), dtype=torch.float32, device=dev)
+        b_ck = torch.empty((B * H * nck, F), dtype=torch.float32, device=dev)
+        status = torch.zeros(4, dtype=torch.int32, device=dev)
+        TttTileMultiKernel.last_status = status
+        rc = lib.ttt_linear_forward(
+            C.byref(d), _ptr(inputs.xq), _ptr(inputs.xk), _ptr(inputs.xv), _ptr(inputs.weight), _ptr(inputs.bias),
+            _ptr(inputs.token_eta), _ptr(inputs.ttt_lr_eta), _ptr(inputs.ln_weight), _ptr(inputs.ln_bias),
+            _ptr(output), _ptr(weight_out), _ptr(bias_out), _ptr(w_ck), _ptr(b_ck), _ptr(status), _stream_ptr(dev))
+        _lib.check(rc)
+        saved = TttSavedStateMulti(inputs.xq, inputs.xk, inputs.xv, inputs.weight, inputs.bias, inputs.token_eta,
+                                   inputs.ttt_lr_eta, inputs.ln_weight, inputs.ln_bias, w_ck, b_ck)
+        return TttOutputs(output, weight_out, bias_out), saved
+
+    @staticmethod
+    def backward_launch(saved: TttSavedStateMulti, grad_outputs: TttOutputs, config: FusedTttConfig,
+                        outer_grad_packed: Optional[torch.Tensor] = None) -> TttInputs:
+        """Gradients w.r.t. the nine inputs, in input order.  Only `grad_outputs.output` is used: upstream
+        gradients of the returned final state are ignored, as in the reference."""
+        if config.mini_batch_len <= 0:
+            raise TttError(_lib.TTT_ERR_SHAPE, "mini_batch_len must be set for TttTileMultiKernel backward")
+        lib = _lib.load()
+        d = _dims(saved.xq, config)
+        _check_inputs(saved, wname="weight_init")
+        go = grad_outputs.output.contiguous()
+        B, H, T, F = saved.xq.shape
+        dev, dt = saved.xq.device, saved.xq.dtype
+        _expect("grad_output", go, (B, H, T, F), dt, dev)
+        g_xq, g_xk, g_xv = (torch.empty_like(saved.xq) for _ in range(3))
+        g_w = torch.empty_like(saved.weight_init)
+        g_b = torch.empty_like(saved.bias)
+        g_lr = torch.empty_like(saved.ttt_lr_eta)
+        g_te = torch.empty(T, dtype=torch.float32, device=dev)
+        g_lnw = torch.empty((H, F), dtype=torch.float32, device=dev)
+        g_lnb = torch.empty((H, F), dtype=torch.float32, device=dev)
+        ws_bytes = lib.ttt_linear_backward_workspace_bytes(C.byref(d))
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        status = torch.zeros(4, dtype=torch.int32, device=dev)
+        TttTileMultiKernel.last_status = status
+        rc = lib.ttt_linear_backward(
+            C.byref(d), _ptr(saved.xq), _ptr(saved.xk), _ptr(saved.xv), _ptr(saved.weight_init), _ptr(saved.bias),
+            _ptr(saved.token_eta), _ptr(saved.ttt_lr_eta), _ptr(saved.ln_weight), _ptr(saved.ln_bias),
+            _ptr(saved.weight_checkpoints), _ptr(saved.bias_checkpoints), _ptr(go), _ptr(g_xq), _ptr(g_xk),
+            _ptr(g_xv), _ptr(g_w), _ptr(g_b), _ptr(g_lr), _ptr(g_te), _ptr(g_lnw), _ptr(g_lnb),
+            _ptr(outer_grad_packed), _ptr(ws), C.c_size_t(ws_bytes), _ptr(status), _stream_ptr(dev))
+        _lib.check(rc)
+        # the three reduced gradients are produced in float32 and cast back, like backward/launch.rs:423-425
+        return TttInputs(g_xq, g_xk, g_xv, g_w, g_b, g_te.to(dt), g_lr, g_lnw.to(dt), g_lnb.to(dt))
+
+    @staticmethod
+    def check_status() -> None:
+        st = TttTileMultiKernel.last_status
+        if st is not None:
+            v = st.cpu().tolist()
+            if v[0] != 0:
+                raise TttError(v[0], f"device-side wait timed out (where={v[1]}, block={v[2]}, stage={v[3]})")
+
+
+def packed_outer_grad_len(heads: int, head_dim: int = 64, mini_batch: int = 16) -> int:
+    """Length of the float32 buffer `outer_grad_packed`: dW0 [H,F,F], db0 [H,F], d ln_weight [H,F],
+    d ln_bias [H,F], d token_eta [CS]."""
+    return heads * head_dim * head_dim + 3 * heads * head_dim + mini_batch
+
+
+class _FusedTttTileMultiFn(torch.autograd.Function):
+    """Registers the operator with autograd the way the reference registers its kernel with Burn's autodiff:
+    one node, saved state = nine inputs + two checkpoint tensors."""
+
+    @staticmethod
+    def forward(ctx, xq, xk, xv, weight, bias, token_eta, ttt_lr_eta, ln_weight, ln_bias, config):
+        outs, saved = TttTileMultiKernel.forward_launch(
+            TttInputs(xq, xk, xv, weight, bias, token_eta, ttt_lr_eta, ln_weight, ln_bias), config)
+        ctx.config = config
+        ctx.saved = saved
+        ctx.mark_non_differentiable(outs.weight, outs.bias)
+        return outs.output, outs.weight, outs.bias
+
+    @staticmethod
+    def backward(ctx, g_out, _g_w, _g_b):
+        g = TttTileMultiKernel.backward_launch(ctx.saved, TttOutputs(g_out, None, None), ctx.config)
+        return g.xq, g.xk, g.xv, g.weight, g.bias, g.token_eta, g.ttt_lr_eta, g.ln_weight, g.ln_bias, None
+
+
+def fused_ttt_tile_forward_multi(xq, xk, xv, weight, bias, token_eta, ttt_lr_eta, ln_weight, ln_bias,
+                                 config: FusedTttConfig):
+    """(output, weight_updated, bias_updated); differentiable w.r.t. the nine tensor inputs through `output`."""
+    return _FusedTttTileMultiFn.apply(xq, xk, xv, weight, bias, token_eta, ttt_lr_eta, ln_weight, ln_bias, config)
+
+
+# --------------------------------------------------------------------------------------------
+# inner-model interface
+# --------------------------------------------------------------------------------------------
+
+@dataclass
+class Qkv:
+    xq: torch.Tensor
+    xk: torch.Tensor
+    xv: torch.Tensor
+
+    def slice_seq(self, r: range) -> "Qkv":
+        return Qkv(self.xq[:, :, r.start:r.stop], self.xk[:, :, r.start:r.stop], self.xv[:, :, r.start:r.stop])
+
+
+@dataclass
+class TTTInputsInner:
+    qkv: Qkv
+    token_eta: torch.Tensor   # [seq_len]
+    ttt_lr_eta: torch.Tensor  # [batch, heads, seq_len]
+    start_idx: int = 0
+
+    def slice_seq(self, r: range) -> "TTTInputsInner":
+        return TTTInputsInner(self.qkv.slice_seq(r), self.token_eta[r.start:r.stop],
+                              self.ttt_lr_eta[:, :, r.start:r.stop], r.start)
+
+
+@dataclass
+class TTTLinearState:
+    weight: torch.Tensor  # [batch, heads, F, F]
+    bias: torch.Tensor    # [batch, heads, F]
+
+
+class TTTLinear(torch.nn.Module):
+    """Parameter holder of the TTT-Linear inner model: weight_init [H,F,F] ~ N(0, 0.02), bias_init [H,F] = 0,
+    per-head LayerNorm weight = 1 / bias = 0."""
+
+    def __init__(self, num_heads: int, head_dim: int, mini_batch_size: int = 16, epsilon: float = 1e-6,
+                 checkpoint_interval: int = 1, device=None, dtype=torch.float32):
+        super().__init__()
+        self.num_heads, self.head_dim = num_heads, head_dim
+        self.mini_batch_size, self.epsilon, self.checkpoint_interval = mini_batch_size, epsilon, checkpoint_interval
+        kw = dict(device=device, dtype=dtype)
+        self.weight_init = torch.nn.Parameter(torch.randn(num_heads, head_dim, head_dim, **kw) * 0.02)
+        self.bias_init = torch.nn.Parameter(torch.zeros(num_heads, head_dim, **kw))
+        self.ln_weight = torch.nn.Parameter(torch.ones(num_heads, head_dim, **kw))
+        self.ln_bias = torch.nn.Parameter(torch.zeros(num_heads, head_dim, **kw))
+
+    def init_state(self, batch_size: int) -> TTTLinearState:
+        return TTTLinearState(self.weight_init.unsqueeze(0).repeat(batch_size, 1, 1, 1),
+                              self.bias_init.unsqueeze(0).repeat(batch_size, 1, 1))
+
+
+class FusedTileMultiTTTLinear(torch.nn.Module):
+    """`fused-tile-multi` inner model: whole-sequence forward in a single launch."""
+
+    def __init__(self, inner: TTTLinear):
+        super().__init__()
+        self.inner = inner
+
+    @staticmethod
+    def name() -> str:
+        return "FusedTileMultiTTTLinear"
+
+    def init_state(self, batch_size: int) -> TTTLinearState:
+        return self.inner.init_state(batch_size)
+
+    def _config(self, head_dim: int) -> FusedTttConfig:
+        i = self.inner
+        return FusedTttConfig.new(i.mini_batch_size, head_dim, i.epsilon, 128, i.checkpoint_interval)
+
+    def forward(self, state: TTTLinearState, inputs: TTTInputsInner) -> torch.Tensor:
+        mb = self.inner.mini_batch_size
+        B, H, T, F = inputs.qkv.xv.shape
+        full, rem = T // mb, T % mb
+        if full == 0:
+            return self.forward_mini_batch(state, inputs, range(0, T))
+        L = full * mb
+        q = inputs.qkv.slice_seq(range(0, L))
+        out, w, b = fused_ttt_tile_forward_multi(
+            q.xq, q.xk, q.xv, state.weight, state.bias, inputs.token_eta, inputs.ttt_lr_eta[:, :, :L],
+            self.inner.ln_weight, self.inner.ln_bias, self._config(F))
+        state.weight, state.bias = w, b
+        if rem == 0:
+            return out
+        tail = self.forward_mini_batch(state, inputs, range(L, T))
+        return torch.cat([out, tail], dim=2)
+
+    def forward_mini_batch(self, state: TTTLinearState, inputs: TTTInputsInner, r: range) -> torch.Tensor:
+        if len(r) != self.inner.mini_batch_size:
+            raise AssertionError("Sequence length must be equal to mini_batch_size")
+        sl = inputs.slice_seq(r)
+        F = sl.qkv.xq.shape[-1]
+        cfg = self._config(F).with_checkpoint_interval(1)
+        out, w, b = fused_ttt_tile_forward_multi(
+            sl.qkv.xq, sl.qkv.xk, sl.qkv.xv, state.weight, state.bias, sl.token_eta, sl.ttt_lr_eta,
+            self.inner.ln_weight, self.inner.ln_bias, cfg)
+        state.weight, state.bias = w, b
+        return out
