@@ -1,0 +1,98 @@
+"""CPU-only checks of the C ABI: the library loads, exports every declared symbol, and rejects bad arguments
+with the documented error codes before touching a GPU (mirrors the reference's panics:
+linear_fused_tile/mod.rs:143, forward/launch.rs:209-213, launch.rs:128-131)."""
+
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+
+import ttt_rs_b200
+from ttt_rs_b200 import _lib
+
+REPO = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from ttt_rs_b200.build import build
+    build()
+    return _lib.load()
+
+
+def _dims(**kw):
+    d = dict(batch=2, heads=2, seq_len=64, head_dim=64, mini_batch=16, checkpoint_interval=4, epsilon=1e-6, dtype=1)
+    d.update(kw)
+    return _lib.TttDims(**d)
+
+
+def test_every_declared_symbol_is_exported(lib):
+    header = (REPO / "include" / "ttt_b200.h").read_text()
+    declared = set(re.findall(r"\b(ttt_(?:b200|linear|mlp)_\w+)\s*\(", header))
+    assert declared, "no declarations found"
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in ttt_b200.h but not exported"
+    assert declared == set(_lib.SYMBOLS), "ctypes binding and header disagree"
+    assert lib.ttt_b200_abi_version() == 1
+
+
+def test_checkpoint_and_workspace_sizes(lib):
+    d = _dims(seq_len=80, checkpoint_interval=2)  # 5 stages -> 3 checkpoints
+    assert lib.ttt_linear_num_checkpoints(C.byref(d)) == 3
+    assert lib.ttt_linear_weight_ckpt_bytes(C.byref(d)) == 2 * 2 * 3 * 64 * 64 * 4
+    assert lib.ttt_linear_bias_ckpt_bytes(C.byref(d)) == 2 * 2 * 3 * 64 * 4
+    streams = 4
+    assert lib.ttt_linear_backward_workspace_bytes(C.byref(d)) == 4 * (streams * 128 + streams * 80 + streams * (4096 + 64))
+
+
+@pytest.mark.parametrize("kw,code", [
+    (dict(seq_len=70), _lib.TTT_ERR_SHAPE),              # not a multiple of the mini-batch
+    (dict(mini_batch=8, seq_len=64), _lib.TTT_ERR_UNSUPPORTED),
+    (dict(head_dim=32), _lib.TTT_ERR_UNSUPPORTED),
+    (dict(checkpoint_interval=0), _lib.TTT_ERR_SHAPE),
+    (dict(batch=0), _lib.TTT_ERR_SHAPE),
+    (dict(dtype=7), _lib.TTT_ERR_UNSUPPORTED),
+])
+def test_bad_dims_are_rejected(lib, kw, code):
+    d = _dims(**kw)
+    fake = C.c_void_p(0x1000)  # never dereferenced: validation fails first
+    rc = lib.ttt_linear_forward(C.byref(d), *([fake] * 14), None, None)
+    assert rc == code, _lib.last_error()
+    assert _lib.last_error()
+    assert lib.ttt_linear_num_checkpoints(C.byref(d)) == -1
+    assert lib.ttt_linear_backward_workspace_bytes(C.byref(d)) == 0
+
+
+def test_null_and_misaligned_pointers_are_rejected(lib):
+    d = _dims()
+    fake = C.c_void_p(0x1000)
+    args = [fake] * 14
+    args[3] = None
+    assert lib.ttt_linear_forward(C.byref(d), *args, None, None) == _lib.TTT_ERR_NULL
+    assert "weight" in _lib.last_error()
+    args = [fake] * 14
+    args[1] = C.c_void_p(0x1008)
+    assert lib.ttt_linear_forward(C.byref(d), *args, None, None) == _lib.TTT_ERR_ALIGN
+    assert "xk" in _lib.last_error()
+    bargs = [fake] * 21 + [None, fake]
+    assert lib.ttt_linear_backward(C.byref(d), *bargs, C.c_size_t(16), None, None) == _lib.TTT_ERR_WORKSPACE
+    assert lib.ttt_linear_forward(None, *([fake] * 14), None, None) == _lib.TTT_ERR_NULL
+
+
+def test_config_epsilon_scaling_matches_reference():
+    # (1e-6f32 / 1e-9f32) as u32 == 1000 (rust/fused/src/lib.rs:298-311)
+    cfg = ttt_rs_b200.FusedTttConfig.new(16, 64, 1e-6, 64)
+    assert cfg.epsilon_scaled == 1000
+    assert abs(cfg.epsilon() - 1e-6) < 1e-12
+    assert cfg.checkpoint_interval == 1
+
+
+def test_host_wrapper_refuses_cpu_tensors():
+    import torch
+    from oracle.ttt_oracle import make_inputs
+    t = make_inputs(1, 1, 16, 64, 16, seed=0, dtype=torch.float32, with_grad_output=False)
+    names = ("xq", "xk", "xv", "weight", "bias", "token_eta", "ttt_lr_eta", "ln_weight", "ln_bias")
+    ins = ttt_rs_b200.TttInputs(*[t[k] for k in names])
+    with pytest.raises(ttt_rs_b200.TttError):
+        ttt_rs_b200.TttTileMultiKernel.forward_launch(ins, ttt_rs_b200.FusedTttConfig.new(16, 64, 1e-6))

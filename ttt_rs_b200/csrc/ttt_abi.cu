@@ -252,7 +252,7 @@ int ttt_linear_backward(const ttt_dims* d, const void* xq, const void* xk, const
   p.d_lr = grad_ttt_lr_eta;
   p.part_ln = ws + wl.off_ln;
   p.part_te = ws + wl.off_te;
-  p.part_w = ws + wl.off_w;
+  p.part_w = (outer_grad_packed != nullptr) ? ws + wl.off_w : nullptr;
   p.status = static_cast<uint32_t*>(status);
   p.H = d->heads;
   p.T = d->seq_len;

@@ -17,7 +17,7 @@
 //     512 bytes of shared memory; G reaches the tensor cores as an A/B operand through movmatrix.
 //   * Output tiles leave through a double-buffered staging tile and a TMA store.
 #include "ttt_kernels.h"
-#include "ttt_tiles.cuh"
+#include "ttt_stage.cuh"
 
 namespace ttt {
 
@@ -29,19 +29,11 @@ struct FwdSmem {
   static constexpr uint32_t SLOT = 3 * TF::BYTES;                  // q, k, v
   static constexpr uint32_t OFF_OUT = FWD_NST * SLOT;              // 2 staging tiles (raw format)
   static constexpr uint32_t OFF_LR = OFF_OUT + 2 * TF::RAW_BYTES;  // FWD_NST x 64 bytes
-  static constexpr uint32_t OFF_XCH = OFF_LR + FWD_NST * 64;       // 2 x XchBuf
-  static constexpr uint32_t OFF_BAR = OFF_XCH + 2 * sizeof(XchBuf);
+  static constexpr uint32_t OFF_XCH = OFF_LR + FWD_NST * 64;       // 2 x Xch4
+  static constexpr uint32_t OFF_BAR = OFF_XCH + 2 * sizeof(Xch4);
   static constexpr uint32_t TOTAL = OFF_BAR + FWD_NST * 8;
   static constexpr uint32_t DYN_BYTES = TOTAL + 1024;  // slack for manual 1024-byte alignment
 };
-
-__device__ __forceinline__ void report_timeout(uint32_t* status, uint32_t where, uint32_t stage) {
-  if (status != nullptr && atomicCAS(status, 0u, (uint32_t)KST_TIMEOUT) == 0u) {
-    status[1] = where;
-    status[2] = blockIdx.x;
-    status[3] = stage;
-  }
-}
 
 template <typename T>
 __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
@@ -57,11 +49,11 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
   const uint32_t raw_u32 = smem_u32(smem_raw);
   const uint32_t base = (raw_u32 + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (base - raw_u32);
-  XchBuf* xch = reinterpret_cast<XchBuf*>(gbase + SM::OFF_XCH);
+  Xch4* xch = reinterpret_cast<Xch4*>(gbase + SM::OFF_XCH);
   const uint32_t bar0 = base + SM::OFF_BAR;
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  const int nb = warp * 16;
+  const Lane L;
+  const int tid = L.tid, lane = L.lane, g = L.g, t = L.t, nb = L.nb;
   const int stream = blockIdx.x;
   const int head = stream % p.H;
   const int NS = p.NS;
@@ -168,11 +160,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
 #pragma unroll
     for (int ks = 0; ks < 4; ++ks) {
       Pk<NP> bw[2][2];
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
-        bw[nt][0] = split_pack<NP>(wt[2 * ks][2 * nt], wt[2 * ks][2 * nt + 1]);
-        bw[nt][1] = split_pack<NP>(wt[2 * ks + 1][2 * nt], wt[2 * ks + 1][2 * nt + 1]);
-      }
+      bfrag_from_state<NP>(wt, ks, bw);
       Pk<NP> ak[4], aq[4], bk[4];
       ldsm_np<NP>(ak, pk + lane_off_A(lane, 16 * ks), TILE_BF16_BYTES, false);
       ldsm_np<NP>(aq, pq + lane_off_A(lane, 16 * ks), TILE_BF16_BYTES, false);
@@ -187,130 +175,38 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
       mma_np<NP>(at[1], aq, bj1);
     }
 
-    // ---- LN statistics of Z1 (rows g, g+8)
+    // ---- LN statistics of Z1, then G = dL/dZ1 and Gp = lr[row] * G
     float mean[2], rstd[2];
-    auto row_stats = [&](const float (&z)[2][4], int& fl) {
-      float s1[2], s2[2];
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        s1[r] = (z[0][2 * r] + z[0][2 * r + 1]) + (z[1][2 * r] + z[1][2 * r + 1]);
-        s2[r] = 0.f;
-        if constexpr (!TWO_PASS) {
-          s2[r] = (z[0][2 * r] * z[0][2 * r] + z[0][2 * r + 1] * z[0][2 * r + 1]) +
-                  (z[1][2 * r] * z[1][2 * r] + z[1][2 * r + 1] * z[1][2 * r + 1]);
-        }
-        s1[r] = quad_sum(s1[r]);
-        if constexpr (!TWO_PASS) s2[r] = quad_sum(s2[r]);
-      }
-      XchBuf* xb = &xch[xsel];
-      xsel ^= 1;
-      if (t == 0) {
-        xch_put(xb, g, warp, s1[0], s2[0]);
-        xch_put(xb, g + 8, warp, s1[1], s2[1]);
-      }
-      fl = __syncthreads_or(fl);
-      const float2 a0 = xch_get(xb, g), a1 = xch_get(xb, g + 8);
-      mean[0] = a0.x * (1.f / HD);
-      mean[1] = a1.x * (1.f / HD);
-      float var[2];
-      if constexpr (!TWO_PASS) {
-        var[0] = fmaxf(a0.y * (1.f / HD) - mean[0] * mean[0], 0.f);
-        var[1] = fmaxf(a1.y * (1.f / HD) - mean[1] * mean[1], 0.f);
-        rstd[0] = rsqrtf(var[0] + p.eps);
-        rstd[1] = rsqrtf(var[1] + p.eps);
-      } else {
-        float q2[2];
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          float acc = 0.f;
-#pragma unroll
-          for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const float d = z[nt][2 * r + e] - mean[r];
-              acc += d * d;
-            }
-          q2[r] = quad_sum(acc);
-        }
-        XchBuf* xb2 = &xch[xsel];
-        xsel ^= 1;
-        if (t == 0) {
-          xch_put(xb2, g, warp, q2[0], 0.f);
-          xch_put(xb2, g + 8, warp, q2[1], 0.f);
-        }
-        __syncthreads();
-        var[0] = xch_get(xb2, g).x * (1.f / HD);
-        var[1] = xch_get(xb2, g + 8).x * (1.f / HD);
-        rstd[0] = 1.0f / sqrtf(var[0] + p.eps);
-        rstd[1] = 1.0f / sqrtf(var[1] + p.eps);
-      }
-    };
-
-    row_stats(z1, fail);
+    ln_row_stats<TWO_PASS>(z1, xch, xsel, L, p.eps, mean, rstd, fail);
     if (fail) {
       failed = true;
       if (tid == 0) report_timeout(p.status, 2, s);
       break;
     }
-
-    // ---- G = dL/dZ1 ; gp = lr[row] * G
-    float xh[2][4], gx[2][4];
+    float gp[2][4];
     {
-      float sa[2] = {0.f, 0.f}, sb[2] = {0.f, 0.f};
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          const int row = g + 8 * r, col = nb + 8 * nt + 2 * t;
-          const float2 kv = ld_pair<T>(tk, row, col), vv = ld_pair<T>(tv, row, col);
-          const float tg[2] = {vv.x - kv.x, vv.y - kv.y};
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int i = 2 * r + e, j = 2 * nt + e;
-            const float x = (z1[nt][i] - mean[r]) * rstd[r];
-            const float gy = gam[j] * x + bet[j] - tg[e];
-            const float gg = gy * gam[j];
-            xh[nt][i] = x;
-            gx[nt][i] = gg;
-            sa[r] += gg;
-            sb[r] += gg * x;
-          }
-        }
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        sa[r] = quad_sum(sa[r]);
-        sb[r] = quad_sum(sb[r]);
-      }
-      XchBuf* xb = &xch[xsel];
+      float xh[2][4], gy[2][4], gx[2][4], sa[2], sb[2];
+      ln_l2_pieces<T>(z1, mean, rstd, gam, bet, tk, tv, L, xh, gy, gx, sa, sb);
+      float2 a0, a1;
+      int f2 = 0;
+      xch_rows2(&xch[xsel], L, sa[0], sb[0], sa[1], sb[1], a0, a1, f2);
       xsel ^= 1;
-      if (t == 0) {
-        xch_put(xb, g, warp, sa[0], sb[0]);
-        xch_put(xb, g + 8, warp, sa[1], sb[1]);
-      }
-      __syncthreads();
-      const float2 a0 = xch_get(xb, g), a1 = xch_get(xb, g + 8);
       const float A[2] = {a0.x * (1.f / HD), a1.x * (1.f / HD)}, Bv[2] = {a0.y * (1.f / HD), a1.y * (1.f / HD)};
+      g_from_pieces(gx, xh, A, Bv, rstd, gp);
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int r = i >> 1;
-          // reuse gx as G' = lr * G
-          gx[nt][i] = (gx[nt][i] - A[r] - xh[nt][i] * Bv[r]) * (rstd[r] * lr_row[r]);
-        }
+        for (int i = 0; i < 4; ++i) gp[nt][i] *= lr_row[i >> 1];
     }
 
-    // ---- G' as tensor-core operands (transposed through movmatrix): plain for M.G, scaled by -te15 for the update
-    Pk<NP> gt[2][2], gu[2][2];
+    // ---- Gp as tensor-core operands, transposed through movmatrix: gt[nt][r] = (Gp block rows 8r.., cols nb+8nt..)^T
+    Pk<NP> gt[2][2];
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        gt[nt][r] = movm_t_np<NP>(split_pack<NP>(gx[nt][2 * r], gx[nt][2 * r + 1]));
-        gu[nt][r] = movm_t_np<NP>(split_pack<NP>(-te15 * gx[nt][2 * r], -te15 * gx[nt][2 * r + 1]));
-      }
+      for (int r = 0; r < 2; ++r) gt[nt][r] = movm_t_np<NP>(split_pack<NP>(gp[nt][2 * r], gp[nt][2 * r + 1]));
 
-    // ---- Zbar = Zq - M G',  M[i][j] = te[i] (1 + Attn[i][j]) for j <= i
+    // ---- Zbar = Zq - M' Gp,  M'[i][j] = te[i] (1 + Attn[i][j]) for j <= i
     {
       Pk<NP> am[4];
 #pragma unroll
@@ -329,26 +225,19 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
       }
     }
 
-    // ---- state update: W^T[nb.., :] += (-te15 G')^T K ; b -= te15 * colsum(G')
+    // ---- state update: W^T[nb.., :] -= te15 * Gp^T K ; b -= te15 * colsum(Gp)
     {
-      const Pk<NP> au[4] = {gu[0][0], gu[1][0], gu[0][1], gu[1][1]};
-#pragma unroll
-      for (int kp = 0; kp < 4; ++kp) {
-        Pk<NP> bk[4];
-        ldsm_np<NP>(bk, pk + lane_off_B_kn(lane, 16 * kp), TILE_BF16_BYTES, true);
-        const Pk<NP> b0[2] = {bk[0], bk[1]}, b1[2] = {bk[2], bk[3]};
-        mma_np<NP>(wt[2 * kp], au, b0);
-        mma_np<NP>(wt[2 * kp + 1], au, b1);
-      }
+      const Pk<NP> agt[4] = {gt[0][0], gt[1][0], gt[0][1], gt[1][1]};
+      state_update<NP>(wt, agt, pk, lane, -te15);
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-        for (int e = 0; e < 2; ++e) bias[2 * nt + e] -= te15 * col_sum(gx[nt][e] + gx[nt][2 + e]);
+        for (int e = 0; e < 2; ++e) bias[2 * nt + e] -= te15 * col_sum(gp[nt][e] + gp[nt][2 + e]);
     }
 
     // ---- out = Q + LN(Zbar)
     int fl2 = 0;
-    row_stats(zq, fl2);
+    ln_row_stats<TWO_PASS>(zq, xch, xsel, L, p.eps, mean, rstd, fl2);
     const uint32_t so = base + SM::OFF_OUT + (s & 1) * TF::RAW_BYTES;
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)

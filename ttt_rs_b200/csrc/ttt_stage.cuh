@@ -1,0 +1,193 @@
+// Stage arithmetic shared by the forward scan and by the backward kernel's re-simulation, so that both
+// walk the same state trajectory from a checkpoint (math: rust/core/src/linear.rs:91-149,
+// rust/core/src/util.rs:141-182; quirks of the fused kernels: forward/kernel.rs:116-165).
+//
+// Register-tile convention ("slab"): float v[2][4] = v[nt][2*r + e] is element
+// (row g + 8r, column 16*warp + 8*nt + 2*t + e) of a 16x64 tile; lane = 4g + t.
+#pragma once
+
+#include "ttt_tiles.cuh"
+
+namespace ttt {
+
+struct Lane {
+  int tid, warp, lane, g, t, nb;
+  __device__ __forceinline__ Lane() {
+    tid = threadIdx.x;
+    warp = tid >> 5;
+    lane = tid & 31;
+    g = lane >> 2;
+    t = lane & 3;
+    nb = warp * 16;
+  }
+};
+
+// Exchange of up to four per-row partial sums across the four warps of the CTA.
+struct __align__(16) Xch4 {
+  float4 v[CS][4];  // [row][warp], 1 KB
+};
+
+// Every thread contributes its two rows (g, g+8); returns the CTA-wide sums for those rows.
+// `flag` is OR-reduced over the CTA by the same barrier (used to spread a timed-out wait).
+__device__ __forceinline__ void xch_rows(Xch4* xb, const Lane& L, const float4 a0, const float4 a1, float4& o0,
+                                         float4& o1, int& flag) {
+  float4 p0, p1;
+  p0.x = quad_sum(a0.x); p0.y = quad_sum(a0.y); p0.z = quad_sum(a0.z); p0.w = quad_sum(a0.w);
+  p1.x = quad_sum(a1.x); p1.y = quad_sum(a1.y); p1.z = quad_sum(a1.z); p1.w = quad_sum(a1.w);
+  if (L.t == 0) {
+    xb->v[L.g][L.warp] = p0;
+    xb->v[L.g + 8][L.warp] = p1;
+  }
+  flag = __syncthreads_or(flag);
+  const float4* r0 = &xb->v[L.g][0];
+  const float4* r1 = &xb->v[L.g + 8][0];
+  o0 = make_float4((r0[0].x + r0[1].x) + (r0[2].x + r0[3].x), (r0[0].y + r0[1].y) + (r0[2].y + r0[3].y),
+                   (r0[0].z + r0[1].z) + (r0[2].z + r0[3].z), (r0[0].w + r0[1].w) + (r0[2].w + r0[3].w));
+  o1 = make_float4((r1[0].x + r1[1].x) + (r1[2].x + r1[3].x), (r1[0].y + r1[1].y) + (r1[2].y + r1[3].y),
+                   (r1[0].z + r1[1].z) + (r1[2].z + r1[3].z), (r1[0].w + r1[1].w) + (r1[2].w + r1[3].w));
+}
+// Two-value variant (same buffer type, half the shuffles).
+__device__ __forceinline__ void xch_rows2(Xch4* xb, const Lane& L, float a0x, float a0y, float a1x, float a1y,
+                                          float2& o0, float2& o1, int& flag) {
+  a0x = quad_sum(a0x); a0y = quad_sum(a0y); a1x = quad_sum(a1x); a1y = quad_sum(a1y);
+  float2* base = reinterpret_cast<float2*>(xb);  // reuse the buffer as float2[16][4] (first 512 bytes)
+  if (L.t == 0) {
+    base[L.g * 4 + L.warp] = make_float2(a0x, a0y);
+    base[(L.g + 8) * 4 + L.warp] = make_float2(a1x, a1y);
+  }
+  flag = __syncthreads_or(flag);
+  const float4 p = *reinterpret_cast<const float4*>(&base[L.g * 4]);
+  const float4 q = *reinterpret_cast<const float4*>(&base[L.g * 4 + 2]);
+  const float4 p2 = *reinterpret_cast<const float4*>(&base[(L.g + 8) * 4]);
+  const float4 q2 = *reinterpret_cast<const float4*>(&base[(L.g + 8) * 4 + 2]);
+  o0 = make_float2((p.x + p.z) + (q.x + q.z), (p.y + p.w) + (q.y + q.w));
+  o1 = make_float2((p2.x + p2.z) + (q2.x + q2.z), (p2.y + p2.w) + (q2.y + q2.w));
+}
+
+// LayerNorm row statistics of a slab: mean and 1/sqrt(var + eps) for rows g and g+8.
+// bf16 I/O uses one exchange (sum, sum of squares); float32 I/O uses the two-pass variance of the reference.
+template <bool TWO_PASS>
+__device__ __forceinline__ void ln_row_stats(const float (&z)[2][4], Xch4* xch, int& xsel, const Lane& L, float eps,
+                                             float (&mean)[2], float (&rstd)[2], int& flag) {
+  float s1[2], s2[2] = {0.f, 0.f};
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    s1[r] = (z[0][2 * r] + z[0][2 * r + 1]) + (z[1][2 * r] + z[1][2 * r + 1]);
+    if constexpr (!TWO_PASS)
+      s2[r] = (z[0][2 * r] * z[0][2 * r] + z[0][2 * r + 1] * z[0][2 * r + 1]) +
+              (z[1][2 * r] * z[1][2 * r] + z[1][2 * r + 1] * z[1][2 * r + 1]);
+  }
+  float2 a0, a1;
+  xch_rows2(&xch[xsel], L, s1[0], s2[0], s1[1], s2[1], a0, a1, flag);
+  xsel ^= 1;
+  mean[0] = a0.x * (1.f / HD);
+  mean[1] = a1.x * (1.f / HD);
+  if constexpr (!TWO_PASS) {
+    rstd[0] = rsqrtf(fmaxf(a0.y * (1.f / HD) - mean[0] * mean[0], 0.f) + eps);
+    rstd[1] = rsqrtf(fmaxf(a1.y * (1.f / HD) - mean[1] * mean[1], 0.f) + eps);
+  } else {
+    float q2[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      float acc = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float d = z[nt][2 * r + e] - mean[r];
+          acc += d * d;
+        }
+      q2[r] = acc;
+    }
+    int f2 = 0;
+    xch_rows2(&xch[xsel], L, q2[0], 0.f, q2[1], 0.f, a0, a1, f2);
+    xsel ^= 1;
+    rstd[0] = 1.0f / sqrtf(a0.x * (1.f / HD) + eps);
+    rstd[1] = 1.0f / sqrtf(a1.x * (1.f / HD) + eps);
+  }
+}
+
+// B fragments of a 64x64 matrix held transposed in accumulator registers (m[kt][2*rn+e] = M[k=8kt+2t+e][n=nb+g+8rn]),
+// for products X[16 x 64(k)] . M[:, nb..nb+15]:  k-step ks, n-tile nt.
+template <int NP>
+__device__ __forceinline__ void bfrag_from_state(const float (&m)[8][4], int ks, Pk<NP> (&b)[2][2]) {
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+    b[nt][0] = split_pack<NP>(m[2 * ks][2 * nt], m[2 * ks][2 * nt + 1]);
+    b[nt][1] = split_pack<NP>(m[2 * ks + 1][2 * nt], m[2 * ks + 1][2 * nt + 1]);
+  }
+}
+
+// LN + L2 gradient pieces for one slab of Z1 given its row statistics.
+// Outputs x_hat, gy = gamma*x_hat + beta - (v - k), gx = gy*gamma and the per-thread partial row sums of gx, gx*x_hat.
+template <typename T>
+__device__ __forceinline__ void ln_l2_pieces(const float (&z1)[2][4], const float (&mean)[2], const float (&rstd)[2],
+                                             const float (&gam)[4], const float (&bet)[4], uint32_t tk, uint32_t tv,
+                                             const Lane& L, float (&xh)[2][4], float (&gy)[2][4], float (&gx)[2][4],
+                                             float (&sa)[2], float (&sb)[2]) {
+  sa[0] = sa[1] = sb[0] = sb[1] = 0.f;
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = L.g + 8 * r, col = L.nb + 8 * nt + 2 * L.t;
+      const float2 kv = ld_pair<T>(tk, row, col), vv = ld_pair<T>(tv, row, col);
+      const float tg[2] = {vv.x - kv.x, vv.y - kv.y};
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int i = 2 * r + e, j = 2 * nt + e;
+        const float x = (z1[nt][i] - mean[r]) * rstd[r];
+        const float y = gam[j] * x + bet[j] - tg[e];
+        const float gg = y * gam[j];
+        xh[nt][i] = x;
+        gy[nt][i] = y;
+        gx[nt][i] = gg;
+        sa[r] += gg;
+        sb[r] += gg * x;
+      }
+    }
+}
+
+// G = (gx - A - x_hat*Bv) * rstd with A = mean(gx), Bv = mean(gx*x_hat) per row.
+__device__ __forceinline__ void g_from_pieces(const float (&gx)[2][4], const float (&xh)[2][4], const float (&A)[2],
+                                              const float (&Bv)[2], const float (&rstd)[2], float (&G)[2][4]) {
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = i >> 1;
+      G[nt][i] = (gx[nt][i] - A[r] - xh[nt][i] * Bv[r]) * rstd[r];
+    }
+}
+
+// State update of one stage from Gp = lr o G held as transposed A fragments (agt = {n-lo/tok-lo, n-hi/tok-lo,
+// n-lo/tok-hi, n-hi/tok-hi}):   tmp = Gp^T K  (16 n x 64 k per warp),   W^T += coef * tmp.
+// Forward uses coef = -te15; the backward's reverse walk undoes a stage with coef = +te15 and the same tmp.
+template <int NP>
+__device__ __forceinline__ void state_update(float (&wt)[8][4], const Pk<NP> (&agt)[4], uint32_t k_planes, int lane,
+                                             float coef) {
+#pragma unroll
+  for (int kp = 0; kp < 4; ++kp) {
+    Pk<NP> bk[4];
+    ldsm_np<NP>(bk, k_planes + lane_off_B_kn(lane, 16 * kp), TILE_BF16_BYTES, true);
+    const Pk<NP> b0[2] = {bk[0], bk[1]}, b1[2] = {bk[2], bk[3]};
+    float t0[4] = {0.f, 0.f, 0.f, 0.f}, t1[4] = {0.f, 0.f, 0.f, 0.f};
+    mma_np<NP>(t0, agt, b0);
+    mma_np<NP>(t1, agt, b1);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      wt[2 * kp][i] = fmaf(coef, t0[i], wt[2 * kp][i]);
+      wt[2 * kp + 1][i] = fmaf(coef, t1[i], wt[2 * kp + 1][i]);
+    }
+  }
+}
+
+__device__ __forceinline__ void report_timeout(uint32_t* status, uint32_t where, uint32_t stage) {
+  if (status != nullptr && atomicCAS(status, 0u, (uint32_t)KST_TIMEOUT) == 0u) {
+    status[1] = where;
+    status[2] = blockIdx.x;
+    status[3] = stage;
+  }
+}
+
+}  // namespace ttt
