@@ -1,0 +1,345 @@
+#!/usr/bin/env python3
+"""Benchmark of the fused TTT inner loop (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg1|cfg0|...]
+
+One "step" is one forward + backward pass of the inner loop of one TTT layer over one batch of synthetic
+input (the protocol of the reference's `ttt-bench --inner-only --backward`: rust/cli/src/bench.rs:193-234,
+throughput = batch * seq_len / time, bench.rs:329).  Rank 0 prints ONE JSON line.
+
+N > 1 is launched with torch.distributed.run, one rank per GPU.  Every rank runs the full per-GPU workload on
+its own (batch x head) streams (weak scaling, no collective on the data path); the packed outer-parameter
+gradients (dW0, db0, d ln_weight, d ln_bias, d token_eta) are all-reduced with NCCL every step, as data-parallel
+training would.
+
+`--impl reference` times the CPU restatement of the reference's algorithm (oracle/) on the host cores; the
+reference's own Rust/Burn CPU backend cannot be built on this box (no Rust toolchain).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+REPO = Path(__file__).resolve().parent
+sys.path.insert(0, str(REPO))
+
+LIN_IN = ("xq", "xk", "xv", "weight", "bias", "token_eta", "ttt_lr_eta", "ln_weight", "ln_bias")
+
+WORKLOADS = {
+    # name: (B, H, T, dtype, checkpoint interval, backward?)
+    "cfg0": dict(B=2, H=4, T=256, dtype="f32", K=1, backward=False,
+                 desc="TTT-Linear inner loop fwd, f32, B=2 H=4 T=256 d=64 mb=16"),
+    "cfg1": dict(B=32, H=12, T=2048, dtype="bf16", K=16, backward=True,
+                 desc="TTT-Linear inner loop fwd+bwd, bf16, B=32 H=12 T=2048 d=64 mb=16 ckpt=16"),
+    "cfg1-f32": dict(B=32, H=12, T=2048, dtype="f32", K=16, backward=True,
+                     desc="TTT-Linear inner loop fwd+bwd, f32, B=32 H=12 T=2048 d=64 mb=16 ckpt=16"),
+    "cfg4-8k": dict(B=8, H=32, T=8192, dtype="bf16", K=16, backward=True,
+                    desc="TTT-Linear inner loop fwd+bwd, bf16, B=8 H=32 T=8192 d=64 mb=16 ckpt=16"),
+}
+F, CS = 64, 16
+
+
+def algorithmic_bytes(w, fwd=True, bwd=True):
+    """HBM bytes one launch must move: per token per head, forward reads q,k,v (3Fs) + lr (s), writes out (Fs) and
+    its share of the float32 checkpoints; backward reads q,k,v,d_out (4Fs) + lr, writes dq,dk,dv (3Fs) + dlr and
+    re-reads the checkpoints; per-stream constants (W0,b0,W_T,b_T; dW,db) amortise over T."""
+    s = 2 if w["dtype"] == "bf16" else 4
+    tok_heads = w["B"] * w["H"] * w["T"]
+    streams = w["B"] * w["H"]
+    ck = (F * F + F) * s / (w["K"] * CS)  # counted at the element size; this build keeps them in float32
+    fb = (4 * F * s + s + ck) * tok_heads + streams * 2 * (F * F + F) * s
+    bb = (7 * F * s + 2 * s + ck) * tok_heads + streams * (F * F + F) * s
+    return (fb if fwd else 0) + (bb if bwd else 0), fb, bb
+
+
+def measured_peaks():
+    p = REPO / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return float(d["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def start(self):
+        if self.nv is not None:
+            self._thr = threading.Thread(target=self._loop, daemon=True)
+            self._thr.start()
+
+    def stop(self):
+        if self._thr is not None:
+            self._stop.set()
+            self._thr.join()
+        med = statistics.median(self.samples) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def make_host_inputs(w, seed):
+    from oracle.ttt_oracle import make_inputs
+    dt = torch.bfloat16 if w["dtype"] == "bf16" else torch.float32
+    return make_inputs(w["B"], w["H"], w["T"], F, CS, seed=seed, dtype=dt, with_grad_output=True)
+
+
+def cpu_step(t, w):
+    """One step of the CPU restatement on a host-resident sample (float32)."""
+    from oracle import ttt_oracle as O
+    args = [t[k] for k in LIN_IN]
+    fw = O.ttt_linear_forward(*args, mini_batch=CS, eps=1e-6, checkpoint_interval=w["K"])
+    if w["backward"]:
+        O.ttt_linear_backward(*args, t["grad_output"], mini_batch=CS, eps=1e-6)
+    return fw
+
+
+def time_cpu(w, steps, warmup, sample_B=1):
+    torch.set_num_threads(os.cpu_count() or 1)
+    sw = dict(w, B=sample_B)
+    t = {k: v.float() for k, v in make_host_inputs(sw, seed=0).items()}
+    for _ in range(warmup):
+        cpu_step(t, w)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_step(t, w)
+    dt = (time.perf_counter() - t0) / steps
+    return sample_B * w["T"] / dt, dt, torch.get_num_threads(), \
+        f"B={sample_B} H={w['H']} T={w['T']} slice of the workload, float32, {steps} step(s)"
+
+
+def run_reference(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 3))
+    val, dt, cores, sample = time_cpu(w, steps, min(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": "ttt_inner_loop_tokens_per_sec", "value": val, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w["desc"]},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "CPU restatement of the reference's algorithm (oracle/ttt_oracle.py) on the host cores; the "
+                "reference's Rust/Burn CPU backend cannot be built here (no cargo/rustc)",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    if args.impl == "reference":
+        run_reference(args, w)
+        return
+
+    import torch.distributed as dist
+    import ttt_rs_b200 as tb
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operator has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    tb.load_library()
+
+    # ---- device-resident inputs (every rank its own seed: independent batches)
+    host = make_host_inputs(w, seed=rank)
+    ins = tb.TttInputs(*[host[k].to(dev) for k in LIN_IN])
+    go = host["grad_output"].to(dev)
+    cfg = tb.FusedTttConfig.new(CS, F, 1e-6, 128, w["K"])
+    packed = torch.zeros(tb.packed_outer_grad_len(w["H"]), device=dev) if w["backward"] else None
+    ev_pairs = []
+
+    def step(record=False):
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if record else None
+        if record:
+            e[0].record()
+        outs, saved = tb.TttTileMultiKernel.forward_launch(ins, cfg)
+        if record:
+            e[1].record()
+        g = None
+        if w["backward"]:
+            g = tb.TttTileMultiKernel.backward_launch(saved, tb.TttOutputs(go, None, None), cfg,
+                                                      outer_grad_packed=packed)
+            if record:
+                e[2].record()
+            if world > 1:
+                dist.all_reduce(packed)
+        if record:
+            ev_pairs.append(e)
+        return outs, g
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    tb.TttTileMultiKernel.check_status()
+    sampler = ClockSampler(local)
+    sampler.start()
+    t_ev0, t_ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_ev0.record()
+    for _ in range(args.steps):
+        step(record=True)
+    t_ev1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = t_ev0.elapsed_time(t_ev1) / args.steps
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev_pairs)
+    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev_pairs) if w["backward"] else None
+    if world > 1:
+        tmax = torch.tensor([ms], device=dev)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        ms = tmax.item()
+    tokens = w["B"] * w["T"] * world
+    value = tokens / (ms * 1e-3)
+
+    # ---- end to end through the public operator with host buffers (pinned), copies inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        e2e = run_e2e(tb, w, host, dev, cfg, world, args)
+
+    peak, peak_kind = measured_peaks()
+    total_b, fb, bb = algorithmic_bytes(w, True, w["backward"])
+    dom_ms, dom_bytes, dom_name = (bwd_ms, bb, "ttt_linear_bwd_kernel") if w["backward"] else (fwd_ms, fb, "ttt_linear_fwd_kernel")
+    achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
+    roof = {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "frac": achieved / peak, "traffic": None, "peak_source": f"of {peak_kind}",
+            "algorithmic_bytes_per_launch": dom_bytes, "ms_per_launch": dom_ms,
+            "fwd": {"achieved": fb / (fwd_ms * 1e-3) / 1e9, "frac": fb / (fwd_ms * 1e-3) / 1e9 / peak, "ms_per_launch": fwd_ms},
+            "step": {"achieved": total_b / (ms * 1e-3) / 1e9, "frac": total_b / (ms * 1e-3) / 1e9 / peak}}
+
+    if rank == 0:
+        line = {
+            "metric": "ttt_inner_loop_tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": w["desc"], "global_batch": w["B"] * world, "parallelism": f"streams-dp{world}",
+                       "l2": "inputs exceed L2: each step streams %.0f MB of operands" % (total_b / 1e6)},
+            "clocks": clocks, "e2e": e2e,
+            "gpu_launches": args.steps * (4 if w["backward"] else 1),
+            "roofline": roof,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            val, dt, cores, sample = time_cpu(w, 1, 0)
+            line["cpu_baseline"] = {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_e2e(tb, w, host, dev, cfg, world, args):
+    """Same metric through the operator a user calls, starting from pinned HOST buffers: every step copies the
+    step's inputs to the device, runs forward (+ backward), and copies output and gradients back to the host."""
+    import torch.distributed as dist
+    names_in = ("xq", "xk", "xv", "ttt_lr_eta") + (("grad_output",) if w["backward"] else ())
+    pinned = {k: host[k].pin_memory() for k in names_in}
+    small = {k: host[k].to(dev) for k in ("weight", "bias", "token_eta", "ln_weight", "ln_bias")}
+    dbuf = {k: torch.empty_like(v, device=dev) for k, v in pinned.items()}
+    out_host = {}
+
+    def one():
+        for k in names_in:
+            dbuf[k].copy_(pinned[k], non_blocking=True)
+        ins = tb.TttInputs(dbuf["xq"], dbuf["xk"], dbuf["xv"], small["weight"], small["bias"], small["token_eta"],
+                           dbuf["ttt_lr_eta"], small["ln_weight"], small["ln_bias"])
+        outs, saved = tb.TttTileMultiKernel.forward_launch(ins, cfg)
+        res = {"output": outs.output}
+        if w["backward"]:
+            g = tb.TttTileMultiKernel.backward_launch(saved, tb.TttOutputs(dbuf["grad_output"], None, None), cfg)
+            res.update(grad_xq=g.xq, grad_xk=g.xk, grad_xv=g.xv, grad_lr=g.ttt_lr_eta, grad_w=g.weight,
+                       grad_b=g.bias, grad_te=g.token_eta, grad_lnw=g.ln_weight, grad_lnb=g.ln_bias)
+        for k, v in res.items():
+            if k not in out_host:
+                out_host[k] = torch.empty(v.shape, dtype=v.dtype, pin_memory=True)
+            out_host[k].copy_(v, non_blocking=True)
+        return res
+
+    for _ in range(2):
+        one()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    steps = max(3, min(args.steps, 10))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        one()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        tmax = torch.tensor([ms], device=dev)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        ms = tmax.item()
+    h2d = sum(v.numel() * v.element_size() for v in pinned.values())
+    d2h = sum(v.numel() * v.element_size() for v in out_host.values())
+    return {"value": w["B"] * w["T"] * world / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": steps}
+
+
+if __name__ == "__main__":
+    main()

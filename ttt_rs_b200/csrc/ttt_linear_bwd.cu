@@ -681,12 +681,12 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 2 : 1))
 //   d_token_eta[t]   = sum over streams of part_te[stream][t]
 //   d_ln_w/b[h][f]   = sum over batch of part_ln[b*H+h][0/1][f]
 //   packed (optional) = { sum_b dW[b,h], sum_b db[b,h], d_ln_w, d_ln_b, d_token_eta folded to [CS] }
+//                       (the fold is a second tiny kernel over the reduced d_token_eta)
 // ----------------------------------------------------------------------------------------------------
 __global__ void ttt_linear_bwd_reduce_kernel(const ReduceParams p) {
   const int H = p.H, B = p.B, T = p.T;
   const int n_te = T, n_ln = 2 * H * HD, n_w = (p.packed != nullptr) ? H * (HD * HD + HD) : 0;
-  const int n_fold = (p.packed != nullptr) ? CS : 0;
-  const int total = n_te + n_ln + n_w + n_fold;
+  const int total = n_te + n_ln + n_w;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
     if (i < n_te) {
       float acc = 0.f;
@@ -698,7 +698,7 @@ __global__ void ttt_linear_bwd_reduce_kernel(const ReduceParams p) {
       for (int b = 0; b < B; ++b) acc += p.part_ln[((size_t)(b * H + h) * 2 + which) * HD + f];
       (which == 0 ? p.d_ln_g : p.d_ln_b)[hf] = acc;
       if (p.packed != nullptr) p.packed[(size_t)H * HD * HD + H * HD + k] = acc;
-    } else if (i < n_te + n_ln + n_w) {
+    } else {
       const int k = i - n_te - n_ln;
       const bool is_w = k < H * HD * HD;
       const int h = is_w ? k / (HD * HD) : (k - H * HD * HD) / HD;
@@ -706,18 +706,19 @@ __global__ void ttt_linear_bwd_reduce_kernel(const ReduceParams p) {
       float acc = 0.f;
       for (int b = 0; b < B; ++b) acc += p.part_w[(size_t)(b * H + h) * (HD * HD + HD) + e];
       p.packed[k] = acc;
-    } else {
-      // token_eta gradient folded over stages: needs every stream's partial again (fixed order)
-      const int c = i - n_te - n_ln - n_w;
-      float acc = 0.f;
-      for (int s = 0; s < T / CS; ++s) {
-        float a2 = 0.f;
-        for (int st = 0; st < B * H; ++st) a2 += p.part_te[(size_t)st * T + s * CS + c];
-        acc += a2;
-      }
-      p.packed[(size_t)H * HD * HD + 3 * H * HD + c] = acc;
     }
   }
+}
+
+// token_eta gradient folded over stages into [CS] (runs after the kernel above, same stream): one warp per
+// mini-batch position, lanes stride over stages, fixed-order shuffle tree.
+__global__ void ttt_linear_bwd_fold_kernel(const ReduceParams p) {
+  const int c = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float acc = 0.f;
+  for (int s = lane; s < p.T / CS; s += 32) acc += p.d_token_eta[s * CS + c];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) p.packed[(size_t)p.H * HD * HD + 3 * p.H * HD + c] = acc;
 }
 
 template <typename T>
@@ -736,11 +737,12 @@ cudaError_t launch_linear_bwd(int dtype, const CUtensorMap* maps, const LinBwdPa
 }
 
 cudaError_t launch_linear_bwd_reduce(const ReduceParams& p, cudaStream_t st) {
-  const int total = p.T + 2 * p.H * HD + (p.packed != nullptr ? p.H * (HD * HD + HD) + CS : 0);
+  const int total = p.T + 2 * p.H * HD + (p.packed != nullptr ? p.H * (HD * HD + HD) : 0);
   const int threads = 128;
   int blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 8) blocks = 148 * 8;
   ttt_linear_bwd_reduce_kernel<<<blocks, threads, 0, st>>>(p);
+  if (p.packed != nullptr) ttt_linear_bwd_fold_kernel<<<1, CS * 32, 0, st>>>(p);
   return cudaGetLastError();
 }
 
