@@ -96,3 +96,18 @@ def test_host_wrapper_refuses_cpu_tensors():
     ins = ttt_rs_b200.TttInputs(*[t[k] for k in names])
     with pytest.raises(ttt_rs_b200.TttError):
         ttt_rs_b200.TttTileMultiKernel.forward_launch(ins, ttt_rs_b200.FusedTttConfig.new(16, 64, 1e-6))
+
+
+def test_cpp_host_mirror_compiles(tmp_path):
+    """The C++ mirror of the operator (host/fused_tile_multi.hpp) is valid C++17 against the public header."""
+    import subprocess
+    src = tmp_path / "t.cpp"
+    src.write_text('#include "ttt_rs_b200/host/fused_tile_multi.hpp"\n'
+                   'int main() { ttt_b200::FusedTttConfig c = ttt_b200::FusedTttConfig::make(16, 64, 1e-6f, 64);\n'
+                   '  return c.epsilon_scaled == 1000 ? 0 : 1; }\n')
+    exe = tmp_path / "t"
+    r = subprocess.run(["g++", "-std=c++17", "-Wall", "-Werror", "-I", str(REPO), str(src), "-o", str(exe),
+                        "-L", str(REPO / "ttt_rs_b200"), "-lttt_b200", f"-Wl,-rpath,{REPO / 'ttt_rs_b200'}"],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    assert subprocess.run([str(exe)]).returncode == 0
