@@ -116,6 +116,32 @@ int ttt_linear_backward(const ttt_dims* d, const void* xq, const void* xk, const
                         float* grad_ln_bias, float* outer_grad_packed, void* workspace, size_t workspace_bytes,
                         void* status, void* stream);
 
+/* Backward without a caller workspace.  (No counterpart in the reference: its host wrapper always allocates its
+ * scratch itself, backward/launch.rs:389-392.)
+ *
+ * For hosts that cannot get device memory where the backward is issued -- an operator hook that receives only the
+ * op's input and output buffers, a runtime whose pool has already claimed the device, a loop that must not call
+ * cudaMalloc because it stalls every stream of the device.  Arguments and results are exactly those of
+ * ttt_linear_backward minus `workspace` / `workspace_bytes`; the per-stream partial sums go to a fixed array of
+ * TTT_NOALLOC_SCRATCH_BYTES bytes inside the library, which every GPU that uses the library keeps resident until
+ * the process ends.  The function itself allocates nothing.
+ *   - Limit: ttt_linear_backward_workspace_bytes(d) must not exceed TTT_NOALLOC_SCRATCH_BYTES
+ *     (batch*heads*(seq_len + 4288)*4 bytes; B=32 H=12 T=2048 needs 9.7 MB).  Larger problems get TTT_ERR_WORKSPACE
+ *     and nothing is launched.
+ *   - The first call on each device looks up the array's device address (one-time set-up, with that device
+ *     current).  Make that first call outside any stream capture.
+ *   - All calls on a device share the one array: two calls whose kernels may overlap on the GPU (different
+ *     streams, no ordering between them) race on it.  Issue them on one stream or order them with events.
+ */
+#define TTT_NOALLOC_SCRATCH_BYTES (16u << 20)
+int ttt_linear_backward_noalloc(const ttt_dims* d, const void* xq, const void* xk, const void* xv,
+                                const void* weight, const void* bias, const void* token_eta,
+                                const void* ttt_lr_eta, const void* ln_weight, const void* ln_bias,
+                                const void* weight_ckpt, const void* bias_ckpt, const void* grad_output,
+                                void* grad_xq, void* grad_xk, void* grad_xv, void* grad_weight, void* grad_bias,
+                                void* grad_ttt_lr_eta, float* grad_token_eta, float* grad_ln_weight,
+                                float* grad_ln_bias, float* outer_grad_packed, void* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

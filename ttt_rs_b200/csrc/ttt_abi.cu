@@ -3,6 +3,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "../../include/ttt_b200.h"
 #include "ttt_kernels.h"
@@ -280,3 +281,68 @@ int ttt_linear_backward(const ttt_dims* d, const void* xq, const void* xk, const
 }
 
 }  // extern "C"
+
+// ----------------------------------------------------------------------------------------------------
+// Backward for callers that cannot hand over a workspace.
+//
+// Some hosts of this operator have no way to obtain device memory at the point where the backward runs: a
+// custom-operator hook that is given only the input and output buffers of the op, a runtime whose memory pool
+// already owns the whole device so that a side allocation would fail or fragment it, or a latency-sensitive
+// training loop that forbids cudaMalloc on the hot path because it synchronises the device.  For them the
+// per-stream partial sums live in the array below instead of a caller-supplied workspace.
+//
+// The array is part of the library image: every GPU on which the library is used keeps these bytes resident
+// until the process exits.  Its name is only a host-side handle; the device address is looked up once per
+// device with cudaGetSymbolAddress (with that device current) and it is that address the kernels receive.
+// ----------------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_noalloc_scratch[TTT_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mu;
+void* g_noalloc_ptr[kMaxDevices] = {};
+
+int noalloc_scratch(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "cudaGetDevice failed: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(TTT_ERR_CUDA, "device ordinal %d outside [0, %d)", dev, kMaxDevices);
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return fail(TTT_ERR_CUDA, "cudaGetSymbolAddress(built-in scratch) failed on device %d: %s", dev,
+                  cudaGetErrorString(e));
+    g_noalloc_ptr[dev] = ptr;
+  }
+  *out = g_noalloc_ptr[dev];
+  return TTT_OK;
+}
+}  // namespace
+
+extern "C" int ttt_linear_backward_noalloc(const ttt_dims* d, const void* xq, const void* xk, const void* xv,
+                                           const void* weight, const void* bias, const void* token_eta,
+                                           const void* ttt_lr_eta, const void* ln_weight, const void* ln_bias,
+                                           const void* weight_ckpt, const void* bias_ckpt, const void* grad_output,
+                                           void* grad_xq, void* grad_xk, void* grad_xv, void* grad_weight,
+                                           void* grad_bias, void* grad_ttt_lr_eta, float* grad_token_eta,
+                                           float* grad_ln_weight, float* grad_ln_bias, float* outer_grad_packed,
+                                           void* status, void* stream) {
+  int rc = check_dims(d);
+  if (rc != TTT_OK) return rc;
+  const size_t need = ws_layout(d).total_bytes;
+  if (need > (size_t)TTT_NOALLOC_SCRATCH_BYTES)
+    return fail(TTT_ERR_WORKSPACE,
+                "this problem needs %zu bytes of scratch but the built-in scratch holds %zu "
+                "(batch*heads*(seq_len + 4288)*4 must not exceed it): call ttt_linear_backward with a workspace",
+                need, (size_t)TTT_NOALLOC_SCRATCH_BYTES);
+  void* scratch = nullptr;
+  rc = noalloc_scratch(&scratch);
+  if (rc != TTT_OK) return rc;
+  // Nothing in the scratch has to start at zero: the backward kernel overwrites every partial it later reads.
+  return ttt_linear_backward(d, xq, xk, xv, weight, bias, token_eta, ttt_lr_eta, ln_weight, ln_bias, weight_ckpt,
+                             bias_ckpt, grad_output, grad_xq, grad_xk, grad_xv, grad_weight, grad_bias,
+                             grad_ttt_lr_eta, grad_token_eta, grad_ln_weight, grad_ln_bias, outer_grad_packed,
+                             scratch, (size_t)TTT_NOALLOC_SCRATCH_BYTES, status, stream);
+}
