@@ -24,13 +24,20 @@
 #include "ttt_kernels.h"
 #include "ttt_stage.cuh"
 
+#ifndef TTT_BWD_SG_BF16
+#define TTT_BWD_SG_BF16 16  // stages stashed per re-simulation pass (bf16 I/O)
+#endif
+#ifndef TTT_BWD_MINB_BF16
+#define TTT_BWD_MINB_BF16 2  // resident blocks per SM the bf16 kernel is compiled for
+#endif
+
 namespace ttt {
 
 template <typename T>
 struct BwdSmem {
   using TF = TileFmt<T>;
   static constexpr int NP = TF::NP;
-  static constexpr int SG = (sizeof(T) == 2) ? 16 : 8;  // stages stashed per re-simulation pass
+  static constexpr int SG = (sizeof(T) == 2) ? TTT_BWD_SG_BF16 : 8;  // stages stashed per re-simulation pass
   static constexpr int NSLOT = 2;
   static constexpr uint32_t PLANES = NP * TILE_BF16_BYTES;             // one operand tile
   static constexpr uint32_t OFF_Q = 0, OFF_K = TF::BYTES, OFF_V = 2 * TF::BYTES, OFF_DO = 2 * TF::BYTES + TF::RAW_BYTES;
@@ -102,7 +109,7 @@ struct OpIter {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 2 : 1))
+__global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 : 1))
     ttt_linear_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                           const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                           const __grid_constant__ CUtensorMap tm_dq, const __grid_constant__ CUtensorMap tm_dk,
