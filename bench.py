@@ -189,6 +189,7 @@ def main():
 
     import torch.distributed as dist
     import ttt_rs_b200 as tb
+    from ttt_rs_b200.distributed import allreduce_outer_grads
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -223,7 +224,7 @@ def main():
             if record:
                 e[2].record()
             if world > 1:
-                dist.all_reduce(packed)
+                allreduce_outer_grads(packed)
         if record:
             ev_pairs.append(e)
         return outs, g
