@@ -67,8 +67,13 @@ const char* ttt_b200_last_error(void);
 
 /* Number of checkpoints per (batch, head) stream: ceil((T / CS) / K)  (forward/launch.rs:221-223). */
 int64_t ttt_linear_num_checkpoints(const ttt_dims* d);
-/* Bytes of the two checkpoint buffers.  They are opaque saved state handed from forward to backward; this
- * library keeps them in float32 whatever `dtype` is: [B*H*NCK, F, F] and [B*H*NCK, F]. */
+/* Bytes of the two saved-state buffers the forward fills and the backward reads back (the role of the reference's
+ * weight_checkpoints / bias_checkpoints tensors, forward/launch.rs:221-226).  Both are opaque to the caller:
+ *   weight_ckpt: float32 W before every K-th stage plus the final W, [B*H*(NCK+1), F, F];
+ *   bias_ckpt:   per stage the lr-scaled LN gradient tile [B*H*T, F] of T, two float4 of row statistics per
+ *                token, and the float32 bias at the start of every stage.
+ * The backward walks W back from each checkpoint with the saved gradient tiles instead of re-simulating the
+ * forward, so `checkpoint_interval` only sets how often W is re-read exactly. */
 size_t ttt_linear_weight_ckpt_bytes(const ttt_dims* d);
 size_t ttt_linear_bias_ckpt_bytes(const ttt_dims* d);
 
@@ -82,7 +87,7 @@ size_t ttt_linear_bias_ckpt_bytes(const ttt_dims* d);
  *   output          T [B,H,T,F]   (out)
  *   weight_out      T [B,H,F,F]   (out) final state
  *   bias_out        T [B,H,F]     (out)
- *   weight_ckpt, bias_ckpt        (out) see ttt_linear_*_ckpt_bytes
+ *   weight_ckpt, bias_ckpt        (out) opaque saved state, ttt_linear_*_ckpt_bytes bytes each
  */
 int ttt_linear_forward(const ttt_dims* d, const void* xq, const void* xk, const void* xv, const void* weight,
                        const void* bias, const void* token_eta, const void* ttt_lr_eta, const void* ln_weight,

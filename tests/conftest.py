@@ -32,8 +32,12 @@ def rel_err(a, b):
     return (a - b).abs().max().item() / scale
 
 
-def assert_close(a, b, rtol, name):
-    """|a-b| <= rtol * (|b| + RMS(b)) elementwise: relative to each element plus the tensor's scale."""
+def assert_close(a, b, rtol, name, max_bad_frac=0.0):
+    """|a-b| <= rtol * (|b| + RMS(b)) elementwise: relative to each element plus the tensor's scale.
+
+    `max_bad_frac` > 0 applies the criterion statistically (used for bfloat16 results, whose storage rounding alone
+    reaches 5e-2 of the RMS on heavy-tailed tensors): at most that fraction of elements may lie outside, and the
+    relative L2 error must stay below rtol / 2."""
     import torch
 
     a = a.detach().double().cpu()
@@ -44,6 +48,11 @@ def assert_close(a, b, rtol, name):
     tol = rtol * (b.abs() + scale)
     diff = (a - b).abs()
     bad = diff > tol
+    if max_bad_frac > 0.0:
+        rel_l2 = ((a - b).norm() / (b.norm() + 1e-300)).item()
+        assert rel_l2 <= rtol / 2, f"{name}: relative L2 error {rel_l2:.3g} above {rtol / 2:g}"
+        if bad.double().mean().item() <= max_bad_frac:
+            return
     if bad.any():
         idx = torch.argmax(diff - tol).item()
         raise AssertionError(

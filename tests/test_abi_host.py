@@ -40,8 +40,9 @@ def test_every_declared_symbol_is_exported(lib):
 def test_checkpoint_and_workspace_sizes(lib):
     d = _dims(seq_len=80, checkpoint_interval=2)  # 5 stages -> 3 checkpoints
     assert lib.ttt_linear_num_checkpoints(C.byref(d)) == 3
-    assert lib.ttt_linear_weight_ckpt_bytes(C.byref(d)) == 2 * 2 * 3 * 64 * 64 * 4
-    assert lib.ttt_linear_bias_ckpt_bytes(C.byref(d)) == 2 * 2 * 3 * 64 * 4
+    assert lib.ttt_linear_weight_ckpt_bytes(C.byref(d)) == 2 * 2 * (3 + 1) * 64 * 64 * 4
+    rows, streams, ns = 2 * 2 * 80, 4, 5  # gradient tiles (bf16) + 32 B of statistics per token + per-stage biases
+    assert lib.ttt_linear_bias_ckpt_bytes(C.byref(d)) == rows * 64 * 2 + rows * 32 + streams * (ns + 1) * 64 * 4
     streams = 4
     assert lib.ttt_linear_backward_workspace_bytes(C.byref(d)) == 4 * (streams * 128 + streams * 80 + streams * (4096 + 64))
 

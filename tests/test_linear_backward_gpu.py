@@ -61,8 +61,9 @@ def test_backward_matches_oracle(dtype, B, H, NS, K):
     _, grads, _ = _run_gpu(t, K)
     ref = _oracle(t)
     r = RTOL[dtype]
+    frac = 1e-4 if dtype == torch.bfloat16 else 0.0
     for name in GRADS:
-        assert_close(getattr(grads, name), ref["grad_" + name], r, f"grad_{name}")
+        assert_close(getattr(grads, name), ref["grad_" + name], r, f"grad_{name}", max_bad_frac=frac)
 
 
 def test_backward_is_deterministic_and_packs_outer_grads():

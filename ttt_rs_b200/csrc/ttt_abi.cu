@@ -89,6 +89,23 @@ int64_t num_ckpt(const ttt_dims* d) {
   return (ns + d->checkpoint_interval - 1) / d->checkpoint_interval;
 }
 
+// Layout of the second saved-state buffer ("aux"): the lr-scaled LN gradient tiles Gp [B*H*T, 64] of the I/O type,
+// then two float4 of row statistics per token, then the float32 bias at the start of every stage (+ final).
+struct AuxLayout {
+  size_t off_gp, off_stats, off_bias, total_bytes;
+};
+AuxLayout aux_layout(const ttt_dims* d) {
+  const size_t rows = (size_t)d->batch * d->heads * d->seq_len;
+  const size_t streams = (size_t)d->batch * d->heads;
+  const size_t ns = (size_t)d->seq_len / d->mini_batch;
+  AuxLayout a;
+  a.off_gp = 0;
+  a.off_stats = a.off_gp + rows * 64 * (d->dtype == TTT_BF16 ? 2 : 4);
+  a.off_bias = a.off_stats + rows * 32;
+  a.total_bytes = a.off_bias + streams * (ns + 1) * 64 * sizeof(float);
+  return a;
+}
+
 // workspace layout of the backward (float32 words)
 struct WsLayout {
   size_t off_ln, off_te, off_w, total_bytes;
@@ -132,11 +149,11 @@ int64_t ttt_linear_num_checkpoints(const ttt_dims* d) {
 }
 size_t ttt_linear_weight_ckpt_bytes(const ttt_dims* d) {
   if (check_dims(d) != TTT_OK) return 0;
-  return (size_t)d->batch * d->heads * num_ckpt(d) * 64 * 64 * sizeof(float);
+  return (size_t)d->batch * d->heads * (num_ckpt(d) + 1) * 64 * 64 * sizeof(float);
 }
 size_t ttt_linear_bias_ckpt_bytes(const ttt_dims* d) {
   if (check_dims(d) != TTT_OK) return 0;
-  return (size_t)d->batch * d->heads * num_ckpt(d) * 64 * sizeof(float);
+  return aux_layout(d).total_bytes;
 }
 
 int ttt_linear_forward(const ttt_dims* d, const void* xq, const void* xk, const void* xv, const void* weight,
@@ -158,9 +175,11 @@ int ttt_linear_forward(const ttt_dims* d, const void* xq, const void* xk, const 
     return fail(TTT_ERR_ALIGN, "status is not 4-byte aligned");
 
   const int64_t rows = (int64_t)d->batch * d->heads * d->seq_len;
-  CUtensorMap maps[4];
-  const void* bases[4] = {xq, xk, xv, output};
-  for (int i = 0; i < 4; ++i) {
+  const AuxLayout al = aux_layout(d);
+  uint8_t* aux = static_cast<uint8_t*>(bias_ckpt);
+  CUtensorMap maps[5];
+  const void* bases[5] = {xq, xk, xv, output, aux + al.off_gp};
+  for (int i = 0; i < 5; ++i) {
     rc = make_tile_map(&maps[i], bases[i], rows, d->dtype);
     if (rc != TTT_OK) return rc;
   }
@@ -174,7 +193,8 @@ int ttt_linear_forward(const ttt_dims* d, const void* xq, const void* xk, const 
   p.w_out = weight_out;
   p.b_out = bias_out;
   p.w_ckpt = static_cast<float*>(weight_ckpt);
-  p.b_ckpt = static_cast<float*>(bias_ckpt);
+  p.stats = reinterpret_cast<float4*>(aux + al.off_stats);
+  p.b_stage = reinterpret_cast<float*>(aux + al.off_bias);
   p.status = static_cast<uint32_t*>(status);
   p.H = d->heads;
   p.T = d->seq_len;
@@ -232,9 +252,11 @@ int ttt_linear_backward(const ttt_dims* d, const void* xq, const void* xk, const
     return fail(TTT_ERR_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes, wl.total_bytes);
 
   const int64_t rows = (int64_t)d->batch * d->heads * d->seq_len;
-  CUtensorMap maps[7];
-  const void* bases[7] = {xq, xk, xv, grad_output, grad_xq, grad_xk, grad_xv};
-  for (int i = 0; i < 7; ++i) {
+  const AuxLayout al = aux_layout(d);
+  const uint8_t* aux = static_cast<const uint8_t*>(bias_ckpt);
+  CUtensorMap maps[8];
+  const void* bases[8] = {xq, xk, xv, grad_output, grad_xq, grad_xk, grad_xv, aux + al.off_gp};
+  for (int i = 0; i < 8; ++i) {
     rc = make_tile_map(&maps[i], bases[i], rows, d->dtype);
     if (rc != TTT_OK) return rc;
   }
@@ -247,7 +269,8 @@ int ttt_linear_backward(const ttt_dims* d, const void* xq, const void* xk, const
   p.ln_g = ln_weight;
   p.ln_b = ln_bias;
   p.w_ckpt = static_cast<const float*>(weight_ckpt);
-  p.b_ckpt = static_cast<const float*>(bias_ckpt);
+  p.stats = reinterpret_cast<const float4*>(aux + al.off_stats);
+  p.b_stage = reinterpret_cast<const float*>(aux + al.off_bias);
   p.d_w = grad_weight;
   p.d_b = grad_bias;
   p.d_lr = grad_ttt_lr_eta;

@@ -244,6 +244,21 @@ __device__ __forceinline__ uint32_t lane_off_B_kn(int lane, int nc) {
 }
 
 // ----------------------------------------------------------------------------------------------------
+// Packed float32x2 arithmetic (one instruction per column pair on sm_100).
+// ----------------------------------------------------------------------------------------------------
+typedef float2 F2;
+__device__ __forceinline__ F2 f2(float a) { return make_float2(a, a); }
+__device__ __forceinline__ F2 f2(float a, float b) { return make_float2(a, b); }
+__device__ __forceinline__ F2 f2fma(F2 a, F2 b, F2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ F2 f2mul(F2 a, F2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ F2 f2add(F2 a, F2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ F2 f2sub(F2 a, F2 b) { return __ffma2_rn(b, make_float2(-1.f, -1.f), a); }
+__device__ __forceinline__ F2 f2neg(F2 a) { return make_float2(-a.x, -a.y); }
+__device__ __forceinline__ float f2hsum(F2 a) { return a.x + a.y; }
+// accumulator quad {r0e0, r0e1, r1e0, r1e1} viewed as the column pair of row r
+__device__ __forceinline__ F2 pr(const float (&c)[4], int r) { return make_float2(c[2 * r], c[2 * r + 1]); }
+
+// ----------------------------------------------------------------------------------------------------
 // Reductions
 // ----------------------------------------------------------------------------------------------------
 // sum over the 4 lanes that share a row (lane bits 0,1)

@@ -16,8 +16,9 @@ struct LinFwdParams {
   const void* ln_b;       // [H,F]
   void* w_out;            // [B,H,F,F]
   void* b_out;            // [B,H,F]
-  float* w_ckpt;          // [B*H*NCK, F, F] float32
-  float* b_ckpt;          // [B*H*NCK, F]    float32
+  float* w_ckpt;          // [B*H*(NCK+1), F, F] float32: state before stage c*K for c < NCK, final state at c = NCK
+  float4* stats;          // [B*H*T][2]: (mean1, rstd1, A, Bv), (mean2, rstd2, 0, 0) per token
+  float* b_stage;         // [B*H*(NS+1), F] float32: bias at the start of every stage, final bias last
   uint32_t* status;       // device uint32[4] or null
   int H, T, NS, K, NCK;
   float eps;
@@ -31,7 +32,8 @@ struct LinBwdParams {
   const void* ln_g;
   const void* ln_b;
   const float* w_ckpt;
-  const float* b_ckpt;
+  const float4* stats;
+  const float* b_stage;
   void* d_w;        // [B,H,F,F] element type T (per batch element), nullable
   void* d_b;        // [B,H,F], nullable
   void* d_lr;       // [B,H,T]
@@ -54,10 +56,10 @@ struct ReduceParams {
   int B, H, T;
 };
 
-// dtype: 0 = float32, 1 = bfloat16.  maps: q, k, v, out.
+// dtype: 0 = float32, 1 = bfloat16.  maps: q, k, v, out, gp (saved lr-scaled LN gradient, [B*H*T, 64] of T).
 cudaError_t launch_linear_fwd(int dtype, const CUtensorMap* maps, const LinFwdParams& p, int nstreams,
                               cudaStream_t st);
-// maps: q, k, v, d_out, d_q, d_k, d_v.
+// maps: q, k, v, d_out, d_q, d_k, d_v, gp.
 cudaError_t launch_linear_bwd(int dtype, const CUtensorMap* maps, const LinBwdParams& p, int nstreams,
                               cudaStream_t st);
 cudaError_t launch_linear_bwd_reduce(const ReduceParams& p, cudaStream_t st);

@@ -1,5 +1,5 @@
 // Fused TTT-Linear backward scan for sm_100a: one 4-warp CTA per (batch, head) stream walks the mini-batches in
-// reverse, recomputing what it needs from the forward's checkpoints.
+// reverse.
 //
 // What it computes is the reference's multi-stage backward kernel
 // (rust/fused/src/linear_fused_tile/backward/kernel.rs:254-429 with the stage body backward/stage.rs:42-1006 and the
@@ -8,28 +8,22 @@
 // into the returned final state are zero (launch.rs:188-194).
 //
 // How it is organised here (none of this follows the reference's design):
-//   * Checkpoint groups are walked last to first.  A group (or sub-group of SG stages when the checkpoint interval
-//     is larger) is first re-simulated forward ONCE from its checkpoint; each simulated stage leaves in shared
-//     memory the lr-scaled LN gradient Gp (as tensor-core operand planes), its four row statistics and the stage's
-//     bias.  The reference instead re-simulates from the checkpoint for every stage.
+//   * No forward re-simulation.  The forward saved, per stage, the lr-scaled LN gradient tile Gp (the operand of its
+//     state update), four + two row statistics per token and the bias; per checkpoint interval it saved W in float32
+//     (and the final W).  Walking back, W_s is recovered in registers from W_{s+1} by re-applying the stage's rank-16
+//     update from Gp with the opposite sign; at every checkpoint boundary W is re-read exactly, which bounds the
+//     rounding drift of the reversal to one interval.  (The reference re-simulates the forward from the checkpoint
+//     for every stage, backward/kernel.rs:339-382.)
 //   * The state W^T and its gradient dW^T stay in registers as float32 accumulators (warp w owns rows n in
-//     [16w,16w+16)).  Walking back, W_s is recovered from W_{s+1} by re-applying the stage's rank-16 update with the
-//     opposite sign from the stashed Gp, so no per-stage copy of W is kept anywhere.
-//   * Products contracting over the feature axis that is split across warps (dZ.W^T, G.dW^T) read bf16 copies of
-//     W_s / dW and of the dZ tiles from shared memory; all other operands chain through registers
+//     [16w,16w+16)).  Products contracting over the feature axis that is split across warps (dZ.W^T, Gp.dW^T) read bf16
+//     copies of W_s / dW and of the dZ tiles from shared memory; all other operands chain through registers
 //     (accumulator -> A fragment, movmatrix for transposes).
+//   * Element-wise math runs on column pairs with packed float32x2 instructions.
 //   * The three gradients that the reference accumulates with float atomics (token_eta, LN weight/bias) are written as
 //     per-stream partials to a workspace and summed by a second kernel in a fixed order, so results are
 //     bitwise reproducible.
 #include "ttt_kernels.h"
 #include "ttt_stage.cuh"
-
-#ifndef TTT_BWD_SG_BF16
-#define TTT_BWD_SG_BF16 16  // stages stashed per re-simulation pass (bf16 I/O)
-#endif
-#ifndef TTT_BWD_MINB_BF16
-#define TTT_BWD_MINB_BF16 2  // resident blocks per SM the bf16 kernel is compiled for
-#endif
 
 namespace ttt {
 
@@ -37,87 +31,40 @@ template <typename T>
 struct BwdSmem {
   using TF = TileFmt<T>;
   static constexpr int NP = TF::NP;
-  static constexpr int SG = (sizeof(T) == 2) ? TTT_BWD_SG_BF16 : 8;  // stages stashed per re-simulation pass
   static constexpr int NSLOT = 2;
-  static constexpr uint32_t PLANES = NP * TILE_BF16_BYTES;             // one operand tile
-  static constexpr uint32_t OFF_Q = 0, OFF_K = TF::BYTES, OFF_V = 2 * TF::BYTES, OFF_DO = 2 * TF::BYTES + TF::RAW_BYTES;
-  static constexpr uint32_t SLOT = 2 * TF::BYTES + 2 * TF::RAW_BYTES;  // q, k (raw+planes), v, d_out (raw)
-  static constexpr uint32_t OFF_STASH = NSLOT * SLOT;                  // SG operand tiles of Gp
-  static constexpr uint32_t OFF_W = OFF_STASH + SG * PLANES;           // W_s^T, 4 sub-tiles [16 n][64 k]
-  static constexpr uint32_t OFF_DW = OFF_W + 4 * PLANES;               // dW^T, same layout
-  static constexpr uint32_t OFF_DZ = OFF_DW + 4 * PLANES;              // dZbar operand tile
-  static constexpr uint32_t OFF_DZ1 = OFF_DZ + PLANES;                 // dZ1 operand tile
-  static constexpr uint32_t OFF_OUT = OFF_DZ1 + PLANES;                // staging: dq, dk, dv (raw format)
-  static constexpr uint32_t OFF_STAT = OFF_OUT + 3 * TF::RAW_BYTES;    // SG x 16 rows x float4 (mean, rstd, A, Bv)
-  static constexpr uint32_t OFF_BIAS = OFF_STAT + SG * 256;            // SG x 64 floats
-  static constexpr uint32_t OFF_LR = OFF_BIAS + SG * 256;              // NSLOT x 64 bytes
-  static constexpr uint32_t OFF_XCH = OFF_LR + NSLOT * 64;             // 2 x Xch4
+  static constexpr uint32_t PLANES = NP * TILE_BF16_BYTES;  // one operand tile
+  // one slot = the tiles of one stage: q, k, gp (raw + operand planes), v, d_out (raw), then small records
+  static constexpr uint32_t OFF_Q = 0, OFF_K = TF::BYTES, OFF_G = 2 * TF::BYTES, OFF_V = 3 * TF::BYTES;
+  static constexpr uint32_t OFF_DO = OFF_V + TF::RAW_BYTES;
+  static constexpr uint32_t OFF_STAT = OFF_DO + TF::RAW_BYTES;  // 16 tokens x 2 float4
+  static constexpr uint32_t OFF_BS = OFF_STAT + 512;            // 64 floats: bias at the start of the stage
+  static constexpr uint32_t OFF_LR = OFF_BS + 256;              // 16 x element
+  static constexpr uint32_t SLOT = OFF_STAT + 1024;
+  static constexpr uint32_t OFF_W = NSLOT * SLOT;               // W_s^T, 4 sub-tiles [16 n][64 k]
+  static constexpr uint32_t OFF_DW = OFF_W + 4 * PLANES;        // dW^T, same layout
+  static constexpr uint32_t OFF_DZ = OFF_DW + 4 * PLANES;       // dZbar operand tile
+  static constexpr uint32_t OFF_DZ1 = OFF_DZ + PLANES;          // dZ1 operand tile
+  static constexpr uint32_t OFF_OUT = OFF_DZ1 + PLANES;         // staging: dq, dk, dv (raw format)
+  static constexpr uint32_t OFF_XCH = OFF_OUT + 3 * TF::RAW_BYTES;
   static constexpr uint32_t OFF_BAR = OFF_XCH + 2 * sizeof(Xch4);
   static constexpr uint32_t TOTAL = OFF_BAR + NSLOT * 8;
   static constexpr uint32_t DYN_BYTES = TOTAL + 1024;
 };
 
-// Order in which stages are visited: for each checkpoint group (last first), for each sub-group of SG stages
-// (last first): simulate stages g0..e-1 forward (stashing those >= a), then run the backward of stages e-1..a.
-struct OpIter {
-  int K, NS, SG;
-  int gi, si, g0, g1, a, e, s;
-  bool sim, done, first;
-  __device__ __forceinline__ void start_sub() {
-    a = g0 + si * SG;
-    e = min(a + SG, g1);
-    sim = true;
-    s = g0;
-    first = true;
-  }
-  __device__ __forceinline__ void start_group() {
-    g0 = gi * K;
-    g1 = min(g0 + K, NS);
-    si = (g1 - g0 + SG - 1) / SG - 1;
-    start_sub();
-  }
-  __device__ __forceinline__ void init(int K_, int NS_, int NCK, int SG_) {
-    K = K_;
-    NS = NS_;
-    SG = SG_;
-    gi = NCK - 1;
-    done = false;
-    start_group();
-  }
-  __device__ __forceinline__ void next() {
-    if (done) return;
-    first = false;
-    if (sim) {
-      if (s + 1 < e) {
-        ++s;
-      } else {
-        sim = false;
-        s = e - 1;
-      }
-    } else if (s > a) {
-      --s;
-    } else if (si > 0) {
-      --si;
-      start_sub();
-    } else if (gi > 0) {
-      --gi;
-      start_group();
-    } else {
-      done = true;
-    }
-  }
-};
+#ifndef TTT_BWD_MINB_BF16
+#define TTT_BWD_MINB_BF16 2  // resident blocks per SM the bf16 kernel is compiled for
+#endif
 
 template <typename T>
 __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 : 1))
     ttt_linear_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                           const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                           const __grid_constant__ CUtensorMap tm_dq, const __grid_constant__ CUtensorMap tm_dk,
-                          const __grid_constant__ CUtensorMap tm_dv, const LinBwdParams p) {
+                          const __grid_constant__ CUtensorMap tm_dv, const __grid_constant__ CUtensorMap tm_g,
+                          const LinBwdParams p) {
   using TF = TileFmt<T>;
   using SM = BwdSmem<T>;
   constexpr int NP = TF::NP;
-  constexpr bool TWO_PASS = (sizeof(T) == 4);
   constexpr uint32_t PL = TILE_BF16_BYTES;  // plane stride
 
   extern __shared__ uint8_t smem_raw[];
@@ -125,8 +72,6 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
   const uint32_t base = (raw_u32 + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (base - raw_u32);
   Xch4* xch = reinterpret_cast<Xch4*>(gbase + SM::OFF_XCH);
-  float4* stat = reinterpret_cast<float4*>(gbase + SM::OFF_STAT);  // [SG][16]
-  float* bstash = reinterpret_cast<float*>(gbase + SM::OFF_BIAS);  // [SG][64]
   const uint32_t bar0 = base + SM::OFF_BAR;
   const uint32_t tW = base + SM::OFF_W, tDW = base + SM::OFF_DW, tDZ = base + SM::OFF_DZ, tDZ1 = base + SM::OFF_DZ1;
 
@@ -135,12 +80,14 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
   const int stream = blockIdx.x;
   const int head = stream % p.H;
   const int row_base = stream * p.T;
+  const int NS = p.NS;
 
   if (tid == 0) {
     prefetch_tmap(&tm_q);
     prefetch_tmap(&tm_k);
     prefetch_tmap(&tm_v);
     prefetch_tmap(&tm_do);
+    prefetch_tmap(&tm_g);
     prefetch_tmap(&tm_dq);
     prefetch_tmap(&tm_dk);
     prefetch_tmap(&tm_dv);
@@ -149,42 +96,36 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
   }
   __syncthreads();
 
-  // loads of one visit: K, V, lr always; Q and d_out only for a backward visit
-  auto issue_loads = [&](int n, int s, bool sim) {
+  // everything stage s needs, into slot n % NSLOT
+  auto issue_loads = [&](int n, int s) {
     const int slot = n % SM::NSLOT;
     const uint32_t bar = bar0 + 8 * slot;
     const uint32_t sl = base + slot * SM::SLOT;
     const int r0 = row_base + s * CS;
-    mbar_expect_tx(bar, (sim ? 2u : 4u) * TF::RAW_BYTES + CS * TF::ELT);
+    mbar_expect_tx(bar, 5u * TF::RAW_BYTES + 512u + 256u + CS * TF::ELT);
     tma_load_tile<T>(sl + SM::OFF_K, &tm_k, r0, bar);
+    tma_load_tile<T>(sl + SM::OFF_G, &tm_g, r0, bar);
+    tma_load_tile<T>(sl + SM::OFF_Q, &tm_q, r0, bar);
     tma_load_tile<T>(sl + SM::OFF_V, &tm_v, r0, bar);
-    if (!sim) {
-      tma_load_tile<T>(sl + SM::OFF_Q, &tm_q, r0, bar);
-      tma_load_tile<T>(sl + SM::OFF_DO, &tm_do, r0, bar);
-    }
-    bulk_load_1d(base + SM::OFF_LR + slot * 64, static_cast<const uint8_t*>(p.lr) + (size_t)r0 * TF::ELT,
-                 CS * TF::ELT, bar);
+    tma_load_tile<T>(sl + SM::OFF_DO, &tm_do, r0, bar);
+    bulk_load_1d(sl + SM::OFF_STAT, p.stats + (size_t)r0 * 2, 512u, bar);
+    bulk_load_1d(sl + SM::OFF_BS, p.b_stage + ((size_t)stream * (NS + 1) + s) * HD, 256u, bar);
+    bulk_load_1d(sl + SM::OFF_LR, static_cast<const uint8_t*>(p.lr) + (size_t)r0 * TF::ELT, CS * TF::ELT, bar);
   };
+  if (tid == 0) issue_loads(0, NS - 1);
 
-  OpIter cur, ahead;
-  cur.init(p.K, p.NS, p.NCK, SM::SG);
-  ahead = cur;
-  if (tid == 0) issue_loads(0, ahead.s, ahead.sim);
-  ahead.next();
-
-  // ---- per-thread constants and accumulators (4 owned columns, rows g and g+8)
-  float gam[4], bet[4];
+  // ---- per-thread constants and accumulators (column pairs nt = 0,1; rows g and g+8)
+  F2 gam[2], bet[2];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int c = nb + 8 * (j >> 1) + 2 * t + (j & 1);
-    gam[j] = ld_as_float<T>(p.ln_g, (size_t)head * HD + c);
-    bet[j] = ld_as_float<T>(p.ln_b, (size_t)head * HD + c);
+  for (int nt = 0; nt < 2; ++nt) {
+    const int c = nb + 8 * nt + 2 * t;
+    gam[nt] = f2(ld_as_float<T>(p.ln_g, (size_t)head * HD + c), ld_as_float<T>(p.ln_g, (size_t)head * HD + c + 1));
+    bet[nt] = f2(ld_as_float<T>(p.ln_b, (size_t)head * HD + c), ld_as_float<T>(p.ln_b, (size_t)head * HD + c + 1));
   }
   const float te_row[2] = {ld_as_float<T>(p.token_eta, g), ld_as_float<T>(p.token_eta, g + 8)};
   const float te15 = ld_as_float<T>(p.token_eta, CS - 1);
-  float bias[4] = {0.f, 0.f, 0.f, 0.f};
-  float dbias[4] = {0.f, 0.f, 0.f, 0.f};                                    // gradient w.r.t. the bias after this stage
-  float dgam[4] = {0.f, 0.f, 0.f, 0.f}, dbet[4] = {0.f, 0.f, 0.f, 0.f};     // un-reduced over the 8 row lanes
+  F2 dbias[2] = {f2(0.f), f2(0.f)};                                 // gradient w.r.t. the bias after this stage
+  F2 dgam[2] = {f2(0.f), f2(0.f)}, dbet[2] = {f2(0.f), f2(0.f)};    // un-reduced over the 8 row lanes
   float wt[8][4], dwt[8][4];
 #pragma unroll
   for (int kt = 0; kt < 8; ++kt)
@@ -196,44 +137,42 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
 
   int xsel = 0;
   bool failed = false;
-  int n = 0;  // visit counter (slot = n % NSLOT)
 
-  // `ahead` stays exactly one visit in front of `cur`; its loads are issued during the current visit
-  for (; !cur.done; cur.next(), ahead.next(), ++n) {
-    const int s = cur.s;
+  for (int s = NS - 1, n = 0; s >= 0; --s, ++n) {
     const int slot = n % SM::NSLOT;
     const uint32_t sl = base + slot * SM::SLOT;
-    const uint32_t tq = sl + SM::OFF_Q, tk = sl + SM::OFF_K, tv = sl + SM::OFF_V, tdo = sl + SM::OFF_DO;
-    const uint32_t pq = tq + TF::PLANE_OFF, pk = tk + TF::PLANE_OFF;
-    const int j = s - cur.a;  // stash index (valid when s >= a)
-    const uint32_t tG = base + SM::OFF_STASH + (uint32_t)(j < 0 ? 0 : j) * SM::PLANES;
+    const uint32_t tq = sl + SM::OFF_Q, tk = sl + SM::OFF_K, tg = sl + SM::OFF_G, tv = sl + SM::OFF_V, tdo = sl + SM::OFF_DO;
+    const uint32_t pq = tq + TF::PLANE_OFF, pk = tk + TF::PLANE_OFF, pg = tg + TF::PLANE_OFF;
+    const uint8_t* gsl = gbase + slot * SM::SLOT;
 
-    if (cur.first) {
-      // state at the group's checkpoint (float32)
-      const size_t ck = (size_t)stream * p.NCK + cur.gi;
-      const float* wc = p.w_ckpt + ck * HD * HD;
+    // ---- at the last stage of a checkpoint interval: exact state after the stage (= next checkpoint / final W)
+    {
+      const int gi = s / p.K;
+      const int g1 = min((gi + 1) * p.K, NS);
+      if (s == g1 - 1) {
+        const float* wc = p.w_ckpt + ((size_t)stream * (p.NCK + 1) + gi + 1) * HD * HD;
 #pragma unroll
-      for (int kt = 0; kt < 8; ++kt)
+        for (int kt = 0; kt < 8; ++kt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) wt[kt][i] = wc[(8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1)];
-#pragma unroll
-      for (int jj = 0; jj < 4; ++jj) bias[jj] = p.b_ckpt[ck * HD + nb + 8 * (jj >> 1) + 2 * t + (jj & 1)];
+          for (int i = 0; i < 4; ++i) wt[kt][i] = wc[(8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1)];
+      }
     }
 
     int fail = mbar_wait_bounded(bar0 + 8 * slot, (n / SM::NSLOT) & 1) ? 0 : 1;
     bool next_issued = false;
     auto issue_next = [&]() {
-      // runs right after the first CTA barrier of this visit: every thread has left the previous visit,
+      // runs right after the first CTA barrier of this stage: every thread has left the previous stage,
       // so the other slot may be overwritten
       if (!next_issued) {
         next_issued = true;
-        if (tid == 0 && !ahead.done) issue_loads(n + 1, ahead.s, ahead.sim);
+        if (tid == 0 && s > 0) issue_loads(n + 1, s - 1);
       }
     };
     if constexpr (NP == 3) {
       if (!fail) {
         split_tile_f32(tk, tid);
-        if (!cur.sim) split_tile_f32(tq, tid);
+        split_tile_f32(tq, tid);
+        split_tile_f32(tg, tid);
       }
       fail = __syncthreads_or(fail);
       if (fail) {
@@ -243,89 +182,22 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       }
       issue_next();
     }
-    const float lr_row[2] = {ld_as_float<T>(gbase + SM::OFF_LR + slot * 64, g),
-                             ld_as_float<T>(gbase + SM::OFF_LR + slot * 64, g + 8)};
+    const float lr_row[2] = {ld_as_float<T>(gsl + SM::OFF_LR, g), ld_as_float<T>(gsl + SM::OFF_LR, g + 8)};
+    const float4* stat = reinterpret_cast<const float4*>(gsl + SM::OFF_STAT);
+    const float* bsv = reinterpret_cast<const float*>(gsl + SM::OFF_BS);
 
-    if (cur.sim) {
-      // =========================== forward re-simulation of stage s ===========================
-      float z1[2][4];
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) z1[nt][i] = bias[2 * nt + (i & 1)];
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-        Pk<NP> bw[2][2], ak[4];
-        bfrag_from_state<NP>(wt, ks, bw);
-        ldsm_np<NP>(ak, pk + lane_off_A(lane, 16 * ks), PL, false);
-        mma_np<NP>(z1[0], ak, bw[0]);
-        mma_np<NP>(z1[1], ak, bw[1]);
-      }
-      float mean[2], rstd[2];
-      ln_row_stats<TWO_PASS>(z1, xch, xsel, L, p.eps, mean, rstd, fail);
-      if (fail) {
-        failed = true;
-        if (tid == 0) report_timeout(p.status, 12, s);
-        break;
-      }
-      issue_next();
-      float gp[2][4];
-      {
-        float xh[2][4], gy[2][4], gx[2][4], sa[2], sb[2];
-        ln_l2_pieces<T>(z1, mean, rstd, gam, bet, tk, tv, L, xh, gy, gx, sa, sb);
-        float2 a0, a1;
-        int f2 = 0;
-        xch_rows2(&xch[xsel], L, sa[0], sb[0], sa[1], sb[1], a0, a1, f2);
-        xsel ^= 1;
-        const float A[2] = {a0.x * (1.f / HD), a1.x * (1.f / HD)}, Bv[2] = {a0.y * (1.f / HD), a1.y * (1.f / HD)};
-        g_from_pieces(gx, xh, A, Bv, rstd, gp);
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) gp[nt][i] *= lr_row[i >> 1];
-        if (j >= 0) {
-          if (warp == 0 && t == 0) {
-            stat[j * CS + g] = make_float4(mean[0], rstd[0], A[0], Bv[0]);
-            stat[j * CS + g + 8] = make_float4(mean[1], rstd[1], A[1], Bv[1]);
-          }
-          if (g == 0) {
-#pragma unroll
-            for (int jj = 0; jj < 4; ++jj) bstash[j * HD + nb + 8 * (jj >> 1) + 2 * t + (jj & 1)] = bias[jj];
-          }
-        }
-      }
-      Pk<NP> gt[2][2];
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          const Pk<NP> pkd = split_pack<NP>(gp[nt][2 * r], gp[nt][2 * r + 1]);
-          if (j >= 0) {
-            const uint32_t a = tG + off_bf16(g + 8 * r, nb + 8 * nt + 2 * t);
-#pragma unroll
-            for (int pp = 0; pp < NP; ++pp) asm volatile("st.shared.b32 [%0], %1;" ::"r"(a + pp * PL), "r"(pkd.p[pp]) : "memory");
-          }
-          gt[nt][r] = movm_t_np<NP>(pkd);
-        }
-      {
-        const Pk<NP> agt[4] = {gt[0][0], gt[1][0], gt[0][1], gt[1][1]};
-        state_update<NP>(wt, agt, pk, lane, -te15);
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-          for (int e = 0; e < 2; ++e) bias[2 * nt + e] -= te15 * col_sum(gp[nt][e] + gp[nt][2 + e]);
-      }
-      continue;
-    }
-
-    // =============================== backward of stage s ===============================
-    // ---- 1. W_s from W_{s+1}: undo the stage's update with the stashed Gp; b_s from the stash
+    // ---- 1. W_s from W_{s+1}: undo the stage's update with the saved Gp; b_s as saved
+    float bias[4];
     {
       Pk<NP> agt[4];
-      ldsm_np<NP>(agt, tG + lane_off_B_nk(lane, nb), PL, true);
+      ldsm_np<NP>(agt, pg + lane_off_B_nk(lane, nb), PL, true);
       state_update<NP>(wt, agt, pk, lane, te15);
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) bias[jj] = bstash[j * HD + nb + 8 * (jj >> 1) + 2 * t + (jj & 1)];
+      for (int nt = 0; nt < 2; ++nt) {
+        const float2 b2 = *reinterpret_cast<const float2*>(bsv + nb + 8 * nt + 2 * t);
+        bias[2 * nt] = b2.x;
+        bias[2 * nt + 1] = b2.y;
+      }
     }
     // ---- 2. operand copies of W_s^T and dW^T (this warp's 16 rows) for the products that contract over n
 #pragma unroll
@@ -364,16 +236,19 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       mma_np<NP>(at[0], aq, bj0);
       mma_np<NP>(at[1], aq, bj1);
     }
-    // ---- 4. LN + L2 pieces of Z1 from the stashed row statistics
-    float mean1[2], rstd1[2], Bv1[2];
-    float xh[2][4], gy[2][4], gx[2][4], G[2][4];
+    // ---- 4. LN + L2 pieces of Z1 from the saved row statistics
+    float mean1[2], rstd1[2], Bv1[2], mean2[2], rstd2[2];
+    F2 xh[2][2], gy[2][2], gx[2][2], G[2][2];
     {
-      const float4 st0 = stat[j * CS + g], st1 = stat[j * CS + g + 8];
-      mean1[0] = st0.x; rstd1[0] = st0.y; mean1[1] = st1.x; rstd1[1] = st1.y;
-      const float A[2] = {st0.z, st1.z};
-      Bv1[0] = st0.w; Bv1[1] = st1.w;
+      const float4 sa0 = stat[2 * g], sb0 = stat[2 * g + 1], sa1 = stat[2 * (g + 8)], sb1 = stat[2 * (g + 8) + 1];
+      mean1[0] = sa0.x; rstd1[0] = sa0.y; mean1[1] = sa1.x; rstd1[1] = sa1.y;
+      const float A[2] = {sa0.z, sa1.z};
+      Bv1[0] = sa0.w; Bv1[1] = sa1.w;
+      mean2[0] = sb0.x; rstd2[0] = sb0.y; mean2[1] = sb1.x; rstd2[1] = sb1.y;
+      F2 z1p[2][2];
+      slab_pairs(z1, z1p);
       float sa[2], sb[2];
-      ln_l2_pieces<T>(z1, mean1, rstd1, gam, bet, tk, tv, L, xh, gy, gx, sa, sb);
+      ln_l2_pieces<T>(z1p, mean1, rstd1, gam, bet, tk, tv, L, xh, gy, gx, sa, sb);
       g_from_pieces(gx, xh, A, Bv1, rstd1, G);
     }
     // ---- 5. Zbar = Zq - M' Gp   (am holds -M')
@@ -383,72 +258,61 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
         const int i = g + 8 * r, jj = 8 * jt + 2 * t;
-        const float m0 = (jj <= i) ? -te_row[r] * (1.f + at[jt][2 * r]) : 0.f;
-        const float m1 = (jj + 1 <= i) ? -te_row[r] * (1.f + at[jt][2 * r + 1]) : 0.f;
-        am[2 * jt + r] = split_pack<NP>(m0, m1);
+        const F2 m = f2fma(pr(at[jt], r), f2(-te_row[r]), f2(-te_row[r]));
+        am[2 * jt + r] = split_pack<NP>((jj <= i) ? m.x : 0.f, (jj + 1 <= i) ? m.y : 0.f);
       }
     {
       Pk<NP> bg[4];
-      ldsm_np<NP>(bg, tG + lane_off_B_kn(lane, nb), PL, true);
+      ldsm_np<NP>(bg, pg + lane_off_B_kn(lane, nb), PL, true);
       const Pk<NP> b0[2] = {bg[0], bg[1]}, b1[2] = {bg[2], bg[3]};
       mma_np<NP>(zq[0], am, b0);
       mma_np<NP>(zq[1], am, b1);
     }
-    // ---- 6. LN statistics of Zbar; 7. LN backward of the output -> dZbar
-    float dzb[2][4], dzsum[4];
+    // ---- 6/7. LN backward of the output (row statistics of Zbar saved by the forward) -> dZbar
+    F2 dzb[2][2], dzsum[2];
     float dq[2][4];
     {
-      float mean2[2], rstd2[2];
-      ln_row_stats<TWO_PASS>(zq, xch, xsel, L, p.eps, mean2, rstd2, fail);
+      F2 xz[2][2], tt[2][2];
+      F2 p1[2] = {f2(0.f), f2(0.f)}, p2[2] = {f2(0.f), f2(0.f)};
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const F2 d = ld_pair<T>(tdo, g + 8 * r, nb + 8 * nt + 2 * t);
+          const F2 x = f2mul(f2sub(pr(zq[nt], r), f2(mean2[r])), f2(rstd2[r]));
+          xz[nt][r] = x;
+          dq[nt][2 * r] = d.x;
+          dq[nt][2 * r + 1] = d.y;
+          dgam[nt] = f2fma(d, x, dgam[nt]);
+          dbet[nt] = f2add(dbet[nt], d);
+          const F2 tv_ = f2mul(d, gam[nt]);
+          tt[nt][r] = tv_;
+          p1[r] = f2add(p1[r], tv_);
+          p2[r] = f2fma(tv_, x, p2[r]);
+        }
+      float2 a0, a1;
+      xch_rows2(&xch[xsel], L, f2hsum(p1[0]), f2hsum(p2[0]), f2hsum(p1[1]), f2hsum(p2[1]), a0, a1, fail);
+      xsel ^= 1;
       if (fail) {
         failed = true;
         if (tid == 0) report_timeout(p.status, 13, s);
         break;
       }
       issue_next();
-      float s1[2] = {0.f, 0.f}, s2[2] = {0.f, 0.f};
-      float tt[2][4];
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          const float2 dv = ld_pair<T>(tdo, g + 8 * r, nb + 8 * nt + 2 * t);
-          const float d[2] = {dv.x, dv.y};
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int i = 2 * r + e, jj = 2 * nt + e;
-            const float xz = (zq[nt][i] - mean2[r]) * rstd2[r];
-            zq[nt][i] = xz;  // keep x_hat of Zbar
-            dq[nt][i] = d[e];
-            dgam[jj] += d[e] * xz;
-            dbet[jj] += d[e];
-            const float tv_ = d[e] * gam[jj];
-            tt[nt][i] = tv_;
-            s1[r] += tv_;
-            s2[r] += tv_ * xz;
-          }
-        }
-      float2 a0, a1;
-      int f2 = 0;
-      xch_rows2(&xch[xsel], L, s1[0], s2[0], s1[1], s2[1], a0, a1, f2);
-      xsel ^= 1;
       const float c1[2] = {a0.x * (1.f / HD), a1.x * (1.f / HD)}, c2[2] = {a0.y * (1.f / HD), a1.y * (1.f / HD)};
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int r = i >> 1;
-          dzb[nt][i] = (tt[nt][i] - c1[r] - zq[nt][i] * c2[r]) * rstd2[r];
-        }
-#pragma unroll
-      for (int jj = 0; jj < 4; ++jj) dzsum[jj] = dzb[jj >> 1][jj & 1] + dzb[jj >> 1][2 + (jj & 1)];
+        for (int r = 0; r < 2; ++r)
+          dzb[nt][r] = f2mul(f2fma(xz[nt][r], f2(-c2[r]), f2sub(tt[nt][r], f2(c1[r]))), f2(rstd2[r]));
+      dzsum[0] = f2add(dzb[0][0], dzb[0][1]);
+      dzsum[1] = f2add(dzb[1][0], dzb[1][1]);
     }
-    // ---- 8. dZbar to shared memory as an operand tile; barrier also publishes tW / tDW
+    // ---- 8. dZbar to shared memory as an operand tile; the barrier also publishes tW / tDW
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int r = 0; r < 2; ++r)
-        st_pair_planes<NP>(tDZ, g + 8 * r, nb + 8 * nt + 2 * t, dzb[nt][2 * r], dzb[nt][2 * r + 1]);
+      for (int r = 0; r < 2; ++r) st_pair_planes<NP>(tDZ, g + 8 * r, nb + 8 * nt + 2 * t, dzb[nt][r].x, dzb[nt][r].y);
     __syncthreads();
 
     // ---- 9. products that need dZbar
@@ -461,9 +325,9 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
     for (int ks = 0; ks < 4; ++ks) {
       Pk<NP> adz[4], bgn[4], bwt[4], ags[4], bdw[4];
       ldsm_np<NP>(adz, tDZ + lane_off_A(lane, 16 * ks), PL, false);
-      ldsm_np<NP>(bgn, tG + lane_off_B_nk(lane, 16 * ks), PL, false);
+      ldsm_np<NP>(bgn, pg + lane_off_B_nk(lane, 16 * ks), PL, false);
       ldsm_np<NP>(bwt, tW + ks * SM::PLANES + lane_off_B_kn(lane, nb), PL, true);
-      ldsm_np<NP>(ags, tG + lane_off_A(lane, 16 * ks), PL, false);
+      ldsm_np<NP>(ags, pg + lane_off_A(lane, 16 * ks), PL, false);
       ldsm_np<NP>(bdw, tDW + ks * SM::PLANES + lane_off_B_kn(lane, nb), PL, true);
       {  // P' = dZbar Gp^T (16x16)
         const Pk<NP> b0[2] = {bgn[0], bgn[1]}, b1[2] = {bgn[2], bgn[3]};
@@ -482,20 +346,23 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       }
     }
     // dM' = -tril(P');  dA = dM' o te[i];  d te[i] = sum_j dM'[i,j] (1 + Attn[i,j])
-    float dte_row[2] = {0.f, 0.f};
+    float dte_row[2];
     Pk<NP> ada[4];
+    {
+      F2 acc[2] = {f2(0.f), f2(0.f)};
 #pragma unroll
-    for (int jt = 0; jt < 2; ++jt)
+      for (int jt = 0; jt < 2; ++jt)
 #pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        const int i = g + 8 * r, jj = 8 * jt + 2 * t;
-        const float d0 = (jj <= i) ? -pp[jt][2 * r] : 0.f;
-        const float d1 = (jj + 1 <= i) ? -pp[jt][2 * r + 1] : 0.f;
-        dte_row[r] += d0 * (1.f + at[jt][2 * r]) + d1 * (1.f + at[jt][2 * r + 1]);
-        ada[2 * jt + r] = split_pack<NP>(d0 * te_row[r], d1 * te_row[r]);
-      }
-    dte_row[0] = quad_sum(dte_row[0]);
-    dte_row[1] = quad_sum(dte_row[1]);
+        for (int r = 0; r < 2; ++r) {
+          const int i = g + 8 * r, jj = 8 * jt + 2 * t;
+          const F2 d = f2((jj <= i) ? -pp[jt][2 * r] : 0.f, (jj + 1 <= i) ? -pp[jt][2 * r + 1] : 0.f);
+          acc[r] = f2add(acc[r], f2fma(d, pr(at[jt], r), d));
+          const F2 da = f2mul(d, f2(te_row[r]));
+          ada[2 * jt + r] = split_pack<NP>(da.x, da.y);
+        }
+      dte_row[0] = quad_sum(f2hsum(acc[0]));
+      dte_row[1] = quad_sum(f2hsum(acc[1]));
+    }
     {
       Pk<NP> bkt[4], bqt[4], bdz[4];
       ldsm_np<NP>(bkt, pk + lane_off_B_kn(lane, nb), PL, true);
@@ -527,34 +394,34 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       }
     }
     // ---- 10. gradient reaching Gp, the lr / token_eta terms, and the first pair of second-derivative sums
-    float u[2][4], v[2][4];
+    F2 u[2][2], v[2][2];
     float s1t[2], s2t[2];
     {
-      float p1[2] = {0.f, 0.f}, p2[2] = {0.f, 0.f}, dl[2] = {0.f, 0.f}, rt[2] = {0.f, 0.f};
+      F2 p1[2] = {f2(0.f), f2(0.f)}, p2[2] = {f2(0.f), f2(0.f)}, pdl[2] = {f2(0.f), f2(0.f)}, prt[2] = {f2(0.f), f2(0.f)};
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-          const float2 kv = ld_pair<T>(tk, g + 8 * r, nb + 8 * nt + 2 * t);
-          const float kk[2] = {kv.x, kv.y};
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int i = 2 * r + e, jj = 2 * nt + e;
-            const float dg = dgp[nt][i] - te15 * (kdw[nt][i] + dbias[jj]);  // dL/dGp
-            dk[nt][i] -= te15 * gl[nt][i];
-            rt[r] += kk[e] * gl[nt][i] + (lr_row[r] * G[nt][i]) * dbias[jj];
-            dl[r] += dg * G[nt][i];
-            const float uu = lr_row[r] * dg;  // dL/dG
-            const float vv = -uu * rstd1[r];
-            u[nt][i] = uu;
-            v[nt][i] = vv;
-            p1[r] += vv;
-            p2[r] += vv * xh[nt][i];
-          }
+          const F2 kk = ld_pair<T>(tk, g + 8 * r, nb + 8 * nt + 2 * t);
+          const F2 glp = pr(gl[nt], r);
+          // dL/dGp = -M'^T dZbar - te15 (K dW + db)
+          const F2 dg = f2fma(f2add(pr(kdw[nt], r), dbias[nt]), f2(-te15), pr(dgp[nt], r));
+          const F2 dkn = f2fma(glp, f2(-te15), pr(dk[nt], r));
+          dk[nt][2 * r] = dkn.x;
+          dk[nt][2 * r + 1] = dkn.y;
+          prt[r] = f2fma(kk, glp, f2fma(f2mul(G[nt][r], f2(lr_row[r])), dbias[nt], prt[r]));
+          pdl[r] = f2fma(dg, G[nt][r], pdl[r]);
+          const F2 uu = f2mul(dg, f2(lr_row[r]));  // dL/dG
+          const F2 vv = f2mul(uu, f2(-rstd1[r]));
+          u[nt][r] = uu;
+          v[nt][r] = vv;
+          p1[r] = f2add(p1[r], vv);
+          p2[r] = f2fma(vv, xh[nt][r], p2[r]);
         }
       float4 o0, o1;
-      int f2 = 0;
-      xch_rows(&xch[xsel], L, make_float4(p1[0], p2[0], dl[0], rt[0]), make_float4(p1[1], p2[1], dl[1], rt[1]), o0, o1, f2);
+      int f2_ = 0;
+      xch_rows(&xch[xsel], L, make_float4(f2hsum(p1[0]), f2hsum(p2[0]), f2hsum(pdl[0]), f2hsum(prt[0])),
+               make_float4(f2hsum(p1[1]), f2hsum(p2[1]), f2hsum(pdl[1]), f2hsum(prt[1])), o0, o1, f2_);
       xsel ^= 1;
       s1t[0] = o0.x * (1.f / HD); s2t[0] = o0.y * (1.f / HD);
       s1t[1] = o1.x * (1.f / HD); s2t[1] = o1.y * (1.f / HD);
@@ -568,44 +435,41 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       }
     }
     // ---- 11. second derivative through LN + L2 gradient -> dZ1, dT
-    float dz1[2][4], dT[2][4];
+    F2 dz1[2][2], dT[2][2];
     {
-      float pd[2] = {0.f, 0.f}, ps[2] = {0.f, 0.f};
-      float dxh[2][4];
+      F2 pd[2] = {f2(0.f), f2(0.f)}, ps[2] = {f2(0.f), f2(0.f)};
+      F2 dxh[2][2];
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int r = i >> 1, jj = 2 * nt + (i & 1);
-          const float dgxh = -v[nt][i] + s1t[r] + xh[nt][i] * s2t[r];
-          const float dy = gam[jj] * dgxh;
-          dgam[jj] += gy[nt][i] * dgxh + dy * xh[nt][i];
-          dbet[jj] += dy;
-          const float dx = dy * gam[jj] + gx[nt][i] * s2t[r] + v[nt][i] * Bv1[r];
-          dxh[nt][i] = dx;
-          dT[nt][i] = -dy;
-          pd[r] += dx;
-          ps[r] -= (dx * xh[nt][i] + u[nt][i] * G[nt][i]) * rstd1[r];
+        for (int r = 0; r < 2; ++r) {
+          const F2 x = xh[nt][r], vv = v[nt][r];
+          const F2 dgxh = f2fma(x, f2(s2t[r]), f2sub(f2(s1t[r]), vv));
+          const F2 dy = f2mul(gam[nt], dgxh);
+          dgam[nt] = f2fma(gy[nt][r], dgxh, f2fma(dy, x, dgam[nt]));
+          dbet[nt] = f2add(dbet[nt], dy);
+          const F2 dx = f2fma(dy, gam[nt], f2fma(gx[nt][r], f2(s2t[r]), f2mul(vv, f2(Bv1[r]))));
+          dxh[nt][r] = dx;
+          dT[nt][r] = f2neg(dy);
+          pd[r] = f2add(pd[r], dx);
+          ps[r] = f2fma(f2fma(dx, x, f2mul(u[nt][r], G[nt][r])), f2(-rstd1[r]), ps[r]);
         }
       float2 a0, a1;
-      int f2 = 0;
-      xch_rows2(&xch[xsel], L, pd[0], ps[0], pd[1], ps[1], a0, a1, f2);
+      int f2_ = 0;
+      xch_rows2(&xch[xsel], L, f2hsum(pd[0]), f2hsum(ps[0]), f2hsum(pd[1]), f2hsum(ps[1]), a0, a1, f2_);
       xsel ^= 1;
       const float D[2] = {a0.x * (1.f / HD), a1.x * (1.f / HD)}, S[2] = {a0.y * (1.f / HD), a1.y * (1.f / HD)};
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int r = i >> 1;
-          dz1[nt][i] = (dxh[nt][i] - D[r]) * rstd1[r] + xh[nt][i] * S[r];
-        }
+        for (int r = 0; r < 2; ++r)
+          dz1[nt][r] = f2fma(f2sub(dxh[nt][r], f2(D[r])), f2(rstd1[r]), f2mul(xh[nt][r], f2(S[r])));
     }
     // ---- 12. dZ1 to shared memory as an operand tile
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int r = 0; r < 2; ++r)
-        st_pair_planes<NP>(tDZ1, g + 8 * r, nb + 8 * nt + 2 * t, dz1[nt][2 * r], dz1[nt][2 * r + 1]);
+      for (int r = 0; r < 2; ++r) st_pair_planes<NP>(tDZ1, g + 8 * r, nb + 8 * nt + 2 * t, dz1[nt][r].x, dz1[nt][r].y);
     if (tid == 0) bulk_wait_read<0>();  // the previous stage's output tiles have left the staging buffers
     __syncthreads();
     // ---- 13. dk += dZ1 W^T ; dW^T += dZ1^T K ; bias gradient
@@ -631,8 +495,10 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       }
     }
 #pragma unroll
-    for (int jj = 0; jj < 4; ++jj)
-      dbias[jj] += col_sum(dzsum[jj] + dz1[jj >> 1][jj & 1] + dz1[jj >> 1][2 + (jj & 1)]);
+    for (int nt = 0; nt < 2; ++nt) {
+      const F2 cs = f2add(dzsum[nt], f2add(dz1[nt][0], dz1[nt][1]));
+      dbias[nt] = f2add(dbias[nt], f2(col_sum(cs.x), col_sum(cs.y)));
+    }
     // ---- 14. outputs: dq = d_out + ..., dk = -dT + ..., dv = dT
     {
       const uint32_t so_q = base + SM::OFF_OUT, so_k = so_q + TF::RAW_BYTES, so_v = so_k + TF::RAW_BYTES;
@@ -641,9 +507,10 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
           const int row = g + 8 * r, col = nb + 8 * nt + 2 * t;
+          const F2 dkk = f2sub(pr(dk[nt], r), dT[nt][r]);
           st_pair<T>(so_q, row, col, dq[nt][2 * r], dq[nt][2 * r + 1]);
-          st_pair<T>(so_k, row, col, dk[nt][2 * r] - dT[nt][2 * r], dk[nt][2 * r + 1] - dT[nt][2 * r + 1]);
-          st_pair<T>(so_v, row, col, dT[nt][2 * r], dT[nt][2 * r + 1]);
+          st_pair<T>(so_k, row, col, dkk.x, dkk.y);
+          st_pair<T>(so_v, row, col, dT[nt][r].x, dT[nt][r].y);
         }
       fence_proxy_async_smem();
       __syncthreads();
@@ -669,14 +536,19 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
         if (p.part_w != nullptr) p.part_w[(size_t)stream * (HD * HD + HD) + idx] = dwt[kt][i];
       }
 #pragma unroll
-    for (int jj = 0; jj < 4; ++jj) {
-      const float dg_ = col_sum(dgam[jj]), db_ = col_sum(dbet[jj]);
+    for (int nt = 0; nt < 2; ++nt) {
+      const float dg_[2] = {col_sum(dgam[nt].x), col_sum(dgam[nt].y)};
+      const float db_[2] = {col_sum(dbet[nt].x), col_sum(dbet[nt].y)};
+      const float dbi[2] = {dbias[nt].x, dbias[nt].y};
       if (g == 0) {
-        const int c = nb + 8 * (jj >> 1) + 2 * t + (jj & 1);
-        st_from_float<T>(p.d_b, (size_t)stream * HD + c, dbias[jj]);
-        if (p.part_w != nullptr) p.part_w[(size_t)stream * (HD * HD + HD) + HD * HD + c] = dbias[jj];
-        p.part_ln[(size_t)stream * 2 * HD + c] = dg_;
-        p.part_ln[(size_t)stream * 2 * HD + HD + c] = db_;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int c = nb + 8 * nt + 2 * t + e;
+          st_from_float<T>(p.d_b, (size_t)stream * HD + c, dbi[e]);
+          if (p.part_w != nullptr) p.part_w[(size_t)stream * (HD * HD + HD) + HD * HD + c] = dbi[e];
+          p.part_ln[(size_t)stream * 2 * HD + c] = dg_[e];
+          p.part_ln[(size_t)stream * 2 * HD + HD + c] = db_[e];
+        }
       }
     }
   }
@@ -733,7 +605,7 @@ static cudaError_t launch_bwd_t(const CUtensorMap* m, const LinBwdParams& p, int
   auto kfn = ttt_linear_bwd_kernel<T>;
   cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BwdSmem<T>::DYN_BYTES);
   if (e != cudaSuccess) return e;
-  kfn<<<nstreams, NTHREADS, BwdSmem<T>::DYN_BYTES, st>>>(m[0], m[1], m[2], m[3], m[4], m[5], m[6], p);
+  kfn<<<nstreams, NTHREADS, BwdSmem<T>::DYN_BYTES, st>>>(m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], p);
   return cudaGetLastError();
 }
 

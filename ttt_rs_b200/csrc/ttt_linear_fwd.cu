@@ -27,8 +27,8 @@ template <typename T>
 struct FwdSmem {
   using TF = TileFmt<T>;
   static constexpr uint32_t SLOT = 3 * TF::BYTES;                  // q, k, v
-  static constexpr uint32_t OFF_OUT = FWD_NST * SLOT;              // 2 staging tiles (raw format)
-  static constexpr uint32_t OFF_LR = OFF_OUT + 2 * TF::RAW_BYTES;  // FWD_NST x 64 bytes
+  static constexpr uint32_t OFF_OUT = FWD_NST * SLOT;              // staging (raw format): 2 x output, 2 x Gp
+  static constexpr uint32_t OFF_LR = OFF_OUT + 4 * TF::RAW_BYTES;  // FWD_NST x 64 bytes
   static constexpr uint32_t OFF_XCH = OFF_LR + FWD_NST * 64;       // 2 x Xch4
   static constexpr uint32_t OFF_BAR = OFF_XCH + 2 * sizeof(Xch4);
   static constexpr uint32_t TOTAL = OFF_BAR + FWD_NST * 8;
@@ -39,7 +39,7 @@ template <typename T>
 __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     ttt_linear_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                           const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
-                          const LinFwdParams p) {
+                          const __grid_constant__ CUtensorMap tm_g, const LinFwdParams p) {
   using TF = TileFmt<T>;
   using SM = FwdSmem<T>;
   constexpr int NP = TF::NP;
@@ -64,6 +64,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     prefetch_tmap(&tm_k);
     prefetch_tmap(&tm_v);
     prefetch_tmap(&tm_o);
+    prefetch_tmap(&tm_g);
     for (int i = 0; i < FWD_NST; ++i) mbar_init(bar0 + 8 * i, 1);
     fence_mbar_init();
   }
@@ -86,16 +87,16 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
   }
 
   // ---- per-thread constants: 4 owned columns c(nt,e) = nb + 8nt + 2t + e, rows g and g+8
-  float gam[4], bet[4], bias[4];
+  F2 gam[2], bet[2];
+  float bias[4];
 #pragma unroll
-  for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const int c = nb + 8 * nt + 2 * t + e;
-      gam[2 * nt + e] = ld_as_float<T>(p.ln_g, (size_t)head * HD + c);
-      bet[2 * nt + e] = ld_as_float<T>(p.ln_b, (size_t)head * HD + c);
-      bias[2 * nt + e] = ld_as_float<T>(p.b0, (size_t)stream * HD + c);
-    }
+  for (int nt = 0; nt < 2; ++nt) {
+    const int c = nb + 8 * nt + 2 * t;
+    gam[nt] = f2(ld_as_float<T>(p.ln_g, (size_t)head * HD + c), ld_as_float<T>(p.ln_g, (size_t)head * HD + c + 1));
+    bet[nt] = f2(ld_as_float<T>(p.ln_b, (size_t)head * HD + c), ld_as_float<T>(p.ln_b, (size_t)head * HD + c + 1));
+    bias[2 * nt] = ld_as_float<T>(p.b0, (size_t)stream * HD + c);
+    bias[2 * nt + 1] = ld_as_float<T>(p.b0, (size_t)stream * HD + c + 1);
+  }
   const float te_row[2] = {ld_as_float<T>(p.token_eta, g), ld_as_float<T>(p.token_eta, g + 8)};
   const float te15 = ld_as_float<T>(p.token_eta, CS - 1);
 
@@ -130,18 +131,18 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
       }
     }
 
-    // ---- checkpoint (state before this stage's update)
+    // ---- saved state: W before the update of every K-th stage, the bias before every stage
     if (s % p.K == 0) {
-      const size_t ck = (size_t)stream * p.NCK + s / p.K;
-      float* wc = p.w_ckpt + ck * HD * HD;
+      float* wc = p.w_ckpt + ((size_t)stream * (p.NCK + 1) + s / p.K) * HD * HD;
 #pragma unroll
       for (int kt = 0; kt < 8; ++kt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) wc[(8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1)] = wt[kt][i];
-      if (g == 0) {
+    }
+    if (g == 0) {
+      float* bs = p.b_stage + ((size_t)stream * (NS + 1) + s) * HD;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) p.b_ckpt[ck * HD + nb + 8 * (j >> 1) + 2 * t + (j & 1)] = bias[j];
-      }
+      for (int j = 0; j < 4; ++j) bs[nb + 8 * (j >> 1) + 2 * t + (j & 1)] = bias[j];
     }
 
     const float lr_row[2] = {ld_as_float<T>(gbase + SM::OFF_LR + slot * 64, g),
@@ -177,34 +178,47 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
 
     // ---- LN statistics of Z1, then G = dL/dZ1 and Gp = lr[row] * G
     float mean[2], rstd[2];
-    ln_row_stats<TWO_PASS>(z1, xch, xsel, L, p.eps, mean, rstd, fail);
+    F2 z1p[2][2];
+    slab_pairs(z1, z1p);
+    ln_row_stats<TWO_PASS>(z1p, xch, xsel, L, p.eps, mean, rstd, fail);
     if (fail) {
       failed = true;
       if (tid == 0) report_timeout(p.status, 2, s);
       break;
     }
-    float gp[2][4];
+    F2 gp[2][2];
+    float4 st1[2];  // saved row statistics of Z1: (mean, rstd, mean(gx), mean(gx * x_hat))
     {
-      float xh[2][4], gy[2][4], gx[2][4], sa[2], sb[2];
-      ln_l2_pieces<T>(z1, mean, rstd, gam, bet, tk, tv, L, xh, gy, gx, sa, sb);
+      F2 xh[2][2], gy[2][2], gx[2][2];
+      float sa[2], sb[2];
+      ln_l2_pieces<T>(z1p, mean, rstd, gam, bet, tk, tv, L, xh, gy, gx, sa, sb);
       float2 a0, a1;
-      int f2 = 0;
-      xch_rows2(&xch[xsel], L, sa[0], sb[0], sa[1], sb[1], a0, a1, f2);
+      int f2_ = 0;
+      xch_rows2(&xch[xsel], L, sa[0], sb[0], sa[1], sb[1], a0, a1, f2_);
       xsel ^= 1;
       const float A[2] = {a0.x * (1.f / HD), a1.x * (1.f / HD)}, Bv[2] = {a0.y * (1.f / HD), a1.y * (1.f / HD)};
-      g_from_pieces(gx, xh, A, Bv, rstd, gp);
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) gp[nt][i] *= lr_row[i >> 1];
+      const float rs[2] = {rstd[0] * lr_row[0], rstd[1] * lr_row[1]};
+      g_from_pieces(gx, xh, A, Bv, rs, gp);
+      st1[0] = make_float4(mean[0], rstd[0], A[0], Bv[0]);
+      st1[1] = make_float4(mean[1], rstd[1], A[1], Bv[1]);
     }
 
     // ---- Gp as tensor-core operands, transposed through movmatrix: gt[nt][r] = (Gp block rows 8r.., cols nb+8nt..)^T
+    // The same values go to the saved Gp tile the backward reads (bf16: exactly the operand bits used here).
+    const uint32_t sg = base + SM::OFF_OUT + (2 + (s & 1)) * TF::RAW_BYTES;
     Pk<NP> gt[2][2];
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int r = 0; r < 2; ++r) gt[nt][r] = movm_t_np<NP>(split_pack<NP>(gp[nt][2 * r], gp[nt][2 * r + 1]));
+      for (int r = 0; r < 2; ++r) {
+        const Pk<NP> pkd = split_pack<NP>(gp[nt][r].x, gp[nt][r].y);
+        if constexpr (NP == 1) {
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(sg + off_bf16(g + 8 * r, nb + 8 * nt + 2 * t)), "r"(pkd.p[0]) : "memory");
+        } else {
+          st_pair<T>(sg, g + 8 * r, nb + 8 * nt + 2 * t, gp[nt][r].x, gp[nt][r].y);
+        }
+        gt[nt][r] = movm_t_np<NP>(pkd);
+      }
 
     // ---- Zbar = Zq - M' Gp,  M'[i][j] = te[i] (1 + Attn[i][j]) for j <= i
     {
@@ -214,9 +228,8 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
           const int i = g + 8 * r, j = 8 * jt + 2 * t;
-          const float m0 = (j <= i) ? -te_row[r] * (1.f + at[jt][2 * r]) : 0.f;
-          const float m1 = (j + 1 <= i) ? -te_row[r] * (1.f + at[jt][2 * r + 1]) : 0.f;
-          am[2 * jt + r] = split_pack<NP>(m0, m1);
+          const F2 m = f2fma(pr(at[jt], r), f2(-te_row[r]), f2(-te_row[r]));
+          am[2 * jt + r] = split_pack<NP>((j <= i) ? m.x : 0.f, (j + 1 <= i) ? m.y : 0.f);
         }
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
@@ -230,29 +243,40 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
       const Pk<NP> agt[4] = {gt[0][0], gt[1][0], gt[0][1], gt[1][1]};
       state_update<NP>(wt, agt, pk, lane, -te15);
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int e = 0; e < 2; ++e) bias[2 * nt + e] -= te15 * col_sum(gp[nt][e] + gp[nt][2 + e]);
+      for (int nt = 0; nt < 2; ++nt) {
+        const F2 cs = f2add(gp[nt][0], gp[nt][1]);
+        bias[2 * nt] -= te15 * col_sum(cs.x);
+        bias[2 * nt + 1] -= te15 * col_sum(cs.y);
+      }
     }
 
     // ---- out = Q + LN(Zbar)
     int fl2 = 0;
-    ln_row_stats<TWO_PASS>(zq, xch, xsel, L, p.eps, mean, rstd, fl2);
+    F2 zb[2][2];
+    slab_pairs(zq, zb);
+    ln_row_stats<TWO_PASS>(zb, xch, xsel, L, p.eps, mean, rstd, fl2);
+    if (L.warp == 0 && t == 0) {
+      float4* sp = p.stats + ((size_t)row_base + (size_t)s * CS) * 2;
+      sp[2 * g] = st1[0];
+      sp[2 * g + 1] = make_float4(mean[0], rstd[0], 0.f, 0.f);
+      sp[2 * (g + 8)] = st1[1];
+      sp[2 * (g + 8) + 1] = make_float4(mean[1], rstd[1], 0.f, 0.f);
+    }
     const uint32_t so = base + SM::OFF_OUT + (s & 1) * TF::RAW_BYTES;
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
         const int row = g + 8 * r, col = nb + 8 * nt + 2 * t;
-        const float2 qv = ld_pair<T>(tq, row, col);
-        const float o0 = qv.x + gam[2 * nt] * ((zq[nt][2 * r] - mean[r]) * rstd[r]) + bet[2 * nt];
-        const float o1 = qv.y + gam[2 * nt + 1] * ((zq[nt][2 * r + 1] - mean[r]) * rstd[r]) + bet[2 * nt + 1];
-        st_pair<T>(so, row, col, o0, o1);
+        const F2 x = f2mul(f2sub(zb[nt][r], f2(mean[r])), f2(rstd[r]));
+        const F2 o = f2add(ld_pair<T>(tq, row, col), f2fma(gam[nt], x, bet[nt]));
+        st_pair<T>(so, row, col, o.x, o.y);
       }
     fence_proxy_async_smem();
     __syncthreads();
     if (tid == 0) {
       tma_store_tile<T>(&tm_o, row_base + s * CS, so);
+      tma_store_tile<T>(&tm_g, row_base + s * CS, sg);
       bulk_commit();
       bulk_wait_read<1>();
       if (s + FWD_NST < NS) issue_loads(s + FWD_NST);
@@ -260,17 +284,23 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
   }
 
   if (!failed) {
-    // ---- final state
+    // ---- final state (returned, and kept as the last checkpoint / last bias record for the backward)
+    float* wc = p.w_ckpt + ((size_t)stream * (p.NCK + 1) + p.NCK) * HD * HD;
 #pragma unroll
     for (int kt = 0; kt < 8; ++kt)
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        st_from_float<T>(p.w_out, (size_t)stream * HD * HD + (8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1),
-                         wt[kt][i]);
+      for (int i = 0; i < 4; ++i) {
+        const int idx = (8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1);
+        st_from_float<T>(p.w_out, (size_t)stream * HD * HD + idx, wt[kt][i]);
+        wc[idx] = wt[kt][i];
+      }
     if (g == 0) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        st_from_float<T>(p.b_out, (size_t)stream * HD + nb + 8 * (j >> 1) + 2 * t + (j & 1), bias[j]);
+      for (int j = 0; j < 4; ++j) {
+        const int c = nb + 8 * (j >> 1) + 2 * t + (j & 1);
+        st_from_float<T>(p.b_out, (size_t)stream * HD + c, bias[j]);
+        p.b_stage[((size_t)stream * (NS + 1) + NS) * HD + c] = bias[j];
+      }
     }
   }
   if (tid == 0) bulk_wait_all<0>();
@@ -281,7 +311,7 @@ static cudaError_t launch_fwd_t(const CUtensorMap* m, const LinFwdParams& p, int
   auto kfn = ttt_linear_fwd_kernel<T>;
   cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FwdSmem<T>::DYN_BYTES);
   if (e != cudaSuccess) return e;
-  kfn<<<nstreams, NTHREADS, FwdSmem<T>::DYN_BYTES, st>>>(m[0], m[1], m[2], m[3], p);
+  kfn<<<nstreams, NTHREADS, FwdSmem<T>::DYN_BYTES, st>>>(m[0], m[1], m[2], m[3], m[4], p);
   return cudaGetLastError();
 }
 

@@ -66,16 +66,15 @@ __device__ __forceinline__ void xch_rows2(Xch4* xb, const Lane& L, float a0x, fl
 
 // LayerNorm row statistics of a slab: mean and 1/sqrt(var + eps) for rows g and g+8.
 // bf16 I/O uses one exchange (sum, sum of squares); float32 I/O uses the two-pass variance of the reference.
+// Slabs here are column pairs: F2 z[nt][r] = columns (nb + 8nt + 2t, +1) of row g + 8r.
 template <bool TWO_PASS>
-__device__ __forceinline__ void ln_row_stats(const float (&z)[2][4], Xch4* xch, int& xsel, const Lane& L, float eps,
+__device__ __forceinline__ void ln_row_stats(const F2 (&z)[2][2], Xch4* xch, int& xsel, const Lane& L, float eps,
                                              float (&mean)[2], float (&rstd)[2], int& flag) {
   float s1[2], s2[2] = {0.f, 0.f};
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
-    s1[r] = (z[0][2 * r] + z[0][2 * r + 1]) + (z[1][2 * r] + z[1][2 * r + 1]);
-    if constexpr (!TWO_PASS)
-      s2[r] = (z[0][2 * r] * z[0][2 * r] + z[0][2 * r + 1] * z[0][2 * r + 1]) +
-              (z[1][2 * r] * z[1][2 * r] + z[1][2 * r + 1] * z[1][2 * r + 1]);
+    s1[r] = f2hsum(f2add(z[0][r], z[1][r]));
+    if constexpr (!TWO_PASS) s2[r] = f2hsum(f2fma(z[0][r], z[0][r], f2mul(z[1][r], z[1][r])));
   }
   float2 a0, a1;
   xch_rows2(&xch[xsel], L, s1[0], s2[0], s1[1], s2[1], a0, a1, flag);
@@ -89,21 +88,23 @@ __device__ __forceinline__ void ln_row_stats(const float (&z)[2][4], Xch4* xch, 
     float q2[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-      float acc = 0.f;
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const float d = z[nt][2 * r + e] - mean[r];
-          acc += d * d;
-        }
-      q2[r] = acc;
+      const F2 d0 = f2sub(z[0][r], f2(mean[r])), d1 = f2sub(z[1][r], f2(mean[r]));
+      q2[r] = f2hsum(f2fma(d0, d0, f2mul(d1, d1)));
     }
-    int f2 = 0;
-    xch_rows2(&xch[xsel], L, q2[0], 0.f, q2[1], 0.f, a0, a1, f2);
+    int f2_ = 0;
+    xch_rows2(&xch[xsel], L, q2[0], 0.f, q2[1], 0.f, a0, a1, f2_);
     xsel ^= 1;
     rstd[0] = 1.0f / sqrtf(a0.x * (1.f / HD) + eps);
     rstd[1] = 1.0f / sqrtf(a1.x * (1.f / HD) + eps);
+  }
+}
+
+// accumulator registers of a 16x16 slab (two n-tiles) viewed as column pairs
+__device__ __forceinline__ void slab_pairs(const float (&c)[2][4], F2 (&z)[2][2]) {
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+    z[nt][0] = pr(c[nt], 0);
+    z[nt][1] = pr(c[nt], 1);
   }
 }
 
@@ -120,44 +121,42 @@ __device__ __forceinline__ void bfrag_from_state(const float (&m)[8][4], int ks,
 
 // LN + L2 gradient pieces for one slab of Z1 given its row statistics.
 // Outputs x_hat, gy = gamma*x_hat + beta - (v - k), gx = gy*gamma and the per-thread partial row sums of gx, gx*x_hat.
+// gam / bet: the thread's column pairs, index nt.
 template <typename T>
-__device__ __forceinline__ void ln_l2_pieces(const float (&z1)[2][4], const float (&mean)[2], const float (&rstd)[2],
-                                             const float (&gam)[4], const float (&bet)[4], uint32_t tk, uint32_t tv,
-                                             const Lane& L, float (&xh)[2][4], float (&gy)[2][4], float (&gx)[2][4],
+__device__ __forceinline__ void ln_l2_pieces(const F2 (&z1)[2][2], const float (&mean)[2], const float (&rstd)[2],
+                                             const F2 (&gam)[2], const F2 (&bet)[2], uint32_t tk, uint32_t tv,
+                                             const Lane& L, F2 (&xh)[2][2], F2 (&gy)[2][2], F2 (&gx)[2][2],
                                              float (&sa)[2], float (&sb)[2]) {
-  sa[0] = sa[1] = sb[0] = sb[1] = 0.f;
+  F2 pa[2] = {f2(0.f), f2(0.f)}, pb[2] = {f2(0.f), f2(0.f)};
 #pragma unroll
   for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       const int row = L.g + 8 * r, col = L.nb + 8 * nt + 2 * L.t;
-      const float2 kv = ld_pair<T>(tk, row, col), vv = ld_pair<T>(tv, row, col);
-      const float tg[2] = {vv.x - kv.x, vv.y - kv.y};
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int i = 2 * r + e, j = 2 * nt + e;
-        const float x = (z1[nt][i] - mean[r]) * rstd[r];
-        const float y = gam[j] * x + bet[j] - tg[e];
-        const float gg = y * gam[j];
-        xh[nt][i] = x;
-        gy[nt][i] = y;
-        gx[nt][i] = gg;
-        sa[r] += gg;
-        sb[r] += gg * x;
-      }
+      const F2 tg = f2sub(ld_pair<T>(tv, row, col), ld_pair<T>(tk, row, col));
+      const F2 x = f2mul(f2sub(z1[nt][r], f2(mean[r])), f2(rstd[r]));
+      const F2 y = f2fma(gam[nt], x, f2sub(bet[nt], tg));
+      const F2 gg = f2mul(y, gam[nt]);
+      xh[nt][r] = x;
+      gy[nt][r] = y;
+      gx[nt][r] = gg;
+      pa[r] = f2add(pa[r], gg);
+      pb[r] = f2fma(gg, x, pb[r]);
     }
+  sa[0] = f2hsum(pa[0]);
+  sa[1] = f2hsum(pa[1]);
+  sb[0] = f2hsum(pb[0]);
+  sb[1] = f2hsum(pb[1]);
 }
 
-// G = (gx - A - x_hat*Bv) * rstd with A = mean(gx), Bv = mean(gx*x_hat) per row.
-__device__ __forceinline__ void g_from_pieces(const float (&gx)[2][4], const float (&xh)[2][4], const float (&A)[2],
-                                              const float (&Bv)[2], const float (&rstd)[2], float (&G)[2][4]) {
+// G = (gx - A - x_hat*Bv) * rstd * scale with A = mean(gx), Bv = mean(gx*x_hat) per row (scale: e.g. lr of the row).
+__device__ __forceinline__ void g_from_pieces(const F2 (&gx)[2][2], const F2 (&xh)[2][2], const float (&A)[2],
+                                              const float (&Bv)[2], const float (&rs)[2], F2 (&G)[2][2]) {
 #pragma unroll
   for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int r = i >> 1;
-      G[nt][i] = (gx[nt][i] - A[r] - xh[nt][i] * Bv[r]) * rstd[r];
-    }
+    for (int r = 0; r < 2; ++r)
+      G[nt][r] = f2mul(f2fma(xh[nt][r], f2(-Bv[r]), f2sub(gx[nt][r], f2(A[r]))), f2(rs[r]));
 }
 
 // State update of one stage from Gp = lr o G held as transposed A fragments (agt = {n-lo/tok-lo, n-hi/tok-lo,

@@ -171,8 +171,11 @@ class TttTileMultiKernel:
         output = torch.empty_like(inputs.xq)
         weight_out = torch.empty_like(inputs.weight)
         bias_out = torch.empty_like(inputs.bias)
-        w_ck = torch.empty((B * H * nck, F, F), dtype=torch.float32, device=dev)
-        b_ck = torch.empty((B * H * nck, F), dtype=torch.float32, device=dev)
+        # opaque saved state, sized by the library: float32 W at every checkpoint (+ the final W), and one buffer
+        # holding the per-stage lr-scaled LN gradient tiles, row statistics and biases
+        w_ck = torch.empty(lib.ttt_linear_weight_ckpt_bytes(C.byref(d)) // 4, dtype=torch.float32,
+                           device=dev).view(B * H * (nck + 1), F, F)
+        b_ck = torch.empty(lib.ttt_linear_bias_ckpt_bytes(C.byref(d)), dtype=torch.uint8, device=dev)
         status = torch.zeros(4, dtype=torch.int32, device=dev)
         TttTileMultiKernel.last_status = status
         rc = lib.ttt_linear_forward(

@@ -107,9 +107,9 @@ struct TttTileMultiKernel {
     out.output = empty(a, in.xq.shape, in.xq.dtype);
     out.weight = empty(a, in.weight.shape, in.weight.dtype);
     out.bias = empty(a, in.bias.shape, in.bias.dtype);
-    const int64_t rows = static_cast<int64_t>(d.batch) * d.heads * nck;
-    DeviceTensor wck = empty(a, {rows, d.head_dim, d.head_dim}, TTT_F32);
-    DeviceTensor bck = empty(a, {rows, d.head_dim}, TTT_F32);
+    // opaque saved state, sized by the library (float32 words)
+    DeviceTensor wck = empty(a, {static_cast<int64_t>(ttt_linear_weight_ckpt_bytes(&d) / 4)}, TTT_F32);
+    DeviceTensor bck = empty(a, {static_cast<int64_t>((ttt_linear_bias_ckpt_bytes(&d) + 3) / 4)}, TTT_F32);
     detail::check(ttt_linear_forward(&d, in.xq.ptr, in.xk.ptr, in.xv.ptr, in.weight.ptr, in.bias.ptr,
                                      in.token_eta.ptr, in.ttt_lr_eta.ptr, in.ln_weight.ptr, in.ln_bias.ptr,
                                      out.output.ptr, out.weight.ptr, out.bias.ptr, wck.ptr, bck.ptr, status, stream));
