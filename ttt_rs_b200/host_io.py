@@ -1,0 +1,104 @@
+"""Running the operator on batches that live in (pinned) host memory.
+
+The streams of a batch are independent, so a host-resident batch is cut into chunks of batch rows and the three
+phases of each chunk -- host-to-device copy of xq/xk/xv/ttt_lr_eta/grad_output, forward + backward, device-to-host
+copy of the output and gradients -- run on three CUDA streams, so that the PCIe transfers in both directions overlap
+the kernels of neighbouring chunks.  Gradients that are sums over the batch (token_eta, LayerNorm weight/bias) are
+accumulated on the device across chunks and copied once.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .fused import FusedTttConfig, TttInputs, TttOutputs, TttTileMultiKernel
+
+_IN = ("xq", "xk", "xv", "ttt_lr_eta")
+
+
+class HostBatchRunner:
+    def __init__(self, config: FusedTttConfig, device: torch.device, chunks: int = 4, backward: bool = True):
+        self.cfg, self.dev, self.chunks, self.backward = config, device, max(1, chunks), backward
+        self.s_in = torch.cuda.Stream(device)
+        self.s_comp = torch.cuda.Stream(device)
+        self.s_out = torch.cuda.Stream(device)
+        self._dbuf = [None, None]
+
+    def _buffers(self, slot: int, like: Dict[str, torch.Tensor], rows: int):
+        cur = self._dbuf[slot]
+        if cur is None or next(iter(cur.values())).shape[0] != rows:
+            cur = {k: torch.empty((rows,) + tuple(v.shape[1:]), dtype=v.dtype, device=self.dev) for k, v in like.items()}
+            self._dbuf[slot] = cur
+        return cur
+
+    def run(self, host_in: Dict[str, torch.Tensor], params: Dict[str, torch.Tensor],
+            host_out: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        """host_in: pinned xq, xk, xv [B,H,T,F], ttt_lr_eta [B,H,T] (+ grad_output [B,H,T,F] when backward);
+        params: device tensors weight [B,H,F,F], bias [B,H,F], token_eta [T], ln_weight, ln_bias [H,F];
+        host_out: pinned buffers filled in place: output (+ grad_xq, grad_xk, grad_xv, grad_ttt_lr_eta, grad_weight,
+        grad_bias, grad_token_eta, grad_ln_weight, grad_ln_bias).  Returns host_out after queuing all work; the
+        caller synchronises (torch.cuda.synchronize or an event) before reading it."""
+        names = _IN + (("grad_output",) if self.backward else ())
+        B = host_in["xq"].shape[0]
+        nchunk = min(self.chunks, B)
+        bounds = [(B * c) // nchunk for c in range(nchunk + 1)]
+        cur = torch.cuda.current_stream(self.dev)
+        for st in (self.s_in, self.s_comp, self.s_out):
+            st.wait_stream(cur)
+        ev_in, ev_comp, keep = [], [], []
+        acc: Dict[str, Optional[torch.Tensor]] = {"token_eta": None, "ln_weight": None, "ln_bias": None}
+        for c in range(nchunk):
+            a, b = bounds[c], bounds[c + 1]
+            slot = c % 2
+            with torch.cuda.stream(self.s_in):
+                if c >= 2:
+                    self.s_in.wait_event(ev_comp[c - 2])  # the kernels of chunk c-2 have consumed this slot
+                buf = self._buffers(slot, {k: host_in[k] for k in names}, b - a)
+                for k in names:
+                    buf[k].copy_(host_in[k][a:b], non_blocking=True)
+                e = torch.cuda.Event()
+                e.record(self.s_in)
+                ev_in.append(e)
+            with torch.cuda.stream(self.s_comp):
+                self.s_comp.wait_event(ev_in[c])
+                ins = TttInputs(buf["xq"], buf["xk"], buf["xv"], params["weight"][a:b], params["bias"][a:b],
+                                params["token_eta"], buf["ttt_lr_eta"], params["ln_weight"], params["ln_bias"])
+                outs, saved = TttTileMultiKernel.forward_launch(ins, self.cfg)
+                res = {"output": outs.output}
+                if self.backward:
+                    g = TttTileMultiKernel.backward_launch(saved, TttOutputs(buf["grad_output"], None, None), self.cfg)
+                    res.update(grad_xq=g.xq, grad_xk=g.xk, grad_xv=g.xv, grad_ttt_lr_eta=g.ttt_lr_eta,
+                               grad_weight=g.weight, grad_bias=g.bias)
+                    for k, v in (("token_eta", g.token_eta), ("ln_weight", g.ln_weight), ("ln_bias", g.ln_bias)):
+                        acc[k] = v.float() if acc[k] is None else acc[k] + v.float()
+                e = torch.cuda.Event()
+                e.record(self.s_comp)
+                ev_comp.append(e)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(ev_comp[c])
+                for k, v in res.items():
+                    host_out[k][a:b].copy_(v, non_blocking=True)
+            keep.append((res, saved))
+        if self.backward:
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(ev_comp[-1])
+                for k in ("token_eta", "ln_weight", "ln_bias"):
+                    host_out["grad_" + k].copy_(acc[k].to(host_out["grad_" + k].dtype), non_blocking=True)
+        cur.wait_stream(self.s_out)
+        cur.wait_stream(self.s_comp)
+        self._keep = keep  # device tensors stay referenced until the next call
+        return host_out
+
+
+def alloc_host_outputs(B: int, H: int, T: int, F: int, dtype: torch.dtype, backward: bool = True):
+    """Pinned host buffers of the shapes `HostBatchRunner.run` fills."""
+    def pin(*shape):
+        return torch.empty(shape, dtype=dtype, pin_memory=True)
+    out = {"output": pin(B, H, T, F)}
+    if backward:
+        out.update(grad_xq=pin(B, H, T, F), grad_xk=pin(B, H, T, F), grad_xv=pin(B, H, T, F),
+                   grad_ttt_lr_eta=pin(B, H, T), grad_weight=pin(B, H, F, F), grad_bias=pin(B, H, F),
+                   grad_token_eta=pin(T), grad_ln_weight=pin(H, F), grad_ln_bias=pin(H, F))
+    return out
