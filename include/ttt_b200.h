@@ -121,6 +121,22 @@ int ttt_linear_backward(const ttt_dims* d, const void* xq, const void* xk, const
                         float* grad_ln_bias, float* outer_grad_packed, void* workspace, size_t workspace_bytes,
                         void* status, void* stream);
 
+/* Forward of the whole sequence for the 2-layer inner model (TTT-MLP, hidden width E = 4*F, GELU tanh).
+ * The reference has no fused kernel for it; this replaces the loop of `TTTMLP::forward_mini_batch`
+ * (rust/core/src/mlp.rs:127-208) behind `TTTInnerModel::forward` (rust/core/src/inner.rs:25-50), with the fused
+ * kernels' convention that token_eta is read at [0, CS).  bf16 only (dtype must be TTT_BF16); checkpoint_interval
+ * is ignored (no backward yet: gradients of this inner model still come from the framework's autodiff).
+ *   xq, xk, xv      bf16 [B,H,T,F]
+ *   w1, b1          bf16 [B,H,F,E], [B,H,E]   initial state, z1 = x @ w1 + b1
+ *   w2, b2          bf16 [B,H,E,F], [B,H,F]
+ *   token_eta [T], ttt_lr_eta [B,H,T], ln_weight / ln_bias [H,F]   bf16
+ *   output          bf16 [B,H,T,F] (out);  w1_out, b1_out, w2_out, b2_out (out) final state, same shapes
+ */
+int ttt_mlp_forward(const ttt_dims* d, const void* xq, const void* xk, const void* xv, const void* w1, const void* b1,
+                    const void* w2, const void* b2, const void* token_eta, const void* ttt_lr_eta,
+                    const void* ln_weight, const void* ln_bias, void* output, void* w1_out, void* b1_out, void* w2_out,
+                    void* b2_out, void* status, void* stream);
+
 /* Backward without a caller workspace.  (No counterpart in the reference: its host wrapper always allocates its
  * scratch itself, backward/launch.rs:389-392.)
  *

@@ -8,10 +8,12 @@ from .fused import (  # noqa: F401
     TTTInputsInner,
     TTTLinear,
     TTTLinearState,
+    TTTMLPState,
     TttInputs,
     TttOutputs,
     TttSavedStateMulti,
     TttTileMultiKernel,
+    fused_ttt_mlp_forward,
     fused_ttt_tile_forward_multi,
     packed_outer_grad_len,
 )

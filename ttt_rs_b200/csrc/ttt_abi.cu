@@ -303,6 +303,37 @@ int ttt_linear_backward(const ttt_dims* d, const void* xq, const void* xk, const
   return TTT_OK;
 }
 
+int ttt_mlp_forward(const ttt_dims* d, const void* xq, const void* xk, const void* xv, const void* w1, const void* b1,
+                    const void* w2, const void* b2, const void* token_eta, const void* ttt_lr_eta,
+                    const void* ln_weight, const void* ln_bias, void* output, void* w1_out, void* b1_out, void* w2_out,
+                    void* b2_out, void* status, void* stream) {
+  int rc = check_dims(d);
+  if (rc != TTT_OK) return rc;
+  if (d->dtype != TTT_BF16) return fail(TTT_ERR_UNSUPPORTED, "the TTT-MLP kernel is built for bf16 only");
+  const NamedPtr ptrs[] = {{"xq", xq}, {"xk", xk}, {"xv", xv}, {"w1", w1}, {"b1", b1}, {"w2", w2}, {"b2", b2},
+                           {"token_eta", token_eta}, {"ttt_lr_eta", ttt_lr_eta}, {"ln_weight", ln_weight},
+                           {"ln_bias", ln_bias}, {"output", output}, {"w1_out", w1_out}, {"b1_out", b1_out},
+                           {"w2_out", w2_out}, {"b2_out", b2_out}};
+  rc = check_ptrs(ptrs, sizeof(ptrs) / sizeof(ptrs[0]));
+  if (rc != TTT_OK) return rc;
+  const int64_t rows = (int64_t)d->batch * d->heads * d->seq_len;
+  CUtensorMap maps[4];
+  const void* bases[4] = {xq, xk, xv, output};
+  for (int i = 0; i < 4; ++i) {
+    rc = make_tile_map(&maps[i], bases[i], rows, d->dtype);
+    if (rc != TTT_OK) return rc;
+  }
+  ttt::MlpFwdParams p;
+  p.w1 = w1; p.b1 = b1; p.w2 = w2; p.b2 = b2;
+  p.token_eta = token_eta; p.lr = ttt_lr_eta; p.ln_g = ln_weight; p.ln_b = ln_bias;
+  p.w1_out = w1_out; p.b1_out = b1_out; p.w2_out = w2_out; p.b2_out = b2_out;
+  p.status = static_cast<uint32_t*>(status);
+  p.H = d->heads; p.T = d->seq_len; p.NS = d->seq_len / d->mini_batch; p.eps = d->epsilon;
+  cudaError_t e = ttt::launch_mlp_fwd(maps, p, d->batch * d->heads, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "MLP forward launch failed: %s", cudaGetErrorString(e));
+  return TTT_OK;
+}
+
 }  // extern "C"
 
 // ----------------------------------------------------------------------------------------------------

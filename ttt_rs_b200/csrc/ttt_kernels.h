@@ -56,6 +56,26 @@ struct ReduceParams {
   int B, H, T;
 };
 
+struct MlpFwdParams {
+  const void* w1;         // [B,H,F,E] bf16, E = 4F
+  const void* b1;         // [B,H,E]
+  const void* w2;         // [B,H,E,F]
+  const void* b2;         // [B,H,F]
+  const void* token_eta;  // [T], first 16 entries read
+  const void* lr;         // [B,H,T]
+  const void* ln_g;       // [H,F]
+  const void* ln_b;       // [H,F]
+  void* w1_out;
+  void* b1_out;
+  void* w2_out;
+  void* b2_out;
+  uint32_t* status;
+  int H, T, NS;
+  float eps;
+};
+// bf16 only.  maps: q, k, v, out.
+cudaError_t launch_mlp_fwd(const CUtensorMap* maps, const MlpFwdParams& p, int nstreams, cudaStream_t st);
+
 // dtype: 0 = float32, 1 = bfloat16.  maps: q, k, v, out, gp (saved lr-scaled LN gradient, [B*H*T, 64] of T).
 cudaError_t launch_linear_fwd(int dtype, const CUtensorMap* maps, const LinFwdParams& p, int nstreams,
                               cudaStream_t st);

@@ -360,3 +360,47 @@ class FusedTileMultiTTTLinear(torch.nn.Module):
             self.inner.ln_weight, self.inner.ln_bias, cfg)
         state.weight, state.bias = w, b
         return out
+
+
+# --------------------------------------------------------------------------------------------
+# TTT-MLP (2-layer inner model): forward only
+# --------------------------------------------------------------------------------------------
+
+@dataclass
+class TTTMLPState:
+    """rust/core/src/mlp.rs:29-53: w1 [B,H,F,4F], b1 [B,H,4F], w2 [B,H,4F,F], b2 [B,H,F]."""
+    w1: torch.Tensor
+    b1: torch.Tensor
+    w2: torch.Tensor
+    b2: torch.Tensor
+
+
+def fused_ttt_mlp_forward(xq, xk, xv, state: TTTMLPState, token_eta, ttt_lr_eta, ln_weight, ln_bias,
+                          config: FusedTttConfig):
+    """Whole-sequence forward of the 2-layer inner model in one launch (the loop of
+    `TTTMLP::forward_mini_batch`, rust/core/src/mlp.rs:127-208).  Returns (output, new TTTMLPState).
+    bf16 only and not differentiable: there is no backward kernel for this inner model yet."""
+    lib = _lib.load()
+    if not xq.is_cuda:
+        raise TttError(_lib.TTT_ERR_CUDA, "inputs must be CUDA tensors: this operator has no CPU path")
+    d = _dims(xq, config)
+    B, H, T, F = xq.shape
+    E = 4 * F
+    dt, dev = xq.dtype, xq.device
+    ts = dict(xq=xq, xk=xk, xv=xv, w1=state.w1, b1=state.b1, w2=state.w2, b2=state.b2, token_eta=token_eta,
+              ttt_lr_eta=ttt_lr_eta, ln_weight=ln_weight, ln_bias=ln_bias)
+    shapes = dict(xq=(B, H, T, F), xk=(B, H, T, F), xv=(B, H, T, F), w1=(B, H, F, E), b1=(B, H, E), w2=(B, H, E, F),
+                  b2=(B, H, F), token_eta=(token_eta.shape[0],), ttt_lr_eta=(B, H, T), ln_weight=(H, F), ln_bias=(H, F))
+    ts = {k: v.contiguous() for k, v in ts.items()}
+    for k, v in ts.items():
+        _expect(k, v, shapes[k], dt, dev)
+    out = torch.empty_like(ts["xq"])
+    new = TTTMLPState(*(torch.empty_like(ts[k]) for k in ("w1", "b1", "w2", "b2")))
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    TttTileMultiKernel.last_status = status
+    rc = lib.ttt_mlp_forward(
+        C.byref(d), *[_ptr(ts[k]) for k in ("xq", "xk", "xv", "w1", "b1", "w2", "b2", "token_eta", "ttt_lr_eta",
+                                           "ln_weight", "ln_bias")],
+        _ptr(out), _ptr(new.w1), _ptr(new.b1), _ptr(new.w2), _ptr(new.b2), _ptr(status), _stream_ptr(dev))
+    _lib.check(rc)
+    return out, new
