@@ -33,6 +33,7 @@ REPO = Path(__file__).resolve().parent
 sys.path.insert(0, str(REPO))
 
 LIN_IN = ("xq", "xk", "xv", "weight", "bias", "token_eta", "ttt_lr_eta", "ln_weight", "ln_bias")
+MLP_IN = ("xq", "xk", "xv", "w1", "b1", "w2", "b2", "token_eta", "ttt_lr_eta", "ln_weight", "ln_bias")
 
 WORKLOADS = {
     # name: (B, H, T, dtype, checkpoint interval, backward?)
@@ -42,6 +43,8 @@ WORKLOADS = {
                  desc="TTT-Linear inner loop fwd+bwd, bf16, B=32 H=12 T=2048 d=64 mb=16 ckpt=16"),
     "cfg1-f32": dict(B=32, H=12, T=2048, dtype="f32", K=16, backward=True,
                      desc="TTT-Linear inner loop fwd+bwd, f32, B=32 H=12 T=2048 d=64 mb=16 ckpt=16"),
+    "cfg2-fwd": dict(B=16, H=12, T=2048, dtype="bf16", K=1, backward=False, inner="mlp",
+                     desc="TTT-MLP inner loop fwd (64-256-64, GELU tanh), bf16, B=16 H=12 T=2048 d=64 mb=16"),
     "cfg4-8k": dict(B=8, H=32, T=8192, dtype="bf16", K=16, backward=True,
                     desc="TTT-Linear inner loop fwd+bwd, bf16, B=8 H=32 T=8192 d=64 mb=16 ckpt=16"),
 }
@@ -57,6 +60,8 @@ def algorithmic_bytes(w, fwd=True, bwd=True):
     streams = w["B"] * w["H"]
     ck = (F * F + F) * s / (w["K"] * CS)  # counted at the element size; this build keeps them in float32
     fb = (4 * F * s + s + ck) * tok_heads + streams * 2 * (F * F + F) * s
+    if w.get("inner") == "mlp":  # no saved state; the per-stream state is W1, b1, W2, b2 read and written once
+        fb = (4 * F * s + s) * tok_heads + streams * 2 * (2 * F * 4 * F + 4 * F + F) * s
     bb = (7 * F * s + 2 * s + ck) * tok_heads + streams * (F * F + F) * s
     return (fb if fwd else 0) + (bb if bwd else 0), fb, bb
 
@@ -124,12 +129,15 @@ class ClockSampler:
 def make_host_inputs(w, seed):
     from oracle.ttt_oracle import make_inputs
     dt = torch.bfloat16 if w["dtype"] == "bf16" else torch.float32
-    return make_inputs(w["B"], w["H"], w["T"], F, CS, seed=seed, dtype=dt, with_grad_output=True)
+    return make_inputs(w["B"], w["H"], w["T"], F, CS, seed=seed, dtype=dt, with_grad_output=True,
+                       inner=w.get("inner", "linear"))
 
 
 def cpu_step(t, w):
     """One step of the CPU restatement on a host-resident sample (float32)."""
     from oracle import ttt_oracle as O
+    if w.get("inner") == "mlp":
+        return O.ttt_mlp_forward(*[t[k] for k in MLP_IN], mini_batch=CS, eps=1e-6)
     args = [t[k] for k in LIN_IN]
     fw = O.ttt_linear_forward(*args, mini_batch=CS, eps=1e-6, checkpoint_interval=w["K"])
     if w["backward"]:
@@ -204,9 +212,15 @@ def main():
 
     # ---- device-resident inputs (every rank its own seed: independent batches)
     host = make_host_inputs(w, seed=rank)
-    ins = tb.TttInputs(*[host[k].to(dev) for k in LIN_IN])
-    go = host["grad_output"].to(dev)
+    mlp = w.get("inner") == "mlp"
     cfg = tb.FusedTttConfig.new(CS, F, 1e-6, 128, w["K"])
+    if mlp:
+        md = {k: host[k].to(dev) for k in MLP_IN}
+        mstate = tb.TTTMLPState(md["w1"], md["b1"], md["w2"], md["b2"])
+        args.no_e2e = True
+    else:
+        ins = tb.TttInputs(*[host[k].to(dev) for k in LIN_IN])
+    go = host["grad_output"].to(dev)
     packed = torch.zeros(tb.packed_outer_grad_len(w["H"]), device=dev) if w["backward"] else None
     ev_pairs = []
 
@@ -214,7 +228,11 @@ def main():
         e = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if record else None
         if record:
             e[0].record()
-        outs, saved = tb.TttTileMultiKernel.forward_launch(ins, cfg)
+        if mlp:
+            outs = tb.fused_ttt_mlp_forward(md["xq"], md["xk"], md["xv"], mstate, md["token_eta"], md["ttt_lr_eta"],
+                                            md["ln_weight"], md["ln_bias"], cfg)
+        else:
+            outs, saved = tb.TttTileMultiKernel.forward_launch(ins, cfg)
         if record:
             e[1].record()
         g = None
@@ -265,7 +283,7 @@ def main():
 
     peak, peak_kind = measured_peaks()
     total_b, fb, bb = algorithmic_bytes(w, True, w["backward"])
-    dom_ms, dom_bytes, dom_name = (bwd_ms, bb, "ttt_linear_bwd_kernel") if w["backward"] else (fwd_ms, fb, "ttt_linear_fwd_kernel")
+    dom_ms, dom_bytes, dom_name = (bwd_ms, bb, "ttt_linear_bwd_kernel") if w["backward"] else (fwd_ms, fb, "ttt_mlp_fwd_kernel" if mlp else "ttt_linear_fwd_kernel")
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
     roof = {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
             "frac": achieved / peak, "traffic": None, "peak_source": f"of {peak_kind}",
