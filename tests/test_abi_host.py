@@ -44,7 +44,9 @@ def test_checkpoint_and_workspace_sizes(lib):
     rows, streams, ns = 2 * 2 * 80, 4, 5  # gradient tiles (bf16) + 32 B of statistics per token + per-stage biases
     assert lib.ttt_linear_bias_ckpt_bytes(C.byref(d)) == rows * 64 * 2 + rows * 32 + streams * (ns + 1) * 64 * 4
     streams = 4
-    assert lib.ttt_linear_backward_workspace_bytes(C.byref(d)) == 4 * (streams * 128 + streams * 80 + streams * (4096 + 64))
+    # LN partials per (stream, chunk), token_eta terms, float32 dW/db, chunk hand-off (W, dW, db), scheduler words
+    assert lib.ttt_linear_backward_workspace_bytes(C.byref(d)) == 4 * (
+        streams * 1 * 128 + streams * 80 + streams * (4096 + 64) + streams * (2 * 4096 + 64) + 8)
 
 
 @pytest.mark.parametrize("kw,code", [

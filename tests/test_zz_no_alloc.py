@@ -81,7 +81,7 @@ def test_noalloc_backward_rejects_problems_larger_than_its_scratch():
     """Needs no GPU: the size check comes before anything touches the device."""
     from ttt_rs_b200 import _lib
     lib = _lib.load()
-    d = _lib.TttDims(64, 32, 8192, 64, 16, 16, 1e-6, _lib.TTT_BF16)  # 2048 streams x (8192 + 4288) floats = 102 MB
+    d = _lib.TttDims(64, 32, 8192, 64, 16, 16, 1e-6, _lib.TTT_BF16)  # 2048 streams x ~24,700 floats = 200 MB
     assert lib.ttt_linear_backward_workspace_bytes(C.byref(d)) > _lib.NOALLOC_SCRATCH_BYTES
     fake = C.c_void_p(0x1000)
     rc = lib.ttt_linear_backward_noalloc(C.byref(d), *([fake] * 21), None, None, None)

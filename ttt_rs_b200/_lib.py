@@ -60,7 +60,7 @@ SYMBOLS = {
     "ttt_mlp_forward": (C.c_int, [_DP] + [_P] * 18),
 }
 
-NOALLOC_SCRATCH_BYTES = 16 << 20  # TTT_NOALLOC_SCRATCH_BYTES
+NOALLOC_SCRATCH_BYTES = 32 << 20  # TTT_NOALLOC_SCRATCH_BYTES
 
 _lib: Optional[C.CDLL] = None
 

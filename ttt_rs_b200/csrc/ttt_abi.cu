@@ -107,16 +107,22 @@ AuxLayout aux_layout(const ttt_dims* d) {
 }
 
 // workspace layout of the backward (float32 words)
+constexpr int kBwdChunkStages = 16;  // stages per work item of the persistent backward kernel
 struct WsLayout {
-  size_t off_ln, off_te, off_w, total_bytes;
+  size_t off_ln, off_te, off_w, off_handoff, off_sched, total_bytes;
+  int nch;
 };
 WsLayout ws_layout(const ttt_dims* d) {
   const size_t streams = (size_t)d->batch * d->heads;
+  const int ns = d->seq_len / d->mini_batch;
   WsLayout w;
+  w.nch = (ns + kBwdChunkStages - 1) / kBwdChunkStages;
   w.off_ln = 0;
-  w.off_te = w.off_ln + streams * 2 * 64;
+  w.off_te = w.off_ln + streams * (size_t)w.nch * 2 * 64;
   w.off_w = w.off_te + streams * (size_t)d->seq_len;
-  const size_t words = w.off_w + streams * (64 * 64 + 64);
+  w.off_handoff = w.off_w + streams * (64 * 64 + 64);
+  w.off_sched = w.off_handoff + streams * (2 * 64 * 64 + 64);
+  const size_t words = w.off_sched + ((1 + streams + 3) & ~(size_t)3);
   w.total_bytes = words * sizeof(float);
   return w;
 }
@@ -277,6 +283,11 @@ int ttt_linear_backward(const ttt_dims* d, const void* xq, const void* xk, const
   p.part_ln = ws + wl.off_ln;
   p.part_te = ws + wl.off_te;
   p.part_w = (outer_grad_packed != nullptr) ? ws + wl.off_w : nullptr;
+  p.handoff = ws + wl.off_handoff;
+  p.sched = reinterpret_cast<int*>(ws + wl.off_sched);
+  p.CH = kBwdChunkStages;
+  p.NCH = wl.nch;
+  p.nstreams = d->batch * d->heads;
   p.status = static_cast<uint32_t*>(status);
   p.H = d->heads;
   p.T = d->seq_len;
@@ -298,6 +309,7 @@ int ttt_linear_backward(const ttt_dims* d, const void* xq, const void* xk, const
   r.B = d->batch;
   r.H = d->heads;
   r.T = d->seq_len;
+  r.NCH = wl.nch;
   e = ttt::launch_linear_bwd_reduce(r, st);
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "backward reduction launch failed: %s", cudaGetErrorString(e));
   return TTT_OK;
@@ -389,7 +401,7 @@ extern "C" int ttt_linear_backward_noalloc(const ttt_dims* d, const void* xq, co
   if (need > (size_t)TTT_NOALLOC_SCRATCH_BYTES)
     return fail(TTT_ERR_WORKSPACE,
                 "this problem needs %zu bytes of scratch but the built-in scratch holds %zu "
-                "(batch*heads*(seq_len + 4288)*4 must not exceed it): call ttt_linear_backward with a workspace",
+                "(about batch*heads*(1.5*seq_len + 12420)*4 bytes are needed): call ttt_linear_backward with a workspace",
                 need, (size_t)TTT_NOALLOC_SCRATCH_BYTES);
   void* scratch = nullptr;
   rc = noalloc_scratch(&scratch);

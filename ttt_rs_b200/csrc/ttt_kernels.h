@@ -37,7 +37,10 @@ struct LinBwdParams {
   void* d_w;        // [B,H,F,F] element type T (per batch element), nullable
   void* d_b;        // [B,H,F], nullable
   void* d_lr;       // [B,H,T]
-  float* part_ln;   // workspace: [B*H][2][F] per-stream partial LN gradients (weight, bias)
+  int* sched;       // workspace: [0] next work item, [1 + stream] chunks of the stream finished so far (zeroed per launch)
+  float* handoff;   // workspace: [B*H][2*F*F + F] W^T, dW^T (register layout) and db handed from chunk to chunk
+  int CH, NCH, nstreams;  // stages per chunk, chunks per stream, B*H
+  float* part_ln;   // workspace: [B*H][NCH][2][F] per-(stream, chunk) partial LN gradients (weight, bias)
   float* part_te;   // workspace: [B*H][T] per-stream token_eta gradient terms
   float* part_w;    // workspace: [B*H][F*F + F] float32 dW, db per stream (for the packed reduction)
   uint32_t* status;
@@ -53,7 +56,7 @@ struct ReduceParams {
   float* d_ln_g;       // [H,F] f32
   float* d_ln_b;       // [H,F] f32
   float* packed;       // nullable: [H*F*F + 3*H*F + CS] f32
-  int B, H, T;
+  int B, H, T, NCH;
 };
 
 struct MlpFwdParams {

@@ -77,10 +77,10 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
 
   const Lane L;
   const int tid = L.tid, lane = L.lane, g = L.g, t = L.t, nb = L.nb, warp = L.warp;
-  const int stream = blockIdx.x;
-  const int head = stream % p.H;
-  const int row_base = stream * p.T;
   const int NS = p.NS;
+  // work item = (stream, chunk of CH stages); set per item below
+  int stream = 0, row_base = 0;
+  __shared__ int s_item;
 
   if (tid == 0) {
     prefetch_tmap(&tm_q);
@@ -112,16 +112,9 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
     bulk_load_1d(sl + SM::OFF_BS, p.b_stage + ((size_t)stream * (NS + 1) + s) * HD, 256u, bar);
     bulk_load_1d(sl + SM::OFF_LR, static_cast<const uint8_t*>(p.lr) + (size_t)r0 * TF::ELT, CS * TF::ELT, bar);
   };
-  if (tid == 0) issue_loads(0, NS - 1);
 
   // ---- per-thread constants and accumulators (column pairs nt = 0,1; rows g and g+8)
   F2 gam[2], bet[2];
-#pragma unroll
-  for (int nt = 0; nt < 2; ++nt) {
-    const int c = nb + 8 * nt + 2 * t;
-    gam[nt] = f2(ld_as_float<T>(p.ln_g, (size_t)head * HD + c), ld_as_float<T>(p.ln_g, (size_t)head * HD + c + 1));
-    bet[nt] = f2(ld_as_float<T>(p.ln_b, (size_t)head * HD + c), ld_as_float<T>(p.ln_b, (size_t)head * HD + c + 1));
-  }
   const float te_row[2] = {ld_as_float<T>(p.token_eta, g), ld_as_float<T>(p.token_eta, g + 8)};
   const float te15 = ld_as_float<T>(p.token_eta, CS - 1);
   F2 dbias[2] = {f2(0.f), f2(0.f)};                                 // gradient w.r.t. the bias after this stage
@@ -137,8 +130,73 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
 
   int xsel = 0;
   bool failed = false;
+  int n = 0;  // stages visited by this block so far (TMA slot = n % NSLOT)
+  const int nitems = p.nstreams * p.NCH;
+  const size_t HOFF = 2 * HD * HD + HD;
 
-  for (int s = NS - 1, n = 0; s >= 0; --s, ++n) {
+  // Persistent block: items are handed out in increasing order, last chunks of all streams first.  An item only
+  // waits for an item with a smaller index (the later chunk of the same stream), which a resident block already
+  // holds, so the launch cannot deadlock as long as all blocks are co-resident (cooperative launch).
+  while (!failed) {
+    if (tid == 0) s_item = atomicAdd(&p.sched[0], 1);
+    __syncthreads();
+    const int item = s_item;
+    __syncthreads();
+    if (item >= nitems) break;
+    const int crank = item / p.nstreams;  // 0 = last chunk of the sequence
+    const int chunk = p.NCH - 1 - crank;
+    stream = item - crank * p.nstreams;
+    row_base = stream * p.T;
+    const int head = stream % p.H;
+    const int s_lo = chunk * p.CH, s_hi = min(s_lo + p.CH, NS) - 1;
+    if (tid == 0) issue_loads(n, s_hi);
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      const int c = nb + 8 * nt + 2 * t;
+      gam[nt] = f2(ld_as_float<T>(p.ln_g, (size_t)head * HD + c), ld_as_float<T>(p.ln_g, (size_t)head * HD + c + 1));
+      bet[nt] = f2(ld_as_float<T>(p.ln_b, (size_t)head * HD + c), ld_as_float<T>(p.ln_b, (size_t)head * HD + c + 1));
+      dgam[nt] = dbet[nt] = f2(0.f);
+    }
+    float* ho = p.handoff + (size_t)stream * HOFF;
+    if (crank == 0) {
+      dbias[0] = dbias[1] = f2(0.f);
+#pragma unroll
+      for (int kt = 0; kt < 8; ++kt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dwt[kt][i] = 0.f;
+    } else {
+      // wait (bounded) until the later chunk of this stream has published its hand-off
+      int ok = 1;
+      if (tid == 0) {
+        ok = 0;
+        const volatile int* flag = p.sched + 1 + stream;
+        for (uint32_t it = 0; it < (1u << 24); ++it) {
+          if (*flag >= crank) {
+            ok = 1;
+            break;
+          }
+          __nanosleep(100);
+        }
+        __threadfence();
+      }
+      if (__syncthreads_or(ok ? 0 : 1)) {
+        failed = true;
+        if (tid == 0) report_timeout(p.status, 15, s_hi);
+        break;
+      }
+#pragma unroll
+      for (int kt = 0; kt < 8; ++kt) {
+        const float4 a = __ldcg(reinterpret_cast<const float4*>(ho) + kt * NTHREADS + tid);
+        const float4 b = __ldcg(reinterpret_cast<const float4*>(ho + HD * HD) + kt * NTHREADS + tid);
+        wt[kt][0] = a.x; wt[kt][1] = a.y; wt[kt][2] = a.z; wt[kt][3] = a.w;
+        dwt[kt][0] = b.x; dwt[kt][1] = b.y; dwt[kt][2] = b.z; dwt[kt][3] = b.w;
+      }
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+        dbias[nt] = __ldcg(reinterpret_cast<const float2*>(ho + 2 * HD * HD + nb + 8 * nt + 2 * t));
+    }
+
+  for (int s = s_hi; s >= s_lo; --s, ++n) {
     const int slot = n % SM::NSLOT;
     const uint32_t sl = base + slot * SM::SLOT;
     const uint32_t tq = sl + SM::OFF_Q, tk = sl + SM::OFF_K, tg = sl + SM::OFF_G, tv = sl + SM::OFF_V, tdo = sl + SM::OFF_DO;
@@ -165,7 +223,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       // so the other slot may be overwritten
       if (!next_issued) {
         next_issued = true;
-        if (tid == 0 && s > 0) issue_loads(n + 1, s - 1);
+        if (tid == 0 && s > s_lo) issue_loads(n + 1, s - 1);
       }
     };
     if constexpr (NP == 3) {
@@ -524,41 +582,67 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
     }
   }
 
-  if (!failed) {
-    // ---- gradients w.r.t. the initial state (per batch element) and per-stream partials for the reduction
-    const size_t wo = (size_t)stream * HD * HD;
-#pragma unroll
-    for (int kt = 0; kt < 8; ++kt)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int idx = (8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1);
-        st_from_float<T>(p.d_w, wo + idx, dwt[kt][i]);
-        if (p.part_w != nullptr) p.part_w[(size_t)stream * (HD * HD + HD) + idx] = dwt[kt][i];
-      }
+    if (failed) break;
+    // ---- end of the item: LN partials of this (stream, chunk); then either hand the state to the earlier chunk
+    // or, for the first chunk of the sequence, write the gradients w.r.t. the initial state
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
       const float dg_[2] = {col_sum(dgam[nt].x), col_sum(dgam[nt].y)};
       const float db_[2] = {col_sum(dbet[nt].x), col_sum(dbet[nt].y)};
-      const float dbi[2] = {dbias[nt].x, dbias[nt].y};
       if (g == 0) {
+        float* pl = p.part_ln + ((size_t)stream * p.NCH + chunk) * 2 * HD;
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const int c = nb + 8 * nt + 2 * t + e;
-          st_from_float<T>(p.d_b, (size_t)stream * HD + c, dbi[e]);
-          if (p.part_w != nullptr) p.part_w[(size_t)stream * (HD * HD + HD) + HD * HD + c] = dbi[e];
-          p.part_ln[(size_t)stream * 2 * HD + c] = dg_[e];
-          p.part_ln[(size_t)stream * 2 * HD + HD + c] = db_[e];
+          pl[nb + 8 * nt + 2 * t + e] = dg_[e];
+          pl[HD + nb + 8 * nt + 2 * t + e] = db_[e];
         }
       }
     }
-  }
+    if (chunk > 0) {
+#pragma unroll
+      for (int kt = 0; kt < 8; ++kt) {
+        reinterpret_cast<float4*>(ho)[kt * NTHREADS + tid] = make_float4(wt[kt][0], wt[kt][1], wt[kt][2], wt[kt][3]);
+        reinterpret_cast<float4*>(ho + HD * HD)[kt * NTHREADS + tid] =
+            make_float4(dwt[kt][0], dwt[kt][1], dwt[kt][2], dwt[kt][3]);
+      }
+      if (g == 0) {
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) *reinterpret_cast<float2*>(ho + 2 * HD * HD + nb + 8 * nt + 2 * t) = dbias[nt];
+      }
+      __threadfence();
+      __syncthreads();
+      if (tid == 0) *reinterpret_cast<volatile int*>(p.sched + 1 + stream) = crank + 1;
+    } else {
+      const size_t wo = (size_t)stream * HD * HD;
+#pragma unroll
+      for (int kt = 0; kt < 8; ++kt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int idx = (8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1);
+          st_from_float<T>(p.d_w, wo + idx, dwt[kt][i]);
+          if (p.part_w != nullptr) p.part_w[(size_t)stream * (HD * HD + HD) + idx] = dwt[kt][i];
+        }
+      if (g == 0) {
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const float dbi[2] = {dbias[nt].x, dbias[nt].y};
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int c = nb + 8 * nt + 2 * t + e;
+            st_from_float<T>(p.d_b, (size_t)stream * HD + c, dbi[e]);
+            if (p.part_w != nullptr) p.part_w[(size_t)stream * (HD * HD + HD) + HD * HD + c] = dbi[e];
+          }
+        }
+      }
+    }
+  }  // item loop
   if (tid == 0) bulk_wait_all<0>();
 }
 
 // ----------------------------------------------------------------------------------------------------
 // Second pass: fixed-order sums of the per-stream partials.
 //   d_token_eta[t]   = sum over streams of part_te[stream][t]
-//   d_ln_w/b[h][f]   = sum over batch of part_ln[b*H+h][0/1][f]
+//   d_ln_w/b[h][f]   = sum over batch and chunks of part_ln[b*H+h][chunk][0/1][f]
 //   packed (optional) = { sum_b dW[b,h], sum_b db[b,h], d_ln_w, d_ln_b, d_token_eta folded to [CS] }
 //                       (the fold is a second tiny kernel over the reduced d_token_eta)
 // ----------------------------------------------------------------------------------------------------
@@ -574,7 +658,8 @@ __global__ void ttt_linear_bwd_reduce_kernel(const ReduceParams p) {
     } else if (i < n_te + n_ln) {
       const int k = i - n_te, which = k / (H * HD), hf = k % (H * HD), h = hf / HD, f = hf % HD;
       float acc = 0.f;
-      for (int b = 0; b < B; ++b) acc += p.part_ln[((size_t)(b * H + h) * 2 + which) * HD + f];
+      for (int b = 0; b < B; ++b)
+        for (int ch = 0; ch < p.NCH; ++ch) acc += p.part_ln[(((size_t)(b * H + h) * p.NCH + ch) * 2 + which) * HD + f];
       (which == 0 ? p.d_ln_g : p.d_ln_b)[hf] = acc;
       if (p.packed != nullptr) p.packed[(size_t)H * HD * HD + H * HD + k] = acc;
     } else {
@@ -605,8 +690,22 @@ static cudaError_t launch_bwd_t(const CUtensorMap* m, const LinBwdParams& p, int
   auto kfn = ttt_linear_bwd_kernel<T>;
   cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BwdSmem<T>::DYN_BYTES);
   if (e != cudaSuccess) return e;
-  kfn<<<nstreams, NTHREADS, BwdSmem<T>::DYN_BYTES, st>>>(m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], p);
-  return cudaGetLastError();
+  // persistent grid: as many blocks as can be resident at once (they wait on one another's hand-offs), never more
+  // than there are work items; launched cooperatively so that co-residency is guaranteed, not assumed
+  int dev = 0, sms = 0, per_sm = 0;
+  if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+  if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+  if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kfn, NTHREADS, BwdSmem<T>::DYN_BYTES)) != cudaSuccess)
+    return e;
+  if (per_sm < 1) return cudaErrorLaunchOutOfResources;
+  int grid = sms * per_sm;
+  const int nitems = nstreams * p.NCH;
+  if (grid > nitems) grid = nitems;
+  if ((e = cudaMemsetAsync(p.sched, 0, sizeof(int) * (size_t)(1 + nstreams), st)) != cudaSuccess) return e;
+  LinBwdParams pp = p;
+  void* args[] = {(void*)&m[0], (void*)&m[1], (void*)&m[2], (void*)&m[3], (void*)&m[4],
+                  (void*)&m[5], (void*)&m[6], (void*)&m[7], (void*)&pp};
+  return cudaLaunchCooperativeKernel((const void*)kfn, dim3(grid), dim3(NTHREADS), args, BwdSmem<T>::DYN_BYTES, st);
 }
 
 cudaError_t launch_linear_bwd(int dtype, const CUtensorMap* maps, const LinBwdParams& p, int nstreams,
