@@ -24,7 +24,7 @@ struct Lane {
 
 // Exchange of up to four per-row partial sums across the four warps of the CTA.
 struct __align__(16) Xch4 {
-  float4 v[CS][4];  // [row][warp], 1 KB
+  float4 v[CS][5];  // [row][warp] with the row padded to 80 bytes: the 8 rows a warp reads fall in distinct banks
 };
 
 // Every thread contributes its two rows (g, g+8); returns the CTA-wide sums for those rows.
@@ -50,16 +50,17 @@ __device__ __forceinline__ void xch_rows(Xch4* xb, const Lane& L, const float4 a
 __device__ __forceinline__ void xch_rows2(Xch4* xb, const Lane& L, float a0x, float a0y, float a1x, float a1y,
                                           float2& o0, float2& o1, int& flag) {
   a0x = quad_sum(a0x); a0y = quad_sum(a0y); a1x = quad_sum(a1x); a1y = quad_sum(a1y);
-  float2* base = reinterpret_cast<float2*>(xb);  // reuse the buffer as float2[16][4] (first 512 bytes)
+  // the buffer reused as float2[16][6]: four warps' pairs per row, rows padded to 48 bytes (conflict-free reads)
+  float2* base = reinterpret_cast<float2*>(xb);
   if (L.t == 0) {
-    base[L.g * 4 + L.warp] = make_float2(a0x, a0y);
-    base[(L.g + 8) * 4 + L.warp] = make_float2(a1x, a1y);
+    base[L.g * 6 + L.warp] = make_float2(a0x, a0y);
+    base[(L.g + 8) * 6 + L.warp] = make_float2(a1x, a1y);
   }
   flag = __syncthreads_or(flag);
-  const float4 p = *reinterpret_cast<const float4*>(&base[L.g * 4]);
-  const float4 q = *reinterpret_cast<const float4*>(&base[L.g * 4 + 2]);
-  const float4 p2 = *reinterpret_cast<const float4*>(&base[(L.g + 8) * 4]);
-  const float4 q2 = *reinterpret_cast<const float4*>(&base[(L.g + 8) * 4 + 2]);
+  const float4 p = *reinterpret_cast<const float4*>(&base[L.g * 6]);
+  const float4 q = *reinterpret_cast<const float4*>(&base[L.g * 6 + 2]);
+  const float4 p2 = *reinterpret_cast<const float4*>(&base[(L.g + 8) * 6]);
+  const float4 q2 = *reinterpret_cast<const float4*>(&base[(L.g + 8) * 6 + 2]);
   o0 = make_float2((p.x + p.z) + (q.x + q.z), (p.y + p.w) + (q.y + q.w));
   o1 = make_float2((p2.x + p2.z) + (q2.x + q2.z), (p2.y + p2.w) + (q2.y + q2.w));
 }
