@@ -117,6 +117,11 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
   F2 gam[2], bet[2];
   const float te_row[2] = {ld_as_float<T>(p.token_eta, g), ld_as_float<T>(p.token_eta, g + 8)};
   const float te15 = ld_as_float<T>(p.token_eta, CS - 1);
+  // as in the forward, the state is carried as What = W / wscale (wscale = -te15), which turns the reversal of a
+  // stage's update into one tensor-core accumulation What -= Gp^T K
+  const bool w_moves = (te15 != 0.f);
+  const float wscale = w_moves ? -te15 : 1.f;
+  const float winv = 1.f / wscale;
   F2 dbias[2] = {f2(0.f), f2(0.f)};                                 // gradient w.r.t. the bias after this stage
   F2 dgam[2] = {f2(0.f), f2(0.f)}, dbet[2] = {f2(0.f), f2(0.f)};    // un-reduced over the 8 row lanes
   float wt[8][4], dwt[8][4];
@@ -212,7 +217,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
 #pragma unroll
         for (int kt = 0; kt < 8; ++kt)
 #pragma unroll
-          for (int i = 0; i < 4; ++i) wt[kt][i] = wc[(8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1)];
+          for (int i = 0; i < 4; ++i) wt[kt][i] = wc[(8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1)] * winv;
       }
     }
 
@@ -248,8 +253,11 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
     float bias[4];
     {
       Pk<NP> agt[4];
-      ldsm_np<NP>(agt, pg + lane_off_B_nk(lane, nb), PL, true);
-      state_update<NP>(wt, agt, pk, lane, te15);
+      if (w_moves) {
+        ldsm_np<NP>(agt, pg + lane_off_B_nk(lane, nb), PL, true);
+        const Pk<NP> ngt[4] = {neg_pk<NP>(agt[0]), neg_pk<NP>(agt[1]), neg_pk<NP>(agt[2]), neg_pk<NP>(agt[3])};
+        state_update_direct<NP>(wt, ngt, pk, lane);
+      }
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
         const float2 b2 = *reinterpret_cast<const float2*>(bsv + nb + 8 * nt + 2 * t);
@@ -262,7 +270,8 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
     for (int kt = 0; kt < 8; ++kt)
 #pragma unroll
       for (int rn = 0; rn < 2; ++rn) {
-        st_pair_planes<NP>(tW + warp * SM::PLANES, g + 8 * rn, 8 * kt + 2 * t, wt[kt][2 * rn], wt[kt][2 * rn + 1]);
+        st_pair_planes<NP>(tW + warp * SM::PLANES, g + 8 * rn, 8 * kt + 2 * t, wt[kt][2 * rn] * wscale,
+                           wt[kt][2 * rn + 1] * wscale);
         st_pair_planes<NP>(tDW + warp * SM::PLANES, g + 8 * rn, 8 * kt + 2 * t, dwt[kt][2 * rn], dwt[kt][2 * rn + 1]);
       }
     // ---- 3. Z1 = K W + b, Zq = Q W + b, KdW = K dW, Attn = Q K^T
@@ -270,12 +279,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        z1[nt][i] = bias[2 * nt + (i & 1)];
-        zq[nt][i] = bias[2 * nt + (i & 1)];
-        kdw[nt][i] = 0.f;
-        at[nt][i] = 0.f;
-      }
+      for (int i = 0; i < 4; ++i) z1[nt][i] = zq[nt][i] = kdw[nt][i] = at[nt][i] = 0.f;
 #pragma unroll
     for (int ks = 0; ks < 4; ++ks) {
       Pk<NP> bw[2][2], bdw[2][2], ak[4], aq[4], bk[4];
@@ -294,6 +298,14 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       mma_np<NP>(at[0], aq, bj0);
       mma_np<NP>(at[1], aq, bj1);
     }
+    // products were taken with What: Z = wscale * acc + b
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        z1[nt][i] = fmaf(z1[nt][i], wscale, bias[2 * nt + (i & 1)]);
+        zq[nt][i] = fmaf(zq[nt][i], wscale, bias[2 * nt + (i & 1)]);
+      }
     // ---- 4. LN + L2 pieces of Z1 from the saved row statistics
     float mean1[2], rstd1[2], Bv1[2], mean2[2], rstd2[2];
     F2 xh[2][2], gy[2][2], gx[2][2], G[2][2];

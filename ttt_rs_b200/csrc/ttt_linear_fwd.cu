@@ -99,6 +99,11 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
   }
   const float te_row[2] = {ld_as_float<T>(p.token_eta, g), ld_as_float<T>(p.token_eta, g + 8)};
   const float te15 = ld_as_float<T>(p.token_eta, CS - 1);
+  // The state is carried as What = W / wscale with wscale = -te15, so that the update W -= te15 Gp^T K becomes
+  // What += Gp^T K, accumulated by the tensor cores straight into the registers.  (te15 == 0: W never changes.)
+  const bool w_moves = (te15 != 0.f);
+  const float wscale = w_moves ? -te15 : 1.f;
+  const float winv = 1.f / wscale;
 
   // ---- state W^T[n][k], n in {nb+g, nb+g+8}: wt[kt][2*rn + e] = W[k = 8kt+2t+e][n = nb+g+8rn]
   float wt[8][4];
@@ -107,7 +112,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int k = 8 * kt + 2 * t + (i & 1), n = nb + g + 8 * (i >> 1);
-      wt[kt][i] = ld_as_float<T>(p.w0, (size_t)stream * HD * HD + k * HD + n);
+      wt[kt][i] = ld_as_float<T>(p.w0, (size_t)stream * HD * HD + k * HD + n) * winv;
     }
 
   int xsel = 0;
@@ -137,7 +142,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
 #pragma unroll
       for (int kt = 0; kt < 8; ++kt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) wc[(8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1)] = wt[kt][i];
+        for (int i = 0; i < 4; ++i) wc[(8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1)] = wt[kt][i] * wscale;
     }
     if (g == 0) {
       float* bs = p.b_stage + ((size_t)stream * (NS + 1) + s) * HD;
@@ -153,11 +158,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        z1[nt][i] = bias[2 * nt + (i & 1)];
-        zq[nt][i] = bias[2 * nt + (i & 1)];
-        at[nt][i] = 0.f;
-      }
+      for (int i = 0; i < 4; ++i) z1[nt][i] = zq[nt][i] = at[nt][i] = 0.f;
 #pragma unroll
     for (int ks = 0; ks < 4; ++ks) {
       Pk<NP> bw[2][2];
@@ -175,11 +176,23 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
       mma_np<NP>(at[0], aq, bj0);
       mma_np<NP>(at[1], aq, bj1);
     }
+    // products were taken with What: Z = wscale * acc + b
+    F2 z1p[2][2], zqp[2][2];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const F2 b2 = f2(bias[2 * nt], bias[2 * nt + 1]);
+        z1p[nt][r] = f2fma(pr(z1[nt], r), f2(wscale), b2);
+        zqp[nt][r] = f2fma(pr(zq[nt], r), f2(wscale), b2);
+      }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      zq[nt][0] = zqp[nt][0].x; zq[nt][1] = zqp[nt][0].y; zq[nt][2] = zqp[nt][1].x; zq[nt][3] = zqp[nt][1].y;
+    }
 
     // ---- LN statistics of Z1, then G = dL/dZ1 and Gp = lr[row] * G
     float mean[2], rstd[2];
-    F2 z1p[2][2];
-    slab_pairs(z1, z1p);
     ln_row_stats<TWO_PASS>(z1p, xch, xsel, L, p.eps, mean, rstd, fail);
     if (fail) {
       failed = true;
@@ -241,7 +254,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     // ---- state update: W^T[nb.., :] -= te15 * Gp^T K ; b -= te15 * colsum(Gp)
     {
       const Pk<NP> agt[4] = {gt[0][0], gt[1][0], gt[0][1], gt[1][1]};
-      state_update<NP>(wt, agt, pk, lane, -te15);
+      if (w_moves) state_update_direct<NP>(wt, agt, pk, lane);
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
         const F2 cs = f2add(gp[nt][0], gp[nt][1]);
@@ -291,8 +304,8 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int idx = (8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1);
-        st_from_float<T>(p.w_out, (size_t)stream * HD * HD + idx, wt[kt][i]);
-        wc[idx] = wt[kt][i];
+        st_from_float<T>(p.w_out, (size_t)stream * HD * HD + idx, wt[kt][i] * wscale);
+        wc[idx] = wt[kt][i] * wscale;
       }
     if (g == 0) {
 #pragma unroll

@@ -182,6 +182,29 @@ __device__ __forceinline__ void state_update(float (&wt)[8][4], const Pk<NP> (&a
   }
 }
 
+// Same rank-16 update accumulated straight into the state registers: S^T += A^T-fragments x K.  Used with the state
+// kept as W / (-te15), so neither temporaries nor a scaling pass are needed; the backward's reversal passes the
+// fragments with their sign bits flipped.
+template <int NP>
+__device__ __forceinline__ void state_update_direct(float (&wt)[8][4], const Pk<NP> (&agt)[4], uint32_t k_planes,
+                                                    int lane) {
+#pragma unroll
+  for (int kp = 0; kp < 4; ++kp) {
+    Pk<NP> bk[4];
+    ldsm_np<NP>(bk, k_planes + lane_off_B_kn(lane, 16 * kp), TILE_BF16_BYTES, true);
+    const Pk<NP> b0[2] = {bk[0], bk[1]}, b1[2] = {bk[2], bk[3]};
+    mma_np<NP>(wt[2 * kp], agt, b0);
+    mma_np<NP>(wt[2 * kp + 1], agt, b1);
+  }
+}
+template <int NP>
+__device__ __forceinline__ Pk<NP> neg_pk(const Pk<NP>& a) {
+  Pk<NP> r;
+#pragma unroll
+  for (int i = 0; i < NP; ++i) r.p[i] = a.p[i] ^ 0x80008000u;
+  return r;
+}
+
 __device__ __forceinline__ void report_timeout(uint32_t* status, uint32_t where, uint32_t stage) {
   if (status != nullptr && atomicCAS(status, 0u, (uint32_t)KST_TIMEOUT) == 0u) {
     status[1] = where;
