@@ -145,6 +145,10 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
   const F2 bet = f2(ld_as_float<T>(p.ln_b, (size_t)head * HD + fc), ld_as_float<T>(p.ln_b, (size_t)head * HD + fc + 1));
   const float te_row[2] = {ld_as_float<T>(p.token_eta, g), ld_as_float<T>(p.token_eta, g + 8)};
   const float te15 = ld_as_float<T>(p.token_eta, CS - 1);
+  // both states are carried divided by wscale = -te15, so that their rank-16 updates accumulate directly by mma
+  const bool w_moves = (te15 != 0.f);
+  const float wscale = w_moves ? -te15 : 1.f;
+  const float winv = 1.f / wscale;
   F2 b2v = f2(ld_as_float<T>(p.b2, (size_t)stream * HD + fc), ld_as_float<T>(p.b2, (size_t)stream * HD + fc + 1));
   F2 b1v[4];
 #pragma unroll
@@ -161,8 +165,8 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int e = eb + 16 * mt + g + 8 * (i >> 1), c = 8 * kt + 2 * t + (i & 1);
-        w1t[mt][kt][i] = ld_as_float<T>(p.w1, (size_t)stream * HD * MLP_E + (size_t)c * MLP_E + e);
-        w2[mt][kt][i] = ld_as_float<T>(p.w2, (size_t)stream * HD * MLP_E + (size_t)e * HD + c);
+        w1t[mt][kt][i] = ld_as_float<T>(p.w1, (size_t)stream * HD * MLP_E + (size_t)c * MLP_E + e) * winv;
+        w2[mt][kt][i] = ld_as_float<T>(p.w2, (size_t)stream * HD * MLP_E + (size_t)e * HD + c) * winv;
       }
   // bf16 copy of this warp's 32 rows of W2 -> sub-tiles 2*warp, 2*warp+1
   auto publish_w2 = [&]() {
@@ -173,7 +177,7 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
 #pragma unroll
         for (int rn = 0; rn < 2; ++rn)
           asm volatile("st.shared.b32 [%0], %1;" ::"r"(tW2 + (2 * warp + mt) * TL + off_bf16(g + 8 * rn, 8 * nt + 2 * t)),
-                       "r"(pack_bf16(w2[mt][nt][2 * rn], w2[mt][nt][2 * rn + 1]))
+                       "r"(pack_bf16(w2[mt][nt][2 * rn] * wscale, w2[mt][nt][2 * rn + 1] * wscale))
                        : "memory");
   };
   publish_w2();
@@ -204,11 +208,7 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
 #pragma unroll
     for (int j = 0; j < 4; ++j)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float b = (i & 1) ? b1v[j].y : b1v[j].x;
-        z1[j][i] = b;
-        zq[j][i] = b;
-      }
+      for (int i = 0; i < 4; ++i) z1[j][i] = zq[j][i] = 0.f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) at[0][i] = at[1][i] = 0.f;
 #pragma unroll
@@ -231,6 +231,15 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
       mma_np<1>(at[0], aq, bj0);
       mma_np<1>(at[1], aq, bj1);
     }
+    // products were taken with W1 / wscale: Z = wscale * acc + b1
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float b = (i & 1) ? b1v[j].y : b1v[j].x;
+        z1[j][i] = fmaf(z1[j][i], wscale, b);
+        zq[j][i] = fmaf(zq[j][i], wscale, b);
+      }
     // ---- S2. X2 = gelu(Z1), D1 = gelu'(Z1); X2 to its operand tile
     F2 x2[4][2], d1[4][2];
 #pragma unroll
@@ -318,7 +327,7 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
 #pragma unroll
       for (int j = 0; j < 4; ++j)
 #pragma unroll
-        for (int r = 0; r < 2; ++r) g1p[j][r] = f2mul(pr(h[j], r), d1[j][r]);
+        for (int r = 0; r < 2; ++r) g1p[j][r] = f2mul(f2mul(pr(h[j], r), f2(wscale)), d1[j][r]);
     }
     // ---- S6. Zb1 = Zq - M1' G1p (G1p transposed through movmatrix; the same fragments update W1 later)
     Pk<1> gt1[4][2];
@@ -424,7 +433,7 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt) {
       const Pk<1> agt[4] = {gt1[2 * mt][0], gt1[2 * mt + 1][0], gt1[2 * mt][1], gt1[2 * mt + 1][1]};
-      state_update<1>(w1t[mt], agt, tk, lane, -te15);
+      if (w_moves) state_update_direct<1>(w1t[mt], agt, tk, lane);
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -440,7 +449,7 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
         const Pk<1> ax[4] = {xt[2 * mt][0], xt[2 * mt + 1][0], xt[2 * mt][1], xt[2 * mt + 1][1]};
-        state_update<1>(w2[mt], ax, tG2, lane, -te15);
+        if (w_moves) state_update_direct<1>(w2[mt], ax, tG2, lane);
       }
       const F2 cs = f2add(g2p[0], g2p[1]);
       b2v = f2fma(f2(col_sum(cs.x), col_sum(cs.y)), f2(-te15), b2v);
@@ -455,8 +464,8 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int e = eb + 16 * mt + g + 8 * (i >> 1), c = 8 * kt + 2 * t + (i & 1);
-          st_from_float<T>(p.w1_out, (size_t)stream * HD * MLP_E + (size_t)c * MLP_E + e, w1t[mt][kt][i]);
-          st_from_float<T>(p.w2_out, (size_t)stream * HD * MLP_E + (size_t)e * HD + c, w2[mt][kt][i]);
+          st_from_float<T>(p.w1_out, (size_t)stream * HD * MLP_E + (size_t)c * MLP_E + e, w1t[mt][kt][i] * wscale);
+          st_from_float<T>(p.w2_out, (size_t)stream * HD * MLP_E + (size_t)e * HD + c, w2[mt][kt][i] * wscale);
         }
     if (g == 0) {
 #pragma unroll
