@@ -300,8 +300,11 @@ def main():
     total_b, fb, bb = algorithmic_bytes(w, True, w["backward"])
     dom_ms, dom_bytes, dom_name = (bwd_ms, bb, "ttt_linear_bwd_kernel") if w["backward"] else (fwd_ms, fb, "ttt_mlp_fwd_kernel" if mlp else "ttt_linear_fwd_kernel")
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
+    # DRAM bytes per launch of the dominant kernel from the committed ncu capture of this same command
+    # (profiles/ttt_linear_bwd_kernel_cfg1_bf16.md: dram__bytes_read.sum + dram__bytes_write.sum); other workloads: none
+    traffic = 599.1e6 + 351.9e6 if args.workload == "cfg1" else None
     roof = {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
-            "frac": achieved / peak, "traffic": None, "peak_source": f"of {peak_kind}",
+            "frac": achieved / peak, "traffic": traffic, "peak_source": f"of {peak_kind}",
             "algorithmic_bytes_per_launch": dom_bytes, "ms_per_launch": dom_ms,
             "fwd": {"achieved": fb / (fwd_ms * 1e-3) / 1e9, "frac": fb / (fwd_ms * 1e-3) / 1e9 / peak, "ms_per_launch": fwd_ms},
             "step": {"achieved": total_b / (ms * 1e-3) / 1e9, "frac": total_b / (ms * 1e-3) / 1e9 / peak}}

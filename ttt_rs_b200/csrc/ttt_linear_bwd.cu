@@ -658,31 +658,49 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
 //   packed (optional) = { sum_b dW[b,h], sum_b db[b,h], d_ln_w, d_ln_b, d_token_eta folded to [CS] }
 //                       (the fold is a second tiny kernel over the reduced d_token_eta)
 // ----------------------------------------------------------------------------------------------------
-__global__ void ttt_linear_bwd_reduce_kernel(const ReduceParams p) {
-  const int H = p.H, B = p.B, T = p.T;
+// Block = 32 consecutive outputs x 8 warps.  Warp w sums terms w, w+8, ... of each output (coalesced 128-byte
+// reads), the eight partial sums meet in shared memory and are added in warp order: a fixed summation order.
+__global__ void __launch_bounds__(256) ttt_linear_bwd_reduce_kernel(const ReduceParams p) {
+  __shared__ float part[8][32];
+  const int H = p.H, B = p.B, T = p.T, NCH = p.NCH;
   const int n_te = T, n_ln = 2 * H * HD, n_w = (p.packed != nullptr) ? H * (HD * HD + HD) : 0;
   const int total = n_te + n_ln + n_w;
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int base = blockIdx.x * 32; base < total; base += gridDim.x * 32) {
+    const int i = base + lane;
+    float acc = 0.f;
     if (i < n_te) {
-      float acc = 0.f;
-      for (int st = 0; st < B * H; ++st) acc += p.part_te[(size_t)st * T + i];
-      p.d_token_eta[i] = acc;
+      for (int st = warp; st < B * H; st += 8) acc += p.part_te[(size_t)st * T + i];
     } else if (i < n_te + n_ln) {
       const int k = i - n_te, which = k / (H * HD), hf = k % (H * HD), h = hf / HD, f = hf % HD;
-      float acc = 0.f;
-      for (int b = 0; b < B; ++b)
-        for (int ch = 0; ch < p.NCH; ++ch) acc += p.part_ln[(((size_t)(b * H + h) * p.NCH + ch) * 2 + which) * HD + f];
-      (which == 0 ? p.d_ln_g : p.d_ln_b)[hf] = acc;
-      if (p.packed != nullptr) p.packed[(size_t)H * HD * HD + H * HD + k] = acc;
-    } else {
+      for (int j = warp; j < B * NCH; j += 8) {
+        const int b = j / NCH, ch = j - b * NCH;
+        acc += p.part_ln[(((size_t)(b * H + h) * NCH + ch) * 2 + which) * HD + f];
+      }
+    } else if (i < total) {
       const int k = i - n_te - n_ln;
       const bool is_w = k < H * HD * HD;
       const int h = is_w ? k / (HD * HD) : (k - H * HD * HD) / HD;
       const int e = is_w ? k % (HD * HD) : HD * HD + (k - H * HD * HD) % HD;
-      float acc = 0.f;
-      for (int b = 0; b < B; ++b) acc += p.part_w[(size_t)(b * H + h) * (HD * HD + HD) + e];
-      p.packed[k] = acc;
+      for (int b = warp; b < B; b += 8) acc += p.part_w[(size_t)(b * H + h) * (HD * HD + HD) + e];
     }
+    part[warp][lane] = acc;
+    __syncthreads();
+    if (warp == 0 && i < total) {
+      float sum = part[0][lane];
+#pragma unroll
+      for (int w = 1; w < 8; ++w) sum += part[w][lane];
+      if (i < n_te) {
+        p.d_token_eta[i] = sum;
+      } else if (i < n_te + n_ln) {
+        const int k = i - n_te;
+        (k < H * HD ? p.d_ln_g : p.d_ln_b)[k % (H * HD)] = sum;
+        if (p.packed != nullptr) p.packed[(size_t)H * HD * HD + H * HD + k] = sum;
+      } else {
+        p.packed[i - n_te - n_ln] = sum;
+      }
+    }
+    __syncthreads();
   }
 }
 
@@ -728,10 +746,9 @@ cudaError_t launch_linear_bwd(int dtype, const CUtensorMap* maps, const LinBwdPa
 
 cudaError_t launch_linear_bwd_reduce(const ReduceParams& p, cudaStream_t st) {
   const int total = p.T + 2 * p.H * HD + (p.packed != nullptr ? p.H * (HD * HD + HD) : 0);
-  const int threads = 128;
-  int blocks = (total + threads - 1) / threads;
+  int blocks = (total + 31) / 32;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  ttt_linear_bwd_reduce_kernel<<<blocks, threads, 0, st>>>(p);
+  ttt_linear_bwd_reduce_kernel<<<blocks, 256, 0, st>>>(p);
   if (p.packed != nullptr) ttt_linear_bwd_fold_kernel<<<1, CS * 32, 0, st>>>(p);
   return cudaGetLastError();
 }

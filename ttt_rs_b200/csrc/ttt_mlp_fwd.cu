@@ -32,8 +32,8 @@ struct MlpSmem {
   static constexpr uint32_t OFF_G2 = OFF_XB2 + 4 * TILE;              // [16 tok][64 n]
   static constexpr uint32_t OFF_OUT = OFF_G2 + TILE;                  // 2 staging tiles
   static constexpr uint32_t OFF_A2 = OFF_OUT + 2 * TILE;              // 8 warps x 32 lanes x 8 floats
-  static constexpr uint32_t OFF_XCH = OFF_A2 + 8 * 32 * 32;           // 2 x [16 rows][8 warps] float2
-  static constexpr uint32_t OFF_LR = OFF_XCH + 2 * 16 * 8 * 8;        // MLP_NST x 32 bytes
+  static constexpr uint32_t OFF_XCH = OFF_A2 + 8 * 32 * 32;           // 2 x [16 rows][10] float2 (8 warps + padding)
+  static constexpr uint32_t OFF_LR = OFF_XCH + 2 * 16 * 10 * 8;       // MLP_NST x 32 bytes
   static constexpr uint32_t OFF_BAR = OFF_LR + MLP_NST * 32;
   static constexpr uint32_t TOTAL = OFF_BAR + MLP_NST * 8;
   static constexpr uint32_t DYN_BYTES = TOTAL + 1024;
@@ -60,20 +60,21 @@ __device__ __forceinline__ F2 gelu2(F2 z, F2* deriv) {
   return f2fma(hz, th, hz);
 }
 
-// row sums of two values over the 8 warps (rows g and g+8); buffer float2[16][8]
+// row sums of two values over the 8 warps (rows g and g+8); buffer float2[16][10] (rows padded to 80 bytes so that
+// the 8 rows a warp reads fall in distinct banks)
 __device__ __forceinline__ void xch8(float2* xb, const Lane& L, float a0x, float a0y, float a1x, float a1y, float2& o0,
                                      float2& o1, int& flag) {
   a0x = quad_sum(a0x); a0y = quad_sum(a0y); a1x = quad_sum(a1x); a1y = quad_sum(a1y);
   if (L.t == 0) {
-    xb[L.g * 8 + L.warp] = make_float2(a0x, a0y);
-    xb[(L.g + 8) * 8 + L.warp] = make_float2(a1x, a1y);
+    xb[L.g * 10 + L.warp] = make_float2(a0x, a0y);
+    xb[(L.g + 8) * 10 + L.warp] = make_float2(a1x, a1y);
   }
   flag = __syncthreads_or(flag);
   float2 s0 = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const float4 p = *reinterpret_cast<const float4*>(&xb[L.g * 8 + 2 * i]);
-    const float4 q = *reinterpret_cast<const float4*>(&xb[(L.g + 8) * 8 + 2 * i]);
+    const float4 p = *reinterpret_cast<const float4*>(&xb[L.g * 10 + 2 * i]);
+    const float4 q = *reinterpret_cast<const float4*>(&xb[(L.g + 8) * 10 + 2 * i]);
     s0.x += p.x + p.z; s0.y += p.y + p.w;
     s1.x += q.x + q.z; s1.y += q.y + q.w;
   }
@@ -102,7 +103,7 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
   const uint32_t base = (raw_u32 + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (base - raw_u32);
   float2* xchb = reinterpret_cast<float2*>(gbase + SM::OFF_XCH);  // 2 x [16][8]
-  float4* a2b = reinterpret_cast<float4*>(gbase + SM::OFF_A2);    // [8 warps][32 lanes][2]
+  float4* a2b = reinterpret_cast<float4*>(gbase + SM::OFF_A2);    // [8 warps][2][32 lanes]
   const uint32_t bar0 = base + SM::OFF_BAR;
   const uint32_t tW2 = base + SM::OFF_W2, tX2 = base + SM::OFF_X2, tXB2 = base + SM::OFF_XB2, tG2 = base + SM::OFF_G2;
 
@@ -280,7 +281,7 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
       const F2 zp[2] = {pr(z2, 0), pr(z2, 1)};
       float2 a0, a1;
       int f0 = 0;
-      xch8(xchb + xsel * 128, L, f2hsum(zp[0]), f2hsum(f2mul(zp[0], zp[0])), f2hsum(zp[1]), f2hsum(f2mul(zp[1], zp[1])),
+      xch8(xchb + xsel * 160, L, f2hsum(zp[0]), f2hsum(f2mul(zp[0], zp[0])), f2hsum(zp[1]), f2hsum(f2mul(zp[1], zp[1])),
            a0, a1, f0);
       xsel ^= 1;
       const float mean[2] = {a0.x * (1.f / HD), a1.x * (1.f / HD)};
@@ -293,7 +294,7 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
         x[r] = f2mul(f2sub(zp[r], f2(mean[r])), f2(rstd[r]));
         gg[r] = f2mul(f2fma(gam, x[r], f2sub(bet, tg)), gam);
       }
-      xch8(xchb + xsel * 128, L, f2hsum(gg[0]), f2hsum(f2mul(gg[0], x[0])), f2hsum(gg[1]), f2hsum(f2mul(gg[1], x[1])),
+      xch8(xchb + xsel * 160, L, f2hsum(gg[0]), f2hsum(f2mul(gg[0], x[0])), f2hsum(gg[1]), f2hsum(f2mul(gg[1], x[1])),
            a0, a1, f0);
       xsel ^= 1;
       const float A[2] = {a0.x * (1.f / HD), a1.x * (1.f / HD)}, Bv[2] = {a0.y * (1.f / HD), a1.y * (1.f / HD)};
@@ -370,15 +371,15 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
           mma_bf16(a2p[jt], A0, A1, A2, A3, pack_bf16(x2[2 * c][jt].x, x2[2 * c][jt].y),
                    pack_bf16(x2[2 * c + 1][jt].x, x2[2 * c + 1][jt].y));
       }
-      a2b[(warp * 32 + lane) * 2] = make_float4(a2p[0][0], a2p[0][1], a2p[0][2], a2p[0][3]);
-      a2b[(warp * 32 + lane) * 2 + 1] = make_float4(a2p[1][0], a2p[1][1], a2p[1][2], a2p[1][3]);
+      a2b[(warp * 2 + 0) * 32 + lane] = make_float4(a2p[0][0], a2p[0][1], a2p[0][2], a2p[0][3]);
+      a2b[(warp * 2 + 1) * 32 + lane] = make_float4(a2p[1][0], a2p[1][1], a2p[1][2], a2p[1][3]);
       __syncthreads();  // B3: partials and the Xb2 tile visible
 #pragma unroll
       for (int jt = 0; jt < 2; ++jt) {
-        float4 acc = a2b[lane * 2 + jt];
+        float4 acc = a2b[jt * 32 + lane];
 #pragma unroll
         for (int w = 1; w < 8; ++w) {
-          const float4 v = a2b[(w * 32 + lane) * 2 + jt];
+          const float4 v = a2b[(w * 2 + jt) * 32 + lane];
           acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
         a2[jt][0] = acc.x; a2[jt][1] = acc.y; a2[jt][2] = acc.z; a2[jt][3] = acc.w;
@@ -408,7 +409,7 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
       const F2 zp[2] = {pr(zb2, 0), pr(zb2, 1)};
       float2 a0, a1;
       int f0 = 0;
-      xch8(xchb + xsel * 128, L, f2hsum(zp[0]), f2hsum(f2mul(zp[0], zp[0])), f2hsum(zp[1]), f2hsum(f2mul(zp[1], zp[1])),
+      xch8(xchb + xsel * 160, L, f2hsum(zp[0]), f2hsum(f2mul(zp[0], zp[0])), f2hsum(zp[1]), f2hsum(f2mul(zp[1], zp[1])),
            a0, a1, f0);
       xsel ^= 1;
       const float mean[2] = {a0.x * (1.f / HD), a1.x * (1.f / HD)};
