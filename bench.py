@@ -47,6 +47,10 @@ WORKLOADS = {
                      desc="TTT-MLP inner loop fwd (64-256-64, GELU tanh), bf16, B=16 H=12 T=2048 d=64 mb=16"),
     "cfg4-8k": dict(B=8, H=32, T=8192, dtype="bf16", K=16, backward=True,
                     desc="TTT-Linear inner loop fwd+bwd, bf16, B=8 H=32 T=8192 d=64 mb=16 ckpt=16"),
+    "cfg4-16k": dict(B=8, H=32, T=16384, dtype="bf16", K=16, backward=True,
+                     desc="TTT-Linear inner loop fwd+bwd, bf16, B=8 H=32 T=16384 d=64 mb=16 ckpt=16"),
+    "cfg4-32k": dict(B=8, H=32, T=32768, dtype="bf16", K=16, backward=True,
+                     desc="TTT-Linear inner loop fwd+bwd, bf16, B=8 H=32 T=32768 d=64 mb=16 ckpt=16"),
 }
 F, CS = 64, 16
 
