@@ -121,6 +121,22 @@ int ttt_linear_backward(const ttt_dims* d, const void* xq, const void* xk, const
                         float* grad_ln_bias, float* outer_grad_packed, void* workspace, size_t workspace_bytes,
                         void* status, void* stream);
 
+/* Backward that also takes upstream gradients of the returned final state (either may be null = zero):
+ *   grad_weight_out  T [B,H,F,F], grad_bias_out  T [B,H,F]
+ * The reference drops these gradients (launch.rs:188-194; backward/kernel.rs:293-300 starts dW_last/db_last at
+ * zero); with them the operator is a complete autograd node, so a long sequence can be trained in chunks with the
+ * state (and its gradient) carried from chunk to chunk.  Everything else as in ttt_linear_backward.
+ */
+int ttt_linear_backward_state_grads(const ttt_dims* d, const void* xq, const void* xk, const void* xv,
+                                    const void* weight, const void* bias, const void* token_eta,
+                                    const void* ttt_lr_eta, const void* ln_weight, const void* ln_bias,
+                                    const void* weight_ckpt, const void* bias_ckpt, const void* grad_output,
+                                    const void* grad_weight_out, const void* grad_bias_out, void* grad_xq,
+                                    void* grad_xk, void* grad_xv, void* grad_weight, void* grad_bias,
+                                    void* grad_ttt_lr_eta, float* grad_token_eta, float* grad_ln_weight,
+                                    float* grad_ln_bias, float* outer_grad_packed, void* workspace,
+                                    size_t workspace_bytes, void* status, void* stream);
+
 /* Forward of the whole sequence for the 2-layer inner model (TTT-MLP, hidden width E = 4*F, GELU tanh).
  * The reference has no fused kernel for it; this replaces the loop of `TTTMLP::forward_mini_batch`
  * (rust/core/src/mlp.rs:127-208) behind `TTTInnerModel::forward` (rust/core/src/inner.rs:25-50), with the fused

@@ -172,11 +172,13 @@ def _stage_states(xk, xv, weight, bias, te, lr_s, g_, be_, cs, eps):
 def ttt_linear_backward(
     xq, xk, xv, weight, bias, token_eta, ttt_lr_eta, ln_weight, ln_bias, grad_output,
     mini_batch: int = 16, eps: float = 1e-6,
+    grad_weight_out: Optional[torch.Tensor] = None, grad_bias_out: Optional[torch.Tensor] = None,
 ) -> Dict[str, torch.Tensor]:
-    """Analytic backward of `ttt_linear_forward` for loss = <grad_output, output>.
+    """Analytic backward of `ttt_linear_forward` for loss = <grad_output, output>
+    (+ <grad_weight_out, final weight> + <grad_bias_out, final bias> when those are given).
 
-    Gradients w.r.t. the returned final state are taken as zero, as the
-    reference's backward does.  Returns dict with
+    By default gradients w.r.t. the returned final state are taken as zero, as the
+    reference's backward does (rust/fused/src/linear_fused_tile/launch.rs:188-194).  Returns dict with
     grad_xq/xk/xv [B,H,T,F], grad_weight [B,H,F,F] (per batch element),
     grad_bias [B,H,F], grad_ttt_lr_eta [B,H,T], grad_token_eta [T]
     (written per stage at stage*CS+i, summed over B and H),
@@ -200,8 +202,8 @@ def ttt_linear_backward(
     dte = torch.zeros(T, dtype=xq.dtype)
     dgam = torch.zeros(B, H, F, dtype=xq.dtype)
     dbet = torch.zeros(B, H, F, dtype=xq.dtype)
-    dW = torch.zeros_like(weight)
-    db = torch.zeros_like(bias)
+    dW = torch.zeros_like(weight) if grad_weight_out is None else grad_weight_out.clone()
+    db = torch.zeros_like(bias) if grad_bias_out is None else grad_bias_out.clone()
 
     for s in reversed(range(ns)):
         Q, Kk, V, lr, dO = q_s[:, :, s], k_s[:, :, s], v_s[:, :, s], lr_s[:, :, s], do_s[:, :, s]
@@ -284,6 +286,7 @@ def ttt_linear_backward(
 def ttt_linear_backward_autograd(
     xq, xk, xv, weight, bias, token_eta, ttt_lr_eta, ln_weight, ln_bias, grad_output,
     mini_batch: int = 16, eps: float = 1e-6,
+    grad_weight_out: Optional[torch.Tensor] = None, grad_bias_out: Optional[torch.Tensor] = None,
 ) -> Dict[str, torch.Tensor]:
     """Same contract as `ttt_linear_backward`, via torch autograd over the forward
     restatement.  Used to cross-check the analytic backward.
@@ -317,7 +320,14 @@ def ttt_linear_backward_autograd(
         W = W - (last * Kk).transpose(-1, -2) @ G
         bb = bb - (last * G).sum(dim=-2)
     out = torch.cat(outs, dim=2)
-    grads = torch.autograd.grad(out, leaves + [te_full], grad_outputs=grad_output)
+    roots, root_grads = [out], [grad_output]
+    if grad_weight_out is not None:
+        roots.append(W)
+        root_grads.append(grad_weight_out)
+    if grad_bias_out is not None:
+        roots.append(bb)
+        root_grads.append(grad_bias_out)
+    grads = torch.autograd.grad(roots, leaves + [te_full], grad_outputs=root_grads)
     names = ["grad_xq", "grad_xk", "grad_xv", "grad_weight", "grad_bias",
              "grad_ttt_lr_eta", "grad_ln_weight", "grad_ln_bias", "grad_token_eta"]
     return dict(zip(names, grads))

@@ -95,3 +95,47 @@ def test_autograd_function_matches_oracle():
     ref = _oracle(t)
     for name in GRADS:
         assert_close(leaves[name].grad, ref["grad_" + name], 1e-4, f"grad_{name}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_backward_with_final_state_gradients(dtype):
+    """Upstream gradients of the returned final state (opt-in; the reference drops them): against the oracle, and
+    as backward-through-time in two chunks that must reproduce the one-shot gradients."""
+    import ttt_rs_b200 as tb
+    dev = torch.device("cuda:0")
+    t = _case(2, 2, 8, 77, dtype)
+    g = torch.Generator().manual_seed(5)
+    gw = (0.1 * torch.randn(t["weight"].shape, generator=g)).to(dtype)
+    gb = (0.1 * torch.randn(t["bias"].shape, generator=g)).to(dtype)
+    cfg = tb.FusedTttConfig.new(16, 64, 1e-6, 128, 4)
+    r = RTOL[dtype]
+    frac = 1e-4 if dtype == torch.bfloat16 else 0.0
+
+    def run(tt, go, gwo=None, gbo=None):
+        ins = tb.TttInputs(*[tt[k].to(dev) for k in LIN_IN])
+        outs, saved = tb.TttTileMultiKernel.forward_launch(ins, cfg)
+        grads = tb.TttTileMultiKernel.backward_launch(
+            saved, tb.TttOutputs(go.to(dev), None if gwo is None else gwo.to(dev), None if gbo is None else gbo.to(dev)),
+            cfg, use_state_grads=True)
+        torch.cuda.synchronize()
+        return outs, grads
+
+    _, grads = run(t, t["grad_output"], gw, gb)
+    ref = O.ttt_linear_backward(*[t[k].double() for k in LIN_IN], t["grad_output"].double(),
+                                grad_weight_out=gw.double(), grad_bias_out=gb.double())
+    for name in GRADS:
+        assert_close(getattr(grads, name), ref["grad_" + name], r, f"grad_{name}", max_bad_frac=frac)
+
+    # chunked: tokens [0,64) then [64,128) with the state carried forward and its gradient carried back
+    _, full = run(t, t["grad_output"])
+    seq = ("xq", "xk", "xv", "ttt_lr_eta")
+    first = {k: (t[k][:, :, :64] if k in seq else t[k]) for k in LIN_IN}
+    o1, _ = run(first, t["grad_output"][:, :, :64])
+    second = {k: (t[k][:, :, 64:] if k in seq else t[k]) for k in LIN_IN}
+    second["weight"], second["bias"] = o1.weight.cpu(), o1.bias.cpu()
+    _, g2 = run(second, t["grad_output"][:, :, 64:])
+    _, g1 = run(first, t["grad_output"][:, :, :64], g2.weight.cpu(), g2.bias.cpu())
+    tol = 2 * r  # the carried state and its gradient are rounded to the I/O type between the chunks
+    assert_close(torch.cat([g1.xk, g2.xk], dim=2), full.xk.double(), tol, "chunked grad_xk", max_bad_frac=frac)
+    assert_close(torch.cat([g1.xq, g2.xq], dim=2), full.xq.double(), tol, "chunked grad_xq", max_bad_frac=frac)
+    assert_close(g1.weight, full.weight.double(), tol, "chunked grad_weight", max_bad_frac=frac)

@@ -125,3 +125,31 @@ def test_gelu_grad_is_derivative(x):
     assert abs(g.item() - O.gelu_tanh_grad(xt.detach()).item()) < 1e-12
     ref = torch.nn.functional.gelu(xt.detach(), approximate="tanh")
     assert abs(ref.item() - O.gelu_tanh(xt.detach()).item()) < 1e-12
+
+
+def test_linear_backward_with_final_state_gradients_matches_autograd():
+    """Upstream gradients for the returned final state: analytic backward == autograd, and the gradients of a
+    sequence equal those of two chunks chained through the state (backward through time in chunks)."""
+    t = O.make_inputs(2, 2, 64, 64, 16, seed=8, dtype=torch.float64)
+    g = torch.Generator().manual_seed(9)
+    gw = torch.randn(t["weight"].shape, generator=g, dtype=torch.float64) * 0.1
+    gb = torch.randn(t["bias"].shape, generator=g, dtype=torch.float64) * 0.1
+    args = [t[k] for k in LIN_IN]
+    a = O.ttt_linear_backward(*args, t["grad_output"], grad_weight_out=gw, grad_bias_out=gb)
+    b = O.ttt_linear_backward_autograd(*args, t["grad_output"], grad_weight_out=gw, grad_bias_out=gb)
+    for k in a:
+        assert_close(a[k], b[k], 1e-9, k)
+    # two chunks of 32 tokens
+    full = O.ttt_linear_backward(*args, t["grad_output"])
+    seq = ("xq", "xk", "xv", "ttt_lr_eta")
+    sl = lambda k, lo, hi: t[k][:, :, lo:hi] if k in seq else t[k]
+    first = {k: sl(k, 0, 32) for k in LIN_IN}
+    f1 = O.ttt_linear_forward(*[first[k] for k in LIN_IN])
+    second = {k: sl(k, 32, 64) for k in LIN_IN}
+    second["weight"], second["bias"] = f1["weight"], f1["bias"]
+    b2 = O.ttt_linear_backward(*[second[k] for k in LIN_IN], t["grad_output"][:, :, 32:])
+    b1 = O.ttt_linear_backward(*[first[k] for k in LIN_IN], t["grad_output"][:, :, :32],
+                               grad_weight_out=b2["grad_weight"], grad_bias_out=b2["grad_bias"])
+    assert_close(torch.cat([b1["grad_xk"], b2["grad_xk"]], dim=2), full["grad_xk"], 1e-9, "chunked grad_xk")
+    assert_close(b1["grad_weight"], full["grad_weight"], 1e-9, "chunked grad_weight")
+    assert_close(b1["grad_ln_weight"] + b2["grad_ln_weight"], full["grad_ln_weight"], 1e-9, "chunked grad_ln_weight")

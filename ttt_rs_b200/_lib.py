@@ -58,6 +58,7 @@ SYMBOLS = {
     "ttt_linear_backward": (C.c_int, [_DP] + [_P] * 23 + [C.c_size_t, _P, _P]),
     "ttt_linear_backward_noalloc": (C.c_int, [_DP] + [_P] * 22 + [_P, _P]),
     "ttt_mlp_forward": (C.c_int, [_DP] + [_P] * 18),
+    "ttt_linear_backward_state_grads": (C.c_int, [_DP] + [_P] * 25 + [C.c_size_t, _P, _P]),
 }
 
 NOALLOC_SCRATCH_BYTES = 32 << 20  # TTT_NOALLOC_SCRATCH_BYTES

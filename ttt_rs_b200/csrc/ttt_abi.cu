@@ -225,6 +225,22 @@ int ttt_linear_backward(const ttt_dims* d, const void* xq, const void* xk, const
                         void* grad_bias, void* grad_ttt_lr_eta, float* grad_token_eta, float* grad_ln_weight,
                         float* grad_ln_bias, float* outer_grad_packed, void* workspace, size_t workspace_bytes,
                         void* status, void* stream) {
+  return ttt_linear_backward_state_grads(d, xq, xk, xv, weight, bias, token_eta, ttt_lr_eta, ln_weight, ln_bias,
+                                         weight_ckpt, bias_ckpt, grad_output, nullptr, nullptr, grad_xq, grad_xk,
+                                         grad_xv, grad_weight, grad_bias, grad_ttt_lr_eta, grad_token_eta,
+                                         grad_ln_weight, grad_ln_bias, outer_grad_packed, workspace, workspace_bytes,
+                                         status, stream);
+}
+
+int ttt_linear_backward_state_grads(const ttt_dims* d, const void* xq, const void* xk, const void* xv,
+                                    const void* weight, const void* bias, const void* token_eta,
+                                    const void* ttt_lr_eta, const void* ln_weight, const void* ln_bias,
+                                    const void* weight_ckpt, const void* bias_ckpt, const void* grad_output,
+                                    const void* grad_weight_out, const void* grad_bias_out, void* grad_xq,
+                                    void* grad_xk, void* grad_xv, void* grad_weight, void* grad_bias,
+                                    void* grad_ttt_lr_eta, float* grad_token_eta, float* grad_ln_weight,
+                                    float* grad_ln_bias, float* outer_grad_packed, void* workspace,
+                                    size_t workspace_bytes, void* status, void* stream) {
   int rc = check_dims(d);
   if (rc != TTT_OK) return rc;
   const NamedPtr ptrs[] = {{"xq", xq},
@@ -253,6 +269,8 @@ int ttt_linear_backward(const ttt_dims* d, const void* xq, const void* xk, const
   if (rc != TTT_OK) return rc;
   if (outer_grad_packed != nullptr && (reinterpret_cast<uintptr_t>(outer_grad_packed) & 15u) != 0)
     return fail(TTT_ERR_ALIGN, "outer_grad_packed is not 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(grad_weight_out) & 15u) != 0 || (reinterpret_cast<uintptr_t>(grad_bias_out) & 15u) != 0)
+    return fail(TTT_ERR_ALIGN, "grad_weight_out / grad_bias_out is not 16-byte aligned");
   const WsLayout wl = ws_layout(d);
   if (workspace_bytes < wl.total_bytes)
     return fail(TTT_ERR_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes, wl.total_bytes);
@@ -277,6 +295,8 @@ int ttt_linear_backward(const ttt_dims* d, const void* xq, const void* xk, const
   p.w_ckpt = static_cast<const float*>(weight_ckpt);
   p.stats = reinterpret_cast<const float4*>(aux + al.off_stats);
   p.b_stage = reinterpret_cast<const float*>(aux + al.off_bias);
+  p.dw_in = grad_weight_out;
+  p.db_in = grad_bias_out;
   p.d_w = grad_weight;
   p.d_b = grad_bias;
   p.d_lr = grad_ttt_lr_eta;

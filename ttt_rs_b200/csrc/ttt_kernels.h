@@ -34,6 +34,8 @@ struct LinBwdParams {
   const float* w_ckpt;
   const float4* stats;
   const float* b_stage;
+  const void* dw_in;  // [B,H,F,F] T: upstream gradient of the returned final weight, or null (zero)
+  const void* db_in;  // [B,H,F]   T: upstream gradient of the returned final bias, or null (zero)
   void* d_w;        // [B,H,F,F] element type T (per batch element), nullable
   void* d_b;        // [B,H,F], nullable
   void* d_lr;       // [B,H,T]

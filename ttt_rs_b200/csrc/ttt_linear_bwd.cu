@@ -164,11 +164,23 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
     }
     float* ho = p.handoff + (size_t)stream * HOFF;
     if (crank == 0) {
+      // gradient flowing into the final state: zero (the reference's behaviour) unless the caller supplies it
       dbias[0] = dbias[1] = f2(0.f);
 #pragma unroll
       for (int kt = 0; kt < 8; ++kt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) dwt[kt][i] = 0.f;
+        for (int i = 0; i < 4; ++i)
+          dwt[kt][i] = (p.dw_in == nullptr)
+                           ? 0.f
+                           : ld_as_float<T>(p.dw_in, (size_t)stream * HD * HD + (8 * kt + 2 * t + (i & 1)) * HD + nb + g +
+                                                         8 * (i >> 1));
+      if (p.db_in != nullptr) {
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const size_t o = (size_t)stream * HD + nb + 8 * nt + 2 * t;
+          dbias[nt] = f2(ld_as_float<T>(p.db_in, o), ld_as_float<T>(p.db_in, o + 1));
+        }
+      }
     } else {
       // wait (bounded) until the later chunk of this stream has published its hand-off
       int ok = 1;

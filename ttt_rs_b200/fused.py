@@ -189,9 +189,10 @@ class TttTileMultiKernel:
 
     @staticmethod
     def backward_launch(saved: TttSavedStateMulti, grad_outputs: TttOutputs, config: FusedTttConfig,
-                        outer_grad_packed: Optional[torch.Tensor] = None) -> TttInputs:
-        """Gradients w.r.t. the nine inputs, in input order.  Only `grad_outputs.output` is used: upstream
-        gradients of the returned final state are ignored, as in the reference."""
+                        outer_grad_packed: Optional[torch.Tensor] = None, use_state_grads: bool = False) -> TttInputs:
+        """Gradients w.r.t. the nine inputs, in input order.  By default only `grad_outputs.output` is used: upstream
+        gradients of the returned final state are ignored, as in the reference.  With `use_state_grads=True`,
+        `grad_outputs.weight` / `.bias` (when not None) are taken as the gradients flowing into the final state."""
         if config.mini_batch_len <= 0:
             raise TttError(_lib.TTT_ERR_SHAPE, "mini_batch_len must be set for TttTileMultiKernel backward")
         lib = _lib.load()
@@ -212,10 +213,19 @@ class TttTileMultiKernel:
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
         status = torch.zeros(4, dtype=torch.int32, device=dev)
         TttTileMultiKernel.last_status = status
-        rc = lib.ttt_linear_backward(
+        gw_out = gb_out = None
+        if use_state_grads:
+            if grad_outputs.weight is not None:
+                gw_out = grad_outputs.weight.contiguous()
+                _expect("grad_outputs.weight", gw_out, (B, H, F, F), dt, dev)
+            if grad_outputs.bias is not None:
+                gb_out = grad_outputs.bias.contiguous()
+                _expect("grad_outputs.bias", gb_out, (B, H, F), dt, dev)
+        rc = lib.ttt_linear_backward_state_grads(
             C.byref(d), _ptr(saved.xq), _ptr(saved.xk), _ptr(saved.xv), _ptr(saved.weight_init), _ptr(saved.bias),
             _ptr(saved.token_eta), _ptr(saved.ttt_lr_eta), _ptr(saved.ln_weight), _ptr(saved.ln_bias),
-            _ptr(saved.weight_checkpoints), _ptr(saved.bias_checkpoints), _ptr(go), _ptr(g_xq), _ptr(g_xk),
+            _ptr(saved.weight_checkpoints), _ptr(saved.bias_checkpoints), _ptr(go), _ptr(gw_out), _ptr(gb_out),
+            _ptr(g_xq), _ptr(g_xk),
             _ptr(g_xv), _ptr(g_w), _ptr(g_b), _ptr(g_lr), _ptr(g_te), _ptr(g_lnw), _ptr(g_lnb),
             _ptr(outer_grad_packed), _ptr(ws), C.c_size_t(ws_bytes), _ptr(status), _stream_ptr(dev))
         _lib.check(rc)
