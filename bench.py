@@ -131,7 +131,7 @@ class ClockSampler:
 
 
 def make_host_inputs(w, seed):
-    from oracle.ttt_oracle import make_inputs
+    from ttt_rs_b200.synthetic import make_inputs
     dt = torch.bfloat16 if w["dtype"] == "bf16" else torch.float32
     return make_inputs(w["B"], w["H"], w["T"], F, CS, seed=seed, dtype=dt, with_grad_output=True,
                        inner=w.get("inner", "linear"))
@@ -167,11 +167,12 @@ def run_reference(args, w):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 3))
-    val, dt, cores, sample = time_cpu(w, steps, min(args.warmup, 1))
+    # each step is a 4-sequence slice of the workload (about a second of host time), so K steps stay within minutes
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+    val, dt, cores, sample = time_cpu(w, steps, warmup, sample_B=min(4, w["B"]))
     line = {
         "impl": "reference", "metric": "ttt_inner_loop_tokens_per_sec", "value": val, "unit": "tokens/s",
-        "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3,
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": w["desc"]},
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
@@ -304,8 +305,8 @@ def main():
     total_b, fb, bb = algorithmic_bytes(w, True, w["backward"])
     dom_ms, dom_bytes, dom_name = (bwd_ms, bb, "ttt_linear_bwd_kernel") if w["backward"] else (fwd_ms, fb, "ttt_mlp_fwd_kernel" if mlp else "ttt_linear_fwd_kernel")
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
-    # DRAM bytes per launch of the dominant kernel from the committed ncu capture of this same command
-    # (profiles/ttt_linear_bwd_kernel_cfg1_bf16.md: dram__bytes_read.sum + dram__bytes_write.sum); other workloads: none
+    # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum) from the committed
+    # ncu summary of this same command under profiles/; other workloads have no capture
     traffic = 599.1e6 + 351.9e6 if args.workload == "cfg1" else None
     roof = {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
             "frac": achieved / peak, "traffic": traffic, "peak_source": f"of {peak_kind}",
@@ -325,7 +326,7 @@ def main():
             "roofline": roof,
         }
         if world == 1 and not args.no_cpu_baseline:
-            val, dt, cores, sample = time_cpu(w, 1, 0)
+            val, dt, cores, sample = time_cpu(w, 6, 1, sample_B=min(8, w["B"]))
             line["cpu_baseline"] = {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -115,21 +115,4 @@ __device__ __forceinline__ void tma_store_tile(const CUtensorMap* tm, int row0, 
   }
 }
 
-// ----------------------------------------------------------------------------------------------------
-// Cross-warp row statistics exchange.  Each warp reduces its 16 columns with shuffles; lane t==0 of each
-// row writes (a, b) to xch[row][warp]; after a CTA barrier every thread sums the four warps' entries.
-// ----------------------------------------------------------------------------------------------------
-struct __align__(16) XchBuf {
-  float2 v[CS][4];  // [row][warp] -> 512 bytes
-};
-
-__device__ __forceinline__ void xch_put(XchBuf* x, int row, int warp, float a, float b) {
-  x->v[row][warp] = make_float2(a, b);
-}
-__device__ __forceinline__ float2 xch_get(const XchBuf* x, int row) {
-  const float4 p = *reinterpret_cast<const float4*>(&x->v[row][0]);
-  const float4 q = *reinterpret_cast<const float4*>(&x->v[row][2]);
-  return make_float2((p.x + p.z) + (q.x + q.z), (p.y + p.w) + (q.y + q.w));
-}
-
 }  // namespace ttt
