@@ -153,6 +153,38 @@ int ttt_mlp_forward(const ttt_dims* d, const void* xq, const void* xk, const voi
                     const void* ln_weight, const void* ln_bias, void* output, void* w1_out, void* b1_out, void* w2_out,
                     void* b2_out, void* status, void* stream);
 
+/* ---- outer-layer steps on either side of the inner loop -------------------------------------------------------
+ * These two entry points replace the tensor-op chains of the reference's `TTT` layer around `inner.forward`
+ * (rust/layer/src/ttt.rs): `get_qkv` :152-197 (reshape + permute to [B,H,T,F], shared-QK causal convolutions
+ * `conv_qk` :228-246, rotary embedding with the permute/undo-permute convention, rust/core/src/util.rs:284-392),
+ * `get_lr` :205-227, and in `forward` :285-296 the permute back, `post_norm` and the optional gelu(tanh) gate.  The
+ * projections themselves (q/k/v/g/o_proj, the per-head lr weights) stay ordinary GEMMs in the caller.
+ * Only `batch`, `heads`, `seq_len`, `head_dim` (64), `mini_batch` (rotary wrap) and `dtype` of `d` are read; seq_len
+ * need not be a multiple of mini_batch here.
+ */
+
+/* Projection outputs -> inner-loop operands.
+ *   q_src, k_src, v_src  [B*T, src_ld] rows = tokens; each points at the first of its H*F head-major columns (the
+ *                        three may be column blocks of one fused projection output).  16-byte aligned, src_ld a
+ *                        multiple of 8 elements.  With the shared-QK convolutions (conv_q_weight != NULL) q_src is
+ *                        the shared projection and k_src is ignored.
+ *   lr_logits            [B*T, lr_ld] x . learnable_ttt_lr_weight^T (first H columns), before the bias
+ *   lr_bias              [H] or NULL
+ *   conv_*_weight / bias [H*F, conv_kernel] / [H*F] depthwise causal taps (conv_kernel <= 4), or all NULL
+ *   rope_mode            0 none, 1 positions (start_idx + t) mod mini_batch (`PosEncoding::Rope`), 2 global positions
+ *   xq, xk, xv           (out) [B,H,T,F];   ttt_lr_eta (out) [B,H,T] = base_lr * sigmoid(logit + bias) / F
+ */
+int ttt_layer_prologue(const ttt_dims* d, const void* q_src, const void* k_src, const void* v_src, int64_t src_ld,
+                       const void* lr_logits, int64_t lr_ld, const void* lr_bias, const void* conv_q_weight,
+                       const void* conv_q_bias, const void* conv_k_weight, const void* conv_k_bias, int conv_kernel,
+                       int start_idx, int rope_mode, float rope_theta, float base_lr, void* xq, void* xk, void* xv,
+                       void* ttt_lr_eta, void* stream);
+
+/* Inner-loop output [B,H,T,F] -> [B,T,H*F] with LayerNorm over H*F (biased variance, `eps` inside the root) and, when
+ * `gate` != NULL, multiplied by gelu_tanh(gate) (gate = x . g_proj^T, [B*T, gate_ld], first H*F columns). */
+int ttt_layer_epilogue(const ttt_dims* d, const void* inner_out, const void* gate, int64_t gate_ld,
+                       const void* post_norm_weight, const void* post_norm_bias, float eps, void* y, void* stream);
+
 /* Backward without a caller workspace.  (No counterpart in the reference: its host wrapper always allocates its
  * scratch itself, backward/launch.rs:389-392.)
  *

@@ -23,6 +23,12 @@ What is produced (all by calling the reference's own `TTTLinear.ttt` /
     from oracle.ttt_oracle.make_inputs): reference float32 and float64 outputs,
     stored as a strided subsample plus full-tensor sums (inputs are regenerated
     from the seed by the tests).
+* layer_linear_f64.npz
+    the whole outer layer (`TTTLinear.forward`: projections, optional shared-QK causal
+    convolutions, rotary embedding, learning-rate gate, inner loop, post norm, optional
+    gate, output projection; the analogue of reference/validate.py:338-415 at head_dim 64):
+    B=2 T=48 H=2 F=64, float64, for the default configuration and for share_qk + use_gate.
+    Inputs, every parameter and the expected output are stored.
 """
 
 from __future__ import annotations
@@ -178,6 +184,49 @@ def gen_cfg0(ref, out_dir: Path):
     np.savez(out_dir / "cfg0_linear_f32.npz", **d)
 
 
+def gen_layer(ref, out_dir: Path):
+    B, T, H, D, cs = 2, 48, 2, 64, 16
+    d = {}
+    for tag, share_qk, use_gate in (("plain", False, False), ("conv_gate", True, True)):
+        torch.manual_seed(7 if share_qk else 5)
+        cfg = ref.TTTConfig(hidden_size=H * D, num_attention_heads=H, mini_batch_size=cs, ttt_layer_type="linear",
+                            ttt_base_lr=1.0, share_qk=share_qk, use_gate=use_gate, conv_kernel=4, pre_conv=False)
+        m = ref.TTTLinear(cfg, layer_idx=0)
+        m.eval()
+        with torch.no_grad():  # make every parameter non-trivial
+            m.ttt_norm_weight.add_(0.1 * torch.randn_like(m.ttt_norm_weight))
+            m.ttt_norm_bias.add_(0.1 * torch.randn_like(m.ttt_norm_bias))
+            m.post_norm.weight.add_(0.1 * torch.randn_like(m.post_norm.weight))
+            m.post_norm.bias.add_(0.1 * torch.randn_like(m.post_norm.bias))
+            m.learnable_ttt_lr_bias.add_(0.1 * torch.randn_like(m.learnable_ttt_lr_bias))
+            m.learnable_token_idx.add_(0.05 * torch.randn_like(m.learnable_token_idx))
+            m.b1.add_(0.05 * torch.randn_like(m.b1))
+        m = m.double()
+        x = (torch.randn(B, T, H * D) * 0.5).double()
+        pos = torch.arange(T).unsqueeze(0).expand(B, -1)
+        with torch.no_grad():
+            y = m(hidden_states=x, attention_mask=None, position_ids=pos, cache_params=None)
+        t = {
+            "input": x, "output_expected": y,
+            "q_proj": m.q_proj.weight, "v_proj": m.v_proj.weight, "o_proj": m.o_proj.weight,
+            "ttt_norm_weight": m.ttt_norm_weight, "ttt_norm_bias": m.ttt_norm_bias,
+            "post_norm_weight": m.post_norm.weight, "post_norm_bias": m.post_norm.bias,
+            "lr_weight": m.learnable_ttt_lr_weight, "lr_bias": m.learnable_ttt_lr_bias,
+            "token_idx": m.token_idx, "learnable_token_idx": m.learnable_token_idx,
+            "W1": m.W1, "b1": m.b1,
+        }
+        if use_gate:
+            t["g_proj"] = m.g_proj.weight
+        if share_qk:
+            t.update(conv_q_weight=m.conv_q.weight, conv_q_bias=m.conv_q.bias,
+                     conv_k_weight=m.conv_k.weight, conv_k_bias=m.conv_k.bias)
+        else:
+            t["k_proj"] = m.k_proj.weight
+        for k, v in t.items():
+            d[f"{tag}.{k}"] = v.detach().double().contiguous().numpy()
+    np.savez_compressed(out_dir / "layer_linear_f64.npz", **d)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("TTT_REFERENCE_ROOT", ""))
@@ -193,6 +242,7 @@ def main():
     gen_validate(ref, out_dir)
     gen_small(ref, out_dir)
     gen_cfg0(ref, out_dir)
+    gen_layer(ref, out_dir)
     for f in sorted(out_dir.glob("*.npz")):
         print(f"{f.name}: {f.stat().st_size} bytes")
 

@@ -1,0 +1,164 @@
+"""Outer-layer kernels (ttt_layer_prologue / ttt_layer_epilogue) and the whole `TTT.forward` on the GPU against the
+CPU restatement and against the reference's own layer outputs (tests/golden/layer_linear_f64.npz)."""
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close
+from oracle import ttt_layer_oracle as LO
+
+RTOL = {torch.float32: 1e-4, torch.bfloat16: 2e-2}
+
+
+def _golden(golden_dir, tag):
+    z = np.load(golden_dir / "layer_linear_f64.npz")
+    return {k.split(".", 1)[1]: torch.from_numpy(z[k]) for k in z.files if k.startswith(tag + ".")}
+
+
+def _layer_from_params(tb, p, share_qk, use_gate, dtype, dev, H):
+    cfg = tb.TTTLayerConfig(hidden_size=p["q_proj"].shape[0], num_heads=H, share_qk=share_qk, use_gate=use_gate)
+    m = tb.TTT(cfg, device=dev, dtype=dtype)
+    inner = tb.new_inner(cfg, device=dev, dtype=dtype)
+    with torch.no_grad():
+        def put(dst, src):
+            dst.copy_(src.reshape(dst.shape).to(dtype))
+        put(m.q_proj, p["q_proj"]); put(m.v_proj, p["v_proj"]); put(m.o_proj, p["o_proj"])
+        if not share_qk:
+            put(m.k_proj, p["k_proj"])
+        else:
+            put(m.q_conv_weight, p["conv_q_weight"]); put(m.q_conv_bias, p["conv_q_bias"])
+            put(m.k_conv_weight, p["conv_k_weight"]); put(m.k_conv_bias, p["conv_k_bias"])
+        if use_gate:
+            put(m.g_proj, p["g_proj"])
+        put(m.learnable_ttt_lr_weight, p["lr_weight"]); put(m.learnable_ttt_lr_bias, p["lr_bias"])
+        put(m.learnable_token_idx, p["learnable_token_idx"])
+        put(m.post_norm_weight, p["post_norm_weight"]); put(m.post_norm_bias, p["post_norm_bias"])
+        put(inner.inner.weight_init, p["W1"]); put(inner.inner.bias_init, p["b1"])
+        put(inner.inner.ln_weight, p["ttt_norm_weight"]); put(inner.inner.ln_bias, p["ttt_norm_bias"])
+    m.invalidate_fused_weight()
+    return m, inner
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tag,share_qk,use_gate", (("plain", False, False), ("conv_gate", True, True)))
+def test_layer_forward_float32_matches_reference_golden(golden_dir, tag, share_qk, use_gate):
+    import ttt_rs_b200 as tb
+    dev = torch.device("cuda:0")
+    p = _golden(golden_dir, tag)
+    m, inner = _layer_from_params(tb, p, share_qk, use_gate, torch.float32, dev, 2)
+    x = p["input"].float().to(dev)
+    with torch.no_grad():
+        state = inner.init_state(x.shape[0])
+        y = m(x, inner, state)
+    tb.TttTileMultiKernel.check_status()
+    # the projections are library float32 GEMMs (TF32 off by default); the kernels compute in float32
+    assert_close(y, p["output_expected"], 2e-4, f"{tag}: layer output")
+    want_state = LO.ttt_layer_forward(p["input"], p, num_heads=2, share_qk=share_qk, use_gate=use_gate)[1]
+    assert_close(state.weight, want_state["weight"], 2e-4, f"{tag}: final inner weight")
+
+
+def _random_case(B, T, H, seed, share_qk, use_gate, dtype):
+    g = torch.Generator().manual_seed(seed)
+    C = H * 64
+    r = lambda *s, sc=1.0: (torch.randn(*s, generator=g) * sc).to(dtype).double()  # noqa: E731
+    p = {"q_proj": r(C, C, sc=C ** -0.5), "v_proj": r(C, C, sc=C ** -0.5), "o_proj": r(C, C, sc=C ** -0.5),
+         "lr_weight": r(H, C, 1, sc=0.02), "lr_bias": r(H, 1, sc=0.1), "token_idx": 1.0 / torch.arange(1, 17).double(),
+         "learnable_token_idx": r(16, sc=0.05), "post_norm_weight": 1 + r(C, sc=0.1), "post_norm_bias": r(C, sc=0.1),
+         "W1": r(H, 64, 64, sc=0.02), "b1": r(H, 1, 64, sc=0.05), "ttt_norm_weight": 1 + r(H, 64, sc=0.1),
+         "ttt_norm_bias": r(H, 64, sc=0.1)}
+    if share_qk:
+        p.update(conv_q_weight=r(C, 1, 4, sc=0.5), conv_q_bias=r(C, sc=0.1), conv_k_weight=r(C, 1, 4, sc=0.5),
+                 conv_k_bias=r(C, sc=0.1))
+    else:
+        p["k_proj"] = r(C, C, sc=C ** -0.5)
+    if use_gate:
+        p["g_proj"] = r(C, C, sc=C ** -0.5)
+    x = r(B, T, C)
+    return x, p
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16))
+@pytest.mark.parametrize("share_qk,use_gate,pos,start", ((False, False, "rope", 0), (True, True, "rope", 21),
+                                                         (False, True, "rope_global", 5), (True, False, "none", 0)))
+def test_prologue_and_epilogue_kernels_match_the_restatement(dtype, share_qk, use_gate, pos, start):
+    """Kernel-level parity on ragged sizes (T not a multiple of the mini-batch or of the kernel's token chunk,
+    heads not a multiple of 4), fed with exactly the projection values the kernels see."""
+    import ttt_rs_b200 as tb
+    dev = torch.device("cuda:0")
+    B, T, H = 3, 83, 3
+    C = H * 64
+    x, p = _random_case(B, T, H, 11, share_qk, use_gate, dtype)
+    cfg = tb.TTTLayerConfig(hidden_size=C, num_heads=H, share_qk=share_qk, use_gate=use_gate, pos_encoding=pos)
+    # projection output as the layer lays it out: q | (k) | v | (g) | lr, rounded to the I/O type
+    blocks = [x @ p["q_proj"].T] + ([] if share_qk else [x @ p["k_proj"].T]) + [x @ p["v_proj"].T]
+    if use_gate:
+        blocks.append(x @ p["g_proj"].T)
+    blocks.append(torch.einsum("btc,hc->bth", x, p["lr_weight"].reshape(H, C)))
+    blocks.append(torch.zeros(B, T, (-sum(b.shape[-1] for b in blocks)) % 8, dtype=torch.float64))
+    proj = torch.cat(blocks, dim=-1).to(dtype)
+    cols = {"q": 0, "k": 0 if share_qk else C, "v": C if share_qk else 2 * C}
+    cols["g"] = cols["v"] + C
+    cols["lr"] = cols["v"] + C + (C if use_gate else 0)
+    conv = (p["conv_q_weight"], p["conv_q_bias"], p["conv_k_weight"], p["conv_k_bias"]) if share_qk else None
+    xq, xk, xv, lr = tb.layer_prologue(proj.to(dev), cfg, q_col=cols["q"], k_col=cols["k"], v_col=cols["v"],
+                                       lr_col=cols["lr"], lr_bias=p["lr_bias"].to(dev), conv=None if conv is None else
+                                       tuple(t.to(dev) for t in conv), start_idx=start)
+    torch.cuda.synchronize()
+    # the restatement on the same rounded projection values
+    pd = proj.double()
+    heads = lambda t: t.reshape(B, T, H, 64).permute(0, 2, 1, 3)  # noqa: E731
+    qs, ks, vs = pd[..., :C], pd[..., cols["k"]:cols["k"] + C], pd[..., cols["v"]:cols["v"] + C]
+    if share_qk:
+        ks = LO.causal_depthwise_conv(qs, p["conv_k_weight"], p["conv_k_bias"])
+        qs = LO.causal_depthwise_conv(qs, p["conv_q_weight"], p["conv_q_bias"])
+    wq, wk, wv = heads(qs), heads(ks), heads(vs)
+    if pos != "none":
+        posv = start + torch.arange(T)
+        posv = posv % 16 if pos == "rope" else posv
+        wq, wk = LO.rope_pairs(wq, posv, 10000.0), LO.rope_pairs(wk, posv, 10000.0)
+    wlr = torch.sigmoid(pd[..., cols["lr"]:cols["lr"] + H].permute(0, 2, 1) + p["lr_bias"].reshape(1, H, 1)) / 64
+    rt = RTOL[dtype]
+    assert_close(xq, wq, rt, "xq"); assert_close(xk, wk, rt, "xk"); assert_close(xv, wv, rt, "xv")
+    assert_close(lr, wlr, rt, "ttt_lr_eta")
+    if dtype == torch.bfloat16:
+        assert torch.equal(xv.cpu(), heads(proj[..., cols["v"]:cols["v"] + C]).contiguous()), "xv must be a pure copy"
+
+    # epilogue
+    inner_out = (torch.randn(B, H, T, 64, generator=torch.Generator().manual_seed(3)) * 2 + 0.3).to(dtype)
+    gate = gate_ld = None
+    if use_gate:
+        gate, gate_ld = proj.to(dev).reshape(B * T, -1)[:, cols["g"]:], proj.shape[-1]
+    y = tb.layer_epilogue(inner_out.to(dev), p["post_norm_weight"].to(dev), p["post_norm_bias"].to(dev), 1e-6,
+                          gate, gate_ld or 0)
+    torch.cuda.synchronize()
+    pw = {"post_norm_weight": p["post_norm_weight"].to(dtype).double(), "post_norm_bias": p["post_norm_bias"].to(dtype).double()}
+    want = LO.layer_epilogue(inner_out.double(), None, pw, use_gate=False)
+    if use_gate:
+        from oracle.ttt_oracle import gelu_tanh
+        want = gelu_tanh(pd[..., cols["g"]:cols["g"] + C]) * want
+    assert_close(y, want, rt, "epilogue")
+
+
+@pytest.mark.gpu
+def test_layer_forward_bfloat16_at_a_wider_shape():
+    import ttt_rs_b200 as tb
+    dev = torch.device("cuda:0")
+    B, T, H = 2, 128, 12
+    x, p = _random_case(B, T, H, 5, False, True, torch.bfloat16)
+    m, inner = _layer_from_params(tb, p, False, True, torch.bfloat16, dev, H)
+    with torch.no_grad():
+        state = inner.init_state(B)
+        y = m(x.to(torch.bfloat16).to(dev), inner, state)
+    tb.TttTileMultiKernel.check_status()
+    want, _ = LO.ttt_layer_forward(x, p, num_heads=H, use_gate=True)
+    assert_close(y, want, 2e-2, "layer output", max_bad_frac=1e-3)
+
+
+def test_layer_forward_refuses_to_run_under_autograd():
+    import ttt_rs_b200 as tb
+    cfg = tb.TTTLayerConfig(hidden_size=128, num_heads=2)
+    m = tb.TTT(cfg)
+    with pytest.raises(RuntimeError, match="no_grad"):
+        m(torch.zeros(1, 16, 128), tb.new_inner(cfg), None)

@@ -432,3 +432,104 @@ extern "C" int ttt_linear_backward_noalloc(const ttt_dims* d, const void* xq, co
                              grad_ttt_lr_eta, grad_token_eta, grad_ln_weight, grad_ln_bias, outer_grad_packed,
                              scratch, (size_t)TTT_NOALLOC_SCRATCH_BYTES, status, stream);
 }
+
+namespace {
+int check_layer_dims(const ttt_dims* d) {
+  if (d == nullptr) return fail(TTT_ERR_NULL, "dims is null");
+  if (d->batch <= 0 || d->heads <= 0 || d->seq_len <= 0) return fail(TTT_ERR_SHAPE, "batch, heads and seq_len must be positive");
+  if (d->dtype != TTT_F32 && d->dtype != TTT_BF16) return fail(TTT_ERR_UNSUPPORTED, "unknown dtype %d", d->dtype);
+  if (d->head_dim != 64) return fail(TTT_ERR_UNSUPPORTED, "Unsupported head_dim=%d (supported: 64)", d->head_dim);
+  if ((int64_t)d->batch * d->heads * d->seq_len >= (int64_t)1 << 31)
+    return fail(TTT_ERR_SHAPE, "batch*heads*seq_len must be below 2^31");
+  return TTT_OK;
+}
+}  // namespace
+
+extern "C" int ttt_layer_prologue(const ttt_dims* d, const void* q_src, const void* k_src, const void* v_src,
+                                  int64_t src_ld, const void* lr_logits, int64_t lr_ld, const void* lr_bias,
+                                  const void* conv_q_weight, const void* conv_q_bias, const void* conv_k_weight,
+                                  const void* conv_k_bias, int conv_kernel, int start_idx, int rope_mode,
+                                  float rope_theta, float base_lr, void* xq, void* xk, void* xv, void* ttt_lr_eta,
+                                  void* stream) {
+  int rc = check_layer_dims(d);
+  if (rc != TTT_OK) return rc;
+  const bool conv = conv_q_weight != nullptr;
+  if (conv != (conv_k_weight != nullptr) || conv != (conv_q_bias != nullptr) || conv != (conv_k_bias != nullptr))
+    return fail(TTT_ERR_NULL, "conv_q_weight, conv_q_bias, conv_k_weight and conv_k_bias must be given together");
+  if (conv && (conv_kernel < 1 || conv_kernel > 4))
+    return fail(TTT_ERR_UNSUPPORTED, "conv_kernel=%d (supported: 1..4)", conv_kernel);
+  if (rope_mode < 0 || rope_mode > 2) return fail(TTT_ERR_UNSUPPORTED, "rope_mode=%d (0 none, 1 wrapped, 2 global)", rope_mode);
+  if (rope_mode == 1 && (d->mini_batch < 1 || d->mini_batch > 64))
+    return fail(TTT_ERR_UNSUPPORTED, "wrapped rotary positions need 1 <= mini_batch <= 64 (got %d)", d->mini_batch);
+  if (rope_mode != 0 && !(rope_theta > 0.f)) return fail(TTT_ERR_SHAPE, "rope_theta must be positive");
+  if (start_idx < 0) return fail(TTT_ERR_SHAPE, "start_idx must be >= 0");
+  const int64_t cols = (int64_t)d->heads * 64;
+  if (src_ld < cols || (src_ld & 7) != 0)
+    return fail(TTT_ERR_SHAPE, "src_ld (%lld) must be >= heads*64 and a multiple of 8", (long long)src_ld);
+  if (lr_ld < d->heads) return fail(TTT_ERR_SHAPE, "lr_ld (%lld) must be >= heads", (long long)lr_ld);
+  const NamedPtr ptrs[] = {{"q_src", q_src}, {"k_src", conv ? q_src : k_src}, {"v_src", v_src}, {"xq", xq},
+                           {"xk", xk},       {"xv", xv}};
+  rc = check_ptrs(ptrs, 6);
+  if (rc != TTT_OK) return rc;
+  if (lr_logits == nullptr || ttt_lr_eta == nullptr) return fail(TTT_ERR_NULL, "lr_logits / ttt_lr_eta is null");
+  ttt::LayerProParams p;
+  p.q_src = q_src;
+  p.k_src = conv ? q_src : k_src;
+  p.v_src = v_src;
+  p.ld_src = (long)src_ld;
+  p.lr_logits = lr_logits;
+  p.ld_lr = (long)lr_ld;
+  p.lr_bias = lr_bias;
+  p.conv_q_w = conv_q_weight;
+  p.conv_q_b = conv_q_bias;
+  p.conv_k_w = conv_k_weight;
+  p.conv_k_b = conv_k_bias;
+  p.conv_k = conv ? conv_kernel : 0;
+  p.xq = xq;
+  p.xk = xk;
+  p.xv = xv;
+  p.lr_out = ttt_lr_eta;
+  p.B = d->batch;
+  p.H = d->heads;
+  p.T = d->seq_len;
+  p.start_idx = start_idx;
+  p.pos_mod = rope_mode == 1 ? d->mini_batch : 1;
+  p.rope_mode = rope_mode;
+  p.rope_theta = rope_mode != 0 ? rope_theta : 1.f;
+  p.base_lr = base_lr;
+  cudaError_t e = ttt::launch_layer_prologue(d->dtype, p, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "layer prologue launch failed: %s", cudaGetErrorString(e));
+  return TTT_OK;
+}
+
+extern "C" int ttt_layer_epilogue(const ttt_dims* d, const void* inner_out, const void* gate, int64_t gate_ld,
+                                  const void* post_norm_weight, const void* post_norm_bias, float eps, void* y,
+                                  void* stream) {
+  int rc = check_layer_dims(d);
+  if (rc != TTT_OK) return rc;
+  if (d->heads > 32) return fail(TTT_ERR_UNSUPPORTED, "heads=%d (supported: up to 32)", d->heads);
+  if (!(eps >= 0.f)) return fail(TTT_ERR_SHAPE, "eps must be >= 0");
+  const NamedPtr ptrs[] = {{"inner_out", inner_out}, {"y", y}};
+  rc = check_ptrs(ptrs, 2);
+  if (rc != TTT_OK) return rc;
+  if (post_norm_weight == nullptr || post_norm_bias == nullptr) return fail(TTT_ERR_NULL, "post_norm_weight / post_norm_bias is null");
+  if (gate != nullptr) {
+    if (gate_ld < (int64_t)d->heads * 64 || (gate_ld & 1) != 0)
+      return fail(TTT_ERR_SHAPE, "gate_ld (%lld) must be >= heads*64 and even", (long long)gate_ld);
+    if ((reinterpret_cast<uintptr_t>(gate) & 7u) != 0) return fail(TTT_ERR_ALIGN, "gate is not 8-byte aligned");
+  }
+  ttt::LayerEpiParams p;
+  p.inner_out = inner_out;
+  p.gate = gate;
+  p.ld_gate = (long)gate_ld;
+  p.ln_w = post_norm_weight;
+  p.ln_b = post_norm_bias;
+  p.y = y;
+  p.B = d->batch;
+  p.H = d->heads;
+  p.T = d->seq_len;
+  p.eps = eps;
+  cudaError_t e = ttt::launch_layer_epilogue(d->dtype, p, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "layer epilogue launch failed: %s", cudaGetErrorString(e));
+  return TTT_OK;
+}

@@ -78,6 +78,41 @@ struct MlpFwdParams {
   int H, T, NS;
   float eps;
 };
+// Outer-layer steps either side of the inner loop (ttt_layer.cu).
+struct LayerProParams {
+  const void* q_src;   // projection outputs, rows = tokens (b*T + t), this head-major column block of H*F columns;
+  const void* k_src;   // with the shared-QK convolutions q_src is the shared projection and k_src is unused
+  const void* v_src;
+  long ld_src;         // row stride of the three sources, in elements
+  const void* lr_logits;  // [B*T, ld_lr], first H columns used
+  long ld_lr;
+  const void* lr_bias;    // [H] or null
+  const void* conv_q_w;   // [H*F, conv_k] or null (no convolution)
+  const void* conv_q_b;   // [H*F]
+  const void* conv_k_w;
+  const void* conv_k_b;
+  int conv_k;
+  void* xq;            // [B,H,T,F]
+  void* xk;
+  void* xv;
+  void* lr_out;        // [B,H,T]
+  int B, H, T;
+  int start_idx, pos_mod, rope_mode;  // rope_mode: 0 none, 1 positions modulo pos_mod, 2 global positions
+  float rope_theta, base_lr;
+};
+struct LayerEpiParams {
+  const void* inner_out;  // [B,H,T,F]
+  const void* gate;       // [B*T, ld_gate] (first H*F columns) or null
+  long ld_gate;
+  const void* ln_w;       // [H*F]
+  const void* ln_b;
+  void* y;                // [B,T,H*F]
+  int B, H, T;
+  float eps;
+};
+cudaError_t launch_layer_prologue(int dtype, const LayerProParams& p, cudaStream_t st);
+cudaError_t launch_layer_epilogue(int dtype, const LayerEpiParams& p, cudaStream_t st);
+
 // bf16 only.  maps: q, k, v, out.
 cudaError_t launch_mlp_fwd(const CUtensorMap* maps, const MlpFwdParams& p, int nstreams, cudaStream_t st);
 

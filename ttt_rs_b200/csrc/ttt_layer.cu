@@ -1,0 +1,330 @@
+// The steps of the outer TTT layer on either side of the inner loop, as two bandwidth-bound kernels (sm_100a).
+//
+// Reference semantics: rust/layer/src/ttt.rs:152-299 (`get_qkv`, `get_lr`, `conv_qk`, `forward`), rotary embedding
+// rust/core/src/util.rs:284-392 (PyTorch twin reference/ttt.py:215-270,701-915).  There the projections' outputs
+// are reshaped and permuted to [B,H,T,F] (one materialised copy per tensor), rotated by separate element-wise
+// kernels, the learning-rate gate is a chain of small tensor ops, and after the inner loop the result is permuted
+// back and normalised by further kernels.  Here:
+//   * ttt_layer_prologue_kernel reads the projection output once in its native [B*T, columns] layout and writes
+//     XQ, XK, XV in the inner loop's [B,H,T,F] layout with the shared-QK causal convolutions and the rotary
+//     rotation applied on the way, plus ttt_lr_eta = base_lr * sigmoid(logit + bias) / F in [B,H,T];
+//   * ttt_layer_epilogue_kernel reads the inner loop's [B,H,T,F] output once and writes [B,T,H*F] with the post
+//     LayerNorm and the optional gelu(tanh) gate applied.
+// Every global access is a full 128-byte (bf16) or 256-byte (f32) row segment per 8 / 32 lanes; no shared-memory
+// staging is needed because a (token, head) row of 64 features is contiguous in both layouts.
+#include "ttt_kernels.h"
+#include "ttt_common.cuh"
+
+namespace ttt {
+
+template <typename T>
+struct Vec8;  // eight consecutive elements
+template <>
+struct Vec8<__nv_bfloat16> {
+  uint4 raw;
+  __device__ __forceinline__ void load(const void* p) { raw = *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ void store(void* p) const { *reinterpret_cast<uint4*>(p) = raw; }
+  __device__ __forceinline__ void unpack(float (&f)[8]) const {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = bf16_lo(w[i]);
+      f[2 * i + 1] = bf16_hi(w[i]);
+    }
+  }
+  __device__ __forceinline__ void pack(const float (&f)[8]) {
+    raw.x = pack_bf16(f[0], f[1]);
+    raw.y = pack_bf16(f[2], f[3]);
+    raw.z = pack_bf16(f[4], f[5]);
+    raw.w = pack_bf16(f[6], f[7]);
+  }
+};
+template <>
+struct Vec8<float> {
+  float4 a, b;
+  __device__ __forceinline__ void load(const void* p) {
+    a = reinterpret_cast<const float4*>(p)[0];
+    b = reinterpret_cast<const float4*>(p)[1];
+  }
+  __device__ __forceinline__ void store(void* p) const {
+    reinterpret_cast<float4*>(p)[0] = a;
+    reinterpret_cast<float4*>(p)[1] = b;
+  }
+  __device__ __forceinline__ void unpack(float (&f)[8]) const {
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+  __device__ __forceinline__ void pack(const float (&f)[8]) {
+    a = make_float4(f[0], f[1], f[2], f[3]);
+    b = make_float4(f[4], f[5], f[6], f[7]);
+  }
+};
+
+constexpr int PRO_THREADS = 256;
+constexpr int PRO_TCHUNK = 64;   // tokens per warp task
+constexpr int PRO_MAXK = 4;      // causal convolution taps supported
+constexpr int PRO_MAXPOS = 64;   // rotary table rows (positions modulo the mini-batch length)
+
+// One warp task = (batch b, group of 4 heads, chunk of PRO_TCHUNK tokens).  Lane = 8*hq + sub handles head
+// 4*hgroup + hq, features [8*sub, 8*sub+8) = rotary pairs 4*sub .. 4*sub+3, and walks the chunk's tokens in groups of
+// PRO_TG whose loads are all issued before any of them is used (memory-level parallelism).
+constexpr int PRO_TG = 4;
+
+template <typename T, bool CONV>
+__global__ void __launch_bounds__(PRO_THREADS) ttt_layer_prologue_kernel(const LayerProParams p) {
+  __shared__ float2 rope_tab[PRO_MAXPOS][32];  // (cos, sin) per position and pair
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int F = HD, H = p.H, NT = p.T;
+  const bool rope = p.rope_mode != 0;
+  const bool rope_wrap = p.rope_mode == 1;
+  const float log2_theta = log2f(p.rope_theta);
+  if (rope && rope_wrap) {
+    for (int e = tid; e < p.pos_mod * 32; e += PRO_THREADS) {
+      const int pos = e >> 5, i = e & 31;
+      const float inv_freq = exp2f(-(2.f * i / F) * log2_theta);
+      float s, c;
+      sincosf(pos * inv_freq, &s, &c);
+      rope_tab[pos][i] = make_float2(c, s);
+    }
+  }
+  __syncthreads();
+
+  const int hq = lane >> 3, sub = lane & 7;
+  const int hgroups = (H + 3) >> 2, tchunks = (NT + PRO_TCHUNK - 1) / PRO_TCHUNK;
+  const long ntasks = (long)p.B * hgroups * tchunks;
+  const int KC = p.conv_k;
+
+  for (long task = (long)blockIdx.x * (PRO_THREADS / 32) + warp; task < ntasks; task += (long)gridDim.x * (PRO_THREADS / 32)) {
+    const int tc = (int)(task % tchunks);
+    const int hg = (int)((task / tchunks) % hgroups);
+    const int b = (int)(task / ((long)tchunks * hgroups));
+    const int h = 4 * hg + hq;
+    if (h >= H) continue;
+    const int col = h * F + 8 * sub;  // first of this lane's 8 columns inside a projection block
+    const int t0 = tc * PRO_TCHUNK, t1 = min(NT, t0 + PRO_TCHUNK);
+
+    // convolution taps and biases of this lane's 8 channels (loop-invariant); window slot j holds token
+    // t-(PRO_MAXK-1)+j and taps are right-aligned (the last tap multiplies token t), so slots older than the kernel
+    // length get zero weights
+    float wq[CONV ? PRO_MAXK : 1][8], wk[CONV ? PRO_MAXK : 1][8], bq[8], bk[8];
+    float hist[CONV ? PRO_MAXK - 1 : 1][8];  // the previous PRO_MAXK-1 rows of the shared projection (oldest first)
+    if constexpr (CONV) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        bq[c] = ld_as_float<T>(p.conv_q_b, (size_t)(col + c));
+        bk[c] = ld_as_float<T>(p.conv_k_b, (size_t)(col + c));
+#pragma unroll
+        for (int j = 0; j < PRO_MAXK; ++j) {
+          const int wj = j - (PRO_MAXK - KC);
+          wq[j][c] = (wj >= 0) ? ld_as_float<T>(p.conv_q_w, (size_t)(col + c) * KC + wj) : 0.f;
+          wk[j][c] = (wj >= 0) ? ld_as_float<T>(p.conv_k_w, (size_t)(col + c) * KC + wj) : 0.f;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < PRO_MAXK - 1; ++j) {
+        const int tt = t0 - (PRO_MAXK - 1) + j;
+        if (tt >= 0) {
+          Vec8<T> v;
+          v.load(static_cast<const T*>(p.q_src) + ((size_t)b * NT + tt) * p.ld_src + col);
+          v.unpack(hist[j]);
+        } else {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) hist[j][c] = 0.f;
+        }
+      }
+    }
+
+    for (int tb = t0; tb < t1; tb += PRO_TG) {
+      Vec8<T> vq[PRO_TG], vk[PRO_TG], vv[PRO_TG];
+#pragma unroll
+      for (int u = 0; u < PRO_TG; ++u) {
+        if (tb + u < t1) {
+          const size_t srow = ((size_t)b * NT + tb + u) * p.ld_src + col;
+          vq[u].load(static_cast<const T*>(p.q_src) + srow);
+          if constexpr (!CONV) vk[u].load(static_cast<const T*>(p.k_src) + srow);
+          vv[u].load(static_cast<const T*>(p.v_src) + srow);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < PRO_TG; ++u) {
+        const int t = tb + u;
+        if (t < t1) {
+          float fq[8], fk[8];
+          if constexpr (CONV) {
+            float cur[8];
+            vq[u].unpack(cur);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              float aq = bq[c], ak = bk[c];
+#pragma unroll
+              for (int j = 0; j < PRO_MAXK - 1; ++j) {
+                aq = fmaf(wq[j][c], hist[j][c], aq);
+                ak = fmaf(wk[j][c], hist[j][c], ak);
+              }
+              fq[c] = fmaf(wq[PRO_MAXK - 1][c], cur[c], aq);
+              fk[c] = fmaf(wk[PRO_MAXK - 1][c], cur[c], ak);
+            }
+#pragma unroll
+            for (int j = 0; j < PRO_MAXK - 2; ++j)
+#pragma unroll
+              for (int c = 0; c < 8; ++c) hist[j][c] = hist[j + 1][c];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) hist[PRO_MAXK - 2][c] = cur[c];
+          } else {
+            vq[u].unpack(fq);
+            vk[u].unpack(fk);
+          }
+          if (rope) {
+            const int pos = p.start_idx + t;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float2 cs;
+              if (rope_wrap) {
+                cs = rope_tab[pos % p.pos_mod][4 * sub + j];
+              } else {
+                const float inv_freq = exp2f(-(2.f * (4 * sub + j) / F) * log2_theta);
+                sincosf(pos * inv_freq, &cs.y, &cs.x);
+              }
+              const float q0 = fq[2 * j], q1 = fq[2 * j + 1], k0 = fk[2 * j], k1 = fk[2 * j + 1];
+              fq[2 * j] = q0 * cs.x - q1 * cs.y;
+              fq[2 * j + 1] = q1 * cs.x + q0 * cs.y;
+              fk[2 * j] = k0 * cs.x - k1 * cs.y;
+              fk[2 * j + 1] = k1 * cs.x + k0 * cs.y;
+            }
+          }
+          if (CONV || rope) {
+            vq[u].pack(fq);
+            vk[u].pack(fk);
+          }
+          const size_t drow = (((size_t)b * H + h) * NT + t) * F + 8 * sub;
+          vq[u].store(static_cast<T*>(p.xq) + drow);
+          vk[u].store(static_cast<T*>(p.xk) + drow);
+          vv[u].store(static_cast<T*>(p.xv) + drow);
+        }
+      }
+    }
+  }
+
+  // ttt_lr_eta[b,h,t] = base_lr / F * sigmoid(logit[b*T+t][h] + bias[h])
+  const long nlr = (long)p.B * H * NT;
+  for (long e = (long)blockIdx.x * PRO_THREADS + tid; e < nlr; e += (long)gridDim.x * PRO_THREADS) {
+    const int t = (int)(e % NT);
+    const int h = (int)((e / NT) % H);
+    const int b = (int)(e / ((long)NT * H));
+    float z = ld_as_float<T>(p.lr_logits, ((size_t)b * NT + t) * p.ld_lr + h);
+    if (p.lr_bias != nullptr) z += ld_as_float<T>(p.lr_bias, (size_t)h);
+    st_from_float<T>(p.lr_out, (size_t)e, p.base_lr / F / (1.f + expf(-z)));
+  }
+}
+
+constexpr int EPI_THREADS = 256;
+
+// One warp per token (b, t): lane holds the feature pair (2*lane, 2*lane+1) of every head.
+template <typename T, int HMAX>
+__global__ void __launch_bounds__(EPI_THREADS) ttt_layer_epilogue_kernel(const LayerEpiParams p) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int H = p.H, T_ = p.T, F = HD, C = H * F;
+  const long ntok = (long)p.B * T_;
+  for (long tok = (long)blockIdx.x * (EPI_THREADS / 32) + warp; tok < ntok; tok += (long)gridDim.x * (EPI_THREADS / 32)) {
+    const int t = (int)(tok % T_);
+    const int b = (int)(tok / T_);
+    float2 v[HMAX];
+    float s = 0.f;
+#pragma unroll
+    for (int h = 0; h < HMAX; ++h) {
+      if (h < H) {
+        const size_t off = (((size_t)b * H + h) * T_ + t) * F + 2 * lane;
+        if constexpr (sizeof(T) == 2) {
+          const uint32_t w = *reinterpret_cast<const uint32_t*>(static_cast<const T*>(p.inner_out) + off);
+          v[h] = make_float2(bf16_lo(w), bf16_hi(w));
+        } else {
+          v[h] = *reinterpret_cast<const float2*>(static_cast<const T*>(p.inner_out) + off);
+        }
+        s += v[h].x + v[h].y;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float mean = s / C;
+    float q = 0.f;
+#pragma unroll
+    for (int h = 0; h < HMAX; ++h) {
+      if (h < H) {
+        const float dx = v[h].x - mean, dy = v[h].y - mean;
+        q = fmaf(dx, dx, fmaf(dy, dy, q));
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+    const float rstd = 1.f / sqrtf(q / C + p.eps);
+#pragma unroll
+    for (int h = 0; h < HMAX; ++h) {
+      if (h < H) {
+        const int c = h * F + 2 * lane;
+        float y0 = (v[h].x - mean) * rstd * ld_as_float<T>(p.ln_w, c) + ld_as_float<T>(p.ln_b, c);
+        float y1 = (v[h].y - mean) * rstd * ld_as_float<T>(p.ln_w, c + 1) + ld_as_float<T>(p.ln_b, c + 1);
+        if (p.gate != nullptr) {
+          const size_t go = (size_t)tok * p.ld_gate + c;
+          const float g0 = ld_as_float<T>(p.gate, go), g1 = ld_as_float<T>(p.gate, go + 1);
+          // gelu, tanh form (rust/layer/src/ttt.rs:290-293; constants thundercube/src/unary_ops.rs:136-137)
+          const float u0 = 0.7978845608028654f * (g0 + 0.044715f * g0 * g0 * g0);
+          const float u1 = 0.7978845608028654f * (g1 + 0.044715f * g1 * g1 * g1);
+          y0 *= 0.5f * g0 * (1.f + tanhf(u0));
+          y1 *= 0.5f * g1 * (1.f + tanhf(u1));
+        }
+        const size_t yo = (size_t)tok * C + c;
+        if constexpr (sizeof(T) == 2) {
+          *reinterpret_cast<uint32_t*>(static_cast<T*>(p.y) + yo) = pack_bf16(y0, y1);
+        } else {
+          *reinterpret_cast<float2*>(static_cast<T*>(p.y) + yo) = make_float2(y0, y1);
+        }
+      }
+    }
+  }
+}
+
+static int sm_count() {
+  int dev = 0, n = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  return n;
+}
+
+cudaError_t launch_layer_prologue(int dtype, const LayerProParams& p, cudaStream_t st) {
+  const long ntasks = (long)p.B * ((p.H + 3) / 4) * ((p.T + PRO_TCHUNK - 1) / PRO_TCHUNK);
+  const long want = (ntasks + PRO_THREADS / 32 - 1) / (PRO_THREADS / 32);
+  const long cap = (long)sm_count() * 8;
+  const int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+  const bool conv = p.conv_q_w != nullptr;
+  if (dtype == 1) {
+    if (conv)
+      ttt_layer_prologue_kernel<__nv_bfloat16, true><<<grid, PRO_THREADS, 0, st>>>(p);
+    else
+      ttt_layer_prologue_kernel<__nv_bfloat16, false><<<grid, PRO_THREADS, 0, st>>>(p);
+  } else {
+    if (conv)
+      ttt_layer_prologue_kernel<float, true><<<grid, PRO_THREADS, 0, st>>>(p);
+    else
+      ttt_layer_prologue_kernel<float, false><<<grid, PRO_THREADS, 0, st>>>(p);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_layer_epilogue(int dtype, const LayerEpiParams& p, cudaStream_t st) {
+  const long ntok = (long)p.B * p.T;
+  const long want = (ntok + EPI_THREADS / 32 - 1) / (EPI_THREADS / 32);
+  const long cap = (long)sm_count() * 8;
+  const int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+  if (dtype == 1) {
+    if (p.H <= 16)
+      ttt_layer_epilogue_kernel<__nv_bfloat16, 16><<<grid, EPI_THREADS, 0, st>>>(p);
+    else
+      ttt_layer_epilogue_kernel<__nv_bfloat16, 32><<<grid, EPI_THREADS, 0, st>>>(p);
+  } else {
+    if (p.H <= 16)
+      ttt_layer_epilogue_kernel<float, 16><<<grid, EPI_THREADS, 0, st>>>(p);
+    else
+      ttt_layer_epilogue_kernel<float, 32><<<grid, EPI_THREADS, 0, st>>>(p);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace ttt

@@ -1,0 +1,210 @@
+"""The outer TTT layer around the fused inner loop (forward / prefill), mirroring the reference's `TTT` module
+(rust/layer/src/ttt.rs:29-299; PyTorch twin reference/ttt.py:598-915): same parameters, same `forward(x, inner,
+state, start_idx)`.
+
+What runs where:
+  * q/k/v(/gate) projections and the per-head learning-rate logits: ONE library GEMM over the concatenated weights
+    (the reference issues one GEMM per projection plus a batched matmul for the gate logits);
+  * head split + permute to [B,H,T,F], shared-QK causal convolutions, rotary embedding, sigmoid learning-rate gate:
+    `ttt_layer_prologue` (one pass over the projection output);
+  * inner loop: the fused kernel behind `FusedTileMultiTTTLinear`;
+  * permute back + post LayerNorm + gelu gate: `ttt_layer_epilogue` (one pass);
+  * output projection: library GEMM.
+There is no PyTorch fallback for the two layer kernels: without the CUDA library the calls raise.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import TttDims
+from .fused import FusedTileMultiTTTLinear, Qkv, TTTInputsInner, TTTLinear, TTTLinearState
+
+ROPE_NONE, ROPE_WRAPPED, ROPE_GLOBAL = 0, 1, 2
+_POS = {"none": ROPE_NONE, "rope": ROPE_WRAPPED, "rope_global": ROPE_GLOBAL}
+
+
+@dataclass
+class TTTLayerConfig:
+    """The fields of the reference's model config this layer reads (rust/config/src/train.rs:14-50,
+    rust/layer/src/ttt.rs:60-145)."""
+    hidden_size: int
+    num_heads: int
+    mini_batch_size: int = 16
+    base_lr: float = 1.0
+    rope_theta: float = 10000.0
+    pos_encoding: str = "rope"   # "rope" (positions modulo the mini-batch), "rope_global", "none"
+    conv_kernel_size: int = 4
+    use_gate: bool = False
+    share_qk: bool = False
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden_size // self.num_heads
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.bfloat16:
+        return _lib.TTT_BF16
+    if dt == torch.float32:
+        return _lib.TTT_F32
+    raise TypeError(f"unsupported dtype {dt} (float32 or bfloat16)")
+
+
+def layer_prologue(proj: torch.Tensor, cfg: TTTLayerConfig, *, q_col: int, k_col: int, v_col: int, lr_col: int,
+                   lr_bias: Optional[torch.Tensor], conv=None, start_idx: int = 0):
+    """proj [B,T,N]: a projection output holding, as column blocks, q at q_col, k at k_col, v at v_col (H*F columns
+    each) and the H learning-rate logits at lr_col.  `conv` = (q_weight [C,1,K] or [C,K], q_bias [C], k_weight, k_bias)
+    for the shared-QK layout.  Returns XQ, XK, XV [B,H,T,F] and ttt_lr_eta [B,H,T]."""
+    lib = _lib.load()
+    B, T, N = proj.shape
+    H, F = cfg.num_heads, cfg.head_dim
+    if not proj.is_cuda or not proj.is_contiguous():
+        raise ValueError("proj must be a contiguous CUDA tensor")
+    dt = proj.dtype
+    esz = proj.element_size()
+    d = TttDims(B, H, T, F, cfg.mini_batch_size, 1, 0.0, _dtype_code(dt))
+    xq, xk, xv = (torch.empty(B, H, T, F, dtype=dt, device=proj.device) for _ in range(3))
+    lr = torch.empty(B, H, T, dtype=dt, device=proj.device)
+    base = proj.data_ptr()
+    col = lambda c: C.c_void_p(base + c * esz)  # noqa: E731
+    cw = [None] * 4
+    kc = 0
+    if conv is not None:
+        cw = [t.to(dt).reshape(t.shape[0], -1).contiguous() if t.dim() > 1 else t.to(dt).contiguous() for t in conv]
+        kc = cw[0].shape[1]
+    bias = None if lr_bias is None else lr_bias.to(dt).reshape(-1).contiguous()
+    stream = C.c_void_p(torch.cuda.current_stream(proj.device).cuda_stream)
+    with torch.cuda.device(proj.device):
+        _lib.check(lib.ttt_layer_prologue(
+            C.byref(d), col(q_col), col(k_col), col(v_col), N, col(lr_col), N, _ptr(bias),
+            _ptr(cw[0]), _ptr(cw[1]), _ptr(cw[2]), _ptr(cw[3]), kc, start_idx, _POS[cfg.pos_encoding],
+            cfg.rope_theta, cfg.base_lr, _ptr(xq), _ptr(xk), _ptr(xv), _ptr(lr), stream))
+    return xq, xk, xv, lr
+
+
+def layer_epilogue(inner_out: torch.Tensor, ln_weight: torch.Tensor, ln_bias: torch.Tensor, eps: float = 1e-6,
+                   gate: Optional[torch.Tensor] = None, gate_ld: int = 0):
+    """inner_out [B,H,T,F] -> [B,T,H*F], post LayerNorm applied, times gelu_tanh(gate) when `gate` (a [B*T, gate_ld]
+    view, first H*F columns) is given."""
+    lib = _lib.load()
+    B, H, T, F = inner_out.shape
+    if not inner_out.is_cuda or not inner_out.is_contiguous():
+        raise ValueError("inner_out must be a contiguous CUDA tensor")
+    dt = inner_out.dtype
+    d = TttDims(B, H, T, F, 16, 1, 0.0, _dtype_code(dt))
+    y = torch.empty(B, T, H * F, dtype=dt, device=inner_out.device)
+    w, b = ln_weight.to(dt).contiguous(), ln_bias.to(dt).contiguous()
+    stream = C.c_void_p(torch.cuda.current_stream(inner_out.device).cuda_stream)
+    with torch.cuda.device(inner_out.device):
+        _lib.check(lib.ttt_layer_epilogue(C.byref(d), _ptr(inner_out), _ptr(gate), gate_ld, _ptr(w), _ptr(b),
+                                          eps, _ptr(y), stream))
+    return y
+
+
+class TTT(torch.nn.Module):
+    """Outer TTT layer.  Parameter names follow the reference (`q_proj`, `k_proj`, `v_proj`, `g_proj`, `o_proj`,
+    `q_conv` / `k_conv`, `learnable_ttt_lr_weight` [H, hidden, 1], `learnable_ttt_lr_bias` [H, 1], `token_idx`,
+    `learnable_token_idx`, `post_norm`)."""
+
+    def __init__(self, config: TTTLayerConfig, device=None, dtype=torch.float32):
+        super().__init__()
+        c = config
+        self.config = c
+        kw = dict(device=device, dtype=dtype)
+        hs = c.hidden_size
+
+        def lin():
+            return torch.nn.Parameter(torch.randn(hs, hs, **kw) * 0.02)
+
+        self.q_proj = lin()
+        self.k_proj = None if c.share_qk else lin()
+        self.v_proj = lin()
+        self.g_proj = lin() if c.use_gate else None
+        self.o_proj = lin()
+        if c.share_qk:
+            k = c.conv_kernel_size
+            self.q_conv_weight = torch.nn.Parameter(torch.randn(hs, 1, k, **kw) * (1.0 / k) ** 0.5)
+            self.q_conv_bias = torch.nn.Parameter(torch.zeros(hs, **kw))
+            self.k_conv_weight = torch.nn.Parameter(torch.randn(hs, 1, k, **kw) * (1.0 / k) ** 0.5)
+            self.k_conv_bias = torch.nn.Parameter(torch.zeros(hs, **kw))
+        self.learnable_ttt_lr_weight = torch.nn.Parameter(torch.randn(c.num_heads, hs, 1, **kw) * 0.02)
+        self.learnable_ttt_lr_bias = torch.nn.Parameter(torch.zeros(c.num_heads, 1, **kw))
+        self.register_buffer("token_idx", 1.0 / torch.arange(1, c.mini_batch_size + 1, **kw))
+        self.learnable_token_idx = torch.nn.Parameter(torch.zeros(c.mini_batch_size, **kw))
+        self.post_norm_weight = torch.nn.Parameter(torch.ones(hs, **kw))
+        self.post_norm_bias = torch.nn.Parameter(torch.zeros(hs, **kw))
+        self._wcat = None
+
+    # ---- one GEMM for every projection of x ----------------------------------------------------------------
+    def _fused_weight(self):
+        """Rows: q | (k) | v | (g) | lr logits (H rows), padded to a multiple of 8 rows.  Cached; call
+        `invalidate_fused_weight()` after changing a parameter."""
+        if self._wcat is None:
+            c = self.config
+            blocks, cols, off = [], {}, 0
+            for name, w in (("q", self.q_proj), ("k", self.k_proj), ("v", self.v_proj), ("g", self.g_proj)):
+                if w is not None:
+                    blocks.append(w)
+                    cols[name] = off
+                    off += w.shape[0]
+            blocks.append(self.learnable_ttt_lr_weight.reshape(c.num_heads, c.hidden_size))
+            cols["lr"] = off
+            off += c.num_heads
+            pad = (-off) % 8
+            if pad:
+                blocks.append(torch.zeros(pad, c.hidden_size, dtype=self.q_proj.dtype, device=self.q_proj.device))
+            if "k" not in cols:
+                cols["k"] = cols["q"]
+            self._wcat = (torch.cat([b.detach() for b in blocks], dim=0).contiguous(), cols)
+        return self._wcat
+
+    def invalidate_fused_weight(self):
+        self._wcat = None
+
+    def get_inner_loop_inputs(self, x: torch.Tensor, start_idx: int):
+        """Hidden states -> (TTTInputsInner, projection output, column map) (rust/layer/src/ttt.rs:250-267)."""
+        c = self.config
+        B, T, _ = x.shape
+        wcat, cols = self._fused_weight()
+        proj = torch.matmul(x, wcat.t())  # [B, T, N], library GEMM
+        conv = None
+        if c.share_qk:
+            conv = (self.q_conv_weight, self.q_conv_bias, self.k_conv_weight, self.k_conv_bias)
+        xq, xk, xv, lr = layer_prologue(proj, c, q_col=cols["q"], k_col=cols["k"], v_col=cols["v"], lr_col=cols["lr"],
+                                        lr_bias=self.learnable_ttt_lr_bias, conv=conv, start_idx=start_idx)
+        te = torch.clamp_min(self.token_idx + self.learnable_token_idx, 0.0)
+        token_eta = te.repeat((T + c.mini_batch_size - 1) // c.mini_batch_size)[:T].to(x.dtype)
+        return TTTInputsInner(Qkv(xq, xk, xv), token_eta, lr, start_idx), proj, cols
+
+    def forward(self, x: torch.Tensor, inner: FusedTileMultiTTTLinear, state: TTTLinearState,
+                start_idx: int = 0) -> torch.Tensor:
+        """x [B, T, hidden] -> [B, T, hidden]; `state` is advanced in place (rust/layer/src/ttt.rs:269-299)."""
+        if torch.is_grad_enabled():
+            raise RuntimeError("TTT.forward is the inference / prefill path (its layer kernels record no autograd "
+                               "graph): call it under torch.no_grad()")
+        c = self.config
+        B, T, _ = x.shape
+        inputs, proj, cols = self.get_inner_loop_inputs(x, start_idx)
+        out = inner.forward(state, inputs)  # [B, H, T, F]
+        gate, gate_ld = None, 0
+        if c.use_gate:
+            gate = proj.reshape(B * T, -1)[:, cols["g"]:]
+            gate_ld = proj.shape[-1]
+        y = layer_epilogue(out.contiguous(), self.post_norm_weight, self.post_norm_bias, 1e-6, gate, gate_ld)
+        return torch.matmul(y, self.o_proj.t())
+
+
+def new_inner(config: TTTLayerConfig, checkpoint_interval: int = 1, device=None, dtype=torch.float32):
+    """The `fused-tile-multi` inner model matching a layer config."""
+    return FusedTileMultiTTTLinear(TTTLinear(config.num_heads, config.head_dim, config.mini_batch_size, 1e-6,
+                                             checkpoint_interval, device=device, dtype=dtype))
