@@ -51,6 +51,13 @@ WORKLOADS = {
                      desc="TTT-Linear inner loop fwd+bwd, bf16, B=8 H=32 T=16384 d=64 mb=16 ckpt=16"),
     "cfg4-32k": dict(B=8, H=32, T=32768, dtype="bf16", K=16, backward=True,
                      desc="TTT-Linear inner loop fwd+bwd, bf16, B=8 H=32 T=32768 d=64 mb=16 ckpt=16"),
+    # the whole outer layer (projections, prologue, inner loop, epilogue, output projection), forward / prefill
+    "layer-fwd": dict(kind="layer", B=8, H=12, T=2048, dtype="bf16", K=1, backward=False,
+                      desc="TTT layer forward (125M layer shape: hidden 768, 12 heads x 64), bf16, B=8 T=2048 mb=16"),
+    "layer-fwd-b32": dict(kind="layer", B=32, H=12, T=2048, dtype="bf16", K=1, backward=False,
+                          desc="TTT layer forward (hidden 768, 12 heads x 64), bf16, B=32 T=2048 mb=16"),
+    "layer-fwd-1b3": dict(kind="layer", B=8, H=32, T=8192, dtype="bf16", K=1, backward=False,
+                          desc="TTT layer forward (1.3B layer shape: hidden 2048, 32 heads x 64), bf16, B=8 T=8192 mb=16"),
 }
 F, CS = 64, 16
 
@@ -183,6 +190,116 @@ def run_reference(args, w):
     print(json.dumps(line), flush=True)
 
 
+def time_events(fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def run_layer(args, w):
+    """Forward of one whole TTT layer on synthetic hidden states: tokens/s of the layer, the time of each piece, and
+    the HBM roofline of the two layer kernels (algorithmic bytes: prologue reads q, k, v and the lr logits once and
+    writes XQ, XK, XV and ttt_lr_eta once; epilogue reads the inner output once and writes the normalised rows once)."""
+    import ttt_rs_b200 as tb
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        raise SystemExit("the layer workloads are single-GPU measurements")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operator has no CPU path")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    tb.load_library()
+    B, H, T = w["B"], w["H"], w["T"]
+    C = H * F
+    dt = torch.bfloat16
+    torch.manual_seed(0)
+    cfg = tb.TTTLayerConfig(hidden_size=C, num_heads=H)
+    m = tb.TTT(cfg, device=dev, dtype=dt)
+    inner = tb.new_inner(cfg, checkpoint_interval=w["K"], device=dev, dtype=dt)
+    x = (torch.randn(B, T, C, device=dev) * 0.5).to(dt)
+    state0 = inner.init_state(B)
+    sampler = ClockSampler(0)
+
+    def whole():
+        with torch.no_grad():
+            st = tb.TTTLinearState(state0.weight, state0.bias)
+            return m(x, inner, st)
+
+    with torch.no_grad():
+        wcat, cols = m._fused_weight()
+        proj = torch.matmul(x, wcat.t())
+        inputs, _, _ = m.get_inner_loop_inputs(x, 0)
+        inner_out = inner.forward(tb.TTTLinearState(state0.weight, state0.bias), inputs)
+        y = tb.layer_epilogue(inner_out, m.post_norm_weight, m.post_norm_bias)
+    tb.TttTileMultiKernel.check_status()
+
+    def pro():
+        return tb.layer_prologue(proj, cfg, q_col=cols["q"], k_col=cols["k"], v_col=cols["v"], lr_col=cols["lr"],
+                                 lr_bias=m.learnable_ttt_lr_bias)
+
+    def epi():
+        return tb.layer_epilogue(inner_out, m.post_norm_weight, m.post_norm_bias)
+
+    def inner_only():
+        with torch.no_grad():
+            return inner.forward(tb.TTTLinearState(state0.weight, state0.bias), inputs)
+
+    sampler.start()
+    ms = time_events(whole, args.steps, args.warmup)
+    clocks = sampler.stop()
+    pieces = {
+        "projections_gemm": time_events(lambda: torch.matmul(x, wcat.t()), args.steps, args.warmup),
+        "ttt_layer_prologue_kernel": time_events(pro, args.steps, args.warmup),
+        "inner_loop_forward": time_events(inner_only, args.steps, args.warmup),
+        "ttt_layer_epilogue_kernel": time_events(epi, args.steps, args.warmup),
+        "output_projection_gemm": time_events(lambda: torch.matmul(y, m.o_proj.t()), args.steps, args.warmup),
+    }
+    peak, peak_kind = measured_peaks()
+    s = 2
+    pro_bytes = (3 * C * s + H * s) * B * T + (3 * C * s + H * s) * B * T
+    epi_bytes = 2 * C * s * B * T
+    pa = pro_bytes / (pieces["ttt_layer_prologue_kernel"] * 1e-3) / 1e9
+    ea = epi_bytes / (pieces["ttt_layer_epilogue_kernel"] * 1e-3) / 1e9
+    line = {
+        "metric": "ttt_layer_forward_tokens_per_sec", "value": B * T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": w["desc"], "global_batch": B,
+                   "l2": "operands of every piece exceed L2 (%.0f MB per tensor)" % (B * T * C * s / 1e6)},
+        "clocks": clocks, "e2e": None, "gpu_launches": args.steps * 3,
+        "pieces_ms": pieces,
+        "roofline": {"bound": "hbm", "kernel": "ttt_layer_prologue_kernel", "achieved": pa, "peak": peak,
+                     "unit": "GB/s", "frac": pa / peak, "traffic": None, "peak_source": f"of {peak_kind}",
+                     "algorithmic_bytes_per_launch": pro_bytes,
+                     "epilogue": {"kernel": "ttt_layer_epilogue_kernel", "achieved": ea, "frac": ea / peak,
+                                  "algorithmic_bytes_per_launch": epi_bytes}},
+    }
+    if not args.no_cpu_baseline:
+        from oracle import ttt_layer_oracle as LO
+        torch.set_num_threads(os.cpu_count() or 1)
+        p = {"q_proj": m.q_proj, "k_proj": m.k_proj, "v_proj": m.v_proj, "o_proj": m.o_proj,
+             "lr_weight": m.learnable_ttt_lr_weight, "lr_bias": m.learnable_ttt_lr_bias, "token_idx": m.token_idx,
+             "learnable_token_idx": m.learnable_token_idx, "post_norm_weight": m.post_norm_weight,
+             "post_norm_bias": m.post_norm_bias, "W1": inner.inner.weight_init, "b1": inner.inner.bias_init,
+             "ttt_norm_weight": inner.inner.ln_weight, "ttt_norm_bias": inner.inner.ln_bias}
+        p = {k: v.detach().float().cpu() for k, v in p.items()}
+        xs = x[:1].float().cpu()
+        LO.ttt_layer_forward(xs[:, :256], p, num_heads=H)
+        t0 = time.perf_counter()
+        for _ in range(3):
+            LO.ttt_layer_forward(xs, p, num_heads=H)
+        dtc = (time.perf_counter() - t0) / 3
+        line["cpu_baseline"] = {"value": T / dtc, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": f"B=1 T={T} slice of the workload, float32, 3 passes"}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -196,6 +313,11 @@ def main():
     w = WORKLOADS[args.workload]
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
+    if w.get("kind") == "layer":
+        if args.impl == "reference":
+            raise SystemExit("--impl reference is defined for the inner-loop workloads")
+        run_layer(args, w)
+        return
     if args.impl == "reference":
         run_reference(args, w)
         return

@@ -514,8 +514,8 @@ extern "C" int ttt_layer_epilogue(const ttt_dims* d, const void* inner_out, cons
   if (rc != TTT_OK) return rc;
   if (post_norm_weight == nullptr || post_norm_bias == nullptr) return fail(TTT_ERR_NULL, "post_norm_weight / post_norm_bias is null");
   if (gate != nullptr) {
-    if (gate_ld < (int64_t)d->heads * 64 || (gate_ld & 1) != 0)
-      return fail(TTT_ERR_SHAPE, "gate_ld (%lld) must be >= heads*64 and even", (long long)gate_ld);
+    if (gate_ld < (int64_t)d->heads * 64 || (gate_ld & 3) != 0)
+      return fail(TTT_ERR_SHAPE, "gate_ld (%lld) must be >= heads*64 and a multiple of 4", (long long)gate_ld);
     if ((reinterpret_cast<uintptr_t>(gate) & 7u) != 0) return fail(TTT_ERR_ALIGN, "gate is not 8-byte aligned");
   }
   ttt::LayerEpiParams p;

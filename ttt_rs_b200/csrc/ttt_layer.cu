@@ -70,7 +70,7 @@ constexpr int PRO_MAXPOS = 64;   // rotary table rows (positions modulo the mini
 constexpr int PRO_TG = 4;
 
 template <typename T, bool CONV>
-__global__ void __launch_bounds__(PRO_THREADS) ttt_layer_prologue_kernel(const LayerProParams p) {
+__global__ void __launch_bounds__(PRO_THREADS, (CONV || sizeof(T) == 4) ? 1 : 3) ttt_layer_prologue_kernel(const LayerProParams p) {
   __shared__ float2 rope_tab[PRO_MAXPOS][32];  // (cos, sin) per position and pair
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int F = HD, H = p.H, NT = p.T;
@@ -218,68 +218,151 @@ __global__ void __launch_bounds__(PRO_THREADS) ttt_layer_prologue_kernel(const L
 
 constexpr int EPI_THREADS = 256;
 
-// One warp per token (b, t): lane holds the feature pair (2*lane, 2*lane+1) of every head.
-template <typename T, int HMAX>
-__global__ void __launch_bounds__(EPI_THREADS) ttt_layer_epilogue_kernel(const LayerEpiParams p) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int H = p.H, T_ = p.T, F = HD, C = H * F;
-  const long ntok = (long)p.B * T_;
-  for (long tok = (long)blockIdx.x * (EPI_THREADS / 32) + warp; tok < ntok; tok += (long)gridDim.x * (EPI_THREADS / 32)) {
-    const int t = (int)(tok % T_);
-    const int b = (int)(tok / T_);
-    float2 v[HMAX];
-    float s = 0.f;
-#pragma unroll
-    for (int h = 0; h < HMAX; ++h) {
-      if (h < H) {
-        const size_t off = (((size_t)b * H + h) * T_ + t) * F + 2 * lane;
-        if constexpr (sizeof(T) == 2) {
-          const uint32_t w = *reinterpret_cast<const uint32_t*>(static_cast<const T*>(p.inner_out) + off);
-          v[h] = make_float2(bf16_lo(w), bf16_hi(w));
-        } else {
-          v[h] = *reinterpret_cast<const float2*>(static_cast<const T*>(p.inner_out) + off);
-        }
-        s += v[h].x + v[h].y;
-      }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    const float mean = s / C;
-    float q = 0.f;
-#pragma unroll
-    for (int h = 0; h < HMAX; ++h) {
-      if (h < H) {
-        const float dx = v[h].x - mean, dy = v[h].y - mean;
-        q = fmaf(dx, dx, fmaf(dy, dy, q));
-      }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
-    const float rstd = 1.f / sqrtf(q / C + p.eps);
-#pragma unroll
-    for (int h = 0; h < HMAX; ++h) {
-      if (h < H) {
-        const int c = h * F + 2 * lane;
-        float y0 = (v[h].x - mean) * rstd * ld_as_float<T>(p.ln_w, c) + ld_as_float<T>(p.ln_b, c);
-        float y1 = (v[h].y - mean) * rstd * ld_as_float<T>(p.ln_w, c + 1) + ld_as_float<T>(p.ln_b, c + 1);
-        if (p.gate != nullptr) {
-          const size_t go = (size_t)tok * p.ld_gate + c;
-          const float g0 = ld_as_float<T>(p.gate, go), g1 = ld_as_float<T>(p.gate, go + 1);
-          // gelu, tanh form (rust/layer/src/ttt.rs:290-293; constants thundercube/src/unary_ops.rs:136-137)
-          const float u0 = 0.7978845608028654f * (g0 + 0.044715f * g0 * g0 * g0);
-          const float u1 = 0.7978845608028654f * (g1 + 0.044715f * g1 * g1 * g1);
-          y0 *= 0.5f * g0 * (1.f + tanhf(u0));
-          y1 *= 0.5f * g1 * (1.f + tanhf(u1));
-        }
-        const size_t yo = (size_t)tok * C + c;
-        if constexpr (sizeof(T) == 2) {
-          *reinterpret_cast<uint32_t*>(static_cast<T*>(p.y) + yo) = pack_bf16(y0, y1);
-        } else {
-          *reinterpret_cast<float2*>(static_cast<T*>(p.y) + yo) = make_float2(y0, y1);
-        }
-      }
-    }
+
+// One CTA per tile of TT consecutive tokens of one batch element.  Load phase: for every head the tile's TT rows of
+// 64 features are one contiguous segment of the [B,H,T,F] tensor; all threads fetch the segments with 16-byte loads
+// (the whole tile is in flight at once) and scatter them into a [TT][H*F] tile in shared memory.  Row phase: each
+// warp takes whole rows from shared memory (three sweeps: sum, squared deviations, output), applies the norm and the
+// optional gate and writes the row to [B,T,H*F] with 16-byte stores.  Several CTAs per SM overlap the two phases.
+// MAXCH: 16-byte chunks of one row per lane (rows of up to 32 * MAXCH chunks = 512 * MAXCH bytes); the tile holds
+// TT = 64 / MAXCH tokens, so the [TT][H*F] staging tile stays at or below 32 KB and several CTAs share an SM.
+template <typename T, int MAXCH>
+__global__ void __launch_bounds__(EPI_THREADS, (MAXCH <= 4 ? 4 : 2)) ttt_layer_epilogue_kernel(const LayerEpiParams p) {
+  constexpr int TT = 64 / MAXCH;
+  constexpr int EPC = 16 / sizeof(T);  // elements per 16-byte chunk
+  constexpr int NPAIR = EPC / 2;
+  constexpr int CPR = HD / EPC;        // chunks per head row
+  extern __shared__ __align__(16) uint8_t epi_smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int H = p.H, NT = p.T, C = H * HD;
+  const size_t tile_bytes = (size_t)TT * C * sizeof(T);
+  float* gam = reinterpret_cast<float*>(epi_smem + 2 * tile_bytes);  // two tiles (double buffer), then gamma, beta
+  float* bet = gam + C;
+  for (int c = tid; c < C; c += EPI_THREADS) {
+    gam[c] = ld_as_float<T>(p.ln_w, (size_t)c);
+    bet[c] = ld_as_float<T>(p.ln_b, (size_t)c);
   }
+  const int tiles_per_b = (NT + TT - 1) / TT;
+  const long ntiles = (long)p.B * tiles_per_b;
+  const int nch = C / EPC;          // chunks per output row
+  constexpr int seg = TT * CPR;     // chunks per head segment of a full tile (a power of two)
+
+  // asynchronous 16-byte copies global -> shared of one tile (no register staging); one commit group per tile
+  auto fetch = [&](long tile_id, int buf) {
+    if (tile_id < ntiles) {
+      const int b = (int)(tile_id / tiles_per_b);
+      const int t0 = (int)(tile_id % tiles_per_b) * TT;
+      const int rows = min(TT, NT - t0);
+      const uint32_t dst0 = smem_u32(epi_smem + buf * tile_bytes);
+      for (int idx = tid; idx < H * seg; idx += EPI_THREADS) {
+        const int h = idx / seg, i = idx - h * seg, r = i / CPR, cc = i - r * CPR;
+        if (r < rows) {
+          const T* src = static_cast<const T*>(p.inner_out) + (((size_t)b * H + h) * NT + t0) * HD + (size_t)i * EPC;
+          const uint32_t dst = dst0 + (uint32_t)(((size_t)r * C + h * HD + cc * EPC) * sizeof(T));
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+        }
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  int buf = 0;
+  fetch(blockIdx.x, 0);
+  for (long tile_id = blockIdx.x; tile_id < ntiles; tile_id += gridDim.x, buf ^= 1) {
+    const int b = (int)(tile_id / tiles_per_b);
+    const int t0 = (int)(tile_id % tiles_per_b) * TT;
+    const int rows = min(TT, NT - t0);
+    fetch(tile_id + gridDim.x, buf ^ 1);  // the other buffer was released by the barrier that ended the last tile
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncthreads();  // this tile has landed for every thread (and gam / bet are written, first time round)
+    const T* tile = reinterpret_cast<const T*>(epi_smem + buf * tile_bytes);
+    for (int r = warp; r < rows; r += EPI_THREADS / 32) {
+      const T* row = tile + (size_t)r * C;
+      F2 v[MAXCH][NPAIR];
+      F2 acc = f2(0.f);
+#pragma unroll
+      for (int j = 0; j < MAXCH; ++j) {
+        const int ch = j * 32 + lane;
+        if (ch < nch) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(row + ch * EPC);
+          if constexpr (sizeof(T) == 2) {
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v[j][k] = f2(bf16_lo(w[k]), bf16_hi(w[k]));
+          } else {
+            v[j][0] = f2(__uint_as_float(raw.x), __uint_as_float(raw.y));
+            v[j][1] = f2(__uint_as_float(raw.z), __uint_as_float(raw.w));
+          }
+#pragma unroll
+          for (int k = 0; k < NPAIR; ++k) acc = f2add(acc, v[j][k]);
+        }
+      }
+      float s = f2hsum(acc);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      const float mean = s / C;
+      acc = f2(0.f);
+#pragma unroll
+      for (int j = 0; j < MAXCH; ++j) {
+        if (j * 32 + lane < nch) {
+#pragma unroll
+          for (int k = 0; k < NPAIR; ++k) {
+            v[j][k] = f2sub(v[j][k], f2(mean));
+            acc = f2fma(v[j][k], v[j][k], acc);
+          }
+        }
+      }
+      float q = f2hsum(acc);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+      const float rstd = 1.f / sqrtf(q / C + p.eps);
+      const size_t tok = (size_t)b * NT + t0 + r;
+#pragma unroll
+      for (int j = 0; j < MAXCH; ++j) {
+        const int ch = j * 32 + lane;
+        if (ch < nch) {
+          const int c0 = ch * EPC;
+          float y[EPC];
+#pragma unroll
+          for (int k = 0; k < NPAIR; ++k) {
+            const F2 g2 = *reinterpret_cast<const F2*>(gam + c0 + 2 * k), b2 = *reinterpret_cast<const F2*>(bet + c0 + 2 * k);
+            const F2 o = f2fma(v[j][k], f2mul(g2, f2(rstd)), b2);
+            y[2 * k] = o.x;
+            y[2 * k + 1] = o.y;
+          }
+          if (p.gate != nullptr) {
+            float gt[EPC];
+            const T* gp = static_cast<const T*>(p.gate) + tok * p.ld_gate + c0;
+            if constexpr (sizeof(T) == 2) {
+              // gate rows are only 8-byte aligned: two 8-byte loads
+              const uint2 g0 = reinterpret_cast<const uint2*>(gp)[0], g1 = reinterpret_cast<const uint2*>(gp)[1];
+              gt[0] = bf16_lo(g0.x); gt[1] = bf16_hi(g0.x); gt[2] = bf16_lo(g0.y); gt[3] = bf16_hi(g0.y);
+              gt[4] = bf16_lo(g1.x); gt[5] = bf16_hi(g1.x); gt[6] = bf16_lo(g1.y); gt[7] = bf16_hi(g1.y);
+            } else {
+              const float2 g0 = reinterpret_cast<const float2*>(gp)[0], g1 = reinterpret_cast<const float2*>(gp)[1];
+              gt[0] = g0.x; gt[1] = g0.y; gt[2] = g1.x; gt[3] = g1.y;
+            }
+#pragma unroll
+            for (int e = 0; e < EPC; ++e) {
+              // gelu, tanh form (rust/layer/src/ttt.rs:290-293; constants thundercube/src/unary_ops.rs:136-137)
+              const float g = gt[e], u = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+              y[e] *= 0.5f * g * (1.f + tanhf(u));
+            }
+          }
+          T* dst = static_cast<T*>(p.y) + tok * C + c0;
+          if constexpr (sizeof(T) == 2) {
+            uint4 o;
+            o.x = pack_bf16(y[0], y[1]); o.y = pack_bf16(y[2], y[3]); o.z = pack_bf16(y[4], y[5]); o.w = pack_bf16(y[6], y[7]);
+            *reinterpret_cast<uint4*>(dst) = o;
+          } else {
+            *reinterpret_cast<float4*>(dst) = make_float4(y[0], y[1], y[2], y[3]);
+          }
+        }
+      }
+    }
+    __syncthreads();  // every warp is done with this buffer before the next iteration refills it
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
 static int sm_count() {
@@ -308,23 +391,29 @@ cudaError_t launch_layer_prologue(int dtype, const LayerProParams& p, cudaStream
   return cudaGetLastError();
 }
 
-cudaError_t launch_layer_epilogue(int dtype, const LayerEpiParams& p, cudaStream_t st) {
-  const long ntok = (long)p.B * p.T;
-  const long want = (ntok + EPI_THREADS / 32 - 1) / (EPI_THREADS / 32);
-  const long cap = (long)sm_count() * 8;
-  const int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
-  if (dtype == 1) {
-    if (p.H <= 16)
-      ttt_layer_epilogue_kernel<__nv_bfloat16, 16><<<grid, EPI_THREADS, 0, st>>>(p);
-    else
-      ttt_layer_epilogue_kernel<__nv_bfloat16, 32><<<grid, EPI_THREADS, 0, st>>>(p);
-  } else {
-    if (p.H <= 16)
-      ttt_layer_epilogue_kernel<float, 16><<<grid, EPI_THREADS, 0, st>>>(p);
-    else
-      ttt_layer_epilogue_kernel<float, 32><<<grid, EPI_THREADS, 0, st>>>(p);
-  }
+template <typename T, int MAXCH>
+static cudaError_t launch_epi_t(const LayerEpiParams& p, cudaStream_t st) {
+  const int C = p.H * HD;
+  constexpr int TT = 64 / MAXCH;
+  const size_t smem = 2 * (size_t)TT * C * sizeof(T) + 2 * (size_t)C * sizeof(float);
+  auto kfn = ttt_layer_epilogue_kernel<T, MAXCH>;
+  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  const long ntiles = (long)p.B * ((p.T + TT - 1) / TT);
+  int per_sm = 1;
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kfn, EPI_THREADS, smem);
+  if (e != cudaSuccess) return e;
+  const long cap = (long)sm_count() * (per_sm < 1 ? 1 : per_sm);
+  const int grid = (int)(ntiles < cap ? ntiles : cap);
+  kfn<<<grid < 1 ? 1 : grid, EPI_THREADS, smem, st>>>(p);
   return cudaGetLastError();
+}
+
+cudaError_t launch_layer_epilogue(int dtype, const LayerEpiParams& p, cudaStream_t st) {
+  // chunks of one row per lane: H*64 elements / (elements per 16 bytes) / 32 lanes
+  if (dtype == 1) return p.H <= 16 ? launch_epi_t<__nv_bfloat16, 4>(p, st) : launch_epi_t<__nv_bfloat16, 8>(p, st);
+  if (p.H <= 8) return launch_epi_t<float, 4>(p, st);
+  return p.H <= 16 ? launch_epi_t<float, 8>(p, st) : launch_epi_t<float, 16>(p, st);
 }
 
 }  // namespace ttt
