@@ -460,7 +460,8 @@ def run_e2e(tb, w, host, dev, cfg, world, args):
     step's inputs to the device, runs forward (+ backward), and copies output and gradients back to the host
     (ttt_rs_b200.host_io.HostBatchRunner: batch chunks pipelined over three streams)."""
     import torch.distributed as dist
-    from ttt_rs_b200.host_io import HostBatchRunner, alloc_host_outputs
+    from ttt_rs_b200.host_io import HostBatchRunner, alloc_host_outputs, bind_host_thread_near
+    numa_node = bind_host_thread_near(dev) if world > 1 else None  # pinned buffers in the GPU's own NUMA node
     names_in = ("xq", "xk", "xv", "ttt_lr_eta") + (("grad_output",) if w["backward"] else ())
     pinned = {k: host[k].pin_memory() for k in names_in}
     params = {k: host[k].to(dev) for k in ("weight", "bias", "token_eta", "ln_weight", "ln_bias")}
@@ -488,7 +489,8 @@ def run_e2e(tb, w, host, dev, cfg, world, args):
     d2h = sum(v.numel() * v.element_size() for v in out_host.values())
     return {"value": w["B"] * w["T"] * world / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": steps,
-            "how": "pinned host buffers, 8 batch chunks pipelined over copy-in / compute / copy-out streams"}
+            "how": "pinned host buffers, 8 batch chunks pipelined over copy-in / compute / copy-out streams",
+            "host_numa_node": numa_node}
 
 
 if __name__ == "__main__":

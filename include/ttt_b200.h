@@ -153,6 +153,20 @@ int ttt_mlp_forward(const ttt_dims* d, const void* xq, const void* xk, const voi
                     const void* ln_weight, const void* ln_bias, void* output, void* w1_out, void* b1_out, void* w2_out,
                     void* b2_out, void* status, void* stream);
 
+/* One mini-batch of fewer than (or exactly) mini_batch tokens: the tail of a sequence whose length is not a multiple
+ * of the mini-batch, and the 1-token decode step.  Semantics: the reference's `TTTInnerModel::forward` calls
+ * `forward_mini_batch` once on the remainder, i.e. the remainder is a mini-batch of its own length
+ * (rust/core/src/inner.rs:25-50, rust/core/src/linear.rs:91-149); the reference's fused kernels reject such shapes
+ * (rust/fused/src/linear_fused_tile/wrapper.rs:152-172), its unfused path computes them.
+ *   d->seq_len = r, 1 <= r <= 16 (d->mini_batch and d->checkpoint_interval are not read); tensors as in
+ *   ttt_linear_forward with T = r; token_eta holds the r coefficients of these positions.  Forward only: nothing is
+ *   saved for a backward.  weight_out / bias_out may alias weight / bias (state advanced in place).
+ */
+int ttt_linear_forward_partial(const ttt_dims* d, const void* xq, const void* xk, const void* xv, const void* weight,
+                               const void* bias, const void* token_eta, const void* ttt_lr_eta,
+                               const void* ln_weight, const void* ln_bias, void* output, void* weight_out,
+                               void* bias_out, void* stream);
+
 /* ---- outer-layer steps on either side of the inner loop -------------------------------------------------------
  * These two entry points replace the tensor-op chains of the reference's `TTT` layer around `inner.forward`
  * (rust/layer/src/ttt.rs): `get_qkv` :152-197 (reshape + permute to [B,H,T,F], shared-QK causal convolutions

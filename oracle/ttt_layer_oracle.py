@@ -102,7 +102,7 @@ def ttt_layer_forward(x, p: Dict[str, torch.Tensor], *, num_heads: int, mini_bat
                                         rope_theta=rope_theta, share_qk=share_qk, start_idx=start_idx)
     if state is None:
         state = {"weight": p["W1"].unsqueeze(0).repeat(B, 1, 1, 1), "bias": p["b1"].reshape(1, H, -1).repeat(B, 1, 1)}
-    r = O.ttt_linear_forward(xq, xk, xv, state["weight"], state["bias"], te, lr, p["ttt_norm_weight"],
-                             p["ttt_norm_bias"], mini_batch=mini_batch, eps=1e-6)
+    r = O.ttt_linear_forward_any_length(xq, xk, xv, state["weight"], state["bias"], te, lr, p["ttt_norm_weight"],
+                                        p["ttt_norm_bias"], mini_batch=mini_batch, eps=1e-6)
     y = layer_epilogue(r["output"], x, p, use_gate=use_gate)
     return y @ p["o_proj"].T, {"weight": r["weight"], "bias": r["bias"]}

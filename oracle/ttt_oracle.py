@@ -151,6 +151,29 @@ def ttt_linear_forward(
 # TTT-Linear analytic backward
 # --------------------------------------------------------------------------
 
+def ttt_linear_forward_any_length(xq, xk, xv, weight, bias, token_eta, ttt_lr_eta, ln_weight, ln_bias,
+                                  mini_batch: int = 16, eps: float = 1e-6) -> Dict[str, torch.Tensor]:
+    """Sequences whose length is not a multiple of the mini-batch, as the inner-model trait's default `forward`
+    handles them (rust/core/src/inner.rs:25-50): the whole mini-batches first, then ONE `forward_mini_batch` on the
+    remainder, which is thereby a mini-batch of its own length with eta[i][j] = token_eta[L+i] * lr[L+j].
+    A 1-token call (decode) is the case L = 0, remainder 1.  Returns dict(output, weight, bias)."""
+    T = xq.shape[2]
+    L = (T // mini_batch) * mini_batch
+    outs = []
+    W, b = weight, bias
+    if L > 0:
+        r = ttt_linear_forward(xq[:, :, :L], xk[:, :, :L], xv[:, :, :L], W, b, token_eta[:L], ttt_lr_eta[:, :, :L],
+                               ln_weight, ln_bias, mini_batch=mini_batch, eps=eps)
+        outs.append(r["output"])
+        W, b = r["weight"], r["bias"]
+    if T > L:
+        r = ttt_linear_forward(xq[:, :, L:], xk[:, :, L:], xv[:, :, L:], W, b, token_eta[L:T], ttt_lr_eta[:, :, L:],
+                               ln_weight, ln_bias, mini_batch=T - L, eps=eps)
+        outs.append(r["output"])
+        W, b = r["weight"], r["bias"]
+    return {"output": torch.cat(outs, dim=2), "weight": W, "bias": b}
+
+
 def _stage_states(xk, xv, weight, bias, te, lr_s, g_, be_, cs, eps):
     """Re-simulate the state (W_s, b_s) seen at the start of every stage."""
     B, H, T, F = xk.shape

@@ -533,3 +533,41 @@ extern "C" int ttt_layer_epilogue(const ttt_dims* d, const void* inner_out, cons
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "layer epilogue launch failed: %s", cudaGetErrorString(e));
   return TTT_OK;
 }
+
+extern "C" int ttt_linear_forward_partial(const ttt_dims* d, const void* xq, const void* xk, const void* xv,
+                                          const void* weight, const void* bias, const void* token_eta,
+                                          const void* ttt_lr_eta, const void* ln_weight, const void* ln_bias,
+                                          void* output, void* weight_out, void* bias_out, void* stream) {
+  if (d == nullptr) return fail(TTT_ERR_NULL, "dims is null");
+  if (d->batch <= 0 || d->heads <= 0) return fail(TTT_ERR_SHAPE, "batch and heads must be positive");
+  if (d->dtype != TTT_F32 && d->dtype != TTT_BF16) return fail(TTT_ERR_UNSUPPORTED, "unknown dtype %d", d->dtype);
+  if (d->head_dim != 64) return fail(TTT_ERR_UNSUPPORTED, "Unsupported head_dim=%d (supported: 64)", d->head_dim);
+  if (d->seq_len < 1 || d->seq_len > 16)
+    return fail(TTT_ERR_SHAPE, "a partial mini-batch has 1..16 tokens (got seq_len=%d)", d->seq_len);
+  if (!(d->epsilon >= 0.f)) return fail(TTT_ERR_SHAPE, "epsilon must be >= 0");
+  const NamedPtr ptrs[] = {{"xq", xq},         {"xk", xk},         {"xv", xv},
+                           {"weight", weight}, {"bias", bias},     {"token_eta", token_eta},
+                           {"ttt_lr_eta", ttt_lr_eta}, {"ln_weight", ln_weight}, {"ln_bias", ln_bias},
+                           {"output", output}, {"weight_out", weight_out}, {"bias_out", bias_out}};
+  for (const NamedPtr& np : ptrs)
+    if (np.p == nullptr) return fail(TTT_ERR_NULL, "%s is null", np.name);
+  ttt::LinPartialParams p;
+  p.xq = xq;
+  p.xk = xk;
+  p.xv = xv;
+  p.w0 = weight;
+  p.b0 = bias;
+  p.token_eta = token_eta;
+  p.lr = ttt_lr_eta;
+  p.ln_g = ln_weight;
+  p.ln_b = ln_bias;
+  p.out = output;
+  p.w_out = weight_out;
+  p.b_out = bias_out;
+  p.H = d->heads;
+  p.R = d->seq_len;
+  p.eps = d->epsilon;
+  cudaError_t e = ttt::launch_linear_partial(d->dtype, p, d->batch * d->heads, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "partial forward launch failed: %s", cudaGetErrorString(e));
+  return TTT_OK;
+}

@@ -113,6 +113,25 @@ struct LayerEpiParams {
 cudaError_t launch_layer_prologue(int dtype, const LayerProParams& p, cudaStream_t st);
 cudaError_t launch_layer_epilogue(int dtype, const LayerEpiParams& p, cudaStream_t st);
 
+// One mini-batch of R <= 16 tokens per stream (decode step, sequence tail): ttt_linear_partial.cu.
+struct LinPartialParams {
+  const void* xq;  // [B,H,R,F]
+  const void* xk;
+  const void* xv;
+  const void* w0;         // [B,H,F,F]
+  const void* b0;         // [B,H,F]
+  const void* token_eta;  // [R]
+  const void* lr;         // [B,H,R]
+  const void* ln_g;       // [H,F]
+  const void* ln_b;
+  void* out;              // [B,H,R,F]
+  void* w_out;            // may alias w0
+  void* b_out;            // may alias b0
+  int H, R;
+  float eps;
+};
+cudaError_t launch_linear_partial(int dtype, const LinPartialParams& p, int nstreams, cudaStream_t st);
+
 // bf16 only.  maps: q, k, v, out.
 cudaError_t launch_mlp_fwd(const CUtensorMap* maps, const MlpFwdParams& p, int nstreams, cudaStream_t st);
 

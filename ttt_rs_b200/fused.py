@@ -188,6 +188,28 @@ class TttTileMultiKernel:
         return TttOutputs(output, weight_out, bias_out), saved
 
     @staticmethod
+    def forward_partial(inputs: TttInputs, config: FusedTttConfig, in_place: bool = False) -> TttOutputs:
+        """One mini-batch of 1..16 tokens (sequence tail, decode step): `ttt_linear_forward_partial`.  Forward only.
+        With `in_place` the state tensors of `inputs` are advanced and returned."""
+        lib = _lib.load()
+        inputs = inputs.map(lambda t: t.contiguous())
+        d = _dims(inputs.xq, config)
+        _check_inputs(inputs)
+        T = inputs.xq.shape[2]
+        if inputs.token_eta.shape[0] < T:
+            raise TttError(_lib.TTT_ERR_SHAPE, "token_eta must hold one entry per token of the partial mini-batch")
+        dev = inputs.xq.device
+        output = torch.empty_like(inputs.xq)
+        weight_out = inputs.weight if in_place else torch.empty_like(inputs.weight)
+        bias_out = inputs.bias if in_place else torch.empty_like(inputs.bias)
+        with torch.cuda.device(dev):
+            _lib.check(lib.ttt_linear_forward_partial(
+                C.byref(d), _ptr(inputs.xq), _ptr(inputs.xk), _ptr(inputs.xv), _ptr(inputs.weight),
+                _ptr(inputs.bias), _ptr(inputs.token_eta), _ptr(inputs.ttt_lr_eta), _ptr(inputs.ln_weight),
+                _ptr(inputs.ln_bias), _ptr(output), _ptr(weight_out), _ptr(bias_out), _stream_ptr(dev)))
+        return TttOutputs(output, weight_out, bias_out)
+
+    @staticmethod
     def backward_launch(saved: TttSavedStateMulti, grad_outputs: TttOutputs, config: FusedTttConfig,
                         outer_grad_packed: Optional[torch.Tensor] = None, use_state_grads: bool = False) -> TttInputs:
         """Gradients w.r.t. the nine inputs, in input order.  By default only `grad_outputs.output` is used: upstream
@@ -327,9 +349,13 @@ class TTTLinear(torch.nn.Module):
 class FusedTileMultiTTTLinear(torch.nn.Module):
     """`fused-tile-multi` inner model: whole-sequence forward in a single launch."""
 
-    def __init__(self, inner: TTTLinear):
+    def __init__(self, inner: TTTLinear, allow_partial: bool = False):
+        """`allow_partial`: run a remainder / decode mini-batch (fewer tokens than the mini-batch) through the
+        partial-mini-batch kernel, with the semantics of the reference's unfused inner model, instead of refusing it
+        as the reference's fused type does.  Inference only (no gradient is recorded for such a call)."""
         super().__init__()
         self.inner = inner
+        self.allow_partial = allow_partial
 
     @staticmethod
     def name() -> str:
@@ -361,7 +387,17 @@ class FusedTileMultiTTTLinear(torch.nn.Module):
 
     def forward_mini_batch(self, state: TTTLinearState, inputs: TTTInputsInner, r: range) -> torch.Tensor:
         if len(r) != self.inner.mini_batch_size:
-            raise AssertionError("Sequence length must be equal to mini_batch_size")
+            if not self.allow_partial or not 0 < len(r) < self.inner.mini_batch_size:
+                raise AssertionError("Sequence length must be equal to mini_batch_size")
+            if torch.is_grad_enabled():
+                raise RuntimeError("a partial mini-batch runs forward only: call it under torch.no_grad()")
+            sl = inputs.slice_seq(r)
+            F = sl.qkv.xq.shape[-1]
+            outs = TttTileMultiKernel.forward_partial(
+                TttInputs(sl.qkv.xq, sl.qkv.xk, sl.qkv.xv, state.weight, state.bias, sl.token_eta, sl.ttt_lr_eta,
+                          self.inner.ln_weight.detach(), self.inner.ln_bias.detach()), self._config(F))
+            state.weight, state.bias = outs.weight, outs.bias
+            return outs.output
         sl = inputs.slice_seq(r)
         F = sl.qkv.xq.shape[-1]
         cfg = self._config(F).with_checkpoint_interval(1)

@@ -102,3 +102,27 @@ def alloc_host_outputs(B: int, H: int, T: int, F: int, dtype: torch.dtype, backw
                    grad_ttt_lr_eta=pin(B, H, T), grad_weight=pin(B, H, F, F), grad_bias=pin(B, H, F),
                    grad_token_eta=pin(T), grad_ln_weight=pin(H, F), grad_ln_bias=pin(H, F))
     return out
+
+
+def bind_host_thread_near(device: torch.device):
+    """Restrict this process to the CPUs of the NUMA node the GPU hangs off, so that pinned buffers allocated
+    afterwards land in that node's memory and host<->device copies of several ranks do not all cross one socket.
+    Returns the node number, or None when the topology cannot be read (then nothing is changed)."""
+    import os
+    try:
+        pr = torch.cuda.get_device_properties(device)
+        bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read().strip())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return node
+    except (OSError, ValueError, AttributeError):
+        return None

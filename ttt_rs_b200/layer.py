@@ -204,7 +204,9 @@ class TTT(torch.nn.Module):
         return torch.matmul(y, self.o_proj.t())
 
 
-def new_inner(config: TTTLayerConfig, checkpoint_interval: int = 1, device=None, dtype=torch.float32):
-    """The `fused-tile-multi` inner model matching a layer config."""
+def new_inner(config: TTTLayerConfig, checkpoint_interval: int = 1, device=None, dtype=torch.float32,
+              allow_partial: bool = False):
+    """The `fused-tile-multi` inner model matching a layer config (`allow_partial`: also accept sequence tails and
+    1-token decode steps, see FusedTileMultiTTTLinear)."""
     return FusedTileMultiTTTLinear(TTTLinear(config.num_heads, config.head_dim, config.mini_batch_size, 1e-6,
-                                             checkpoint_interval, device=device, dtype=dtype))
+                                             checkpoint_interval, device=device, dtype=dtype), allow_partial)
