@@ -58,6 +58,11 @@ WORKLOADS = {
                           desc="TTT layer forward (hidden 768, 12 heads x 64), bf16, B=32 T=2048 mb=16"),
     "layer-fwd-1b3": dict(kind="layer", B=8, H=32, T=8192, dtype="bf16", K=1, backward=False,
                           desc="TTT layer forward (1.3B layer shape: hidden 2048, 32 heads x 64), bf16, B=8 T=8192 mb=16"),
+    # one decode step of the inner model (a mini-batch of one token per stream, state advanced in place)
+    "decode": dict(kind="decode", B=8, H=12, T=1, dtype="bf16", K=1, backward=False,
+                   desc="TTT-Linear inner model decode step (1 token per stream), bf16, B=8 H=12 d=64"),
+    "decode-b256": dict(kind="decode", B=256, H=12, T=1, dtype="bf16", K=1, backward=False,
+                        desc="TTT-Linear inner model decode step (1 token per stream), bf16, B=256 H=12 d=64"),
 }
 F, CS = 64, 16
 
@@ -300,6 +305,82 @@ def run_layer(args, w):
     print(json.dumps(line), flush=True)
 
 
+def run_decode(args, w):
+    """One-token steps of the inner model through `ttt_linear_forward_partial`, state resident and advanced in place.
+    Algorithmic HBM bytes per step: the state is read and written once (2 (F^2 + F) s per stream) plus the token's
+    q, k, v, output rows and lr (4 F s + s)."""
+    import ttt_rs_b200 as tb
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operator has no CPU path")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    tb.load_library()
+    from ttt_rs_b200.synthetic import make_inputs
+    B, H = w["B"], w["H"]
+    t = make_inputs(B, H, 16, F, CS, seed=0, dtype=torch.bfloat16, with_grad_output=False)
+    d = {k: v.to(dev) for k, v in t.items()}
+    cfg = tb.FusedTttConfig.new(CS, F, 1e-6, 128, 1)
+    ins = tb.TttInputs(d["xq"][:, :, :1].contiguous(), d["xk"][:, :, :1].contiguous(), d["xv"][:, :, :1].contiguous(),
+                       d["weight"], d["bias"], d["token_eta"][:1].contiguous(), d["ttt_lr_eta"][:, :, :1].contiguous(),
+                       d["ln_weight"], d["ln_bias"])
+    tb.TttTileMultiKernel.forward_partial(ins, cfg, in_place=True)  # the public call, once (validates the operands)
+    # the timed loop binds the same C-ABI call with prebuilt arguments: the host-side cost of a step is then the
+    # foreign call alone, as it would be from the reference's Rust host
+    import ctypes as C
+    from ttt_rs_b200 import _lib
+    lib = _lib.load()
+    dd = _lib.TttDims(B, H, 1, F, CS, 1, float(cfg.epsilon()), _lib.TTT_BF16)
+    out = torch.empty_like(ins.xq)
+    ptr = lambda x: C.c_void_p(x.data_ptr())  # noqa: E731
+    cargs = [C.byref(dd)] + [ptr(x) for x in (ins.xq, ins.xk, ins.xv, ins.weight, ins.bias, ins.token_eta,
+                                                ins.ttt_lr_eta, ins.ln_weight, ins.ln_bias, out, ins.weight, ins.bias)]
+    cargs.append(C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+
+    def one():
+        rc = lib.ttt_linear_forward_partial(*cargs)
+        if rc != 0:
+            raise RuntimeError(_lib.last_error())
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms = time_events(one, max(args.steps, 200), args.warmup)
+    clocks = sampler.stop()
+    peak, peak_kind = measured_peaks()
+    s = 2
+    nbytes = B * H * (2 * (F * F + F) * s + 4 * F * s + s)
+    ach = nbytes / (ms * 1e-3) / 1e9
+    line = {
+        "metric": "ttt_inner_decode_tokens_per_sec", "value": B / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": max(args.steps, 200), "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": w["desc"], "global_batch": B,
+                   "l2": "state of all streams: %.1f MB (L2-resident below 126 MB: the figure is an L2/launch-latency "
+                         "number, not an HBM number)" % (B * H * (F * F + F) * s / 1e6)},
+        "clocks": clocks, "e2e": None, "gpu_launches": max(args.steps, 200),
+        "roofline": {"bound": "hbm", "kernel": "ttt_linear_partial_kernel", "achieved": ach, "peak": peak,
+                     "unit": "GB/s", "frac": ach / peak, "traffic": None, "peak_source": f"of {peak_kind}",
+                     "algorithmic_bytes_per_launch": nbytes},
+    }
+    if not args.no_cpu_baseline:
+        from oracle import ttt_oracle as O
+        torch.set_num_threads(os.cpu_count() or 1)
+        names = LIN_IN
+        c = {k: t[k].float() for k in names}
+        for k in ("xq", "xk", "xv", "ttt_lr_eta"):
+            c[k] = c[k][:, :, :1]
+        sb = min(B, 32)
+        c = {k: (v[:sb] if v.dim() >= 3 else v) for k, v in c.items()}
+        O.ttt_linear_forward(*[c[k] for k in names], mini_batch=1)
+        t0 = time.perf_counter()
+        n = 20
+        for _ in range(n):
+            O.ttt_linear_forward(*[c[k] for k in names], mini_batch=1)
+        dtc = (time.perf_counter() - t0) / n
+        line["cpu_baseline"] = {"value": sb / dtc, "unit": "tokens/s", "cores": torch.get_num_threads(),
+                                "kind": "port", "sample": f"B={sb} slice, float32, {n} steps"}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -313,6 +394,11 @@ def main():
     w = WORKLOADS[args.workload]
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
+    if w.get("kind") == "decode":
+        if args.impl == "reference":
+            raise SystemExit("--impl reference is defined for the inner-loop workloads")
+        run_decode(args, w)
+        return
     if w.get("kind") == "layer":
         if args.impl == "reference":
             raise SystemExit("--impl reference is defined for the inner-loop workloads")

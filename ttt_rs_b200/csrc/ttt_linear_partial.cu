@@ -25,10 +25,11 @@ struct PartialSmem {
 };
 
 // Sums over the 64 columns (threads) of two values per row, for rows < r.  Every thread gets the totals.
-__device__ __forceinline__ void row_sums(PartialSmem& sm, int r, int tid, float (&a)[CS], float (&b)[CS]) {
+template <int RM>
+__device__ __forceinline__ void row_sums(PartialSmem& sm, int r, int tid, float (&a)[RM], float (&b)[RM]) {
   const int warp = tid >> 5, lane = tid & 31;
 #pragma unroll
-  for (int i = 0; i < CS; ++i) {
+  for (int i = 0; i < RM; ++i) {
     if (i < r) {
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
@@ -43,7 +44,7 @@ __device__ __forceinline__ void row_sums(PartialSmem& sm, int r, int tid, float 
   }
   __syncthreads();
 #pragma unroll
-  for (int i = 0; i < CS; ++i) {
+  for (int i = 0; i < RM; ++i) {
     if (i < r) {
       a[i] = sm.red[0][i][0] + sm.red[1][i][0];
       b[i] = sm.red[0][i][1] + sm.red[1][i][1];
@@ -52,7 +53,9 @@ __device__ __forceinline__ void row_sums(PartialSmem& sm, int r, int tid, float 
   __syncthreads();  // red may be reused
 }
 
-template <typename T>
+// RM: compile-time bound on the number of rows (1 for the decode step, 4, or 16), so that short mini-batches do not
+// pay for sixteen rows of predicated-off arithmetic.
+template <typename T, int RM>
 __global__ void __launch_bounds__(PT_THREADS) ttt_linear_partial_kernel(const LinPartialParams p) {
   __shared__ PartialSmem sm;
   const int n = threadIdx.x;
@@ -89,9 +92,9 @@ __global__ void __launch_bounds__(PT_THREADS) ttt_linear_partial_kernel(const Li
   }
 
   // Z1 = K W + b and Zq = Q W + b, column n
-  float z1[CS], zq[CS];
+  float z1[RM], zq[RM];
 #pragma unroll
-  for (int i = 0; i < CS; ++i) {
+  for (int i = 0; i < RM; ++i) {
     z1[i] = zq[i] = bias;
     if (i < r) {
 #pragma unroll
@@ -103,24 +106,24 @@ __global__ void __launch_bounds__(PT_THREADS) ttt_linear_partial_kernel(const Li
   }
 
   // LayerNorm statistics of Z1 (two-pass variance), then G = dL/dZ1
-  float a[CS], b2[CS], mean[CS], rstd[CS];
+  float a[RM], b2[RM], mean[RM], rstd[RM];
 #pragma unroll
-  for (int i = 0; i < CS; ++i) {
+  for (int i = 0; i < RM; ++i) {
     a[i] = z1[i];
     b2[i] = 0.f;
   }
-  row_sums(sm, r, n, a, b2);
+  row_sums<RM>(sm, r, n, a, b2);
 #pragma unroll
-  for (int i = 0; i < CS; ++i) {
+  for (int i = 0; i < RM; ++i) {
     mean[i] = a[i] * (1.f / HD);
     const float d = z1[i] - mean[i];
     a[i] = d * d;
     b2[i] = 0.f;
   }
-  row_sums(sm, r, n, a, b2);
-  float xh[CS], gx[CS], g[CS];
+  row_sums<RM>(sm, r, n, a, b2);
+  float xh[RM], gx[RM], g[RM];
 #pragma unroll
-  for (int i = 0; i < CS; ++i) {
+  for (int i = 0; i < RM; ++i) {
     rstd[i] = 1.f / sqrtf(a[i] * (1.f / HD) + p.eps);
     xh[i] = (z1[i] - mean[i]) * rstd[i];
     const float tgt = (i < r) ? sm.v[i][n] - sm.k[i][n] : 0.f;
@@ -128,35 +131,35 @@ __global__ void __launch_bounds__(PT_THREADS) ttt_linear_partial_kernel(const Li
     a[i] = gx[i];
     b2[i] = gx[i] * xh[i];
   }
-  row_sums(sm, r, n, a, b2);
+  row_sums<RM>(sm, r, n, a, b2);
 #pragma unroll
-  for (int i = 0; i < CS; ++i)
+  for (int i = 0; i < RM; ++i)
     g[i] = (i < r) ? (gx[i] - a[i] * (1.f / HD) - xh[i] * b2[i] * (1.f / HD)) * rstd[i] : 0.f;
 
   // Zbar = Zq - sum_{j<=i} te[i] lr[j] (1 + Attn[i][j]) G[j];  out = Q + LN(Zbar)
 #pragma unroll
-  for (int i = 0; i < CS; ++i) {
+  for (int i = 0; i < RM; ++i) {
     if (i < r) {
       float s = 0.f;
 #pragma unroll
-      for (int j = 0; j < CS; ++j)
+      for (int j = 0; j < RM; ++j)
         if (j <= i && j < r) s = fmaf(sm.lr[j] * (1.f + sm.attn[i][j]), g[j], s);
       zq[i] -= sm.te[i] * s;
     }
     a[i] = zq[i];
     b2[i] = 0.f;
   }
-  row_sums(sm, r, n, a, b2);
+  row_sums<RM>(sm, r, n, a, b2);
 #pragma unroll
-  for (int i = 0; i < CS; ++i) {
+  for (int i = 0; i < RM; ++i) {
     mean[i] = a[i] * (1.f / HD);
     const float d = zq[i] - mean[i];
     a[i] = d * d;
     b2[i] = 0.f;
   }
-  row_sums(sm, r, n, a, b2);
+  row_sums<RM>(sm, r, n, a, b2);
 #pragma unroll
-  for (int i = 0; i < CS; ++i) {
+  for (int i = 0; i < RM; ++i) {
     if (i < r) {
       const float rs = 1.f / sqrtf(a[i] * (1.f / HD) + p.eps);
       st_from_float<T>(p.out, (row0 + i) * HD + n, sm.q[i][n] + gam * (zq[i] - mean[i]) * rs + bet);
@@ -165,11 +168,11 @@ __global__ void __launch_bounds__(PT_THREADS) ttt_linear_partial_kernel(const Li
 
   // state update with the last row of eta: W -= (te[r-1] lr o K)^T G,  b -= sum_j te[r-1] lr[j] G[j]
   const float te_last = sm.te[r - 1];
-  float gl[CS];
+  float gl[RM];
 #pragma unroll
-  for (int j = 0; j < CS; ++j) gl[j] = (j < r) ? te_last * sm.lr[j] * g[j] : 0.f;
+  for (int j = 0; j < RM; ++j) gl[j] = (j < r) ? te_last * sm.lr[j] * g[j] : 0.f;
 #pragma unroll
-  for (int j = 0; j < CS; ++j) {
+  for (int j = 0; j < RM; ++j) {
     if (j < r) {
       bias -= gl[j];
 #pragma unroll
@@ -182,10 +185,21 @@ __global__ void __launch_bounds__(PT_THREADS) ttt_linear_partial_kernel(const Li
 }
 
 cudaError_t launch_linear_partial(int dtype, const LinPartialParams& p, int nstreams, cudaStream_t st) {
-  if (dtype == 1)
-    ttt_linear_partial_kernel<__nv_bfloat16><<<nstreams, PT_THREADS, 0, st>>>(p);
-  else
-    ttt_linear_partial_kernel<float><<<nstreams, PT_THREADS, 0, st>>>(p);
+  if (dtype == 1) {
+    if (p.R == 1)
+      ttt_linear_partial_kernel<__nv_bfloat16, 1><<<nstreams, PT_THREADS, 0, st>>>(p);
+    else if (p.R <= 4)
+      ttt_linear_partial_kernel<__nv_bfloat16, 4><<<nstreams, PT_THREADS, 0, st>>>(p);
+    else
+      ttt_linear_partial_kernel<__nv_bfloat16, 16><<<nstreams, PT_THREADS, 0, st>>>(p);
+  } else {
+    if (p.R == 1)
+      ttt_linear_partial_kernel<float, 1><<<nstreams, PT_THREADS, 0, st>>>(p);
+    else if (p.R <= 4)
+      ttt_linear_partial_kernel<float, 4><<<nstreams, PT_THREADS, 0, st>>>(p);
+    else
+      ttt_linear_partial_kernel<float, 16><<<nstreams, PT_THREADS, 0, st>>>(p);
+  }
   return cudaGetLastError();
 }
 
