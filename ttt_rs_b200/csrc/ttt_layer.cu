@@ -60,7 +60,7 @@ struct Vec8<float> {
 };
 
 constexpr int PRO_THREADS = 256;
-constexpr int PRO_TCHUNK = 64;   // tokens per warp task
+constexpr int PRO_TCHUNK = 32;   // tokens per warp task
 constexpr int PRO_MAXK = 4;      // causal convolution taps supported
 constexpr int PRO_MAXPOS = 64;   // rotary table rows (positions modulo the mini-batch length)
 
@@ -322,11 +322,16 @@ __global__ void __launch_bounds__(EPI_THREADS, (MAXCH <= 4 ? 4 : 2)) ttt_layer_e
         const int ch = j * 32 + lane;
         if (ch < nch) {
           const int c0 = ch * EPC;
-          float y[EPC];
+          float y[EPC], gq[EPC], bq[EPC];
+#pragma unroll
+          for (int e = 0; e < EPC; e += 4) {
+            const float4 g4 = *reinterpret_cast<const float4*>(gam + c0 + e), b4 = *reinterpret_cast<const float4*>(bet + c0 + e);
+            gq[e] = g4.x; gq[e + 1] = g4.y; gq[e + 2] = g4.z; gq[e + 3] = g4.w;
+            bq[e] = b4.x; bq[e + 1] = b4.y; bq[e + 2] = b4.z; bq[e + 3] = b4.w;
+          }
 #pragma unroll
           for (int k = 0; k < NPAIR; ++k) {
-            const F2 g2 = *reinterpret_cast<const F2*>(gam + c0 + 2 * k), b2 = *reinterpret_cast<const F2*>(bet + c0 + 2 * k);
-            const F2 o = f2fma(v[j][k], f2mul(g2, f2(rstd)), b2);
+            const F2 o = f2fma(v[j][k], f2mul(f2(gq[2 * k], gq[2 * k + 1]), f2(rstd)), f2(bq[2 * k], bq[2 * k + 1]));
             y[2 * k] = o.x;
             y[2 * k + 1] = o.y;
           }
