@@ -114,3 +114,47 @@ def test_cpp_host_mirror_compiles(tmp_path):
                        capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
     assert subprocess.run([str(exe)]).returncode == 0
+
+
+def test_partial_and_layer_entry_points_validate_their_arguments(lib):
+    """Argument checks of the entry points around the main path; all fail before anything touches the device."""
+    fake = C.c_void_p(0x1000)
+    # partial mini-batch: 1..16 tokens, head_dim 64
+    for seq, code in ((0, _lib.TTT_ERR_SHAPE), (17, _lib.TTT_ERR_SHAPE)):
+        assert lib.ttt_linear_forward_partial(C.byref(_dims(seq_len=seq)), *([fake] * 12), None) == code
+    assert lib.ttt_linear_forward_partial(C.byref(_dims(seq_len=3, head_dim=32)), *([fake] * 12), None) == \
+        _lib.TTT_ERR_UNSUPPORTED
+    args = [fake] * 12
+    args[9] = None
+    assert lib.ttt_linear_forward_partial(C.byref(_dims(seq_len=3)), *args, None) == _lib.TTT_ERR_NULL
+    assert "output" in _lib.last_error()
+
+    # layer prologue
+    d = _dims(seq_len=37)  # need not be a multiple of the mini-batch here
+
+    def pro(src_ld=128, lr_ld=8, conv=(None, None, None, None), kc=0, start=0, mode=1, theta=10000.0, q=fake):
+        return lib.ttt_layer_prologue(C.byref(d), q, fake, fake, src_ld, fake, lr_ld, None, *conv, kc, start, mode,
+                                      theta, 1.0, fake, fake, fake, fake, None)
+
+    assert pro(src_ld=120) == _lib.TTT_ERR_SHAPE          # narrower than heads * 64
+    assert pro(src_ld=132) == _lib.TTT_ERR_SHAPE          # rows would lose 16-byte alignment
+    assert pro(lr_ld=1) == _lib.TTT_ERR_SHAPE
+    assert pro(mode=3) == _lib.TTT_ERR_UNSUPPORTED
+    assert pro(theta=0.0) == _lib.TTT_ERR_SHAPE
+    assert pro(start=-1) == _lib.TTT_ERR_SHAPE
+    assert pro(conv=(fake, fake, fake, None), kc=4) == _lib.TTT_ERR_NULL
+    assert pro(conv=(fake, fake, fake, fake), kc=5) == _lib.TTT_ERR_UNSUPPORTED
+    assert pro(q=C.c_void_p(0x1004)) == _lib.TTT_ERR_ALIGN
+    assert lib.ttt_layer_prologue(C.byref(_dims(head_dim=32)), *([fake] * 3), 128, fake, 8, *([None] * 5), 0, 0, 1,
+                                  10000.0, 1.0, fake, fake, fake, fake, None) == _lib.TTT_ERR_UNSUPPORTED
+
+    # layer epilogue
+    def epi(dd=d, gate=None, gate_ld=0, w=fake, eps=1e-6):
+        return lib.ttt_layer_epilogue(C.byref(dd), fake, gate, gate_ld, w, fake, eps, fake, None)
+
+    assert epi(w=None) == _lib.TTT_ERR_NULL
+    assert epi(gate=fake, gate_ld=64) == _lib.TTT_ERR_SHAPE
+    assert epi(gate=fake, gate_ld=130) == _lib.TTT_ERR_SHAPE
+    assert epi(gate=C.c_void_p(0x1004), gate_ld=128) == _lib.TTT_ERR_ALIGN
+    assert epi(dd=_dims(heads=33)) == _lib.TTT_ERR_UNSUPPORTED
+    assert epi(eps=-1.0) == _lib.TTT_ERR_SHAPE
