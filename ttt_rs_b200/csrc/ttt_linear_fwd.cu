@@ -16,12 +16,15 @@
 //   * Row statistics for the two LayerNorms are warp-shuffle reduced and exchanged across the 4 warps through
 //     512 bytes of shared memory; G reaches the tensor cores as an A/B operand through movmatrix.
 //   * Output tiles leave through a double-buffered staging tile and a TMA store.
+#include <type_traits>
+
 #include "ttt_kernels.h"
 #include "ttt_stage.cuh"
 
 namespace ttt {
 
-constexpr int FWD_NST = 3;  // TMA pipeline depth (stages in flight)
+constexpr int FWD_NST = 3;  // TMA pipeline depth (stages in flight); the stage loop is unrolled by it
+static_assert(FWD_NST == 3, "the stage loop below is written out for three slots");
 
 template <typename T>
 struct FwdSmem {
@@ -118,8 +121,10 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
   int xsel = 0;
   bool failed = false;
 
-  for (int s = 0; s < NS; ++s) {
-    const int slot = s % FWD_NST;
+  // One stage with its ring slot known at compile time, so every shared-memory address is a hoisted lane offset plus
+  // an immediate.  Returns false after a timed-out wait.
+  auto stage = [&](const int s, auto slot_tag) -> bool {
+    constexpr int slot = decltype(slot_tag)::value;
     const uint32_t tq = base + slot * SM::SLOT, tk = tq + TF::BYTES, tv = tk + TF::BYTES;
     const uint32_t pq = tq + TF::PLANE_OFF, pk = tk + TF::PLANE_OFF;
     int fail = mbar_wait_bounded(bar0 + 8 * slot, (s / FWD_NST) & 1) ? 0 : 1;
@@ -132,7 +137,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
       if (fail) {
         failed = true;
         if (tid == 0) report_timeout(p.status, 1, s);
-        break;
+        return false;
       }
     }
 
@@ -197,7 +202,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     if (fail) {
       failed = true;
       if (tid == 0) report_timeout(p.status, 2, s);
-      break;
+      return false;
     }
     F2 gp[2][2];
     float4 st1[2];  // saved row statistics of Z1: (mean, rstd, mean(gx), mean(gx * x_hat))
@@ -294,6 +299,12 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
       bulk_wait_read<1>();
       if (s + FWD_NST < NS) issue_loads(s + FWD_NST);
     }
+    return true;
+  };
+  for (int s0 = 0; s0 < NS; s0 += FWD_NST) {
+    if (!stage(s0, std::integral_constant<int, 0>{})) break;
+    if (s0 + 1 < NS && !stage(s0 + 1, std::integral_constant<int, 1>{})) break;
+    if (s0 + 2 < NS && !stage(s0 + 2, std::integral_constant<int, 2>{})) break;
   }
 
   if (!failed) {
