@@ -199,6 +199,31 @@ int ttt_layer_prologue(const ttt_dims* d, const void* q_src, const void* k_src, 
 int ttt_layer_epilogue(const ttt_dims* d, const void* inner_out, const void* gate, int64_t gate_ld,
                        const void* post_norm_weight, const void* post_norm_bias, float eps, void* y, void* stream);
 
+/* Gradients of the two layer steps (training; the reference gets them from Burn autodiff over the same tensor ops).
+ *
+ * ttt_layer_prologue_backward: gradients of XQ, XK, XV [B,H,T,F] and of ttt_lr_eta [B,H,T] -> gradient of the
+ * projection output: grad_q_dst / grad_k_dst / grad_v_dst are its H*F-column blocks ([B*T, dst_ld]; inverse rotation
+ * applied to q and k), grad_lr_logits its logit columns ([B*T, lr_ld]; `lr_cols` >= H columns are written, the ones
+ * after the first H with zeros, so that padding columns of a fused projection are defined).  `ttt_lr_eta` is the
+ * forward's output.  The shared-QK convolution layout has no backward here (TTT_ERR_UNSUPPORTED is not needed:
+ * there is simply no convolution argument); its weights' gradients are not produced by this library.
+ *
+ * ttt_layer_epilogue_backward: grad_y [B*T, H*F] -> grad_inner_out [B,H,T,F], grad_gate ([B*T, grad_gate_ld], only
+ * with a gate) and float32 grad_post_norm_weight / grad_post_norm_bias [H*F] (written, summed over all tokens in a
+ * fixed order).  `workspace` must hold ttt_layer_epilogue_backward_workspace_bytes(d) bytes.
+ */
+int ttt_layer_prologue_backward(const ttt_dims* d, const void* grad_xq, const void* grad_xk, const void* grad_xv,
+                                const void* grad_ttt_lr_eta, const void* ttt_lr_eta, int start_idx, int rope_mode,
+                                float rope_theta, float base_lr, void* grad_q_dst, void* grad_k_dst,
+                                void* grad_v_dst, int64_t dst_ld, void* grad_lr_logits, int64_t lr_ld, int lr_cols,
+                                void* stream);
+size_t ttt_layer_epilogue_backward_workspace_bytes(const ttt_dims* d);
+int ttt_layer_epilogue_backward(const ttt_dims* d, const void* grad_y, const void* inner_out, const void* gate,
+                                int64_t gate_ld, const void* post_norm_weight, const void* post_norm_bias,
+                                float eps, void* grad_inner_out, void* grad_gate, int64_t grad_gate_ld,
+                                float* grad_post_norm_weight, float* grad_post_norm_bias, void* workspace,
+                                size_t workspace_bytes, void* stream);
+
 /* Backward without a caller workspace.  (No counterpart in the reference: its host wrapper always allocates its
  * scratch itself, backward/launch.rs:389-392.)
  *

@@ -156,9 +156,47 @@ def test_layer_forward_bfloat16_at_a_wider_shape():
     assert_close(y, want, 2e-2, "layer output", max_bad_frac=1e-3)
 
 
-def test_layer_forward_refuses_to_run_under_autograd():
+def test_training_with_shared_qk_convolutions_is_refused():
     import ttt_rs_b200 as tb
-    cfg = tb.TTTLayerConfig(hidden_size=128, num_heads=2)
+    cfg = tb.TTTLayerConfig(hidden_size=128, num_heads=2, share_qk=True)
     m = tb.TTT(cfg)
-    with pytest.raises(RuntimeError, match="no_grad"):
+    with pytest.raises(NotImplementedError, match="shared-QK"):
         m(torch.zeros(1, 16, 128), tb.new_inner(cfg), None)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("use_gate", (False, True))
+def test_layer_training_gradients_match_autograd_of_the_restatement(use_gate):
+    """Whole-layer backward (projection GEMM gradients by torch, every other step by this repo's gradient kernels)
+    against float64 autograd through the CPU restatement."""
+    import ttt_rs_b200 as tb
+    dev = torch.device("cuda:0")
+    B, T, H = 2, 48, 3
+    x, p = _random_case(B, T, H, 31, False, use_gate, torch.float32)
+    m, inner = _layer_from_params(tb, p, False, use_gate, torch.float32, dev, H)
+    xg = x.float().to(dev).requires_grad_(True)
+    gy = torch.randn(B, T, H * 64, generator=torch.Generator().manual_seed(2)).double()
+    state = inner.init_state(B)
+    y = m(xg, inner, state)
+    y.backward(gy.float().to(dev))
+    torch.cuda.synchronize()
+    tb.TttTileMultiKernel.check_status()
+
+    leaves = {k: v.clone().requires_grad_(True) for k, v in p.items() if k != "token_idx"}
+    leaves["token_idx"] = p["token_idx"]
+    xr = x.clone().requires_grad_(True)
+    yr, _ = LO.ttt_layer_forward(xr, leaves, num_heads=H, use_gate=use_gate)
+    yr.backward(gy)
+    assert_close(y, yr, 2e-4, "output")
+    rt = 1e-3
+    assert_close(xg.grad, xr.grad, rt, "d input")
+    pairs = {"q_proj": m.q_proj, "k_proj": m.k_proj, "v_proj": m.v_proj, "o_proj": m.o_proj,
+             "lr_weight": m.learnable_ttt_lr_weight, "lr_bias": m.learnable_ttt_lr_bias,
+             "learnable_token_idx": m.learnable_token_idx, "post_norm_weight": m.post_norm_weight,
+             "post_norm_bias": m.post_norm_bias, "W1": inner.inner.weight_init, "b1": inner.inner.bias_init,
+             "ttt_norm_weight": inner.inner.ln_weight, "ttt_norm_bias": inner.inner.ln_bias}
+    if use_gate:
+        pairs["g_proj"] = m.g_proj
+    for name, param in pairs.items():
+        assert param.grad is not None, f"no gradient reached {name}"
+        assert_close(param.grad.reshape(leaves[name].grad.shape), leaves[name].grad, rt, f"d {name}")

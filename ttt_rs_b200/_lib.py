@@ -62,6 +62,11 @@ SYMBOLS = {
     "ttt_linear_forward_partial": (C.c_int, [_DP] + [_P] * 13),
     "ttt_layer_prologue": (C.c_int, [_DP, _P, _P, _P, C.c_int64, _P, C.c_int64, _P, _P, _P, _P, _P, C.c_int, C.c_int,
                                      C.c_int, C.c_float, C.c_float, _P, _P, _P, _P, _P]),
+    "ttt_layer_prologue_backward": (C.c_int, [_DP, _P, _P, _P, _P, _P, C.c_int, C.c_int, C.c_float, C.c_float, _P, _P,
+                                              _P, C.c_int64, _P, C.c_int64, C.c_int, _P]),
+    "ttt_layer_epilogue_backward_workspace_bytes": (C.c_size_t, [_DP]),
+    "ttt_layer_epilogue_backward": (C.c_int, [_DP, _P, _P, _P, C.c_int64, _P, _P, C.c_float, _P, _P, C.c_int64, _P,
+                                              _P, _P, C.c_size_t, _P]),
     "ttt_layer_epilogue": (C.c_int, [_DP, _P, _P, C.c_int64, _P, _P, C.c_float, _P, _P]),
 }
 

@@ -571,3 +571,106 @@ extern "C" int ttt_linear_forward_partial(const ttt_dims* d, const void* xq, con
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "partial forward launch failed: %s", cudaGetErrorString(e));
   return TTT_OK;
 }
+
+extern "C" int ttt_layer_prologue_backward(const ttt_dims* d, const void* grad_xq, const void* grad_xk,
+                                           const void* grad_xv, const void* grad_ttt_lr_eta, const void* ttt_lr_eta,
+                                           int start_idx, int rope_mode, float rope_theta, float base_lr,
+                                           void* grad_q_dst, void* grad_k_dst, void* grad_v_dst, int64_t dst_ld,
+                                           void* grad_lr_logits, int64_t lr_ld, int lr_cols, void* stream) {
+  int rc = check_layer_dims(d);
+  if (rc != TTT_OK) return rc;
+  if (rope_mode < 0 || rope_mode > 2) return fail(TTT_ERR_UNSUPPORTED, "rope_mode=%d (0 none, 1 wrapped, 2 global)", rope_mode);
+  if (rope_mode == 1 && (d->mini_batch < 1 || d->mini_batch > 64))
+    return fail(TTT_ERR_UNSUPPORTED, "wrapped rotary positions need 1 <= mini_batch <= 64 (got %d)", d->mini_batch);
+  if (rope_mode != 0 && !(rope_theta > 0.f)) return fail(TTT_ERR_SHAPE, "rope_theta must be positive");
+  if (start_idx < 0) return fail(TTT_ERR_SHAPE, "start_idx must be >= 0");
+  if (!(base_lr != 0.f)) return fail(TTT_ERR_SHAPE, "base_lr must be non-zero");
+  if (dst_ld < (int64_t)d->heads * 64 || (dst_ld & 7) != 0)
+    return fail(TTT_ERR_SHAPE, "dst_ld (%lld) must be >= heads*64 and a multiple of 8", (long long)dst_ld);
+  if (lr_cols < d->heads || lr_ld < lr_cols)
+    return fail(TTT_ERR_SHAPE, "need heads <= lr_cols <= lr_ld (got lr_cols=%d, lr_ld=%lld)", lr_cols, (long long)lr_ld);
+  const NamedPtr ptrs[] = {{"grad_xq", grad_xq},       {"grad_xk", grad_xk},       {"grad_xv", grad_xv},
+                           {"grad_q_dst", grad_q_dst}, {"grad_k_dst", grad_k_dst}, {"grad_v_dst", grad_v_dst}};
+  rc = check_ptrs(ptrs, 6);
+  if (rc != TTT_OK) return rc;
+  if (grad_ttt_lr_eta == nullptr || ttt_lr_eta == nullptr || grad_lr_logits == nullptr)
+    return fail(TTT_ERR_NULL, "grad_ttt_lr_eta / ttt_lr_eta / grad_lr_logits is null");
+  ttt::LayerProBwdParams p;
+  p.dxq = grad_xq;
+  p.dxk = grad_xk;
+  p.dxv = grad_xv;
+  p.dlr = grad_ttt_lr_eta;
+  p.lr = ttt_lr_eta;
+  p.dq_dst = grad_q_dst;
+  p.dk_dst = grad_k_dst;
+  p.dv_dst = grad_v_dst;
+  p.ld_dst = (long)dst_ld;
+  p.dlogits_dst = grad_lr_logits;
+  p.ld_dlr = (long)lr_ld;
+  p.lr_cols = lr_cols;
+  p.B = d->batch;
+  p.H = d->heads;
+  p.T = d->seq_len;
+  p.start_idx = start_idx;
+  p.pos_mod = rope_mode == 1 ? d->mini_batch : 1;
+  p.rope_mode = rope_mode;
+  p.rope_theta = rope_mode != 0 ? rope_theta : 1.f;
+  p.base_lr = base_lr;
+  cudaError_t e = ttt::launch_layer_prologue_bwd(d->dtype, p, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "layer prologue backward launch failed: %s", cudaGetErrorString(e));
+  return TTT_OK;
+}
+
+extern "C" size_t ttt_layer_epilogue_backward_workspace_bytes(const ttt_dims* d) {
+  if (check_layer_dims(d) != TTT_OK || d->heads > 32) return 0;
+  return (size_t)ttt::layer_epilogue_bwd_max_ctas() * 2 * d->heads * 64 * sizeof(float);
+}
+
+extern "C" int ttt_layer_epilogue_backward(const ttt_dims* d, const void* grad_y, const void* inner_out,
+                                           const void* gate, int64_t gate_ld, const void* post_norm_weight,
+                                           const void* post_norm_bias, float eps, void* grad_inner_out,
+                                           void* grad_gate, int64_t grad_gate_ld, float* grad_post_norm_weight,
+                                           float* grad_post_norm_bias, void* workspace, size_t workspace_bytes,
+                                           void* stream) {
+  int rc = check_layer_dims(d);
+  if (rc != TTT_OK) return rc;
+  if (d->heads > 32) return fail(TTT_ERR_UNSUPPORTED, "heads=%d (supported: up to 32)", d->heads);
+  if (!(eps >= 0.f)) return fail(TTT_ERR_SHAPE, "eps must be >= 0");
+  const NamedPtr ptrs[] = {{"grad_y", grad_y}, {"inner_out", inner_out}, {"grad_inner_out", grad_inner_out}};
+  rc = check_ptrs(ptrs, 3);
+  if (rc != TTT_OK) return rc;
+  if (post_norm_weight == nullptr || post_norm_bias == nullptr || grad_post_norm_weight == nullptr ||
+      grad_post_norm_bias == nullptr)
+    return fail(TTT_ERR_NULL, "post_norm_weight / post_norm_bias / their gradients must not be null");
+  if (gate != nullptr) {
+    if (grad_gate == nullptr) return fail(TTT_ERR_NULL, "grad_gate is null although a gate is given");
+    const int64_t cols = (int64_t)d->heads * 64;
+    if (gate_ld < cols || (gate_ld & 3) != 0 || grad_gate_ld < cols || (grad_gate_ld & 3) != 0)
+      return fail(TTT_ERR_SHAPE, "gate_ld / grad_gate_ld must be >= heads*64 and multiples of 4");
+    if ((reinterpret_cast<uintptr_t>(gate) & 7u) != 0 || (reinterpret_cast<uintptr_t>(grad_gate) & 7u) != 0)
+      return fail(TTT_ERR_ALIGN, "gate / grad_gate is not 8-byte aligned");
+  }
+  const size_t need = ttt_layer_epilogue_backward_workspace_bytes(d);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(TTT_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+  ttt::LayerEpiBwdParams p;
+  p.dy = grad_y;
+  p.inner_out = inner_out;
+  p.gate = gate;
+  p.ld_gate = (long)gate_ld;
+  p.ln_w = post_norm_weight;
+  p.ln_b = post_norm_bias;
+  p.d_inner = grad_inner_out;
+  p.dgate = grad_gate;
+  p.ld_dgate = (long)grad_gate_ld;
+  p.d_ln_w = grad_post_norm_weight;
+  p.d_ln_b = grad_post_norm_bias;
+  p.partials = static_cast<float*>(workspace);
+  p.B = d->batch;
+  p.H = d->heads;
+  p.T = d->seq_len;
+  p.eps = eps;
+  cudaError_t e = ttt::launch_layer_epilogue_bwd(d->dtype, p, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "layer epilogue backward launch failed: %s", cudaGetErrorString(e));
+  return TTT_OK;
+}

@@ -110,7 +110,43 @@ struct LayerEpiParams {
   int B, H, T;
   float eps;
 };
+struct LayerProBwdParams {
+  const void* dxq;  // [B,H,T,F] gradients of the prologue's outputs
+  const void* dxk;
+  const void* dxv;
+  const void* dlr;  // [B,H,T]
+  const void* lr;   // [B,H,T] the forward's ttt_lr_eta
+  void* dq_dst;     // [B*T, ld_dst] column blocks of the projection-output gradient
+  void* dk_dst;
+  void* dv_dst;
+  long ld_dst;
+  void* dlogits_dst;  // [B*T, ld_dlr]: lr_cols columns written (H logit gradients, then zeros)
+  long ld_dlr;
+  int lr_cols;
+  int B, H, T;
+  int start_idx, pos_mod, rope_mode;
+  float rope_theta, base_lr;
+};
+struct LayerEpiBwdParams {
+  const void* dy;         // [B*T, H*F] gradient of the epilogue's output
+  const void* inner_out;  // [B,H,T,F]
+  const void* gate;       // [B*T, ld_gate] or null
+  long ld_gate;
+  const void* ln_w;
+  const void* ln_b;
+  void* d_inner;          // [B,H,T,F]
+  void* dgate;            // [B*T, ld_dgate] (written when gate != null)
+  long ld_dgate;
+  float* d_ln_w;          // [H*F] float32
+  float* d_ln_b;
+  float* partials;        // workspace: [CTAs][2][H*F] float32
+  int B, H, T;
+  float eps;
+};
 cudaError_t launch_layer_prologue(int dtype, const LayerProParams& p, cudaStream_t st);
+cudaError_t launch_layer_prologue_bwd(int dtype, const LayerProBwdParams& p, cudaStream_t st);
+cudaError_t launch_layer_epilogue_bwd(int dtype, const LayerEpiBwdParams& p, cudaStream_t st);
+int layer_epilogue_bwd_max_ctas();
 cudaError_t launch_layer_epilogue(int dtype, const LayerEpiParams& p, cudaStream_t st);
 
 // One mini-batch of R <= 16 tokens per stream (decode step, sequence tail): ttt_linear_partial.cu.

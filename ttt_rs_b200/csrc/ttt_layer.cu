@@ -422,3 +422,381 @@ cudaError_t launch_layer_epilogue(int dtype, const LayerEpiParams& p, cudaStream
 }
 
 }  // namespace ttt
+
+// =====================================================================================================
+// Backward of the two layer steps (training).  Reference: Burn autodiff over the tensor ops of
+// rust/layer/src/ttt.rs:152-299; here each step's gradient is one more bandwidth-bound pass.
+// =====================================================================================================
+namespace ttt {
+
+// Prologue backward (configuration without the shared-QK convolutions): gradients of XQ, XK, XV [B,H,T,F] go back
+// to the projection layout [B*T, ld] with the inverse rotation applied to q and k; the gradient of ttt_lr_eta goes
+// back through the sigmoid to the logits' columns (lr = c sigma(z), c = base_lr / F  =>  dz = dlr * lr * (1 - lr/c));
+// padding columns after the H logit columns are zeroed.
+template <typename T>
+__global__ void __launch_bounds__(PRO_THREADS, sizeof(T) == 2 ? 3 : 1) ttt_layer_prologue_bwd_kernel(const LayerProBwdParams p) {
+  __shared__ float2 rope_tab[PRO_MAXPOS][32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int F = HD, H = p.H, NT = p.T;
+  const bool rope = p.rope_mode != 0, rope_wrap = p.rope_mode == 1;
+  const float log2_theta = log2f(p.rope_theta);
+  if (rope && rope_wrap) {
+    for (int e = tid; e < p.pos_mod * 32; e += PRO_THREADS) {
+      const int pos = e >> 5, i = e & 31;
+      float s, c;
+      sincosf(pos * exp2f(-(2.f * i / F) * log2_theta), &s, &c);
+      rope_tab[pos][i] = make_float2(c, s);
+    }
+  }
+  __syncthreads();
+  const int hq = lane >> 3, sub = lane & 7;
+  const int hgroups = (H + 3) >> 2, tchunks = (NT + PRO_TCHUNK - 1) / PRO_TCHUNK;
+  const long ntasks = (long)p.B * hgroups * tchunks;
+  for (long task = (long)blockIdx.x * (PRO_THREADS / 32) + warp; task < ntasks; task += (long)gridDim.x * (PRO_THREADS / 32)) {
+    const int tc = (int)(task % tchunks);
+    const int hg = (int)((task / tchunks) % hgroups);
+    const int b = (int)(task / ((long)tchunks * hgroups));
+    const int h = 4 * hg + hq;
+    if (h >= H) continue;
+    const int col = h * F + 8 * sub;
+    const int t0 = tc * PRO_TCHUNK, t1 = min(NT, t0 + PRO_TCHUNK);
+    for (int tb = t0; tb < t1; tb += PRO_TG) {
+      Vec8<T> vq[PRO_TG], vk[PRO_TG], vv[PRO_TG];
+#pragma unroll
+      for (int u = 0; u < PRO_TG; ++u) {
+        if (tb + u < t1) {
+          const size_t srow = (((size_t)b * H + h) * NT + tb + u) * F + 8 * sub;
+          vq[u].load(static_cast<const T*>(p.dxq) + srow);
+          vk[u].load(static_cast<const T*>(p.dxk) + srow);
+          vv[u].load(static_cast<const T*>(p.dxv) + srow);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < PRO_TG; ++u) {
+        const int t = tb + u;
+        if (t < t1) {
+          if (rope) {
+            float fq[8], fk[8];
+            vq[u].unpack(fq);
+            vk[u].unpack(fk);
+            const int pos = p.start_idx + t;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float2 cs;
+              if (rope_wrap) {
+                cs = rope_tab[pos % p.pos_mod][4 * sub + j];
+              } else {
+                sincosf(pos * exp2f(-(2.f * (4 * sub + j) / F) * log2_theta), &cs.y, &cs.x);
+              }
+              // transpose of the forward rotation
+              const float q0 = fq[2 * j], q1 = fq[2 * j + 1], k0 = fk[2 * j], k1 = fk[2 * j + 1];
+              fq[2 * j] = q0 * cs.x + q1 * cs.y;
+              fq[2 * j + 1] = q1 * cs.x - q0 * cs.y;
+              fk[2 * j] = k0 * cs.x + k1 * cs.y;
+              fk[2 * j + 1] = k1 * cs.x - k0 * cs.y;
+            }
+            vq[u].pack(fq);
+            vk[u].pack(fk);
+          }
+          const size_t drow = ((size_t)b * NT + t) * p.ld_dst + col;
+          vq[u].store(static_cast<T*>(p.dq_dst) + drow);
+          vk[u].store(static_cast<T*>(p.dk_dst) + drow);
+          vv[u].store(static_cast<T*>(p.dv_dst) + drow);
+        }
+      }
+    }
+  }
+  const float inv_c = (float)F / p.base_lr;
+  const long nlr = (long)p.B * NT * p.lr_cols;
+  for (long e = (long)blockIdx.x * PRO_THREADS + tid; e < nlr; e += (long)gridDim.x * PRO_THREADS) {
+    const int h = (int)(e % p.lr_cols);
+    const long row = e / p.lr_cols;  // b * T + t
+    float dz = 0.f;
+    if (h < H) {
+      const int t = (int)(row % NT), b = (int)(row / NT);
+      const size_t i = ((size_t)b * H + h) * NT + t;
+      const float lr = ld_as_float<T>(p.lr, i);
+      dz = ld_as_float<T>(p.dlr, i) * lr * (1.f - lr * inv_c);
+    }
+    st_from_float<T>(p.dlogits_dst, (size_t)row * p.ld_dlr + h, dz);
+  }
+}
+
+// Epilogue backward.  Same tiling as the forward kernel: the inner-output tile is fetched into shared memory, each
+// warp takes whole rows, recomputes the row statistics, forms
+//   dn = dy * gelu(g),  dg = dy * n * gelu'(g)   (n = gamma x_hat + beta; without a gate dn = dy),
+//   dz = rstd * (dx - mean(dx) - x_hat * mean(dx * x_hat)),  dx = dn * gamma,
+// writes dz back into the tile (then scattered to [B,H,T,F] per head segment) and keeps the per-column sums of
+// dn * x_hat and dn in registers; every CTA writes its sums to `partials` and a second kernel adds them in a fixed order.
+template <typename T, int MAXCH>
+__global__ void __launch_bounds__(EPI_THREADS, 1) ttt_layer_epilogue_bwd_kernel(const LayerEpiBwdParams p) {
+  constexpr int TT = 64 / MAXCH;
+  constexpr int EPC = 16 / sizeof(T);
+  constexpr int CPR = HD / EPC;
+  extern __shared__ __align__(16) uint8_t epi_smem[];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int H = p.H, NT = p.T, C = H * HD;
+  const size_t tile_bytes = (size_t)TT * C * sizeof(T);
+  float* gam = reinterpret_cast<float*>(epi_smem + 2 * tile_bytes);
+  float* bet = gam + C;
+  for (int c = tid; c < C; c += EPI_THREADS) {
+    gam[c] = ld_as_float<T>(p.ln_w, (size_t)c);
+    bet[c] = ld_as_float<T>(p.ln_b, (size_t)c);
+  }
+  const int tiles_per_b = (NT + TT - 1) / TT;
+  const long ntiles = (long)p.B * tiles_per_b;
+  const int nch = C / EPC;
+  constexpr int seg = TT * CPR;
+
+  auto fetch = [&](long tile_id, int buf) {
+    if (tile_id < ntiles) {
+      const int b = (int)(tile_id / tiles_per_b);
+      const int t0 = (int)(tile_id % tiles_per_b) * TT;
+      const int rows = min(TT, NT - t0);
+      const uint32_t dst0 = smem_u32(epi_smem + buf * tile_bytes);
+      for (int idx = tid; idx < H * seg; idx += EPI_THREADS) {
+        const int h = idx / seg, i = idx - h * seg, r = i / CPR, cc = i - r * CPR;
+        if (r < rows) {
+          const T* src = static_cast<const T*>(p.inner_out) + (((size_t)b * H + h) * NT + t0) * HD + (size_t)i * EPC;
+          const uint32_t dst = dst0 + (uint32_t)(((size_t)r * C + h * HD + cc * EPC) * sizeof(T));
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+        }
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  float acc_g[MAXCH][EPC], acc_b[MAXCH][EPC];  // column sums of dn * x_hat and dn over this CTA's rows
+#pragma unroll
+  for (int j = 0; j < MAXCH; ++j)
+#pragma unroll
+    for (int e = 0; e < EPC; ++e) acc_g[j][e] = acc_b[j][e] = 0.f;
+
+  int buf = 0;
+  fetch(blockIdx.x, 0);
+  for (long tile_id = blockIdx.x; tile_id < ntiles; tile_id += gridDim.x, buf ^= 1) {
+    const int b = (int)(tile_id / tiles_per_b);
+    const int t0 = (int)(tile_id % tiles_per_b) * TT;
+    const int rows = min(TT, NT - t0);
+    fetch(tile_id + gridDim.x, buf ^ 1);
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncthreads();
+    T* tile = reinterpret_cast<T*>(epi_smem + buf * tile_bytes);
+    for (int r = warp; r < rows; r += EPI_THREADS / 32) {
+      T* row = tile + (size_t)r * C;
+      const size_t tok = (size_t)b * NT + t0 + r;
+      float v[MAXCH][EPC];
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < MAXCH; ++j) {
+        const int ch = j * 32 + lane;
+        if (ch < nch) {
+          if constexpr (sizeof(T) == 2) {
+            Vec8<T> raw;
+            raw.load(row + ch * EPC);
+            raw.unpack(v[j]);
+          } else {
+            const float4 f = *reinterpret_cast<const float4*>(row + ch * EPC);
+            v[j][0] = f.x; v[j][1] = f.y; v[j][2] = f.z; v[j][3] = f.w;
+          }
+#pragma unroll
+          for (int e = 0; e < EPC; ++e) s += v[j][e];
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      const float mean = s / C;
+      float q = 0.f;
+#pragma unroll
+      for (int j = 0; j < MAXCH; ++j)
+        if (j * 32 + lane < nch) {
+#pragma unroll
+          for (int e = 0; e < EPC; ++e) {
+            v[j][e] -= mean;
+            q = fmaf(v[j][e], v[j][e], q);
+          }
+        }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+      const float rstd = 1.f / sqrtf(q / C + p.eps);
+      // pass 1: x_hat, dn (and dg), dx = dn * gamma and its two row sums; dx is kept in v, x_hat recomputed later
+      float dxv[MAXCH][EPC];
+      float m1 = 0.f, m2 = 0.f;
+#pragma unroll
+      for (int j = 0; j < MAXCH; ++j) {
+        const int ch = j * 32 + lane;
+        if (ch < nch) {
+          const int c0 = ch * EPC;
+          float dy[EPC];
+          const T* dyp = static_cast<const T*>(p.dy) + tok * C + c0;
+          if constexpr (sizeof(T) == 2) {
+            Vec8<T> raw;
+            raw.load(dyp);
+            raw.unpack(dy);
+          } else {
+            const float4 f = *reinterpret_cast<const float4*>(dyp);
+            dy[0] = f.x; dy[1] = f.y; dy[2] = f.z; dy[3] = f.w;
+          }
+          float gt[EPC], dg[EPC];
+          if (p.gate != nullptr) {
+            const T* gp = static_cast<const T*>(p.gate) + tok * p.ld_gate + c0;
+            if constexpr (sizeof(T) == 2) {
+              const uint2 g0 = reinterpret_cast<const uint2*>(gp)[0], g1 = reinterpret_cast<const uint2*>(gp)[1];
+              gt[0] = bf16_lo(g0.x); gt[1] = bf16_hi(g0.x); gt[2] = bf16_lo(g0.y); gt[3] = bf16_hi(g0.y);
+              gt[4] = bf16_lo(g1.x); gt[5] = bf16_hi(g1.x); gt[6] = bf16_lo(g1.y); gt[7] = bf16_hi(g1.y);
+            } else {
+              const float2 g0 = reinterpret_cast<const float2*>(gp)[0], g1 = reinterpret_cast<const float2*>(gp)[1];
+              gt[0] = g0.x; gt[1] = g0.y; gt[2] = g1.x; gt[3] = g1.y;
+            }
+          }
+#pragma unroll
+          for (int e = 0; e < EPC; ++e) {
+            const float xh = v[j][e] * rstd;
+            float dn = dy[e];
+            if (p.gate != nullptr) {
+              const float g = gt[e], g2 = g * g;
+              const float u = 0.7978845608028654f * (g + 0.044715f * g * g2);
+              const float th = tanhf(u);
+              const float gelu = 0.5f * g * (1.f + th);
+              const float dgelu = 0.5f * (1.f + th) + 0.5f * g * (1.f - th * th) * 0.7978845608028654f * (1.f + 3.f * 0.044715f * g2);
+              dg[e] = dy[e] * (gam[c0 + e] * xh + bet[c0 + e]) * dgelu;
+              dn = dy[e] * gelu;
+            }
+            acc_g[j][e] = fmaf(dn, xh, acc_g[j][e]);
+            acc_b[j][e] += dn;
+            const float dx = dn * gam[c0 + e];
+            dxv[j][e] = dx;
+            m1 += dx;
+            m2 = fmaf(dx, xh, m2);
+          }
+          if (p.gate != nullptr) {
+            T* dgp = static_cast<T*>(p.dgate) + tok * p.ld_dgate + c0;
+            if constexpr (sizeof(T) == 2) {
+              uint2 o0, o1;
+              o0.x = pack_bf16(dg[0], dg[1]); o0.y = pack_bf16(dg[2], dg[3]);
+              o1.x = pack_bf16(dg[4], dg[5]); o1.y = pack_bf16(dg[6], dg[7]);
+              reinterpret_cast<uint2*>(dgp)[0] = o0;
+              reinterpret_cast<uint2*>(dgp)[1] = o1;
+            } else {
+              reinterpret_cast<float2*>(dgp)[0] = make_float2(dg[0], dg[1]);
+              reinterpret_cast<float2*>(dgp)[1] = make_float2(dg[2], dg[3]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        m1 += __shfl_xor_sync(0xffffffffu, m1, o);
+        m2 += __shfl_xor_sync(0xffffffffu, m2, o);
+      }
+      m1 /= C;
+      m2 /= C;
+      // pass 2: dz back into the tile, in place
+#pragma unroll
+      for (int j = 0; j < MAXCH; ++j) {
+        const int ch = j * 32 + lane;
+        if (ch < nch) {
+          float dz[EPC];
+#pragma unroll
+          for (int e = 0; e < EPC; ++e) dz[e] = rstd * (dxv[j][e] - m1 - v[j][e] * rstd * m2);
+          if constexpr (sizeof(T) == 2) {
+            Vec8<T> o;
+            o.pack(dz);
+            o.store(row + ch * EPC);
+          } else {
+            *reinterpret_cast<float4*>(row + ch * EPC) = make_float4(dz[0], dz[1], dz[2], dz[3]);
+          }
+        }
+      }
+    }
+    __syncthreads();  // the tile now holds dz for every row
+    for (int idx = tid; idx < H * seg; idx += EPI_THREADS) {
+      const int h = idx / seg, i = idx - h * seg, r = i / CPR, cc = i - r * CPR;
+      if (r < rows) {
+        T* dst = static_cast<T*>(p.d_inner) + (((size_t)b * H + h) * NT + t0) * HD + (size_t)i * EPC;
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(tile + (size_t)r * C + h * HD + cc * EPC);
+      }
+    }
+    __syncthreads();  // done with this buffer before the next iteration refills it
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+  // CTA-wide column sums: warps add their registers through shared memory in warp order, then one row per CTA
+  float* red = reinterpret_cast<float*>(epi_smem);  // reuse of the tile area: 2 * C floats
+  __syncthreads();
+  for (int w = 0; w < EPI_THREADS / 32; ++w) {
+    if (warp == w) {
+#pragma unroll
+      for (int j = 0; j < MAXCH; ++j) {
+        const int ch = j * 32 + lane;
+        if (ch < nch) {
+#pragma unroll
+          for (int e = 0; e < EPC; ++e) {
+            const int c = ch * EPC + e;
+            red[c] = (w == 0 ? 0.f : red[c]) + acc_g[j][e];
+            red[C + c] = (w == 0 ? 0.f : red[C + c]) + acc_b[j][e];
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  float* out = p.partials + (size_t)blockIdx.x * 2 * C;
+  for (int c = tid; c < 2 * C; c += EPI_THREADS) out[c] = red[c];
+}
+
+// d post_norm_weight / d post_norm_bias: the CTAs' partial rows added in a fixed order.
+__global__ void ttt_layer_epilogue_bwd_reduce_kernel(const float* partials, int nparts, int C, float* dw, float* db) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= 2 * C) return;
+  float s = 0.f;
+  for (int i = 0; i < nparts; ++i) s += partials[(size_t)i * 2 * C + c];
+  if (c < C)
+    dw[c] = s;
+  else
+    db[c - C] = s;
+}
+
+cudaError_t launch_layer_prologue_bwd(int dtype, const LayerProBwdParams& p, cudaStream_t st) {
+  const long ntasks = (long)p.B * ((p.H + 3) / 4) * ((p.T + PRO_TCHUNK - 1) / PRO_TCHUNK);
+  const long want = (ntasks + PRO_THREADS / 32 - 1) / (PRO_THREADS / 32);
+  const long cap = (long)sm_count() * 8;
+  const int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
+  if (dtype == 1)
+    ttt_layer_prologue_bwd_kernel<__nv_bfloat16><<<grid, PRO_THREADS, 0, st>>>(p);
+  else
+    ttt_layer_prologue_bwd_kernel<float><<<grid, PRO_THREADS, 0, st>>>(p);
+  return cudaGetLastError();
+}
+
+int layer_epilogue_bwd_max_ctas() { return sm_count() * 2; }
+
+template <typename T, int MAXCH>
+static cudaError_t launch_epi_bwd_t(LayerEpiBwdParams p, cudaStream_t st) {
+  const int C = p.H * HD;
+  constexpr int TT = 64 / MAXCH;
+  const size_t smem = 2 * (size_t)TT * C * sizeof(T) + 2 * (size_t)C * sizeof(float);
+  auto kfn = ttt_layer_epilogue_bwd_kernel<T, MAXCH>;
+  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  const long ntiles = (long)p.B * ((p.T + TT - 1) / TT);
+  int per_sm = 1;
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kfn, EPI_THREADS, smem);
+  if (e != cudaSuccess) return e;
+  if (per_sm > 2) per_sm = 2;
+  const long cap = (long)sm_count() * (per_sm < 1 ? 1 : per_sm);
+  const int grid = (int)(ntiles < cap ? ntiles : cap);
+  kfn<<<grid < 1 ? 1 : grid, EPI_THREADS, smem, st>>>(p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  ttt_layer_epilogue_bwd_reduce_kernel<<<(2 * C + 255) / 256, 256, 0, st>>>(p.partials, grid < 1 ? 1 : grid, C, p.d_ln_w, p.d_ln_b);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_layer_epilogue_bwd(int dtype, const LayerEpiBwdParams& p, cudaStream_t st) {
+  if (dtype == 1) return p.H <= 16 ? launch_epi_bwd_t<__nv_bfloat16, 4>(p, st) : launch_epi_bwd_t<__nv_bfloat16, 8>(p, st);
+  if (p.H <= 8) return launch_epi_bwd_t<float, 4>(p, st);
+  return p.H <= 16 ? launch_epi_bwd_t<float, 8>(p, st) : launch_epi_bwd_t<float, 16>(p, st);
+}
+
+}  // namespace ttt

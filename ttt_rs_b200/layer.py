@@ -10,7 +10,10 @@ What runs where:
   * inner loop: the fused kernel behind `FusedTileMultiTTTLinear`;
   * permute back + post LayerNorm + gelu gate: `ttt_layer_epilogue` (one pass);
   * output projection: library GEMM.
-There is no PyTorch fallback for the two layer kernels: without the CUDA library the calls raise.
+Under autograd the same kernels run with their gradient kernels (`ttt_layer_prologue_backward`,
+`ttt_layer_epilogue_backward`) joined by torch autograd, so the layer trains end to end (separate q / k projections;
+the shared-QK convolution layout is inference-only).
+There is no PyTorch fallback for the layer kernels: without the CUDA library the calls raise.
 """
 
 from __future__ import annotations
@@ -111,6 +114,77 @@ def layer_epilogue(inner_out: torch.Tensor, ln_weight: torch.Tensor, ln_bias: to
     return y
 
 
+class _PrologueFn(torch.autograd.Function):
+    """`ttt_layer_prologue` with its gradient `ttt_layer_prologue_backward` (layout q | k | v | lr logits | padding,
+    no shared-QK convolutions)."""
+
+    @staticmethod
+    def forward(ctx, proj, lr_bias, cfg, cols, start_idx):
+        xq, xk, xv, lr = layer_prologue(proj, cfg, q_col=cols["q"], k_col=cols["k"], v_col=cols["v"],
+                                        lr_col=cols["lr"], lr_bias=lr_bias, start_idx=start_idx)
+        ctx.save_for_backward(lr)
+        ctx.meta = (cfg, cols, start_idx, proj.shape)
+        return xq, xk, xv, lr
+
+    @staticmethod
+    def backward(ctx, dxq, dxk, dxv, dlr):
+        (lr,) = ctx.saved_tensors
+        cfg, cols, start_idx, (B, T, N) = ctx.meta
+        lib = _lib.load()
+        H, F = cfg.num_heads, cfg.head_dim
+        dt = lr.dtype
+        esz = lr.element_size()
+        dproj = torch.empty(B, T, N, dtype=dt, device=lr.device)
+        d = TttDims(B, H, T, F, cfg.mini_batch_size, 1, 0.0, _dtype_code(dt))
+        base = dproj.data_ptr()
+        col = lambda c: C.c_void_p(base + c * esz)  # noqa: E731
+        stream = C.c_void_p(torch.cuda.current_stream(lr.device).cuda_stream)
+        with torch.cuda.device(lr.device):
+            _lib.check(lib.ttt_layer_prologue_backward(
+                C.byref(d), _ptr(dxq.contiguous()), _ptr(dxk.contiguous()), _ptr(dxv.contiguous()),
+                _ptr(dlr.contiguous()), _ptr(lr), start_idx, _POS[cfg.pos_encoding], cfg.rope_theta, cfg.base_lr,
+                col(cols["q"]), col(cols["k"]), col(cols["v"]), N, col(cols["lr"]), N, N - cols["lr"], stream))
+        dbias = dproj[..., cols["lr"]:cols["lr"] + H].float().sum(dim=(0, 1)).to(dt).reshape(H, 1)
+        return dproj, dbias, None, None, None
+
+
+class _EpilogueFn(torch.autograd.Function):
+    """`ttt_layer_epilogue` with its gradient `ttt_layer_epilogue_backward`."""
+
+    @staticmethod
+    def forward(ctx, inner_out, gate, ln_weight, ln_bias, eps):
+        inner_out = inner_out.contiguous()
+        g2d, ld = (None, 0) if gate is None else (gate.contiguous().reshape(-1, gate.shape[-1]), gate.shape[-1])
+        y = layer_epilogue(inner_out, ln_weight, ln_bias, eps, g2d, ld)
+        ctx.save_for_backward(inner_out, g2d, ln_weight, ln_bias)
+        ctx.eps = eps
+        ctx.gate_shape = None if gate is None else gate.shape
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        inner_out, g2d, ln_weight, ln_bias = ctx.saved_tensors
+        lib = _lib.load()
+        B, H, T, F = inner_out.shape
+        dt, dev = inner_out.dtype, inner_out.device
+        d = TttDims(B, H, T, F, 16, 1, 0.0, _dtype_code(dt))
+        d_inner = torch.empty_like(inner_out)
+        d_gate = None if g2d is None else torch.empty_like(g2d)
+        dw = torch.empty(H * F, dtype=torch.float32, device=dev)
+        db = torch.empty(H * F, dtype=torch.float32, device=dev)
+        ws_bytes = lib.ttt_layer_epilogue_backward_workspace_bytes(C.byref(d))
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        w, b = ln_weight.to(dt).contiguous(), ln_bias.to(dt).contiguous()
+        stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        with torch.cuda.device(dev):
+            _lib.check(lib.ttt_layer_epilogue_backward(
+                C.byref(d), _ptr(dy.contiguous()), _ptr(inner_out), _ptr(g2d), 0 if g2d is None else g2d.shape[1],
+                _ptr(w), _ptr(b), ctx.eps, _ptr(d_inner), _ptr(d_gate), 0 if d_gate is None else d_gate.shape[1],
+                _ptr(dw), _ptr(db), _ptr(ws), ws_bytes, stream))
+        dg = None if d_gate is None else d_gate.reshape(ctx.gate_shape)
+        return d_inner, dg, dw.to(ln_weight.dtype), db.to(ln_bias.dtype), None
+
+
 class TTT(torch.nn.Module):
     """Outer TTT layer.  Parameter names follow the reference (`q_proj`, `k_proj`, `v_proj`, `g_proj`, `o_proj`,
     `q_conv` / `k_conv`, `learnable_ttt_lr_weight` [H, hidden, 1], `learnable_ttt_lr_bias` [H, 1], `token_idx`,
@@ -190,8 +264,7 @@ class TTT(torch.nn.Module):
                 start_idx: int = 0) -> torch.Tensor:
         """x [B, T, hidden] -> [B, T, hidden]; `state` is advanced in place (rust/layer/src/ttt.rs:269-299)."""
         if torch.is_grad_enabled():
-            raise RuntimeError("TTT.forward is the inference / prefill path (its layer kernels record no autograd "
-                               "graph): call it under torch.no_grad()")
+            return self._forward_train(x, inner, state, start_idx)
         c = self.config
         B, T, _ = x.shape
         inputs, proj, cols = self.get_inner_loop_inputs(x, start_idx)
@@ -202,6 +275,34 @@ class TTT(torch.nn.Module):
             gate_ld = proj.shape[-1]
         y = layer_epilogue(out.contiguous(), self.post_norm_weight, self.post_norm_bias, 1e-6, gate, gate_ld)
         return torch.matmul(y, self.o_proj.t())
+
+
+def _train_forward(self, x, inner, state, start_idx):
+    """Training path: the same kernels, each with its gradient kernel, joined by torch autograd (which also supplies
+    the gradients of the library GEMMs).  The gate projection is a GEMM of its own here, so that every column of the
+    fused projection's gradient is written by exactly one kernel."""
+    c = self.config
+    if c.share_qk:
+        raise NotImplementedError("training with the shared-QK convolutions: the prologue's gradient kernel covers "
+                                  "the separate q / k projection layout only")
+    B, T, _ = x.shape
+    H, hs = c.num_heads, c.hidden_size
+    pad = (-(3 * hs + H)) % 8
+    blocks = [self.q_proj, self.k_proj, self.v_proj, self.learnable_ttt_lr_weight.reshape(H, hs)]
+    if pad:
+        blocks.append(torch.zeros(pad, hs, dtype=x.dtype, device=x.device))
+    cols = {"q": 0, "k": hs, "v": 2 * hs, "lr": 3 * hs}
+    proj = torch.matmul(x, torch.cat(blocks, dim=0).t())
+    xq, xk, xv, lr = _PrologueFn.apply(proj, self.learnable_ttt_lr_bias, c, cols, start_idx)
+    te = torch.clamp_min(self.token_idx + self.learnable_token_idx, 0.0)
+    token_eta = te.repeat((T + c.mini_batch_size - 1) // c.mini_batch_size)[:T].to(x.dtype)
+    out = inner.forward(state, TTTInputsInner(Qkv(xq, xk, xv), token_eta, lr, start_idx))
+    gate = torch.matmul(x, self.g_proj.t()) if c.use_gate else None
+    y = _EpilogueFn.apply(out, gate, self.post_norm_weight, self.post_norm_bias, 1e-6)
+    return torch.matmul(y, self.o_proj.t())
+
+
+TTT._forward_train = _train_forward
 
 
 def new_inner(config: TTTLayerConfig, checkpoint_interval: int = 1, device=None, dtype=torch.float32,
