@@ -56,6 +56,8 @@ WORKLOADS = {
                       desc="TTT layer forward (125M layer shape: hidden 768, 12 heads x 64), bf16, B=8 T=2048 mb=16"),
     "layer-fwd-b32": dict(kind="layer", B=32, H=12, T=2048, dtype="bf16", K=1, backward=False,
                           desc="TTT layer forward (hidden 768, 12 heads x 64), bf16, B=32 T=2048 mb=16"),
+    "layer-train-b32": dict(kind="layer", train=True, B=32, H=12, T=2048, dtype="bf16", K=16, backward=True,
+                            desc="TTT layer forward + backward (hidden 768, 12 heads x 64), bf16, B=32 T=2048 mb=16 ckpt=16"),
     "layer-fwd-1b3": dict(kind="layer", B=8, H=32, T=8192, dtype="bf16", K=1, backward=False,
                           desc="TTT layer forward (1.3B layer shape: hidden 2048, 32 heads x 64), bf16, B=8 T=8192 mb=16"),
     # one decode step of the inner model (a mini-batch of one token per stream, state advanced in place)
@@ -255,9 +257,40 @@ def run_layer(args, w):
         with torch.no_grad():
             return inner.forward(tb.TTTLinearState(state0.weight, state0.bias), inputs)
 
+    train = bool(w.get("train"))
+    if train:
+        args.no_cpu_baseline = True  # the CPU leg of the layer workloads times the forward only
+        xg = x.clone().requires_grad_(True)
+        gy = (torch.randn(B, T, C, device=dev) * 1e-2).to(dt)
+
+        def whole():  # noqa: F811  forward + backward of the layer, gradients of the input and of every parameter
+            yy = m(xg, inner, inner.init_state(B))
+            yy.backward(gy)
+            return yy
+
     sampler.start()
     ms = time_events(whole, args.steps, args.warmup)
     clocks = sampler.stop()
+    if train:
+        tb.TttTileMultiKernel.check_status()
+        from ttt_rs_b200.layer import _EpilogueFn, _PrologueFn  # the gradient kernels alone
+        dxs = [torch.randn_like(inputs.qkv.xq) for _ in range(3)]
+        dlr = torch.randn_like(inputs.ttt_lr_eta)
+        pcols = {"q": 0, "k": C, "v": 2 * C, "lr": 3 * C}
+        pproj = torch.empty(B, T, 3 * C + H + (-(3 * C + H)) % 8, device=dev, dtype=dt)
+
+        class _Ctx:
+            saved_tensors = (inputs.ttt_lr_eta,)
+            meta = (cfg, pcols, 0, pproj.shape)
+
+        class _Ctx2:
+            saved_tensors = (inner_out, None, m.post_norm_weight.detach(), m.post_norm_bias.detach())
+            eps = 1e-6
+            gate_shape = None
+
+        gyy = torch.randn_like(y)
+        pb_ms = time_events(lambda: _PrologueFn.backward(_Ctx, *dxs, dlr), args.steps, args.warmup)
+        eb_ms = time_events(lambda: _EpilogueFn.backward(_Ctx2, gyy), args.steps, args.warmup)
     pieces = {
         "projections_gemm": time_events(lambda: torch.matmul(x, wcat.t()), args.steps, args.warmup),
         "ttt_layer_prologue_kernel": time_events(pro, args.steps, args.warmup),
@@ -302,6 +335,17 @@ def run_layer(args, w):
         dtc = (time.perf_counter() - t0) / 3
         line["cpu_baseline"] = {"value": T / dtc, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
                                 "sample": f"B=1 T={T} slice of the workload, float32, 3 passes"}
+    if train:
+        line["metric"] = "ttt_layer_train_tokens_per_sec"
+        line["pieces_ms"]["ttt_layer_prologue_bwd_kernel"] = pb_ms
+        line["pieces_ms"]["ttt_layer_epilogue_bwd_kernels"] = eb_ms
+        line["roofline"]["prologue_bwd"] = {"achieved": pro_bytes / (pb_ms * 1e-3) / 1e9,
+                                            "frac": pro_bytes / (pb_ms * 1e-3) / 1e9 / peak,
+                                            "algorithmic_bytes_per_launch": pro_bytes}
+        eb_bytes = 3 * C * s * B * T  # dy and the inner output in, the inner-output gradient out
+        line["roofline"]["epilogue_bwd"] = {"achieved": eb_bytes / (eb_ms * 1e-3) / 1e9,
+                                            "frac": eb_bytes / (eb_ms * 1e-3) / 1e9 / peak,
+                                            "algorithmic_bytes_per_launch": eb_bytes}
     print(json.dumps(line), flush=True)
 
 
