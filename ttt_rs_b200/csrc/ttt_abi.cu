@@ -623,7 +623,7 @@ extern "C" int ttt_layer_prologue_backward(const ttt_dims* d, const void* grad_x
 
 extern "C" size_t ttt_layer_epilogue_backward_workspace_bytes(const ttt_dims* d) {
   if (check_layer_dims(d) != TTT_OK || d->heads > 32) return 0;
-  return (size_t)ttt::layer_epilogue_bwd_max_ctas() * 2 * d->heads * 64 * sizeof(float);
+  return ttt::layer_epilogue_bwd_workspace_bytes(d->batch, d->heads, d->seq_len);
 }
 
 extern "C" int ttt_layer_epilogue_backward(const ttt_dims* d, const void* grad_y, const void* inner_out,
@@ -666,6 +666,7 @@ extern "C" int ttt_layer_epilogue_backward(const ttt_dims* d, const void* grad_y
   p.d_ln_w = grad_post_norm_weight;
   p.d_ln_b = grad_post_norm_bias;
   p.partials = static_cast<float*>(workspace);
+  p.row_stats = nullptr;
   p.B = d->batch;
   p.H = d->heads;
   p.T = d->seq_len;

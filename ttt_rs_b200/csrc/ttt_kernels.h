@@ -139,14 +139,15 @@ struct LayerEpiBwdParams {
   long ld_dgate;
   float* d_ln_w;          // [H*F] float32
   float* d_ln_b;
-  float* partials;        // workspace: [CTAs][2][H*F] float32
+  float* partials;        // workspace (float32): [B*T][2] row statistics, then [slabs][2][H*F] partial sums
+  float2* row_stats;      // set by the launcher (start of the workspace)
   int B, H, T;
   float eps;
 };
 cudaError_t launch_layer_prologue(int dtype, const LayerProParams& p, cudaStream_t st);
 cudaError_t launch_layer_prologue_bwd(int dtype, const LayerProBwdParams& p, cudaStream_t st);
 cudaError_t launch_layer_epilogue_bwd(int dtype, const LayerEpiBwdParams& p, cudaStream_t st);
-int layer_epilogue_bwd_max_ctas();
+size_t layer_epilogue_bwd_workspace_bytes(int B, int H, int T);
 cudaError_t launch_layer_epilogue(int dtype, const LayerEpiParams& p, cudaStream_t st);
 
 // One mini-batch of R <= 16 tokens per stream (decode step, sequence tail): ttt_linear_partial.cu.

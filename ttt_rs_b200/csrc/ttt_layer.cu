@@ -526,10 +526,10 @@ __global__ void __launch_bounds__(PRO_THREADS, sizeof(T) == 2 ? 3 : 1) ttt_layer
 // warp takes whole rows, recomputes the row statistics, forms
 //   dn = dy * gelu(g),  dg = dy * n * gelu'(g)   (n = gamma x_hat + beta; without a gate dn = dy),
 //   dz = rstd * (dx - mean(dx) - x_hat * mean(dx * x_hat)),  dx = dn * gamma,
-// writes dz back into the tile (then scattered to [B,H,T,F] per head segment) and keeps the per-column sums of
-// dn * x_hat and dn in registers; every CTA writes its sums to `partials` and a second kernel adds them in a fixed order.
+// writes dz back into the tile (then scattered to [B,H,T,F] per head segment) and leaves (mean, rstd) of every row in
+// `row_stats` for the parameter-gradient kernel below.
 template <typename T, int MAXCH>
-__global__ void __launch_bounds__(EPI_THREADS, 1) ttt_layer_epilogue_bwd_kernel(const LayerEpiBwdParams p) {
+__global__ void __launch_bounds__(EPI_THREADS, (MAXCH <= 4 ? 2 : 1)) ttt_layer_epilogue_bwd_kernel(const LayerEpiBwdParams p) {
   constexpr int TT = 64 / MAXCH;
   constexpr int EPC = 16 / sizeof(T);
   constexpr int CPR = HD / EPC;
@@ -565,12 +565,6 @@ __global__ void __launch_bounds__(EPI_THREADS, 1) ttt_layer_epilogue_bwd_kernel(
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-
-  float acc_g[MAXCH][EPC], acc_b[MAXCH][EPC];  // column sums of dn * x_hat and dn over this CTA's rows
-#pragma unroll
-  for (int j = 0; j < MAXCH; ++j)
-#pragma unroll
-    for (int e = 0; e < EPC; ++e) acc_g[j][e] = acc_b[j][e] = 0.f;
 
   int buf = 0;
   fetch(blockIdx.x, 0);
@@ -619,7 +613,8 @@ __global__ void __launch_bounds__(EPI_THREADS, 1) ttt_layer_epilogue_bwd_kernel(
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
       const float rstd = 1.f / sqrtf(q / C + p.eps);
-      // pass 1: x_hat, dn (and dg), dx = dn * gamma and its two row sums; dx is kept in v, x_hat recomputed later
+      if (lane == 0) p.row_stats[tok] = make_float2(mean, rstd);
+      // pass 1: x_hat, dn (and dg), dx = dn * gamma and its two row sums
       float dxv[MAXCH][EPC];
       float m1 = 0.f, m2 = 0.f;
 #pragma unroll
@@ -662,8 +657,6 @@ __global__ void __launch_bounds__(EPI_THREADS, 1) ttt_layer_epilogue_bwd_kernel(
               dg[e] = dy[e] * (gam[c0 + e] * xh + bet[c0 + e]) * dgelu;
               dn = dy[e] * gelu;
             }
-            acc_g[j][e] = fmaf(dn, xh, acc_g[j][e]);
-            acc_b[j][e] += dn;
             const float dx = dn * gam[c0 + e];
             dxv[j][e] = dx;
             m1 += dx;
@@ -721,40 +714,83 @@ __global__ void __launch_bounds__(EPI_THREADS, 1) ttt_layer_epilogue_bwd_kernel(
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 
-  // CTA-wide column sums: warps add their registers through shared memory in warp order, then one row per CTA
-  float* red = reinterpret_cast<float*>(epi_smem);  // reuse of the tile area: 2 * C floats
-  __syncthreads();
-  for (int w = 0; w < EPI_THREADS / 32; ++w) {
-    if (warp == w) {
-#pragma unroll
-      for (int j = 0; j < MAXCH; ++j) {
-        const int ch = j * 32 + lane;
-        if (ch < nch) {
-#pragma unroll
-          for (int e = 0; e < EPC; ++e) {
-            const int c = ch * EPC + e;
-            red[c] = (w == 0 ? 0.f : red[c]) + acc_g[j][e];
-            red[C + c] = (w == 0 ? 0.f : red[C + c]) + acc_b[j][e];
-          }
-        }
-      }
-    }
-    __syncthreads();
-  }
-  float* out = p.partials + (size_t)blockIdx.x * 2 * C;
-  for (int c = tid; c < 2 * C; c += EPI_THREADS) out[c] = red[c];
 }
 
-// d post_norm_weight / d post_norm_bias: the CTAs' partial rows added in a fixed order.
-__global__ void ttt_layer_epilogue_bwd_reduce_kernel(const float* partials, int nparts, int C, float* dw, float* db) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= 2 * C) return;
+// Parameter gradients of the post norm: d weight[c] = sum over tokens of dn * x_hat, d bias[c] = sum of dn.  One CTA
+// per slab of PARAM_SLAB tokens, one thread per column pair, rows walked in order; the slab's sums go to `partials`.
+constexpr int PARAM_SLAB = 128;
+template <typename T>
+__global__ void ttt_layer_epilogue_bwd_param_kernel(const LayerEpiBwdParams p) {
+  const int H = p.H, NT = p.T, C = H * HD;
+  const int pair = threadIdx.x;          // columns 2*pair, 2*pair+1
+  const int c = 2 * pair, h = c / HD, f = c % HD;
+  const long ntok = (long)p.B * NT;
+  const long row0 = (long)blockIdx.x * PARAM_SLAB;
+  const long row1 = row0 + PARAM_SLAB < ntok ? row0 + PARAM_SLAB : ntok;
+  auto ld2 = [](const void* base, size_t idx) -> float2 {
+    if constexpr (sizeof(T) == 2) {
+      const uint32_t w = *reinterpret_cast<const uint32_t*>(static_cast<const T*>(base) + idx);
+      return make_float2(bf16_lo(w), bf16_hi(w));
+    } else {
+      return *reinterpret_cast<const float2*>(static_cast<const T*>(base) + idx);
+    }
+  };
+  float2 ag = make_float2(0.f, 0.f), ab = make_float2(0.f, 0.f);
+  int t = (int)(row0 % NT), b = (int)(row0 / NT);
+  size_t zoff = (((size_t)b * H + h) * NT + t) * HD + f;  // advances by one row per token, re-based at a batch boundary
+  size_t doff = (size_t)row0 * C + c, goff = (size_t)row0 * p.ld_gate + c;
+#pragma unroll 4
+  for (long tok = row0; tok < row1; ++tok) {
+    const float2 st = p.row_stats[tok];
+    const float2 z = ld2(p.inner_out, zoff);
+    float2 dn = ld2(p.dy, doff);
+    if (p.gate != nullptr) {
+      const float2 g = ld2(p.gate, goff);
+      const float u0 = 0.7978845608028654f * (g.x + 0.044715f * g.x * g.x * g.x);
+      const float u1 = 0.7978845608028654f * (g.y + 0.044715f * g.y * g.y * g.y);
+      dn.x *= 0.5f * g.x * (1.f + tanhf(u0));
+      dn.y *= 0.5f * g.y * (1.f + tanhf(u1));
+    }
+    ag.x = fmaf(dn.x, (z.x - st.x) * st.y, ag.x);
+    ag.y = fmaf(dn.y, (z.y - st.x) * st.y, ag.y);
+    ab.x += dn.x;
+    ab.y += dn.y;
+    doff += C;
+    goff += p.ld_gate;
+    zoff += HD;
+    if (++t == NT) {
+      t = 0;
+      ++b;
+      zoff = ((size_t)b * H + h) * NT * HD + f;
+    }
+  }
+  float* out = p.partials + (size_t)blockIdx.x * 2 * C;
+  *reinterpret_cast<float2*>(out + c) = ag;
+  *reinterpret_cast<float2*>(out + C + c) = ab;
+}
+
+// d post_norm_weight / d post_norm_bias: the slabs' partial rows added in a fixed order.  A CTA owns 32 columns;
+// its 8 warps each add an interleaved eighth of the parts (lanes = columns, so every load is one coalesced 128-byte
+// row segment), and the eight sums are combined in warp order through shared memory.
+__global__ void __launch_bounds__(256) ttt_layer_epilogue_bwd_reduce_kernel(const float* partials, int nparts, int C,
+                                                                            float* dw, float* db) {
+  __shared__ float red[8][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;  // column of the [2][C] row
   float s = 0.f;
-  for (int i = 0; i < nparts; ++i) s += partials[(size_t)i * 2 * C + c];
-  if (c < C)
-    dw[c] = s;
-  else
-    db[c - C] = s;
+  if (c < 2 * C)
+    for (int i = warp; i < nparts; i += 8) s += partials[(size_t)i * 2 * C + c];
+  red[warp][lane] = s;
+  __syncthreads();
+  if (warp == 0 && c < 2 * C) {
+    float tot = red[0][lane];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) tot += red[w][lane];
+    if (c < C)
+      dw[c] = tot;
+    else
+      db[c - C] = tot;
+  }
 }
 
 cudaError_t launch_layer_prologue_bwd(int dtype, const LayerProBwdParams& p, cudaStream_t st) {
@@ -769,7 +805,10 @@ cudaError_t launch_layer_prologue_bwd(int dtype, const LayerProBwdParams& p, cud
   return cudaGetLastError();
 }
 
-int layer_epilogue_bwd_max_ctas() { return sm_count() * 2; }
+size_t layer_epilogue_bwd_workspace_bytes(int B, int H, int T) {
+  const size_t ntok = (size_t)B * T, nslab = (ntok + PARAM_SLAB - 1) / PARAM_SLAB;
+  return ntok * sizeof(float2) + nslab * 2 * (size_t)H * HD * sizeof(float);
+}
 
 template <typename T, int MAXCH>
 static cudaError_t launch_epi_bwd_t(LayerEpiBwdParams p, cudaStream_t st) {
@@ -789,11 +828,20 @@ static cudaError_t launch_epi_bwd_t(LayerEpiBwdParams p, cudaStream_t st) {
   kfn<<<grid < 1 ? 1 : grid, EPI_THREADS, smem, st>>>(p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  ttt_layer_epilogue_bwd_reduce_kernel<<<(2 * C + 255) / 256, 256, 0, st>>>(p.partials, grid < 1 ? 1 : grid, C, p.d_ln_w, p.d_ln_b);
+  const long ntok = (long)p.B * p.T;
+  const int nslab = (int)((ntok + PARAM_SLAB - 1) / PARAM_SLAB);
+  ttt_layer_epilogue_bwd_param_kernel<T><<<nslab, C / 2, 0, st>>>(p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  ttt_layer_epilogue_bwd_reduce_kernel<<<(2 * C + 31) / 32, 256, 0, st>>>(p.partials, nslab, C, p.d_ln_w, p.d_ln_b);
   return cudaGetLastError();
 }
 
-cudaError_t launch_layer_epilogue_bwd(int dtype, const LayerEpiBwdParams& p, cudaStream_t st) {
+cudaError_t launch_layer_epilogue_bwd(int dtype, const LayerEpiBwdParams& p0, cudaStream_t st) {
+  // workspace: (mean, rstd) per token, then the slabs' partial parameter gradients
+  LayerEpiBwdParams p = p0;
+  p.row_stats = reinterpret_cast<float2*>(p0.partials);
+  p.partials = p0.partials + 2 * (size_t)p0.B * p0.T;
   if (dtype == 1) return p.H <= 16 ? launch_epi_bwd_t<__nv_bfloat16, 4>(p, st) : launch_epi_bwd_t<__nv_bfloat16, 8>(p, st);
   if (p.H <= 8) return launch_epi_bwd_t<float, 4>(p, st);
   return p.H <= 16 ? launch_epi_bwd_t<float, 8>(p, st) : launch_epi_bwd_t<float, 16>(p, st);
