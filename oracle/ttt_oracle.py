@@ -399,6 +399,200 @@ def ttt_mlp_forward(
     return {"output": torch.cat(outs, dim=2), "w1": W1, "b1": B1, "w2": W2, "b2": B2}
 
 
+def gelu_tanh_grad2(x):
+    """Second derivative of the tanh-form GELU."""
+    u = GELU_C0 * x * (1.0 + GELU_C1 * x * x)
+    t = torch.tanh(u)
+    du = GELU_C0 * (1.0 + 3.0 * GELU_C1 * x * x)
+    d2u = 6.0 * GELU_C0 * GELU_C1 * x
+    return (1.0 - t * t) * du + 0.5 * x * (1.0 - t * t) * (d2u - 2.0 * t * du * du)
+
+
+def _ln_l2_grad_backward(u, z, target, g_, be_, eps):
+    """Backward of G = ln_l2_grad(z, target): given u = dL/dG returns (dz, dtarget, dgamma rows, dbeta rows)
+    (the second-derivative formulas of rust/fused/src/linear_fused_tile/layer_norm.rs:429-709)."""
+    F = z.shape[-1]
+    xh, sig = ln_stats(z, eps)
+    gy = g_ * xh + be_ - target
+    gxh = gy * g_
+    sum_gxh_xh = (gxh * xh).sum(-1, keepdim=True)
+    G = (F * gxh - gxh.sum(-1, keepdim=True) - xh * sum_gxh_xh) / (sig * F)
+    v = -u / sig
+    s1 = v.sum(-1, keepdim=True)
+    s2 = (v * xh).sum(-1, keepdim=True)
+    dgxh = u / sig + s1 / F + xh * s2 / F
+    dy = g_ * dgxh
+    dgam = (gy * dgxh + dy * xh).sum(-2)
+    dbet = dy.sum(-2)
+    dxh = dy * g_ + gxh * s2 / F + v * sum_gxh_xh / F
+    S = (-(dxh * xh + u * G) / sig).sum(-1, keepdim=True)
+    dz = dxh / sig - dxh.sum(-1, keepdim=True) / (sig * F) + xh * S / F
+    return dz, -g_ * dgxh, dgam, dbet
+
+
+def ttt_mlp_backward(
+    xq, xk, xv, w1, b1, w2, b2, token_eta, ttt_lr_eta, ln_weight, ln_bias, grad_output,
+    mini_batch: int = 16, eps: float = 1e-6,
+) -> Dict[str, torch.Tensor]:
+    """Analytic backward of `ttt_mlp_forward` for loss = <grad_output, output> (gradients w.r.t. the returned final
+    state taken as zero, as the reference's fused operators do).  The reference obtains this gradient from Burn
+    autodiff over rust/core/src/mlp.rs:127-208; this is the stage-by-stage form a fused kernel needs: a reverse walk
+    over the stages carrying (dW1, db1, dW2, db2).  Returns grad_xq/xk/xv, grad_w1/b1/w2/b2 (per batch element),
+    grad_ttt_lr_eta, grad_token_eta [T] (per stage position, summed over B and H), grad_ln_weight/bias [H,F]."""
+    B, H, T, F = xq.shape
+    cs = mini_batch
+    ns = T // cs
+    g_ = ln_weight.view(1, H, 1, F)
+    be_ = ln_bias.view(1, H, 1, F)
+    te = token_eta[:cs]
+    te_col = te.view(1, 1, cs, 1)
+    q_s, k_s, v_s, do_s = (_stage_views(t, cs) for t in (xq, xk, xv, grad_output))
+    lr_s = _stage_views(ttt_lr_eta, cs)
+    tr = lambda m: m.transpose(-1, -2)  # noqa: E731
+
+    # states at the start of every stage
+    states = []
+    W1, B1, W2, B2 = w1, b1, w2, b2
+    for s in range(ns):
+        states.append((W1, B1, W2, B2))
+        Kk, V, lr = k_s[:, :, s], v_s[:, :, s], lr_s[:, :, s]
+        z1 = Kk @ W1 + B1.unsqueeze(-2)
+        x2 = gelu_tanh(z1)
+        g2 = ln_l2_grad(x2 @ W2 + B2.unsqueeze(-2), V - Kk, g_, be_, eps)
+        g1 = (g2 @ tr(W2)) * gelu_tanh_grad(z1)
+        last = (te[cs - 1] * lr).unsqueeze(-1)
+        W1 = W1 - tr(last * Kk) @ g1
+        B1 = B1 - (last * g1).sum(-2)
+        W2 = W2 - tr(last * x2) @ g2
+        B2 = B2 - (last * g2).sum(-2)
+
+    dq = torch.empty_like(xq).reshape(B, H, ns, cs, F)
+    dk, dv = torch.empty_like(dq), torch.empty_like(dq)
+    dlr = torch.empty_like(ttt_lr_eta).reshape(B, H, ns, cs)
+    dte = torch.zeros(T, dtype=xq.dtype)
+    dgam = torch.zeros(B, H, F, dtype=xq.dtype)
+    dbet = torch.zeros(B, H, F, dtype=xq.dtype)
+    dW1, dB1, dW2, dB2 = (torch.zeros_like(t) for t in (w1, b1, w2, b2))
+
+    for s in reversed(range(ns)):
+        Q, Kk, V, lr, dO = q_s[:, :, s], k_s[:, :, s], v_s[:, :, s], lr_s[:, :, s], do_s[:, :, s]
+        W1, B1, W2, B2 = states[s]
+        # ---- recompute the forward intermediates of the stage
+        z1 = Kk @ W1 + B1.unsqueeze(-2)
+        gp1 = gelu_tanh_grad(z1)
+        x2 = gelu_tanh(z1)
+        z2 = x2 @ W2 + B2.unsqueeze(-2)
+        g2 = ln_l2_grad(z2, V - Kk, g_, be_, eps)
+        hmat = g2 @ tr(W2)
+        g1 = hmat * gp1
+        eta = _eta_matrices(te, lr)
+        a1 = torch.tril(Q @ tr(Kk))
+        m1 = eta * (1.0 + a1)
+        z1b = Q @ W1 + B1.unsqueeze(-2) - m1 @ g1
+        x2b = gelu_tanh(z1b)
+        a2 = torch.tril(x2b @ tr(x2))
+        m2 = eta * (1.0 + a2)
+        z2b = x2b @ W2 + B2.unsqueeze(-2) - m2 @ g2
+        xhb, sigb = ln_stats(z2b, eps)
+        ell_c = (te[cs - 1] * lr).unsqueeze(-1)
+        # ---- 1. output LayerNorm
+        dgam += (dO * xhb).sum(-2)
+        dbet += dO.sum(-2)
+        t_ = dO * g_
+        dz2b = (F * t_ - t_.sum(-1, keepdim=True) - xhb * (t_ * xhb).sum(-1, keepdim=True)) / (sigb * F)
+        # ---- 2. z2b = x2b W2 + b2 - M2 g2
+        dx2b = dz2b @ tr(W2)
+        nW2 = dW2 + tr(x2b) @ dz2b
+        nB2 = dB2 + dz2b.sum(-2)
+        dm2 = -torch.tril(dz2b @ tr(g2))
+        dg2 = -(tr(m2) @ dz2b)
+        da2 = dm2 * eta
+        deta = dm2 * (1.0 + a2)
+        dx2b = dx2b + da2 @ x2
+        dx2 = tr(da2) @ x2b
+        # ---- 3./4. x2b = gelu(z1b), z1b = Q W1 + b1 - M1 g1
+        dz1b = dx2b * gelu_tanh_grad(z1b)
+        dq_in = dz1b @ tr(W1)
+        nW1 = dW1 + tr(Q) @ dz1b
+        nB1 = dB1 + dz1b.sum(-2)
+        dm1 = -torch.tril(dz1b @ tr(g1))
+        dg1 = -(tr(m1) @ dz1b)
+        da1 = dm1 * eta
+        deta = deta + dm1 * (1.0 + a1)
+        dq_in = dq_in + da1 @ Kk
+        dk_acc = tr(da1) @ Q
+        # ---- 5. the four state updates (dW1 ... are the gradients w.r.t. the NEXT stage's state here)
+        gl1 = g1 @ tr(dW1)          # [cs, F]
+        gl2 = g2 @ tr(dW2)          # [cs, E]
+        dg1 = dg1 - (ell_c * Kk) @ dW1 - ell_c * dB1.unsqueeze(-2)
+        dg2 = dg2 - (ell_c * x2) @ dW2 - ell_c * dB2.unsqueeze(-2)
+        dk_acc = dk_acc - ell_c * gl1
+        dx2 = dx2 - ell_c * gl2
+        dell = -((gl1 * Kk).sum(-1) + (g1 * dB1.unsqueeze(-2)).sum(-1)
+                 + (gl2 * x2).sum(-1) + (g2 * dB2.unsqueeze(-2)).sum(-1))
+        # ---- 6. g1 = (g2 W2^T) o gelu'(z1)
+        dh = dg1 * gp1
+        dz1 = dg1 * hmat * gelu_tanh_grad2(z1)
+        dg2 = dg2 + dh @ W2
+        nW2 = nW2 + tr(dh) @ g2
+        # ---- 7. g2 = d/dz2 of the LayerNorm reconstruction loss
+        dz2, dT, dga, dbe = _ln_l2_grad_backward(dg2, z2, V - Kk, g_, be_, eps)
+        dgam += dga
+        dbet += dbe
+        # ---- 8./9./10. z2 = x2 W2 + b2, x2 = gelu(z1), z1 = K W1 + b1
+        dx2 = dx2 + dz2 @ tr(W2)
+        nW2 = nW2 + tr(x2) @ dz2
+        nB2 = nB2 + dz2.sum(-2)
+        dz1 = dz1 + dx2 * gp1
+        dk_acc = dk_acc + dz1 @ tr(W1)
+        nW1 = nW1 + tr(Kk) @ dz1
+        nB1 = nB1 + dz1.sum(-2)
+        # ---- 11. eta factors
+        dte_stage = (deta * lr.unsqueeze(-2)).sum(-1)
+        dte_stage[..., cs - 1] += (dell * lr).sum(-1)
+        dte[s * cs:(s + 1) * cs] = dte_stage.sum(dim=(0, 1))
+        dlr[:, :, s] = (deta * te_col).sum(-2) + dell * te[cs - 1]
+        # ---- assemble
+        dq[:, :, s] = dO + dq_in
+        dv[:, :, s] = dT
+        dk[:, :, s] = dk_acc - dT
+        dW1, dB1, dW2, dB2 = nW1, nB1, nW2, nB2
+
+    return {
+        "grad_xq": dq.reshape(B, H, T, F), "grad_xk": dk.reshape(B, H, T, F), "grad_xv": dv.reshape(B, H, T, F),
+        "grad_w1": dW1, "grad_b1": dB1, "grad_w2": dW2, "grad_b2": dB2,
+        "grad_ttt_lr_eta": dlr.reshape(B, H, T), "grad_token_eta": dte,
+        "grad_ln_weight": dgam.sum(0), "grad_ln_bias": dbet.sum(0),
+    }
+
+
+def ttt_mlp_backward_autograd(
+    xq, xk, xv, w1, b1, w2, b2, token_eta, ttt_lr_eta, ln_weight, ln_bias, grad_output,
+    mini_batch: int = 16, eps: float = 1e-6,
+) -> Dict[str, torch.Tensor]:
+    """Same contract as `ttt_mlp_backward`, by torch autograd over `ttt_mlp_forward` (token_eta is a [CS] base
+    vector tiled over the stages, so its gradient is reported per stage position)."""
+    cs = mini_batch
+    T = xq.shape[2]
+    ns = T // cs
+    leaves = [t.detach().clone().requires_grad_(True)
+              for t in (xq, xk, xv, w1, b1, w2, b2, ttt_lr_eta, ln_weight, ln_bias)]
+    q, k, v, W1, B1, W2, B2, lr, g, be = leaves
+    te_full = token_eta[:cs].detach().repeat(ns).clone().requires_grad_(True)
+    outs = []
+    for s in range(ns):
+        sl = slice(s * cs, (s + 1) * cs)
+        r = ttt_mlp_forward(q[:, :, sl], k[:, :, sl], v[:, :, sl], W1, B1, W2, B2, te_full[sl], lr[:, :, sl], g, be,
+                            mini_batch=cs, eps=eps)
+        outs.append(r["output"])
+        W1, B1, W2, B2 = r["w1"], r["b1"], r["w2"], r["b2"]
+    out = torch.cat(outs, dim=2)
+    grads = torch.autograd.grad(out, leaves + [te_full], grad_outputs=grad_output)
+    names = ("grad_xq", "grad_xk", "grad_xv", "grad_w1", "grad_b1", "grad_w2", "grad_b2", "grad_ttt_lr_eta",
+             "grad_ln_weight", "grad_ln_bias", "grad_token_eta")
+    return dict(zip(names, grads))
+
+
 # --------------------------------------------------------------------------
 # Synthetic inputs: the seeded generator lives with the product (the benchmark
 # uses it too); re-exported here because every parity test feeds the oracle and

@@ -153,3 +153,22 @@ def test_linear_backward_with_final_state_gradients_matches_autograd():
     assert_close(torch.cat([b1["grad_xk"], b2["grad_xk"]], dim=2), full["grad_xk"], 1e-9, "chunked grad_xk")
     assert_close(b1["grad_weight"], full["grad_weight"], 1e-9, "chunked grad_weight")
     assert_close(b1["grad_ln_weight"] + b2["grad_ln_weight"], full["grad_ln_weight"], 1e-9, "chunked grad_ln_weight")
+
+
+def test_mlp_analytic_backward_matches_autograd():
+    """The stage-by-stage TTT-MLP backward (the form a fused kernel needs: reverse walk carrying dW1, db1, dW2, db2,
+    GELU second derivative, LayerNorm second derivative) against torch autograd over the forward restatement."""
+    t = O.make_inputs(2, 2, 48, 64, 16, seed=3, dtype=torch.float64, inner="mlp")
+    g = torch.Generator().manual_seed(5)
+    t["ln_weight"] = 1 + 0.1 * torch.randn(t["ln_weight"].shape, generator=g, dtype=torch.float64)
+    t["ln_bias"] = 0.1 * torch.randn(t["ln_bias"].shape, generator=g, dtype=torch.float64)
+    for k in ("b1", "b2"):
+        t[k] = 0.05 * torch.randn(t[k].shape, generator=g, dtype=torch.float64)
+    t["grad_output"] = torch.randn(t["xq"].shape, generator=g, dtype=torch.float64)
+    names = ("xq", "xk", "xv", "w1", "b1", "w2", "b2", "token_eta", "ttt_lr_eta", "ln_weight", "ln_bias", "grad_output")
+    a = O.ttt_mlp_backward(*[t[k] for k in names])
+    b = O.ttt_mlp_backward_autograd(*[t[k] for k in names])
+    assert set(a) == set(b)
+    for k in a:
+        err = (a[k] - b[k]).abs().max().item() / (b[k].abs().max().item() + 1e-300)
+        assert err < 1e-11, f"{k}: {err}"
