@@ -153,6 +153,24 @@ int ttt_mlp_forward(const ttt_dims* d, const void* xq, const void* xk, const voi
                     const void* ln_weight, const void* ln_bias, void* output, void* w1_out, void* b1_out, void* w2_out,
                     void* b2_out, void* status, void* stream);
 
+/* TTT-MLP backward (bf16): gradient of ttt_mlp_forward for loss = <grad_output, output>; gradients w.r.t. the returned
+ * final state are taken as zero, as for the TTT-Linear operator.  The reference has no fused counterpart: it
+ * differentiates the tensor ops of rust/core/src/mlp.rs:127-208 with Burn autodiff.  Inputs are the forward's inputs
+ * (nothing saved by the forward is needed: the kernel re-walks the sequence), outputs:
+ *   grad_xq, grad_xk, grad_xv [B,H,T,F]; grad_w1 [B,H,F,4F], grad_b1 [B,H,4F], grad_w2 [B,H,4F,F], grad_b2 [B,H,F]
+ *   (per batch element); grad_ttt_lr_eta [B,H,T]; float32 grad_token_eta [T] (per stage position, summed over B, H),
+ *   float32 grad_ln_weight / grad_ln_bias [H,F] (summed over B).  All written, never accumulated into.
+ * `workspace`: ttt_mlp_backward_workspace_bytes(d) bytes (state, state gradients and the saved per-stage inner
+ * gradients of every stream: about B*H*(264 KB + 20 KB per mini-batch)).
+ */
+size_t ttt_mlp_backward_workspace_bytes(const ttt_dims* d);
+int ttt_mlp_backward(const ttt_dims* d, const void* xq, const void* xk, const void* xv, const void* w1, const void* b1,
+                     const void* w2, const void* b2, const void* token_eta, const void* ttt_lr_eta,
+                     const void* ln_weight, const void* ln_bias, const void* grad_output, void* grad_xq, void* grad_xk,
+                     void* grad_xv, void* grad_w1, void* grad_b1, void* grad_w2, void* grad_b2, void* grad_ttt_lr_eta,
+                     float* grad_token_eta, float* grad_ln_weight, float* grad_ln_bias, void* workspace,
+                     size_t workspace_bytes, void* status, void* stream);
+
 /* One mini-batch of fewer than (or exactly) mini_batch tokens: the tail of a sequence whose length is not a multiple
  * of the mini-batch, and the 1-token decode step.  Semantics: the reference's `TTTInnerModel::forward` calls
  * `forward_mini_batch` once on the remainder, i.e. the remainder is a mini-batch of its own length

@@ -13,6 +13,7 @@ from .fused import (  # noqa: F401
     TttOutputs,
     TttSavedStateMulti,
     TttTileMultiKernel,
+    fused_ttt_mlp_backward,
     fused_ttt_mlp_forward,
     fused_ttt_tile_forward_multi,
     packed_outer_grad_len,

@@ -675,3 +675,64 @@ extern "C" int ttt_layer_epilogue_backward(const ttt_dims* d, const void* grad_y
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "layer epilogue backward launch failed: %s", cudaGetErrorString(e));
   return TTT_OK;
 }
+
+namespace {
+struct MlpWsLayout {
+  size_t stride_floats, off_te, off_ln, total_bytes;
+};
+MlpWsLayout mlp_ws_layout(const ttt_dims* d) {
+  const size_t streams = (size_t)d->batch * d->heads;
+  MlpWsLayout l;
+  l.stride_floats = ttt::mlp_bwd_ws_stride_floats(d->seq_len);
+  l.off_te = streams * l.stride_floats;
+  l.off_ln = l.off_te + streams * (size_t)d->seq_len;
+  l.total_bytes = (l.off_ln + streams * 2 * 64) * sizeof(float);
+  return l;
+}
+}  // namespace
+
+extern "C" size_t ttt_mlp_backward_workspace_bytes(const ttt_dims* d) {
+  if (check_dims(d) != TTT_OK || d->dtype != TTT_BF16) return 0;
+  return mlp_ws_layout(d).total_bytes;
+}
+
+extern "C" int ttt_mlp_backward(const ttt_dims* d, const void* xq, const void* xk, const void* xv, const void* w1,
+                                const void* b1, const void* w2, const void* b2, const void* token_eta,
+                                const void* ttt_lr_eta, const void* ln_weight, const void* ln_bias,
+                                const void* grad_output, void* grad_xq, void* grad_xk, void* grad_xv, void* grad_w1,
+                                void* grad_b1, void* grad_w2, void* grad_b2, void* grad_ttt_lr_eta,
+                                float* grad_token_eta, float* grad_ln_weight, float* grad_ln_bias, void* workspace,
+                                size_t workspace_bytes, void* status, void* stream) {
+  (void)status;
+  int rc = check_dims(d);
+  if (rc != TTT_OK) return rc;
+  if (d->dtype != TTT_BF16) return fail(TTT_ERR_UNSUPPORTED, "the TTT-MLP kernels are built for bf16 only");
+  const NamedPtr ptrs[] = {{"xq", xq}, {"xk", xk}, {"xv", xv}, {"w1", w1}, {"b1", b1}, {"w2", w2}, {"b2", b2},
+                           {"token_eta", token_eta}, {"ttt_lr_eta", ttt_lr_eta}, {"ln_weight", ln_weight},
+                           {"ln_bias", ln_bias}, {"grad_output", grad_output}, {"grad_xq", grad_xq},
+                           {"grad_xk", grad_xk}, {"grad_xv", grad_xv}, {"grad_w1", grad_w1}, {"grad_b1", grad_b1},
+                           {"grad_w2", grad_w2}, {"grad_b2", grad_b2}, {"grad_ttt_lr_eta", grad_ttt_lr_eta},
+                           {"grad_token_eta", grad_token_eta}, {"grad_ln_weight", grad_ln_weight},
+                           {"grad_ln_bias", grad_ln_bias}};
+  for (const NamedPtr& np : ptrs)
+    if (np.p == nullptr) return fail(TTT_ERR_NULL, "%s is null", np.name);
+  const MlpWsLayout l = mlp_ws_layout(d);
+  if (workspace == nullptr || workspace_bytes < l.total_bytes)
+    return fail(TTT_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", l.total_bytes, workspace_bytes);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return fail(TTT_ERR_ALIGN, "workspace is not 16-byte aligned");
+  float* ws = static_cast<float*>(workspace);
+  ttt::MlpBwdParams p;
+  p.xq = xq; p.xk = xk; p.xv = xv; p.w1 = w1; p.b1 = b1; p.w2 = w2; p.b2 = b2;
+  p.token_eta = token_eta; p.lr = ttt_lr_eta; p.ln_g = ln_weight; p.ln_b = ln_bias; p.d_out = grad_output;
+  p.d_q = grad_xq; p.d_k = grad_xk; p.d_v = grad_xv; p.d_w1 = grad_w1; p.d_b1 = grad_b1; p.d_w2 = grad_w2;
+  p.d_b2 = grad_b2; p.d_lr = grad_ttt_lr_eta; p.d_token_eta = grad_token_eta; p.d_ln_g = grad_ln_weight;
+  p.d_ln_b = grad_ln_bias;
+  p.workspace = ws;
+  p.ws_stride = l.stride_floats;
+  p.part_te = ws + l.off_te;
+  p.part_ln = ws + l.off_ln;
+  p.H = d->heads; p.T = d->seq_len; p.NS = d->seq_len / d->mini_batch; p.eps = d->epsilon;
+  cudaError_t e = ttt::launch_mlp_bwd(p, d->batch, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "MLP backward launch failed: %s", cudaGetErrorString(e));
+  return TTT_OK;
+}

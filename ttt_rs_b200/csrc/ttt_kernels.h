@@ -169,6 +169,41 @@ struct LinPartialParams {
 };
 cudaError_t launch_linear_partial(int dtype, const LinPartialParams& p, int nstreams, cudaStream_t st);
 
+// TTT-MLP backward (ttt_mlp_bwd.cu), bf16 I/O.
+struct MlpBwdParams {
+  const void* xq;  // [B,H,T,F]
+  const void* xk;
+  const void* xv;
+  const void* w1;  // [B,H,F,E]
+  const void* b1;  // [B,H,E]
+  const void* w2;  // [B,H,E,F]
+  const void* b2;  // [B,H,F]
+  const void* token_eta;
+  const void* lr;
+  const void* ln_g;
+  const void* ln_b;
+  const void* d_out;  // [B,H,T,F]
+  void* d_q;
+  void* d_k;
+  void* d_v;
+  void* d_w1;
+  void* d_b1;
+  void* d_w2;
+  void* d_b2;
+  void* d_lr;
+  float* d_token_eta;  // [T] float32
+  float* d_ln_g;       // [H,F] float32
+  float* d_ln_b;
+  float* workspace;    // per stream `ws_stride` floats: state, state gradients, saved inner gradients
+  size_t ws_stride;
+  float* part_te;      // [B*H][T]
+  float* part_ln;      // [B*H][2][F]
+  int H, T, NS;
+  float eps;
+};
+size_t mlp_bwd_ws_stride_floats(int T);
+cudaError_t launch_mlp_bwd(const MlpBwdParams& p, int B, cudaStream_t st);
+
 // bf16 only.  maps: q, k, v, out.
 cudaError_t launch_mlp_fwd(const CUtensorMap* maps, const MlpFwdParams& p, int nstreams, cudaStream_t st);
 

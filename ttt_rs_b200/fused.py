@@ -450,3 +450,43 @@ def fused_ttt_mlp_forward(xq, xk, xv, state: TTTMLPState, token_eta, ttt_lr_eta,
         _ptr(out), _ptr(new.w1), _ptr(new.b1), _ptr(new.w2), _ptr(new.b2), _ptr(status), _stream_ptr(dev))
     _lib.check(rc)
     return out, new
+
+
+def fused_ttt_mlp_backward(xq, xk, xv, state: TTTMLPState, token_eta, ttt_lr_eta, ln_weight, ln_bias, grad_output,
+                           config: FusedTttConfig):
+    """Gradient of `fused_ttt_mlp_forward` for loss = <grad_output, output> (`ttt_mlp_backward`; `state` is the state
+    the forward started from).  Returns a dict: grad_xq, grad_xk, grad_xv, grad_w1, grad_b1, grad_w2, grad_b2 (per
+    batch element), grad_ttt_lr_eta, and float32 grad_token_eta [T], grad_ln_weight, grad_ln_bias [H, F]."""
+    lib = _lib.load()
+    if not xq.is_cuda:
+        raise TttError(_lib.TTT_ERR_CUDA, "inputs must be CUDA tensors: this operator has no CPU path")
+    d = _dims(xq, config)
+    B, H, T, F = xq.shape
+    E = 4 * F
+    dt, dev = xq.dtype, xq.device
+    ts = dict(xq=xq, xk=xk, xv=xv, w1=state.w1, b1=state.b1, w2=state.w2, b2=state.b2, token_eta=token_eta,
+              ttt_lr_eta=ttt_lr_eta, ln_weight=ln_weight, ln_bias=ln_bias, grad_output=grad_output)
+    shapes = dict(xq=(B, H, T, F), xk=(B, H, T, F), xv=(B, H, T, F), w1=(B, H, F, E), b1=(B, H, E), w2=(B, H, E, F),
+                  b2=(B, H, F), token_eta=(token_eta.shape[0],), ttt_lr_eta=(B, H, T), ln_weight=(H, F), ln_bias=(H, F),
+                  grad_output=(B, H, T, F))
+    ts = {k: v.contiguous() for k, v in ts.items()}
+    for k, v in ts.items():
+        _expect(k, v, shapes[k], dt, dev)
+    g = {"grad_" + k: torch.empty_like(ts[k]) for k in ("xq", "xk", "xv", "w1", "b1", "w2", "b2", "ttt_lr_eta")}
+    g["grad_token_eta"] = torch.empty(T, dtype=torch.float32, device=dev)
+    g["grad_ln_weight"] = torch.empty(H, F, dtype=torch.float32, device=dev)
+    g["grad_ln_bias"] = torch.empty(H, F, dtype=torch.float32, device=dev)
+    ws_bytes = lib.ttt_mlp_backward_workspace_bytes(C.byref(d))
+    if ws_bytes == 0:
+        raise TttError(_lib.TTT_ERR_SHAPE, _lib.last_error() or "unsupported problem for the TTT-MLP backward")
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    names_in = ("xq", "xk", "xv", "w1", "b1", "w2", "b2", "token_eta", "ttt_lr_eta", "ln_weight", "ln_bias",
+                "grad_output")
+    names_out = ("grad_xq", "grad_xk", "grad_xv", "grad_w1", "grad_b1", "grad_w2", "grad_b2", "grad_ttt_lr_eta",
+                 "grad_token_eta", "grad_ln_weight", "grad_ln_bias")
+    with torch.cuda.device(dev):
+        rc = lib.ttt_mlp_backward(C.byref(d), *[_ptr(ts[k]) for k in names_in], *[_ptr(g[k]) for k in names_out],
+                                  _ptr(ws), ws_bytes, None, _stream_ptr(dev))
+    _lib.check(rc)
+    g["_workspace"] = ws  # keeps the scratch alive until the caller drops the result
+    return g
