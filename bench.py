@@ -45,6 +45,8 @@ WORKLOADS = {
                      desc="TTT-Linear inner loop fwd+bwd, f32, B=32 H=12 T=2048 d=64 mb=16 ckpt=16"),
     "cfg2-fwd": dict(B=16, H=12, T=2048, dtype="bf16", K=1, backward=False, inner="mlp",
                      desc="TTT-MLP inner loop fwd (64-256-64, GELU tanh), bf16, B=16 H=12 T=2048 d=64 mb=16"),
+    "cfg2": dict(B=16, H=12, T=2048, dtype="bf16", K=1, backward=True, inner="mlp",
+                 desc="TTT-MLP inner loop fwd+bwd (64-256-64, GELU tanh), bf16, B=16 H=12 T=2048 d=64 mb=16"),
     "cfg4-8k": dict(B=8, H=32, T=8192, dtype="bf16", K=16, backward=True,
                     desc="TTT-Linear inner loop fwd+bwd, bf16, B=8 H=32 T=8192 d=64 mb=16 ckpt=16"),
     "cfg4-16k": dict(B=8, H=32, T=16384, dtype="bf16", K=16, backward=True,
@@ -81,6 +83,8 @@ def algorithmic_bytes(w, fwd=True, bwd=True):
     if w.get("inner") == "mlp":  # no saved state; the per-stream state is W1, b1, W2, b2 read and written once
         fb = (4 * F * s + s) * tok_heads + streams * 2 * (2 * F * 4 * F + 4 * F + F) * s
     bb = (7 * F * s + 2 * s + ck) * tok_heads + streams * (F * F + F) * s
+    if w.get("inner") == "mlp":  # backward: q,k,v,d_out in, dq,dk,dv out, lr in, dlr out; state in, state gradient out
+        bb = (7 * F * s + 2 * s) * tok_heads + streams * 2 * (2 * F * 4 * F + 4 * F + F) * s
     return (fb if fwd else 0) + (bb if bwd else 0), fb, bb
 
 
@@ -155,7 +159,10 @@ def cpu_step(t, w):
     """One step of the CPU restatement on a host-resident sample (float32)."""
     from oracle import ttt_oracle as O
     if w.get("inner") == "mlp":
-        return O.ttt_mlp_forward(*[t[k] for k in MLP_IN], mini_batch=CS, eps=1e-6)
+        fw = O.ttt_mlp_forward(*[t[k] for k in MLP_IN], mini_batch=CS, eps=1e-6)
+        if w["backward"]:
+            O.ttt_mlp_backward(*[t[k] for k in MLP_IN], t["grad_output"], mini_batch=CS, eps=1e-6)
+        return fw
     args = [t[k] for k in LIN_IN]
     fw = O.ttt_linear_forward(*args, mini_batch=CS, eps=1e-6, checkpoint_interval=w["K"])
     if w["backward"]:
@@ -496,7 +503,12 @@ def main():
         if record:
             e[1].record()
         g = None
-        if w["backward"]:
+        if w["backward"] and mlp:
+            g = tb.fused_ttt_mlp_backward(md["xq"], md["xk"], md["xv"], mstate, md["token_eta"], md["ttt_lr_eta"],
+                                          md["ln_weight"], md["ln_bias"], go, cfg)
+            if record:
+                e[2].record()
+        elif w["backward"]:
             i = step_no[0] % 2
             step_no[0] += 1
             if pending[i] is not None:
@@ -555,7 +567,7 @@ def main():
 
     peak, peak_kind = measured_peaks()
     total_b, fb, bb = algorithmic_bytes(w, True, w["backward"])
-    dom_ms, dom_bytes, dom_name = (bwd_ms, bb, "ttt_linear_bwd_kernel") if w["backward"] else (fwd_ms, fb, "ttt_mlp_fwd_kernel" if mlp else "ttt_linear_fwd_kernel")
+    dom_ms, dom_bytes, dom_name = (bwd_ms, bb, "ttt_mlp_bwd_kernel" if mlp else "ttt_linear_bwd_kernel") if w["backward"] else (fwd_ms, fb, "ttt_mlp_fwd_kernel" if mlp else "ttt_linear_fwd_kernel")
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
     # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum) from the committed
     # ncu summary of this same command under profiles/; other workloads have no capture
@@ -574,7 +586,7 @@ def main():
             "config": {"workload": w["desc"], "global_batch": w["B"] * world, "parallelism": f"streams-dp{world}",
                        "l2": "inputs exceed L2: each step streams %.0f MB of operands" % (total_b / 1e6)},
             "clocks": clocks, "e2e": e2e,
-            "gpu_launches": args.steps * (4 if w["backward"] else 1),
+            "gpu_launches": args.steps * ((3 if mlp else 4) if w["backward"] else 1),
             "roofline": roof,
         }
         if world == 1 and not args.no_cpu_baseline:

@@ -703,7 +703,6 @@ extern "C" int ttt_mlp_backward(const ttt_dims* d, const void* xq, const void* x
                                 void* grad_b1, void* grad_w2, void* grad_b2, void* grad_ttt_lr_eta,
                                 float* grad_token_eta, float* grad_ln_weight, float* grad_ln_bias, void* workspace,
                                 size_t workspace_bytes, void* status, void* stream) {
-  (void)status;
   int rc = check_dims(d);
   if (rc != TTT_OK) return rc;
   if (d->dtype != TTT_BF16) return fail(TTT_ERR_UNSUPPORTED, "the TTT-MLP kernels are built for bf16 only");
@@ -731,6 +730,7 @@ extern "C" int ttt_mlp_backward(const ttt_dims* d, const void* xq, const void* x
   p.ws_stride = l.stride_floats;
   p.part_te = ws + l.off_te;
   p.part_ln = ws + l.off_ln;
+  p.trace = static_cast<unsigned int*>(status);  // only instrumented builds write here (16 words)
   p.H = d->heads; p.T = d->seq_len; p.NS = d->seq_len / d->mini_batch; p.eps = d->epsilon;
   cudaError_t e = ttt::launch_mlp_bwd(p, d->batch, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "MLP backward launch failed: %s", cudaGetErrorString(e));

@@ -198,6 +198,7 @@ struct MlpBwdParams {
   size_t ws_stride;
   float* part_te;      // [B*H][T]
   float* part_ln;      // [B*H][2][F]
+  unsigned int* trace;  // optional 16 words (per-phase cycle counts of block 0 in instrumented builds), else null
   int H, T, NS;
   float eps;
 };

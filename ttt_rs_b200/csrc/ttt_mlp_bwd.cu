@@ -23,53 +23,104 @@ namespace ttt {
 
 constexpr int MB_THREADS = 256;
 constexpr int MB_E = 256;  // hidden width of the inner MLP (4 * head_dim)
+// Row strides of the shared-memory tiles: width + 8 floats.  With a stride of 8 (mod 32) the 64-bit fragment loads of
+// a half-warp (4 rows x 4 column pairs) fall in 16 distinct bank pairs; unpadded rows would put the 8 rows of a
+// fragment in the same bank (8-way conflicts on every operand load).
+constexpr int EP = MB_E + 8, FP = HD + 8, CP = CS + 8;
 constexpr float GELU_C0 = 0.7978845608028654f, GELU_C1 = 0.044715f;
 
-struct Mat {  // element (i, j) at p[i * rs + j * cs]
+// A float32 matrix view with compile-time strides: element (i, j) at p[i * RS + j * CS_] (shared or global memory).
+template <int RS, int CS_>
+struct MatT {
   float* p;
-  int rs, cs;
+  static constexpr int rs = RS, cs = CS_;
 };
-__device__ __forceinline__ Mat mat(float* p, int rs, int cs = 1) { return Mat{p, rs, cs}; }
-__device__ __forceinline__ Mat tr(const Mat& m) { return Mat{m.p, m.cs, m.rs}; }
-__device__ __forceinline__ float at(const Mat& m, int i, int j) { return m.p[(size_t)i * m.rs + (size_t)j * m.cs]; }
+template <int RS, int CS_>
+__device__ __forceinline__ MatT<CS_, RS> tr(const MatT<RS, CS_> m) { return MatT<CS_, RS>{m.p}; }
+// the pair (i, k), (i, k+1) of an A operand / the pair (k, j), (k+1, j) of a B operand: one 64-bit load when the
+// pair is contiguous in memory (k even, strides even, bases 8-byte aligned)
+template <class MA>
+__device__ __forceinline__ float2 pair_k_of_A(const MA m, int i, int k) {
+  const float* q = m.p + i * MA::rs + k * MA::cs;
+  if constexpr (MA::cs == 1) return *reinterpret_cast<const float2*>(q);
+  else return make_float2(q[0], q[MA::cs]);
+}
+template <class MB>
+__device__ __forceinline__ float2 pair_k_of_B(const MB m, int k, int j) {
+  const float* q = m.p + k * MB::rs + j * MB::cs;
+  if constexpr (MB::rs == 1) return *reinterpret_cast<const float2*>(q);
+  else return make_float2(q[0], q[MB::rs]);
+}
 
-// C[M x N] = (ACC ? C : 0) + alpha * A[M x K] . B[K x N];  M % 16 == 0, N % 8 == 0, K % 16 == 0.
+// C[M x N] = (ACC ? C : 0) + alpha * A[M x K] . B[K x N];  M % 16 == 0, N % 8 == 0, K in {16, 64, 256}; every
+// extent and stride is a compile-time constant, so operand addresses are a lane offset plus immediates.
 // Output tiles of 16 x 8 are dealt to the warps round-robin (the same tile always goes to the same warp, so
-// successive accumulations into one matrix need no barrier between them).
-template <bool ACC>
-__device__ void tile_mma(const Mat C, const Mat A, const Mat B, int M, int N, int K, float alpha) {
+// successive accumulations into one matrix need no barrier between them).  A warp works on up to four of its tiles
+// at a time with the contraction loop unrolled by two, so that the operand loads of several fragments (many of them
+// from the L2-resident state in the workspace) are in flight together.
+template <bool ACC, int K, int M, int N, class MC, class MA, class MB>
+__device__ void tile_mma(const MC C, const MA A, const MB B, float alpha) {
+  constexpr int NW = MB_THREADS / 32, ntn = N / 8, total = (M / 16) * ntn;
+  constexpr int TG = total >= 4 * NW ? 4 : (total + NW - 1) / NW;  // tiles of a warp in flight together
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int ntn = N >> 3, total = (M >> 4) * ntn;
-  for (int tile = warp; tile < total; tile += MB_THREADS / 32) {
-    const int mt = tile / ntn, nt = tile - mt * ntn;
-    const int i0 = 16 * mt + g, j0 = 8 * nt;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+  for (int tile0 = warp; tile0 < total; tile0 += NW * TG) {
+    int i0[TG], j0[TG];
+    bool on[TG];
+    float acc[TG][4], cin[TG][4];
+#pragma unroll
+    for (int u = 0; u < TG; ++u) {
+      const int tile = tile0 + u * NW;
+      on[u] = tile < total;
+      const int tl = on[u] ? tile : tile0, mt = tl / ntn;
+      i0[u] = 16 * mt + g;
+      j0[u] = 8 * (tl - mt * ntn);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        acc[u][q] = 0.f;
+        cin[u][q] = (ACC && on[u]) ? C.p[(i0[u] + 8 * (q >> 1)) * MC::rs + (j0[u] + 2 * t + (q & 1)) * MC::cs] : 0.f;
+      }
+    }
+#pragma unroll(K >= 64 ? 2 : 1)
     for (int k0 = 0; k0 < K; k0 += 16) {
       const int ka = k0 + 2 * t, kb = ka + 8;
-      const uint32_t a0 = pack_bf16(at(A, i0, ka), at(A, i0, ka + 1));
-      const uint32_t a1 = pack_bf16(at(A, i0 + 8, ka), at(A, i0 + 8, ka + 1));
-      const uint32_t a2 = pack_bf16(at(A, i0, kb), at(A, i0, kb + 1));
-      const uint32_t a3 = pack_bf16(at(A, i0 + 8, kb), at(A, i0 + 8, kb + 1));
-      const uint32_t b0 = pack_bf16(at(B, ka, j0 + g), at(B, ka + 1, j0 + g));
-      const uint32_t b1 = pack_bf16(at(B, kb, j0 + g), at(B, kb + 1, j0 + g));
-      mma_bf16(acc, a0, a1, a2, a3, b0, b1);
+      float2 fa[TG][4], fb[TG][2];
+#pragma unroll
+      for (int u = 0; u < TG; ++u) {
+        fa[u][0] = pair_k_of_A(A, i0[u], ka);
+        fa[u][1] = pair_k_of_A(A, i0[u] + 8, ka);
+        fa[u][2] = pair_k_of_A(A, i0[u], kb);
+        fa[u][3] = pair_k_of_A(A, i0[u] + 8, kb);
+        fb[u][0] = pair_k_of_B(B, ka, j0[u] + g);
+        fb[u][1] = pair_k_of_B(B, kb, j0[u] + g);
+      }
+#pragma unroll
+      for (int u = 0; u < TG; ++u)
+        mma_bf16(acc[u], pack_bf16(fa[u][0].x, fa[u][0].y), pack_bf16(fa[u][1].x, fa[u][1].y),
+                 pack_bf16(fa[u][2].x, fa[u][2].y), pack_bf16(fa[u][3].x, fa[u][3].y),
+                 pack_bf16(fb[u][0].x, fb[u][0].y), pack_bf16(fb[u][1].x, fb[u][1].y));
     }
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const int i = i0 + 8 * (q >> 1), j = j0 + 2 * t + (q & 1);
-      float* c = C.p + (size_t)i * C.rs + (size_t)j * C.cs;
-      *c = (ACC ? *c : 0.f) + alpha * acc[q];
-    }
+    for (int u = 0; u < TG; ++u)
+      if (on[u]) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float* c = C.p + (i0[u] + 8 * (q >> 1)) * MC::rs + (j0[u] + 2 * t + (q & 1)) * MC::cs;
+          *c = cin[u][q] + alpha * acc[u][q];
+        }
+      }
   }
 }
 
-__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.f + tanhf(GELU_C0 * x * (1.f + GELU_C1 * x * x))); }
+// tanh(x) = 1 - 2 / (1 + e^{2x}) with the fast exponential and division (relative error ~1e-6, as in the forward kernel)
+__device__ __forceinline__ float tanh_fast(float x) { return 1.f - __fdividef(2.f, 1.f + __expf(2.f * x)); }
+__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.f + tanh_fast(GELU_C0 * x * (1.f + GELU_C1 * x * x))); }
 __device__ __forceinline__ float gelu_d1(float x) {
-  const float th = tanhf(GELU_C0 * x * (1.f + GELU_C1 * x * x));
+  const float th = tanh_fast(GELU_C0 * x * (1.f + GELU_C1 * x * x));
   return 0.5f * x * ((1.f - th * th) * (GELU_C0 + 3.f * GELU_C0 * GELU_C1 * x * x)) + 0.5f * (1.f + th);
 }
 __device__ __forceinline__ float gelu_d2(float x) {
-  const float th = tanhf(GELU_C0 * x * (1.f + GELU_C1 * x * x));
+  const float th = tanh_fast(GELU_C0 * x * (1.f + GELU_C1 * x * x));
   const float du = GELU_C0 * (1.f + 3.f * GELU_C1 * x * x), d2u = 6.f * GELU_C0 * GELU_C1 * x;
   return (1.f - th * th) * du + 0.5f * x * (1.f - th * th) * (d2u - 2.f * th * du * du);
 }
@@ -80,36 +131,21 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-// Shared-memory tiles (float32, row-major [16][N]).
+// Shared-memory tiles (float32, [16][width + 8]).
 struct MlpBwdSmem {
-  float z1[CS][MB_E], x2[CS][MB_E], hm[CS][MB_E], g1[CS][MB_E], z1b[CS][MB_E], x2b[CS][MB_E];
-  float t1[CS][MB_E], t2[CS][MB_E], t3[CS][MB_E], t4[CS][MB_E];  // dx2b/dz1b, dg1/dh, dx2, dz1 (+ scratch in pass 1)
-  float q[CS][HD], k[CS][HD], v[CS][HD], dO[CS][HD];
-  float z2[CS][HD], g2[CS][HD], z2b[CS][HD], dz2b[CS][HD], dg2[CS][HD], dz2[CS][HD], dq[CS][HD], dk[CS][HD], gl1[CS][HD];
-  float eta[CS][CS], a1[CS][CS], a2[CS][CS], m1[CS][CS], m2[CS][CS], dm[CS][CS], da[CS][CS], deta[CS][CS];
-  float lr[CS], te[CS], ell[CS], dell[CS], mean[CS], rstd[CS];
-  float colpart[8][2 * HD];  // per-warp partial column sums (fixed-order combine)
+  float z1[CS][EP], x2[CS][EP], g1[CS][EP], z1b[CS][EP], x2b[CS][EP];
+  float t1[CS][EP], t2[CS][EP], t3[CS][EP], t4[CS][EP];  // dx2b/dz1b, dg1/dh, dx2, dz1 (+ scratch)
+  float q[CS][FP], k[CS][FP], v[CS][FP], dO[CS][FP];
+  float z2[CS][FP], g2[CS][FP], z2b[CS][FP], dz2b[CS][FP], dg2[CS][FP], dz2[CS][FP], dk[CS][FP], gl1[CS][FP];
+  float eta[CS][CP], a1[CS][CP], a2[CS][CP], m1[CS][CP], m2[CS][CP], dm[CS][CP], da[CS][CP], deta[CS][CP];
+  float lr[CS], te[CS], ell[CS], dell[CS];
+  float b1[MB_E], db1[MB_E], b2[HD], db2[HD];  // biases and their gradients stay on chip for the whole walk
   float dgam[HD], dbet[HD];  // this stream's LayerNorm parameter gradients
 };
-
-// mean and 1/sqrt(var + eps) of every row of a [16][64] tile (two-pass variance); warp w takes rows 2w, 2w+1
-__device__ void row_stats64(const float (*x)[HD], float* mean, float* rstd, float eps) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#pragma unroll
-  for (int rr = 0; rr < 2; ++rr) {
-    const int r = 2 * warp + rr;
-    const float a = x[r][lane], b = x[r][lane + 32];
-    const float mu = warp_sum(a + b) * (1.f / HD);
-    const float var = warp_sum((a - mu) * (a - mu) + (b - mu) * (b - mu)) * (1.f / HD);
-    if (lane == 0) {
-      mean[r] = mu;
-      rstd[r] = 1.f / sqrtf(var + eps);
-    }
-  }
-}
+static_assert(sizeof(MlpBwdSmem) + 1024 <= 227 * 1024, "shared-memory tiles exceed one SM");
 
 // G = d/dz of 0.5 |LN(z) - (v - k)|^2 for a [16][64] tile (rust/core/src/util.rs:155-182)
-__device__ void ln_l2_grad_tile(MlpBwdSmem& S, const float (*z)[HD], float (*G)[HD], const float* gam, const float* bet,
+__device__ void ln_l2_grad_tile(MlpBwdSmem& S, const float (*z)[FP], float (*G)[FP], const float* gam, const float* bet,
                                 float eps) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll
@@ -136,20 +172,34 @@ __device__ void ln_l2_grad_tile(MlpBwdSmem& S, const float (*z)[HD], float (*G)[
   }
 }
 
-// column sums of a [16][N] tile (optionally scaled per row) added, with sign, to dst[N] (global or shared)
-__device__ void add_colsum(float* dst, const float* tile, int N, const float* rowscale, float sign) {
+// column sums of a [16][N] tile (row stride ld) added, with sign, to dst[N]
+__device__ void add_colsum(float* dst, const float* tile, int N, int ld, float sign) {
   for (int c = threadIdx.x; c < N; c += MB_THREADS) {
     float s = 0.f;
 #pragma unroll
-    for (int r = 0; r < CS; ++r) s += tile[r * N + c] * (rowscale ? rowscale[r] : 1.f);
+    for (int r = 0; r < CS; ++r) s += tile[r * ld + c];
     dst[c] += sign * s;
   }
 }
 
-__device__ void load_tile_bf16(float (*dst)[HD], const __nv_bfloat16* src) {
-  for (int e = threadIdx.x; e < CS * HD; e += MB_THREADS) dst[e / HD][e % HD] = __bfloat162float(src[e]);
+// Up to four [16][64] bf16 tiles from global memory into float32 shared tiles: every thread owns four consecutive
+// elements (one 8-byte load) of each tile, and all loads are issued before the first value is used (a load that
+// waits behind the previous tile's dependent stores would cost a full memory round trip per tile).
+template <int NT>
+__device__ void load_tiles_bf16(float (*const (&dst)[NT])[FP], const __nv_bfloat16* const (&src)[NT]) {
+  const int e = 4 * threadIdx.x, r = e / HD, c = e % HD;
+  uint2 raw[NT];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) raw[i] = *reinterpret_cast<const uint2*>(src[i] + e);
+#pragma unroll
+  for (int i = 0; i < NT; ++i) {
+    dst[i][r][c] = bf16_lo(raw[i].x);
+    dst[i][r][c + 1] = bf16_hi(raw[i].x);
+    dst[i][r][c + 2] = bf16_lo(raw[i].y);
+    dst[i][r][c + 3] = bf16_hi(raw[i].y);
+  }
 }
-__device__ void store_tile_bf16(__nv_bfloat16* dst, const float (*src)[HD]) {
+__device__ void store_tile_bf16(__nv_bfloat16* dst, const float (*src)[FP]) {
   for (int e = threadIdx.x; e < CS * HD; e += MB_THREADS) dst[e] = __float2bfloat16_rn(src[e / HD][e % HD]);
 }
 
@@ -167,11 +217,11 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
   float* W2 = W1 + F * E;
   float* dW1 = W2 + E * F;
   float* dW2 = dW1 + F * E;
-  float* b1 = dW2 + E * F;
-  float* b2 = b1 + E;
-  float* db1 = b2 + F;
-  float* db2 = db1 + E;
-  float* g1p_all = db2 + F;
+  float* g1p_all = dW2 + E * F + 2 * (E + F);  // (2 (E + F) floats of the stride are unused)
+  float* const b1 = S.b1;
+  float* const b2 = S.b2;
+  float* const db1 = S.db1;
+  float* const db2 = S.db2;
   float* g2p_all = g1p_all + (size_t)NS * CS * E;
 
   __shared__ float gam[HD], bet[HD];
@@ -198,135 +248,164 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
   }
   __syncthreads();
   const float te_last = S.te[CS - 1];
+#ifdef TTT_MLP_TRACE
+  unsigned long long tr_acc[16] = {0}, tr_last = clock64();
+#define TRM(i) { __syncthreads(); const unsigned long long n_ = clock64(); tr_acc[i] += n_ - tr_last; tr_last = n_; }
+#else
+#define TRM(i)
+#endif
 
-  const Mat mW1 = mat(W1, E), mW2 = mat(W2, F), mdW1 = mat(dW1, E), mdW2 = mat(dW2, F);
-  const Mat mK = mat(&S.k[0][0], HD), mQ = mat(&S.q[0][0], HD);
-  const Mat mz1 = mat(&S.z1[0][0], E), mx2 = mat(&S.x2[0][0], E), mh = mat(&S.hm[0][0], E), mg1 = mat(&S.g1[0][0], E);
-  const Mat mz1b = mat(&S.z1b[0][0], E), mx2b = mat(&S.x2b[0][0], E);
-  const Mat mt1 = mat(&S.t1[0][0], E), mt2 = mat(&S.t2[0][0], E), mt3 = mat(&S.t3[0][0], E), mt4 = mat(&S.t4[0][0], E);
-  const Mat mz2 = mat(&S.z2[0][0], HD), mg2 = mat(&S.g2[0][0], HD), mz2b = mat(&S.z2b[0][0], HD);
-  const Mat mdz2b = mat(&S.dz2b[0][0], HD), mdg2 = mat(&S.dg2[0][0], HD), mdz2 = mat(&S.dz2[0][0], HD);
-  const Mat mdq = mat(&S.dq[0][0], HD), mdk = mat(&S.dk[0][0], HD), mgl1 = mat(&S.gl1[0][0], HD);
-  const Mat ma1 = mat(&S.a1[0][0], CS), ma2 = mat(&S.a2[0][0], CS), mm1 = mat(&S.m1[0][0], CS), mm2 = mat(&S.m2[0][0], CS);
-  const Mat mdm = mat(&S.dm[0][0], CS), mda = mat(&S.da[0][0], CS);
+  const MatT<MB_E, 1> mW1{W1}, mdW1{dW1};
+  const MatT<HD, 1> mW2{W2}, mdW2{dW2};
+  const MatT<FP, 1> mK{&S.k[0][0]}, mQ{&S.q[0][0]};
+  const MatT<EP, 1> mz1{&S.z1[0][0]}, mx2{&S.x2[0][0]}, mg1{&S.g1[0][0]}, mz1b{&S.z1b[0][0]}, mx2b{&S.x2b[0][0]};
+  const MatT<EP, 1> mt1{&S.t1[0][0]}, mt2{&S.t2[0][0]}, mt3{&S.t3[0][0]}, mt4{&S.t4[0][0]};
+  const MatT<FP, 1> mz2{&S.z2[0][0]}, mg2{&S.g2[0][0]}, mz2b{&S.z2b[0][0]};
+  const MatT<FP, 1> mdz2b{&S.dz2b[0][0]}, mdg2{&S.dg2[0][0]}, mdz2{&S.dz2[0][0]}, mdk{&S.dk[0][0]}, mgl1{&S.gl1[0][0]};
+  const MatT<FP, 1> mdq = mz2b;  // z2b is dead once the output LayerNorm has been differentiated: its tile then holds dq
+  float(*const dq)[FP] = S.z2b;
+  const MatT<CP, 1> ma1{&S.a1[0][0]}, ma2{&S.a2[0][0]}, mm1{&S.m1[0][0]}, mm2{&S.m2[0][0]}, mdm{&S.dm[0][0]}, mda{&S.da[0][0]};
 
-  // z1 = K W1 + b1, x2 = gelu(z1), z2 = x2 W2 + b2, g2, h = g2 W2^T, g1 = h o gelu'(z1)   (from the state in the workspace)
+// element-wise loops over a [16][E] / [16][F] / [16][16] tile: r = row (token), c = column
+#define FOR_E(r, c) for (int e_ = tid, r = e_ / MB_E, c = e_ % MB_E; e_ < CS * MB_E; e_ += MB_THREADS, r = e_ / MB_E, c = e_ % MB_E)
+#define FOR_F(r, c) for (int e_ = tid, r = e_ / HD, c = e_ % HD; e_ < CS * HD; e_ += MB_THREADS, r = e_ / HD, c = e_ % HD)
+#define FOR_C(r, c) for (int e_ = tid, r = e_ / CS, c = e_ % CS; e_ < CS * CS; e_ += MB_THREADS, r = e_ / CS, c = e_ % CS)
+
+  // z1 = K W1 + b1, x2 = gelu(z1), z2 = x2 W2 + b2, g2, g1 = (g2 W2^T) o gelu'(z1)   (from the state in the workspace)
   auto inner_forward = [&]() {
-    tile_mma<false>(mz1, mK, mW1, CS, E, F, 1.f);
+    tile_mma<false, HD, CS, MB_E>(mz1, mK, mW1, 1.f);
     __syncthreads();
-    for (int e = tid; e < CS * E; e += MB_THREADS) {
-      const float z = S.z1[0][e] + b1[e % E];
-      S.z1[0][e] = z;
-      S.x2[0][e] = gelu_f(z);
+    FOR_E(r, c) {
+      const float z = S.z1[r][c] + b1[c];
+      S.z1[r][c] = z;
+      S.x2[r][c] = gelu_f(z);
     }
     __syncthreads();
-    tile_mma<false>(mz2, mx2, mW2, CS, F, E, 1.f);
+    tile_mma<false, MB_E, CS, HD>(mz2, mx2, mW2, 1.f);
     __syncthreads();
-    for (int e = tid; e < CS * F; e += MB_THREADS) S.z2[0][e] += b2[e % F];
+    FOR_F(r, c) S.z2[r][c] += b2[c];
     __syncthreads();
     ln_l2_grad_tile(S, S.z2, S.g2, gam, bet, p.eps);
     __syncthreads();
-    tile_mma<false>(mh, mg2, tr(mW2), CS, E, F, 1.f);
+    tile_mma<false, HD, CS, MB_E>(mg1, mg2, tr(mW2), 1.f);
     __syncthreads();
-    for (int e = tid; e < CS * E; e += MB_THREADS) S.g1[0][e] = S.hm[0][e] * gelu_d1(S.z1[0][e]);
+    FOR_E(r, c) S.g1[r][c] *= gelu_d1(S.z1[r][c]);
     __syncthreads();
   };
 
   // ============================== pass 1: forward walk, saving g1p and g2p ==============================
   for (int s = 0; s < NS; ++s) {
     const size_t r0 = (row_base + (size_t)s * CS) * HD;
-    load_tile_bf16(S.k, static_cast<const T*>(p.xk) + r0);
-    load_tile_bf16(S.v, static_cast<const T*>(p.xv) + r0);
+    {
+      float(*const dst[2])[FP] = {S.k, S.v};
+      const T* const src[2] = {static_cast<const T*>(p.xk) + r0, static_cast<const T*>(p.xv) + r0};
+      load_tiles_bf16<2>(dst, src);
+    }
     if (tid < CS) S.ell[tid] = te_last * ld_as_float<T>(p.lr, row_base + (size_t)s * CS + tid);
     __syncthreads();
+    TRM(0)
     inner_forward();
+    TRM(1)
     float* g1p = g1p_all + (size_t)s * CS * E;
     float* g2p = g2p_all + (size_t)s * CS * F;
-    for (int e = tid; e < CS * E; e += MB_THREADS) {
-      const float v_ = S.ell[e / E] * S.g1[0][e];
-      g1p[e] = v_;
-      S.t1[0][e] = v_;
+    FOR_E(r, c) {
+      const float v_ = S.ell[r] * S.g1[r][c];
+      g1p[e_] = v_;
+      S.t1[r][c] = v_;
     }
-    for (int e = tid; e < CS * F; e += MB_THREADS) {
-      const float v_ = S.ell[e / F] * S.g2[0][e];
-      g2p[e] = v_;
-      S.dg2[0][e] = v_;
+    FOR_F(r, c) {
+      const float v_ = S.ell[r] * S.g2[r][c];
+      g2p[e_] = v_;
+      S.dg2[r][c] = v_;
     }
     __syncthreads();
-    tile_mma<true>(mW1, tr(mK), mt1, F, E, CS, -1.f);   // W1 -= K^T g1p
-    tile_mma<true>(mW2, tr(mx2), mdg2, E, F, CS, -1.f);  // W2 -= X2^T g2p
-    add_colsum(b1, &S.t1[0][0], E, nullptr, -1.f);
-    add_colsum(b2, &S.dg2[0][0], F, nullptr, -1.f);
+    tile_mma<true, CS, HD, MB_E>(mW1, tr(mK), mt1, -1.f);   // W1 -= K^T g1p
+    tile_mma<true, CS, MB_E, HD>(mW2, tr(mx2), mdg2, -1.f);  // W2 -= X2^T g2p
+    add_colsum(b1, &S.t1[0][0], E, EP, -1.f);
+    add_colsum(b2, &S.dg2[0][0], F, FP, -1.f);
     __syncthreads();
+    TRM(2)
   }
 
   // ============================== pass 2: backward walk ==============================
   for (int s = NS - 1; s >= 0; --s) {
     const size_t r0 = (row_base + (size_t)s * CS) * HD;
-    load_tile_bf16(S.q, static_cast<const T*>(p.xq) + r0);
-    load_tile_bf16(S.k, static_cast<const T*>(p.xk) + r0);
-    load_tile_bf16(S.v, static_cast<const T*>(p.xv) + r0);
-    load_tile_bf16(S.dO, static_cast<const T*>(p.d_out) + r0);
+    const float* g1p = g1p_all + (size_t)s * CS * E;
+    const float* g2p = g2p_all + (size_t)s * CS * F;
+    {
+      // every global load of the stage's inputs is issued before the first dependent store
+      float4 g1v[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) g1v[i] = reinterpret_cast<const float4*>(g1p)[tid + MB_THREADS * i];
+      const float4 g2v = reinterpret_cast<const float4*>(g2p)[tid];
+      float(*const dst[4])[FP] = {S.q, S.k, S.v, S.dO};
+      const T* const src[4] = {static_cast<const T*>(p.xq) + r0, static_cast<const T*>(p.xk) + r0,
+                               static_cast<const T*>(p.xv) + r0, static_cast<const T*>(p.d_out) + r0};
+      load_tiles_bf16<4>(dst, src);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int e = 4 * (tid + MB_THREADS * i), r = e / MB_E, c = e % MB_E;
+        S.t1[r][c] = g1v[i].x; S.t1[r][c + 1] = g1v[i].y; S.t1[r][c + 2] = g1v[i].z; S.t1[r][c + 3] = g1v[i].w;
+      }
+      const int e = 4 * tid, r = e / HD, c = e % HD;
+      S.dg2[r][c] = g2v.x; S.dg2[r][c + 1] = g2v.y; S.dg2[r][c + 2] = g2v.z; S.dg2[r][c + 3] = g2v.w;
+    }
     if (tid < CS) {
       S.lr[tid] = ld_as_float<T>(p.lr, row_base + (size_t)s * CS + tid);
       S.ell[tid] = te_last * S.lr[tid];
     }
-    const float* g1p = g1p_all + (size_t)s * CS * E;
-    const float* g2p = g2p_all + (size_t)s * CS * F;
-    for (int e = tid; e < CS * E; e += MB_THREADS) S.t1[0][e] = g1p[e];
-    for (int e = tid; e < CS * F; e += MB_THREADS) S.dg2[0][e] = g2p[e];
     __syncthreads();
+    TRM(3)
     // ---- state at the start of this stage: undo the stage's updates (W1 first: X2 depends on it)
-    tile_mma<true>(mW1, tr(mK), mt1, F, E, CS, 1.f);
-    add_colsum(b1, &S.t1[0][0], E, nullptr, 1.f);
+    tile_mma<true, CS, HD, MB_E>(mW1, tr(mK), mt1, 1.f);
+    add_colsum(b1, &S.t1[0][0], E, EP, 1.f);
     __syncthreads();
-    tile_mma<false>(mz1, mK, mW1, CS, E, F, 1.f);
+    tile_mma<false, HD, CS, MB_E>(mz1, mK, mW1, 1.f);
     __syncthreads();
-    for (int e = tid; e < CS * E; e += MB_THREADS) S.x2[0][e] = gelu_f(S.z1[0][e] + b1[e % E]);
+    FOR_E(r, c) S.x2[r][c] = gelu_f(S.z1[r][c] + b1[c]);
     __syncthreads();
-    tile_mma<true>(mW2, tr(mx2), mdg2, E, F, CS, 1.f);
-    add_colsum(b2, &S.dg2[0][0], F, nullptr, 1.f);
+    tile_mma<true, CS, MB_E, HD>(mW2, tr(mx2), mdg2, 1.f);
+    add_colsum(b2, &S.dg2[0][0], F, FP, 1.f);
     __syncthreads();
+    TRM(4)
     // ---- forward intermediates of the stage
     inner_forward();
-    for (int e = tid; e < CS * CS; e += MB_THREADS) {
-      const int i = e / CS, j = e % CS;
-      S.eta[i][j] = (j <= i) ? S.te[i] * S.lr[j] : 0.f;
-    }
-    tile_mma<false>(ma1, mQ, tr(mK), CS, CS, F, 1.f);
+    TRM(5)
+    FOR_C(i, j) S.eta[i][j] = (j <= i) ? S.te[i] * S.lr[j] : 0.f;
+    tile_mma<false, HD, CS, CS>(ma1, mQ, tr(mK), 1.f);
     __syncthreads();
-    for (int e = tid; e < CS * CS; e += MB_THREADS) {
-      const int i = e / CS, j = e % CS;
+    FOR_C(i, j) {
       const float a = (j <= i) ? S.a1[i][j] : 0.f;
       S.a1[i][j] = a;
       S.m1[i][j] = S.eta[i][j] * (1.f + a);
     }
-    tile_mma<false>(mz1b, mQ, mW1, CS, E, F, 1.f);
+    tile_mma<false, HD, CS, MB_E>(mz1b, mQ, mW1, 1.f);
     __syncthreads();
-    tile_mma<true>(mz1b, mm1, mg1, CS, E, CS, -1.f);
+    tile_mma<true, CS, CS, MB_E>(mz1b, mm1, mg1, -1.f);
     __syncthreads();
-    for (int e = tid; e < CS * E; e += MB_THREADS) {
-      const float z = S.z1b[0][e] + b1[e % E];
-      S.z1b[0][e] = z;
-      S.x2b[0][e] = gelu_f(z);
+    FOR_E(r, c) {
+      const float z = S.z1b[r][c] + b1[c];
+      S.z1b[r][c] = z;
+      S.x2b[r][c] = gelu_f(z);
     }
     __syncthreads();
-    tile_mma<false>(ma2, mx2b, tr(mx2), CS, CS, E, 1.f);
-    tile_mma<false>(mz2b, mx2b, mW2, CS, F, E, 1.f);
+    tile_mma<false, MB_E, CS, CS>(ma2, mx2b, tr(mx2), 1.f);
+    tile_mma<false, MB_E, CS, HD>(mz2b, mx2b, mW2, 1.f);
     __syncthreads();
-    for (int e = tid; e < CS * CS; e += MB_THREADS) {
-      const int i = e / CS, j = e % CS;
+    FOR_C(i, j) {
       const float a = (j <= i) ? S.a2[i][j] : 0.f;
       S.a2[i][j] = a;
       S.m2[i][j] = S.eta[i][j] * (1.f + a);
     }
     __syncthreads();
-    tile_mma<true>(mz2b, mm2, mg2, CS, F, CS, -1.f);
+    tile_mma<true, CS, CS, HD>(mz2b, mm2, mg2, -1.f);
     __syncthreads();
-    for (int e = tid; e < CS * F; e += MB_THREADS) S.z2b[0][e] += b2[e % F];
+    FOR_F(r, c) S.z2b[r][c] += b2[c];
     __syncthreads();
 
-    // ---- 1. output LayerNorm: dz2b, LN parameter gradients
+    TRM(6)
+    // ---- 1. output LayerNorm: dz2b, LN parameter gradients (per-warp column partials in t4, not live yet)
+    float(*colpart)[2 * HD] = reinterpret_cast<float(*)[2 * HD]>(&S.t4[0][0]);
     {
       float pg[2] = {0.f, 0.f}, pb[2] = {0.f, 0.f};
 #pragma unroll
@@ -355,69 +434,69 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       }
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        S.colpart[warp][lane + 32 * e] = pg[e];
-        S.colpart[warp][64 + lane + 32 * e] = pb[e];
+        colpart[warp][lane + 32 * e] = pg[e];
+        colpart[warp][64 + lane + 32 * e] = pb[e];
       }
     }
     __syncthreads();
     if (tid < 2 * HD) {
       float s_ = 0.f;
 #pragma unroll
-      for (int w = 0; w < 8; ++w) s_ += S.colpart[w][tid];
+      for (int w = 0; w < 8; ++w) s_ += colpart[w][tid];
       if (tid < HD) S.dgam[tid] += s_; else S.dbet[tid - HD] += s_;
     }
+    TRM(7)
     // ---- 2. z2b = x2b W2 + b2 - M2 g2
-    tile_mma<false>(mt1, mdz2b, tr(mW2), CS, E, F, 1.f);         // dx2b = dz2b W2^T
-    tile_mma<false>(mdm, mdz2b, tr(mg2), CS, CS, F, -1.f);        // dM2 = -tril(dz2b g2^T)
-    tile_mma<false>(mdg2, tr(mm2), mdz2b, CS, F, CS, -1.f);       // dg2 = -M2^T dz2b
+    tile_mma<false, HD, CS, MB_E>(mt1, mdz2b, tr(mW2), 1.f);         // dx2b = dz2b W2^T
+    tile_mma<false, HD, CS, CS>(mdm, mdz2b, tr(mg2), -1.f);        // dM2 = -tril(dz2b g2^T)
+    tile_mma<false, CS, CS, HD>(mdg2, tr(mm2), mdz2b, -1.f);        // dg2 = -M2^T dz2b
     __syncthreads();
-    for (int e = tid; e < CS * CS; e += MB_THREADS) {
-      const int i = e / CS, j = e % CS;
+    FOR_C(i, j) {
       const float d = (j <= i) ? S.dm[i][j] : 0.f;
       S.da[i][j] = d * S.eta[i][j];
       S.deta[i][j] = d * (1.f + S.a2[i][j]);
     }
     __syncthreads();
-    tile_mma<true>(mt1, mda, mx2, CS, E, CS, 1.f);               // dx2b += dA2 x2
-    tile_mma<false>(mt3, tr(mda), mx2b, CS, E, CS, 1.f);          // dx2 = dA2^T x2b
+    tile_mma<true, CS, CS, MB_E>(mt1, mda, mx2, 1.f);                // dx2b += dA2 x2
+    tile_mma<false, CS, CS, MB_E>(mt3, tr(mda), mx2b, 1.f);           // dx2 = dA2^T x2b
     __syncthreads();
+    TRM(8)
     // ---- 3./4. dz1b = dx2b o gelu'(z1b);  z1b = Q W1 + b1 - M1 g1
-    for (int e = tid; e < CS * E; e += MB_THREADS) S.t1[0][e] *= gelu_d1(S.z1b[0][e]);
+    FOR_E(r, c) S.t1[r][c] *= gelu_d1(S.z1b[r][c]);
     __syncthreads();
-    tile_mma<false>(mdq, mt1, tr(mW1), CS, F, E, 1.f);            // dq = dz1b W1^T
-    tile_mma<false>(mdm, mt1, tr(mg1), CS, CS, E, -1.f);          // dM1 = -tril(dz1b g1^T)
-    tile_mma<false>(mt2, tr(mm1), mt1, CS, E, CS, -1.f);          // dg1 = -M1^T dz1b
+    tile_mma<false, MB_E, CS, HD>(mdq, mt1, tr(mW1), 1.f);          // dq = dz1b W1^T
+    tile_mma<false, MB_E, CS, CS>(mdm, mt1, tr(mg1), -1.f);        // dM1 = -tril(dz1b g1^T)
+    tile_mma<false, CS, CS, MB_E>(mt2, tr(mm1), mt1, -1.f);           // dg1 = -M1^T dz1b
     __syncthreads();
-    for (int e = tid; e < CS * CS; e += MB_THREADS) {
-      const int i = e / CS, j = e % CS;
+    FOR_C(i, j) {
       const float d = (j <= i) ? S.dm[i][j] : 0.f;
       S.da[i][j] = d * S.eta[i][j];
       S.deta[i][j] += d * (1.f + S.a1[i][j]);
     }
     __syncthreads();
-    tile_mma<true>(mdq, mda, mK, CS, F, CS, 1.f);                 // dq += dA1 K
-    tile_mma<false>(mdk, tr(mda), mQ, CS, F, CS, 1.f);            // dk = dA1^T Q
+    TRM(9)
+    tile_mma<true, CS, CS, HD>(mdq, mda, mK, 1.f);                 // dq += dA1 K
+    tile_mma<false, CS, CS, HD>(mdk, tr(mda), mQ, 1.f);             // dk = dA1^T Q
     // ---- 5. the four state updates; dW1, db1, dW2, db2 still hold the gradients w.r.t. the next stage's state
-    tile_mma<false>(mgl1, mg1, tr(mdW1), CS, F, E, 1.f);          // gl1 = g1 dW1^T
-    tile_mma<false>(mt4, mg2, tr(mdW2), CS, E, F, 1.f);           // gl2 = g2 dW2^T   (t4 as scratch)
-    __syncthreads();
+    tile_mma<false, MB_E, CS, HD>(mgl1, mg1, tr(mdW1), 1.f);        // gl1 = g1 dW1^T
+    tile_mma<false, HD, CS, MB_E>(mt4, mg2, tr(mdW2), 1.f);           // gl2 = g2 dW2^T   (t4 as scratch)
     //   dg1 -= (l o K) dW1 + l (x) db1 : l o K is built in dz2, which is free until step 7
-    for (int e = tid; e < CS * F; e += MB_THREADS) S.dz2[0][e] = S.ell[e / F] * S.k[0][e];
+    FOR_F(r, c) S.dz2[r][c] = S.ell[r] * S.k[r][c];
     __syncthreads();
-    tile_mma<true>(mt2, mdz2, mdW1, CS, E, F, -1.f);              // dg1 -= (l o K) dW1
+    tile_mma<true, HD, CS, MB_E>(mt2, mdz2, mdW1, -1.f);             // dg1 -= (l o K) dW1
+    //   dg2 -= (l o x2) dW2 + l (x) db2 : l o x2 goes to z1b (dead after step 3)
+    FOR_E(r, c) S.z1b[r][c] = S.ell[r] * S.x2[r][c];
     __syncthreads();
-    for (int e = tid; e < CS * E; e += MB_THREADS) S.t2[0][e] -= S.ell[e / E] * db1[e % E];
-    // dg2 -= (l o x2) dW2 + l (x) db2 : l o x2 into z1b (dead after step 3)
-    for (int e = tid; e < CS * E; e += MB_THREADS) S.z1b[0][e] = S.ell[e / E] * S.x2[0][e];
-    __syncthreads();
-    tile_mma<true>(mdg2, mz1b, mdW2, CS, F, E, -1.f);
-    __syncthreads();
-    for (int e = tid; e < CS * F; e += MB_THREADS) {
-      S.dg2[0][e] -= S.ell[e / F] * db2[e % F];
-      S.dk[0][e] -= S.ell[e / F] * S.gl1[0][e];                   // dk -= l o gl1
+    FOR_E(r, c) {
+      S.t2[r][c] -= S.ell[r] * db1[c];
+      S.t3[r][c] -= S.ell[r] * S.t4[r][c];                        // dx2 -= l o gl2
     }
-    for (int e = tid; e < CS * E; e += MB_THREADS) S.t3[0][e] -= S.ell[e / E] * S.t4[0][e];  // dx2 -= l o gl2
+    tile_mma<true, MB_E, CS, HD>(mdg2, mz1b, mdW2, -1.f);
     __syncthreads();
+    FOR_F(r, c) {
+      S.dg2[r][c] -= S.ell[r] * db2[c];
+      S.dk[r][c] -= S.ell[r] * S.gl1[r][c];                       // dk -= l o gl1
+    }
     // dell[j] = -( gl1[j].K[j] + g1[j].db1 + gl2[j].x2[j] + g2[j].db2 )
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
@@ -429,17 +508,24 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       if (lane == 0) S.dell[r] = -acc;
     }
     __syncthreads();
-    // ---- 6. g1 = (g2 W2^T) o gelu'(z1):  dh = dg1 o gelu'(z1) (in t2),  dz1 = dg1 o h o gelu''(z1) (t4)
-    for (int e = tid; e < CS * E; e += MB_THREADS) {
-      const float d = S.t2[0][e], z = S.z1[0][e];
-      S.t4[0][e] = d * S.hm[0][e] * gelu_d2(z);
-      S.t2[0][e] = d * gelu_d1(z);
+    TRM(10)
+    // ---- 6. g1 = h o gelu'(z1), h = g2 W2^T (recomputed into z1b, whose scratch use is over):
+    //         dh = dg1 o gelu'(z1) (in t2),  dz1 = dg1 o h o gelu''(z1) (t4)
+    tile_mma<false, HD, CS, MB_E>(mz1b, mg2, tr(mW2), 1.f);
+    __syncthreads();
+    FOR_E(r, c) {
+      const float d = S.t2[r][c], z = S.z1[r][c];
+      S.t4[r][c] = d * S.z1b[r][c] * gelu_d2(z);
+      S.t2[r][c] = d * gelu_d1(z);
     }
     __syncthreads();
-    tile_mma<true>(mdg2, mt2, mW2, CS, F, E, 1.f);                // dg2 += dh W2
-    tile_mma<true>(mdW2, tr(mt2), mg2, E, F, CS, 1.f);            // dW2 += dh^T g2
+    tile_mma<true, MB_E, CS, HD>(mdg2, mt2, mW2, 1.f);             // dg2 += dh W2
+    tile_mma<true, CS, MB_E, HD>(mdW2, tr(mt2), mg2, 1.f);            // dW2 += dh^T g2
     __syncthreads();
+    TRM(11)
     // ---- 7. second derivative through g2 = ln_l2_grad(z2, v - k): dz2, d target, LN parameter gradients
+    //         (column partials in t2: dh is no longer needed)
+    colpart = reinterpret_cast<float(*)[2 * HD]>(&S.t2[0][0]);
     {
       float pg[2] = {0.f, 0.f}, pb[2] = {0.f, 0.f};
 #pragma unroll
@@ -488,33 +574,35 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       }
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        S.colpart[warp][lane + 32 * e] = pg[e];
-        S.colpart[warp][64 + lane + 32 * e] = pb[e];
+        colpart[warp][lane + 32 * e] = pg[e];
+        colpart[warp][64 + lane + 32 * e] = pb[e];
       }
     }
     __syncthreads();
     if (tid < 2 * HD) {
       float s_ = 0.f;
 #pragma unroll
-      for (int w = 0; w < 8; ++w) s_ += S.colpart[w][tid];
+      for (int w = 0; w < 8; ++w) s_ += colpart[w][tid];
       if (tid < HD) S.dgam[tid] += s_; else S.dbet[tid - HD] += s_;
     }
+    TRM(12)
     // ---- 8./9./10. z2 = x2 W2 + b2, x2 = gelu(z1), z1 = K W1 + b1
-    tile_mma<true>(mt3, mdz2, tr(mW2), CS, E, F, 1.f);            // dx2 += dz2 W2^T
+    tile_mma<true, HD, CS, MB_E>(mt3, mdz2, tr(mW2), 1.f);           // dx2 += dz2 W2^T
     __syncthreads();
-    for (int e = tid; e < CS * E; e += MB_THREADS) S.t4[0][e] += S.t3[0][e] * gelu_d1(S.z1[0][e]);  // dz1 += dx2 o gelu'
+    FOR_E(r, c) S.t4[r][c] += S.t3[r][c] * gelu_d1(S.z1[r][c]);   // dz1 += dx2 o gelu'(z1)
     __syncthreads();
-    tile_mma<true>(mdk, mt4, tr(mW1), CS, F, E, 1.f);             // dk += dz1 W1^T
+    tile_mma<true, MB_E, CS, HD>(mdk, mt4, tr(mW1), 1.f);          // dk += dz1 W1^T
+    TRM(13)
     // ---- gradients w.r.t. this stage's state (all reads of the next-stage gradients are done)
-    tile_mma<true>(mdW2, tr(mx2b), mdz2b, E, F, CS, 1.f);         // dW2 += x2b^T dz2b
-    tile_mma<true>(mdW2, tr(mx2), mdz2, E, F, CS, 1.f);           // dW2 += x2^T dz2
-    tile_mma<true>(mdW1, tr(mQ), mt1, F, E, CS, 1.f);             // dW1 += Q^T dz1b
-    tile_mma<true>(mdW1, tr(mK), mt4, F, E, CS, 1.f);             // dW1 += K^T dz1
-    add_colsum(db2, &S.dz2b[0][0], F, nullptr, 1.f);
-    add_colsum(db1, &S.t1[0][0], E, nullptr, 1.f);
-    __syncthreads();
-    add_colsum(db2, &S.dz2[0][0], F, nullptr, 1.f);
-    add_colsum(db1, &S.t4[0][0], E, nullptr, 1.f);
+    tile_mma<true, CS, MB_E, HD>(mdW2, tr(mx2b), mdz2b, 1.f);         // dW2 += x2b^T dz2b
+    tile_mma<true, CS, MB_E, HD>(mdW2, tr(mx2), mdz2, 1.f);           // dW2 += x2^T dz2
+    tile_mma<true, CS, HD, MB_E>(mdW1, tr(mQ), mt1, 1.f);             // dW1 += Q^T dz1b
+    tile_mma<true, CS, HD, MB_E>(mdW1, tr(mK), mt4, 1.f);             // dW1 += K^T dz1
+    add_colsum(db2, &S.dz2b[0][0], F, FP, 1.f);
+    add_colsum(db1, &S.t1[0][0], E, EP, 1.f);
+    add_colsum(db2, &S.dz2[0][0], F, FP, 1.f);
+    add_colsum(db1, &S.t4[0][0], E, EP, 1.f);
+    TRM(14)
     // ---- 11. eta factors and outputs of the stage
     if (tid < CS) {
       const int i = tid;
@@ -530,16 +618,24 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       st_from_float<T>(p.d_lr, row_base + (size_t)s * CS + i, dlr);
     }
     __syncthreads();
-    for (int e = tid; e < CS * F; e += MB_THREADS) {
-      S.dq[0][e] += S.dO[0][e];
-      S.dk[0][e] -= S.gl1[0][e];  // gl1 holds d target: dk -= dT, dv = dT
+    FOR_F(r, c) {
+      dq[r][c] += S.dO[r][c];
+      S.dk[r][c] -= S.gl1[r][c];  // gl1 holds d target: dk -= dT, dv = dT
     }
     __syncthreads();
-    store_tile_bf16(static_cast<T*>(p.d_q) + r0, S.dq);
+    store_tile_bf16(static_cast<T*>(p.d_q) + r0, dq);
     store_tile_bf16(static_cast<T*>(p.d_k) + r0, S.dk);
     store_tile_bf16(static_cast<T*>(p.d_v) + r0, S.gl1);
     __syncthreads();
+    TRM(15)
   }
+#ifdef TTT_MLP_TRACE
+  if (tid == 0 && blockIdx.x == 0 && p.trace != nullptr)
+    for (int i = 0; i < 16; ++i) p.trace[i] = (unsigned int)(tr_acc[i] / NS);
+#endif
+#undef FOR_E
+#undef FOR_F
+#undef FOR_C
 
   // ---- gradients w.r.t. the initial state, per-stream LayerNorm parameter gradients
   for (int e = tid; e < F * E; e += MB_THREADS) {

@@ -425,7 +425,7 @@ def fused_ttt_mlp_forward(xq, xk, xv, state: TTTMLPState, token_eta, ttt_lr_eta,
                           config: FusedTttConfig):
     """Whole-sequence forward of the 2-layer inner model in one launch (the loop of
     `TTTMLP::forward_mini_batch`, rust/core/src/mlp.rs:127-208).  Returns (output, new TTTMLPState).
-    bf16 only and not differentiable: there is no backward kernel for this inner model yet."""
+    bf16 only.  Its gradient is `fused_ttt_mlp_backward` (no autograd node is recorded here)."""
     lib = _lib.load()
     if not xq.is_cuda:
         raise TttError(_lib.TTT_ERR_CUDA, "inputs must be CUDA tensors: this operator has no CPU path")
