@@ -93,16 +93,27 @@ def layer_epilogue(inner_out, x, p: Dict[str, torch.Tensor], *, use_gate: bool =
 
 def ttt_layer_forward(x, p: Dict[str, torch.Tensor], *, num_heads: int, mini_batch: int = 16, base_lr: float = 1.0,
                       rope_theta: float = 10000.0, share_qk: bool = False, use_gate: bool = False,
-                      start_idx: int = 0, state: Optional[Dict[str, torch.Tensor]] = None):
-    """Whole layer, TTT-Linear inner model.  `state` = {"weight" [B,H,F,F], "bias" [B,H,F]} (defaults to the
-    parameters W1, b1 repeated over the batch: rust/core/src/linear.rs:84-89).  Returns (output [B,T,C], new state)."""
+                      start_idx: int = 0, state: Optional[Dict[str, torch.Tensor]] = None, inner: str = "linear"):
+    """Whole layer.  inner = "linear": `state` = {"weight" [B,H,F,F], "bias" [B,H,F]} (defaults to the parameters W1,
+    b1 repeated over the batch: rust/core/src/linear.rs:84-89); inner = "mlp": `state` = {"w1" [B,H,F,4F], "b1",
+    "w2" [B,H,4F,F], "b2"} from the parameters W1, b1, W2, b2 (rust/core/src/mlp.rs:29-53; whole mini-batches only).
+    Returns (output [B,T,C], new state)."""
     B, T, C = x.shape
     H = num_heads
     xq, xk, xv, lr, te = layer_prologue(x, p, num_heads=H, mini_batch=mini_batch, base_lr=base_lr,
                                         rope_theta=rope_theta, share_qk=share_qk, start_idx=start_idx)
-    if state is None:
-        state = {"weight": p["W1"].unsqueeze(0).repeat(B, 1, 1, 1), "bias": p["b1"].reshape(1, H, -1).repeat(B, 1, 1)}
-    r = O.ttt_linear_forward_any_length(xq, xk, xv, state["weight"], state["bias"], te, lr, p["ttt_norm_weight"],
-                                        p["ttt_norm_bias"], mini_batch=mini_batch, eps=1e-6)
+    if inner == "mlp":
+        if state is None:
+            state = {"w1": p["W1"].unsqueeze(0).repeat(B, 1, 1, 1), "b1": p["b1"].reshape(1, H, -1).repeat(B, 1, 1),
+                     "w2": p["W2"].unsqueeze(0).repeat(B, 1, 1, 1), "b2": p["b2"].reshape(1, H, -1).repeat(B, 1, 1)}
+        r = O.ttt_mlp_forward(xq, xk, xv, state["w1"], state["b1"], state["w2"], state["b2"], te, lr,
+                              p["ttt_norm_weight"], p["ttt_norm_bias"], mini_batch=mini_batch, eps=1e-6)
+        new_state = {k: r[k] for k in ("w1", "b1", "w2", "b2")}
+    else:
+        if state is None:
+            state = {"weight": p["W1"].unsqueeze(0).repeat(B, 1, 1, 1), "bias": p["b1"].reshape(1, H, -1).repeat(B, 1, 1)}
+        r = O.ttt_linear_forward_any_length(xq, xk, xv, state["weight"], state["bias"], te, lr, p["ttt_norm_weight"],
+                                            p["ttt_norm_bias"], mini_batch=mini_batch, eps=1e-6)
+        new_state = {"weight": r["weight"], "bias": r["bias"]}
     y = layer_epilogue(r["output"], x, p, use_gate=use_gate)
-    return y @ p["o_proj"].T, {"weight": r["weight"], "bias": r["bias"]}
+    return y @ p["o_proj"].T, new_state

@@ -27,7 +27,8 @@ What is produced (all by calling the reference's own `TTTLinear.ttt` /
     the whole outer layer (`TTTLinear.forward`: projections, optional shared-QK causal
     convolutions, rotary embedding, learning-rate gate, inner loop, post norm, optional
     gate, output projection; the analogue of reference/validate.py:338-415 at head_dim 64):
-    B=2 T=48 H=2 F=64, float64, for the default configuration and for share_qk + use_gate.
+    B=2 T=48 H=2 F=64, float64, for the default configuration and for share_qk + use_gate, plus
+    (tag "mlp") the default configuration with the 2-layer inner model (`TTTMLP.forward`).
     Inputs, every parameter and the expected output are stored.
 """
 
@@ -187,11 +188,12 @@ def gen_cfg0(ref, out_dir: Path):
 def gen_layer(ref, out_dir: Path):
     B, T, H, D, cs = 2, 48, 2, 64, 16
     d = {}
-    for tag, share_qk, use_gate in (("plain", False, False), ("conv_gate", True, True)):
-        torch.manual_seed(7 if share_qk else 5)
-        cfg = ref.TTTConfig(hidden_size=H * D, num_attention_heads=H, mini_batch_size=cs, ttt_layer_type="linear",
+    for tag, share_qk, use_gate, kind in (("plain", False, False, "linear"), ("conv_gate", True, True, "linear"),
+                                          ("mlp", False, False, "mlp")):
+        torch.manual_seed({"plain": 5, "conv_gate": 7, "mlp": 9}[tag])
+        cfg = ref.TTTConfig(hidden_size=H * D, num_attention_heads=H, mini_batch_size=cs, ttt_layer_type=kind,
                             ttt_base_lr=1.0, share_qk=share_qk, use_gate=use_gate, conv_kernel=4, pre_conv=False)
-        m = ref.TTTLinear(cfg, layer_idx=0)
+        m = (ref.TTTLinear if kind == "linear" else ref.TTTMLP)(cfg, layer_idx=0)
         m.eval()
         with torch.no_grad():  # make every parameter non-trivial
             m.ttt_norm_weight.add_(0.1 * torch.randn_like(m.ttt_norm_weight))
@@ -201,6 +203,8 @@ def gen_layer(ref, out_dir: Path):
             m.learnable_ttt_lr_bias.add_(0.1 * torch.randn_like(m.learnable_ttt_lr_bias))
             m.learnable_token_idx.add_(0.05 * torch.randn_like(m.learnable_token_idx))
             m.b1.add_(0.05 * torch.randn_like(m.b1))
+            if kind == "mlp":
+                m.b2.add_(0.05 * torch.randn_like(m.b2))
         m = m.double()
         x = (torch.randn(B, T, H * D) * 0.5).double()
         pos = torch.arange(T).unsqueeze(0).expand(B, -1)
@@ -215,6 +219,8 @@ def gen_layer(ref, out_dir: Path):
             "token_idx": m.token_idx, "learnable_token_idx": m.learnable_token_idx,
             "W1": m.W1, "b1": m.b1,
         }
+        if kind == "mlp":
+            t.update(W2=m.W2, b2=m.b2)
         if use_gate:
             t["g_proj"] = m.g_proj.weight
         if share_qk:

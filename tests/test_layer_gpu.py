@@ -200,3 +200,48 @@ def test_layer_training_gradients_match_autograd_of_the_restatement(use_gate):
     for name, param in pairs.items():
         assert param.grad is not None, f"no gradient reached {name}"
         assert_close(param.grad.reshape(leaves[name].grad.shape), leaves[name].grad, rt, f"d {name}")
+
+
+@pytest.mark.gpu
+def test_layer_with_mlp_inner_model_forward_and_training(golden_dir):
+    """The outer layer around the 2-layer inner model: forward against the reference's `TTTMLP.forward` output
+    (bf16 kernels, so at bf16 tolerance), and one training step against float64 autograd of the restatement."""
+    import ttt_rs_b200 as tb
+    dev = torch.device("cuda:0")
+    p = _golden(golden_dir, "mlp")
+    H, dt = 2, torch.bfloat16
+    pb = {k: v.to(dt).double() for k, v in p.items()}   # what the bf16 layer actually holds
+    cfg = tb.TTTLayerConfig(hidden_size=128, num_heads=H)
+    m = tb.TTT(cfg, device=dev, dtype=dt)
+    mlp = tb.TTTMLP(H, 64, 16, 1e-6, device=dev, dtype=dt)
+    inner = tb.FusedTTTMLP(mlp)
+    with torch.no_grad():
+        for dst, src in ((m.q_proj, "q_proj"), (m.k_proj, "k_proj"), (m.v_proj, "v_proj"), (m.o_proj, "o_proj"),
+                         (m.learnable_ttt_lr_weight, "lr_weight"), (m.learnable_ttt_lr_bias, "lr_bias"),
+                         (m.learnable_token_idx, "learnable_token_idx"), (m.post_norm_weight, "post_norm_weight"),
+                         (m.post_norm_bias, "post_norm_bias"), (mlp.w1_init, "W1"), (mlp.b1_init, "b1"),
+                         (mlp.w2_init, "W2"), (mlp.b2_init, "b2"), (mlp.ln_weight, "ttt_norm_weight"),
+                         (mlp.ln_bias, "ttt_norm_bias")):
+            dst.copy_(p[src].reshape(dst.shape).to(dt))
+    m.invalidate_fused_weight()
+    x = p["input"].to(dt)
+    with torch.no_grad():
+        y = m(x.to(dev), inner, inner.init_state(x.shape[0]))
+    want, _ = LO.ttt_layer_forward(x.double(), pb, num_heads=H, inner="mlp")
+    assert_close(y, want, 2e-2, "layer output (mlp inner)", max_bad_frac=2e-3)
+    assert_close(y, p["output_expected"], 5e-2, "layer output against the float64 reference", max_bad_frac=5e-3)
+
+    # training step
+    xg = x.to(dev).requires_grad_(True)
+    gy = torch.randn(x.shape, generator=torch.Generator().manual_seed(4)).to(dt)
+    m(xg, inner, inner.init_state(x.shape[0])).backward(gy.to(dev))
+    torch.cuda.synchronize()
+    leaves = {k: v.clone().requires_grad_(True) for k, v in pb.items() if k != "token_idx"}
+    leaves["token_idx"] = pb["token_idx"]
+    xr = x.double().requires_grad_(True)
+    LO.ttt_layer_forward(xr, leaves, num_heads=H, inner="mlp")[0].backward(gy.double())
+    assert_close(xg.grad, xr.grad, 3e-2, "d input", max_bad_frac=5e-3)
+    for name, param in (("W1", mlp.w1_init), ("W2", mlp.w2_init), ("b1", mlp.b1_init), ("q_proj", m.q_proj),
+                        ("v_proj", m.v_proj), ("o_proj", m.o_proj), ("post_norm_weight", m.post_norm_weight)):
+        assert param.grad is not None, name
+        assert_close(param.grad.reshape(leaves[name].grad.shape), leaves[name].grad, 3e-2, f"d {name}", max_bad_frac=5e-3)

@@ -36,3 +36,55 @@ def test_mlp_backward_matches_autograd_of_the_restatement(B, H, NS):
               "grad_ln_weight", "grad_ln_bias"):
         assert_close(g[k], want[k], 2e-2, k, max_bad_frac=2e-3)
     assert_close(fold(g["grad_token_eta"]), fold(want["grad_token_eta"]), 2e-2, "grad_token_eta (folded)")
+
+
+@pytest.mark.gpu
+def test_mlp_backward_at_the_benchmark_size_on_sampled_streams():
+    """Config 2 in full (B=16 H=12 T=2048: 192 streams in two waves, 128 stages, 540 MB workspace); the streams are
+    independent, so three of them are checked against float64 autograd and the batch reductions by linearity."""
+    import ttt_rs_b200 as tb
+    dev = torch.device("cuda:0")
+    B, H, T = 16, 12, 2048
+    t = O.make_inputs(B, H, T, 64, 16, seed=0, dtype=torch.bfloat16, inner="mlp")
+    cfg = tb.FusedTttConfig.new(16, 64, 1e-6, 128, 1)
+    d = {k: v.to(dev) for k, v in t.items()}
+    g = tb.fused_ttt_mlp_backward(d["xq"], d["xk"], d["xv"], tb.TTTMLPState(d["w1"], d["b1"], d["w2"], d["b2"]),
+                                  d["token_eta"], d["ttt_lr_eta"], d["ln_weight"], d["ln_bias"], d["grad_output"], cfg)
+    torch.cuda.synchronize()
+    for k, v in g.items():
+        if k != "_workspace":
+            assert torch.isfinite(v.float()).all(), k
+    for b, h in ((0, 0), (7, 5), (15, 11)):  # first wave, middle, last stream of the second wave
+        one = {k: (v[b:b + 1, h:h + 1] if v.dim() >= 3 else v) for k, v in t.items()}
+        one["ln_weight"], one["ln_bias"] = t["ln_weight"][h:h + 1], t["ln_bias"][h:h + 1]
+        want = O.ttt_mlp_backward_autograd(*[one[k].double() for k in MLP_IN], one["grad_output"].double())
+        for k in ("grad_xq", "grad_xk", "grad_xv", "grad_w1", "grad_b1", "grad_w2", "grad_b2", "grad_ttt_lr_eta"):
+            assert_close(g[k][b:b + 1, h:h + 1], want[k], 2e-2, f"stream ({b},{h}) {k}", max_bad_frac=2e-3)
+    # a second run gives the same bits (fixed-order reductions, no atomics)
+    g2 = tb.fused_ttt_mlp_backward(d["xq"], d["xk"], d["xv"], tb.TTTMLPState(d["w1"], d["b1"], d["w2"], d["b2"]),
+                                   d["token_eta"], d["ttt_lr_eta"], d["ln_weight"], d["ln_bias"], d["grad_output"], cfg)
+    torch.cuda.synchronize()
+    for k in ("grad_xq", "grad_w1", "grad_token_eta", "grad_ln_weight"):
+        assert torch.equal(g[k], g2[k]), f"{k} differs between two runs"
+
+
+@pytest.mark.gpu
+def test_mlp_autograd_node():
+    """`fused_ttt_mlp` under torch autograd: gradients reach the leaves and equal the direct backward call."""
+    import ttt_rs_b200 as tb
+    dev = torch.device("cuda:0")
+    t = _case(1, 2, 32, 77)
+    cfg = tb.FusedTttConfig.new(16, 64, 1e-6, 128, 1)
+    d = {k: v.to(dev) for k, v in t.items()}
+    leaves = {k: d[k].clone().requires_grad_(True) for k in ("xq", "xk", "xv", "w1", "b1", "w2", "b2", "ttt_lr_eta",
+                                                             "ln_weight", "ln_bias")}
+    out, _ = tb.fused_ttt_mlp(leaves["xq"], leaves["xk"], leaves["xv"],
+                              tb.TTTMLPState(leaves["w1"], leaves["b1"], leaves["w2"], leaves["b2"]), d["token_eta"],
+                              leaves["ttt_lr_eta"], leaves["ln_weight"], leaves["ln_bias"], cfg)
+    out.backward(d["grad_output"])
+    g = tb.fused_ttt_mlp_backward(d["xq"], d["xk"], d["xv"], tb.TTTMLPState(d["w1"], d["b1"], d["w2"], d["b2"]),
+                                  d["token_eta"], d["ttt_lr_eta"], d["ln_weight"], d["ln_bias"], d["grad_output"], cfg)
+    torch.cuda.synchronize()
+    for k in ("xq", "xk", "xv", "w1", "b1", "w2", "b2", "ttt_lr_eta"):
+        assert torch.equal(leaves[k].grad, g["grad_" + k]), k
+    assert torch.equal(leaves["ln_weight"].grad, g["grad_ln_weight"].to(torch.bfloat16))

@@ -2,17 +2,20 @@
 
 from ._lib import TttDims, TttError, load as load_library  # noqa: F401
 from .fused import (  # noqa: F401
+    FusedTTTMLP,
     FusedTileMultiTTTLinear,
     FusedTttConfig,
     Qkv,
     TTTInputsInner,
     TTTLinear,
     TTTLinearState,
+    TTTMLP,
     TTTMLPState,
     TttInputs,
     TttOutputs,
     TttSavedStateMulti,
     TttTileMultiKernel,
+    fused_ttt_mlp,
     fused_ttt_mlp_backward,
     fused_ttt_mlp_forward,
     fused_ttt_tile_forward_multi,

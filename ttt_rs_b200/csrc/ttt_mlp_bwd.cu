@@ -62,6 +62,10 @@ template <bool ACC, int K, int M, int N, class MC, class MA, class MB>
 __device__ void tile_mma(const MC C, const MA A, const MB B, float alpha) {
   constexpr int NW = MB_THREADS / 32, ntn = N / 8, total = (M / 16) * ntn;
   constexpr int TG = total >= 4 * NW ? 4 : (total + NW - 1) / NW;  // tiles of a warp in flight together
+  // The tiles of one group are tile0 + u * NW: with N a multiple of 8 * NW * TG they share their rows (one A fragment
+  // serves all of them), with N == 8 * NW they share their columns (one B fragment).
+  constexpr bool SHARE_A = TG > 1 && (ntn % (NW * TG) == 0);
+  constexpr bool SHARE_B = TG > 1 && !SHARE_A && ntn == NW;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 #pragma unroll 1
   for (int tile0 = warp; tile0 < total; tile0 += NW * TG) {
@@ -84,21 +88,27 @@ __device__ void tile_mma(const MC C, const MA A, const MB B, float alpha) {
 #pragma unroll(K >= 64 ? 2 : 1)
     for (int k0 = 0; k0 < K; k0 += 16) {
       const int ka = k0 + 2 * t, kb = ka + 8;
-      float2 fa[TG][4], fb[TG][2];
+      uint32_t pa[TG][4], pb[TG][2];
 #pragma unroll
       for (int u = 0; u < TG; ++u) {
-        fa[u][0] = pair_k_of_A(A, i0[u], ka);
-        fa[u][1] = pair_k_of_A(A, i0[u] + 8, ka);
-        fa[u][2] = pair_k_of_A(A, i0[u], kb);
-        fa[u][3] = pair_k_of_A(A, i0[u] + 8, kb);
-        fb[u][0] = pair_k_of_B(B, ka, j0[u] + g);
-        fb[u][1] = pair_k_of_B(B, kb, j0[u] + g);
+        if (u == 0 || !SHARE_A) {
+          const float2 f0 = pair_k_of_A(A, i0[u], ka), f1 = pair_k_of_A(A, i0[u] + 8, ka);
+          const float2 f2_ = pair_k_of_A(A, i0[u], kb), f3 = pair_k_of_A(A, i0[u] + 8, kb);
+          pa[u][0] = pack_bf16(f0.x, f0.y); pa[u][1] = pack_bf16(f1.x, f1.y);
+          pa[u][2] = pack_bf16(f2_.x, f2_.y); pa[u][3] = pack_bf16(f3.x, f3.y);
+        } else {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) pa[u][q] = pa[0][q];
+        }
+        if (u == 0 || !SHARE_B) {
+          const float2 h0 = pair_k_of_B(B, ka, j0[u] + g), h1 = pair_k_of_B(B, kb, j0[u] + g);
+          pb[u][0] = pack_bf16(h0.x, h0.y); pb[u][1] = pack_bf16(h1.x, h1.y);
+        } else {
+          pb[u][0] = pb[0][0]; pb[u][1] = pb[0][1];
+        }
       }
 #pragma unroll
-      for (int u = 0; u < TG; ++u)
-        mma_bf16(acc[u], pack_bf16(fa[u][0].x, fa[u][0].y), pack_bf16(fa[u][1].x, fa[u][1].y),
-                 pack_bf16(fa[u][2].x, fa[u][2].y), pack_bf16(fa[u][3].x, fa[u][3].y),
-                 pack_bf16(fb[u][0].x, fb[u][0].y), pack_bf16(fb[u][1].x, fb[u][1].y));
+      for (int u = 0; u < TG; ++u) mma_bf16(acc[u], pa[u][0], pa[u][1], pa[u][2], pa[u][3], pb[u][0], pb[u][1]);
     }
 #pragma unroll
     for (int u = 0; u < TG; ++u)
@@ -272,7 +282,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
 #define FOR_C(r, c) for (int e_ = tid, r = e_ / CS, c = e_ % CS; e_ < CS * CS; e_ += MB_THREADS, r = e_ / CS, c = e_ % CS)
 
   // z1 = K W1 + b1, x2 = gelu(z1), z2 = x2 W2 + b2, g2, g1 = (g2 W2^T) o gelu'(z1)   (from the state in the workspace)
-  auto inner_forward = [&]() {
+  auto forward_first_layer = [&]() {
     tile_mma<false, HD, CS, MB_E>(mz1, mK, mW1, 1.f);
     __syncthreads();
     FOR_E(r, c) {
@@ -281,6 +291,8 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       S.x2[r][c] = gelu_f(z);
     }
     __syncthreads();
+  };
+  auto forward_second_layer = [&]() {
     tile_mma<false, MB_E, CS, HD>(mz2, mx2, mW2, 1.f);
     __syncthreads();
     FOR_F(r, c) S.z2[r][c] += b2[c];
@@ -304,7 +316,8 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     if (tid < CS) S.ell[tid] = te_last * ld_as_float<T>(p.lr, row_base + (size_t)s * CS + tid);
     __syncthreads();
     TRM(0)
-    inner_forward();
+    forward_first_layer();
+    forward_second_layer();
     TRM(1)
     float* g1p = g1p_all + (size_t)s * CS * E;
     float* g2p = g2p_all + (size_t)s * CS * F;
@@ -360,16 +373,13 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     tile_mma<true, CS, HD, MB_E>(mW1, tr(mK), mt1, 1.f);
     add_colsum(b1, &S.t1[0][0], E, EP, 1.f);
     __syncthreads();
-    tile_mma<false, HD, CS, MB_E>(mz1, mK, mW1, 1.f);
-    __syncthreads();
-    FOR_E(r, c) S.x2[r][c] = gelu_f(S.z1[r][c] + b1[c]);
-    __syncthreads();
+    forward_first_layer();  // z1 and x2 of this stage, needed to undo the second layer's update
     tile_mma<true, CS, MB_E, HD>(mW2, tr(mx2), mdg2, 1.f);
     add_colsum(b2, &S.dg2[0][0], F, FP, 1.f);
     __syncthreads();
     TRM(4)
     // ---- forward intermediates of the stage
-    inner_forward();
+    forward_second_layer();
     TRM(5)
     FOR_C(i, j) S.eta[i][j] = (j <= i) ? S.te[i] * S.lr[j] : 0.f;
     tile_mma<false, HD, CS, CS>(ma1, mQ, tr(mK), 1.f);

@@ -490,3 +490,85 @@ def fused_ttt_mlp_backward(xq, xk, xv, state: TTTMLPState, token_eta, ttt_lr_eta
     _lib.check(rc)
     g["_workspace"] = ws  # keeps the scratch alive until the caller drops the result
     return g
+
+
+class _FusedTttMlpFn(torch.autograd.Function):
+    """TTT-MLP inner loop as an autograd node: forward `ttt_mlp_forward`, backward `ttt_mlp_backward`.  Like the
+    TTT-Linear operator (and the reference's fused operators, launch.rs:188-194) gradients arriving at the returned
+    final state are ignored."""
+
+    @staticmethod
+    def forward(ctx, xq, xk, xv, w1, b1, w2, b2, token_eta, ttt_lr_eta, ln_weight, ln_bias, config):
+        out, new = fused_ttt_mlp_forward(xq, xk, xv, TTTMLPState(w1, b1, w2, b2), token_eta, ttt_lr_eta, ln_weight,
+                                         ln_bias, config)
+        ctx.save_for_backward(xq, xk, xv, w1, b1, w2, b2, token_eta, ttt_lr_eta, ln_weight, ln_bias)
+        ctx.config = config
+        return out, new.w1, new.b1, new.w2, new.b2
+
+    @staticmethod
+    def backward(ctx, g_out, *_state_grads):
+        xq, xk, xv, w1, b1, w2, b2, token_eta, lr, ln_w, ln_b = ctx.saved_tensors
+        g = fused_ttt_mlp_backward(xq, xk, xv, TTTMLPState(w1, b1, w2, b2), token_eta, lr, ln_w, ln_b,
+                                   g_out.contiguous(), ctx.config)
+        dt = xq.dtype
+        return (g["grad_xq"], g["grad_xk"], g["grad_xv"], g["grad_w1"], g["grad_b1"], g["grad_w2"], g["grad_b2"],
+                g["grad_token_eta"].to(dt), g["grad_ttt_lr_eta"], g["grad_ln_weight"].to(dt), g["grad_ln_bias"].to(dt),
+                None)
+
+
+def fused_ttt_mlp(xq, xk, xv, state: TTTMLPState, token_eta, ttt_lr_eta, ln_weight, ln_bias, config: FusedTttConfig):
+    """Differentiable whole-sequence TTT-MLP inner loop: returns (output, new TTTMLPState)."""
+    out, w1, b1, w2, b2 = _FusedTttMlpFn.apply(xq, xk, xv, state.w1, state.b1, state.w2, state.b2, token_eta,
+                                               ttt_lr_eta, ln_weight, ln_bias, config)
+    return out, TTTMLPState(w1, b1, w2, b2)
+
+
+class TTTMLP(torch.nn.Module):
+    """Parameter holder of the 2-layer inner model (rust/core/src/mlp.rs:29-53): w1_init [H,F,4F], b1_init [H,4F],
+    w2_init [H,4F,F], b2_init [H,F] (weights ~ N(0, 0.02), biases 0), per-head LayerNorm weight = 1 / bias = 0."""
+
+    def __init__(self, num_heads: int, head_dim: int, mini_batch_size: int = 16, epsilon: float = 1e-6, device=None,
+                 dtype=torch.bfloat16):
+        super().__init__()
+        self.num_heads, self.head_dim = num_heads, head_dim
+        self.mini_batch_size, self.epsilon = mini_batch_size, epsilon
+        kw = dict(device=device, dtype=dtype)
+        E = 4 * head_dim
+        self.w1_init = torch.nn.Parameter(torch.randn(num_heads, head_dim, E, **kw) * 0.02)
+        self.b1_init = torch.nn.Parameter(torch.zeros(num_heads, E, **kw))
+        self.w2_init = torch.nn.Parameter(torch.randn(num_heads, E, head_dim, **kw) * 0.02)
+        self.b2_init = torch.nn.Parameter(torch.zeros(num_heads, head_dim, **kw))
+        self.ln_weight = torch.nn.Parameter(torch.ones(num_heads, head_dim, **kw))
+        self.ln_bias = torch.nn.Parameter(torch.zeros(num_heads, head_dim, **kw))
+
+    def init_state(self, batch_size: int) -> TTTMLPState:
+        r = lambda t: t.unsqueeze(0).repeat(batch_size, *([1] * t.dim()))  # noqa: E731
+        return TTTMLPState(r(self.w1_init), r(self.b1_init), r(self.w2_init), r(self.b2_init))
+
+
+class FusedTTTMLP(torch.nn.Module):
+    """The 2-layer inner model behind the fused kernels, with the `forward(state, inputs)` interface of the inner-model
+    trait (rust/core/src/inner.rs:13-58).  Whole mini-batches only; bf16 only; differentiable."""
+
+    def __init__(self, inner: TTTMLP):
+        super().__init__()
+        self.inner = inner
+
+    @staticmethod
+    def name() -> str:
+        return "FusedTTTMLP"
+
+    def init_state(self, batch_size: int) -> TTTMLPState:
+        return self.inner.init_state(batch_size)
+
+    def forward(self, state: TTTMLPState, inputs: TTTInputsInner) -> torch.Tensor:
+        i = self.inner
+        B, H, T, F = inputs.qkv.xv.shape
+        if T % i.mini_batch_size != 0:
+            raise AssertionError("Sequence length must be a multiple of mini_batch_size")
+        cfg = FusedTttConfig.new(i.mini_batch_size, F, i.epsilon, 128, 1)
+        fn = fused_ttt_mlp if torch.is_grad_enabled() else fused_ttt_mlp_forward
+        out, new = fn(inputs.qkv.xq, inputs.qkv.xk, inputs.qkv.xv, state, inputs.token_eta, inputs.ttt_lr_eta,
+                      i.ln_weight, i.ln_bias, cfg)
+        state.w1, state.b1, state.w2, state.b2 = new.w1, new.b1, new.w2, new.b2
+        return out
