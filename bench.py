@@ -69,6 +69,7 @@ WORKLOADS = {
                         desc="TTT-Linear inner model decode step (1 token per stream), bf16, B=256 H=12 d=64"),
 }
 F, CS = 64, 16
+E2E_CHUNKS = int(os.environ.get("TTT_E2E_CHUNKS", "10"))
 
 
 def algorithmic_bytes(w, fwd=True, bwd=True):
@@ -608,7 +609,7 @@ def run_e2e(tb, w, host, dev, cfg, world, args):
     pinned = {k: host[k].pin_memory() for k in names_in}
     params = {k: host[k].to(dev) for k in ("weight", "bias", "token_eta", "ln_weight", "ln_bias")}
     out_host = alloc_host_outputs(w["B"], w["H"], w["T"], F, host["xq"].dtype, w["backward"])
-    runner = HostBatchRunner(cfg, dev, chunks=8, backward=w["backward"])
+    runner = HostBatchRunner(cfg, dev, chunks=E2E_CHUNKS, backward=w["backward"])
 
     for _ in range(2):
         runner.run(pinned, params, out_host)
@@ -631,7 +632,7 @@ def run_e2e(tb, w, host, dev, cfg, world, args):
     d2h = sum(v.numel() * v.element_size() for v in out_host.values())
     return {"value": w["B"] * w["T"] * world / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": steps,
-            "how": "pinned host buffers, 8 batch chunks pipelined over copy-in / compute / copy-out streams",
+            "how": f"pinned host buffers, {E2E_CHUNKS} tapered batch chunks pipelined over copy-in / compute / copy-out streams",
             "host_numa_node": numa_node}
 
 

@@ -18,20 +18,45 @@ from .fused import FusedTttConfig, TttInputs, TttOutputs, TttTileMultiKernel
 _IN = ("xq", "xk", "xv", "ttt_lr_eta")
 
 
+def chunk_bounds(batch: int, chunks: int, taper: bool = True):
+    """Row boundaries of the batch chunks.  With `taper` the first and last chunks are smaller (weights 1, 2, 4, ...,
+    4, 2, 1): the pipeline's fill (first copy-in + first kernels) and drain (last kernels + last copy-out) then cost a
+    fraction of a full chunk, while the total number of chunks -- each costs a fixed, latency-bound kernel time --
+    stays small."""
+    n = max(1, min(chunks, batch))
+    if not taper or n < 5:
+        return [(batch * c) // n for c in range(n + 1)]
+    w = [1.0, 2.0] + [4.0] * (n - 4) + [2.0, 1.0]
+    tot, acc, bounds = sum(w), 0.0, [0]
+    for x in w:
+        acc += x
+        b = round(batch * acc / tot)
+        bounds.append(min(batch, max(bounds[-1] + 1, b)))
+    bounds[-1] = batch
+    for i in range(n - 1, 0, -1):  # keep the boundaries strictly increasing if the batch is small
+        bounds[i] = min(bounds[i], bounds[i + 1] - 1)
+    return bounds
+
+
 class HostBatchRunner:
-    def __init__(self, config: FusedTttConfig, device: torch.device, chunks: int = 4, backward: bool = True):
+    def __init__(self, config: FusedTttConfig, device: torch.device, chunks: int = 4, backward: bool = True,
+                 taper: bool = True):
         self.cfg, self.dev, self.chunks, self.backward = config, device, max(1, chunks), backward
+        self.taper = taper
         self.s_in = torch.cuda.Stream(device)
         self.s_comp = torch.cuda.Stream(device)
         self.s_out = torch.cuda.Stream(device)
         self._dbuf = [None, None]
 
-    def _buffers(self, slot: int, like: Dict[str, torch.Tensor], rows: int):
+    def _buffers(self, slot: int, like: Dict[str, torch.Tensor], rows: int, capacity: int):
+        """Device staging buffers of a slot: allocated once at the largest chunk size (`capacity` rows) and handed out
+        as views, so that chunks of different sizes never free memory that kernels of another stream still read."""
         cur = self._dbuf[slot]
-        if cur is None or next(iter(cur.values())).shape[0] != rows:
-            cur = {k: torch.empty((rows,) + tuple(v.shape[1:]), dtype=v.dtype, device=self.dev) for k, v in like.items()}
+        if cur is None or next(iter(cur.values())).shape[0] < capacity:
+            cur = {k: torch.empty((capacity,) + tuple(v.shape[1:]), dtype=v.dtype, device=self.dev)
+                   for k, v in like.items()}
             self._dbuf[slot] = cur
-        return cur
+        return {k: v[:rows] for k, v in cur.items()}
 
     def run(self, host_in: Dict[str, torch.Tensor], params: Dict[str, torch.Tensor],
             host_out: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
@@ -42,8 +67,9 @@ class HostBatchRunner:
         caller synchronises (torch.cuda.synchronize or an event) before reading it."""
         names = _IN + (("grad_output",) if self.backward else ())
         B = host_in["xq"].shape[0]
-        nchunk = min(self.chunks, B)
-        bounds = [(B * c) // nchunk for c in range(nchunk + 1)]
+        bounds = chunk_bounds(B, self.chunks, self.taper)
+        nchunk = len(bounds) - 1
+        max_rows = max(bounds[i + 1] - bounds[i] for i in range(nchunk))
         cur = torch.cuda.current_stream(self.dev)
         for st in (self.s_in, self.s_comp, self.s_out):
             st.wait_stream(cur)
@@ -55,7 +81,7 @@ class HostBatchRunner:
             with torch.cuda.stream(self.s_in):
                 if c >= 2:
                     self.s_in.wait_event(ev_comp[c - 2])  # the kernels of chunk c-2 have consumed this slot
-                buf = self._buffers(slot, {k: host_in[k] for k in names}, b - a)
+                buf = self._buffers(slot, {k: host_in[k] for k in names}, b - a, max_rows)
                 for k in names:
                     buf[k].copy_(host_in[k][a:b], non_blocking=True)
                 e = torch.cuda.Event()
