@@ -65,6 +65,10 @@ WORKLOADS = {
     # one decode step of the inner model (a mini-batch of one token per stream, state advanced in place)
     "decode": dict(kind="decode", B=8, H=12, T=1, dtype="bf16", K=1, backward=False,
                    desc="TTT-Linear inner model decode step (1 token per stream), bf16, B=8 H=12 d=64"),
+    # token-by-token generation through one whole layer (projection GEMM, prologue, decode kernel, epilogue, output
+    # GEMM), eager launches against one CUDA graph per rotary phase
+    "decode-layer": dict(kind="decode-layer", B=8, H=12, T=1, dtype="bf16", K=1, backward=False,
+                         desc="TTT layer decode step (hidden 768, 12 heads x 64), bf16, B=8, 1 token per step"),
     "decode-b256": dict(kind="decode", B=256, H=12, T=1, dtype="bf16", K=1, backward=False,
                         desc="TTT-Linear inner model decode step (1 token per stream), bf16, B=256 H=12 d=64"),
 }
@@ -433,6 +437,66 @@ def run_decode(args, w):
     print(json.dumps(line), flush=True)
 
 
+def run_decode_layer(args, w):
+    """One-token steps through the whole layer after a 64-token prefill: eager (five launches + host work per step)
+    and replayed from CUDA graphs (ttt_rs_b200.layer.DecodeGraphs)."""
+    import ttt_rs_b200 as tb
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operator has no CPU path")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    tb.load_library()
+    B, H = w["B"], w["H"]
+    C = H * F
+    dt = torch.bfloat16
+    torch.manual_seed(0)
+    cfg = tb.TTTLayerConfig(hidden_size=C, num_heads=H)
+    layer = tb.TTT(cfg, device=dev, dtype=dt)
+    steps = max(args.steps, 64)
+    x = (torch.randn(B, 64 + steps + 16, C, device=dev) * 0.5).to(dt)
+
+    def fresh():
+        inner = tb.new_inner(cfg, device=dev, dtype=dt, allow_partial=True, partial_in_place=True)
+        state = inner.init_state(B)
+        state.weight, state.bias = state.weight.contiguous(), state.bias.contiguous()
+        with torch.no_grad():
+            layer(x[:, :64], inner, state, 0)
+        return inner, state
+
+    inner, state = fresh()
+    pos = [64]
+
+    def eager():
+        with torch.no_grad():
+            layer(x[:, pos[0]:pos[0] + 1].contiguous(), inner, state, pos[0])
+        pos[0] = 64 + (pos[0] - 63) % (steps + 15)
+
+    ms_eager = time_events(eager, steps, 16)
+    inner, state = fresh()
+    dec = tb.DecodeGraphs(layer, inner, state, B)
+    pos[0] = 64
+
+    def graph():
+        dec.step(x[:, pos[0]:pos[0] + 1], pos[0])
+        pos[0] = 64 + (pos[0] - 63) % (steps + 15)
+
+    sampler = ClockSampler(0)
+    time_events(graph, 16, 16)  # the first pass over the 16 rotary phases captures their graphs
+    sampler.start()
+    ms_graph = time_events(graph, steps, 0)
+    clocks = sampler.stop()
+    line = {
+        "metric": "ttt_layer_decode_tokens_per_sec", "value": B / (ms_graph * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": steps, "warmup": 16, "ms_per_step": ms_graph, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": w["desc"], "global_batch": B, "l2": "launch-bound: the step moves about 8 MB"},
+        "clocks": clocks, "e2e": None, "gpu_launches": steps * 3,
+        "eager_ms_per_step": ms_eager, "graph_ms_per_step": ms_graph,
+        "roofline": None,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -446,6 +510,11 @@ def main():
     w = WORKLOADS[args.workload]
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
+    if w.get("kind") == "decode-layer":
+        if args.impl == "reference":
+            raise SystemExit("--impl reference is defined for the inner-loop workloads")
+        run_decode_layer(args, w)
+        return
     if w.get("kind") == "decode":
         if args.impl == "reference":
             raise SystemExit("--impl reference is defined for the inner-loop workloads")

@@ -109,3 +109,37 @@ def test_layer_prefill_then_token_by_token_decode():
         want.append(y)
     assert_close(torch.cat(ys, dim=1), torch.cat(want, dim=1), 2e-4, "prefill + decode outputs")
     assert_close(state.weight, st["weight"], 2e-4, "state after decode")
+
+
+@pytest.mark.gpu
+def test_decode_through_cuda_graphs_equals_eager_decode():
+    """The captured decode step (one CUDA graph per rotary phase, state advanced in place) gives the same bits as
+    calling the layer token by token, across two wraps of the rotary positions."""
+    import ttt_rs_b200 as tb
+    dev = torch.device("cuda:0")
+    B, H, T0, steps = 2, 2, 16, 35
+    cfg = tb.TTTLayerConfig(hidden_size=H * 64, num_heads=H, use_gate=True)
+    torch.manual_seed(3)
+    layer = tb.TTT(cfg, device=dev, dtype=torch.bfloat16)
+    x = (torch.randn(B, T0 + steps, H * 64, device=dev) * 0.5).to(torch.bfloat16)
+
+    def run(use_graphs):
+        inner = tb.new_inner(cfg, device=dev, dtype=torch.bfloat16, allow_partial=True, partial_in_place=True)
+        with torch.no_grad():
+            inner.inner.weight_init.copy_(torch.randn(H, 64, 64, generator=torch.Generator().manual_seed(1)) * 0.02)
+            state = inner.init_state(B)
+            state.weight, state.bias = state.weight.contiguous(), state.bias.contiguous()
+            layer(x[:, :T0], inner, state, 0)  # prefill
+            dec = tb.DecodeGraphs(layer, inner, state, B) if use_graphs else None
+            outs = []
+            for i in range(steps):
+                xi = x[:, T0 + i:T0 + i + 1]
+                y = dec.step(xi, T0 + i) if use_graphs else layer(xi.contiguous(), inner, state, T0 + i)
+                outs.append(y.clone())
+        torch.cuda.synchronize()
+        return torch.cat(outs, dim=1), state.weight.clone()
+
+    ye, we = run(False)
+    yg, wg = run(True)
+    assert torch.equal(ye, yg), "outputs differ between eager and graph decode"
+    assert torch.equal(we, wg), "state differs between eager and graph decode"

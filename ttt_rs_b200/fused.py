@@ -349,13 +349,16 @@ class TTTLinear(torch.nn.Module):
 class FusedTileMultiTTTLinear(torch.nn.Module):
     """`fused-tile-multi` inner model: whole-sequence forward in a single launch."""
 
-    def __init__(self, inner: TTTLinear, allow_partial: bool = False):
+    def __init__(self, inner: TTTLinear, allow_partial: bool = False, partial_in_place: bool = False):
         """`allow_partial`: run a remainder / decode mini-batch (fewer tokens than the mini-batch) through the
         partial-mini-batch kernel, with the semantics of the reference's unfused inner model, instead of refusing it
-        as the reference's fused type does.  Inference only (no gradient is recorded for such a call)."""
+        as the reference's fused type does.  Inference only (no gradient is recorded for such a call).
+        `partial_in_place`: such a call advances the state tensors in place (same device addresses every step, which
+        a captured CUDA graph of the decode step needs) instead of binding new tensors to the state."""
         super().__init__()
         self.inner = inner
         self.allow_partial = allow_partial
+        self.partial_in_place = partial_in_place
 
     @staticmethod
     def name() -> str:
@@ -395,7 +398,8 @@ class FusedTileMultiTTTLinear(torch.nn.Module):
             F = sl.qkv.xq.shape[-1]
             outs = TttTileMultiKernel.forward_partial(
                 TttInputs(sl.qkv.xq, sl.qkv.xk, sl.qkv.xv, state.weight, state.bias, sl.token_eta, sl.ttt_lr_eta,
-                          self.inner.ln_weight.detach(), self.inner.ln_bias.detach()), self._config(F))
+                          self.inner.ln_weight.detach(), self.inner.ln_bias.detach()), self._config(F),
+                in_place=self.partial_in_place)
             state.weight, state.bias = outs.weight, outs.bias
             return outs.output
         sl = inputs.slice_seq(r)

@@ -306,8 +306,55 @@ TTT._forward_train = _train_forward
 
 
 def new_inner(config: TTTLayerConfig, checkpoint_interval: int = 1, device=None, dtype=torch.float32,
-              allow_partial: bool = False):
+              allow_partial: bool = False, partial_in_place: bool = False):
     """The `fused-tile-multi` inner model matching a layer config (`allow_partial`: also accept sequence tails and
-    1-token decode steps, see FusedTileMultiTTTLinear)."""
+    1-token decode steps; `partial_in_place`: advance the state in place on such calls, see FusedTileMultiTTTLinear)."""
     return FusedTileMultiTTTLinear(TTTLinear(config.num_heads, config.head_dim, config.mini_batch_size, 1e-6,
-                                             checkpoint_interval, device=device, dtype=dtype), allow_partial)
+                                             checkpoint_interval, device=device, dtype=dtype), allow_partial,
+                                   partial_in_place)
+
+
+class DecodeGraphs:
+    """Token-by-token generation through one layer with the whole step (projection GEMM, prologue, decode kernel,
+    epilogue, output GEMM: five launches, launch-bound at small batch) captured once per rotary phase as a CUDA graph.
+
+    The rotary position enters the prologue as a scalar argument, so with positions wrapped at the mini-batch there
+    are `mini_batch_size` distinct steps; each is captured on first use.  The state is advanced in place, the input
+    is read from `self.x` [B, 1, hidden] and the result lands in the tensor `step` returns (overwritten by the next
+    step of the same phase)."""
+
+    def __init__(self, layer: "TTT", inner: FusedTileMultiTTTLinear, state: TTTLinearState, batch: int):
+        c = layer.config
+        if c.pos_encoding == "rope_global":
+            raise ValueError("rope_global positions never repeat: the step cannot be captured once per phase")
+        if not (inner.allow_partial and inner.partial_in_place):
+            raise ValueError("the inner model must be built with allow_partial=True, partial_in_place=True")
+        self.layer, self.inner, self.state = layer, inner, state
+        p = layer.q_proj
+        self.x = torch.zeros(batch, 1, c.hidden_size, dtype=p.dtype, device=p.device)
+        self.period = c.mini_batch_size if c.pos_encoding == "rope" else 1
+        self._graphs, self._outs = {}, {}
+
+    def step(self, x: torch.Tensor, start_idx: int) -> torch.Tensor:
+        """One token per sequence: x [B, 1, hidden] at position `start_idx`."""
+        self.x.copy_(x)
+        ph = start_idx % self.period
+        g = self._graphs.get(ph)
+        if g is None:
+            # warm-up run on a side stream (lazy initialisation of the libraries must happen outside the capture);
+            # it advances the state once, so the state is saved and restored around it
+            w0, b0 = self.state.weight.clone(), self.state.bias.clone()
+            s = torch.cuda.Stream(self.x.device)
+            s.wait_stream(torch.cuda.current_stream(self.x.device))
+            with torch.cuda.stream(s), torch.no_grad():
+                self.layer(self.x, self.inner, self.state, ph)
+            torch.cuda.current_stream(self.x.device).wait_stream(s)
+            self.state.weight.copy_(w0)
+            self.state.bias.copy_(b0)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g), torch.no_grad():
+                self._outs[ph] = self.layer(self.x, self.inner, self.state, ph)
+            self._graphs[ph] = g
+            # the capture itself does not execute: the state is still w0, b0 and the replay below does the step
+        g.replay()
+        return self._outs[ph]
