@@ -260,11 +260,23 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     {
       const Pk<NP> agt[4] = {gt[0][0], gt[1][0], gt[0][1], gt[1][1]};
       if (w_moves) state_update_direct<NP>(wt, agt, pk, lane);
+      if constexpr (NP == 1) {
+        // column sums of the bf16 Gp tile as a product with a tile of ones (every row of the result is the sum)
+        constexpr uint32_t ONES = 0x3F803F80u;
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
-        const F2 cs = f2add(gp[nt][0], gp[nt][1]);
-        bias[2 * nt] -= te15 * col_sum(cs.x);
-        bias[2 * nt + 1] -= te15 * col_sum(cs.y);
+        for (int nt = 0; nt < 2; ++nt) {
+          float cs[4] = {0.f, 0.f, 0.f, 0.f};
+          mma_bf16(cs, ONES, ONES, ONES, ONES, gt[nt][0].p[0], gt[nt][1].p[0]);
+          bias[2 * nt] -= te15 * cs[0];
+          bias[2 * nt + 1] -= te15 * cs[1];
+        }
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const F2 cs = f2add(gp[nt][0], gp[nt][1]);
+          bias[2 * nt] -= te15 * col_sum(cs.x);
+          bias[2 * nt + 1] -= te15 * col_sum(cs.y);
+        }
       }
     }
 

@@ -41,10 +41,15 @@ __device__ __forceinline__ void xch_rows(Xch4* xb, const Lane& L, const float4 a
   flag = __syncthreads_or(flag);
   const float4* r0 = &xb->v[L.g][0];
   const float4* r1 = &xb->v[L.g + 8][0];
-  o0 = make_float4((r0[0].x + r0[1].x) + (r0[2].x + r0[3].x), (r0[0].y + r0[1].y) + (r0[2].y + r0[3].y),
-                   (r0[0].z + r0[1].z) + (r0[2].z + r0[3].z), (r0[0].w + r0[1].w) + (r0[2].w + r0[3].w));
-  o1 = make_float4((r1[0].x + r1[1].x) + (r1[2].x + r1[3].x), (r1[0].y + r1[1].y) + (r1[2].y + r1[3].y),
-                   (r1[0].z + r1[1].z) + (r1[2].z + r1[3].z), (r1[0].w + r1[1].w) + (r1[2].w + r1[3].w));
+  // (w0 + w1) + (w2 + w3) per component, two components per packed add
+  auto sum4 = [](const float4* r) {
+    const float4 a = r[0], b = r[1], c = r[2], d = r[3];
+    const F2 lo = f2add(f2add(f2(a.x, a.y), f2(b.x, b.y)), f2add(f2(c.x, c.y), f2(d.x, d.y)));
+    const F2 hi = f2add(f2add(f2(a.z, a.w), f2(b.z, b.w)), f2add(f2(c.z, c.w), f2(d.z, d.w)));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+  };
+  o0 = sum4(r0);
+  o1 = sum4(r1);
 }
 // Two-value variant (same buffer type, half the shuffles).
 __device__ __forceinline__ void xch_rows2(Xch4* xb, const Lane& L, float a0x, float a0y, float a1x, float a1y,
@@ -61,8 +66,9 @@ __device__ __forceinline__ void xch_rows2(Xch4* xb, const Lane& L, float a0x, fl
   const float4 q = *reinterpret_cast<const float4*>(&base[L.g * 6 + 2]);
   const float4 p2 = *reinterpret_cast<const float4*>(&base[(L.g + 8) * 6]);
   const float4 q2 = *reinterpret_cast<const float4*>(&base[(L.g + 8) * 6 + 2]);
-  o0 = make_float2((p.x + p.z) + (q.x + q.z), (p.y + p.w) + (q.y + q.w));
-  o1 = make_float2((p2.x + p2.z) + (q2.x + q2.z), (p2.y + p2.w) + (q2.y + q2.w));
+  // (w0 + w1) + (w2 + w3) for both values of a row with packed adds
+  o0 = f2add(f2add(f2(p.x, p.y), f2(p.z, p.w)), f2add(f2(q.x, q.y), f2(q.z, q.w)));
+  o1 = f2add(f2add(f2(p2.x, p2.y), f2(p2.z, p2.w)), f2add(f2(q2.x, q2.y), f2(q2.z, q2.w)));
 }
 
 // LayerNorm row statistics of a slab: mean and 1/sqrt(var + eps) for rows g and g+8.
