@@ -1,4 +1,4 @@
-// TTT-MLP backward (bf16 I/O, float32 state), first version: one 8-warp CTA per (batch, head) stream.
+// TTT-MLP backward (bf16 I/O, float32 state), first version: one 16-warp CTA per (batch, head) stream.
 //
 // What it computes: the gradient of the whole-sequence TTT-MLP forward (semantics rust/core/src/mlp.rs:127-208; the
 // reference obtains this gradient from Burn autodiff, it has no fused MLP kernel) for loss = <grad_output, output>:
@@ -21,7 +21,9 @@
 
 namespace ttt {
 
-constexpr int MB_THREADS = 256;
+constexpr int MB_THREADS = 512;
+constexpr int MB_NW = MB_THREADS / 32;  // warps of the CTA
+constexpr int MB_RPW = CS / MB_NW;       // tile rows a warp owns in the row-wise (LayerNorm) steps
 constexpr int MB_E = 256;  // hidden width of the inner MLP (4 * head_dim)
 // Row strides of the shared-memory tiles: width + 8 floats.  With a stride of 8 (mod 32) the 64-bit fragment loads of
 // a half-warp (4 rows x 4 column pairs) fall in 16 distinct bank pairs; unpadded rows would put the 8 rows of a
@@ -61,11 +63,13 @@ __device__ __forceinline__ float2 pair_k_of_B(const MB m, int k, int j) {
 template <bool ACC, int K, int M, int N, class MC, class MA, class MB>
 __device__ void tile_mma(const MC C, const MA A, const MB B, float alpha) {
   constexpr int NW = MB_THREADS / 32, ntn = N / 8, total = (M / 16) * ntn;
-  constexpr int TG = total >= 4 * NW ? 4 : (total + NW - 1) / NW;  // tiles of a warp in flight together
-  // The tiles of one group are tile0 + u * NW: with N a multiple of 8 * NW * TG they share their rows (one A fragment
-  // serves all of them), with N == 8 * NW they share their columns (one B fragment).
+  // Tiles of a warp in flight together: tile0 + u * NW, u < TG.  When the tiles of a row of the output go round the
+  // warps a whole number of times (ntn = NW * TG) they share their rows (one A fragment serves all of them); when NW
+  // is a multiple of ntn they share their columns (one B fragment).
+  constexpr int TG0 = total >= 4 * NW ? 4 : (total + NW - 1) / NW;
+  constexpr int TG = (ntn % NW == 0 && ntn / NW >= 2 && ntn / NW <= 4) ? ntn / NW : TG0;
   constexpr bool SHARE_A = TG > 1 && (ntn % (NW * TG) == 0);
-  constexpr bool SHARE_B = TG > 1 && !SHARE_A && ntn == NW;
+  constexpr bool SHARE_B = TG > 1 && !SHARE_A && (NW % ntn == 0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 #pragma unroll 1
   for (int tile0 = warp; tile0 < total; tile0 += NW * TG) {
@@ -159,8 +163,8 @@ __device__ void ln_l2_grad_tile(MlpBwdSmem& S, const float (*z)[FP], float (*G)[
                                 float eps) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll
-  for (int rr = 0; rr < 2; ++rr) {
-    const int r = 2 * warp + rr;
+  for (int rr = 0; rr < MB_RPW; ++rr) {
+    const int r = MB_RPW * warp + rr;
     float xv[2], gx[2];
     const float a = z[r][lane], b = z[r][lane + 32];
     const float mu = warp_sum(a + b) * (1.f / HD);
@@ -192,21 +196,20 @@ __device__ void add_colsum(float* dst, const float* tile, int N, int ld, float s
   }
 }
 
-// Up to four [16][64] bf16 tiles from global memory into float32 shared tiles: every thread owns four consecutive
-// elements (one 8-byte load) of each tile, and all loads are issued before the first value is used (a load that
+// Up to four [16][64] bf16 tiles from global memory into float32 shared tiles: every thread owns two consecutive
+// elements (one 4-byte load) of each tile, and all loads are issued before the first value is used (a load that
 // waits behind the previous tile's dependent stores would cost a full memory round trip per tile).
 template <int NT>
 __device__ void load_tiles_bf16(float (*const (&dst)[NT])[FP], const __nv_bfloat16* const (&src)[NT]) {
-  const int e = 4 * threadIdx.x, r = e / HD, c = e % HD;
-  uint2 raw[NT];
+  static_assert(MB_THREADS * 2 == CS * HD, "two elements per thread");
+  const int e = 2 * threadIdx.x, r = e / HD, c = e % HD;
+  uint32_t raw[NT];
 #pragma unroll
-  for (int i = 0; i < NT; ++i) raw[i] = *reinterpret_cast<const uint2*>(src[i] + e);
+  for (int i = 0; i < NT; ++i) raw[i] = *reinterpret_cast<const uint32_t*>(src[i] + e);
 #pragma unroll
   for (int i = 0; i < NT; ++i) {
-    dst[i][r][c] = bf16_lo(raw[i].x);
-    dst[i][r][c + 1] = bf16_hi(raw[i].x);
-    dst[i][r][c + 2] = bf16_lo(raw[i].y);
-    dst[i][r][c + 3] = bf16_hi(raw[i].y);
+    dst[i][r][c] = bf16_lo(raw[i]);
+    dst[i][r][c + 1] = bf16_hi(raw[i]);
   }
 }
 __device__ void store_tile_bf16(__nv_bfloat16* dst, const float (*src)[FP]) {
@@ -347,21 +350,22 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     const float* g2p = g2p_all + (size_t)s * CS * F;
     {
       // every global load of the stage's inputs is issued before the first dependent store
-      float4 g1v[4];
+      constexpr int G1V = CS * MB_E / 4 / MB_THREADS;
+      float4 g1v[G1V];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) g1v[i] = reinterpret_cast<const float4*>(g1p)[tid + MB_THREADS * i];
-      const float4 g2v = reinterpret_cast<const float4*>(g2p)[tid];
+      for (int i = 0; i < G1V; ++i) g1v[i] = reinterpret_cast<const float4*>(g1p)[tid + MB_THREADS * i];
+      const float2 g2v = reinterpret_cast<const float2*>(g2p)[tid];
       float(*const dst[4])[FP] = {S.q, S.k, S.v, S.dO};
       const T* const src[4] = {static_cast<const T*>(p.xq) + r0, static_cast<const T*>(p.xk) + r0,
                                static_cast<const T*>(p.xv) + r0, static_cast<const T*>(p.d_out) + r0};
       load_tiles_bf16<4>(dst, src);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < G1V; ++i) {
         const int e = 4 * (tid + MB_THREADS * i), r = e / MB_E, c = e % MB_E;
         S.t1[r][c] = g1v[i].x; S.t1[r][c + 1] = g1v[i].y; S.t1[r][c + 2] = g1v[i].z; S.t1[r][c + 3] = g1v[i].w;
       }
-      const int e = 4 * tid, r = e / HD, c = e % HD;
-      S.dg2[r][c] = g2v.x; S.dg2[r][c + 1] = g2v.y; S.dg2[r][c + 2] = g2v.z; S.dg2[r][c + 3] = g2v.w;
+      const int e = 2 * tid, r = e / HD, c = e % HD;
+      S.dg2[r][c] = g2v.x; S.dg2[r][c + 1] = g2v.y;
     }
     if (tid < CS) {
       S.lr[tid] = ld_as_float<T>(p.lr, row_base + (size_t)s * CS + tid);
@@ -419,8 +423,8 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     {
       float pg[2] = {0.f, 0.f}, pb[2] = {0.f, 0.f};
 #pragma unroll
-      for (int rr = 0; rr < 2; ++rr) {
-        const int r = 2 * warp + rr;
+      for (int rr = 0; rr < MB_RPW; ++rr) {
+        const int r = MB_RPW * warp + rr;
         const float a = S.z2b[r][lane], b = S.z2b[r][lane + 32];
         const float mu = warp_sum(a + b) * (1.f / HD);
         const float var = warp_sum((a - mu) * (a - mu) + (b - mu) * (b - mu)) * (1.f / HD);
@@ -452,7 +456,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     if (tid < 2 * HD) {
       float s_ = 0.f;
 #pragma unroll
-      for (int w = 0; w < 8; ++w) s_ += colpart[w][tid];
+      for (int w = 0; w < MB_NW; ++w) s_ += colpart[w][tid];
       if (tid < HD) S.dgam[tid] += s_; else S.dbet[tid - HD] += s_;
     }
     TRM(7)
@@ -509,8 +513,8 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     }
     // dell[j] = -( gl1[j].K[j] + g1[j].db1 + gl2[j].x2[j] + g2[j].db2 )
 #pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-      const int r = 2 * warp + rr;
+    for (int rr = 0; rr < MB_RPW; ++rr) {
+      const int r = MB_RPW * warp + rr;
       float acc = 0.f;
       for (int c = lane; c < F; c += 32) acc += S.gl1[r][c] * S.k[r][c] + S.g2[r][c] * db2[c];
       for (int c = lane; c < E; c += 32) acc += S.g1[r][c] * db1[c] + S.t4[r][c] * S.x2[r][c];
@@ -539,8 +543,8 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     {
       float pg[2] = {0.f, 0.f}, pb[2] = {0.f, 0.f};
 #pragma unroll
-      for (int rr = 0; rr < 2; ++rr) {
-        const int r = 2 * warp + rr;
+      for (int rr = 0; rr < MB_RPW; ++rr) {
+        const int r = MB_RPW * warp + rr;
         const float a = S.z2[r][lane], b = S.z2[r][lane + 32];
         const float mu = warp_sum(a + b) * (1.f / HD);
         const float var = warp_sum((a - mu) * (a - mu) + (b - mu) * (b - mu)) * (1.f / HD);
@@ -592,7 +596,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     if (tid < 2 * HD) {
       float s_ = 0.f;
 #pragma unroll
-      for (int w = 0; w < 8; ++w) s_ += colpart[w][tid];
+      for (int w = 0; w < MB_NW; ++w) s_ += colpart[w][tid];
       if (tid < HD) S.dgam[tid] += s_; else S.dbet[tid - HD] += s_;
     }
     TRM(12)
