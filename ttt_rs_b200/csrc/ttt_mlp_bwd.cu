@@ -54,6 +54,21 @@ struct SB {
 template <int LD, bool TR>
 __device__ __forceinline__ SB<LD, !TR> tr(const SB<LD, TR> m) { return SB<LD, !TR>{m.a}; }
 
+// float32 matrix [R][C] in the workspace, stored tile by tile in accumulator-fragment order: the 16 x 8 tile
+// (r / 16, c / 8) occupies 128 consecutive floats, its rows 0..7 before its rows 8..15, and inside a half the
+// element (r % 8, c % 8) sits at 8 * (r % 8) + (c % 8).  A warp's read-modify-write of an output tile is then two
+// contiguous 256-byte accesses instead of sixteen 32-byte row pieces, and so are the operand fetches along a row.
+// TR = true: the operand is the transpose of the stored matrix.
+template <int R, int C, bool TR>
+struct MatG {
+  float* p;
+  static __device__ __forceinline__ int at(int r, int c) {
+    return (((r >> 4) * (C / 8) + (c >> 3)) << 7) + (((r >> 3) & 1) << 6) + ((r & 7) << 3) + (c & 7);
+  }
+};
+template <int R, int C, bool TR>
+__device__ __forceinline__ MatG<R, C, !TR> tr(const MatG<R, C, TR> m) { return MatG<R, C, !TR>{m.p}; }
+
 __device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
 }
@@ -107,6 +122,42 @@ __device__ __forceinline__ void load_B(const MatT<RS, CS_> B, int k0, int j0, in
     }
   }
 }
+template <int R, int C, bool TR>
+__device__ __forceinline__ void load_A(const MatG<R, C, TR> A, int i0, int k0, int lane, uint32_t (&r)[4]) {
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int i = i0 + g + 8 * (q & 1), k = k0 + 2 * t + 8 * (q >> 1);
+    if constexpr (!TR) {  // stored [i][k]: the pair (k, k + 1) is adjacent
+      const float2 f = *reinterpret_cast<const float2*>(A.p + A.at(i, k));
+      r[q] = pack_bf16(f.x, f.y);
+    } else {
+      r[q] = pack_bf16(A.p[A.at(k, i)], A.p[A.at(k + 1, i)]);
+    }
+  }
+}
+template <int R, int C, bool TR>
+__device__ __forceinline__ void load_B(const MatG<R, C, TR> B, int k0, int j0, int lane, uint32_t (&r)[2]) {
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    const int k = k0 + 2 * t + 8 * q, j = j0 + g;
+    if constexpr (TR) {  // stored [j][k]: the pair (k, k + 1) is adjacent
+      const float2 f = *reinterpret_cast<const float2*>(B.p + B.at(j, k));
+      r[q] = pack_bf16(f.x, f.y);
+    } else {
+      r[q] = pack_bf16(B.p[B.at(k, j)], B.p[B.at(k + 1, j)]);
+    }
+  }
+}
+template <int R, int C>
+__device__ __forceinline__ float2 c_load(const MatG<R, C, false> M, int i, int j) {
+  return *reinterpret_cast<const float2*>(M.p + M.at(i, j));
+}
+template <int R, int C>
+__device__ __forceinline__ void c_store(const MatG<R, C, false> M, int i, int j, float x, float y) {
+  *reinterpret_cast<float2*>(M.p + M.at(i, j)) = make_float2(x, y);
+}
 // the output pair (i, j), (i, j + 1)
 template <int RS>
 __device__ __forceinline__ float2 c_load(const MatT<RS, 1> C, int i, int j) {
@@ -137,21 +188,29 @@ struct Prod {
 template <int K, class MA, class MB>
 __device__ __forceinline__ Prod<K, MA, MB> prod(const MA a, const MB b) { return Prod<K, MA, MB>{a, b}; }
 
+template <class X>
+struct is_global_operand : std::false_type {};
+template <int R, int C, bool TR>
+struct is_global_operand<MatG<R, C, TR>> : std::true_type {};
+
 // C[M x N] = (ACC ? C : 0) + alpha * sum over the given products of A[M x K] . B[K x N];  M % 16 == 0, N % 8 == 0,
 // K % 16 == 0; every extent and stride is a compile-time constant.  With an epilogue functor the finished pair
 // (i, j), (i, j + 1) goes to epi(i, j, x, y) instead of being stored to C.
 // Output tiles of 16 x 8 are dealt to the warps round-robin (the same tile always goes to the same warp, so
-// successive accumulations into one matrix need no barrier between them).  A warp works on up to four of its tiles
-// at a time: tile0 + u * NW, u < TG.  When the tiles of a row of the output go round the warps a whole number of
-// times they share their rows (one A fragment serves all of them); when NW is a multiple of the tiles per row they
-// share their columns (one B fragment).
-template <bool ACC, int M, int N, class MC, class EPI, class... PR>
+// successive accumulations into one matrix need no barrier between them).  A warp works on up to TGMAX of its tiles
+// at a time: tile0 + u * NW, u < TG, so that their loads (for an accumulation into the float32 state in the
+// workspace: a round trip to L2) are in flight together.  When a row of output tiles goes round the warps GA times,
+// GA consecutive tiles of a warp share their rows (one A fragment serves them); when NW is a multiple of the tiles
+// per row all tiles of a warp share their columns (one B fragment).
+template <bool ACC, int M, int N, int TGMAX = 4, class MC, class EPI, class... PR>
 __device__ __forceinline__ void tile_mma(const MC C, const float alpha, EPI epi, const PR... pr) {
-  constexpr int NW = MB_NW, ntn = N / 8, total = (M / 16) * ntn;
-  constexpr int TG0 = total >= 4 * NW ? 4 : (total + NW - 1) / NW;
-  constexpr int TG = (ntn % NW == 0 && ntn / NW >= 2 && ntn / NW <= 4) ? ntn / NW : TG0;
-  constexpr bool SHARE_A = TG > 1 && (ntn % (NW * TG) == 0);
-  constexpr bool SHARE_B = TG > 1 && !SHARE_A && (NW % ntn == 0);
+  constexpr int NW = MB_NW, ntn = N / 8, total = (M / 16) * ntn, per_warp = (total + NW - 1) / NW;
+  constexpr int GA = (ntn % NW == 0) ? ntn / NW : 1;
+  constexpr bool SHARE_B = (NW % ntn == 0) && per_warp > 1;
+  constexpr int TG1 = per_warp < TGMAX ? per_warp : TGMAX;
+  constexpr int TG = TG1 < GA ? GA : TG1 / GA * GA;
+  constexpr int NA = TG / GA, NB = SHARE_B ? 1 : TG;
+  static_assert(TG % GA == 0 && GA <= 4, "tile grouping");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 #pragma unroll 1
   for (int tile0 = warp; tile0 < total; tile0 += NW * TG) {
@@ -176,27 +235,24 @@ __device__ __forceinline__ void tile_mma(const MC C, const float alpha, EPI epi,
       }
     }
     auto run = [&](const auto P) {
-      constexpr int K = std::remove_reference<decltype(P)>::type::K;
-#pragma unroll(K >= 64 ? 2 : 1)
+      typedef typename std::remove_cv<typename std::remove_reference<decltype(P)>::type>::type PT;
+      constexpr int K = PT::K;
+      // operands in the workspace: the whole contraction unrolled, so that the loads of all steps are in flight
+      constexpr bool GLOBAL = is_global_operand<decltype(PT::A)>::value || is_global_operand<decltype(PT::B)>::value;
+#pragma unroll(GLOBAL ? 16 : (K >= 64 ? 2 : 1))
       for (int k0 = 0; k0 < K; k0 += 16) {
-        uint32_t pa[TG][4], pb[TG][2];
+        uint32_t pa[NA][4], pb[NB][2];
 #pragma unroll
         for (int u = 0; u < TG; ++u) {
-          if (u == 0 || !SHARE_A) {
-            load_A(P.A, i0[u], k0, lane, pa[u]);
-          } else {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) pa[u][q] = pa[0][q];
-          }
-          if (u == 0 || !SHARE_B) {
-            load_B(P.B, k0, j0[u], lane, pb[u]);
-          } else {
-            pb[u][0] = pb[0][0];
-            pb[u][1] = pb[0][1];
-          }
+          if (u % GA == 0) load_A(P.A, i0[u], k0, lane, pa[u / GA]);
+          if (u == 0 || !SHARE_B) load_B(P.B, k0, j0[u], lane, pb[SHARE_B ? 0 : u]);
         }
 #pragma unroll
-        for (int u = 0; u < TG; ++u) mma_bf16(acc[u], pa[u][0], pa[u][1], pa[u][2], pa[u][3], pb[u][0], pb[u][1]);
+        for (int u = 0; u < TG; ++u) {
+          const uint32_t(&a)[4] = pa[u / GA];
+          const uint32_t(&b_)[2] = pb[SHARE_B ? 0 : u];
+          mma_bf16(acc[u], a[0], a[1], a[2], a[3], b_[0], b_[1]);
+        }
       }
     };
     (run(pr), ...);
@@ -262,8 +318,8 @@ __device__ __forceinline__ void for_c(Fn f) {
 struct __align__(16) MlpBwdSmem {
   // bf16 operand tiles
   bf z1[CS][EB], x2[CS][EB], g1[CS][EB], z1b[CS][EB], x2b[CS][EB];
-  bf t1[CS][EB], t2[CS][EB], t4[CS][EB];  // g1p | dz1b;  dg1, dh;  gl2, dz1
-  bf q[CS][FB], k[CS][FB], v[CS][FB], dO[CS][FB], g2[CS][FB], g2p[CS][FB], g2pn[CS][FB], dz2b[CS][FB], dz2[CS][FB];
+  bf t1[CS][EB], t2[CS][EB], t3[CS][EB], t4[CS][EB];  // g1p | dz1b;  dg1, dh;  gl2;  dz1 (and column partials)
+  bf q[CS][FB], k[CS][FB], v[CS][FB], dO[CS][FB], g2[CS][FB], g2p[CS][FB], dz2b[CS][FB], dz2[CS][FB];
   bf m1[CS][CB], m2[CS][CB], m1n[CS][CB], m2n[CS][CB], da1[CS][CB], da2[CS][CB];  // m*n = -m*
   bf w1[HD][EB], w2[MB_E][FB];  // bf16 shadows of the float32 state in the workspace
   // float32 tiles
@@ -320,7 +376,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
   constexpr int F = HD, E = MB_E;
   const size_t row_base = (size_t)stream * p.T;
 
-  // per-stream workspace: W1 [F][E], W2 [E][F], dW1, dW2 (float32), then g1p [NS][16][E], g2p [NS][16][F] (bf16)
+  // per-stream workspace: W1 [F][E], W2 [E][F], dW1, dW2 (float32, in the tile order of MatG), then g1p [NS][16][E], g2p [NS][16][F] (bf16)
   float* ws = p.workspace + (size_t)stream * p.ws_stride;
   float* W1 = ws;
   float* W2 = W1 + F * E;
@@ -343,8 +399,8 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
   for (int e = tid; e < F * E; e += MB_THREADS) {
     const bf a = static_cast<const bf*>(p.w1)[(size_t)stream * F * E + e];
     const bf b = static_cast<const bf*>(p.w2)[(size_t)stream * F * E + e];
-    W1[e] = __bfloat162float(a);
-    W2[e] = __bfloat162float(b);
+    W1[MatG<F, E, false>::at(e / E, e % E)] = __bfloat162float(a);
+    W2[MatG<E, F, false>::at(e / F, e % F)] = __bfloat162float(b);
     S.w1[e / E][e % E] = a;
     S.w2[e / F][e % F] = b;
     dW1[e] = 0.f;
@@ -360,18 +416,25 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
   }
   __syncthreads();
   const float te_last = S.te[CS - 1];
+// per-phase cycle counts of block 0 (instrumented builds only; written to the status words after the walk)
+#ifdef TTT_MLP_TRACE
+  unsigned long long tr_acc[16] = {0}, tr_last = clock64();
+#define TRM(i) { __syncthreads(); const unsigned long long n_ = clock64(); tr_acc[i] += n_ - tr_last; tr_last = n_; }
+#else
+#define TRM(i)
+#endif
 
   // ---- operand / output views
-  const MatT<E, 1> mW1{W1}, mdW1{dW1};
-  const MatT<F, 1> mW2{W2}, mdW2{dW2};
+  const MatG<F, E, false> mW1{W1}, mdW1{dW1};
+  const MatG<E, F, false> mW2{W2}, mdW2{dW2};
   const MatT<1, 1> none{nullptr};
   typedef SB<EB, false> TE;
   typedef SB<FB, false> TF_;
   typedef SB<CB, false> TC;
   const TE sx2{smem_u32(S.x2)}, sg1{smem_u32(S.g1)}, sz1b{smem_u32(S.z1b)}, sx2b{smem_u32(S.x2b)};
-  const TE st1{smem_u32(S.t1)}, st2{smem_u32(S.t2)}, st4{smem_u32(S.t4)}, sw1{smem_u32(S.w1)};
+  const TE st1{smem_u32(S.t1)}, st2{smem_u32(S.t2)}, st3{smem_u32(S.t3)}, st4{smem_u32(S.t4)}, sw1{smem_u32(S.w1)};
   const TF_ sq{smem_u32(S.q)}, sk{smem_u32(S.k)}, sg2{smem_u32(S.g2)}, sg2p{smem_u32(S.g2p)}, sdz2b{smem_u32(S.dz2b)};
-  const TF_ sdz2{smem_u32(S.dz2)}, sw2{smem_u32(S.w2)}, sg2pn{smem_u32(S.g2pn)};
+  const TF_ sdz2{smem_u32(S.dz2)}, sw2{smem_u32(S.w2)};
   const TC sm1{smem_u32(S.m1)}, sm2{smem_u32(S.m2)}, sm1n{smem_u32(S.m1n)}, sm2n{smem_u32(S.m2n)};
   const TC sda1{smem_u32(S.da1)}, sda2{smem_u32(S.da2)};
   const MatT<FP, 1> mdq{&S.z2b[0][0]}, mdg2{&S.dg2[0][0]}, mdk{&S.dk[0][0]}, mgl1{&S.gl1[0][0]};
@@ -381,14 +444,14 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
 
   // W += sign * A^T B with the float32 master in the workspace and its bf16 shadow refreshed together
   auto update_w1 = [&](const float sign) {  // W1 += sign * K^T t1
-    tile_mma<true, F, E>(mW1, sign, [&](int i, int j, float x, float y) {
-      *reinterpret_cast<float2*>(W1 + i * E + j) = make_float2(x, y);
+    tile_mma<true, F, E, 8>(mW1, sign, [&](int i, int j, float x, float y) {
+      c_store(mW1, i, j, x, y);
       stb2(&S.w1[i][j], x, y);
     }, prod<CS>(tr(sk), st1));
   };
   auto update_w2 = [&](const float sign) {  // W2 += sign * X2^T g2p
-    tile_mma<true, E, F>(mW2, sign, [&](int i, int j, float x, float y) {
-      *reinterpret_cast<float2*>(W2 + i * F + j) = make_float2(x, y);
+    tile_mma<true, E, F, 8>(mW2, sign, [&](int i, int j, float x, float y) {
+      c_store(mW2, i, j, x, y);
       stb2(&S.w2[i][j], x, y);
     }, prod<CS>(tr(sx2), sg2p));
   };
@@ -444,14 +507,17 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       S.ell[tid - 256] = te_last * ld_as_float<T>(p.lr, row_base + (size_t)s * CS + (tid - 256));
     }
     __syncthreads();
+    TRM(0)
     forward_first_layer();
     forward_second_layer(std::true_type{}, reinterpret_cast<uint32_t*>(g1p_all + (size_t)s * CS * E),
                          reinterpret_cast<uint32_t*>(g2p_all + (size_t)s * CS * F));
+    TRM(1)
     update_w1(-1.f);
     update_w2(-1.f);
     add_colsum(b1, &S.t1[0][0], E, EB, -1.f);
     add_colsum(b2, &S.g2p[0][0], F, FB, -1.f);
     __syncthreads();
+    TRM(2)
   }
 
   // ============================== pass 2: backward walk ==============================
@@ -471,17 +537,14 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       if (tid < 128) g2v = reinterpret_cast<const uint4*>(g2p_all + (size_t)s * CS * F)[tid];
       *reinterpret_cast<uint4*>(&dst[r][c]) = in;
       *reinterpret_cast<uint4*>(&S.t1[tid >> 5][8 * (tid & 31)]) = g1v;
-      if (tid < 128) {
-        *reinterpret_cast<uint4*>(&S.g2p[r][c]) = g2v;
-        const uint32_t sgn = 0x80008000u;  // -(l o g2): the sign bits of the eight bf16 values flipped
-        *reinterpret_cast<uint4*>(&S.g2pn[r][c]) = make_uint4(g2v.x ^ sgn, g2v.y ^ sgn, g2v.z ^ sgn, g2v.w ^ sgn);
-      }
+      if (tid < 128) *reinterpret_cast<uint4*>(&S.g2p[r][c]) = g2v;
     }
     if (tid < CS) {
       S.lr[tid] = ld_as_float<T>(p.lr, row_base + (size_t)s * CS + tid);
       S.ell[tid] = te_last * S.lr[tid];
     }
     __syncthreads();
+    TRM(3)
     // ---- state at the start of this stage: undo the stage's updates (W1 first: X2 depends on it)
     update_w1(1.f);
     add_colsum(b1, &S.t1[0][0], E, EB, 1.f);
@@ -490,8 +553,10 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     update_w2(1.f);
     add_colsum(b2, &S.g2p[0][0], F, FB, 1.f);
     __syncthreads();
+    TRM(4)
     // ---- forward intermediates of the stage
     forward_second_layer(std::false_type{}, nullptr, nullptr);
+    TRM(5)
     for_c([&](int i, int j) { S.eta[i][j] = (j <= i) ? S.te[i] * S.lr[j] : 0.f; });
     tile_mma<false, CS, CS>(ma1, 1.f, noepi, prod<F>(sq, tr(sk)));                 // a1 = Q K^T
     __syncthreads();
@@ -523,6 +588,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     }, prod<E>(sx2b, sw2), prod<CS>(sm2n, sg2));
     __syncthreads();
 
+    TRM(6)
     // ---- 1. output LayerNorm: dz2b, LN parameter gradients (one row per warp, columns 2 lane, 2 lane + 1)
     {
       const int r = warp, c = 2 * lane;
@@ -549,6 +615,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       for (int w = 0; w < MB_NW; ++w) s_ += cp[w][tid];
       if (tid < HD) S.dgam[tid] += s_; else S.dbet[tid - HD] += s_;
     }
+    TRM(7)
     // ---- 2. z2b = x2b W2 + b2 - M2 g2
     tile_mma<false, CS, CS>(mdm, -1.f, noepi, prod<F>(sdz2b, tr(sg2)));            // dM2 = -tril(dz2b g2^T)
     tile_mma<false, CS, F>(mdg2, 1.f, noepi, prod<CS>(tr(sm2n), sdz2b));           // dg2 = -M2^T dz2b
@@ -559,6 +626,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       S.deta[i][j] = d * (1.f + S.a2[i][j]);
     });
     __syncthreads();
+    TRM(8)
     // ---- 3. dz1b = (dz2b W2^T + dA2 x2) o gelu'(z1b)  (kept in t1)
     tile_mma<false, CS, E>(none, 1.f, [&](int i, int j, float x, float y) {
       const float2 z = ldb2(&S.z1b[i][j]);
@@ -585,9 +653,10 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     __syncthreads();
     tile_mma<false, CS, F>(mdq, 1.f, noepi, prod<E>(st1, tr(sw1)), prod<CS>(sda1, sk));   // dq = dz1b W1^T + dA1 K
     tile_mma<false, CS, F>(mdk, 1.f, noepi, prod<CS>(tr(sda1), sq));               // dk = dA1^T Q
+    TRM(9)
     // ---- 5. the four state updates; dW1, db1, dW2, db2 still hold the gradients w.r.t. the next stage's state
     tile_mma<false, CS, F>(mgl1, 1.f, noepi, prod<E>(sg1, tr(mdW1)));              // gl1 = g1 dW1^T
-    tile_mma<false, CS, E>(st4, 1.f, noepi, prod<F>(sg2, tr(mdW2)));               // gl2 = g2 dW2^T
+    tile_mma<false, CS, E>(st3, 1.f, noepi, prod<F>(sg2, tr(mdW2)));               // gl2 = g2 dW2^T
     tile_mma<false, CS, E>(none, -1.f, [&](int i, int j, float x, float y) {         // dg1 = -M1^T dz1b - (l o K) dW1 - l (x) db1
       stb2(&S.t2[i][j], x - S.ell[i] * db1[j], y - S.ell[i] * db1[j + 1]);
     }, prod<CS>(tr(sm1), st1), prod<F>(sdz2, mdW1));
@@ -606,7 +675,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       }
 #pragma unroll
       for (int c = 2 * lane; c < E; c += 64) {
-        const float2 g_ = ldb2(&S.g1[r][c]), l2 = ldb2(&S.t4[r][c]), x = ldb2(&S.x2[r][c]);
+        const float2 g_ = ldb2(&S.g1[r][c]), l2 = ldb2(&S.t3[r][c]), x = ldb2(&S.x2[r][c]);
         acc += g_.x * db1[c] + g_.y * db1[c + 1] + l2.x * x.x + l2.y * x.y;
       }
       acc = warp_sum(acc);
@@ -618,6 +687,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       *d = make_float2(d->x - S.ell[r] * gl.x, d->y - S.ell[r] * gl.y);
     });
     __syncthreads();
+    TRM(10)
     // ---- 6. g1 = h o gelu'(z1), h = g2 W2^T (recomputed):  dz1 = dg1 o h o gelu''(z1) (t4),  dh = dg1 o gelu'(z1) (t2)
     tile_mma<false, CS, E>(none, 1.f, [&](int i, int j, float hx, float hy) {
       const float2 d = ldb2(&S.t2[i][j]), z = ldb2(&S.z1[i][j]);
@@ -627,6 +697,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     __syncthreads();
     tile_mma<true, CS, F>(mdg2, 1.f, noepi, prod<E>(st2, sw2));                    // dg2 += dh W2
     __syncthreads();
+    TRM(11)
     // ---- 7. second derivative through g2 = ln_l2_grad(z2, v - k): dz2, d target (into gl1, which is dead by now),
     //         LN parameter gradients (column partials in z1b's tile, whose scratch use is over)
     {
@@ -680,20 +751,25 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       for (int w = 0; w < MB_NW; ++w) s_ += colpart[w][tid];
       if (tid < HD) S.dgam[tid] += s_; else S.dbet[tid - HD] += s_;
     }
+    TRM(12)
     // ---- 8./9./10. z2 = x2 W2 + b2, x2 = gelu(z1), z1 = K W1 + b1:
-    //      dx2 = dA2^T x2b + dz2 W2^T - (l o g2) dW2^T  (never stored);  dz1 += dx2 o gelu'(z1) (t4);  dk += dz1 W1^T
+    //      dx2 = dA2^T x2b + dz2 W2^T - l o gl2  (never stored);  dz1 += dx2 o gelu'(z1) (t4);  dk += dz1 W1^T
     tile_mma<false, CS, E>(none, 1.f, [&](int i, int j, float x, float y) {
-      const float2 z = ldb2(&S.z1[i][j]), d = ldb2(&S.t4[i][j]);
+      const float2 z = ldb2(&S.z1[i][j]), d = ldb2(&S.t4[i][j]), gl2 = ldb2(&S.t3[i][j]);
+      x -= S.ell[i] * gl2.x;
+      y -= S.ell[i] * gl2.y;
       stb2(&S.t4[i][j], d.x + x * gelu_d1(z.x), d.y + y * gelu_d1(z.y));
-    }, prod<CS>(tr(sda2), sx2b), prod<F>(sdz2, tr(sw2)), prod<F>(sg2pn, tr(mdW2)));
+    }, prod<CS>(tr(sda2), sx2b), prod<F>(sdz2, tr(sw2)));
     __syncthreads();
     tile_mma<true, CS, F>(mdk, 1.f, noepi, prod<E>(st4, tr(sw1)));
+    TRM(13)
     // ---- gradients w.r.t. this stage's state (all reads of the next-stage gradients are done): one pass over each
     //      float32 master, the contraction running over the tokens of all the tile pairs
-    tile_mma<true, E, F>(mdW2, 1.f, noepi, prod<CS>(tr(st2), sg2), prod<CS>(tr(sx2b), sdz2b), prod<CS>(tr(sx2), sdz2));
-    tile_mma<true, F, E>(mdW1, 1.f, noepi, prod<CS>(tr(sq), st1), prod<CS>(tr(sk), st4));
+    tile_mma<true, E, F, 8>(mdW2, 1.f, noepi, prod<CS>(tr(st2), sg2), prod<CS>(tr(sx2b), sdz2b), prod<CS>(tr(sx2), sdz2));
+    tile_mma<true, F, E, 8>(mdW1, 1.f, noepi, prod<CS>(tr(sq), st1), prod<CS>(tr(sk), st4));
     add_colsum(db2, &S.dz2b[0][0], F, FB, 1.f);
     add_colsum(db1, &S.t1[0][0], E, EB, 1.f);
+    TRM(14)
     // ---- 11. eta factors and outputs of the stage
     if (tid >= MB_THREADS - CS) {
       const int i = tid - (MB_THREADS - CS);
@@ -720,12 +796,18 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       static_cast<uint32_t*>(p.d_v)[at] = pack_bf16(dT.x, dT.y);
     });
     __syncthreads();
+    TRM(15)
   }
+#ifdef TTT_MLP_TRACE
+  if (tid == 0 && blockIdx.x == 0 && p.trace != nullptr)
+    for (int i = 0; i < 16; ++i) p.trace[i] = (unsigned int)(tr_acc[i] / NS);
+#endif
+#undef TRM
 
   // ---- gradients w.r.t. the initial state, per-stream LayerNorm parameter gradients
   for (int e = tid; e < F * E; e += MB_THREADS) {
-    st_from_float<T>(p.d_w1, (size_t)stream * F * E + e, dW1[e]);
-    st_from_float<T>(p.d_w2, (size_t)stream * F * E + e, dW2[e]);
+    st_from_float<T>(p.d_w1, (size_t)stream * F * E + e, dW1[mdW1.at(e / E, e % E)]);
+    st_from_float<T>(p.d_w2, (size_t)stream * F * E + e, dW2[mdW2.at(e / F, e % F)]);
   }
   for (int e = tid; e < E; e += MB_THREADS) st_from_float<T>(p.d_b1, (size_t)stream * E + e, db1[e]);
   if (tid < F) {
