@@ -139,15 +139,16 @@ __device__ __forceinline__ void load_A(const MatG<R, C, TR> A, int i0, int k0, i
 template <int R, int C, bool TR>
 __device__ __forceinline__ void load_B(const MatG<R, C, TR> B, int k0, int j0, int lane, uint32_t (&r)[2]) {
   const int g = lane >> 2, t = lane & 3;
-#pragma unroll
-  for (int q = 0; q < 2; ++q) {
-    const int k = k0 + 2 * t + 8 * q, j = j0 + g;
-    if constexpr (TR) {  // stored [j][k]: the pair (k, k + 1) is adjacent
-      const float2 f = *reinterpret_cast<const float2*>(B.p + B.at(j, k));
-      r[q] = pack_bf16(f.x, f.y);
-    } else {
-      r[q] = pack_bf16(B.p[B.at(k, j)], B.p[B.at(k + 1, j)]);
-    }
+  // k0 is a multiple of 16 and j0 of 8, so the tile index and the place inside the tile separate
+  if constexpr (TR) {  // stored [j][k]: the pair (k, k + 1) is adjacent; the two registers lie in neighbouring tiles
+    const float* s = B.p + ((((j0 >> 4) * (C / 8) + (k0 >> 3)) << 7) + (((j0 >> 3) & 1) << 6) + (g << 3) + 2 * t);
+    const float2 f0 = *reinterpret_cast<const float2*>(s), f1 = *reinterpret_cast<const float2*>(s + 128);
+    r[0] = pack_bf16(f0.x, f0.y);
+    r[1] = pack_bf16(f1.x, f1.y);
+  } else {  // stored [k][j]: rows 2t, 2t + 1 of the upper and of the lower half of one tile
+    const float* s = B.p + ((((k0 >> 4) * (C / 8) + (j0 >> 3)) << 7) + (t << 4) + g);
+    r[0] = pack_bf16(s[0], s[8]);
+    r[1] = pack_bf16(s[64], s[72]);
   }
 }
 template <int R, int C>
@@ -273,15 +274,14 @@ __device__ __forceinline__ void tile_mma(const MC C, const float alpha, EPI epi,
 // ---- element-wise helpers --------------------------------------------------------------------------------------
 // tanh(x) = 1 - 2 / (1 + e^{2x}) with the fast exponential and division (relative error ~1e-6, as in the forward kernel)
 __device__ __forceinline__ float tanh_fast(float x) { return 1.f - __fdividef(2.f, 1.f + __expf(2.f * x)); }
-__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.f + tanh_fast(GELU_C0 * x * (1.f + GELU_C1 * x * x))); }
-__device__ __forceinline__ float gelu_d1(float x) {
-  const float th = tanh_fast(GELU_C0 * x * (1.f + GELU_C1 * x * x));
-  return 0.5f * x * ((1.f - th * th) * (GELU_C0 + 3.f * GELU_C0 * GELU_C1 * x * x)) + 0.5f * (1.f + th);
-}
-__device__ __forceinline__ float gelu_d2(float x) {
-  const float th = tanh_fast(GELU_C0 * x * (1.f + GELU_C1 * x * x));
-  const float du = GELU_C0 * (1.f + 3.f * GELU_C1 * x * x), d2u = 6.f * GELU_C0 * GELU_C1 * x;
-  return (1.f - th * th) * du + 0.5f * x * (1.f - th * th) * (d2u - 2.f * th * du * du);
+// gelu(x), gelu'(x) and (D2) gelu''(x) from one tanh
+template <bool D2>
+__device__ __forceinline__ void gelu_all(float x, float& f, float& d1, float& d2) {
+  const float x2 = x * x, th = tanh_fast(GELU_C0 * x * (1.f + GELU_C1 * x2));
+  const float hs = 0.5f * x * (1.f - th * th), du = GELU_C0 * (1.f + 3.f * GELU_C1 * x2);
+  f = 0.5f * x * (1.f + th);
+  d1 = hs * du + 0.5f * (1.f + th);
+  if constexpr (D2) d2 = (1.f - th * th) * du + hs * (6.f * GELU_C0 * GELU_C1 * x - 2.f * th * du * du);
 }
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -317,7 +317,8 @@ __device__ __forceinline__ void for_c(Fn f) {
 
 struct __align__(16) MlpBwdSmem {
   // bf16 operand tiles
-  bf z1[CS][EB], x2[CS][EB], g1[CS][EB], z1b[CS][EB], x2b[CS][EB];
+  bf gd1[CS][EB], gd2[CS][EB], x2[CS][EB], g1[CS][EB];  // gelu'(z1), gelu''(z1), gelu(z1), g1
+  bf z1b[CS][EB], x2b[CS][EB];  // gelu'(z1b) (then scratch: l o x2, column partials), gelu(z1b)
   bf t1[CS][EB], t2[CS][EB], t3[CS][EB], t4[CS][EB];  // g1p | dz1b;  dg1, dh;  gl2;  dz1 (and column partials)
   bf q[CS][FB], k[CS][FB], v[CS][FB], dO[CS][FB], g2[CS][FB], g2p[CS][FB], dz2b[CS][FB], dz2[CS][FB];
   bf m1[CS][CB], m2[CS][CB], m1n[CS][CB], m2n[CS][CB], da1[CS][CB], da2[CS][CB];  // m*n = -m*
@@ -455,13 +456,16 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       stb2(&S.w2[i][j], x, y);
     }, prod<CS>(tr(sx2), sg2p));
   };
-  // z1 = K W1 + b1, x2 = gelu(z1)
-  auto forward_first_layer = [&]() {
+  // z1 = K W1 + b1, x2 = gelu(z1); z1 itself is only needed through gelu'(z1) and (pass 2) gelu''(z1)
+  auto forward_first_layer = [&](auto d2_tag) {
+    constexpr bool D2 = decltype(d2_tag)::value;
     tile_mma<false, CS, E>(none, 1.f, [&](int i, int j, float x, float y) {
-      x += b1[j];
-      y += b1[j + 1];
-      stb2(&S.z1[i][j], x, y);
-      stb2(&S.x2[i][j], gelu_f(x), gelu_f(y));
+      float f0, f1, a0, a1, c0 = 0.f, c1 = 0.f;
+      gelu_all<D2>(x + b1[j], f0, a0, c0);
+      gelu_all<D2>(y + b1[j + 1], f1, a1, c1);
+      stb2(&S.x2[i][j], f0, f1);
+      stb2(&S.gd1[i][j], a0, a1);
+      if constexpr (D2) stb2(&S.gd2[i][j], c0, c1);
     }, prod<F>(sk, sw1));
     __syncthreads();
   };
@@ -476,9 +480,9 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     ln_l2_grad_tile<SAVE>(S, S.z2, S.g2, p.eps, g2p);
     __syncthreads();
     tile_mma<false, CS, E>(none, 1.f, [&](int i, int j, float x, float y) {
-      const float2 z = ldb2(&S.z1[i][j]);
-      x *= gelu_d1(z.x);
-      y *= gelu_d1(z.y);
+      const float2 d1 = ldb2(&S.gd1[i][j]);
+      x *= d1.x;
+      y *= d1.y;
       stb2(&S.g1[i][j], x, y);
       if constexpr (SAVE) {
         const uint32_t v = pack_bf16(S.ell[i] * x, S.ell[i] * y);
@@ -508,7 +512,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     }
     __syncthreads();
     TRM(0)
-    forward_first_layer();
+    forward_first_layer(std::false_type{});
     forward_second_layer(std::true_type{}, reinterpret_cast<uint32_t*>(g1p_all + (size_t)s * CS * E),
                          reinterpret_cast<uint32_t*>(g2p_all + (size_t)s * CS * F));
     TRM(1)
@@ -549,7 +553,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     update_w1(1.f);
     add_colsum(b1, &S.t1[0][0], E, EB, 1.f);
     __syncthreads();
-    forward_first_layer();  // z1 and x2 of this stage, needed to undo the second layer's update
+    forward_first_layer(std::true_type{});  // x2 (and the GELU derivatives) of this stage, needed to undo the second layer's update
     update_w2(1.f);
     add_colsum(b2, &S.g2p[0][0], F, FB, 1.f);
     __syncthreads();
@@ -568,10 +572,11 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     });
     __syncthreads();
     tile_mma<false, CS, E>(none, 1.f, [&](int i, int j, float x, float y) {          // z1b = Q W1 - M1 g1 + b1; x2b = gelu
-      x += b1[j];
-      y += b1[j + 1];
-      stb2(&S.z1b[i][j], x, y);
-      stb2(&S.x2b[i][j], gelu_f(x), gelu_f(y));
+      float f0, f1, a0, a1, c0, c1;
+      gelu_all<false>(x + b1[j], f0, a0, c0);
+      gelu_all<false>(y + b1[j + 1], f1, a1, c1);
+      stb2(&S.z1b[i][j], a0, a1);  // gelu'(z1b), all that step 3 needs of z1b
+      stb2(&S.x2b[i][j], f0, f1);
     }, prod<F>(sq, sw1), prod<CS>(sm1n, sg1));
     __syncthreads();
     tile_mma<false, CS, CS>(ma2, 1.f, noepi, prod<E>(sx2b, tr(sx2)));              // a2 = x2b x2^T
@@ -629,8 +634,8 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     TRM(8)
     // ---- 3. dz1b = (dz2b W2^T + dA2 x2) o gelu'(z1b)  (kept in t1)
     tile_mma<false, CS, E>(none, 1.f, [&](int i, int j, float x, float y) {
-      const float2 z = ldb2(&S.z1b[i][j]);
-      stb2(&S.t1[i][j], x * gelu_d1(z.x), y * gelu_d1(z.y));
+      const float2 d1 = ldb2(&S.z1b[i][j]);
+      stb2(&S.t1[i][j], x * d1.x, y * d1.y);
     }, prod<F>(sdz2b, tr(sw2)), prod<CS>(sda2, sx2));
     __syncthreads();
     // ---- 4. z1b = Q W1 + b1 - M1 g1
@@ -690,9 +695,9 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     TRM(10)
     // ---- 6. g1 = h o gelu'(z1), h = g2 W2^T (recomputed):  dz1 = dg1 o h o gelu''(z1) (t4),  dh = dg1 o gelu'(z1) (t2)
     tile_mma<false, CS, E>(none, 1.f, [&](int i, int j, float hx, float hy) {
-      const float2 d = ldb2(&S.t2[i][j]), z = ldb2(&S.z1[i][j]);
-      stb2(&S.t4[i][j], d.x * hx * gelu_d2(z.x), d.y * hy * gelu_d2(z.y));
-      stb2(&S.t2[i][j], d.x * gelu_d1(z.x), d.y * gelu_d1(z.y));
+      const float2 d = ldb2(&S.t2[i][j]), d1 = ldb2(&S.gd1[i][j]), d2 = ldb2(&S.gd2[i][j]);
+      stb2(&S.t4[i][j], d.x * hx * d2.x, d.y * hy * d2.y);
+      stb2(&S.t2[i][j], d.x * d1.x, d.y * d1.y);
     }, prod<F>(sg2, tr(sw2)));
     __syncthreads();
     tile_mma<true, CS, F>(mdg2, 1.f, noepi, prod<E>(st2, sw2));                    // dg2 += dh W2
@@ -755,10 +760,10 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     // ---- 8./9./10. z2 = x2 W2 + b2, x2 = gelu(z1), z1 = K W1 + b1:
     //      dx2 = dA2^T x2b + dz2 W2^T - l o gl2  (never stored);  dz1 += dx2 o gelu'(z1) (t4);  dk += dz1 W1^T
     tile_mma<false, CS, E>(none, 1.f, [&](int i, int j, float x, float y) {
-      const float2 z = ldb2(&S.z1[i][j]), d = ldb2(&S.t4[i][j]), gl2 = ldb2(&S.t3[i][j]);
+      const float2 d1 = ldb2(&S.gd1[i][j]), d = ldb2(&S.t4[i][j]), gl2 = ldb2(&S.t3[i][j]);
       x -= S.ell[i] * gl2.x;
       y -= S.ell[i] * gl2.y;
-      stb2(&S.t4[i][j], d.x + x * gelu_d1(z.x), d.y + y * gelu_d1(z.y));
+      stb2(&S.t4[i][j], d.x + x * d1.x, d.y + y * d1.y);
     }, prod<CS>(tr(sda2), sx2b), prod<F>(sdz2, tr(sw2)));
     __syncthreads();
     tile_mma<true, CS, F>(mdk, 1.f, noepi, prod<E>(st4, tr(sw1)));
