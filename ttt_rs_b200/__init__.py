@@ -17,6 +17,7 @@ from .fused import (  # noqa: F401
     TttTileMultiKernel,
     fused_ttt_mlp,
     fused_ttt_mlp_backward,
+    check_mlp_status,
     fused_ttt_mlp_forward,
     fused_ttt_tile_forward_multi,
     packed_outer_grad_len,

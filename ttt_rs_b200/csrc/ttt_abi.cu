@@ -678,7 +678,7 @@ extern "C" int ttt_layer_epilogue_backward(const ttt_dims* d, const void* grad_y
 
 namespace {
 struct MlpWsLayout {
-  size_t stride_floats, off_te, off_ln, total_bytes;
+  size_t stride_floats, off_te, off_ln, off_sched, total_bytes;
 };
 MlpWsLayout mlp_ws_layout(const ttt_dims* d) {
   const size_t streams = (size_t)d->batch * d->heads;
@@ -686,7 +686,8 @@ MlpWsLayout mlp_ws_layout(const ttt_dims* d) {
   l.stride_floats = ttt::mlp_bwd_ws_stride_floats(d->seq_len);
   l.off_te = streams * l.stride_floats;
   l.off_ln = l.off_te + streams * (size_t)d->seq_len;
-  l.total_bytes = (l.off_ln + streams * 2 * 64) * sizeof(float);
+  l.off_sched = l.off_ln + streams * 2 * 64;
+  l.total_bytes = (l.off_sched + ((1 + streams + 3) & ~(size_t)3)) * sizeof(float);
   return l;
 }
 }  // namespace
@@ -730,7 +731,9 @@ extern "C" int ttt_mlp_backward(const ttt_dims* d, const void* xq, const void* x
   p.ws_stride = l.stride_floats;
   p.part_te = ws + l.off_te;
   p.part_ln = ws + l.off_ln;
-  p.trace = static_cast<unsigned int*>(status);  // only instrumented builds write here (16 words)
+  p.sched = reinterpret_cast<int*>(ws + l.off_sched);
+  p.status = static_cast<uint32_t*>(status);
+  p.trace = static_cast<unsigned int*>(status);  // instrumented builds write 16 words of cycle counts here instead
   p.H = d->heads; p.T = d->seq_len; p.NS = d->seq_len / d->mini_batch; p.eps = d->epsilon;
   cudaError_t e = ttt::launch_mlp_bwd(p, d->batch, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "MLP backward launch failed: %s", cudaGetErrorString(e));

@@ -199,9 +199,14 @@ struct MlpBwdParams {
   float* part_te;      // [B*H][T]
   float* part_ln;      // [B*H][2][F]
   unsigned int* trace;  // optional 16 words (per-phase cycle counts of block 0 in instrumented builds), else null
+  int* sched;           // [1 + B*H] work-item counter and per-stream count of finished items (zeroed by the launcher)
+  uint32_t* status;     // optional 4 words: {TTT_ERR_TIMEOUT, where, block, item} if a hand-off wait ran out
   int H, T, NS;
+  int nstreams, CH, NCH;  // set by the launcher: streams, stages per work item, items per pass
   float eps;
 };
+// per-stream hand-off record between work items: b1, b2, db1, db2, d ln_weight, d ln_bias
+constexpr int MLP_BWD_HANDOFF_FLOATS = 2 * 256 + 4 * 64;
 size_t mlp_bwd_ws_stride_floats(int T);
 cudaError_t launch_mlp_bwd(const MlpBwdParams& p, int B, cudaStream_t st);
 

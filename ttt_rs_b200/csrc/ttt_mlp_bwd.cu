@@ -27,6 +27,7 @@ namespace ttt {
 constexpr int MB_THREADS = 512;
 constexpr int MB_NW = MB_THREADS / 32;  // warps of the CTA
 constexpr int MB_E = 256;               // hidden width of the inner MLP (4 * head_dim)
+constexpr int MLP_BWD_CHUNK = 8;        // stages per work item
 static_assert(MB_NW == CS, "the row-wise (LayerNorm) steps give one tile row to each warp");
 // Row lengths of the shared-memory tiles: width + 8 elements.  For bf16 tiles the row stride is then an odd multiple
 // of 16 bytes, so the eight 16-byte rows of an ldmatrix 8x8 block fall in distinct banks; for float32 tiles a stride
@@ -58,7 +59,8 @@ __device__ __forceinline__ SB<LD, !TR> tr(const SB<LD, TR> m) { return SB<LD, !T
 // (r / 16, c / 8) occupies 128 consecutive floats, its rows 0..7 before its rows 8..15, and inside a half the
 // element (r % 8, c % 8) sits at 8 * (r % 8) + (c % 8).  A warp's read-modify-write of an output tile is then two
 // contiguous 256-byte accesses instead of sixteen 32-byte row pieces, and so are the operand fetches along a row.
-// TR = true: the operand is the transpose of the stored matrix.
+// TR = true: the operand is the transpose of the stored matrix.  Successive work items of a stream may run on
+// different SMs, so every read of these matrices bypasses L1 (ld.global.cg).
 template <int R, int C, bool TR>
 struct MatG {
   float* p;
@@ -129,10 +131,10 @@ __device__ __forceinline__ void load_A(const MatG<R, C, TR> A, int i0, int k0, i
   for (int q = 0; q < 4; ++q) {
     const int i = i0 + g + 8 * (q & 1), k = k0 + 2 * t + 8 * (q >> 1);
     if constexpr (!TR) {  // stored [i][k]: the pair (k, k + 1) is adjacent
-      const float2 f = *reinterpret_cast<const float2*>(A.p + A.at(i, k));
+      const float2 f = __ldcg(reinterpret_cast<const float2*>(A.p + A.at(i, k)));
       r[q] = pack_bf16(f.x, f.y);
     } else {
-      r[q] = pack_bf16(A.p[A.at(k, i)], A.p[A.at(k + 1, i)]);
+      r[q] = pack_bf16(__ldcg(A.p + A.at(k, i)), __ldcg(A.p + A.at(k + 1, i)));
     }
   }
 }
@@ -142,18 +144,18 @@ __device__ __forceinline__ void load_B(const MatG<R, C, TR> B, int k0, int j0, i
   // k0 is a multiple of 16 and j0 of 8, so the tile index and the place inside the tile separate
   if constexpr (TR) {  // stored [j][k]: the pair (k, k + 1) is adjacent; the two registers lie in neighbouring tiles
     const float* s = B.p + ((((j0 >> 4) * (C / 8) + (k0 >> 3)) << 7) + (((j0 >> 3) & 1) << 6) + (g << 3) + 2 * t);
-    const float2 f0 = *reinterpret_cast<const float2*>(s), f1 = *reinterpret_cast<const float2*>(s + 128);
+    const float2 f0 = __ldcg(reinterpret_cast<const float2*>(s)), f1 = __ldcg(reinterpret_cast<const float2*>(s + 128));
     r[0] = pack_bf16(f0.x, f0.y);
     r[1] = pack_bf16(f1.x, f1.y);
   } else {  // stored [k][j]: rows 2t, 2t + 1 of the upper and of the lower half of one tile
     const float* s = B.p + ((((k0 >> 4) * (C / 8) + (j0 >> 3)) << 7) + (t << 4) + g);
-    r[0] = pack_bf16(s[0], s[8]);
-    r[1] = pack_bf16(s[64], s[72]);
+    r[0] = pack_bf16(__ldcg(s), __ldcg(s + 8));
+    r[1] = pack_bf16(__ldcg(s + 64), __ldcg(s + 72));
   }
 }
 template <int R, int C>
 __device__ __forceinline__ float2 c_load(const MatG<R, C, false> M, int i, int j) {
-  return *reinterpret_cast<const float2*>(M.p + M.at(i, j));
+  return __ldcg(reinterpret_cast<const float2*>(M.p + M.at(i, j)));
 }
 template <int R, int C>
 __device__ __forceinline__ void c_store(const MatG<R, C, false> M, int i, int j, float x, float y) {
@@ -373,47 +375,109 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
   MlpBwdSmem& S = *reinterpret_cast<MlpBwdSmem*>(mlp_bwd_smem);
   typedef __nv_bfloat16 T;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int stream = blockIdx.x, head = stream % p.H, NS = p.NS;
+  const int NS = p.NS;
   constexpr int F = HD, E = MB_E;
-  const size_t row_base = (size_t)stream * p.T;
+  constexpr int HO_B1 = 0, HO_B2 = E, HO_DB1 = E + F, HO_DB2 = 2 * E + F, HO_DG = 2 * E + 2 * F, HO_DB = 2 * E + 3 * F;
+  static_assert(HO_DB + F == MLP_BWD_HANDOFF_FLOATS, "hand-off record");
+  float* const b1 = S.b1;
+  float* const b2 = S.b2;
+  float* const db1 = S.db1;
+  float* const db2 = S.db2;
+  __shared__ int s_item;
 
-  // per-stream workspace: W1 [F][E], W2 [E][F], dW1, dW2 (float32, in the tile order of MatG), then g1p [NS][16][E], g2p [NS][16][F] (bf16)
+  // Persistent block.  A stream is a chain of 2 NCH work items: its chunks of CH stages in pass 1 (ranks 0 ..
+  // NCH-1, forward), then in pass 2 (ranks NCH .. 2 NCH-1, backward).  Items are handed out rank by rank over all
+  // streams, so an item only waits for an item with a smaller index (its predecessor in the chain), which is done or
+  // held by a resident block: the launch cannot deadlock while all blocks are co-resident (cooperative launch).
+  // Between items the stream's state lives in the workspace: the four float32 matrices anyway, the biases, their
+  // gradients and the LayerNorm parameter gradients in a small hand-off record.
+  const int nitems = p.nstreams * 2 * p.NCH;
+  while (true) {
+    if (tid == 0) s_item = atomicAdd(&p.sched[0], 1);
+    __syncthreads();
+    const int item = s_item;
+    __syncthreads();
+    if (item >= nitems) break;
+    const int rank = item / p.nstreams, stream = item - rank * p.nstreams, head = stream % p.H;
+    const bool pass1 = rank < p.NCH;
+    const int chunk = pass1 ? rank : 2 * p.NCH - 1 - rank;
+    const int s_lo = chunk * p.CH, s_hi = min(s_lo + p.CH, NS);
+    const size_t row_base = (size_t)stream * p.T;
+
+  // per-stream workspace: W1 [F][E], W2 [E][F], dW1, dW2 (float32, in the tile order of MatG), the hand-off record,
+  // then g1p [NS][16][E], g2p [NS][16][F] (bf16)
   float* ws = p.workspace + (size_t)stream * p.ws_stride;
   float* W1 = ws;
   float* W2 = W1 + F * E;
   float* dW1 = W2 + E * F;
   float* dW2 = dW1 + F * E;
-  bf* g1p_all = reinterpret_cast<bf*>(dW2 + E * F);
+  float* ho = dW2 + E * F;
+  bf* g1p_all = reinterpret_cast<bf*>(ho + MLP_BWD_HANDOFF_FLOATS);
   bf* g2p_all = g1p_all + (size_t)NS * CS * E;
-  float* const b1 = S.b1;
-  float* const b2 = S.b2;
-  float* const db1 = S.db1;
-  float* const db2 = S.db2;
 
+  if (rank > 0) {
+    // wait (bounded) until the previous item of this stream has published its state
+    int ok = 1;
+    if (tid == 0) {
+      ok = 0;
+      const volatile int* flag = p.sched + 1 + stream;
+      for (uint32_t it = 0; it < (1u << 24); ++it) {
+        if (*flag >= rank) {
+          ok = 1;
+          break;
+        }
+        __nanosleep(100);
+      }
+      __threadfence();
+    }
+    if (__syncthreads_or(ok ? 0 : 1)) {
+      if (tid == 0 && p.status != nullptr && atomicCAS(p.status, 0u, (uint32_t)KST_TIMEOUT) == 0u) {
+        p.status[1] = 1u;
+        p.status[2] = blockIdx.x;
+        p.status[3] = (uint32_t)item;
+      }
+      break;
+    }
+  }
   if (tid < HD) {
     S.gam[tid] = ld_as_float<T>(p.ln_g, (size_t)head * HD + tid);
     S.bet[tid] = ld_as_float<T>(p.ln_b, (size_t)head * HD + tid);
-    S.dgam[tid] = 0.f;
-    S.dbet[tid] = 0.f;
+    const bool fresh = rank <= p.NCH;  // the LayerNorm parameter gradients start with pass 2
+    S.dgam[tid] = fresh ? 0.f : __ldcg(ho + HO_DG + tid);
+    S.dbet[tid] = fresh ? 0.f : __ldcg(ho + HO_DB + tid);
   }
   if (tid < CS) S.te[tid] = ld_as_float<T>(p.token_eta, (size_t)tid);
-  for (int e = tid; e < F * E; e += MB_THREADS) {
-    const bf a = static_cast<const bf*>(p.w1)[(size_t)stream * F * E + e];
-    const bf b = static_cast<const bf*>(p.w2)[(size_t)stream * F * E + e];
-    W1[MatG<F, E, false>::at(e / E, e % E)] = __bfloat162float(a);
-    W2[MatG<E, F, false>::at(e / F, e % F)] = __bfloat162float(b);
-    S.w1[e / E][e % E] = a;
-    S.w2[e / F][e % F] = b;
-    dW1[e] = 0.f;
-    dW2[e] = 0.f;
+  if (rank == 0) {
+    for (int e = tid; e < F * E; e += MB_THREADS) {
+      const bf a = static_cast<const bf*>(p.w1)[(size_t)stream * F * E + e];
+      const bf b = static_cast<const bf*>(p.w2)[(size_t)stream * F * E + e];
+      W1[MatG<F, E, false>::at(e / E, e % E)] = __bfloat162float(a);
+      W2[MatG<E, F, false>::at(e / F, e % F)] = __bfloat162float(b);
+      S.w1[e / E][e % E] = a;
+      S.w2[e / F][e % F] = b;
+    }
+    for (int e = tid; e < E; e += MB_THREADS) b1[e] = ld_as_float<T>(p.b1, (size_t)stream * E + e);
+    if (tid < F) b2[tid] = ld_as_float<T>(p.b2, (size_t)stream * F + tid);
+  } else {
+    // bf16 shadows from the float32 state the previous item left in the workspace
+    for (int e = 2 * tid; e < F * E; e += 2 * MB_THREADS) {
+      const float2 a = __ldcg(reinterpret_cast<const float2*>(W1 + MatG<F, E, false>::at(e / E, e % E)));
+      const float2 b = __ldcg(reinterpret_cast<const float2*>(W2 + MatG<E, F, false>::at(e / F, e % F)));
+      stb2(&S.w1[e / E][e % E], a.x, a.y);
+      stb2(&S.w2[e / F][e % F], b.x, b.y);
+    }
+    for (int e = tid; e < E; e += MB_THREADS) b1[e] = __ldcg(ho + HO_B1 + e);
+    if (tid < F) b2[tid] = __ldcg(ho + HO_B2 + tid);
   }
-  for (int e = tid; e < E; e += MB_THREADS) {
-    b1[e] = ld_as_float<T>(p.b1, (size_t)stream * E + e);
-    db1[e] = 0.f;
-  }
-  if (tid < F) {
-    b2[tid] = ld_as_float<T>(p.b2, (size_t)stream * F + tid);
-    db2[tid] = 0.f;
+  if (!pass1) {
+    const bool fresh = rank == p.NCH;  // first item of pass 2: the gradients w.r.t. the final state are zero
+    if (fresh)
+      for (int e = tid; e < F * E; e += MB_THREADS) {
+        dW1[e] = 0.f;
+        dW2[e] = 0.f;
+      }
+    for (int e = tid; e < E; e += MB_THREADS) db1[e] = fresh ? 0.f : __ldcg(ho + HO_DB1 + e);
+    if (tid < F) db2[tid] = fresh ? 0.f : __ldcg(ho + HO_DB2 + tid);
   }
   __syncthreads();
   const float te_last = S.te[CS - 1];
@@ -499,7 +563,8 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
   };
 
   // ============================== pass 1: forward walk, saving g1p and g2p ==============================
-  for (int s = 0; s < NS; ++s) {
+  if (pass1)
+  for (int s = s_lo; s < s_hi; ++s) {
     const size_t r0 = (row_base + (size_t)s * CS) * HD;
     if (tid < 256) {
       int r, c;
@@ -526,11 +591,12 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
 
   // ============================== pass 2: backward walk ==============================
   float(*const colpart)[2 * HD] = reinterpret_cast<float(*)[2 * HD]>(&S.z1b[0][0]);  // only while z1b is not live
-  for (int s = NS - 1; s >= 0; --s) {
+  if (!pass1)
+  for (int s = s_hi - 1; s >= s_lo; --s) {
     const size_t r0 = (row_base + (size_t)s * CS) * HD;
     {
       // the stage's inputs, one 16-byte piece per thread and tile
-      const uint4 g1v = reinterpret_cast<const uint4*>(g1p_all + (size_t)s * CS * E)[tid];
+      const uint4 g1v = __ldcg(reinterpret_cast<const uint4*>(g1p_all + (size_t)s * CS * E) + tid);
       int r, c;
       tile_piece(tid & 127, r, c);
       const int which = tid >> 7;
@@ -538,7 +604,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       bf(*dst)[FB] = which == 0 ? S.q : which == 1 ? S.k : which == 2 ? S.v : S.dO;
       const uint4 in = *reinterpret_cast<const uint4*>(src + r * HD + c);
       uint4 g2v = make_uint4(0u, 0u, 0u, 0u);
-      if (tid < 128) g2v = reinterpret_cast<const uint4*>(g2p_all + (size_t)s * CS * F)[tid];
+      if (tid < 128) g2v = __ldcg(reinterpret_cast<const uint4*>(g2p_all + (size_t)s * CS * F) + tid);
       *reinterpret_cast<uint4*>(&dst[r][c]) = in;
       *reinterpret_cast<uint4*>(&S.t1[tid >> 5][8 * (tid & 31)]) = g1v;
       if (tid < 128) *reinterpret_cast<uint4*>(&S.g2p[r][c]) = g2v;
@@ -803,23 +869,41 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     __syncthreads();
     TRM(15)
   }
+  __syncthreads();
+  if (rank < 2 * p.NCH - 1) {
+    // hand the stream to its next item
+    for (int e = tid; e < E; e += MB_THREADS) {
+      ho[HO_B1 + e] = b1[e];
+      ho[HO_DB1 + e] = db1[e];
+    }
+    if (tid < F) {
+      ho[HO_B2 + tid] = b2[tid];
+      ho[HO_DB2 + tid] = db2[tid];
+      ho[HO_DG + tid] = S.dgam[tid];
+      ho[HO_DB + tid] = S.dbet[tid];
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) *reinterpret_cast<volatile int*>(p.sched + 1 + stream) = rank + 1;
+  } else {
+    // ---- gradients w.r.t. the initial state, per-stream LayerNorm parameter gradients
+    for (int e = tid; e < F * E; e += MB_THREADS) {
+      st_from_float<T>(p.d_w1, (size_t)stream * F * E + e, __ldcg(dW1 + MatG<F, E, false>::at(e / E, e % E)));
+      st_from_float<T>(p.d_w2, (size_t)stream * F * E + e, __ldcg(dW2 + MatG<E, F, false>::at(e / F, e % F)));
+    }
+    for (int e = tid; e < E; e += MB_THREADS) st_from_float<T>(p.d_b1, (size_t)stream * E + e, db1[e]);
+    if (tid < F) {
+      st_from_float<T>(p.d_b2, (size_t)stream * F + tid, db2[tid]);
+      p.part_ln[(size_t)stream * 2 * HD + tid] = S.dgam[tid];
+      p.part_ln[(size_t)stream * 2 * HD + HD + tid] = S.dbet[tid];
+    }
+  }
+  }  // item loop
 #ifdef TTT_MLP_TRACE
   if (tid == 0 && blockIdx.x == 0 && p.trace != nullptr)
     for (int i = 0; i < 16; ++i) p.trace[i] = (unsigned int)(tr_acc[i] / NS);
 #endif
 #undef TRM
-
-  // ---- gradients w.r.t. the initial state, per-stream LayerNorm parameter gradients
-  for (int e = tid; e < F * E; e += MB_THREADS) {
-    st_from_float<T>(p.d_w1, (size_t)stream * F * E + e, dW1[mdW1.at(e / E, e % E)]);
-    st_from_float<T>(p.d_w2, (size_t)stream * F * E + e, dW2[mdW2.at(e / F, e % F)]);
-  }
-  for (int e = tid; e < E; e += MB_THREADS) st_from_float<T>(p.d_b1, (size_t)stream * E + e, db1[e]);
-  if (tid < F) {
-    st_from_float<T>(p.d_b2, (size_t)stream * F + tid, db2[tid]);
-    p.part_ln[(size_t)stream * 2 * HD + tid] = S.dgam[tid];
-    p.part_ln[(size_t)stream * 2 * HD + HD + tid] = S.dbet[tid];
-  }
 }
 
 // grad_token_eta[t] = sum over streams, grad_ln_weight / grad_ln_bias [h][f] = sum over the batch; fixed order.
@@ -838,18 +922,34 @@ __global__ void ttt_mlp_bwd_reduce_kernel(const float* part_te, const float* par
   }
 }
 
-// floats of workspace per stream: the four float32 state matrices, then the bf16 g1p / g2p tiles of every stage
+// floats of workspace per stream: the four float32 state matrices, the hand-off record, then the bf16 g1p / g2p tiles
+// of every stage
 size_t mlp_bwd_ws_stride_floats(int T) {
   const size_t ns = (size_t)T / CS;
-  return 4 * (size_t)HD * MB_E + ns * CS * (MB_E + HD) / 2;
+  return 4 * (size_t)HD * MB_E + MLP_BWD_HANDOFF_FLOATS + ns * CS * (MB_E + HD) / 2;
 }
 
-cudaError_t launch_mlp_bwd(const MlpBwdParams& p, int B, cudaStream_t st) {
+cudaError_t launch_mlp_bwd(const MlpBwdParams& p0, int B, cudaStream_t st) {
+  MlpBwdParams p = p0;
+  p.nstreams = B * p.H;
+  p.CH = MLP_BWD_CHUNK;
+  p.NCH = (p.NS + p.CH - 1) / p.CH;
   const size_t smem = sizeof(MlpBwdSmem);
   cudaError_t e = cudaFuncSetAttribute(ttt_mlp_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  ttt_mlp_bwd_kernel<<<B * p.H, MB_THREADS, smem, st>>>(p);
-  e = cudaGetLastError();
+  // persistent grid: blocks wait on one another's hand-offs, so all of them must be resident (cooperative launch);
+  // more blocks than streams would only wait (a stream's items run one after the other)
+  int dev = 0, sms = 0, per_sm = 0;
+  if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+  if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+  if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ttt_mlp_bwd_kernel, MB_THREADS, smem)) != cudaSuccess)
+    return e;
+  if (per_sm < 1) return cudaErrorLaunchOutOfResources;
+  int grid = sms * per_sm;
+  if (grid > p.nstreams) grid = p.nstreams;
+  if ((e = cudaMemsetAsync(p.sched, 0, sizeof(int) * (size_t)(1 + p.nstreams), st)) != cudaSuccess) return e;
+  void* args[] = {(void*)&p};
+  e = cudaLaunchCooperativeKernel((const void*)ttt_mlp_bwd_kernel, dim3(grid), dim3(MB_THREADS), args, smem, st);
   if (e != cudaSuccess) return e;
   const int n = p.T + 2 * p.H * HD;
   ttt_mlp_bwd_reduce_kernel<<<(n + 255) / 256, 256, 0, st>>>(p.part_te, p.part_ln, B, p.H, p.T, p.d_token_eta,

@@ -488,12 +488,22 @@ def fused_ttt_mlp_backward(xq, xk, xv, state: TTTMLPState, token_eta, ttt_lr_eta
                 "grad_output")
     names_out = ("grad_xq", "grad_xk", "grad_xv", "grad_w1", "grad_b1", "grad_w2", "grad_b2", "grad_ttt_lr_eta",
                  "grad_token_eta", "grad_ln_weight", "grad_ln_bias")
+    status = torch.zeros(16, dtype=torch.int32, device=dev)
     with torch.cuda.device(dev):
         rc = lib.ttt_mlp_backward(C.byref(d), *[_ptr(ts[k]) for k in names_in], *[_ptr(g[k]) for k in names_out],
-                                  _ptr(ws), ws_bytes, None, _stream_ptr(dev))
+                                  _ptr(ws), ws_bytes, _ptr(status), _stream_ptr(dev))
     _lib.check(rc)
     g["_workspace"] = ws  # keeps the scratch alive until the caller drops the result
+    g["_status"] = status  # {0,..} unless a hand-off wait between work items ran out: see `check_mlp_status`
     return g
+
+
+def check_mlp_status(grads) -> None:
+    """After synchronising: raise if the TTT-MLP backward that produced `grads` reported a device-side wait timeout
+    (its blocks hand the stream state to one another; every such wait is bounded)."""
+    v = grads["_status"].cpu().tolist()
+    if v[0] != 0:
+        raise TttError(v[0], f"device-side wait timed out (where={v[1]}, block={v[2]}, item={v[3]})")
 
 
 class _FusedTttMlpFn(torch.autograd.Function):
