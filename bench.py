@@ -566,8 +566,10 @@ def main():
         if record:
             e[0].record()
         if mlp:
+            # training step: the forward fills the backward's workspace on the way
+            mws = tb.mlp_backward_workspace(md["xq"], cfg) if w["backward"] else None
             outs = tb.fused_ttt_mlp_forward(md["xq"], md["xk"], md["xv"], mstate, md["token_eta"], md["ttt_lr_eta"],
-                                            md["ln_weight"], md["ln_bias"], cfg)
+                                            md["ln_weight"], md["ln_bias"], cfg, backward_workspace=mws)
         else:
             outs, saved = tb.TttTileMultiKernel.forward_launch(ins, cfg)
         if record:
@@ -575,7 +577,7 @@ def main():
         g = None
         if w["backward"] and mlp:
             g = tb.fused_ttt_mlp_backward(md["xq"], md["xk"], md["xv"], mstate, md["token_eta"], md["ttt_lr_eta"],
-                                          md["ln_weight"], md["ln_bias"], go, cfg)
+                                          md["ln_weight"], md["ln_bias"], go, cfg, workspace_from_forward=mws)
             if record:
                 e[2].record()
         elif w["backward"]:

@@ -141,22 +141,28 @@ int ttt_linear_backward_state_grads(const ttt_dims* d, const void* xq, const voi
  * The reference has no fused kernel for it; this replaces the loop of `TTTMLP::forward_mini_batch`
  * (rust/core/src/mlp.rs:127-208) behind `TTTInnerModel::forward` (rust/core/src/inner.rs:25-50), with the fused
  * kernels' convention that token_eta is read at [0, CS).  bf16 only (dtype must be TTT_BF16); checkpoint_interval
- * is ignored (no backward yet: gradients of this inner model still come from the framework's autodiff).
+ * is ignored (the backward, ttt_mlp_backward, reverses the state updates instead of reloading checkpoints).
  *   xq, xk, xv      bf16 [B,H,T,F]
  *   w1, b1          bf16 [B,H,F,E], [B,H,E]   initial state, z1 = x @ w1 + b1
  *   w2, b2          bf16 [B,H,E,F], [B,H,F]
  *   token_eta [T], ttt_lr_eta [B,H,T], ln_weight / ln_bias [H,F]   bf16
  *   output          bf16 [B,H,T,F] (out);  w1_out, b1_out, w2_out, b2_out (out) final state, same shapes
+ *   backward_workspace (optional, out): ttt_mlp_backward_workspace_bytes(d) bytes, 16-byte aligned.  When given, the
+ *                   forward leaves there the float32 final state and the bf16 operands of every state update, which
+ *                   is all the backward's own first pass would compute: pass the buffer on to ttt_mlp_backward
+ *                   with workspace_from_forward = 1.  NULL (with 0 bytes) for inference.
  */
 int ttt_mlp_forward(const ttt_dims* d, const void* xq, const void* xk, const void* xv, const void* w1, const void* b1,
                     const void* w2, const void* b2, const void* token_eta, const void* ttt_lr_eta,
                     const void* ln_weight, const void* ln_bias, void* output, void* w1_out, void* b1_out, void* w2_out,
-                    void* b2_out, void* status, void* stream);
+                    void* b2_out, void* backward_workspace, size_t backward_workspace_bytes, void* status,
+                    void* stream);
 
 /* TTT-MLP backward (bf16): gradient of ttt_mlp_forward for loss = <grad_output, output>; gradients w.r.t. the returned
  * final state are taken as zero, as for the TTT-Linear operator.  The reference has no fused counterpart: it
  * differentiates the tensor ops of rust/core/src/mlp.rs:127-208 with Burn autodiff.  Inputs are the forward's inputs
- * (nothing saved by the forward is needed: the kernel re-walks the sequence), outputs:
+ * (nothing saved by the forward is needed: the kernel re-walks the sequence; with `workspace_from_forward` != 0 the
+ * workspace is the one a ttt_mlp_forward call on the same inputs filled, and the re-walk is skipped), outputs:
  *   grad_xq, grad_xk, grad_xv [B,H,T,F]; grad_w1 [B,H,F,4F], grad_b1 [B,H,4F], grad_w2 [B,H,4F,F], grad_b2 [B,H,F]
  *   (per batch element); grad_ttt_lr_eta [B,H,T]; float32 grad_token_eta [T] (per stage position, summed over B, H),
  *   float32 grad_ln_weight / grad_ln_bias [H,F] (summed over B).  All written, never accumulated into.
@@ -174,7 +180,7 @@ int ttt_mlp_backward(const ttt_dims* d, const void* xq, const void* xk, const vo
                      const void* ln_weight, const void* ln_bias, const void* grad_output, void* grad_xq, void* grad_xk,
                      void* grad_xv, void* grad_w1, void* grad_b1, void* grad_w2, void* grad_b2, void* grad_ttt_lr_eta,
                      float* grad_token_eta, float* grad_ln_weight, float* grad_ln_bias, void* workspace,
-                     size_t workspace_bytes, void* status, void* stream);
+                     size_t workspace_bytes, int workspace_from_forward, void* status, void* stream);
 
 /* One mini-batch of fewer than (or exactly) mini_batch tokens: the tail of a sequence whose length is not a multiple
  * of the mini-batch, and the 1-token decode step.  Semantics: the reference's `TTTInnerModel::forward` calls

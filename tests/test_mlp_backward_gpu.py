@@ -20,15 +20,24 @@ def _case(B, H, T, seed):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("B,H,NS", ((1, 1, 1), (2, 3, 4), (1, 2, 12)))
-def test_mlp_backward_matches_autograd_of_the_restatement(B, H, NS):
+@pytest.mark.parametrize("from_forward", (False, True))
+@pytest.mark.parametrize("B,H,NS", ((1, 1, 1), (2, 3, 4), (1, 2, 12), (1, 1, 19)))
+def test_mlp_backward_matches_autograd_of_the_restatement(B, H, NS, from_forward):
+    """Both ways into the backward: on its own (it re-walks the sequence first), and on the workspace that the
+    forward call filled on the way (final state + the operands of every state update)."""
     import ttt_rs_b200 as tb
     dev = torch.device("cuda:0")
     t = _case(B, H, NS * 16, 50 + NS)
     cfg = tb.FusedTttConfig.new(16, 64, 1e-6, 128, 1)
     d = {k: v.to(dev) for k, v in t.items()}
-    g = tb.fused_ttt_mlp_backward(d["xq"], d["xk"], d["xv"], tb.TTTMLPState(d["w1"], d["b1"], d["w2"], d["b2"]),
-                                  d["token_eta"], d["ttt_lr_eta"], d["ln_weight"], d["ln_bias"], d["grad_output"], cfg)
+    st = tb.TTTMLPState(d["w1"], d["b1"], d["w2"], d["b2"])
+    ws = None
+    if from_forward:
+        ws = tb.mlp_backward_workspace(d["xq"], cfg)
+        tb.fused_ttt_mlp_forward(d["xq"], d["xk"], d["xv"], st, d["token_eta"], d["ttt_lr_eta"], d["ln_weight"],
+                                 d["ln_bias"], cfg, backward_workspace=ws)
+    g = tb.fused_ttt_mlp_backward(d["xq"], d["xk"], d["xv"], st, d["token_eta"], d["ttt_lr_eta"], d["ln_weight"],
+                                  d["ln_bias"], d["grad_output"], cfg, workspace_from_forward=ws)
     torch.cuda.synchronize()
     tb.check_mlp_status(g)
     want = O.ttt_mlp_backward_autograd(*[t[k].double() for k in MLP_IN], t["grad_output"].double())
@@ -36,7 +45,15 @@ def test_mlp_backward_matches_autograd_of_the_restatement(B, H, NS):
     for k in ("grad_xq", "grad_xk", "grad_xv", "grad_w1", "grad_b1", "grad_w2", "grad_b2", "grad_ttt_lr_eta",
               "grad_ln_weight", "grad_ln_bias"):
         assert_close(g[k], want[k], 2e-2, k, max_bad_frac=2e-3)
-    assert_close(fold(g["grad_token_eta"]), fold(want["grad_token_eta"]), 2e-2, "grad_token_eta (folded)")
+    # token_eta: every (stage, position) entry at the bf16 tolerance.  The sum over the stages of one position can
+    # cancel heavily (entries of both signs; for position 15, which also carries the step-size gradient of the state
+    # updates, |sum| is up to 30 times smaller than the sum of the magnitudes), so the folded vector is held to the
+    # usual criterion or to 5e-3 of the sum of the magnitudes of its terms, whichever is larger.
+    assert_close(g["grad_token_eta"], want["grad_token_eta"], 2e-2, "grad_token_eta (per stage and position)")
+    fw = fold(want["grad_token_eta"])
+    err = (fold(g["grad_token_eta"]) - fw).abs()
+    bound = torch.maximum(2e-2 * (fw.abs() + fw.pow(2).mean().sqrt()), 5e-3 * fold(want["grad_token_eta"].abs()))
+    assert bool((err <= bound).all()), f"grad_token_eta folded: error {err.tolist()} above {bound.tolist()}"
 
 
 @pytest.mark.gpu
@@ -49,10 +66,14 @@ def test_mlp_backward_at_the_benchmark_size_on_sampled_streams():
     t = O.make_inputs(B, H, T, 64, 16, seed=0, dtype=torch.bfloat16, inner="mlp")
     cfg = tb.FusedTttConfig.new(16, 64, 1e-6, 128, 1)
     d = {k: v.to(dev) for k, v in t.items()}
-    g = tb.fused_ttt_mlp_backward(d["xq"], d["xk"], d["xv"], tb.TTTMLPState(d["w1"], d["b1"], d["w2"], d["b2"]),
-                                  d["token_eta"], d["ttt_lr_eta"], d["ln_weight"], d["ln_bias"], d["grad_output"], cfg)
+    st = tb.TTTMLPState(d["w1"], d["b1"], d["w2"], d["b2"])
+    ws = tb.mlp_backward_workspace(d["xq"], cfg)
+    tb.fused_ttt_mlp_forward(d["xq"], d["xk"], d["xv"], st, d["token_eta"], d["ttt_lr_eta"], d["ln_weight"],
+                             d["ln_bias"], cfg, backward_workspace=ws)
+    g = tb.fused_ttt_mlp_backward(d["xq"], d["xk"], d["xv"], st, d["token_eta"], d["ttt_lr_eta"], d["ln_weight"],
+                                  d["ln_bias"], d["grad_output"], cfg, workspace_from_forward=ws)
     torch.cuda.synchronize()
-    tb.check_mlp_status(g)  # 192 streams x 32 work items handed between the persistent blocks, no wait ran out
+    tb.check_mlp_status(g)  # 192 streams x 16 work items handed between the persistent blocks, no wait ran out
     for k, v in g.items():
         if not k.startswith("_"):
             assert torch.isfinite(v.float()).all(), k
@@ -63,16 +84,27 @@ def test_mlp_backward_at_the_benchmark_size_on_sampled_streams():
         for k in ("grad_xq", "grad_xk", "grad_xv", "grad_w1", "grad_b1", "grad_w2", "grad_b2", "grad_ttt_lr_eta"):
             assert_close(g[k][b:b + 1, h:h + 1], want[k], 2e-2, f"stream ({b},{h}) {k}", max_bad_frac=2e-3)
     # a second run gives the same bits (fixed-order reductions, no atomics)
-    g2 = tb.fused_ttt_mlp_backward(d["xq"], d["xk"], d["xv"], tb.TTTMLPState(d["w1"], d["b1"], d["w2"], d["b2"]),
-                                   d["token_eta"], d["ttt_lr_eta"], d["ln_weight"], d["ln_bias"], d["grad_output"], cfg)
+    tb.fused_ttt_mlp_forward(d["xq"], d["xk"], d["xv"], st, d["token_eta"], d["ttt_lr_eta"], d["ln_weight"],
+                             d["ln_bias"], cfg, backward_workspace=ws)
+    g2 = tb.fused_ttt_mlp_backward(d["xq"], d["xk"], d["xv"], st, d["token_eta"], d["ttt_lr_eta"], d["ln_weight"],
+                                   d["ln_bias"], d["grad_output"], cfg, workspace_from_forward=ws)
     torch.cuda.synchronize()
     for k in ("grad_xq", "grad_w1", "grad_token_eta", "grad_ln_weight"):
         assert torch.equal(g[k], g2[k]), f"{k} differs between two runs"
+    # and the backward that walks the sequence itself (32 work items per stream) agrees with it
+    g3 = tb.fused_ttt_mlp_backward(d["xq"], d["xk"], d["xv"], st, d["token_eta"], d["ttt_lr_eta"], d["ln_weight"],
+                                   d["ln_bias"], d["grad_output"], cfg)
+    torch.cuda.synchronize()
+    tb.check_mlp_status(g3)
+    for k in ("grad_xq", "grad_xk", "grad_w1", "grad_w2", "grad_ttt_lr_eta"):
+        assert_close(g3[k], g[k].float(), 2e-2, f"{k}: own forward walk vs workspace from the forward",
+                     max_bad_frac=2e-3)
 
 
 @pytest.mark.gpu
 def test_mlp_autograd_node():
-    """`fused_ttt_mlp` under torch autograd: gradients reach the leaves and equal the direct backward call."""
+    """`fused_ttt_mlp` under torch autograd: gradients reach the leaves and equal the direct calls (forward filling
+    the backward's workspace, then the backward on it)."""
     import ttt_rs_b200 as tb
     dev = torch.device("cuda:0")
     t = _case(1, 2, 32, 77)
@@ -84,8 +116,12 @@ def test_mlp_autograd_node():
                               tb.TTTMLPState(leaves["w1"], leaves["b1"], leaves["w2"], leaves["b2"]), d["token_eta"],
                               leaves["ttt_lr_eta"], leaves["ln_weight"], leaves["ln_bias"], cfg)
     out.backward(d["grad_output"])
-    g = tb.fused_ttt_mlp_backward(d["xq"], d["xk"], d["xv"], tb.TTTMLPState(d["w1"], d["b1"], d["w2"], d["b2"]),
-                                  d["token_eta"], d["ttt_lr_eta"], d["ln_weight"], d["ln_bias"], d["grad_output"], cfg)
+    st = tb.TTTMLPState(d["w1"], d["b1"], d["w2"], d["b2"])
+    ws = tb.mlp_backward_workspace(d["xq"], cfg)
+    tb.fused_ttt_mlp_forward(d["xq"], d["xk"], d["xv"], st, d["token_eta"], d["ttt_lr_eta"], d["ln_weight"],
+                             d["ln_bias"], cfg, backward_workspace=ws)
+    g = tb.fused_ttt_mlp_backward(d["xq"], d["xk"], d["xv"], st, d["token_eta"], d["ttt_lr_eta"], d["ln_weight"],
+                                  d["ln_bias"], d["grad_output"], cfg, workspace_from_forward=ws)
     torch.cuda.synchronize()
     for k in ("xq", "xk", "xv", "w1", "b1", "w2", "b2", "ttt_lr_eta"):
         assert torch.equal(leaves[k].grad, g["grad_" + k]), k

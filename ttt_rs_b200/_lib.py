@@ -57,10 +57,10 @@ SYMBOLS = {
     "ttt_linear_backward_workspace_bytes": (C.c_size_t, [_DP]),
     "ttt_linear_backward": (C.c_int, [_DP] + [_P] * 23 + [C.c_size_t, _P, _P]),
     "ttt_linear_backward_noalloc": (C.c_int, [_DP] + [_P] * 22 + [_P, _P]),
-    "ttt_mlp_forward": (C.c_int, [_DP] + [_P] * 18),
+    "ttt_mlp_forward": (C.c_int, [_DP] + [_P] * 17 + [C.c_size_t, _P, _P]),
     "ttt_linear_backward_state_grads": (C.c_int, [_DP] + [_P] * 25 + [C.c_size_t, _P, _P]),
     "ttt_mlp_backward_workspace_bytes": (C.c_size_t, [_DP]),
-    "ttt_mlp_backward": (C.c_int, [_DP] + [_P] * 24 + [C.c_size_t, _P, _P]),
+    "ttt_mlp_backward": (C.c_int, [_DP] + [_P] * 24 + [C.c_size_t, C.c_int, _P, _P]),
     "ttt_linear_forward_partial": (C.c_int, [_DP] + [_P] * 13),
     "ttt_layer_prologue": (C.c_int, [_DP, _P, _P, _P, C.c_int64, _P, C.c_int64, _P, _P, _P, _P, _P, C.c_int, C.c_int,
                                      C.c_int, C.c_float, C.c_float, _P, _P, _P, _P, _P]),

@@ -129,6 +129,23 @@ WsLayout ws_layout(const ttt_dims* d) {
 
 }  // namespace
 
+// workspace of the TTT-MLP backward (which the forward can pre-fill)
+namespace {
+struct MlpWsLayout {
+  size_t stride_floats, off_te, off_ln, off_sched, total_bytes;
+};
+MlpWsLayout mlp_ws_layout(const ttt_dims* d) {
+  const size_t streams = (size_t)d->batch * d->heads;
+  MlpWsLayout l;
+  l.stride_floats = ttt::mlp_bwd_ws_stride_floats(d->seq_len);
+  l.off_te = streams * l.stride_floats;
+  l.off_ln = l.off_te + streams * (size_t)d->seq_len;
+  l.off_sched = l.off_ln + streams * 2 * 64;
+  l.total_bytes = (l.off_sched + ((1 + streams + 3) & ~(size_t)3)) * sizeof(float);
+  return l;
+}
+}  // namespace
+
 extern "C" {
 
 int ttt_b200_abi_version(void) { return TTT_B200_ABI_VERSION; }
@@ -338,10 +355,19 @@ int ttt_linear_backward_state_grads(const ttt_dims* d, const void* xq, const voi
 int ttt_mlp_forward(const ttt_dims* d, const void* xq, const void* xk, const void* xv, const void* w1, const void* b1,
                     const void* w2, const void* b2, const void* token_eta, const void* ttt_lr_eta,
                     const void* ln_weight, const void* ln_bias, void* output, void* w1_out, void* b1_out, void* w2_out,
-                    void* b2_out, void* status, void* stream) {
+                    void* b2_out, void* backward_workspace, size_t backward_workspace_bytes, void* status,
+                    void* stream) {
   int rc = check_dims(d);
   if (rc != TTT_OK) return rc;
   if (d->dtype != TTT_BF16) return fail(TTT_ERR_UNSUPPORTED, "the TTT-MLP kernel is built for bf16 only");
+  const MlpWsLayout wl = mlp_ws_layout(d);
+  if (backward_workspace != nullptr) {
+    if (backward_workspace_bytes < wl.total_bytes)
+      return fail(TTT_ERR_WORKSPACE, "backward workspace of %zu bytes needed, %zu given", wl.total_bytes,
+                  backward_workspace_bytes);
+    if ((reinterpret_cast<uintptr_t>(backward_workspace) & 15u) != 0)
+      return fail(TTT_ERR_ALIGN, "backward workspace is not 16-byte aligned");
+  }
   const NamedPtr ptrs[] = {{"xq", xq}, {"xk", xk}, {"xv", xv}, {"w1", w1}, {"b1", b1}, {"w2", w2}, {"b2", b2},
                            {"token_eta", token_eta}, {"ttt_lr_eta", ttt_lr_eta}, {"ln_weight", ln_weight},
                            {"ln_bias", ln_bias}, {"output", output}, {"w1_out", w1_out}, {"b1_out", b1_out},
@@ -360,6 +386,8 @@ int ttt_mlp_forward(const ttt_dims* d, const void* xq, const void* xk, const voi
   p.token_eta = token_eta; p.lr = ttt_lr_eta; p.ln_g = ln_weight; p.ln_b = ln_bias;
   p.w1_out = w1_out; p.b1_out = b1_out; p.w2_out = w2_out; p.b2_out = b2_out;
   p.status = static_cast<uint32_t*>(status);
+  p.bwd_ws = static_cast<float*>(backward_workspace);
+  p.bwd_ws_stride = wl.stride_floats;
   p.H = d->heads; p.T = d->seq_len; p.NS = d->seq_len / d->mini_batch; p.eps = d->epsilon;
   cudaError_t e = ttt::launch_mlp_fwd(maps, p, d->batch * d->heads, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "MLP forward launch failed: %s", cudaGetErrorString(e));
@@ -676,21 +704,6 @@ extern "C" int ttt_layer_epilogue_backward(const ttt_dims* d, const void* grad_y
   return TTT_OK;
 }
 
-namespace {
-struct MlpWsLayout {
-  size_t stride_floats, off_te, off_ln, off_sched, total_bytes;
-};
-MlpWsLayout mlp_ws_layout(const ttt_dims* d) {
-  const size_t streams = (size_t)d->batch * d->heads;
-  MlpWsLayout l;
-  l.stride_floats = ttt::mlp_bwd_ws_stride_floats(d->seq_len);
-  l.off_te = streams * l.stride_floats;
-  l.off_ln = l.off_te + streams * (size_t)d->seq_len;
-  l.off_sched = l.off_ln + streams * 2 * 64;
-  l.total_bytes = (l.off_sched + ((1 + streams + 3) & ~(size_t)3)) * sizeof(float);
-  return l;
-}
-}  // namespace
 
 extern "C" size_t ttt_mlp_backward_workspace_bytes(const ttt_dims* d) {
   if (check_dims(d) != TTT_OK || d->dtype != TTT_BF16) return 0;
@@ -703,7 +716,7 @@ extern "C" int ttt_mlp_backward(const ttt_dims* d, const void* xq, const void* x
                                 const void* grad_output, void* grad_xq, void* grad_xk, void* grad_xv, void* grad_w1,
                                 void* grad_b1, void* grad_w2, void* grad_b2, void* grad_ttt_lr_eta,
                                 float* grad_token_eta, float* grad_ln_weight, float* grad_ln_bias, void* workspace,
-                                size_t workspace_bytes, void* status, void* stream) {
+                                size_t workspace_bytes, int workspace_from_forward, void* status, void* stream) {
   int rc = check_dims(d);
   if (rc != TTT_OK) return rc;
   if (d->dtype != TTT_BF16) return fail(TTT_ERR_UNSUPPORTED, "the TTT-MLP kernels are built for bf16 only");
@@ -732,6 +745,7 @@ extern "C" int ttt_mlp_backward(const ttt_dims* d, const void* xq, const void* x
   p.part_te = ws + l.off_te;
   p.part_ln = ws + l.off_ln;
   p.sched = reinterpret_cast<int*>(ws + l.off_sched);
+  p.pass1_done = workspace_from_forward != 0;
   p.status = static_cast<uint32_t*>(status);
   p.trace = static_cast<unsigned int*>(status);  // instrumented builds write 16 words of cycle counts here instead
   p.H = d->heads; p.T = d->seq_len; p.NS = d->seq_len / d->mini_batch; p.eps = d->epsilon;

@@ -75,6 +75,8 @@ struct MlpFwdParams {
   void* w2_out;
   void* b2_out;
   uint32_t* status;
+  float* bwd_ws;         // optional: the backward's workspace; the forward then leaves there what the backward's own
+  size_t bwd_ws_stride;  // first pass would compute (final state, final biases, lr-scaled inner gradients per stage)
   int H, T, NS;
   float eps;
 };
@@ -203,10 +205,21 @@ struct MlpBwdParams {
   uint32_t* status;     // optional 4 words: {TTT_ERR_TIMEOUT, where, block, item} if a hand-off wait ran out
   int H, T, NS;
   int nstreams, CH, NCH;  // set by the launcher: streams, stages per work item, items per pass
+  int pass1_done;         // the forward already filled the workspace (ttt_mlp_forward with backward_workspace)
   float eps;
 };
-// per-stream hand-off record between work items: b1, b2, db1, db2, d ln_weight, d ln_bias
+// Per-stream block of the TTT-MLP backward's workspace, in floats: W1 [64][256], W2 [256][64], dW1, dW2 (float32, each
+// stored tile by tile in accumulator-fragment order, see mlp_state_at), the hand-off record between work items
+// (b1, b2, db1, db2, d ln_weight, d ln_bias), then per stage the bf16 tiles lr o g1 [NS][16][256] and lr o g2
+// [NS][16][64], then the float32 biases b1 | b2 at the start of every stage [NS][256 + 64].
 constexpr int MLP_BWD_HANDOFF_FLOATS = 2 * 256 + 4 * 64;
+constexpr int MLP_HO_B1 = 0, MLP_HO_B2 = 256, MLP_HO_DB1 = 320, MLP_HO_DB2 = 576, MLP_HO_DG = 640, MLP_HO_DB = 704;
+// element (r, c) of a float32 matrix with C columns stored in accumulator-fragment order: the 16 x 8 tile
+// (r / 16, c / 8) occupies 128 consecutive floats, its rows 0..7 before its rows 8..15, and inside a half the
+// element (r % 8, c % 8) sits at 8 * (r % 8) + (c % 8)
+__host__ __device__ inline int mlp_state_at(int r, int c, int C) {
+  return (((r >> 4) * (C / 8) + (c >> 3)) << 7) + (((r >> 3) & 1) << 6) + ((r & 7) << 3) + (c & 7);
+}
 size_t mlp_bwd_ws_stride_floats(int T);
 cudaError_t launch_mlp_bwd(const MlpBwdParams& p, int B, cudaStream_t st);
 

@@ -7,8 +7,9 @@
 //
 // How: the stage-by-stage analytic backward (reverse walk over the mini-batches carrying dW1, db1, dW2, db2; GELU
 // and LayerNorm second derivatives).
-//   pass 1 walks forward once and saves the lr-scaled inner gradients g1p = l o g1, g2p = l o g2 of every stage (bf16:
-//          exactly the operand values of the state update, so that pass 2 can undo the update);
+//   pass 1 walks forward once and saves the lr-scaled inner gradients g1p = lr o g1, g2p = lr o g2 of every stage
+//          (bf16: exactly the operand values of the state update, so that pass 2 can undo the update); the forward
+//          kernel can do this instead while it runs (it then also leaves the final state in the workspace);
 //   pass 2 walks backward: W1_s = W1_{s+1} + K^T g1p, W2_s = W2_{s+1} + X2^T g2p recover the state of the stage,
 //          the stage's forward intermediates are recomputed from it, and the gradient steps follow.
 // Where things live: the float32 masters of W1, W2, dW1, dW2 (256 KB per stream) stay in the workspace (L2-resident
@@ -64,9 +65,7 @@ __device__ __forceinline__ SB<LD, !TR> tr(const SB<LD, TR> m) { return SB<LD, !T
 template <int R, int C, bool TR>
 struct MatG {
   float* p;
-  static __device__ __forceinline__ int at(int r, int c) {
-    return (((r >> 4) * (C / 8) + (c >> 3)) << 7) + (((r >> 3) & 1) << 6) + ((r & 7) << 3) + (c & 7);
-  }
+  static __device__ __forceinline__ int at(int r, int c) { return mlp_state_at(r, c, C); }
 };
 template <int R, int C, bool TR>
 __device__ __forceinline__ MatG<R, C, !TR> tr(const MatG<R, C, TR> m) { return MatG<R, C, !TR>{m.p}; }
@@ -353,8 +352,8 @@ __device__ __forceinline__ void ln_l2_grad_tile(MlpBwdSmem& S, const float (*z)[
   const float s2 = warp_sum(gx0 * x0 + gx1 * x1) * (1.f / HD);
   const float G0 = (gx0 - s1 - x0 * s2) * rs, G1 = (gx1 - s1 - x1 * s2) * rs;
   stb2(&G[r][c], G0, G1);
-  if constexpr (SAVE) {  // l o G, rounded once from the float32 value
-    const uint32_t v = pack_bf16(S.ell[r] * G0, S.ell[r] * G1);
+  if constexpr (SAVE) {  // lr o G, rounded once from the float32 value
+    const uint32_t v = pack_bf16(S.lr[r] * G0, S.lr[r] * G1);
     g2p_global[(r * HD + c) >> 1] = v;
     *reinterpret_cast<uint32_t*>(&S.g2p[r][c]) = v;
   }
@@ -377,8 +376,10 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int NS = p.NS;
   constexpr int F = HD, E = MB_E;
-  constexpr int HO_B1 = 0, HO_B2 = E, HO_DB1 = E + F, HO_DB2 = 2 * E + F, HO_DG = 2 * E + 2 * F, HO_DB = 2 * E + 3 * F;
-  static_assert(HO_DB + F == MLP_BWD_HANDOFF_FLOATS, "hand-off record");
+  constexpr int HO_B1 = MLP_HO_B1, HO_B2 = MLP_HO_B2, HO_DB1 = MLP_HO_DB1, HO_DB2 = MLP_HO_DB2, HO_DG = MLP_HO_DG,
+                HO_DB = MLP_HO_DB;
+  static_assert(HO_B2 == E && HO_DB1 == E + F && HO_DB2 == 2 * E + F && HO_DG == 2 * E + 2 * F &&
+                    HO_DB == 2 * E + 3 * F && HO_DB + F == MLP_BWD_HANDOFF_FLOATS, "hand-off record");
   float* const b1 = S.b1;
   float* const b2 = S.b2;
   float* const db1 = S.db1;
@@ -391,21 +392,23 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
   // held by a resident block: the launch cannot deadlock while all blocks are co-resident (cooperative launch).
   // Between items the stream's state lives in the workspace: the four float32 matrices anyway, the biases, their
   // gradients and the LayerNorm parameter gradients in a small hand-off record.
-  const int nitems = p.nstreams * 2 * p.NCH;
+  // When the forward has already filled the workspace (pass1_done) the chains start at rank NCH.
+  const int rank0 = p.pass1_done ? p.NCH : 0;
+  const int nitems = p.nstreams * (2 * p.NCH - rank0);
   while (true) {
     if (tid == 0) s_item = atomicAdd(&p.sched[0], 1);
     __syncthreads();
     const int item = s_item;
     __syncthreads();
     if (item >= nitems) break;
-    const int rank = item / p.nstreams, stream = item - rank * p.nstreams, head = stream % p.H;
+    const int rel = item / p.nstreams, rank = rank0 + rel, stream = item - rel * p.nstreams, head = stream % p.H;
     const bool pass1 = rank < p.NCH;
     const int chunk = pass1 ? rank : 2 * p.NCH - 1 - rank;
     const int s_lo = chunk * p.CH, s_hi = min(s_lo + p.CH, NS);
     const size_t row_base = (size_t)stream * p.T;
 
   // per-stream workspace: W1 [F][E], W2 [E][F], dW1, dW2 (float32, in the tile order of MatG), the hand-off record,
-  // then g1p [NS][16][E], g2p [NS][16][F] (bf16)
+  // then g1p [NS][16][E], g2p [NS][16][F] (bf16), then b1 | b2 at the start of every stage [NS][E + F] (float32)
   float* ws = p.workspace + (size_t)stream * p.ws_stride;
   float* W1 = ws;
   float* W2 = W1 + F * E;
@@ -414,15 +417,16 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
   float* ho = dW2 + E * F;
   bf* g1p_all = reinterpret_cast<bf*>(ho + MLP_BWD_HANDOFF_FLOATS);
   bf* g2p_all = g1p_all + (size_t)NS * CS * E;
+  float* bst = reinterpret_cast<float*>(g2p_all + (size_t)NS * CS * F);  // [NS][E + F]: b1, b2 at the start of a stage
 
-  if (rank > 0) {
+  if (rel > 0) {
     // wait (bounded) until the previous item of this stream has published its state
     int ok = 1;
     if (tid == 0) {
       ok = 0;
       const volatile int* flag = p.sched + 1 + stream;
       for (uint32_t it = 0; it < (1u << 24); ++it) {
-        if (*flag >= rank) {
+        if (*flag >= rel) {
           ok = 1;
           break;
         }
@@ -508,14 +512,15 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
   const NoEpi noepi;
 
   // W += sign * A^T B with the float32 master in the workspace and its bf16 shadow refreshed together
-  auto update_w1 = [&](const float sign) {  // W1 += sign * K^T t1
-    tile_mma<true, F, E, 8>(mW1, sign, [&](int i, int j, float x, float y) {
+  // (t1 / g2p hold lr o g1 / lr o g2, the operands of the forward's update; its scale te[15] is applied here)
+  auto update_w1 = [&](const float sign) {  // W1 += sign * te[15] * K^T t1
+    tile_mma<true, F, E, 8>(mW1, sign * te_last, [&](int i, int j, float x, float y) {
       c_store(mW1, i, j, x, y);
       stb2(&S.w1[i][j], x, y);
     }, prod<CS>(tr(sk), st1));
   };
-  auto update_w2 = [&](const float sign) {  // W2 += sign * X2^T g2p
-    tile_mma<true, E, F, 8>(mW2, sign, [&](int i, int j, float x, float y) {
+  auto update_w2 = [&](const float sign) {  // W2 += sign * te[15] * X2^T g2p
+    tile_mma<true, E, F, 8>(mW2, sign * te_last, [&](int i, int j, float x, float y) {
       c_store(mW2, i, j, x, y);
       stb2(&S.w2[i][j], x, y);
     }, prod<CS>(tr(sx2), sg2p));
@@ -549,7 +554,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       y *= d1.y;
       stb2(&S.g1[i][j], x, y);
       if constexpr (SAVE) {
-        const uint32_t v = pack_bf16(S.ell[i] * x, S.ell[i] * y);
+        const uint32_t v = pack_bf16(S.lr[i] * x, S.lr[i] * y);
         g1p[(i * E + j) >> 1] = v;
         *reinterpret_cast<uint32_t*>(&S.t1[i][j]) = v;
       }
@@ -573,8 +578,9 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       bf(*dst)[FB] = tid < 128 ? S.k : S.v;
       *reinterpret_cast<uint4*>(&dst[r][c]) = *reinterpret_cast<const uint4*>(src + r * HD + c);
     } else if (tid < 256 + CS) {
-      S.ell[tid - 256] = te_last * ld_as_float<T>(p.lr, row_base + (size_t)s * CS + (tid - 256));
+      S.lr[tid - 256] = ld_as_float<T>(p.lr, row_base + (size_t)s * CS + (tid - 256));
     }
+    for (int e = tid; e < E + F; e += MB_THREADS) bst[(size_t)s * (E + F) + e] = e < E ? b1[e] : b2[e - E];
     __syncthreads();
     TRM(0)
     forward_first_layer(std::false_type{});
@@ -583,8 +589,8 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     TRM(1)
     update_w1(-1.f);
     update_w2(-1.f);
-    add_colsum(b1, &S.t1[0][0], E, EB, -1.f);
-    add_colsum(b2, &S.g2p[0][0], F, FB, -1.f);
+    add_colsum(b1, &S.t1[0][0], E, EB, -te_last);
+    add_colsum(b2, &S.g2p[0][0], F, FB, -te_last);
     __syncthreads();
     TRM(2)
   }
@@ -608,6 +614,12 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       *reinterpret_cast<uint4*>(&dst[r][c]) = in;
       *reinterpret_cast<uint4*>(&S.t1[tid >> 5][8 * (tid & 31)]) = g1v;
       if (tid < 128) *reinterpret_cast<uint4*>(&S.g2p[r][c]) = g2v;
+      // the biases at the start of the stage were saved on the way forward (they are not recovered by undoing the
+      // update: the forward takes its column sums in float32, the operand tiles are bf16)
+      if (tid < E + F) {
+        const float v = __ldcg(bst + (size_t)s * (E + F) + tid);
+        if (tid < E) b1[tid] = v; else b2[tid - E] = v;
+      }
     }
     if (tid < CS) {
       S.lr[tid] = ld_as_float<T>(p.lr, row_base + (size_t)s * CS + tid);
@@ -617,11 +629,9 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     TRM(3)
     // ---- state at the start of this stage: undo the stage's updates (W1 first: X2 depends on it)
     update_w1(1.f);
-    add_colsum(b1, &S.t1[0][0], E, EB, 1.f);
     __syncthreads();
     forward_first_layer(std::true_type{});  // x2 (and the GELU derivatives) of this stage, needed to undo the second layer's update
     update_w2(1.f);
-    add_colsum(b2, &S.g2p[0][0], F, FB, 1.f);
     __syncthreads();
     TRM(4)
     // ---- forward intermediates of the stage
@@ -884,7 +894,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     }
     __threadfence();
     __syncthreads();
-    if (tid == 0) *reinterpret_cast<volatile int*>(p.sched + 1 + stream) = rank + 1;
+    if (tid == 0) *reinterpret_cast<volatile int*>(p.sched + 1 + stream) = rel + 1;
   } else {
     // ---- gradients w.r.t. the initial state, per-stream LayerNorm parameter gradients
     for (int e = tid; e < F * E; e += MB_THREADS) {
@@ -922,11 +932,11 @@ __global__ void ttt_mlp_bwd_reduce_kernel(const float* part_te, const float* par
   }
 }
 
-// floats of workspace per stream: the four float32 state matrices, the hand-off record, then the bf16 g1p / g2p tiles
-// of every stage
+// floats of workspace per stream: the four float32 state matrices, the hand-off record, the bf16 g1p / g2p tiles of
+// every stage, the float32 biases at the start of every stage
 size_t mlp_bwd_ws_stride_floats(int T) {
   const size_t ns = (size_t)T / CS;
-  return 4 * (size_t)HD * MB_E + MLP_BWD_HANDOFF_FLOATS + ns * CS * (MB_E + HD) / 2;
+  return 4 * (size_t)HD * MB_E + MLP_BWD_HANDOFF_FLOATS + ns * CS * (MB_E + HD) / 2 + ns * (MB_E + HD);
 }
 
 cudaError_t launch_mlp_bwd(const MlpBwdParams& p0, int B, cudaStream_t st) {

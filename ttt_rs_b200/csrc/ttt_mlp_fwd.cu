@@ -125,6 +125,14 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
   }
   __syncthreads();
 
+  // Optional: the backward's per-stream workspace block (layout in ttt_kernels.h).  The lr-scaled inner gradients of
+  // every stage (the bf16 operands of the state updates) and the final state go there, so that the backward can
+  // start its reverse walk at once.
+  float* const bws = p.bwd_ws != nullptr ? p.bwd_ws + (size_t)stream * p.bwd_ws_stride : nullptr;
+  uint32_t* const sv_g1p = bws != nullptr ? reinterpret_cast<uint32_t*>(bws + 4 * HD * MLP_E + MLP_BWD_HANDOFF_FLOATS) : nullptr;
+  uint32_t* const sv_g2p = bws != nullptr ? sv_g1p + (size_t)NS * CS * MLP_E / 2 : nullptr;
+  float* const sv_bst = bws != nullptr ? reinterpret_cast<float*>(sv_g2p + (size_t)NS * CS * HD / 2) : nullptr;
+
   auto issue_loads = [&](int s) {
     const int slot = s % MLP_NST;
     const uint32_t bar = bar0 + 8 * slot;
@@ -189,6 +197,12 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
     const int slot = s % MLP_NST;
     const uint32_t tq = base + slot * SM::SLOT, tk = tq + TL, tv = tk + TL;
     int fail = mbar_wait_bounded(bar0 + 8 * slot, (s / MLP_NST) & 1) ? 0 : 1;
+    if (sv_bst != nullptr && g == 0) {  // biases at the start of the stage, for the backward
+      float* const bs = sv_bst + (size_t)s * (MLP_E + HD);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) *reinterpret_cast<float2*>(bs + eb + 8 * j + 2 * t) = b1v[j];
+      *reinterpret_cast<float2*>(bs + MLP_E + fc) = b2v;
+    }
     const float lr_row[2] = {ld_as_float<T>(gbase + SM::OFF_LR + slot * 32, g),
                              ld_as_float<T>(gbase + SM::OFF_LR + slot * 32, g + 8)};
 
@@ -301,7 +315,9 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
         g2p[r] = f2mul(f2fma(x[r], f2(-Bv[r]), f2sub(gg[r], f2(A[r]))), f2(rstd[r] * lr_row[r]));
-        asm volatile("st.shared.b32 [%0], %1;" ::"r"(tG2 + off_bf16(g + 8 * r, fc)), "r"(pack_bf16(g2p[r].x, g2p[r].y)) : "memory");
+        const uint32_t pk2 = pack_bf16(g2p[r].x, g2p[r].y);
+        asm volatile("st.shared.b32 [%0], %1;" ::"r"(tG2 + off_bf16(g + 8 * r, fc)), "r"(pk2) : "memory");
+        if (sv_g2p != nullptr) sv_g2p[((size_t)s * CS + g + 8 * r) * (HD / 2) + (fc >> 1)] = pk2;
       }
     }
     __syncthreads();  // B2: G2p tile visible
@@ -335,7 +351,11 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
 #pragma unroll
     for (int j = 0; j < 4; ++j)
 #pragma unroll
-      for (int r = 0; r < 2; ++r) gt1[j][r] = movm_t_np<1>(split_pack<1>(g1p[j][r].x, g1p[j][r].y));
+      for (int r = 0; r < 2; ++r) {
+        const Pk<1> pk1 = split_pack<1>(g1p[j][r].x, g1p[j][r].y);
+        if (sv_g1p != nullptr) sv_g1p[((size_t)s * CS + g + 8 * r) * (MLP_E / 2) + ((eb + 8 * j + 2 * t) >> 1)] = pk1.p[0];
+        gt1[j][r] = movm_t_np<1>(pk1);
+      }
     {
       Pk<1> am1[4];
       masked_operand(at, am1);
@@ -438,6 +458,8 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
+      // float32 column sums, like the reference; the backward's reverse walk subtracts the sums of the bf16 operand
+      // values instead, which moves the recovered biases by rounding noise only (~1e-3 of one stage's step)
       const F2 cs = f2add(g1p[j][0], g1p[j][1]);
       b1v[j] = f2fma(f2(col_sum(cs.x), col_sum(cs.y)), f2(-te15), b1v[j]);
     }
@@ -468,6 +490,27 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
           st_from_float<T>(p.w1_out, (size_t)stream * HD * MLP_E + (size_t)c * MLP_E + e, w1t[mt][kt][i] * wscale);
           st_from_float<T>(p.w2_out, (size_t)stream * HD * MLP_E + (size_t)e * HD + c, w2[mt][kt][i] * wscale);
         }
+    if (bws != nullptr) {
+      float* const M1 = bws;
+      float* const M2 = bws + HD * MLP_E;
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int kt = 0; kt < 8; ++kt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int e = eb + 16 * mt + g + 8 * (i >> 1), c = 8 * kt + 2 * t + (i & 1);
+            M1[mlp_state_at(c, e, MLP_E)] = w1t[mt][kt][i] * wscale;
+            M2[mlp_state_at(e, c, HD)] = w2[mt][kt][i] * wscale;
+          }
+      if (g == 0) {
+        float* const ho = bws + 4 * HD * MLP_E;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<float2*>(ho + MLP_HO_B1 + eb + 8 * j + 2 * t) = b1v[j];
+        *reinterpret_cast<float2*>(ho + MLP_HO_B2 + fc) = b2v;
+      }
+    }
     if (g == 0) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {

@@ -425,11 +425,23 @@ class TTTMLPState:
     b2: torch.Tensor
 
 
+def mlp_backward_workspace(xq: torch.Tensor, config: FusedTttConfig) -> torch.Tensor:
+    """Scratch buffer of the TTT-MLP backward for inputs shaped like `xq` [B,H,T,F]; `fused_ttt_mlp_forward` can
+    fill it on the way (`backward_workspace=`), which saves the backward its own forward walk."""
+    lib = _lib.load()
+    d = _dims(xq, config)
+    n = lib.ttt_mlp_backward_workspace_bytes(C.byref(d))
+    if n == 0:
+        raise TttError(_lib.TTT_ERR_SHAPE, _lib.last_error() or "unsupported problem for the TTT-MLP backward")
+    return torch.empty(n, dtype=torch.uint8, device=xq.device)
+
+
 def fused_ttt_mlp_forward(xq, xk, xv, state: TTTMLPState, token_eta, ttt_lr_eta, ln_weight, ln_bias,
-                          config: FusedTttConfig):
+                          config: FusedTttConfig, backward_workspace: Optional[torch.Tensor] = None):
     """Whole-sequence forward of the 2-layer inner model in one launch (the loop of
     `TTTMLP::forward_mini_batch`, rust/core/src/mlp.rs:127-208).  Returns (output, new TTTMLPState).
-    bf16 only.  Its gradient is `fused_ttt_mlp_backward` (no autograd node is recorded here)."""
+    bf16 only.  Its gradient is `fused_ttt_mlp_backward` (no autograd node is recorded here); a buffer from
+    `mlp_backward_workspace` passed as `backward_workspace` is filled for it."""
     lib = _lib.load()
     if not xq.is_cuda:
         raise TttError(_lib.TTT_ERR_CUDA, "inputs must be CUDA tensors: this operator has no CPU path")
@@ -451,16 +463,19 @@ def fused_ttt_mlp_forward(xq, xk, xv, state: TTTMLPState, token_eta, ttt_lr_eta,
     rc = lib.ttt_mlp_forward(
         C.byref(d), *[_ptr(ts[k]) for k in ("xq", "xk", "xv", "w1", "b1", "w2", "b2", "token_eta", "ttt_lr_eta",
                                            "ln_weight", "ln_bias")],
-        _ptr(out), _ptr(new.w1), _ptr(new.b1), _ptr(new.w2), _ptr(new.b2), _ptr(status), _stream_ptr(dev))
+        _ptr(out), _ptr(new.w1), _ptr(new.b1), _ptr(new.w2), _ptr(new.b2), _ptr(backward_workspace),
+        0 if backward_workspace is None else backward_workspace.numel(), _ptr(status), _stream_ptr(dev))
     _lib.check(rc)
     return out, new
 
 
 def fused_ttt_mlp_backward(xq, xk, xv, state: TTTMLPState, token_eta, ttt_lr_eta, ln_weight, ln_bias, grad_output,
-                           config: FusedTttConfig):
+                           config: FusedTttConfig, workspace_from_forward: Optional[torch.Tensor] = None):
     """Gradient of `fused_ttt_mlp_forward` for loss = <grad_output, output> (`ttt_mlp_backward`; `state` is the state
     the forward started from).  Returns a dict: grad_xq, grad_xk, grad_xv, grad_w1, grad_b1, grad_w2, grad_b2 (per
-    batch element), grad_ttt_lr_eta, and float32 grad_token_eta [T], grad_ln_weight, grad_ln_bias [H, F]."""
+    batch element), grad_ttt_lr_eta, and float32 grad_token_eta [T], grad_ln_weight, grad_ln_bias [H, F].
+    `workspace_from_forward`: the buffer the forward call on the same inputs filled (`backward_workspace=`); the
+    kernel then skips its own forward walk.  The buffer is consumed (the backward overwrites the state in it)."""
     lib = _lib.load()
     if not xq.is_cuda:
         raise TttError(_lib.TTT_ERR_CUDA, "inputs must be CUDA tensors: this operator has no CPU path")
@@ -483,7 +498,12 @@ def fused_ttt_mlp_backward(xq, xk, xv, state: TTTMLPState, token_eta, ttt_lr_eta
     ws_bytes = lib.ttt_mlp_backward_workspace_bytes(C.byref(d))
     if ws_bytes == 0:
         raise TttError(_lib.TTT_ERR_SHAPE, _lib.last_error() or "unsupported problem for the TTT-MLP backward")
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    if workspace_from_forward is not None:
+        ws = workspace_from_forward
+        if ws.device != dev or ws.dtype != torch.uint8 or ws.numel() < ws_bytes:
+            raise TttError(_lib.TTT_ERR_WORKSPACE, f"workspace_from_forward must be {ws_bytes} bytes on {dev}")
+    else:
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
     names_in = ("xq", "xk", "xv", "w1", "b1", "w2", "b2", "token_eta", "ttt_lr_eta", "ln_weight", "ln_bias",
                 "grad_output")
     names_out = ("grad_xq", "grad_xk", "grad_xv", "grad_w1", "grad_b1", "grad_w2", "grad_b2", "grad_ttt_lr_eta",
@@ -491,7 +511,8 @@ def fused_ttt_mlp_backward(xq, xk, xv, state: TTTMLPState, token_eta, ttt_lr_eta
     status = torch.zeros(16, dtype=torch.int32, device=dev)
     with torch.cuda.device(dev):
         rc = lib.ttt_mlp_backward(C.byref(d), *[_ptr(ts[k]) for k in names_in], *[_ptr(g[k]) for k in names_out],
-                                  _ptr(ws), ws_bytes, _ptr(status), _stream_ptr(dev))
+                                  _ptr(ws), ws_bytes, 0 if workspace_from_forward is None else 1, _ptr(status),
+                                  _stream_ptr(dev))
     _lib.check(rc)
     g["_workspace"] = ws  # keeps the scratch alive until the caller drops the result
     g["_status"] = status  # {0,..} unless a hand-off wait between work items ran out: see `check_mlp_status`
@@ -513,17 +534,21 @@ class _FusedTttMlpFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, xq, xk, xv, w1, b1, w2, b2, token_eta, ttt_lr_eta, ln_weight, ln_bias, config):
+        # the forward fills the backward's workspace on the way (final state + the operands of every state update)
+        ws = mlp_backward_workspace(xq, config)
         out, new = fused_ttt_mlp_forward(xq, xk, xv, TTTMLPState(w1, b1, w2, b2), token_eta, ttt_lr_eta, ln_weight,
-                                         ln_bias, config)
+                                         ln_bias, config, backward_workspace=ws)
         ctx.save_for_backward(xq, xk, xv, w1, b1, w2, b2, token_eta, ttt_lr_eta, ln_weight, ln_bias)
         ctx.config = config
+        ctx.workspace = ws
         return out, new.w1, new.b1, new.w2, new.b2
 
     @staticmethod
     def backward(ctx, g_out, *_state_grads):
         xq, xk, xv, w1, b1, w2, b2, token_eta, lr, ln_w, ln_b = ctx.saved_tensors
+        ws, ctx.workspace = ctx.workspace, None  # consumed by the backward: a second backward re-walks the sequence
         g = fused_ttt_mlp_backward(xq, xk, xv, TTTMLPState(w1, b1, w2, b2), token_eta, lr, ln_w, ln_b,
-                                   g_out.contiguous(), ctx.config)
+                                   g_out.contiguous(), ctx.config, workspace_from_forward=ws)
         dt = xq.dtype
         return (g["grad_xq"], g["grad_xk"], g["grad_xv"], g["grad_w1"], g["grad_b1"], g["grad_w2"], g["grad_b2"],
                 g["grad_token_eta"].to(dt), g["grad_ttt_lr_eta"], g["grad_ln_weight"].to(dt), g["grad_ln_bias"].to(dt),
