@@ -253,6 +253,27 @@ int ttt_layer_epilogue_backward(const ttt_dims* d, const void* grad_y, const voi
                                 float* grad_post_norm_weight, float* grad_post_norm_bias, void* workspace,
                                 size_t workspace_bytes, void* stream);
 
+/* Shared-QK causal depthwise convolutions as a training step of their own (the reference: `conv_qk`,
+ * rust/layer/src/ttt.rs:205-227, nn.Conv1d(groups=C, padding=K-1)(x)[..., :T] in reference/ttt.py:647-663; gradients
+ * there come from autodiff).  Inference applies the convolutions inside ttt_layer_prologue; for training they are a
+ * step with its own gradient, whose outputs go through ttt_layer_prologue / ttt_layer_prologue_backward as separate
+ * q and k blocks.  C = heads * head_dim channels; weights are [C][4] with tap j multiplying token t - 3 + j (a shorter
+ * kernel is passed zero-padded at the front), biases [C]; zeros before the start of each sequence.
+ *   ttt_layer_qk_conv:          x [B*T, x_ld] (first C columns) -> q, k [B*T, C]
+ *   ttt_layer_qk_conv_backward: grad_q, grad_k [B*T, C] -> grad_x [B*T, C] and float32 parameter gradients
+ *                               grad_q_params / grad_k_params [5*C]: d weight as [4][C] (tap-major), then d bias [C];
+ *                               written, summed over all tokens in a fixed order.  `workspace`:
+ *                               ttt_layer_qk_conv_backward_workspace_bytes(d) bytes, 16-byte aligned.
+ */
+int ttt_layer_qk_conv(const ttt_dims* d, const void* x, int64_t x_ld, const void* conv_q_weight,
+                      const void* conv_q_bias, const void* conv_k_weight, const void* conv_k_bias, void* q, void* k,
+                      void* stream);
+size_t ttt_layer_qk_conv_backward_workspace_bytes(const ttt_dims* d);
+int ttt_layer_qk_conv_backward(const ttt_dims* d, const void* grad_q, const void* grad_k, const void* x, int64_t x_ld,
+                               const void* conv_q_weight, const void* conv_k_weight, void* grad_x,
+                               float* grad_q_params, float* grad_k_params, void* workspace, size_t workspace_bytes,
+                               void* stream);
+
 /* Backward without a caller workspace.  (No counterpart in the reference: its host wrapper always allocates its
  * scratch itself, backward/launch.rs:389-392.)
  *

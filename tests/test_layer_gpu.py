@@ -156,24 +156,16 @@ def test_layer_forward_bfloat16_at_a_wider_shape():
     assert_close(y, want, 2e-2, "layer output", max_bad_frac=1e-3)
 
 
-def test_training_with_shared_qk_convolutions_is_refused():
-    import ttt_rs_b200 as tb
-    cfg = tb.TTTLayerConfig(hidden_size=128, num_heads=2, share_qk=True)
-    m = tb.TTT(cfg)
-    with pytest.raises(NotImplementedError, match="shared-QK"):
-        m(torch.zeros(1, 16, 128), tb.new_inner(cfg), None)
-
-
 @pytest.mark.gpu
-@pytest.mark.parametrize("use_gate", (False, True))
-def test_layer_training_gradients_match_autograd_of_the_restatement(use_gate):
+@pytest.mark.parametrize("use_gate,share_qk", ((False, False), (True, False), (True, True)))
+def test_layer_training_gradients_match_autograd_of_the_restatement(use_gate, share_qk):
     """Whole-layer backward (projection GEMM gradients by torch, every other step by this repo's gradient kernels)
     against float64 autograd through the CPU restatement."""
     import ttt_rs_b200 as tb
     dev = torch.device("cuda:0")
-    B, T, H = 2, 48, 3
-    x, p = _random_case(B, T, H, 31, False, use_gate, torch.float32)
-    m, inner = _layer_from_params(tb, p, False, use_gate, torch.float32, dev, H)
+    B, T, H = 2, 80 if share_qk else 48, 3  # 80 tokens: two chunks of the convolution gradient kernel
+    x, p = _random_case(B, T, H, 31, share_qk, use_gate, torch.float32)
+    m, inner = _layer_from_params(tb, p, share_qk, use_gate, torch.float32, dev, H)
     xg = x.float().to(dev).requires_grad_(True)
     gy = torch.randn(B, T, H * 64, generator=torch.Generator().manual_seed(2)).double()
     state = inner.init_state(B)
@@ -185,18 +177,23 @@ def test_layer_training_gradients_match_autograd_of_the_restatement(use_gate):
     leaves = {k: v.clone().requires_grad_(True) for k, v in p.items() if k != "token_idx"}
     leaves["token_idx"] = p["token_idx"]
     xr = x.clone().requires_grad_(True)
-    yr, _ = LO.ttt_layer_forward(xr, leaves, num_heads=H, use_gate=use_gate)
+    yr, _ = LO.ttt_layer_forward(xr, leaves, num_heads=H, use_gate=use_gate, share_qk=share_qk)
     yr.backward(gy)
     assert_close(y, yr, 2e-4, "output")
     rt = 1e-3
     assert_close(xg.grad, xr.grad, rt, "d input")
-    pairs = {"q_proj": m.q_proj, "k_proj": m.k_proj, "v_proj": m.v_proj, "o_proj": m.o_proj,
+    pairs = {"q_proj": m.q_proj, "v_proj": m.v_proj, "o_proj": m.o_proj,
              "lr_weight": m.learnable_ttt_lr_weight, "lr_bias": m.learnable_ttt_lr_bias,
              "learnable_token_idx": m.learnable_token_idx, "post_norm_weight": m.post_norm_weight,
              "post_norm_bias": m.post_norm_bias, "W1": inner.inner.weight_init, "b1": inner.inner.bias_init,
              "ttt_norm_weight": inner.inner.ln_weight, "ttt_norm_bias": inner.inner.ln_bias}
     if use_gate:
         pairs["g_proj"] = m.g_proj
+    if share_qk:
+        pairs.update({"conv_q_weight": m.q_conv_weight, "conv_q_bias": m.q_conv_bias,
+                      "conv_k_weight": m.k_conv_weight, "conv_k_bias": m.k_conv_bias})
+    else:
+        pairs["k_proj"] = m.k_proj
     for name, param in pairs.items():
         assert param.grad is not None, f"no gradient reached {name}"
         assert_close(param.grad.reshape(leaves[name].grad.shape), leaves[name].grad, rt, f"d {name}")
@@ -245,3 +242,34 @@ def test_layer_with_mlp_inner_model_forward_and_training(golden_dir):
                         ("v_proj", m.v_proj), ("o_proj", m.o_proj), ("post_norm_weight", m.post_norm_weight)):
         assert param.grad is not None, name
         assert_close(param.grad.reshape(leaves[name].grad.shape), leaves[name].grad, 3e-2, f"d {name}", max_bad_frac=5e-3)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,K", ((torch.float32, 4), (torch.float32, 3), (torch.bfloat16, 4)))
+def test_shared_qk_convolution_step_and_its_gradient(dtype, K):
+    """`ttt_layer_qk_conv` / `ttt_layer_qk_conv_backward` on a ragged size (T not a multiple of the kernel's token
+    chunk, a kernel shorter than four taps) against float64 autograd through the restatement's convolution."""
+    import ttt_rs_b200 as tb
+    from ttt_rs_b200.layer import _QkConvFn
+    dev = torch.device("cuda:0")
+    B, T, H = 2, 150, 3
+    C, N = H * 64, H * 64 + 72  # the convolutions read a column block of a wider projection output
+    g = torch.Generator().manual_seed(5)
+    r = lambda *s, sc=1.0: (torch.randn(*s, generator=g) * sc).to(dtype).double()  # noqa: E731
+    proj, wq, bq, wk, bk = r(B, T, N), r(C, 1, K, sc=0.5), r(C, sc=0.1), r(C, 1, K, sc=0.5), r(C, sc=0.1)
+    gq, gk = r(B, T, C), r(B, T, C)
+    cfg = tb.TTTLayerConfig(hidden_size=C, num_heads=H, share_qk=True, conv_kernel_size=K)
+    leaves = [t.to(dtype).to(dev).requires_grad_(True) for t in (proj, wq, bq, wk, bk)]
+    q, k = _QkConvFn.apply(leaves[0], 0, C, leaves[1], leaves[2], leaves[3], leaves[4], cfg)
+    torch.autograd.backward((q, k), (gq.to(dtype).to(dev), gk.to(dtype).to(dev)))
+    torch.cuda.synchronize()
+    ref = [t.clone().requires_grad_(True) for t in (proj, wq, bq, wk, bk)]
+    qr = LO.causal_depthwise_conv(ref[0][..., :C], ref[1], ref[2])
+    kr = LO.causal_depthwise_conv(ref[0][..., :C], ref[3], ref[4])
+    torch.autograd.backward((qr, kr), (gq, gk))
+    bf = dtype == torch.bfloat16
+    rt, frac = (2e-2, 2e-3) if bf else (1e-4, 0.0)
+    assert_close(q, qr, rt, "conv_q output", max_bad_frac=frac)
+    assert_close(k, kr, rt, "conv_k output", max_bad_frac=frac)
+    for name, a, b in zip(("d proj", "d conv_q_weight", "d conv_q_bias", "d conv_k_weight", "d conv_k_bias"), leaves, ref):
+        assert_close(a.grad, b.grad, rt, name, max_bad_frac=frac)

@@ -649,6 +649,58 @@ extern "C" int ttt_layer_prologue_backward(const ttt_dims* d, const void* grad_x
   return TTT_OK;
 }
 
+extern "C" int ttt_layer_qk_conv(const ttt_dims* d, const void* x, int64_t x_ld, const void* conv_q_weight,
+                                 const void* conv_q_bias, const void* conv_k_weight, const void* conv_k_bias, void* q,
+                                 void* k, void* stream) {
+  int rc = check_layer_dims(d);
+  if (rc != TTT_OK) return rc;
+  const int64_t C = (int64_t)d->heads * 64;
+  if (x_ld < C || (x_ld & 7) != 0) return fail(TTT_ERR_SHAPE, "x_ld (%lld) must be >= heads*64 and a multiple of 8", (long long)x_ld);
+  const NamedPtr ptrs[] = {{"x", x}, {"q", q}, {"k", k}};
+  rc = check_ptrs(ptrs, 3);
+  if (rc != TTT_OK) return rc;
+  if (conv_q_weight == nullptr || conv_q_bias == nullptr || conv_k_weight == nullptr || conv_k_bias == nullptr)
+    return fail(TTT_ERR_NULL, "a convolution weight or bias is null");
+  ttt::LayerConvParams p;
+  p.x = x; p.ld_x = (long)x_ld; p.wq = conv_q_weight; p.bq = conv_q_bias; p.wk = conv_k_weight; p.bk = conv_k_bias;
+  p.q = q; p.k = k; p.B = d->batch; p.T = d->seq_len; p.C = (int)C;
+  cudaError_t e = ttt::launch_layer_conv(d->dtype, p, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "shared-QK convolution launch failed: %s", cudaGetErrorString(e));
+  return TTT_OK;
+}
+
+extern "C" size_t ttt_layer_qk_conv_backward_workspace_bytes(const ttt_dims* d) {
+  if (check_layer_dims(d) != TTT_OK) return 0;
+  const size_t nch = ((size_t)d->seq_len + ttt::LAYER_CONV_CHUNK - 1) / ttt::LAYER_CONV_CHUNK;
+  return (size_t)d->batch * nch * 10 * (size_t)d->heads * 64 * sizeof(float);
+}
+
+extern "C" int ttt_layer_qk_conv_backward(const ttt_dims* d, const void* grad_q, const void* grad_k, const void* x,
+                                          int64_t x_ld, const void* conv_q_weight, const void* conv_k_weight,
+                                          void* grad_x, float* grad_q_params, float* grad_k_params, void* workspace,
+                                          size_t workspace_bytes, void* stream) {
+  int rc = check_layer_dims(d);
+  if (rc != TTT_OK) return rc;
+  const int64_t C = (int64_t)d->heads * 64;
+  if (x_ld < C || (x_ld & 7) != 0) return fail(TTT_ERR_SHAPE, "x_ld (%lld) must be >= heads*64 and a multiple of 8", (long long)x_ld);
+  const NamedPtr ptrs[] = {{"grad_q", grad_q}, {"grad_k", grad_k}, {"x", x}, {"grad_x", grad_x}};
+  rc = check_ptrs(ptrs, 4);
+  if (rc != TTT_OK) return rc;
+  if (conv_q_weight == nullptr || conv_k_weight == nullptr || grad_q_params == nullptr || grad_k_params == nullptr)
+    return fail(TTT_ERR_NULL, "a convolution weight or parameter-gradient buffer is null");
+  const size_t need = ttt_layer_qk_conv_backward_workspace_bytes(d);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(TTT_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return fail(TTT_ERR_ALIGN, "workspace is not 16-byte aligned");
+  ttt::LayerConvBwdParams p;
+  p.dq = grad_q; p.dk = grad_k; p.x = x; p.ld_x = (long)x_ld; p.wq = conv_q_weight; p.wk = conv_k_weight;
+  p.dx = grad_x; p.partials = static_cast<float*>(workspace); p.dparams_q = grad_q_params; p.dparams_k = grad_k_params;
+  p.B = d->batch; p.T = d->seq_len; p.C = (int)C;
+  cudaError_t e = ttt::launch_layer_conv_bwd(d->dtype, p, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "shared-QK convolution backward launch failed: %s", cudaGetErrorString(e));
+  return TTT_OK;
+}
+
 extern "C" size_t ttt_layer_epilogue_backward_workspace_bytes(const ttt_dims* d) {
   if (check_layer_dims(d) != TTT_OK || d->heads > 32) return 0;
   return ttt::layer_epilogue_bwd_workspace_bytes(d->batch, d->heads, d->seq_len);

@@ -146,6 +146,36 @@ struct LayerEpiBwdParams {
   int B, H, T;
   float eps;
 };
+// Shared-QK causal depthwise convolutions as a training step of their own (ttt_layer.cu): q = conv_q(x) + bq,
+// k = conv_k(x) + bk over the token axis, four taps aligned to the end (tap j multiplies token t - 3 + j; shorter
+// kernels are passed zero-padded at the front), zeros before the start of the sequence.
+struct LayerConvParams {
+  const void* x;   // [B*T, ld_x] shared projection output, C = H*F columns used
+  long ld_x;
+  const void* wq;  // [C][4]
+  const void* bq;  // [C]
+  const void* wk;
+  const void* bk;
+  void* q;         // [B*T, C] (out)
+  void* k;         // [B*T, C] (out)
+  int B, T, C;
+};
+struct LayerConvBwdParams {
+  const void* dq;  // [B*T, C]
+  const void* dk;
+  const void* x;   // as in the forward
+  long ld_x;
+  const void* wq;
+  const void* wk;
+  void* dx;        // [B*T, C] (out)
+  float* partials; // [B * ceil(T / LAYER_CONV_CHUNK)][10 C] per-chunk parameter-gradient partials
+  float* dparams_q;  // [5 C]: d wq as [4][C] (tap-major), then d bq [C]
+  float* dparams_k;  // [5 C]
+  int B, T, C;
+};
+constexpr int LAYER_CONV_CHUNK = 64;  // tokens a thread walks
+cudaError_t launch_layer_conv(int dtype, const LayerConvParams& p, cudaStream_t st);
+cudaError_t launch_layer_conv_bwd(int dtype, const LayerConvBwdParams& p, cudaStream_t st);
 cudaError_t launch_layer_prologue(int dtype, const LayerProParams& p, cudaStream_t st);
 cudaError_t launch_layer_prologue_bwd(int dtype, const LayerProBwdParams& p, cudaStream_t st);
 cudaError_t launch_layer_epilogue_bwd(int dtype, const LayerEpiBwdParams& p, cudaStream_t st);

@@ -847,4 +847,195 @@ cudaError_t launch_layer_epilogue_bwd(int dtype, const LayerEpiBwdParams& p0, cu
   return p.H <= 16 ? launch_epi_bwd_t<float, 8>(p, st) : launch_epi_bwd_t<float, 16>(p, st);
 }
 
+// ----------------------------------------------------------------------------------------------------
+// Shared-QK convolutions as a differentiable step (training path of the shared-QK layout; inference applies them
+// inside the prologue kernel).  A thread owns four adjacent channels and walks LAYER_CONV_CHUNK tokens of one batch
+// row with a rolling window, so every global access of a warp is one contiguous row piece.
+// ----------------------------------------------------------------------------------------------------
+template <typename T>
+struct Vec4;
+template <>
+struct Vec4<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const void* p, float (&f)[4]) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    f[0] = bf16_lo(r.x); f[1] = bf16_hi(r.x); f[2] = bf16_lo(r.y); f[3] = bf16_hi(r.y);
+  }
+  static __device__ __forceinline__ void store(void* p, const float (&f)[4]) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]));
+  }
+};
+template <>
+struct Vec4<float> {
+  static __device__ __forceinline__ void load(const void* p, float (&f)[4]) {
+    const float4 r = *reinterpret_cast<const float4*>(p);
+    f[0] = r.x; f[1] = r.y; f[2] = r.z; f[3] = r.w;
+  }
+  static __device__ __forceinline__ void store(void* p, const float (&f)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) ttt_layer_conv_kernel(const LayerConvParams p) {
+  const int ncg = p.C / 4, nch = (p.T + LAYER_CONV_CHUNK - 1) / LAYER_CONV_CHUNK;
+  const long total = (long)p.B * nch * ncg;
+  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
+    const int cg = (int)(idx % ncg);
+    const long rest = idx / ncg;
+    const int ch = (int)(rest % nch), b = (int)(rest / nch);
+    const int c0 = 4 * cg, t0 = ch * LAYER_CONV_CHUNK, t1 = min(t0 + LAYER_CONV_CHUNK, p.T);
+    float wq[4][4], wk[4][4], bq[4], bk[4];  // [channel][tap]
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      Vec4<T>::load(static_cast<const T*>(p.wq) + (size_t)(c0 + c) * 4, wq[c]);
+      Vec4<T>::load(static_cast<const T*>(p.wk) + (size_t)(c0 + c) * 4, wk[c]);
+    }
+    Vec4<T>::load(static_cast<const T*>(p.bq) + c0, bq);
+    Vec4<T>::load(static_cast<const T*>(p.bk) + c0, bk);
+    const T* xb = static_cast<const T*>(p.x) + (size_t)b * p.T * p.ld_x + c0;
+    float win[3][4];  // x at t-3, t-2, t-1
+#pragma unroll
+    for (int d = 0; d < 3; ++d) {
+      const int t = t0 - 3 + d;
+      if (t >= 0) {
+        Vec4<T>::load(xb + (size_t)t * p.ld_x, win[d]);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) win[d][c] = 0.f;
+      }
+    }
+    for (int t = t0; t < t1; ++t) {
+      float xv[4], q[4], k[4];
+      Vec4<T>::load(xb + (size_t)t * p.ld_x, xv);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        q[c] = bq[c] + wq[c][0] * win[0][c] + wq[c][1] * win[1][c] + wq[c][2] * win[2][c] + wq[c][3] * xv[c];
+        k[c] = bk[c] + wk[c][0] * win[0][c] + wk[c][1] * win[1][c] + wk[c][2] * win[2][c] + wk[c][3] * xv[c];
+        win[0][c] = win[1][c];
+        win[1][c] = win[2][c];
+        win[2][c] = xv[c];
+      }
+      const size_t o = ((size_t)b * p.T + t) * p.C + c0;
+      Vec4<T>::store(static_cast<T*>(p.q) + o, q);
+      Vec4<T>::store(static_cast<T*>(p.k) + o, k);
+    }
+  }
+}
+
+// dx[t] = sum_j wq[j] dq[t + 3 - j] + wk[j] dk[t + 3 - j] (terms beyond the sequence end dropped); parameter
+// gradients d w[j] = sum_t d out[t] x[t - 3 + j], d b = sum_t d out[t], as per-chunk partials (summed afterwards in a
+// fixed order).  The chunk is walked from its last token to its first.
+template <typename T>
+__global__ void __launch_bounds__(256) ttt_layer_conv_bwd_kernel(const LayerConvBwdParams p) {
+  const int ncg = p.C / 4, nch = (p.T + LAYER_CONV_CHUNK - 1) / LAYER_CONV_CHUNK;
+  const long total = (long)p.B * nch * ncg;
+  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
+    const int cg = (int)(idx % ncg);
+    const long rest = idx / ncg;
+    const int ch = (int)(rest % nch), b = (int)(rest / nch);
+    const int c0 = 4 * cg, t0 = ch * LAYER_CONV_CHUNK, t1 = min(t0 + LAYER_CONV_CHUNK, p.T);
+    float wq[4][4], wk[4][4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      Vec4<T>::load(static_cast<const T*>(p.wq) + (size_t)(c0 + c) * 4, wq[c]);
+      Vec4<T>::load(static_cast<const T*>(p.wk) + (size_t)(c0 + c) * 4, wk[c]);
+    }
+    const T* xb = static_cast<const T*>(p.x) + (size_t)b * p.T * p.ld_x + c0;
+    const T* dqb = static_cast<const T*>(p.dq) + (size_t)b * p.T * p.C + c0;
+    const T* dkb = static_cast<const T*>(p.dk) + (size_t)b * p.T * p.C + c0;
+    float gq[3][4], gk[3][4];  // d out at t+1, t+2, t+3
+    float xw[4][4];            // x at t, t-1, t-2, t-3
+    float aq[5][4], ak[5][4];  // accumulators: taps 0..3, bias
+#pragma unroll
+    for (int j = 0; j < 5; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) aq[j][c] = ak[j][c] = 0.f;
+#pragma unroll
+    for (int d = 0; d < 3; ++d) {
+      const int t = t1 + d;
+      if (t < p.T) {
+        Vec4<T>::load(dqb + (size_t)t * p.C, gq[d]);
+        Vec4<T>::load(dkb + (size_t)t * p.C, gk[d]);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) gq[d][c] = gk[d][c] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int d = 0; d < 4; ++d) {
+      const int t = t1 - 1 - d;
+      if (t >= 0) {
+        Vec4<T>::load(xb + (size_t)t * p.ld_x, xw[d]);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) xw[d][c] = 0.f;
+      }
+    }
+    for (int t = t1 - 1; t >= t0; --t) {
+      float dqv[4], dkv[4], dx[4];
+      Vec4<T>::load(dqb + (size_t)t * p.C, dqv);
+      Vec4<T>::load(dkb + (size_t)t * p.C, dkv);
+      float xn[4];  // x at t-4, for the next step
+      if (t - 4 >= 0) {
+        Vec4<T>::load(xb + (size_t)(t - 4) * p.ld_x, xn);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) xn[c] = 0.f;
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        // tap j multiplies x[t - 3 + j]: its transpose sends d out[t + 3 - j] to x[t]
+        dx[c] = wq[c][3] * dqv[c] + wq[c][2] * gq[0][c] + wq[c][1] * gq[1][c] + wq[c][0] * gq[2][c] +
+                wk[c][3] * dkv[c] + wk[c][2] * gk[0][c] + wk[c][1] * gk[1][c] + wk[c][0] * gk[2][c];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          aq[j][c] += dqv[c] * xw[3 - j][c];
+          ak[j][c] += dkv[c] * xw[3 - j][c];
+        }
+        aq[4][c] += dqv[c];
+        ak[4][c] += dkv[c];
+        gq[2][c] = gq[1][c]; gq[1][c] = gq[0][c]; gq[0][c] = dqv[c];
+        gk[2][c] = gk[1][c]; gk[1][c] = gk[0][c]; gk[0][c] = dkv[c];
+        xw[0][c] = xw[1][c]; xw[1][c] = xw[2][c]; xw[2][c] = xw[3][c]; xw[3][c] = xn[c];
+      }
+      Vec4<T>::store(static_cast<T*>(p.dx) + ((size_t)b * p.T + t) * p.C + c0, dx);
+    }
+    float* row = p.partials + ((size_t)b * nch + ch) * 10 * p.C;
+#pragma unroll
+    for (int j = 0; j < 5; ++j) {
+      *reinterpret_cast<float4*>(row + (size_t)j * p.C + c0) = make_float4(aq[j][0], aq[j][1], aq[j][2], aq[j][3]);
+      *reinterpret_cast<float4*>(row + (size_t)(5 + j) * p.C + c0) = make_float4(ak[j][0], ak[j][1], ak[j][2], ak[j][3]);
+    }
+  }
+}
+
+static int conv_grid(const long total) {
+  const long want = (total + 255) / 256, cap = (long)sm_count() * 8;
+  return (int)(want < 1 ? 1 : (want > cap ? cap : want));
+}
+
+cudaError_t launch_layer_conv(int dtype, const LayerConvParams& p, cudaStream_t st) {
+  const long total = (long)p.B * ((p.T + LAYER_CONV_CHUNK - 1) / LAYER_CONV_CHUNK) * (p.C / 4);
+  if (dtype == 1)
+    ttt_layer_conv_kernel<__nv_bfloat16><<<conv_grid(total), 256, 0, st>>>(p);
+  else
+    ttt_layer_conv_kernel<float><<<conv_grid(total), 256, 0, st>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_layer_conv_bwd(int dtype, const LayerConvBwdParams& p, cudaStream_t st) {
+  const int nch = (p.T + LAYER_CONV_CHUNK - 1) / LAYER_CONV_CHUNK;
+  const long total = (long)p.B * nch * (p.C / 4);
+  if (dtype == 1)
+    ttt_layer_conv_bwd_kernel<__nv_bfloat16><<<conv_grid(total), 256, 0, st>>>(p);
+  else
+    ttt_layer_conv_bwd_kernel<float><<<conv_grid(total), 256, 0, st>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  // sum the chunks' partial rows [10 C] in a fixed order: first 5 C -> the q parameters, last 5 C -> the k parameters
+  ttt_layer_epilogue_bwd_reduce_kernel<<<(10 * p.C + 31) / 32, 256, 0, st>>>(p.partials, p.B * nch, 5 * p.C,
+                                                                            p.dparams_q, p.dparams_k);
+  return cudaGetLastError();
+}
+
 }  // namespace ttt

@@ -11,8 +11,9 @@ What runs where:
   * permute back + post LayerNorm + gelu gate: `ttt_layer_epilogue` (one pass);
   * output projection: library GEMM.
 Under autograd the same kernels run with their gradient kernels (`ttt_layer_prologue_backward`,
-`ttt_layer_epilogue_backward`) joined by torch autograd, so the layer trains end to end (separate q / k projections;
-the shared-QK convolution layout is inference-only).
+`ttt_layer_epilogue_backward`) joined by torch autograd, so the layer trains end to end; with the shared-QK layout the
+two convolutions are a step of their own there (`ttt_layer_qk_conv`, `ttt_layer_qk_conv_backward`) instead of being
+applied inside the prologue kernel.
 There is no PyTorch fallback for the layer kernels: without the CUDA library the calls raise.
 """
 
@@ -139,13 +140,82 @@ class _PrologueFn(torch.autograd.Function):
         base = dproj.data_ptr()
         col = lambda c: C.c_void_p(base + c * esz)  # noqa: E731
         stream = C.c_void_p(torch.cuda.current_stream(lr.device).cuda_stream)
+        dxq, dxk, dxv, dlr = (t.contiguous() for t in (dxq, dxk, dxv, dlr))  # named: copies must outlive the launch
         with torch.cuda.device(lr.device):
             _lib.check(lib.ttt_layer_prologue_backward(
-                C.byref(d), _ptr(dxq.contiguous()), _ptr(dxk.contiguous()), _ptr(dxv.contiguous()),
-                _ptr(dlr.contiguous()), _ptr(lr), start_idx, _POS[cfg.pos_encoding], cfg.rope_theta, cfg.base_lr,
+                C.byref(d), _ptr(dxq), _ptr(dxk), _ptr(dxv),
+                _ptr(dlr), _ptr(lr), start_idx, _POS[cfg.pos_encoding], cfg.rope_theta, cfg.base_lr,
                 col(cols["q"]), col(cols["k"]), col(cols["v"]), N, col(cols["lr"]), N, N - cols["lr"], stream))
         dbias = dproj[..., cols["lr"]:cols["lr"] + H].float().sum(dim=(0, 1)).to(dt).reshape(H, 1)
         return dproj, dbias, None, None, None
+
+
+def _taps4(w: torch.Tensor, dt) -> torch.Tensor:
+    """Depthwise convolution weight [C,1,K] or [C,K] (K <= 4) -> [C,4], taps aligned to the end (tap j multiplies
+    token t - 3 + j)."""
+    w2 = w.reshape(w.shape[0], -1).to(dt)
+    K = w2.shape[1]
+    if K > 4:
+        raise ValueError(f"convolution kernels of up to 4 taps are supported (got {K})")
+    return torch.nn.functional.pad(w2, (4 - K, 0)).contiguous()
+
+
+class _QkConvFn(torch.autograd.Function):
+    """Shared-QK causal depthwise convolutions as a differentiable step (`ttt_layer_qk_conv` and its gradient
+    `ttt_layer_qk_conv_backward`): xqk [B,T,C] (a column block of the projection output) -> conv_q(xqk), conv_k(xqk)."""
+
+    @staticmethod
+    def forward(ctx, proj, col, C_, wq, bq, wk, bk, cfg):
+        lib = _lib.load()
+        B, T, N = proj.shape
+        dt, dev = proj.dtype, proj.device
+        d = TttDims(B, cfg.num_heads, T, cfg.head_dim, cfg.mini_batch_size, 1, 0.0, _dtype_code(dt))
+        q = torch.empty(B, T, C_, dtype=dt, device=dev)
+        k = torch.empty(B, T, C_, dtype=dt, device=dev)
+        w4q, w4k = _taps4(wq, dt), _taps4(wk, dt)
+        bqc, bkc = bq.to(dt).contiguous(), bk.to(dt).contiguous()
+        x = C.c_void_p(proj.data_ptr() + col * proj.element_size())
+        stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        with torch.cuda.device(dev):
+            _lib.check(lib.ttt_layer_qk_conv(C.byref(d), x, N, _ptr(w4q), _ptr(bqc), _ptr(w4k), _ptr(bkc), _ptr(q),
+                                             _ptr(k), stream))
+        ctx.save_for_backward(proj, w4q, w4k)
+        ctx.meta = (cfg, col, C_, wq.shape, wk.shape, wq.dtype, bq.dtype)
+        return q, k
+
+    @staticmethod
+    def backward(ctx, dq, dk):
+        proj, w4q, w4k = ctx.saved_tensors
+        cfg, col, C_, wq_shape, wk_shape, wdt, bdt = ctx.meta
+        lib = _lib.load()
+        B, T, N = proj.shape
+        dt, dev = proj.dtype, proj.device
+        d = TttDims(B, cfg.num_heads, T, cfg.head_dim, cfg.mini_batch_size, 1, 0.0, _dtype_code(dt))
+        dx = torch.empty(B, T, C_, dtype=dt, device=dev)
+        gq = torch.empty(5 * C_, dtype=torch.float32, device=dev)
+        gk = torch.empty(5 * C_, dtype=torch.float32, device=dev)
+        ws_bytes = lib.ttt_layer_qk_conv_backward_workspace_bytes(C.byref(d))
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        x = C.c_void_p(proj.data_ptr() + col * proj.element_size())
+        stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        dq, dk = dq.contiguous(), dk.contiguous()  # named: a temporary copy must outlive the launch
+        with torch.cuda.device(dev):
+            _lib.check(lib.ttt_layer_qk_conv_backward(C.byref(d), _ptr(dq), _ptr(dk), x, N,
+                                                      _ptr(w4q), _ptr(w4k), _ptr(dx), _ptr(gq), _ptr(gk), _ptr(ws),
+                                                      ws_bytes, stream))
+        dproj = torch.zeros_like(proj)
+        dproj[..., col:col + C_] = dx
+
+        def params(g, shape):
+            K = 1
+            for n in shape[1:]:
+                K *= n
+            dw = g[:4 * C_].reshape(4, C_).t()[:, 4 - K:]  # [C, K], the kernel's own taps
+            return dw.reshape(shape).to(wdt), g[4 * C_:].to(bdt)
+
+        dwq, dbq = params(gq, wq_shape)
+        dwk, dbk = params(gk, wk_shape)
+        return dproj, None, None, dwq, dbq, dwk, dbk, None
 
 
 class _EpilogueFn(torch.autograd.Function):
@@ -176,9 +246,10 @@ class _EpilogueFn(torch.autograd.Function):
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
         w, b = ln_weight.to(dt).contiguous(), ln_bias.to(dt).contiguous()
         stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        dy = dy.contiguous()
         with torch.cuda.device(dev):
             _lib.check(lib.ttt_layer_epilogue_backward(
-                C.byref(d), _ptr(dy.contiguous()), _ptr(inner_out), _ptr(g2d), 0 if g2d is None else g2d.shape[1],
+                C.byref(d), _ptr(dy), _ptr(inner_out), _ptr(g2d), 0 if g2d is None else g2d.shape[1],
                 _ptr(w), _ptr(b), ctx.eps, _ptr(d_inner), _ptr(d_gate), 0 if d_gate is None else d_gate.shape[1],
                 _ptr(dw), _ptr(db), _ptr(ws), ws_bytes, stream))
         dg = None if d_gate is None else d_gate.reshape(ctx.gate_shape)
@@ -282,17 +353,31 @@ def _train_forward(self, x, inner, state, start_idx):
     the gradients of the library GEMMs).  The gate projection is a GEMM of its own here, so that every column of the
     fused projection's gradient is written by exactly one kernel."""
     c = self.config
-    if c.share_qk:
-        raise NotImplementedError("training with the shared-QK convolutions: the prologue's gradient kernel covers "
-                                  "the separate q / k projection layout only")
     B, T, _ = x.shape
     H, hs = c.num_heads, c.hidden_size
-    pad = (-(3 * hs + H)) % 8
-    blocks = [self.q_proj, self.k_proj, self.v_proj, self.learnable_ttt_lr_weight.reshape(H, hs)]
-    if pad:
-        blocks.append(torch.zeros(pad, hs, dtype=x.dtype, device=x.device))
+    if c.share_qk:
+        # shared projection | v | lr logits, then the two convolutions as a step of their own (with its gradient
+        # kernel); the prologue sees the usual q | k | v | lr layout
+        pad0 = (-(2 * hs + H)) % 8
+        blocks = [self.q_proj, self.v_proj, self.learnable_ttt_lr_weight.reshape(H, hs)]
+        if pad0:
+            blocks.append(torch.zeros(pad0, hs, dtype=x.dtype, device=x.device))
+        proj0 = torch.matmul(x, torch.cat(blocks, dim=0).t())
+        qc, kc = _QkConvFn.apply(proj0, 0, hs, self.q_conv_weight, self.q_conv_bias, self.k_conv_weight,
+                                 self.k_conv_bias, c)
+        rest = proj0[..., hs:2 * hs + H]
+        pad = (-(3 * hs + H)) % 8
+        parts = [qc, kc, rest]
+        if pad:
+            parts.append(torch.zeros(B, T, pad, dtype=x.dtype, device=x.device))
+        proj = torch.cat(parts, dim=-1)
+    else:
+        pad = (-(3 * hs + H)) % 8
+        blocks = [self.q_proj, self.k_proj, self.v_proj, self.learnable_ttt_lr_weight.reshape(H, hs)]
+        if pad:
+            blocks.append(torch.zeros(pad, hs, dtype=x.dtype, device=x.device))
+        proj = torch.matmul(x, torch.cat(blocks, dim=0).t())
     cols = {"q": 0, "k": hs, "v": 2 * hs, "lr": 3 * hs}
-    proj = torch.matmul(x, torch.cat(blocks, dim=0).t())
     xq, xk, xv, lr = _PrologueFn.apply(proj, self.learnable_ttt_lr_bias, c, cols, start_idx)
     te = torch.clamp_min(self.token_idx + self.learnable_token_idx, 0.0)
     token_eta = te.repeat((T + c.mini_batch_size - 1) // c.mini_batch_size)[:T].to(x.dtype)
