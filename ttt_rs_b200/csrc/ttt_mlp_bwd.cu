@@ -629,16 +629,9 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     TRM(3)
     // ---- state at the start of this stage: undo the stage's updates (W1 first: X2 depends on it)
     update_w1(1.f);
-    __syncthreads();
-    forward_first_layer(std::true_type{});  // x2 (and the GELU derivatives) of this stage, needed to undo the second layer's update
-    update_w2(1.f);
-    __syncthreads();
-    TRM(4)
-    // ---- forward intermediates of the stage
-    forward_second_layer(std::false_type{}, nullptr, nullptr);
-    TRM(5)
+    // (in the same phase, since neither depends on the state: the eta matrix and a1 = Q K^T)
     for_c([&](int i, int j) { S.eta[i][j] = (j <= i) ? S.te[i] * S.lr[j] : 0.f; });
-    tile_mma<false, CS, CS>(ma1, 1.f, noepi, prod<F>(sq, tr(sk)));                 // a1 = Q K^T
+    tile_mma<false, CS, CS>(ma1, 1.f, noepi, prod<F>(sq, tr(sk)));
     __syncthreads();
     for_c([&](int i, int j) {
       const float a = (j <= i) ? S.a1[i][j] : 0.f, m = S.eta[i][j] * (1.f + a);
@@ -646,7 +639,13 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       S.m1[i][j] = __float2bfloat16_rn(m);
       S.m1n[i][j] = __float2bfloat16_rn(-m);
     });
+    forward_first_layer(std::true_type{});  // x2 (and the GELU derivatives) of this stage, needed to undo the second layer's update
+    update_w2(1.f);
     __syncthreads();
+    TRM(4)
+    // ---- forward intermediates of the stage
+    forward_second_layer(std::false_type{}, nullptr, nullptr);
+    TRM(5)
     tile_mma<false, CS, E>(none, 1.f, [&](int i, int j, float x, float y) {          // z1b = Q W1 - M1 g1 + b1; x2b = gelu
       float f0, f1, a0, a1, c0, c1;
       gelu_all<false>(x + b1[j], f0, a0, c0);
@@ -656,6 +655,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     }, prod<F>(sq, sw1), prod<CS>(sm1n, sg1));
     __syncthreads();
     tile_mma<false, CS, CS>(ma2, 1.f, noepi, prod<E>(sx2b, tr(sx2)));              // a2 = x2b x2^T
+    tile_mma<false, CS, F>(mdq, 1.f, noepi, prod<E>(sx2b, sw2));                   // z2b = x2b W2 ... (float32 tile)
     __syncthreads();
     for_c([&](int i, int j) {
       const float a = (j <= i) ? S.a2[i][j] : 0.f, m = S.eta[i][j] * (1.f + a);
@@ -664,9 +664,9 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       S.m2n[i][j] = __float2bfloat16_rn(-m);
     });
     __syncthreads();
-    tile_mma<false, CS, F>(none, 1.f, [&](int i, int j, float x, float y) {          // z2b = x2b W2 - M2 g2 + b2
+    tile_mma<true, CS, F>(mdq, 1.f, [&](int i, int j, float x, float y) {           // ... - M2 g2 + b2
       *reinterpret_cast<float2*>(&S.z2b[i][j]) = make_float2(x + b2[j], y + b2[j + 1]);
-    }, prod<E>(sx2b, sw2), prod<CS>(sm2n, sg2));
+    }, prod<CS>(sm2n, sg2));
     __syncthreads();
 
     TRM(6)
@@ -767,7 +767,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       const float2 gl = *reinterpret_cast<const float2*>(&S.gl1[r][c]);
       *d = make_float2(d->x - S.ell[r] * gl.x, d->y - S.ell[r] * gl.y);
     });
-    __syncthreads();
+    // (no barrier: step 6 reads and writes none of what the two loops above touch)
     TRM(10)
     // ---- 6. g1 = h o gelu'(z1), h = g2 W2^T (recomputed):  dz1 = dg1 o h o gelu''(z1) (t4),  dh = dg1 o gelu'(z1) (t2)
     tile_mma<false, CS, E>(none, 1.f, [&](int i, int j, float hx, float hy) {
