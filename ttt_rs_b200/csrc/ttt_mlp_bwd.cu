@@ -395,6 +395,9 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
   // When the forward has already filled the workspace (pass1_done) the chains start at rank NCH.
   const int rank0 = p.pass1_done ? p.NCH : 0;
   const int nitems = p.nstreams * (2 * p.NCH - rank0);
+#ifdef TTT_MLP_TRACE
+  unsigned long long tr_acc[16] = {0}, tr_last = 0;
+#endif
   while (true) {
     if (tid == 0) s_item = atomicAdd(&p.sched[0], 1);
     __syncthreads();
@@ -487,7 +490,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
   const float te_last = S.te[CS - 1];
 // per-phase cycle counts of block 0 (instrumented builds only; written to the status words after the walk)
 #ifdef TTT_MLP_TRACE
-  unsigned long long tr_acc[16] = {0}, tr_last = clock64();
+  tr_last = clock64();
 #define TRM(i) { __syncthreads(); const unsigned long long n_ = clock64(); tr_acc[i] += n_ - tr_last; tr_last = n_; }
 #else
 #define TRM(i)
