@@ -600,34 +600,50 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
 
   // ============================== pass 2: backward walk ==============================
   float(*const colpart)[2 * HD] = reinterpret_cast<float(*)[2 * HD]>(&S.z1b[0][0]);  // only while z1b is not live
+  // The inputs of a stage (one 16-byte piece per thread and tile, the lr row, the biases at the start of the stage:
+  // those were saved on the way forward, they are not recovered by undoing the update, since the forward takes its
+  // column sums in float32 and the operand tiles are bf16) are fetched into registers while the previous stage
+  // writes its outputs, and put in place when the stage begins.
+  struct StageIn {
+    uint4 g1v, in, g2v;
+    float bias, lr;
+  };
+  auto fetch = [&](const int s) {
+    StageIn v;
+    const size_t r0 = (row_base + (size_t)s * CS) * HD;
+    v.g1v = __ldcg(reinterpret_cast<const uint4*>(g1p_all + (size_t)s * CS * E) + tid);
+    int r, c;
+    tile_piece(tid & 127, r, c);
+    const int which = tid >> 7;
+    const T* src = static_cast<const T*>(which == 0 ? p.xq : which == 1 ? p.xk : which == 2 ? p.xv : p.d_out) + r0;
+    v.in = *reinterpret_cast<const uint4*>(src + r * HD + c);
+    v.g2v = make_uint4(0u, 0u, 0u, 0u);
+    if (tid < 128) v.g2v = __ldcg(reinterpret_cast<const uint4*>(g2p_all + (size_t)s * CS * F) + tid);
+    v.bias = tid < E + F ? __ldcg(bst + (size_t)s * (E + F) + tid) : 0.f;
+    v.lr = tid < CS ? ld_as_float<T>(p.lr, row_base + (size_t)s * CS + tid) : 0.f;
+    return v;
+  };
+  auto commit = [&](const StageIn& v) {
+    int r, c;
+    tile_piece(tid & 127, r, c);
+    const int which = tid >> 7;
+    bf(*dst)[FB] = which == 0 ? S.q : which == 1 ? S.k : which == 2 ? S.v : S.dO;
+    *reinterpret_cast<uint4*>(&dst[r][c]) = v.in;
+    *reinterpret_cast<uint4*>(&S.t1[tid >> 5][8 * (tid & 31)]) = v.g1v;
+    if (tid < 128) *reinterpret_cast<uint4*>(&S.g2p[r][c]) = v.g2v;
+    if (tid < E) b1[tid] = v.bias;
+    else if (tid < E + F) b2[tid - E] = v.bias;
+    if (tid < CS) {
+      S.lr[tid] = v.lr;
+      S.ell[tid] = te_last * v.lr;
+    }
+  };
+  StageIn nxt;
+  if (!pass1) nxt = fetch(s_hi - 1);
   if (!pass1)
   for (int s = s_hi - 1; s >= s_lo; --s) {
     const size_t r0 = (row_base + (size_t)s * CS) * HD;
-    {
-      // the stage's inputs, one 16-byte piece per thread and tile
-      const uint4 g1v = __ldcg(reinterpret_cast<const uint4*>(g1p_all + (size_t)s * CS * E) + tid);
-      int r, c;
-      tile_piece(tid & 127, r, c);
-      const int which = tid >> 7;
-      const T* src = static_cast<const T*>(which == 0 ? p.xq : which == 1 ? p.xk : which == 2 ? p.xv : p.d_out) + r0;
-      bf(*dst)[FB] = which == 0 ? S.q : which == 1 ? S.k : which == 2 ? S.v : S.dO;
-      const uint4 in = *reinterpret_cast<const uint4*>(src + r * HD + c);
-      uint4 g2v = make_uint4(0u, 0u, 0u, 0u);
-      if (tid < 128) g2v = __ldcg(reinterpret_cast<const uint4*>(g2p_all + (size_t)s * CS * F) + tid);
-      *reinterpret_cast<uint4*>(&dst[r][c]) = in;
-      *reinterpret_cast<uint4*>(&S.t1[tid >> 5][8 * (tid & 31)]) = g1v;
-      if (tid < 128) *reinterpret_cast<uint4*>(&S.g2p[r][c]) = g2v;
-      // the biases at the start of the stage were saved on the way forward (they are not recovered by undoing the
-      // update: the forward takes its column sums in float32, the operand tiles are bf16)
-      if (tid < E + F) {
-        const float v = __ldcg(bst + (size_t)s * (E + F) + tid);
-        if (tid < E) b1[tid] = v; else b2[tid - E] = v;
-      }
-    }
-    if (tid < CS) {
-      S.lr[tid] = ld_as_float<T>(p.lr, row_base + (size_t)s * CS + tid);
-      S.ell[tid] = te_last * S.lr[tid];
-    }
+    commit(nxt);
     __syncthreads();
     TRM(3)
     // ---- state at the start of this stage: undo the stage's updates (W1 first: X2 depends on it)
@@ -871,6 +887,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     __syncthreads();
     add_colsum(db2, &S.dz2[0][0], F, FB, 1.f);
     add_colsum(db1, &S.t4[0][0], E, EB, 1.f);
+    if (s > s_lo) nxt = fetch(s - 1);
     for_f2([&](int r, int c) {  // dq += dO;  dk -= dT;  dv = dT  (gl1 holds d target)
       const float2 a = *reinterpret_cast<const float2*>(&dq[r][c]), o = ldb2(&S.dO[r][c]);
       const float2 b = *reinterpret_cast<const float2*>(&S.dk[r][c]), dT = *reinterpret_cast<const float2*>(&S.gl1[r][c]);
