@@ -65,6 +65,15 @@ int ttt_b200_abi_version(void);
 const char* ttt_b200_status_string(int status);
 const char* ttt_b200_last_error(void);
 
+/* Diagnostic knob for the persistent TTT-Linear backward (no counterpart in the reference, whose streaming kernels
+ * spin without a limit: rust/fused/src/linear_fused_tile/streaming/d2d/kernel.rs:123-145).  Blocks of that kernel
+ * wait, with an iteration limit, for the hand-off of the later chunk of their stream; when the limit is reached they
+ * write {TTT_ERR_TIMEOUT, 15, block, stage} to `status` and return.  `poll_limit` replaces the limit (0 restores the
+ * default, 2^24 polls of about 100 ns); `first_item` > 0 makes the launch skip that many work items, which -- set to
+ * batch*heads -- leaves every remaining item waiting for a hand-off nobody publishes, so that a test can watch the
+ * wait give up.  Process-wide; affects launches issued after the call.  Leave at (0, 0) in production. */
+void ttt_b200_debug_handoff(uint32_t poll_limit, int32_t first_item);
+
 /* Number of checkpoints per (batch, head) stream: ceil((T / CS) / K)  (forward/launch.rs:221-223). */
 int64_t ttt_linear_num_checkpoints(const ttt_dims* d);
 /* Bytes of the two saved-state buffers the forward fills and the backward reads back (the role of the reference's

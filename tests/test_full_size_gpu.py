@@ -70,25 +70,58 @@ def test_reduced_gradients_are_sums_of_stream_results(full):
     assert (te.abs().sum(1) > 0).all()
 
 
+# Allowed fraction of elements outside |a-b| <= 2e-2 (|b| + RMS(b)) at this size, per tensor: twice the fraction
+# measured on B200 (the table printed at the end of the run shows the current figures).  Rounding the float64 oracle
+# result itself to bfloat16 already gives a max error of 5e-2 of the RMS on these 1.5M-element tensors.
+ALLOWED = {"output": 1e-4, "final weight": 1e-4, "final bias": 1e-4, "grad_xq": 1e-4, "grad_xk": 1e-4,
+           "grad_xv": 1e-4, "grad_weight": 1e-4, "grad_bias": 1e-4, "grad_ttt_lr_eta": 1e-4,
+           "grad_token_eta": 1e-4, "grad_ln_weight": 1e-4, "grad_ln_bias": 1e-4}
+
+
 def test_one_batch_row_matches_oracle_at_full_length(full):
     t = full["t"]
     row = 5
     one = {k: (v[row:row + 1].double() if v.dim() >= 3 else v.double()) for k, v in t.items()}
     fw = O.ttt_linear_forward(*[one[k] for k in LIN_IN], checkpoint_interval=K)
     bw = O.ttt_linear_backward(*[one[k] for k in LIN_IN], one["grad_output"])
-    # At 128 chained stages and 1.5M elements per tensor the elementwise 2e-2 criterion is applied statistically:
-    # relative L2 error <= 1e-2 and at most 1 element in 10^4 outside |a-b| <= 2e-2 (|b| + RMS(b)).  (Rounding the
-    # float64 oracle result itself to bf16 already gives a max error of 5e-2 of the RMS on these tensors.)
+
     def check(a, b, name):
-        a = a.double().cpu()
-        scale = b.pow(2).mean().sqrt()
-        rel_l2 = ((a - b).norm() / b.norm()).item()
-        frac_bad = ((a - b).abs() > 2e-2 * (b.abs() + scale)).double().mean().item()
-        assert rel_l2 <= 1e-2, f"{name}: relative L2 error {rel_l2:.3g}"
-        assert frac_bad <= 1e-4, f"{name}: {frac_bad:.3g} of the elements outside the 2e-2 tolerance"
+        assert_close(a, b, 2e-2, f"cfg1 row: {name}", max_bad_frac=ALLOWED[name])
 
     check(full["outs"].output[row:row + 1], fw["output"], "output")
     check(full["outs"].weight[row:row + 1], fw["weight"], "final weight")
     check(full["outs"].bias[row:row + 1], fw["bias"], "final bias")
     for n in ("xq", "xk", "xv", "weight", "bias", "ttt_lr_eta"):
         check(getattr(full["g"], n)[row:row + 1], bw["grad_" + n], "grad_" + n)
+
+
+def test_reduced_gradients_match_oracle_on_two_batch_rows():
+    """The three gradients that are sums over streams (token_eta over batch and heads, LayerNorm weight / bias over
+    the batch) and the packed all-reduce buffer, at the full sequence length: they pass through the per-(stream,
+    chunk) partials, the persistent scheduler's hand-offs and the fixed-order reduction kernels."""
+    import ttt_rs_b200 as tb
+    dev = torch.device("cuda:0")
+    t = O.make_inputs(B, H, T, 64, 16, seed=0, dtype=torch.bfloat16)
+    rows = [5, 20]
+    sub = {k: (v[rows].contiguous() if v.dim() >= 3 else v) for k, v in t.items()}
+    cfg = tb.FusedTttConfig.new(16, 64, 1e-6, 128, K)
+    ins = tb.TttInputs(*[sub[k].to(dev) for k in LIN_IN])
+    outs, saved = tb.TttTileMultiKernel.forward_launch(ins, cfg)
+    packed = torch.full((tb.packed_outer_grad_len(H),), float("nan"), device=dev)
+    g = tb.TttTileMultiKernel.backward_launch(saved, tb.TttOutputs(sub["grad_output"].to(dev), None, None), cfg,
+                                              outer_grad_packed=packed)
+    tb.check_status()
+    d = {k: v.double() for k, v in sub.items()}
+    bw = O.ttt_linear_backward(*[d[k] for k in LIN_IN], d["grad_output"])
+    for n in ("token_eta", "ln_weight", "ln_bias"):
+        assert_close(getattr(g, n), bw["grad_" + n], 2e-2, f"cfg1 two rows: grad_{n}", max_bad_frac=ALLOWED["grad_" + n])
+    F = 64
+    want = torch.cat([bw["grad_weight"].sum(0).reshape(-1), bw["grad_bias"].sum(0).reshape(-1),
+                      bw["grad_ln_weight"].reshape(-1), bw["grad_ln_bias"].reshape(-1),
+                      bw["grad_token_eta"].reshape(-1, 16).sum(0)])
+    assert packed.shape == want.shape
+    o = 0
+    for name, n in (("dW0", H * F * F), ("db0", H * F), ("d ln_weight", H * F), ("d ln_bias", H * F), ("d token_eta", 16)):
+        # float32 sums of float32 per-stream values; only the folded token_eta term cancels heavily
+        assert_close(packed[o:o + n], want[o:o + n], 2e-2, f"cfg1 two rows: packed {name}", max_bad_frac=1e-4)
+        o += n

@@ -1,0 +1,107 @@
+"""Long-context TTT-Linear at the 1.3B layer shape (32 heads x 64, bf16, checkpoint interval 16; sequence lengths
+8192 and 32768 = 512 and 2048 chained mini-batches).  The reference's own tests stop at T = 2048
+(rust/fused/src/linear_fused_tile/tests.rs:95-102), so at these lengths the float64 oracle is the only judge.  The
+backward walks the state back from each checkpoint with the saved gradient tiles; these cases are the evidence that
+its rounding drift stays bounded by one checkpoint interval however long the chain is."""
+
+import pytest
+import torch
+
+from conftest import assert_close
+from oracle import ttt_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+LIN_IN = ("xq", "xk", "xv", "weight", "bias", "token_eta", "ttt_lr_eta", "ln_weight", "ln_bias")
+PER_STREAM = ("xq", "xk", "xv", "weight", "bias", "ttt_lr_eta")
+H, K = 32, 16
+# allowed fraction outside the 2e-2 criterion: twice what was measured on B200 (see the table at the end of the run)
+ALLOWED = 2e-4
+
+
+def _run(t, dev, packed=None):
+    import ttt_rs_b200 as tb
+    cfg = tb.FusedTttConfig.new(16, 64, 1e-6, 128, K)
+    ins = tb.TttInputs(*[t[k].to(dev) for k in LIN_IN])
+    outs, saved = tb.TttTileMultiKernel.forward_launch(ins, cfg)
+    g = tb.TttTileMultiKernel.backward_launch(saved, tb.TttOutputs(t["grad_output"].to(dev), None, None), cfg,
+                                              outer_grad_packed=packed)
+    tb.check_status()
+    return outs, g
+
+
+def _stream(t, b, h):
+    """Inputs of one (batch, head) stream as a B=1, H=1 problem in float64."""
+    one = {}
+    for k, v in t.items():
+        if k in ("ln_weight", "ln_bias"):
+            one[k] = v[h:h + 1].double()
+        elif v.dim() >= 3:
+            one[k] = v[b:b + 1, h:h + 1].double()
+        else:
+            one[k] = v.double()
+    return one
+
+
+def _check_stream(outs, g, t, b, h, tag):
+    one = _stream(t, b, h)
+    fw = O.ttt_linear_forward(*[one[k] for k in LIN_IN], checkpoint_interval=K)
+    bw = O.ttt_linear_backward(*[one[k] for k in LIN_IN], one["grad_output"])
+    sl = (slice(b, b + 1), slice(h, h + 1))
+    assert_close(outs.output[sl], fw["output"], 2e-2, f"{tag}: output", max_bad_frac=ALLOWED)
+    assert_close(outs.weight[sl], fw["weight"], 2e-2, f"{tag}: final weight", max_bad_frac=ALLOWED)
+    assert_close(outs.bias[sl], fw["bias"], 2e-2, f"{tag}: final bias", max_bad_frac=ALLOWED)
+    for n in PER_STREAM:
+        assert_close(getattr(g, n)[sl], bw["grad_" + n], 2e-2, f"{tag}: grad_{n}", max_bad_frac=ALLOWED)
+
+
+def test_t8192_all_streams_finite_independent_and_sampled_streams_match_oracle():
+    """B=8 H=32 T=8192 in one launch: every result finite, a batch-row subset bit-identical when run alone, and three
+    streams (first, middle, last of the grid) against the float64 oracle over all 512 stages."""
+    dev = torch.device("cuda:0")
+    B, T = 8, 8192
+    t = O.make_inputs(B, H, T, 64, 16, seed=4, dtype=torch.bfloat16)
+    outs, g = _run(t, dev)
+    assert torch.isfinite(outs.output.float()).all()
+    for n in LIN_IN:
+        assert torch.isfinite(getattr(g, n).float()).all(), n
+    rows = [2, 7]
+    sub = {k: (v[rows].contiguous() if v.dim() >= 3 else v) for k, v in t.items()}
+    o2, g2 = _run(sub, dev)
+    assert torch.equal(o2.output, outs.output[rows])
+    for n in PER_STREAM:
+        assert torch.equal(getattr(g2, n), getattr(g, n)[rows]), n
+    for b, h in ((0, 0), (3, 17), (7, 31)):
+        _check_stream(outs, g, t, b, h, f"T=8192 stream ({b},{h})")
+
+
+def test_t8192_reduced_gradients_of_one_batch_row_match_oracle():
+    """One batch row with all 32 heads at T=8192: the gradients that are sums over streams and mini-batches
+    (token_eta, LayerNorm weight / bias) and the packed buffer, against the oracle on the same 32 streams."""
+    import ttt_rs_b200 as tb
+    dev = torch.device("cuda:0")
+    T = 8192
+    t = O.make_inputs(1, H, T, 64, 16, seed=5, dtype=torch.bfloat16)
+    packed = torch.full((tb.packed_outer_grad_len(H),), float("nan"), device=dev)
+    outs, g = _run(t, dev, packed)
+    d = {k: v.double() for k, v in t.items()}
+    bw = O.ttt_linear_backward(*[d[k] for k in LIN_IN], d["grad_output"])
+    for n in ("token_eta", "ln_weight", "ln_bias"):
+        assert_close(getattr(g, n), bw["grad_" + n], 2e-2, f"T=8192 one row: grad_{n}", max_bad_frac=ALLOWED)
+    F = 64
+    o = H * F * F + H * F
+    assert_close(packed[o:o + H * F], bw["grad_ln_weight"].reshape(-1), 2e-2, "T=8192 one row: packed d ln_weight",
+                 max_bad_frac=ALLOWED)
+    assert_close(packed[:H * F * F], bw["grad_weight"].sum(0).reshape(-1), 2e-2, "T=8192 one row: packed dW0",
+                 max_bad_frac=ALLOWED)
+
+
+def test_t32768_sampled_streams_match_oracle():
+    """T=32768 (2048 chained stages, 128 checkpoint intervals) on one batch row: two streams against the oracle."""
+    dev = torch.device("cuda:0")
+    T = 32768
+    t = O.make_inputs(1, H, T, 64, 16, seed=6, dtype=torch.bfloat16)
+    outs, g = _run(t, dev)
+    assert torch.isfinite(outs.output.float()).all()
+    for b, h in ((0, 5), (0, 30)):
+        _check_stream(outs, g, t, b, h, f"T=32768 stream ({b},{h})")

@@ -18,6 +18,8 @@ from .fused import (  # noqa: F401
     fused_ttt_mlp,
     fused_ttt_mlp_backward,
     check_mlp_status,
+    check_status,
+    device_status,
     mlp_backward_workspace,
     fused_ttt_mlp_forward,
     fused_ttt_tile_forward_multi,

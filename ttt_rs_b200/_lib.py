@@ -50,6 +50,7 @@ SYMBOLS = {
     "ttt_b200_abi_version": (C.c_int, []),
     "ttt_b200_status_string": (C.c_char_p, [C.c_int]),
     "ttt_b200_last_error": (C.c_char_p, []),
+    "ttt_b200_debug_handoff": (None, [C.c_uint32, C.c_int32]),
     "ttt_linear_num_checkpoints": (C.c_int64, [_DP]),
     "ttt_linear_weight_ckpt_bytes": (C.c_size_t, [_DP]),
     "ttt_linear_bias_ckpt_bytes": (C.c_size_t, [_DP]),

@@ -2,6 +2,7 @@
 // Signatures and their reference counterparts are documented in include/ttt_b200.h.
 #include <cstdarg>
 #include <cstdio>
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
@@ -11,6 +12,12 @@
 namespace {
 
 thread_local char g_err[512] = "";
+
+// Diagnostic knobs of the persistent backward (ttt_b200_debug_handoff): poll limit of the hand-off wait and an offset
+// added to the work-item numbers.
+constexpr uint32_t kHandoffPollsDefault = 1u << 24;
+std::atomic<uint32_t> g_handoff_polls{kHandoffPollsDefault};
+std::atomic<int32_t> g_item_base{0};
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -165,6 +172,11 @@ const char* ttt_b200_status_string(int s) {
 }
 
 const char* ttt_b200_last_error(void) { return g_err; }
+
+void ttt_b200_debug_handoff(uint32_t poll_limit, int32_t first_item) {
+  g_handoff_polls.store(poll_limit == 0 ? kHandoffPollsDefault : poll_limit);
+  g_item_base.store(first_item < 0 ? 0 : first_item);
+}
 
 int64_t ttt_linear_num_checkpoints(const ttt_dims* d) {
   if (check_dims(d) != TTT_OK) return -1;
@@ -325,6 +337,8 @@ int ttt_linear_backward_state_grads(const ttt_dims* d, const void* xq, const voi
   p.CH = kBwdChunkStages;
   p.NCH = wl.nch;
   p.nstreams = d->batch * d->heads;
+  p.handoff_polls = g_handoff_polls.load();
+  p.item_base = g_item_base.load();
   p.status = static_cast<uint32_t*>(status);
   p.H = d->heads;
   p.T = d->seq_len;

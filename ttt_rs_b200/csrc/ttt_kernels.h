@@ -42,6 +42,9 @@ struct LinBwdParams {
   int* sched;       // workspace: [0] next work item, [1 + stream] chunks of the stream finished so far (zeroed per launch)
   float* handoff;   // workspace: [B*H][2*F*F + F] W^T, dW^T (register layout) and db handed from chunk to chunk
   int CH, NCH, nstreams;  // stages per chunk, chunks per stream, B*H
+  uint32_t handoff_polls;  // iteration limit of the wait for another chunk's hand-off (each poll sleeps ~100 ns)
+  int item_base;           // added to every work-item number (0 in normal use; the wait-limit test starts past the
+                           // items that would publish the first hand-offs, so that a wait runs out)
   float* part_ln;   // workspace: [B*H][NCH][2][F] per-(stream, chunk) partial LN gradients (weight, bias)
   float* part_te;   // workspace: [B*H][T] per-stream token_eta gradient terms
   float* part_w;    // workspace: [B*H][F*F + F] float32 dW, db per stream (for the packed reduction)

@@ -145,7 +145,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
   while (!failed) {
     if (tid == 0) s_item = atomicAdd(&p.sched[0], 1);
     __syncthreads();
-    const int item = s_item;
+    const int item = s_item + p.item_base;
     __syncthreads();
     if (item >= nitems) break;
     const int crank = item / p.nstreams;  // 0 = last chunk of the sequence
@@ -187,7 +187,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       if (tid == 0) {
         ok = 0;
         const volatile int* flag = p.sched + 1 + stream;
-        for (uint32_t it = 0; it < (1u << 24); ++it) {
+        for (uint32_t it = 0; it < p.handoff_polls; ++it) {
           if (*flag >= crank) {
             ok = 1;
             break;
@@ -199,6 +199,8 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       if (__syncthreads_or(ok ? 0 : 1)) {
         failed = true;
         if (tid == 0) report_timeout(p.status, 15, s_hi);
+        // the loads of stage s_hi are in flight into this block's shared memory: let them land before leaving
+        mbar_wait_bounded(bar0 + 8 * (n % SM::NSLOT), (n / SM::NSLOT) & 1);
         break;
       }
 #pragma unroll

@@ -20,8 +20,9 @@ torch is used for device memory and streams only; all arithmetic happens in libt
 from __future__ import annotations
 
 import ctypes as C
+import threading
 from dataclasses import dataclass, fields
-from typing import Optional, Tuple
+from typing import Dict, Optional, Tuple
 
 import numpy as np
 import torch
@@ -30,6 +31,56 @@ from . import _lib
 from ._lib import TttDims, TttError
 
 _DTYPES = {torch.float32: _lib.TTT_F32, torch.bfloat16: _lib.TTT_BF16}
+
+# --------------------------------------------------------------------------------------------
+# device-side status words
+# --------------------------------------------------------------------------------------------
+# One 16-word int32 buffer per device, handed to every launch.  A kernel whose bounded wait runs out writes
+# {TTT_ERR_TIMEOUT, where, block, stage} there by compare-and-swap from zero and returns early, so the first report
+# on a device sticks until `check_status` has read (and cleared) it, however many launches follow.
+_STATUS_WORDS = 16
+_status_lock = threading.Lock()
+_status_buffers: Dict[Tuple[str, int], torch.Tensor] = {}
+
+
+def device_status(device) -> torch.Tensor:
+    """The status words of `device` (created zeroed on first use).  Shared by all launches on that device."""
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise TttError(_lib.TTT_ERR_CUDA, "status words live on a CUDA device")
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (device.type, idx)
+    with _status_lock:
+        buf = _status_buffers.get(key)
+        if buf is None:
+            buf = torch.zeros(_STATUS_WORDS, dtype=torch.int32, device=torch.device("cuda", idx))
+            _status_buffers[key] = buf
+        return buf
+
+
+def _raise_if_reported(words, what: str = "") -> None:
+    if words[0] != 0:
+        raise TttError(int(words[0]), f"device-side wait timed out{what} (where={words[1]}, block={words[2]}, "
+                                      f"stage={words[3]}): outputs of launches since the last check are not valid")
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise `TttError` if any launch since the last check reported a timed-out device-side wait.
+    `device` None checks every device that has run a launch.  Call it once per step, after the step's work: a kernel
+    that gave up returns early and leaves its outputs unwritten.  The report is cleared when it is raised."""
+    with _status_lock:
+        if device is None:
+            bufs = list(_status_buffers.items())
+        else:
+            device = torch.device(device)
+            idx = device.index if device.index is not None else torch.cuda.current_device()
+            bufs = [(k, v) for k, v in _status_buffers.items() if k == (device.type, idx)]
+    for (kind, idx), buf in bufs:
+        torch.cuda.synchronize(torch.device(kind, idx))
+        words = buf.cpu().tolist()
+        if words[0] != 0:
+            buf.zero_()
+            _raise_if_reported(words, f" on {kind}:{idx}")
 
 
 # --------------------------------------------------------------------------------------------
@@ -72,9 +123,11 @@ class TttInputs:
     ttt_lr_eta: torch.Tensor
     ln_weight: torch.Tensor
     ln_bias: torch.Tensor
+    #: set on the gradients `backward_launch` returns: the status words of the device the launch ran on
+    status: Optional[torch.Tensor] = None
 
     def map(self, fn):
-        return TttInputs(*[fn(getattr(self, f.name)) for f in fields(self)])
+        return TttInputs(*[fn(getattr(self, f.name)) for f in fields(self) if f.name != "status"], status=self.status)
 
 
 @dataclass
@@ -97,6 +150,8 @@ class TttSavedStateMulti:
     ln_bias: torch.Tensor
     weight_checkpoints: torch.Tensor
     bias_checkpoints: torch.Tensor
+    #: status words of the device the forward ran on (see `check_status`)
+    status: Optional[torch.Tensor] = None
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -138,9 +193,9 @@ def _check_inputs(i, wname="weight"):
     _expect("xv", i.xv, (B, H, T, F), dt, dev)
     _expect(wname, getattr(i, wname), (B, H, F, F), dt, dev)
     _expect("bias", i.bias, (B, H, F), dt, dev)
-    if i.token_eta.dim() != 1 or i.token_eta.shape[0] < 1:
-        raise TttError(_lib.TTT_ERR_SHAPE, "token_eta must be [seq_len]")
-    _expect("token_eta", i.token_eta, (i.token_eta.shape[0],), dt, dev)
+    if i.token_eta.dim() != 1 or i.token_eta.shape[0] != T:
+        raise TttError(_lib.TTT_ERR_SHAPE, f"token_eta must be [seq_len] = [{T}], got {tuple(i.token_eta.shape)}")
+    _expect("token_eta", i.token_eta, (T,), dt, dev)
     _expect("ttt_lr_eta", i.ttt_lr_eta, (B, H, T), dt, dev)
     _expect("ln_weight", i.ln_weight, (H, F), dt, dev)
     _expect("ln_bias", i.ln_bias, (H, F), dt, dev)
@@ -148,10 +203,6 @@ def _check_inputs(i, wname="weight"):
 
 class TttTileMultiKernel:
     """The multi-stage tiled TTT-Linear operator: one launch walks every mini-batch of the sequence."""
-
-    #: when set, every launch allocates a 4-word device status buffer and the last one is kept here; call
-    #: `check_status()` after synchronising to surface device-side wait timeouts
-    last_status: Optional[torch.Tensor] = None
 
     @staticmethod
     def forward_launch(inputs: TttInputs, config: FusedTttConfig) -> Tuple[TttOutputs, TttSavedStateMulti]:
@@ -161,8 +212,6 @@ class TttTileMultiKernel:
         inputs = inputs.map(lambda t: t.contiguous())
         d = _dims(inputs.xq, config)
         _check_inputs(inputs)
-        if inputs.token_eta.shape[0] < config.mini_batch_len:
-            raise TttError(_lib.TTT_ERR_SHAPE, "token_eta must hold at least mini_batch_len entries")
         dev = inputs.xq.device
         nck = lib.ttt_linear_num_checkpoints(C.byref(d))
         if nck < 0:
@@ -176,15 +225,16 @@ class TttTileMultiKernel:
         w_ck = torch.empty(lib.ttt_linear_weight_ckpt_bytes(C.byref(d)) // 4, dtype=torch.float32,
                            device=dev).view(B * H * (nck + 1), F, F)
         b_ck = torch.empty(lib.ttt_linear_bias_ckpt_bytes(C.byref(d)), dtype=torch.uint8, device=dev)
-        status = torch.zeros(4, dtype=torch.int32, device=dev)
-        TttTileMultiKernel.last_status = status
-        rc = lib.ttt_linear_forward(
-            C.byref(d), _ptr(inputs.xq), _ptr(inputs.xk), _ptr(inputs.xv), _ptr(inputs.weight), _ptr(inputs.bias),
-            _ptr(inputs.token_eta), _ptr(inputs.ttt_lr_eta), _ptr(inputs.ln_weight), _ptr(inputs.ln_bias),
-            _ptr(output), _ptr(weight_out), _ptr(bias_out), _ptr(w_ck), _ptr(b_ck), _ptr(status), _stream_ptr(dev))
+        status = device_status(dev)
+        with torch.cuda.device(dev):
+            rc = lib.ttt_linear_forward(
+                C.byref(d), _ptr(inputs.xq), _ptr(inputs.xk), _ptr(inputs.xv), _ptr(inputs.weight),
+                _ptr(inputs.bias), _ptr(inputs.token_eta), _ptr(inputs.ttt_lr_eta), _ptr(inputs.ln_weight),
+                _ptr(inputs.ln_bias), _ptr(output), _ptr(weight_out), _ptr(bias_out), _ptr(w_ck), _ptr(b_ck),
+                _ptr(status), _stream_ptr(dev))
         _lib.check(rc)
         saved = TttSavedStateMulti(inputs.xq, inputs.xk, inputs.xv, inputs.weight, inputs.bias, inputs.token_eta,
-                                   inputs.ttt_lr_eta, inputs.ln_weight, inputs.ln_bias, w_ck, b_ck)
+                                   inputs.ttt_lr_eta, inputs.ln_weight, inputs.ln_bias, w_ck, b_ck, status)
         return TttOutputs(output, weight_out, bias_out), saved
 
     @staticmethod
@@ -195,9 +245,6 @@ class TttTileMultiKernel:
         inputs = inputs.map(lambda t: t.contiguous())
         d = _dims(inputs.xq, config)
         _check_inputs(inputs)
-        T = inputs.xq.shape[2]
-        if inputs.token_eta.shape[0] < T:
-            raise TttError(_lib.TTT_ERR_SHAPE, "token_eta must hold one entry per token of the partial mini-batch")
         dev = inputs.xq.device
         output = torch.empty_like(inputs.xq)
         weight_out = inputs.weight if in_place else torch.empty_like(inputs.weight)
@@ -233,8 +280,7 @@ class TttTileMultiKernel:
         g_lnb = torch.empty((H, F), dtype=torch.float32, device=dev)
         ws_bytes = lib.ttt_linear_backward_workspace_bytes(C.byref(d))
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-        status = torch.zeros(4, dtype=torch.int32, device=dev)
-        TttTileMultiKernel.last_status = status
+        status = device_status(dev)
         gw_out = gb_out = None
         if use_state_grads:
             if grad_outputs.weight is not None:
@@ -243,24 +289,22 @@ class TttTileMultiKernel:
             if grad_outputs.bias is not None:
                 gb_out = grad_outputs.bias.contiguous()
                 _expect("grad_outputs.bias", gb_out, (B, H, F), dt, dev)
-        rc = lib.ttt_linear_backward_state_grads(
-            C.byref(d), _ptr(saved.xq), _ptr(saved.xk), _ptr(saved.xv), _ptr(saved.weight_init), _ptr(saved.bias),
-            _ptr(saved.token_eta), _ptr(saved.ttt_lr_eta), _ptr(saved.ln_weight), _ptr(saved.ln_bias),
-            _ptr(saved.weight_checkpoints), _ptr(saved.bias_checkpoints), _ptr(go), _ptr(gw_out), _ptr(gb_out),
-            _ptr(g_xq), _ptr(g_xk),
-            _ptr(g_xv), _ptr(g_w), _ptr(g_b), _ptr(g_lr), _ptr(g_te), _ptr(g_lnw), _ptr(g_lnb),
-            _ptr(outer_grad_packed), _ptr(ws), C.c_size_t(ws_bytes), _ptr(status), _stream_ptr(dev))
+        with torch.cuda.device(dev):
+            rc = lib.ttt_linear_backward_state_grads(
+                C.byref(d), _ptr(saved.xq), _ptr(saved.xk), _ptr(saved.xv), _ptr(saved.weight_init),
+                _ptr(saved.bias), _ptr(saved.token_eta), _ptr(saved.ttt_lr_eta), _ptr(saved.ln_weight),
+                _ptr(saved.ln_bias), _ptr(saved.weight_checkpoints), _ptr(saved.bias_checkpoints), _ptr(go),
+                _ptr(gw_out), _ptr(gb_out), _ptr(g_xq), _ptr(g_xk), _ptr(g_xv), _ptr(g_w), _ptr(g_b), _ptr(g_lr),
+                _ptr(g_te), _ptr(g_lnw), _ptr(g_lnb), _ptr(outer_grad_packed), _ptr(ws), C.c_size_t(ws_bytes),
+                _ptr(status), _stream_ptr(dev))
         _lib.check(rc)
         # the three reduced gradients are produced in float32 and cast back, like backward/launch.rs:423-425
-        return TttInputs(g_xq, g_xk, g_xv, g_w, g_b, g_te.to(dt), g_lr, g_lnw.to(dt), g_lnb.to(dt))
+        return TttInputs(g_xq, g_xk, g_xv, g_w, g_b, g_te.to(dt), g_lr, g_lnw.to(dt), g_lnb.to(dt), status)
 
     @staticmethod
-    def check_status() -> None:
-        st = TttTileMultiKernel.last_status
-        if st is not None:
-            v = st.cpu().tolist()
-            if v[0] != 0:
-                raise TttError(v[0], f"device-side wait timed out (where={v[1]}, block={v[2]}, stage={v[3]})")
+    def check_status(device=None) -> None:
+        """See the module-level `check_status`."""
+        check_status(device)
 
 
 def packed_outer_grad_len(heads: int, head_dim: int = 64, mini_batch: int = 16) -> int:
@@ -380,7 +424,7 @@ class FusedTileMultiTTTLinear(torch.nn.Module):
         L = full * mb
         q = inputs.qkv.slice_seq(range(0, L))
         out, w, b = fused_ttt_tile_forward_multi(
-            q.xq, q.xk, q.xv, state.weight, state.bias, inputs.token_eta, inputs.ttt_lr_eta[:, :, :L],
+            q.xq, q.xk, q.xv, state.weight, state.bias, inputs.token_eta[:L], inputs.ttt_lr_eta[:, :, :L],
             self.inner.ln_weight, self.inner.ln_bias, self._config(F))
         state.weight, state.bias = w, b
         if rem == 0:
@@ -458,13 +502,13 @@ def fused_ttt_mlp_forward(xq, xk, xv, state: TTTMLPState, token_eta, ttt_lr_eta,
         _expect(k, v, shapes[k], dt, dev)
     out = torch.empty_like(ts["xq"])
     new = TTTMLPState(*(torch.empty_like(ts[k]) for k in ("w1", "b1", "w2", "b2")))
-    status = torch.zeros(4, dtype=torch.int32, device=dev)
-    TttTileMultiKernel.last_status = status
-    rc = lib.ttt_mlp_forward(
-        C.byref(d), *[_ptr(ts[k]) for k in ("xq", "xk", "xv", "w1", "b1", "w2", "b2", "token_eta", "ttt_lr_eta",
-                                           "ln_weight", "ln_bias")],
-        _ptr(out), _ptr(new.w1), _ptr(new.b1), _ptr(new.w2), _ptr(new.b2), _ptr(backward_workspace),
-        0 if backward_workspace is None else backward_workspace.numel(), _ptr(status), _stream_ptr(dev))
+    status = device_status(dev)
+    with torch.cuda.device(dev):
+        rc = lib.ttt_mlp_forward(
+            C.byref(d), *[_ptr(ts[k]) for k in ("xq", "xk", "xv", "w1", "b1", "w2", "b2", "token_eta", "ttt_lr_eta",
+                                               "ln_weight", "ln_bias")],
+            _ptr(out), _ptr(new.w1), _ptr(new.b1), _ptr(new.w2), _ptr(new.b2), _ptr(backward_workspace),
+            0 if backward_workspace is None else backward_workspace.numel(), _ptr(status), _stream_ptr(dev))
     _lib.check(rc)
     return out, new
 
@@ -508,23 +552,21 @@ def fused_ttt_mlp_backward(xq, xk, xv, state: TTTMLPState, token_eta, ttt_lr_eta
                 "grad_output")
     names_out = ("grad_xq", "grad_xk", "grad_xv", "grad_w1", "grad_b1", "grad_w2", "grad_b2", "grad_ttt_lr_eta",
                  "grad_token_eta", "grad_ln_weight", "grad_ln_bias")
-    status = torch.zeros(16, dtype=torch.int32, device=dev)
+    status = device_status(dev)
     with torch.cuda.device(dev):
         rc = lib.ttt_mlp_backward(C.byref(d), *[_ptr(ts[k]) for k in names_in], *[_ptr(g[k]) for k in names_out],
                                   _ptr(ws), ws_bytes, 0 if workspace_from_forward is None else 1, _ptr(status),
                                   _stream_ptr(dev))
     _lib.check(rc)
     g["_workspace"] = ws  # keeps the scratch alive until the caller drops the result
-    g["_status"] = status  # {0,..} unless a hand-off wait between work items ran out: see `check_mlp_status`
+    g["_status"] = status  # the device's status words: see `check_status`
     return g
 
 
 def check_mlp_status(grads) -> None:
-    """After synchronising: raise if the TTT-MLP backward that produced `grads` reported a device-side wait timeout
-    (its blocks hand the stream state to one another; every such wait is bounded)."""
-    v = grads["_status"].cpu().tolist()
-    if v[0] != 0:
-        raise TttError(v[0], f"device-side wait timed out (where={v[1]}, block={v[2]}, item={v[3]})")
+    """Raise if a launch on the device that produced `grads` reported a device-side wait timeout (the blocks of the
+    TTT-MLP backward hand the stream state to one another; every such wait is bounded).  Same as `check_status`."""
+    check_status(grads["_status"].device)
 
 
 class _FusedTttMlpFn(torch.autograd.Function):

@@ -288,13 +288,19 @@ class TTT(torch.nn.Module):
         self.learnable_token_idx = torch.nn.Parameter(torch.zeros(c.mini_batch_size, **kw))
         self.post_norm_weight = torch.nn.Parameter(torch.ones(hs, **kw))
         self.post_norm_bias = torch.nn.Parameter(torch.zeros(hs, **kw))
-        self._wcat = None
+        self._wcat, self._wcat_key = None, None
 
     # ---- one GEMM for every projection of x ----------------------------------------------------------------
     def _fused_weight(self):
-        """Rows: q | (k) | v | (g) | lr logits (H rows), padded to a multiple of 8 rows.  Cached; call
-        `invalidate_fused_weight()` after changing a parameter."""
-        if self._wcat is None:
+        """Rows: q | (k) | v | (g) | lr logits (H rows), padded to a multiple of 8 rows.  The concatenation is cached
+        and rebuilt whenever one of its source parameters has changed: the cache key holds each parameter's storage
+        address, in-place version counter, dtype and device, so an optimizer step, `load_state_dict`, `.to()` or a
+        dtype cast all invalidate it."""
+        srcs = [w for w in (self.q_proj, self.k_proj, self.v_proj, self.g_proj) if w is not None]
+        srcs.append(self.learnable_ttt_lr_weight)
+        key = tuple((w.data_ptr(), w._version, w.dtype, w.device) for w in srcs)
+        if self._wcat is None or self._wcat_key != key:
+            self._wcat_key = key
             c = self.config
             blocks, cols, off = [], {}, 0
             for name, w in (("q", self.q_proj), ("k", self.k_proj), ("v", self.v_proj), ("g", self.g_proj)):
