@@ -114,14 +114,15 @@ def pytest_terminal_summary(terminalreporter, exitstatus, config):
         key = (name, rtol)
         if key not in worst or m["max_rel"] > worst[key][1]["max_rel"]:
             worst[key] = (allowed, m)
-    rows = sorted(worst.items(), key=lambda kv: (kv[0][1], -kv[1][1]["out"], -kv[1][1]["max_rel"]))
+    # loosest tolerance class (bfloat16 results) first, worst offenders first within a class
+    rows = sorted(worst.items(), key=lambda kv: (-kv[0][1], -kv[1][1]["out"], -kv[1][1]["max_rel"]))
     lines = ["parity figures (GPU result vs oracle; worst call per name): rtol | max/RMS | rel L2 | outside (allowed) "
              "| outside strict | name"]
     for (name, rtol), (allowed, m) in rows:
         lines.append(f"  {rtol:g} | {m['max_rel']:.3g} | {m['rel_l2']:.3g} | {m['out']:.3g} ({allowed:g}) | "
                      f"{m['out_strict']:.3g} | {name}")
     terminalreporter.write_line("")
-    shown = lines if len(lines) <= 70 else lines[:70] + [f"  ... {len(lines) - 70} more rows"]
+    shown = lines if len(lines) <= 90 else lines[:90] + [f"  ... {len(lines) - 90} more rows"]
     for ln in shown:
         terminalreporter.write_line(ln)
     path = os.environ.get("TTT_PARITY_REPORT")

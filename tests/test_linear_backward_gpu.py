@@ -130,8 +130,10 @@ def test_backward_with_final_state_gradients(dtype):
     _, full = run(t, t["grad_output"])
     seq = ("xq", "xk", "xv", "ttt_lr_eta")
     first = {k: (t[k][:, :, :64] if k in seq else t[k]) for k in LIN_IN}
+    first["token_eta"] = t["token_eta"][:64]  # [seq_len] of the chunk; the kernels read positions [0, 16) only
     o1, _ = run(first, t["grad_output"][:, :, :64])
     second = {k: (t[k][:, :, 64:] if k in seq else t[k]) for k in LIN_IN}
+    second["token_eta"] = t["token_eta"][64:]
     second["weight"], second["bias"] = o1.weight.cpu(), o1.bias.cpu()
     _, g2 = run(second, t["grad_output"][:, :, 64:])
     _, g1 = run(first, t["grad_output"][:, :, :64], g2.weight.cpu(), g2.bias.cpu())

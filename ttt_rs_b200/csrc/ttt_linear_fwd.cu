@@ -16,6 +16,8 @@
 //   * Row statistics for the two LayerNorms are warp-shuffle reduced and exchanged across the 4 warps through
 //     512 bytes of shared memory; G reaches the tensor cores as an A/B operand through movmatrix.
 //   * Output tiles leave through a double-buffered staging tile and a TMA store.
+#include <cstdlib>
+#include <cstring>
 #include <type_traits>
 
 #include "ttt_kernels.h"
@@ -353,7 +355,15 @@ static cudaError_t launch_fwd_t(const CUtensorMap* m, const LinFwdParams& p, int
 
 cudaError_t launch_linear_fwd(int dtype, const CUtensorMap* maps, const LinFwdParams& p, int nstreams,
                               cudaStream_t st) {
-  if (dtype == 1) return launch_fwd_t<__nv_bfloat16>(maps, p, nstreams, st);
+  if (dtype == 1) {
+    // TTT_FWD_KERNEL=cta4 selects the four-warps-per-stream kernel of this file for bf16 (A/B measurements);
+    // the default is the one-warp-per-stream kernel
+    static const bool cta4 = [] {
+      const char* e = getenv("TTT_FWD_KERNEL");
+      return e != nullptr && strcmp(e, "cta4") == 0;
+    }();
+    return cta4 ? launch_fwd_t<__nv_bfloat16>(maps, p, nstreams, st) : launch_linear_fwd_w1(maps, p, nstreams, st);
+  }
   return launch_fwd_t<float>(maps, p, nstreams, st);
 }
 
