@@ -7,13 +7,18 @@ One "step" is one forward + backward pass of the inner loop of one TTT layer ove
 input (the protocol of the reference's `ttt-bench --inner-only --backward`: rust/cli/src/bench.rs:193-234,
 throughput = batch * seq_len / time, bench.rs:329).  Rank 0 prints ONE JSON line.
 
-N > 1 is launched with torch.distributed.run, one rank per GPU.  Every rank runs the full per-GPU workload on
-its own (batch x head) streams (weak scaling, no collective on the data path); the packed outer-parameter
-gradients (dW0, db0, d ln_weight, d ln_bias, d token_eta) are all-reduced with NCCL every step, as data-parallel
-training would.
+N > 1 is launched with torch.distributed.run, one rank per GPU.  The default is STRONG scaling: the seed-0
+tensors of the workload are partitioned by batch rows (rank r owns rows [r B/N, (r+1) B/N) of the same tensors:
+independent (batch x head) streams, no collective on the data path) and the value is tokens/s of the global batch.
+`--scaling weak` gives every rank the full per-GPU workload instead (its own seed); with N > 1 the default run also
+measures that mode and reports it under the extra key "weak".  In both modes the packed outer-parameter gradients
+(dW0, db0, d ln_weight, d ln_bias, d token_eta) are all-reduced with NCCL every step, as data-parallel training
+would.
 
-`--impl reference` times the CPU restatement of the reference's algorithm (oracle/) on the host cores; the
-reference's own Rust/Burn CPU backend cannot be built on this box (no Rust toolchain).
+`--impl reference` times the reference's own CPU implementation of the path on the host cores: its PyTorch module
+(`reference/ttt.py`, forward + autograd backward), staged under oracle/_ref by the build where a reference checkout
+was present, else the CPU restatement in oracle/ttt_oracle.py.  The reference's Rust/Burn CPU backend cannot be
+built on this box (no Rust toolchain).
 """
 
 from __future__ import annotations
@@ -170,8 +175,20 @@ def make_host_inputs(w, seed):
                        inner=w.get("inner", "linear"))
 
 
+CPU_SAMPLE_B = 2  # batch rows of the workload that one CPU step covers (both arms use the same slice)
+
+
+def cpu_kind():
+    from oracle import ref_arm
+    return "reference" if ref_arm.available() else "port"
+
+
 def cpu_step(t, w):
-    """One step of the CPU restatement on a host-resident sample (float32)."""
+    """One step on a host-resident sample (float32): the reference's own PyTorch module (forward + autograd
+    backward) when it was staged under oracle/_ref, else the CPU restatement."""
+    from oracle import ref_arm
+    if ref_arm.available():
+        return ref_arm.step(t, w.get("inner", "linear"), mini_batch=CS, backward=w["backward"])
     from oracle import ttt_oracle as O
     if w.get("inner") == "mlp":
         fw = O.ttt_mlp_forward(*[t[k] for k in MLP_IN], mini_batch=CS, eps=1e-6)
@@ -185,8 +202,9 @@ def cpu_step(t, w):
     return fw
 
 
-def time_cpu(w, steps, warmup, sample_B=1):
+def time_cpu(w, steps, warmup, sample_B=CPU_SAMPLE_B):
     torch.set_num_threads(os.cpu_count() or 1)
+    sample_B = min(sample_B, w["B"])
     sw = dict(w, B=sample_B)
     t = {k: v.float() for k, v in make_host_inputs(sw, seed=0).items()}
     for _ in range(warmup):
@@ -195,26 +213,34 @@ def time_cpu(w, steps, warmup, sample_B=1):
     for _ in range(steps):
         cpu_step(t, w)
     dt = (time.perf_counter() - t0) / steps
+    code = "reference/ttt.py (TTT%s.ttt + autograd)" % ("MLP" if w.get("inner") == "mlp" else "Linear") \
+        if cpu_kind() == "reference" else "oracle/ttt_oracle.py (analytic backward)"
     return sample_B * w["T"] / dt, dt, torch.get_num_threads(), \
-        f"B={sample_B} H={w['H']} T={w['T']} slice of the workload, float32, {steps} step(s)"
+        f"rows [0,{sample_B}) of the workload (B={sample_B} H={w['H']} T={w['T']}), float32, {steps} step(s) after " \
+        f"{warmup} warm-up, {code}"
 
 
 def run_reference(args, w):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    # each step is a 4-sequence slice of the workload (about a second of host time), so K steps stay within minutes
+    # each step is a 2-row slice of the workload (a second or two of host time), so K steps stay within minutes
     steps, warmup = max(1, args.steps), max(0, args.warmup)
-    val, dt, cores, sample = time_cpu(w, steps, warmup, sample_B=min(4, w["B"]))
+    val, dt, cores, sample = time_cpu(w, steps, warmup)
+    kind = cpu_kind()
     line = {
         "impl": "reference", "metric": "ttt_inner_loop_tokens_per_sec", "value": val, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "higher_is_better": True, "scaling": "strong" if args.scaling != "weak" else "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
         "config": {"workload": w["desc"]},
-        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "note": "CPU restatement of the reference's algorithm (oracle/ttt_oracle.py) on the host cores; the "
-                "reference's Rust/Burn CPU backend cannot be built here (no cargo/rustc)",
+        "note": ("the reference's own PyTorch implementation of the path (reference/ttt.py, staged by the build under "
+                 "oracle/_ref) on the host cores" if kind == "reference" else
+                 "CPU restatement of the reference's algorithm (oracle/ttt_oracle.py) on the host cores: no reference "
+                 "checkout was present at build time") +
+                "; the reference's Rust/Burn CPU backend cannot be built here (no cargo/rustc)",
     }
     print(json.dumps(line), flush=True)
 
@@ -507,66 +533,42 @@ def run_decode_layer(args, w):
     print(json.dumps(line), flush=True)
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS))
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-e2e", action="store_true")
-    args = ap.parse_args()
-    w = WORKLOADS[args.workload]
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+def profile_traffic(kernel_workload: str):
+    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of a kernel on a workload, read from the
+    committed ncu summary `profiles/<kernel_workload>.md` (a line `dram_bytes_per_launch: <read> + <write>`), or None
+    when no capture of the current kernel is on file."""
+    f = REPO / "profiles" / f"{kernel_workload}.md"
+    try:
+        for ln in f.read_text().splitlines():
+            if ln.lower().startswith("dram_bytes_per_launch:"):
+                rd, wr = ln.split(":", 1)[1].split("+")
+                return float(rd) + float(wr.split()[0])
+    except (OSError, ValueError):
+        pass
+    return None
 
-    if w.get("kind") == "decode-layer":
-        if args.impl == "reference":
-            raise SystemExit("--impl reference is defined for the inner-loop workloads")
-        run_decode_layer(args, w)
-        return
-    if w.get("kind") == "decode":
-        if args.impl == "reference":
-            raise SystemExit("--impl reference is defined for the inner-loop workloads")
-        run_decode(args, w)
-        return
-    if w.get("kind") == "layer":
-        if args.impl == "reference":
-            raise SystemExit("--impl reference is defined for the inner-loop workloads")
-        run_layer(args, w)
-        return
-    if args.impl == "reference":
-        run_reference(args, w)
-        return
 
+def shard_rows(t, a, b):
+    """Batch rows [a, b) of every per-stream tensor of a host input dict (parameters shared by all streams stay)."""
+    return {k: (v[a:b].contiguous() if v.dim() >= 3 else v) for k, v in t.items()}
+
+
+def bench_inner(tb, w, host, dev, world, rank, args, name):
+    """Times `args.steps` forward(+backward) passes of the inner loop on this rank's device-resident `host` tensors.
+    Returns per-rank results; the caller turns them into tokens/s of the job."""
     import torch.distributed as dist
-    import ttt_rs_b200 as tb
     from ttt_rs_b200.distributed import allreduce_outer_grads
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the operator has no CPU path")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    tb.load_library()
-
-    # ---- device-resident inputs (every rank its own seed: independent batches)
-    host = make_host_inputs(w, seed=rank)
     mlp = w.get("inner") == "mlp"
     cfg = tb.FusedTttConfig.new(CS, F, 1e-6, 128, w["K"])
     if mlp:
         md = {k: host[k].to(dev) for k in MLP_IN}
         mstate = tb.TTTMLPState(md["w1"], md["b1"], md["w2"], md["b2"])
-        args.no_e2e = True
     else:
         ins = tb.TttInputs(*[host[k].to(dev) for k in LIN_IN])
     go = host["grad_output"].to(dev)
+    H = host["xq"].shape[1]
     # two packed outer-gradient buffers: the all-reduce of step i overlaps the forward of step i+1
-    packed = [torch.zeros(tb.packed_outer_grad_len(w["H"]), device=dev) for _ in range(2)] if w["backward"] else None
+    packed = [torch.zeros(tb.packed_outer_grad_len(H), device=dev) for _ in range(2)] if w["backward"] else None
     pending = [None, None]
     ev_pairs = []
     step_no = [0]
@@ -617,8 +619,8 @@ def main():
     for _ in range(args.warmup):
         step()
     barrier()
-    tb.TttTileMultiKernel.check_status()
-    sampler = ClockSampler(local)
+    tb.check_status(dev)
+    sampler = ClockSampler(dev.index)
     sampler.start()
     t_ev0, t_ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -632,34 +634,38 @@ def main():
     t_ev1.record()
     barrier()
     clocks = sampler.stop()
+    tb.check_status(dev)  # a kernel that gave up on a wait leaves its outputs unwritten: such a run has no number
     ms = t_ev0.elapsed_time(t_ev1) / args.steps
     fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev_pairs)
     bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev_pairs) if w["backward"] else None
     if world > 1:
-        tmax = torch.tensor([ms], device=dev)
+        tmax = torch.tensor([ms, fwd_ms, bwd_ms or 0.0], device=dev)
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        ms = tmax.item()
-    tokens = w["B"] * w["T"] * world
-    value = tokens / (ms * 1e-3)
+        ms, fwd_ms = tmax[0].item(), tmax[1].item()
+        bwd_ms = tmax[2].item() if w["backward"] else None
+    return {"ms": ms, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "clocks": clocks, "cfg": cfg, "mlp": mlp}
 
-    # ---- end to end through the public operator with host buffers (pinned), copies inside the timed region
-    e2e = None
-    if not args.no_e2e:
-        e2e = run_e2e(tb, w, host, dev, cfg, world, args)
 
+def roofline_of(w, res, name):
+    """Roofline object of a measured workload `w` (the tensors one GPU processed) from bench_inner's timings."""
     peak, peak_kind = measured_peaks()
+    mlp = res["mlp"]
+    ms, fwd_ms, bwd_ms = res["ms"], res["fwd_ms"], res["bwd_ms"]
     total_b, fb, bb = algorithmic_bytes(w, True, w["backward"])
-    dom_ms, dom_bytes, dom_name = (bwd_ms, bb, "ttt_mlp_bwd_kernel" if mlp else "ttt_linear_bwd_kernel") if w["backward"] else (fwd_ms, fb, "ttt_mlp_fwd_kernel" if mlp else "ttt_linear_fwd_kernel")
+    if w["backward"]:
+        dom_ms, dom_bytes, dom_name = bwd_ms, bb, ("ttt_mlp_bwd_kernel" if mlp else "ttt_linear_bwd_kernel")
+    else:
+        dom_ms, dom_bytes, dom_name = fwd_ms, fb, ("ttt_mlp_fwd_kernel" if mlp else "ttt_linear_fwd_kernel")
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
-    # DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum) from the committed
-    # ncu summary of this same command under profiles/; other workloads have no capture
-    traffic = 599.1e6 + 351.9e6 if args.workload == "cfg1" else None
+    # DRAM bytes per launch of the dominant kernel from the committed ncu summary of this workload, when there is one
+    traffic = profile_traffic(f"{dom_name}_{name}_{w['dtype']}")
     roof = {"bound": "hbm", "kernel": dom_name, "achieved": achieved, "peak": peak, "unit": "GB/s",
             "frac": achieved / peak, "traffic": traffic, "peak_source": f"of {peak_kind}",
             "algorithmic_bytes_per_launch": dom_bytes, "ms_per_launch": dom_ms,
-            "fwd": {"achieved": fb / (fwd_ms * 1e-3) / 1e9, "frac": fb / (fwd_ms * 1e-3) / 1e9 / peak, "ms_per_launch": fwd_ms},
-            "step": {"achieved": total_b / (ms * 1e-3) / 1e9, "frac": total_b / (ms * 1e-3) / 1e9 / peak}}
-
+            "fwd": {"achieved": fb / (fwd_ms * 1e-3) / 1e9, "frac": fb / (fwd_ms * 1e-3) / 1e9 / peak,
+                    "ms_per_launch": fwd_ms},
+            "step": {"achieved": total_b / (ms * 1e-3) / 1e9, "frac": total_b / (ms * 1e-3) / 1e9 / peak,
+                     "algorithmic_bytes": total_b}}
     if mlp:
         # The 2-layer inner model has ~9 times the contraction work of TTT-Linear on the same bytes: its roofline is
         # the slower of the two (north star), which here is the tensor one.  Algorithmic FLOPs per stage and stream
@@ -679,30 +685,180 @@ def main():
             roof["fwd"] = {"achieved": f_fwd / (fwd_ms * 1e-3) / 1e12, "frac": f_fwd / (fwd_ms * 1e-3) / 1e12 / tpeak,
                            "ms_per_launch": fwd_ms}
             roof["step"] = {"achieved": tot_f / (ms * 1e-3) / 1e12, "frac": tot_f / (ms * 1e-3) / 1e12 / tpeak}
+    return roof
+
+
+def side_workload(tb, name, dev, args):
+    """A compact record of another workload measured in the same run (single GPU): per-kernel times and roofline."""
+    w = WORKLOADS[name]
+    host = make_host_inputs(w, seed=0)
+    a2 = argparse.Namespace(**vars(args))
+    a2.steps, a2.warmup = max(3, min(args.steps, 5)), 3
+    res = bench_inner(tb, w, host, dev, 1, 0, a2, name)
+    roof = roofline_of(w, res, name)
+    out = {"workload": w["desc"], "ms_per_step": res["ms"], "fwd_ms": res["fwd_ms"], "bwd_ms": res["bwd_ms"],
+           "tokens_per_s": w["B"] * w["T"] / (res["ms"] * 1e-3), "steps": a2.steps,
+           "roofline": {"bound": roof["bound"], "kernel": roof["kernel"], "frac": roof["frac"],
+                        "achieved": roof["achieved"], "unit": roof["unit"], "step_frac": roof["step"]["frac"],
+                        "fwd_frac": roof["fwd"]["frac"]}}
+    del host
+    torch.cuda.empty_cache()
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS))
+    ap.add_argument("--scaling", default="auto", choices=["auto", "strong", "weak"],
+                    help="N > 1: partition the workload's batch over the ranks (strong) or give every rank the whole "
+                         "per-GPU workload (weak); auto = strong as the line's value plus weak as an extra key")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-side-workloads", action="store_true",
+                    help="skip the compact cfg2 / cfg4-8k records a default single-GPU cfg1 run adds")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    if w.get("kind") in ("decode-layer", "decode", "layer"):
+        if args.impl == "reference":
+            raise SystemExit("--impl reference is defined for the inner-loop workloads")
+        {"decode-layer": run_decode_layer, "decode": run_decode, "layer": run_layer}[w["kind"]](args, w)
+        return
+    if args.impl == "reference":
+        run_reference(args, w)
+        return
+
+    import torch.distributed as dist
+    import ttt_rs_b200 as tb
+    from ttt_rs_b200.distributed import shard_batch
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operator has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    tb.load_library()
+    if w["B"] % world != 0 and args.scaling != "weak":
+        raise SystemExit(f"strong scaling needs the batch ({w['B']}) to be a multiple of the rank count ({world})")
+
+    mode = "weak" if args.scaling == "weak" else "strong"
+    if world == 1:
+        mode = "strong"  # one GPU: the whole workload either way
+    # ---- device-resident inputs: strong = this rank's batch rows of the seed-0 tensors; weak = a whole workload
+    # per rank, seeded by the rank
+    if mode == "strong":
+        a, b = shard_batch(w["B"], rank, world)
+        host = shard_rows(make_host_inputs(w, seed=0), a, b)
+        w_rank = dict(w, B=b - a)
+        tokens = w["B"] * w["T"]
+    else:
+        host = make_host_inputs(w, seed=rank)
+        w_rank = w
+        tokens = w["B"] * w["T"] * world
+    res = bench_inner(tb, w_rank, host, dev, world, rank, args, args.workload)
+    ms = res["ms"]
+    value = tokens / (ms * 1e-3)
+    roof = roofline_of(w_rank, res, args.workload)
+    mlp = res["mlp"]
+
+    # ---- end to end through the public operator with host buffers (pinned), copies inside the timed region
+    e2e = None
+    if not args.no_e2e and not mlp:
+        e2e = run_e2e(tb, w_rank, host, dev, res["cfg"], world, args, tokens)
+
+    weak = None
+    if world > 1 and args.scaling == "auto":
+        hostw = make_host_inputs(w, seed=rank)
+        a2 = argparse.Namespace(**vars(args))
+        a2.steps = max(3, min(args.steps, 10))
+        rw = bench_inner(tb, w, hostw, dev, world, rank, a2, args.workload)
+        weak = {"value": w["B"] * w["T"] * world / (rw["ms"] * 1e-3), "unit": "tokens/s", "ms_per_step": rw["ms"],
+                "global_batch": w["B"] * world, "steps": a2.steps,
+                "note": "every rank runs the whole per-GPU workload on its own seed (no data-path collective)"}
+        del hostw
 
     if rank == 0:
+        streams = w_rank["B"] * w_rank["H"]
         line = {
             "metric": "ttt_inner_loop_tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
-            "config": {"workload": w["desc"], "global_batch": w["B"] * world, "parallelism": f"streams-dp{world}",
-                       "l2": "inputs exceed L2: each step streams %.0f MB of operands" % (total_b / 1e6)},
-            "clocks": clocks, "e2e": e2e,
+            "scaling": mode, "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": w["desc"], "global_batch": w["B"] * (world if mode == "weak" else 1),
+                       "parallelism": f"streams-dp{world}", "streams_per_gpu": streams,
+                       "l2": "inputs exceed L2: each step streams %.0f MB of operands per GPU"
+                             % (roof["step"].get("algorithmic_bytes", 0) / 1e6) if not mlp else
+                             "inputs exceed L2 (%.0f MB of operands per step)" % (algorithmic_bytes(w_rank)[0] / 1e6)},
+            "clocks": res["clocks"], "e2e": e2e,
             "gpu_launches": args.steps * ((3 if mlp else 4) if w["backward"] else 1),
             "roofline": roof,
         }
+        if weak is not None:
+            line["weak"] = weak
+        if world == 1 and args.workload == "cfg1" and not args.no_side_workloads:
+            line["workloads"] = {n: side_workload(tb, n, dev, args) for n in ("cfg2", "cfg4-8k")}
         if world == 1 and not args.no_cpu_baseline:
-            val, dt, cores, sample = time_cpu(w, 6, 1, sample_B=min(8, w["B"]))
-            line["cpu_baseline"] = {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+            val, dt, cores, sample = time_cpu(w, 3, 1)
+            line["cpu_baseline"] = {"value": val, "unit": "tokens/s", "cores": cores, "kind": cpu_kind(),
+                                    "sample": sample}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_e2e(tb, w, host, dev, cfg, world, args):
+def copy_ceiling(pinned, out_host, dev, world, steps):
+    """Time of plain pinned-memory copies of one step's byte counts -- every input host-to-device on one stream, every
+    output device-to-host on another, concurrently, on all ranks at once -- with no kernel in between: the floor the
+    host link puts under the end-to-end step."""
+    import torch.distributed as dist
+    din = {k: torch.empty_like(v, device=dev) for k, v in pinned.items()}
+    dout = {k: torch.empty_like(v, device=dev) for k, v in out_host.items()}
+    s1, s2 = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+    def once():
+        cur = torch.cuda.current_stream(dev)
+        s1.wait_stream(cur)
+        s2.wait_stream(cur)
+        with torch.cuda.stream(s1):
+            for k, v in pinned.items():
+                din[k].copy_(v, non_blocking=True)
+        with torch.cuda.stream(s2):
+            for k, v in out_host.items():
+                v.copy_(dout[k], non_blocking=True)
+        cur.wait_stream(s1)
+        cur.wait_stream(s2)
+
+    once()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        once()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        tmax = torch.tensor([ms], device=dev)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        ms = tmax.item()
+    return ms
+
+
+def run_e2e(tb, w, host, dev, cfg, world, args, tokens):
     """Same metric through the operator a user calls, starting from pinned HOST buffers: every step copies the
     step's inputs to the device, runs forward (+ backward), and copies output and gradients back to the host
-    (ttt_rs_b200.host_io.HostBatchRunner: batch chunks pipelined over three streams)."""
+    (ttt_rs_b200.host_io.HostBatchRunner: batch chunks pipelined over three streams).  `w` / `host` are this rank's
+    share of the workload; `tokens` the job's tokens per step."""
     import torch.distributed as dist
     from ttt_rs_b200.host_io import HostBatchRunner, alloc_host_outputs, bind_host_thread_near
     numa_node = bind_host_thread_near(dev) if world > 1 else None  # pinned buffers in the GPU's own NUMA node
@@ -724,6 +880,7 @@ def run_e2e(tb, w, host, dev, cfg, world, args):
         runner.run(pinned, params, out_host)
     e1.record()
     torch.cuda.synchronize()
+    tb.check_status(dev)
     ms = e0.elapsed_time(e1) / steps
     if world > 1:
         tmax = torch.tensor([ms], device=dev)
@@ -731,8 +888,13 @@ def run_e2e(tb, w, host, dev, cfg, world, args):
         ms = tmax.item()
     h2d = sum(v.numel() * v.element_size() for v in pinned.values())
     d2h = sum(v.numel() * v.element_size() for v in out_host.values())
-    return {"value": w["B"] * w["T"] * world / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
+    ceiling = copy_ceiling(pinned, out_host, dev, world, steps)
+    return {"value": tokens / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": steps,
+            "copy_ceiling_ms": ceiling,
+            "copy_ceiling_note": "the same H2D and D2H byte counts as plain pinned cudaMemcpyAsync on two streams, all "
+                                 "ranks at once, no kernels: the step is bound by the host link when ms_per_step is "
+                                 "close to it (bytes are per rank)",
             "how": f"pinned host buffers, {E2E_CHUNKS} tapered batch chunks pipelined over copy-in / compute / copy-out streams",
             "host_numa_node": numa_node}
 

@@ -12,16 +12,21 @@
  * Conventions
  *  - Every tensor pointer is a DEVICE pointer to a contiguous row-major buffer, 16-byte aligned.
  *  - The caller owns and allocates every buffer (as the reference's host wrappers do with `empty_like`);
- *    the library allocates nothing and keeps no state between calls, so calls are re-entrant and may be
- *    issued from any thread.  Calls enqueue work on `stream` and never synchronise.
+ *    the library allocates nothing.  Apart from two documented exceptions it keeps no state between calls, so
+ *    calls are re-entrant and may be issued from any thread: ttt_linear_backward_noalloc (one scratch array per
+ *    device shared by all its calls, and a cached device address: see its section) and the diagnostic knob
+ *    ttt_b200_debug_handoff (process-wide).  Calls enqueue work on `stream` and never synchronise.
  *  - `dtype` selects the element type of all tensors marked T below: TTT_F32 or TTT_BF16.  Arithmetic is
  *    float32 (bf16 tensor-core operands with float32 accumulation; three-plane split operands for TTT_F32).
  *  - Return value: TTT_OK or an error code; ttt_b200_last_error() gives a thread-local message.  Where the
  *    reference panics (unsupported tile config, seq_len not a multiple of the mini-batch:
  *    linear_fused_tile/mod.rs:143, forward/launch.rs:209-213) these functions return an error and launch
  *    nothing.
- *  - `status`, when non-null, points to 4 zero-initialised device uint32 words; a kernel whose bounded wait on
- *    a TMA completion barrier expires writes {TTT_ERR_TIMEOUT, where, block, stage} there and returns early.
+ *  - `status`, when non-null, points to 4 device uint32 words (16 for ttt_mlp_backward) that the caller zeroed
+ *    once; a kernel whose bounded wait (on a TMA completion barrier, or on another block's hand-off) expires
+ *    writes {TTT_ERR_TIMEOUT, where, block, stage} there by compare-and-swap from zero and returns early, leaving
+ *    its outputs unwritten.  Launches never clear the words, so one buffer per device can serve every launch and
+ *    the first report survives until the host reads and clears it.
  */
 #ifndef TTT_B200_H
 #define TTT_B200_H

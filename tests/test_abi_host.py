@@ -158,3 +158,23 @@ def test_partial_and_layer_entry_points_validate_their_arguments(lib):
     assert epi(gate=C.c_void_p(0x1004), gate_ld=128) == _lib.TTT_ERR_ALIGN
     assert epi(dd=_dims(heads=33)) == _lib.TTT_ERR_UNSUPPORTED
     assert epi(eps=-1.0) == _lib.TTT_ERR_SHAPE
+
+
+def test_rust_declarations_in_the_integration_guide_match_the_header():
+    """INTEGRATION.md carries the Rust `extern "C"` block a maintainer would paste; it is generated from the header.
+    The committed text must equal a fresh generation, and every declaration must have as many arguments as the
+    ctypes table that the tests call through."""
+    import sys
+    sys.path.insert(0, str(REPO / "include"))
+    import gen_rust_ffi as G
+    assert G.current_doc_block() == G.doc_block(), "run `python include/gen_rust_ffi.py --update`"
+    decls = {name: params for _ret, name, params in G.declarations()}
+    assert set(decls) == set(_lib.SYMBOLS)
+    for name, (_res, argtypes) in _lib.SYMBOLS.items():
+        assert len(decls[name]) == len(argtypes), f"{name}: header has {len(decls[name])} arguments, ctypes {len(argtypes)}"
+    rust = G.rust_block()
+    for name, params in decls.items():
+        m = re.search(r"pub fn %s\((.*?)\)( ->|;)" % name, rust, flags=re.S)
+        assert m is not None, name
+        n_rust = 0 if not m.group(1).strip() else m.group(1).count(":")
+        assert n_rust == len(params), f"{name}: Rust block has {n_rust} arguments, header {len(params)}"

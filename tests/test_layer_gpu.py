@@ -273,3 +273,26 @@ def test_shared_qk_convolution_step_and_its_gradient(dtype, K):
     assert_close(k, kr, rt, "conv_k output", max_bad_frac=frac)
     for name, a, b in zip(("d proj", "d conv_q_weight", "d conv_q_bias", "d conv_k_weight", "d conv_k_bias"), leaves, ref):
         assert_close(a.grad, b.grad, rt, name, max_bad_frac=frac)
+
+
+@pytest.mark.gpu
+def test_inference_forward_follows_in_place_parameter_updates(golden_dir):
+    """The no_grad forward runs every projection as one GEMM over a cached concatenation of the q/k/v/g/lr weights.
+    An optimizer step (an in-place update of a parameter) between two such forwards must be seen by the second:
+    compare it with the restatement evaluated at the updated parameters."""
+    import ttt_rs_b200 as tb
+    dev = torch.device("cuda:0")
+    p = dict(_golden(golden_dir, "plain"))
+    m, inner = _layer_from_params(tb, p, False, False, torch.float32, dev, 2)
+    x = p["input"].float().to(dev)
+    with torch.no_grad():
+        y0 = m(x, inner, inner.init_state(x.shape[0]))
+        m.q_proj.mul_(0.5)                      # what an optimizer does: same storage, new values
+        m.learnable_ttt_lr_weight.add_(0.01)
+        y1 = m(x, inner, inner.init_state(x.shape[0]))
+    tb.check_status()
+    p["q_proj"] = p["q_proj"] * 0.5
+    p["lr_weight"] = p["lr_weight"] + 0.01
+    want = LO.ttt_layer_forward(p["input"], p, num_heads=2)[0]
+    assert_close(y1, want, 2e-4, "layer output after in-place parameter update")
+    assert (y1 - y0).abs().max().item() > 1e-3, "the update must change the output"

@@ -52,8 +52,9 @@ def _check_stream(outs, g, t, b, h, tag):
     bw = O.ttt_linear_backward(*[one[k] for k in LIN_IN], one["grad_output"])
     sl = (slice(b, b + 1), slice(h, h + 1))
     assert_close(outs.output[sl], fw["output"], 2e-2, f"{tag}: output", max_bad_frac=allowed)
-    assert_close(outs.weight[sl], fw["weight"], 2e-2, f"{tag}: final weight", max_bad_frac=allowed)
-    assert_close(outs.bias[sl], fw["bias"], 2e-2, f"{tag}: final bias", max_bad_frac=allowed)
+    # the final state is small (4096 + 64 values): plain elementwise criterion, no outliers allowed
+    assert_close(outs.weight[sl], fw["weight"], 2e-2, f"{tag}: final weight")
+    assert_close(outs.bias[sl], fw["bias"], 2e-2, f"{tag}: final bias")
     for n in PER_STREAM:
         assert_close(getattr(g, n)[sl], bw["grad_" + n], 2e-2, f"{tag}: grad_{n}", max_bad_frac=allowed)
 

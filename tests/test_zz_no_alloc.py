@@ -78,8 +78,11 @@ def test_noalloc_backward_matches_workspace_backward_twice_in_a_row():
 
 
 def test_noalloc_backward_rejects_problems_larger_than_its_scratch():
-    """Needs no GPU: the size check comes before anything touches the device."""
+    """Needs no GPU: the size check comes before anything touches the device.  (The library is built first if it is
+    not there yet, so the test also passes alone on a fresh checkout.)"""
     from ttt_rs_b200 import _lib
+    from ttt_rs_b200.build import build
+    build()
     lib = _lib.load()
     d = _lib.TttDims(64, 32, 8192, 64, 16, 16, 1e-6, _lib.TTT_BF16)  # 2048 streams x ~24,700 floats = 200 MB
     assert lib.ttt_linear_backward_workspace_bytes(C.byref(d)) > _lib.NOALLOC_SCRATCH_BYTES

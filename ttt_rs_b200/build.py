@@ -15,7 +15,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libttt_b200.so"
-SOURCES = ["ttt_abi.cu", "ttt_linear_fwd.cu", "ttt_linear_fwd_w1.cu", "ttt_linear_bwd.cu", "ttt_mlp_fwd.cu", "ttt_layer.cu", "ttt_linear_partial.cu", "ttt_mlp_bwd.cu"]
+SOURCES = ["ttt_abi.cu", "ttt_linear_fwd.cu", "ttt_linear_bwd.cu", "ttt_mlp_fwd.cu", "ttt_layer.cu", "ttt_linear_partial.cu", "ttt_mlp_bwd.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xptxas", "-v",

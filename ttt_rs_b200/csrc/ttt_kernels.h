@@ -262,8 +262,6 @@ cudaError_t launch_mlp_fwd(const CUtensorMap* maps, const MlpFwdParams& p, int n
 // dtype: 0 = float32, 1 = bfloat16.  maps: q, k, v, out, gp (saved lr-scaled LN gradient, [B*H*T, 64] of T).
 cudaError_t launch_linear_fwd(int dtype, const CUtensorMap* maps, const LinFwdParams& p, int nstreams,
                               cudaStream_t st);
-// bf16 forward with one warp per stream (ttt_linear_fwd_w1.cu); same maps, parameters and saved state.
-cudaError_t launch_linear_fwd_w1(const CUtensorMap* maps, const LinFwdParams& p, int nstreams, cudaStream_t st);
 // maps: q, k, v, d_out, d_q, d_k, d_v, gp.
 cudaError_t launch_linear_bwd(int dtype, const CUtensorMap* maps, const LinBwdParams& p, int nstreams,
                               cudaStream_t st);

@@ -296,19 +296,19 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       for (int i = 0; i < 4; ++i) z1[nt][i] = zq[nt][i] = kdw[nt][i] = at[nt][i] = 0.f;
 #pragma unroll
     for (int ks = 0; ks < 4; ++ks) {
-      Pk<NP> bw[2][2], bdw[2][2], ak[4], aq[4], bk[4];
+      Pk<NP> bw[2][2], bdw[2][2], ak[4], aq[4];
       bfrag_from_state<NP>(wt, ks, bw);
       bfrag_from_state<NP>(dwt, ks, bdw);
       ldsm_np<NP>(ak, pk + lane_off_A(lane, 16 * ks), PL, false);
       ldsm_np<NP>(aq, pq + lane_off_A(lane, 16 * ks), PL, false);
-      ldsm_np<NP>(bk, pk + lane_off_B_nk(lane, 16 * ks), PL, false);
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
         mma_np<NP>(z1[nt], ak, bw[nt]);
         mma_np<NP>(zq[nt], aq, bw[nt]);
         mma_np<NP>(kdw[nt], ak, bdw[nt]);
       }
-      const Pk<NP> bj0[2] = {bk[0], bk[1]}, bj1[2] = {bk[2], bk[3]};
+      // the A fragments of K are also the B fragments of Q K^T (the same four 8x8 blocks in another order)
+      const Pk<NP> bj0[2] = {ak[0], ak[2]}, bj1[2] = {ak[1], ak[3]};
       mma_np<NP>(at[0], aq, bj0);
       mma_np<NP>(at[1], aq, bj1);
     }
@@ -407,14 +407,13 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       for (int i = 0; i < 4; ++i) pp[nt][i] = gl[nt][i] = dk[nt][i] = dgp[nt][i] = 0.f;
 #pragma unroll
     for (int ks = 0; ks < 4; ++ks) {
-      Pk<NP> adz[4], bgn[4], bwt[4], ags[4], bdw[4];
+      Pk<NP> adz[4], bwt[4], ags[4], bdw[4];
       ldsm_np<NP>(adz, tDZ + lane_off_A(lane, 16 * ks), PL, false);
-      ldsm_np<NP>(bgn, pg + lane_off_B_nk(lane, 16 * ks), PL, false);
       ldsm_np<NP>(bwt, tW + ks * SM::PLANES + lane_off_B_kn(lane, nb), PL, true);
       ldsm_np<NP>(ags, pg + lane_off_A(lane, 16 * ks), PL, false);
       ldsm_np<NP>(bdw, tDW + ks * SM::PLANES + lane_off_B_kn(lane, nb), PL, true);
-      {  // P' = dZbar Gp^T (16x16)
-        const Pk<NP> b0[2] = {bgn[0], bgn[1]}, b1[2] = {bgn[2], bgn[3]};
+      {  // P' = dZbar Gp^T (16x16); the A fragments of Gp serve as its B fragments (same 8x8 blocks, other order)
+        const Pk<NP> b0[2] = {ags[0], ags[2]}, b1[2] = {ags[1], ags[3]};
         mma_np<NP>(pp[0], adz, b0);
         mma_np<NP>(pp[1], adz, b1);
       }

@@ -16,8 +16,6 @@
 //   * Row statistics for the two LayerNorms are warp-shuffle reduced and exchanged across the 4 warps through
 //     512 bytes of shared memory; G reaches the tensor cores as an A/B operand through movmatrix.
 //   * Output tiles leave through a double-buffered staging tile and a TMA store.
-#include <cstdlib>
-#include <cstring>
 #include <type_traits>
 
 #include "ttt_kernels.h"
@@ -170,16 +168,16 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     for (int ks = 0; ks < 4; ++ks) {
       Pk<NP> bw[2][2];
       bfrag_from_state<NP>(wt, ks, bw);
-      Pk<NP> ak[4], aq[4], bk[4];
+      Pk<NP> ak[4], aq[4];
       ldsm_np<NP>(ak, pk + lane_off_A(lane, 16 * ks), TILE_BF16_BYTES, false);
       ldsm_np<NP>(aq, pq + lane_off_A(lane, 16 * ks), TILE_BF16_BYTES, false);
-      ldsm_np<NP>(bk, pk + lane_off_B_nk(lane, 16 * ks), TILE_BF16_BYTES, false);
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
         mma_np<NP>(z1[nt], ak, bw[nt]);
         mma_np<NP>(zq[nt], aq, bw[nt]);
       }
-      const Pk<NP> bj0[2] = {bk[0], bk[1]}, bj1[2] = {bk[2], bk[3]};
+      // the A fragments of K are also the B fragments of Q K^T (the same four 8x8 blocks in another order)
+      const Pk<NP> bj0[2] = {ak[0], ak[2]}, bj1[2] = {ak[1], ak[3]};
       mma_np<NP>(at[0], aq, bj0);
       mma_np<NP>(at[1], aq, bj1);
     }
@@ -355,15 +353,7 @@ static cudaError_t launch_fwd_t(const CUtensorMap* m, const LinFwdParams& p, int
 
 cudaError_t launch_linear_fwd(int dtype, const CUtensorMap* maps, const LinFwdParams& p, int nstreams,
                               cudaStream_t st) {
-  if (dtype == 1) {
-    // TTT_FWD_KERNEL=cta4 selects the four-warps-per-stream kernel of this file for bf16 (A/B measurements);
-    // the default is the one-warp-per-stream kernel
-    static const bool cta4 = [] {
-      const char* e = getenv("TTT_FWD_KERNEL");
-      return e != nullptr && strcmp(e, "cta4") == 0;
-    }();
-    return cta4 ? launch_fwd_t<__nv_bfloat16>(maps, p, nstreams, st) : launch_linear_fwd_w1(maps, p, nstreams, st);
-  }
+  if (dtype == 1) return launch_fwd_t<__nv_bfloat16>(maps, p, nstreams, st);
   return launch_fwd_t<float>(maps, p, nstreams, st);
 }
 
