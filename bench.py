@@ -76,6 +76,10 @@ WORKLOADS = {
                          desc="TTT layer decode step (hidden 768, 12 heads x 64), bf16, B=8, 1 token per step"),
     "decode-b256": dict(kind="decode", B=256, H=12, T=1, dtype="bf16", K=1, backward=False,
                         desc="TTT-Linear inner model decode step (1 token per stream), bf16, B=256 H=12 d=64"),
+    # round-trip latency of one dependent tensor-core step: tcgen05 (descriptor operands, accumulator in tensor
+    # memory) against mma.sync (operands and accumulator in registers); a measurement program, not a throughput line
+    "chain-latency": dict(kind="probe", B=1, H=1, T=16, dtype="bf16", K=1, backward=False,
+                          desc="dependent tensor-core step round trip, tcgen05 vs mma.sync (csrc/probe_chain_latency.cu)"),
 }
 F, CS = 64, 16
 E2E_CHUNKS = int(os.environ.get("TTT_E2E_CHUNKS", "10"))
@@ -724,6 +728,17 @@ def main():
     w = WORKLOADS[args.workload]
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
+    if w.get("kind") == "probe":
+        import subprocess
+        from ttt_rs_b200.build import build_probe
+        out = subprocess.run([str(build_probe())], capture_output=True, text=True, timeout=120)
+        if out.returncode != 0:
+            raise SystemExit(f"probe failed ({out.returncode}): {out.stderr[-400:]}")
+        line = json.loads(out.stdout.strip().splitlines()[-1])
+        line.update({"metric": "dependent_tensor_core_step_cycles", "unit": "cycles/step", "higher_is_better": False,
+                     "config": {"workload": w["desc"]}})
+        print(json.dumps(line), flush=True)
+        return
     if w.get("kind") in ("decode-layer", "decode", "layer"):
         if args.impl == "reference":
             raise SystemExit("--impl reference is defined for the inner-loop workloads")

@@ -15,6 +15,8 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libttt_b200.so"
+PROBE_SRC = CSRC / "probe_chain_latency.cu"      # stand-alone measurement program (bench.py --workload chain-latency)
+PROBE_BIN = PKG / "build" / "probe_chain_latency"
 SOURCES = ["ttt_abi.cu", "ttt_linear_fwd.cu", "ttt_linear_bwd.cu", "ttt_mlp_fwd.cu", "ttt_layer.cu", "ttt_linear_partial.cu", "ttt_mlp_bwd.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -33,12 +35,26 @@ def needs_build() -> bool:
     if not LIB.exists():
         return True
     t = LIB.stat().st_mtime
-    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + \
+    deps = [p for p in CSRC.glob("*.cu") if p != PROBE_SRC] + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + \
         list((PKG.parent / "include").glob("*.h"))
     return any(p.stat().st_mtime > t for p in deps)
 
 
+def build_probe(force: bool = False) -> Path:
+    """The tensor-core chain-latency probe: its own executable, nothing of the library depends on it."""
+    if not force and PROBE_BIN.exists() and PROBE_BIN.stat().st_mtime >= PROBE_SRC.stat().st_mtime:
+        return PROBE_BIN
+    PROBE_BIN.parent.mkdir(exist_ok=True)
+    cmd = [find_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+           "-o", str(PROBE_BIN), str(PROBE_SRC)]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed on {PROBE_SRC.name}:\n{r.stdout}")
+    return PROBE_BIN
+
+
 def build(force: bool = False, verbose: bool = False) -> Path:
+    build_probe(force)
     if not force and not needs_build():
         return LIB
     nvcc = find_nvcc()
