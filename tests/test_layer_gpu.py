@@ -153,7 +153,7 @@ def test_layer_forward_bfloat16_at_a_wider_shape():
         y = m(x.to(torch.bfloat16).to(dev), inner, state)
     tb.TttTileMultiKernel.check_status()
     want, _ = LO.ttt_layer_forward(x, p, num_heads=H, use_gate=True)
-    assert_close(y, want, 2e-2, "layer output", max_bad_frac=1e-3)
+    assert_close(y, want, 2e-2, "layer output", max_bad_frac=2e-4)  # measured 9.2e-5 on B200
 
 
 @pytest.mark.gpu
@@ -225,8 +225,8 @@ def test_layer_with_mlp_inner_model_forward_and_training(golden_dir):
     with torch.no_grad():
         y = m(x.to(dev), inner, inner.init_state(x.shape[0]))
     want, _ = LO.ttt_layer_forward(x.double(), pb, num_heads=H, inner="mlp")
-    assert_close(y, want, 2e-2, "layer output (mlp inner)", max_bad_frac=2e-3)
-    assert_close(y, p["output_expected"], 5e-2, "layer output against the float64 reference", max_bad_frac=5e-3)
+    assert_close(y, want, 2e-2, "layer output (mlp inner)", max_bad_frac=1e-4)  # measured 0
+    assert_close(y, p["output_expected"], 5e-2, "layer output against the float64 reference", max_bad_frac=1e-4)  # measured 0
 
     # training step
     xg = x.to(dev).requires_grad_(True)
@@ -237,11 +237,11 @@ def test_layer_with_mlp_inner_model_forward_and_training(golden_dir):
     leaves["token_idx"] = pb["token_idx"]
     xr = x.double().requires_grad_(True)
     LO.ttt_layer_forward(xr, leaves, num_heads=H, inner="mlp")[0].backward(gy.double())
-    assert_close(xg.grad, xr.grad, 3e-2, "d input", max_bad_frac=5e-3)
+    assert_close(xg.grad, xr.grad, 3e-2, "d input", max_bad_frac=1e-4)  # measured 0
     for name, param in (("W1", mlp.w1_init), ("W2", mlp.w2_init), ("b1", mlp.b1_init), ("q_proj", m.q_proj),
                         ("v_proj", m.v_proj), ("o_proj", m.o_proj), ("post_norm_weight", m.post_norm_weight)):
         assert param.grad is not None, name
-        assert_close(param.grad.reshape(leaves[name].grad.shape), leaves[name].grad, 3e-2, f"d {name}", max_bad_frac=5e-3)
+        assert_close(param.grad.reshape(leaves[name].grad.shape), leaves[name].grad, 3e-2, f"d {name}", max_bad_frac=1e-4)
 
 
 @pytest.mark.gpu

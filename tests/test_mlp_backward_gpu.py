@@ -44,7 +44,7 @@ def test_mlp_backward_matches_autograd_of_the_restatement(B, H, NS, from_forward
     fold = lambda x: x.double().cpu().reshape(-1, 16).sum(0)  # noqa: E731  token_eta gradient per position
     for k in ("grad_xq", "grad_xk", "grad_xv", "grad_w1", "grad_b1", "grad_w2", "grad_b2", "grad_ttt_lr_eta",
               "grad_ln_weight", "grad_ln_bias"):
-        assert_close(g[k], want[k], 2e-2, k, max_bad_frac=2e-3)
+        assert_close(g[k], want[k], 2e-2, k, max_bad_frac=1e-3)  # twice the worst fraction measured on B200 (4.9e-4)
     # token_eta: every (stage, position) entry at the bf16 tolerance.  The sum over the stages of one position can
     # cancel heavily (entries of both signs; for position 15, which also carries the step-size gradient of the state
     # updates, |sum| is up to 30 times smaller than the sum of the magnitudes), so the folded vector is held to the
@@ -82,7 +82,7 @@ def test_mlp_backward_at_the_benchmark_size_on_sampled_streams():
         one["ln_weight"], one["ln_bias"] = t["ln_weight"][h:h + 1], t["ln_bias"][h:h + 1]
         want = O.ttt_mlp_backward_autograd(*[one[k].double() for k in MLP_IN], one["grad_output"].double())
         for k in ("grad_xq", "grad_xk", "grad_xv", "grad_w1", "grad_b1", "grad_w2", "grad_b2", "grad_ttt_lr_eta"):
-            assert_close(g[k][b:b + 1, h:h + 1], want[k], 2e-2, f"stream ({b},{h}) {k}", max_bad_frac=2e-3)
+            assert_close(g[k][b:b + 1, h:h + 1], want[k], 2e-2, f"stream ({b},{h}) {k}", max_bad_frac=1e-3)  # measured at most 4.9e-4
     # a second run gives the same bits (fixed-order reductions, no atomics)
     tb.fused_ttt_mlp_forward(d["xq"], d["xk"], d["xv"], st, d["token_eta"], d["ttt_lr_eta"], d["ln_weight"],
                              d["ln_bias"], cfg, backward_workspace=ws)
@@ -98,7 +98,7 @@ def test_mlp_backward_at_the_benchmark_size_on_sampled_streams():
     tb.check_mlp_status(g3)
     for k in ("grad_xq", "grad_xk", "grad_w1", "grad_w2", "grad_ttt_lr_eta"):
         assert_close(g3[k], g[k].float(), 2e-2, f"{k}: own forward walk vs workspace from the forward",
-                     max_bad_frac=2e-3)
+                     max_bad_frac=2.5e-4)  # measured at most 1.1e-4
 
 
 @pytest.mark.gpu

@@ -78,8 +78,8 @@ def test_host_mirror_runs_the_tail_of_a_ragged_sequence(dtype):
     want = O.ttt_linear_forward_any_length(*[t[k].double() for k in LIN_IN], mini_batch=16)
     rt = RTOL[dtype]
     assert out.shape == (B, H, T, 64)
-    assert_close(out, want["output"], rt, "output", max_bad_frac=1e-3 if dtype == torch.bfloat16 else 0.0)
-    assert_close(state.weight, want["weight"], rt, "weight", max_bad_frac=1e-3 if dtype == torch.bfloat16 else 0.0)
+    assert_close(out, want["output"], rt, "output", max_bad_frac=1e-4 if dtype == torch.bfloat16 else 0.0)
+    assert_close(state.weight, want["weight"], rt, "weight", max_bad_frac=1e-4 if dtype == torch.bfloat16 else 0.0)
     # the reference's fused type refuses the tail; so does the mirror unless asked otherwise
     strict = tb.FusedTileMultiTTTLinear(inner)
     with pytest.raises(AssertionError, match="mini_batch_size"), torch.no_grad():
