@@ -242,6 +242,16 @@ int ttt_layer_prologue(const ttt_dims* d, const void* q_src, const void* k_src, 
 int ttt_layer_epilogue(const ttt_dims* d, const void* inner_out, const void* gate, int64_t gate_ld,
                        const void* post_norm_weight, const void* post_norm_bias, float eps, void* y, void* stream);
 
+/* The layer's projections as one product on the tensor cores (tcgen05, accumulators in tensor memory):
+ *     c[m, n] = a[m, k] . b[n, k]^T       bf16 operands and result, float32 accumulation
+ * `a` = hidden states with one token per row (row pitch lda elements), `b` = a weight matrix as the layer stores it,
+ * one output feature per row (pitch ldb) -- so q/k/v/g/lr weights stacked by rows give all projections of the token
+ * in one call, and o_proj is the same call on the epilogue's output.  Replaces the `Linear` forwards of
+ * rust/layer/src/ttt.rs:152-227,289-299 (Burn matmul).  All pointers 16-byte aligned, pitches multiples of 8
+ * elements; any m, n, k > 0 (edges are clipped / zero-filled by the tensor maps).  `status`: optional 4 words. */
+int ttt_gemm_bf16_tn(int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, const void* b, int64_t ldb, void* c,
+                     int64_t ldc, void* status, void* stream);
+
 /* Gradients of the two layer steps (training; the reference gets them from Burn autodiff over the same tensor ops).
  *
  * ttt_layer_prologue_backward: gradients of XQ, XK, XV [B,H,T,F] and of ttt_lr_eta [B,H,T] -> gradient of the

@@ -29,7 +29,7 @@ def _dims(**kw):
 
 def test_every_declared_symbol_is_exported(lib):
     header = (REPO / "include" / "ttt_b200.h").read_text()
-    declared = set(re.findall(r"\b(ttt_(?:b200|linear|mlp|layer)_\w+)\s*\(", header))
+    declared = set(re.findall(r"\b(ttt_(?:b200|linear|mlp|layer|gemm)_\w+)\s*\(", header))
     assert declared, "no declarations found"
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in ttt_b200.h but not exported"

@@ -17,7 +17,7 @@ CSRC = PKG / "csrc"
 LIB = PKG / "libttt_b200.so"
 PROBE_SRC = CSRC / "probe_chain_latency.cu"      # stand-alone measurement program (bench.py --workload chain-latency)
 PROBE_BIN = PKG / "build" / "probe_chain_latency"
-SOURCES = ["ttt_abi.cu", "ttt_linear_fwd.cu", "ttt_linear_bwd.cu", "ttt_mlp_fwd.cu", "ttt_layer.cu", "ttt_linear_partial.cu", "ttt_mlp_bwd.cu"]
+SOURCES = ["ttt_abi.cu", "ttt_linear_fwd.cu", "ttt_linear_bwd.cu", "ttt_mlp_fwd.cu", "ttt_layer.cu", "ttt_linear_partial.cu", "ttt_mlp_bwd.cu", "ttt_gemm.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xptxas", "-v",

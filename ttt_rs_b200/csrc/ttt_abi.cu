@@ -60,6 +60,22 @@ int make_tile_map(CUtensorMap* m, const void* base, int64_t rows, int dtype) {
   return TTT_OK;
 }
 
+// 2-D bf16 view [rows, cols] with a row pitch of `ld` elements, box = 64 columns x 128 rows, 128-byte swizzle
+// (operand and result tiles of the projection GEMM).
+int make_gemm_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld) {
+  EncodeFn enc = get_encode_fn();
+  if (enc == nullptr) return fail(TTT_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)(ld * 2)};
+  const cuuint32_t box[2] = {64, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(TTT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return TTT_OK;
+}
+
 int check_dims(const ttt_dims* d) {
   if (d == nullptr) return fail(TTT_ERR_NULL, "dims is null");
   if (d->batch <= 0 || d->heads <= 0 || d->seq_len <= 0 || d->head_dim <= 0 || d->mini_batch <= 0)
@@ -172,6 +188,29 @@ const char* ttt_b200_status_string(int s) {
 }
 
 const char* ttt_b200_last_error(void) { return g_err; }
+
+int ttt_gemm_bf16_tn(int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, const void* b, int64_t ldb, void* c,
+                     int64_t ldc, void* status, void* stream) {
+  if (m <= 0 || n <= 0 || k <= 0 || m >= ((int64_t)1 << 31) || n >= ((int64_t)1 << 31) || k >= ((int64_t)1 << 31))
+    return fail(TTT_ERR_SHAPE, "m, n, k must be positive and below 2^31");
+  if (lda < k || ldb < k || ldc < n) return fail(TTT_ERR_SHAPE, "a row pitch is shorter than the row");
+  if ((lda | ldb | ldc) % 8 != 0) return fail(TTT_ERR_ALIGN, "row pitches must be multiples of 8 elements (16 bytes)");
+  const NamedPtr ptrs[] = {{"a", a}, {"b", b}, {"c", c}};
+  int rc = check_ptrs(ptrs, 3);
+  if (rc != TTT_OK) return rc;
+  CUtensorMap maps[3];
+  if ((rc = make_gemm_map(&maps[0], a, m, k, lda)) != TTT_OK) return rc;
+  if ((rc = make_gemm_map(&maps[1], b, n, k, ldb)) != TTT_OK) return rc;
+  if ((rc = make_gemm_map(&maps[2], c, m, n, ldc)) != TTT_OK) return rc;
+  ttt::GemmParams p;
+  p.M = (int)m;
+  p.N = (int)n;
+  p.K = (int)k;
+  p.status = static_cast<uint32_t*>(status);
+  cudaError_t e = ttt::launch_gemm_bf16_tn(maps, p, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "GEMM launch failed: %s", cudaGetErrorString(e));
+  return TTT_OK;
+}
 
 void ttt_b200_debug_handoff(uint32_t poll_limit, int32_t first_item) {
   g_handoff_polls.store(poll_limit == 0 ? kHandoffPollsDefault : poll_limit);
@@ -402,6 +441,12 @@ int ttt_mlp_forward(const ttt_dims* d, const void* xq, const void* xk, const voi
   p.status = static_cast<uint32_t*>(status);
   p.bwd_ws = static_cast<float*>(backward_workspace);
   p.bwd_ws_stride = wl.stride_floats;
+  // with a workspace the launch is persistent and uses the workspace's scheduler words (the backward re-zeroes them)
+  p.sched = backward_workspace != nullptr ? reinterpret_cast<int*>(static_cast<float*>(backward_workspace) + wl.off_sched)
+                                          : nullptr;
+  p.nstreams = d->batch * d->heads;
+  p.CH = p.NCH = 0;
+  p.handoff_polls = g_handoff_polls.load();
   p.H = d->heads; p.T = d->seq_len; p.NS = d->seq_len / d->mini_batch; p.eps = d->epsilon;
   cudaError_t e = ttt::launch_mlp_fwd(maps, p, d->batch * d->heads, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "MLP forward launch failed: %s", cudaGetErrorString(e));

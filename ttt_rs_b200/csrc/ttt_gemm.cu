@@ -1,0 +1,206 @@
+// bf16 GEMM for the outer layer's projections on the 5th-generation tensor cores (sm_100a):
+//     C[M, N] = A[M, K] . B[N, K]^T      (A = hidden states, rows = tokens; B = a weight matrix as the layer stores
+//                                          it, rows = output features; float32 accumulation, bf16 result)
+// This is the product behind the reference layer's `Linear` projections q/k/v/g, the per-head learning-rate weights
+// and o_proj (rust/layer/src/ttt.rs:152-227,289-299), which it gets from Burn's matmul.
+//
+// One CTA computes one 128 x 128 tile of C:
+//   * warp 0 (one lane) is the TMA producer: A and B tiles of 128 rows x 64 k (128-byte rows, 128-byte swizzle) into
+//     a ring of GEMM_STAGES shared-memory stages, completion counted in bytes on the stage's `full` mbarrier;
+//   * warp 1 (one lane) issues tcgen05.mma (cta_group::1, kind::f16, M = 128, N = 128, K = 16): operands by
+//     shared-memory descriptor, accumulator 128 lanes x 128 columns of float32 in tensor memory; after the four
+//     k-steps of a stage a tcgen05.commit on the stage's `empty` mbarrier hands the stage back to the producer, and
+//     after the last stage a commit on `acc` releases the epilogue;
+//   * warps 2-5 are the epilogue: each reads its quarter of the tensor-memory lanes (one row per thread) with
+//     tcgen05.ld, converts to bf16, writes a swizzled staging tile in the (by then idle) stage buffers, and one thread
+//     stores the tile with TMA (rows / columns beyond M / N are clipped by the tensor map).
+// Two CTAs fit on an SM (3 x 32 KB stages, 128 of 512 tensor-memory columns each), so one tile's epilogue overlaps the
+// other's main loop.  No thread-block cluster, no multicast.
+//
+// Every mbarrier wait is bounded: on expiry the role sets a flag, everybody falls through to the common exit, tensor
+// memory is freed and the status words get {TTT_ERR_TIMEOUT, where, block, k-block}.
+#include "ttt_kernels.h"
+#include "ttt_stage.cuh"
+
+namespace ttt {
+
+constexpr int GEMM_BM = 128, GEMM_BN = 128, GEMM_BK = 64, GEMM_STAGES = 3;
+constexpr uint32_t GEMM_TILE_BYTES = GEMM_BM * GEMM_BK * 2;  // 16 KB: one operand tile of a stage
+constexpr int GEMM_THREADS = 192;
+
+struct GemmSmem {
+  static constexpr uint32_t OFF_A = 0;
+  static constexpr uint32_t OFF_B = GEMM_STAGES * GEMM_TILE_BYTES;
+  static constexpr uint32_t OFF_BAR = 2 * GEMM_STAGES * GEMM_TILE_BYTES;  // full[S], empty[S], acc
+  static constexpr uint32_t OFF_TMEM = OFF_BAR + (2 * GEMM_STAGES + 1) * 8;
+  static constexpr uint32_t TOTAL = OFF_TMEM + 8;
+  static constexpr uint32_t DYN_BYTES = TOTAL + 1024;
+};
+
+// shared-memory matrix descriptor for a K-major bf16 tile of 128-byte rows with 128-byte swizzle: start address >> 4,
+// stride between 8-row groups = 1024 bytes, descriptor version 1 (sm_100), layout type 2 (SWIZZLE_128B)
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
+  return (uint64_t)((saddr >> 4) & 0x3fff) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+// instruction descriptor, kind::f16: D float32 (bit 4), A and B bf16 (bits 7, 10), both K-major, N >> 3 at bit 17,
+// M >> 4 at bit 24
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
+      "%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(GEMM_THREADS, 2)
+    ttt_gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                            const __grid_constant__ CUtensorMap tm_c, const GemmParams p) {
+  using SM = GemmSmem;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_u32 = smem_u32(smem_raw);
+  const uint32_t base = (raw_u32 + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - raw_u32);
+  const uint32_t bar_full = base + SM::OFF_BAR, bar_empty = bar_full + 8 * GEMM_STAGES,
+                 bar_acc = bar_empty + 8 * GEMM_STAGES;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + SM::OFF_TMEM);
+  __shared__ int s_fail;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n0 = blockIdx.x * GEMM_BN, m0 = blockIdx.y * GEMM_BM;
+  const int KB = (p.K + GEMM_BK - 1) / GEMM_BK;
+
+  if (tid == 0) {
+    prefetch_tmap(&tm_a);
+    prefetch_tmap(&tm_b);
+    prefetch_tmap(&tm_c);
+    for (int i = 0; i < 2 * GEMM_STAGES + 1; ++i) mbar_init(bar_full + 8 * i, 1);
+    fence_mbar_init();
+    s_fail = 0;
+  }
+  if (warp == 1) {  // tensor memory: 128 columns of float32 accumulators (the same warp frees them at the end)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 128;" ::"r"(base + SM::OFF_TMEM)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer
+    if (lane == 0) {
+      for (int kb = 0; kb < KB; ++kb) {
+        const int st = kb % GEMM_STAGES;
+        if (kb >= GEMM_STAGES && !mbar_wait_bounded(bar_empty + 8 * st, ((kb / GEMM_STAGES) - 1) & 1)) {
+          s_fail = 1;
+          report_timeout(p.status, 31, kb);
+          break;
+        }
+        mbar_expect_tx(bar_full + 8 * st, 2 * GEMM_TILE_BYTES);
+        tma_load_2d(base + SM::OFF_A + st * GEMM_TILE_BYTES, &tm_a, kb * GEMM_BK, m0, bar_full + 8 * st);
+        tma_load_2d(base + SM::OFF_B + st * GEMM_TILE_BYTES, &tm_b, kb * GEMM_BK, n0, bar_full + 8 * st);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(GEMM_BM, GEMM_BN);
+      bool ok = true;
+      for (int kb = 0; kb < KB && ok; ++kb) {
+        const int st = kb % GEMM_STAGES;
+        if (!mbar_wait_bounded(bar_full + 8 * st, (kb / GEMM_STAGES) & 1)) {
+          s_fail = 1;
+          report_timeout(p.status, 32, kb);
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = base + SM::OFF_A + st * GEMM_TILE_BYTES, b_addr = base + SM::OFF_B + st * GEMM_TILE_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < GEMM_BK / 16; ++ks)  // 32 bytes per k-step inside the swizzled 128-byte rows
+          umma_bf16(tmem, umma_desc_sw128(a_addr + 32 * ks), umma_desc_sw128(b_addr + 32 * ks), idesc,
+                    (kb | ks) != 0 ? 1u : 0u);
+        umma_commit(bar_empty + 8 * st);  // the stage is free once these products have read it
+      }
+      umma_commit(bar_acc);  // arrives when every product issued above is complete (at once if none was issued)
+    }
+  } else {
+    // ---------------- epilogue: 4 warps, warp w reads the tensor-memory lanes of quarter w % 4
+    const int q = warp & 3;
+    const int row = 32 * q + lane;
+    const bool ok = mbar_wait_bounded(bar_acc, 0);
+    if (!ok) {
+      s_fail = 1;
+      if (lane == 0) report_timeout(p.status, 33, 0);
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok && s_fail == 0) {
+#pragma unroll
+      for (int c = 0; c < GEMM_BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem + ((uint32_t)(32 * q) << 16) + 32 * c, r);
+        // staging: two [128 rows][64 columns] bf16 tiles in the swizzled layout the TMA store expects, in the first
+        // two A stages (every product has completed, so the ring is idle)
+        const uint32_t tile = base + SM::OFF_A + (c >> 1) * GEMM_TILE_BYTES;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int chunk = (c & 1) * 4 + i;  // 16-byte chunk of the 128-byte row
+          const uint32_t v0 = pack_bf16(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+          const uint32_t v1 = pack_bf16(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+          const uint32_t v2 = pack_bf16(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+          const uint32_t v3 = pack_bf16(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+          asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(tile + row * 128 + ((chunk ^ (row & 7)) << 4)),
+                       "r"(v0), "r"(v1), "r"(v2), "r"(v3)
+                       : "memory");
+        }
+      }
+      fence_proxy_async_smem();
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+    if (warp == 2 && lane == 0 && s_fail == 0) {
+      tma_store_2d(&tm_c, n0, m0, base + SM::OFF_A);
+      if (n0 + 64 < p.N) tma_store_2d(&tm_c, n0 + 64, m0, base + SM::OFF_A + GEMM_TILE_BYTES);
+      bulk_commit();
+      bulk_wait_all<0>();
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 128;" ::"r"(tmem) : "memory");
+}
+
+cudaError_t launch_gemm_bf16_tn(const CUtensorMap* maps, const GemmParams& p, cudaStream_t st) {
+  auto kfn = ttt_gemm_bf16_tn_kernel;
+  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmSmem::DYN_BYTES);
+  if (e != cudaSuccess) return e;
+  dim3 grid((p.N + GEMM_BN - 1) / GEMM_BN, (p.M + GEMM_BM - 1) / GEMM_BM);
+  kfn<<<grid, GEMM_THREADS, GemmSmem::DYN_BYTES, st>>>(maps[0], maps[1], maps[2], p);
+  return cudaGetLastError();
+}
+
+}  // namespace ttt

@@ -80,6 +80,10 @@ struct MlpFwdParams {
   uint32_t* status;
   float* bwd_ws;         // optional: the backward's workspace; the forward then leaves there what the backward's own
   size_t bwd_ws_stride;  // first pass would compute (final state, final biases, lr-scaled inner gradients per stage)
+  int* sched;            // with bwd_ws: [1 + B*H] work-item counter and per-stream count of finished chunks (the
+                         // persistent launch; zeroed by the launcher), else null
+  int nstreams, CH, NCH; // set by the launcher: streams, stages per work item, items per stream
+  uint32_t handoff_polls;  // iteration limit of the wait for the previous chunk's state
   int H, T, NS;
   float eps;
 };
@@ -255,6 +259,13 @@ __host__ __device__ inline int mlp_state_at(int r, int c, int C) {
 }
 size_t mlp_bwd_ws_stride_floats(int T);
 cudaError_t launch_mlp_bwd(const MlpBwdParams& p, int B, cudaStream_t st);
+
+// bf16 projection GEMM C[M,N] = A[M,K] . B[N,K]^T on tcgen05 (ttt_gemm.cu).  maps: A, B (loads, box 64 x 128), C (store).
+struct GemmParams {
+  int M, N, K;
+  uint32_t* status;  // optional 4 words
+};
+cudaError_t launch_gemm_bf16_tn(const CUtensorMap* maps, const GemmParams& p, cudaStream_t st);
 
 // bf16 only.  maps: q, k, v, out.
 cudaError_t launch_mlp_fwd(const CUtensorMap* maps, const MlpFwdParams& p, int nstreams, cudaStream_t st);

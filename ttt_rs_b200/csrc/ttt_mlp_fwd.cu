@@ -14,6 +14,15 @@
 // K.W1 / Q.W1, W2 directly the B operand of G2p.W2^T, and both rank-16 updates accumulate into them.  The two products
 // that contract over e (X2.W2, Xb2.W2) read a bf16 copy of W2 that every warp refreshes in shared memory after its
 // update; X2, Xb2 and G2p pass through shared-memory operand tiles; A2 is summed from per-warp register partials.
+//
+// Scheduling.  One CTA fills an SM (255 registers x 256 threads), so a launch of one CTA per stream runs in whole
+// waves: 192 streams on 148 SMs cost two stream-times.  When the caller passes the backward's workspace (training),
+// the kernel is launched persistently instead: blocks take work items (stream, chunk of MLP_FWD_CHUNK stages), first
+// chunks of all streams first; a chunk leaves the float32 state and biases in the stream's workspace block (where
+// the final state is due anyway) and the next chunk of that stream -- on whichever block takes it -- picks them up.
+// An item waits only for an item of smaller index, which a resident block already holds (cooperative launch), and
+// the wait is bounded.  Without a workspace (inference) there is nowhere to park 128 KB of state per stream, and the
+// kernel runs one block per stream as before.
 #include "ttt_kernels.h"
 #include "ttt_stage.cuh"
 
@@ -22,6 +31,7 @@ namespace ttt {
 constexpr int MLP_THREADS = 256;
 constexpr int MLP_E = 256;
 constexpr int MLP_NST = 2;
+constexpr int MLP_FWD_CHUNK = 16;  // stages per work item of the persistent launch
 
 struct MlpSmem {
   static constexpr uint32_t TILE = TILE_BF16_BYTES;                   // [16][64] bf16
@@ -110,10 +120,12 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
   const Lane L;
   const int tid = L.tid, lane = L.lane, g = L.g, t = L.t, warp = L.warp;
   const int eb = 32 * warp, fb = 8 * warp;
-  const int stream = blockIdx.x;
-  const int head = stream % p.H;
   const int NS = p.NS;
-  const int row_base = stream * p.T;
+  const bool persistent = (p.sched != nullptr);
+  const int CH = persistent ? p.CH : NS, NCH = persistent ? p.NCH : 1;
+  const int nitems = persistent ? p.nstreams * NCH : (int)gridDim.x;
+  __shared__ int s_item;
+  int stream = 0, head = 0, row_base = 0;
 
   if (tid == 0) {
     prefetch_tmap(&tm_q);
@@ -127,14 +139,15 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
 
   // Optional: the backward's per-stream workspace block (layout in ttt_kernels.h).  The lr-scaled inner gradients of
   // every stage (the bf16 operands of the state updates) and the final state go there, so that the backward can
-  // start its reverse walk at once.
-  float* const bws = p.bwd_ws != nullptr ? p.bwd_ws + (size_t)stream * p.bwd_ws_stride : nullptr;
-  uint32_t* const sv_g1p = bws != nullptr ? reinterpret_cast<uint32_t*>(bws + 4 * HD * MLP_E + MLP_BWD_HANDOFF_FLOATS) : nullptr;
-  uint32_t* const sv_g2p = bws != nullptr ? sv_g1p + (size_t)NS * CS * MLP_E / 2 : nullptr;
-  float* const sv_bst = bws != nullptr ? reinterpret_cast<float*>(sv_g2p + (size_t)NS * CS * HD / 2) : nullptr;
+  // start its reverse walk at once.  Set per work item.
+  float* bws = nullptr;
+  uint32_t* sv_g1p = nullptr;
+  uint32_t* sv_g2p = nullptr;
+  float* sv_bst = nullptr;
 
-  auto issue_loads = [&](int s) {
-    const int slot = s % MLP_NST;
+  // stage s of the current stream into ring slot n % MLP_NST (n counts the stages this block has visited)
+  auto issue_loads = [&](int n, int s) {
+    const int slot = n % MLP_NST;
     const uint32_t bar = bar0 + 8 * slot;
     const uint32_t tq = base + slot * SM::SLOT;
     mbar_expect_tx(bar, 3 * TL + CS * 2);
@@ -144,39 +157,20 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
     tma_load_2d(tq + 2 * TL, &tm_v, 0, r0, bar);
     bulk_load_1d(base + SM::OFF_LR + slot * 32, static_cast<const uint8_t*>(p.lr) + (size_t)r0 * 2, CS * 2, bar);
   };
-  if (tid == 0) {
-    for (int s = 0; s < MLP_NST && s < NS; ++s) issue_loads(s);
-  }
 
   // ---- constants: F-space column pair (fb + 2t, +1); E-space column pairs j = 0..3: (eb + 8j + 2t, +1)
   const int fc = fb + 2 * t;
-  const F2 gam = f2(ld_as_float<T>(p.ln_g, (size_t)head * HD + fc), ld_as_float<T>(p.ln_g, (size_t)head * HD + fc + 1));
-  const F2 bet = f2(ld_as_float<T>(p.ln_b, (size_t)head * HD + fc), ld_as_float<T>(p.ln_b, (size_t)head * HD + fc + 1));
+  F2 gam = f2(0.f), bet = f2(0.f);
   const float te_row[2] = {ld_as_float<T>(p.token_eta, g), ld_as_float<T>(p.token_eta, g + 8)};
   const float te15 = ld_as_float<T>(p.token_eta, CS - 1);
   // both states are carried divided by wscale = -te15, so that their rank-16 updates accumulate directly by mma
   const bool w_moves = (te15 != 0.f);
   const float wscale = w_moves ? -te15 : 1.f;
   const float winv = 1.f / wscale;
-  F2 b2v = f2(ld_as_float<T>(p.b2, (size_t)stream * HD + fc), ld_as_float<T>(p.b2, (size_t)stream * HD + fc + 1));
+  F2 b2v = f2(0.f);
   F2 b1v[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const size_t o = (size_t)stream * MLP_E + eb + 8 * j + 2 * t;
-    b1v[j] = f2(ld_as_float<T>(p.b1, o), ld_as_float<T>(p.b1, o + 1));
-  }
   // ---- state: w1t[mt][kt][2rn+e'] = W1[k = 8kt+2t+e'][e = eb+16mt+g+8rn];  w2[mt][nt][2rn+e'] = W2[e = eb+16mt+g+8rn][n = 8nt+2t+e']
   float w1t[2][8][4], w2[2][8][4];
-#pragma unroll
-  for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-    for (int kt = 0; kt < 8; ++kt)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int e = eb + 16 * mt + g + 8 * (i >> 1), c = 8 * kt + 2 * t + (i & 1);
-        w1t[mt][kt][i] = ld_as_float<T>(p.w1, (size_t)stream * HD * MLP_E + (size_t)c * MLP_E + e) * winv;
-        w2[mt][kt][i] = ld_as_float<T>(p.w2, (size_t)stream * HD * MLP_E + (size_t)e * HD + c) * winv;
-      }
   // bf16 copy of this warp's 32 rows of W2 -> sub-tiles 2*warp, 2*warp+1
   auto publish_w2 = [&]() {
 #pragma unroll
@@ -189,14 +183,97 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
                        "r"(pack_bf16(w2[mt][nt][2 * rn] * wscale, w2[mt][nt][2 * rn + 1] * wscale))
                        : "memory");
   };
-  publish_w2();
 
   int xsel = 0;
   bool failed = false;
-  for (int s = 0; s < NS; ++s) {
-    const int slot = s % MLP_NST;
+  int n = 0;  // stages visited by this block so far (ring slot and barrier phase)
+  for (int round = 0; !failed; ++round) {
+    // ---- next work item: (stream, chunk); one block per stream and a single chunk when not persistent
+    int item;
+    if (persistent) {
+      if (tid == 0) s_item = atomicAdd(&p.sched[0], 1);
+      __syncthreads();
+      item = s_item;
+      __syncthreads();
+    } else {
+      item = (round == 0) ? (int)blockIdx.x : nitems;
+    }
+    if (item >= nitems) break;
+    const int chunk = persistent ? item / p.nstreams : 0;
+    stream = persistent ? item - chunk * p.nstreams : item;
+    head = stream % p.H;
+    row_base = stream * p.T;
+    const int s_lo = chunk * CH, s_hi = min(s_lo + CH, NS) - 1;
+    bws = p.bwd_ws != nullptr ? p.bwd_ws + (size_t)stream * p.bwd_ws_stride : nullptr;
+    sv_g1p = bws != nullptr ? reinterpret_cast<uint32_t*>(bws + 4 * HD * MLP_E + MLP_BWD_HANDOFF_FLOATS) : nullptr;
+    sv_g2p = bws != nullptr ? sv_g1p + (size_t)NS * CS * MLP_E / 2 : nullptr;
+    sv_bst = bws != nullptr ? reinterpret_cast<float*>(sv_g2p + (size_t)NS * CS * HD / 2) : nullptr;
+    gam = f2(ld_as_float<T>(p.ln_g, (size_t)head * HD + fc), ld_as_float<T>(p.ln_g, (size_t)head * HD + fc + 1));
+    bet = f2(ld_as_float<T>(p.ln_b, (size_t)head * HD + fc), ld_as_float<T>(p.ln_b, (size_t)head * HD + fc + 1));
+    if (chunk == 0) {
+      // the stream starts from the caller's initial state
+      b2v = f2(ld_as_float<T>(p.b2, (size_t)stream * HD + fc), ld_as_float<T>(p.b2, (size_t)stream * HD + fc + 1));
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const size_t o = (size_t)stream * MLP_E + eb + 8 * j + 2 * t;
+        b1v[j] = f2(ld_as_float<T>(p.b1, o), ld_as_float<T>(p.b1, o + 1));
+      }
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int kt = 0; kt < 8; ++kt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int e = eb + 16 * mt + g + 8 * (i >> 1), c = 8 * kt + 2 * t + (i & 1);
+            w1t[mt][kt][i] = ld_as_float<T>(p.w1, (size_t)stream * HD * MLP_E + (size_t)c * MLP_E + e) * winv;
+            w2[mt][kt][i] = ld_as_float<T>(p.w2, (size_t)stream * HD * MLP_E + (size_t)e * HD + c) * winv;
+          }
+    } else {
+      // wait (bounded) until the previous chunk of this stream has parked its state in the workspace block
+      int ok = 1;
+      if (tid == 0) {
+        ok = 0;
+        const volatile int* flag = p.sched + 1 + stream;
+        for (uint32_t it = 0; it < p.handoff_polls; ++it) {
+          if (*flag >= chunk) {
+            ok = 1;
+            break;
+          }
+          __nanosleep(100);
+        }
+        __threadfence();
+      }
+      if (__syncthreads_or(ok ? 0 : 1)) {
+        failed = true;
+        if (tid == 0) report_timeout(p.status, 22, item);
+        break;
+      }
+      // raw register images (already divided by wscale), 16 float4 per thread and matrix; biases in the hand-off record
+      const float4* h1 = reinterpret_cast<const float4*>(bws);
+      const float4* h2 = reinterpret_cast<const float4*>(bws + HD * MLP_E);
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int kt = 0; kt < 8; ++kt) {
+          const float4 a = __ldcg(h1 + (mt * 8 + kt) * MLP_THREADS + tid);
+          const float4 b = __ldcg(h2 + (mt * 8 + kt) * MLP_THREADS + tid);
+          w1t[mt][kt][0] = a.x; w1t[mt][kt][1] = a.y; w1t[mt][kt][2] = a.z; w1t[mt][kt][3] = a.w;
+          w2[mt][kt][0] = b.x; w2[mt][kt][1] = b.y; w2[mt][kt][2] = b.z; w2[mt][kt][3] = b.w;
+        }
+      const float* ho = bws + 4 * HD * MLP_E;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b1v[j] = __ldcg(reinterpret_cast<const float2*>(ho + MLP_HO_B1 + eb + 8 * j + 2 * t));
+      b2v = __ldcg(reinterpret_cast<const float2*>(ho + MLP_HO_B2 + fc));
+    }
+    if (tid == 0) {
+      for (int s = s_lo; s < s_lo + MLP_NST && s <= s_hi; ++s) issue_loads(n + (s - s_lo), s);
+    }
+    publish_w2();
+
+  for (int s = s_lo; s <= s_hi; ++s, ++n) {
+    const int slot = n % MLP_NST;
     const uint32_t tq = base + slot * SM::SLOT, tk = tq + TL, tv = tk + TL;
-    int fail = mbar_wait_bounded(bar0 + 8 * slot, (s / MLP_NST) & 1) ? 0 : 1;
+    int fail = mbar_wait_bounded(bar0 + 8 * slot, (n / MLP_NST) & 1) ? 0 : 1;
     if (sv_bst != nullptr && g == 0) {  // biases at the start of the stage, for the backward
       float* const bs = sv_bst + (size_t)s * (MLP_E + HD);
 #pragma unroll
@@ -272,7 +349,7 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
       if (tid == 0) report_timeout(p.status, 21, s);
       break;
     }
-    if (tid == 0 && s >= 1 && s + 1 < NS) issue_loads(s + 1);
+    if (tid == 0 && s > s_lo && s < s_hi) issue_loads(n + 1, s + 1);
 
     // B fragments of W2[:, fb..fb+7] for two k-steps (32 hidden rows) from the bf16 copy
     const int m_ = lane >> 3, r_ = lane & 7;
@@ -435,7 +512,7 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
       const float mean[2] = {a0.x * (1.f / HD), a1.x * (1.f / HD)};
       const float rstd[2] = {rsqrtf(fmaxf(a0.y * (1.f / HD) - mean[0] * mean[0], 0.f) + p.eps),
                              rsqrtf(fmaxf(a1.y * (1.f / HD) - mean[1] * mean[1], 0.f) + p.eps)};
-      const uint32_t so = base + SM::OFF_OUT + (s & 1) * TL;
+      const uint32_t so = base + SM::OFF_OUT + (n & 1) * TL;
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
         const F2 x = f2mul(f2sub(zp[r], f2(mean[r])), f2(rstd[r]));
@@ -477,9 +554,30 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
       const F2 cs = f2add(g2p[0], g2p[1]);
       b2v = f2fma(f2(col_sum(cs.x), col_sum(cs.y)), f2(-te15), b2v);
     }
-    publish_w2();
+    if (s < s_hi) publish_w2();
   }
-  if (!failed) {
+  if (failed) break;
+  if (chunk < NCH - 1) {
+    // ---- park the state for the next chunk of this stream: register images into the stream's workspace block
+    float4* h1 = reinterpret_cast<float4*>(bws);
+    float4* h2 = reinterpret_cast<float4*>(bws + HD * MLP_E);
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int kt = 0; kt < 8; ++kt) {
+        h1[(mt * 8 + kt) * MLP_THREADS + tid] = make_float4(w1t[mt][kt][0], w1t[mt][kt][1], w1t[mt][kt][2], w1t[mt][kt][3]);
+        h2[(mt * 8 + kt) * MLP_THREADS + tid] = make_float4(w2[mt][kt][0], w2[mt][kt][1], w2[mt][kt][2], w2[mt][kt][3]);
+      }
+    if (g == 0) {
+      float* const ho = bws + 4 * HD * MLP_E;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) *reinterpret_cast<float2*>(ho + MLP_HO_B1 + eb + 8 * j + 2 * t) = b1v[j];
+      *reinterpret_cast<float2*>(ho + MLP_HO_B2 + fc) = b2v;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) *reinterpret_cast<volatile int*>(p.sched + 1 + stream) = chunk + 1;
+  } else {
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
@@ -522,6 +620,7 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
       st_from_float<T>(p.b2_out, (size_t)stream * HD + fc + 1, b2v.y);
     }
   }
+  }  // work items
   if (tid == 0) bulk_wait_all<0>();
 }
 
@@ -529,7 +628,25 @@ cudaError_t launch_mlp_fwd(const CUtensorMap* m, const MlpFwdParams& p, int nstr
   auto kfn = ttt_mlp_fwd_kernel;
   cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MlpSmem::DYN_BYTES);
   if (e != cudaSuccess) return e;
-  kfn<<<nstreams, MLP_THREADS, MlpSmem::DYN_BYTES, st>>>(m[0], m[1], m[2], m[3], p);
-  return cudaGetLastError();
+  if (p.sched == nullptr) {  // no workspace to park state in: one block per stream
+    kfn<<<nstreams, MLP_THREADS, MlpSmem::DYN_BYTES, st>>>(m[0], m[1], m[2], m[3], p);
+    return cudaGetLastError();
+  }
+  // persistent: as many blocks as are co-resident (they wait on one another's hand-offs), never more than items
+  int dev = 0, sms = 0, per_sm = 0;
+  if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+  if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+  if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kfn, MLP_THREADS, MlpSmem::DYN_BYTES)) != cudaSuccess)
+    return e;
+  if (per_sm < 1) return cudaErrorLaunchOutOfResources;
+  MlpFwdParams pp = p;
+  pp.nstreams = nstreams;
+  pp.CH = MLP_FWD_CHUNK;
+  pp.NCH = (p.NS + MLP_FWD_CHUNK - 1) / MLP_FWD_CHUNK;
+  int grid = sms * per_sm;
+  if (grid > nstreams * pp.NCH) grid = nstreams * pp.NCH;
+  if ((e = cudaMemsetAsync(pp.sched, 0, sizeof(int) * (size_t)(1 + nstreams), st)) != cudaSuccess) return e;
+  void* args[] = {(void*)&m[0], (void*)&m[1], (void*)&m[2], (void*)&m[3], (void*)&pp};
+  return cudaLaunchCooperativeKernel((const void*)kfn, dim3(grid), dim3(MLP_THREADS), args, MlpSmem::DYN_BYTES, st);
 }
 }  // namespace ttt

@@ -115,6 +115,30 @@ def layer_epilogue(inner_out: torch.Tensor, ln_weight: torch.Tensor, ln_bias: to
     return y
 
 
+def gemm_bf16_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a [M, K] . b[N, K]^T -> [M, N], bf16 with float32 accumulation, on the library's tcgen05 GEMM
+    (`ttt_gemm_bf16_tn`): `a` has one token per row, `b` is a weight matrix with one output feature per row, as the
+    layer's projections store them.  Rows of both must be contiguous; K and N multiples of 8."""
+    from .fused import device_status
+    lib = _lib.load()
+    if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
+        raise ValueError(f"gemm_bf16_tn: shapes {tuple(a.shape)} and {tuple(b.shape)} do not contract")
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or not a.is_cuda or b.device != a.device:
+        raise ValueError("gemm_bf16_tn takes bf16 CUDA tensors on one device: there is no CPU path")
+    if a.stride(1) != 1:
+        a = a.contiguous()
+    if b.stride(1) != 1:
+        b = b.contiguous()
+    M, K = a.shape
+    N = b.shape[0]
+    c = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    stream = C.c_void_p(torch.cuda.current_stream(a.device).cuda_stream)
+    with torch.cuda.device(a.device):
+        _lib.check(lib.ttt_gemm_bf16_tn(M, N, K, _ptr(a), a.stride(0), _ptr(b), b.stride(0), _ptr(c), c.stride(0),
+                                        _ptr(device_status(a.device)), stream))
+    return c
+
+
 class _PrologueFn(torch.autograd.Function):
     """`ttt_layer_prologue` with its gradient `ttt_layer_prologue_backward` (layout q | k | v | lr logits | padding,
     no shared-QK convolutions)."""
@@ -322,12 +346,20 @@ class TTT(torch.nn.Module):
     def invalidate_fused_weight(self):
         self._wcat = None
 
+    @staticmethod
+    def _project(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        """x [..., K] . weight[N, K]^T -> [..., N].  bf16 on a GPU: the library's own tensor-core GEMM
+        (`ttt_gemm_bf16_tn`); float32 (the parity configuration) is a float32 library product."""
+        if x.dtype == torch.bfloat16 and x.is_cuda and weight.shape[0] % 8 == 0 and weight.shape[1] % 8 == 0:
+            return gemm_bf16_tn(x.reshape(-1, x.shape[-1]), weight).reshape(*x.shape[:-1], weight.shape[0])
+        return torch.matmul(x, weight.t())
+
     def get_inner_loop_inputs(self, x: torch.Tensor, start_idx: int):
         """Hidden states -> (TTTInputsInner, projection output, column map) (rust/layer/src/ttt.rs:250-267)."""
         c = self.config
         B, T, _ = x.shape
         wcat, cols = self._fused_weight()
-        proj = torch.matmul(x, wcat.t())  # [B, T, N], library GEMM
+        proj = self._project(x, wcat)  # [B, T, N]: every projection of the token in one product
         conv = None
         if c.share_qk:
             conv = (self.q_conv_weight, self.q_conv_bias, self.k_conv_weight, self.k_conv_bias)
@@ -351,7 +383,7 @@ class TTT(torch.nn.Module):
             gate = proj.reshape(B * T, -1)[:, cols["g"]:]
             gate_ld = proj.shape[-1]
         y = layer_epilogue(out.contiguous(), self.post_norm_weight, self.post_norm_bias, 1e-6, gate, gate_ld)
-        return torch.matmul(y, self.o_proj.t())
+        return self._project(y, self.o_proj.detach())
 
 
 def _train_forward(self, x, inner, state, start_idx):
