@@ -292,7 +292,7 @@ def run_layer(args, w):
 
     with torch.no_grad():
         wcat, cols = m._fused_weight()
-        proj = torch.matmul(x, wcat.t())
+        proj = tb.gemm_bf16_tn(x.reshape(B * T, C), wcat).reshape(B, T, -1)
         inputs, _, _ = m.get_inner_loop_inputs(x, 0)
         inner_out = inner.forward(tb.TTTLinearState(state0.weight, state0.bias), inputs)
         y = tb.layer_epilogue(inner_out, m.post_norm_weight, m.post_norm_bias)
@@ -343,12 +343,20 @@ def run_layer(args, w):
         gyy = torch.randn_like(y)
         pb_ms = time_events(lambda: _PrologueFn.backward(_Ctx, *dxs, dlr), args.steps, args.warmup)
         eb_ms = time_events(lambda: _EpilogueFn.backward(_Ctx2, gyy), args.steps, args.warmup)
+    fused_ok = m._can_fuse_projections(x, cols)
     pieces = {
-        "projections_gemm": time_events(lambda: torch.matmul(x, wcat.t()), args.steps, args.warmup),
+        "projections_and_prologue_fused": time_events(
+            lambda: tb.layer_projections(x, wcat, cols, cfg, m.learnable_ttt_lr_bias, 0), args.steps, args.warmup)
+        if fused_ok else None,
+        "projections_gemm": time_events(lambda: tb.gemm_bf16_tn(x.reshape(B * T, C), wcat), args.steps, args.warmup),
+        "projections_gemm_cublas_for_comparison": time_events(lambda: torch.matmul(x, wcat.t()), args.steps, args.warmup),
         "ttt_layer_prologue_kernel": time_events(pro, args.steps, args.warmup),
         "inner_loop_forward": time_events(inner_only, args.steps, args.warmup),
         "ttt_layer_epilogue_kernel": time_events(epi, args.steps, args.warmup),
-        "output_projection_gemm": time_events(lambda: torch.matmul(y, m.o_proj.t()), args.steps, args.warmup),
+        "output_projection_gemm": time_events(lambda: tb.gemm_bf16_tn(y.reshape(B * T, C), m.o_proj.detach()), args.steps,
+                                              args.warmup),
+        "output_projection_gemm_cublas_for_comparison": time_events(lambda: torch.matmul(y, m.o_proj.t()), args.steps,
+                                                                    args.warmup),
     }
     peak, peak_kind = measured_peaks()
     s = 2
@@ -356,6 +364,9 @@ def run_layer(args, w):
     epi_bytes = 2 * C * s * B * T
     pa = pro_bytes / (pieces["ttt_layer_prologue_kernel"] * 1e-3) / 1e9
     ea = epi_bytes / (pieces["ttt_layer_epilogue_kernel"] * 1e-3) / 1e9
+    tpeak, tkind = measured_tensor_peak()
+    gflop = 2.0 * B * T * C * wcat.shape[0]
+    gemm_tf = gflop / (pieces["projections_gemm"] * 1e-3) / 1e12
     line = {
         "metric": "ttt_layer_forward_tokens_per_sec", "value": B * T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
@@ -368,7 +379,11 @@ def run_layer(args, w):
                      "unit": "GB/s", "frac": pa / peak, "traffic": None, "peak_source": f"of {peak_kind}",
                      "algorithmic_bytes_per_launch": pro_bytes,
                      "epilogue": {"kernel": "ttt_layer_epilogue_kernel", "achieved": ea, "frac": ea / peak,
-                                  "algorithmic_bytes_per_launch": epi_bytes}},
+                                  "algorithmic_bytes_per_launch": epi_bytes},
+                     "projections_gemm": {"kernel": "ttt_gemm_bf16_tn_kernel", "bound": "tensor", "achieved": gemm_tf,
+                                          "unit": "TFLOP/s", "peak": tpeak, "frac": gemm_tf / tpeak,
+                                          "peak_source": f"of {tkind} (cuBLAS bf16 burst)",
+                                          "flops_per_launch": gflop}},
     }
     if not args.no_cpu_baseline:
         from oracle import ttt_layer_oracle as LO

@@ -252,6 +252,22 @@ int ttt_layer_epilogue(const ttt_dims* d, const void* inner_out, const void* gat
 int ttt_gemm_bf16_tn(int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, const void* b, int64_t ldb, void* c,
                      int64_t ldc, void* status, void* stream);
 
+/* All projections of the layer and the step that follows them, in one launch (bf16, head_dim 64): the product
+ * x . weights^T of ttt_gemm_bf16_tn with `weights` = the q | k | v | (g) | lr rows stacked, whose epilogue does what
+ * `get_qkv` / `get_lr` do with the projection output (rust/layer/src/ttt.rs:152-227; this library's
+ * ttt_layer_prologue without the shared-QK convolutions): q and k are rotated and written as xq / xk [B,H,T,F], v as
+ * xv, the gate columns to `gate` [B*T, H*F] (pass g_col = -1 and gate = NULL when the layer has none), the logits as
+ * ttt_lr_eta[b,h,t] = base_lr / F * sigmoid(logit + lr_bias[h]).  The [B*T, rows] projection output is never stored.
+ *   x [B*T, x_ld] (first `hidden` columns), weights [w_rows, w_ld]; *_col: first weight row of each block (multiples
+ *   of 64; q, k, v, g blocks are heads*64 rows, the lr block `heads` rows); rope_mode 0 or 1 (positions
+ *   (start_idx + t) mod mini_batch, mini_batch <= 16).  seq_len must be a multiple of 128; other shapes, global
+ *   rotary positions and the shared-QK layout go through ttt_gemm_bf16_tn + ttt_layer_prologue. */
+int ttt_layer_projections(const ttt_dims* d, const void* x, int64_t x_ld, int64_t hidden, const void* weights,
+                          int64_t w_ld, int64_t w_rows, int64_t q_col, int64_t k_col, int64_t v_col, int64_t g_col,
+                          int64_t lr_col, const void* lr_bias, int start_idx, int rope_mode, float rope_theta,
+                          float base_lr, void* xq, void* xk, void* xv, void* gate, void* ttt_lr_eta, void* status,
+                          void* stream);
+
 /* Gradients of the two layer steps (training; the reference gets them from Burn autodiff over the same tensor ops).
  *
  * ttt_layer_prologue_backward: gradients of XQ, XK, XV [B,H,T,F] and of ttt_lr_eta [B,H,T] -> gradient of the

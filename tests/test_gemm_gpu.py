@@ -61,3 +61,56 @@ def test_gemm_rejects_bad_arguments():
     assert lib.ttt_gemm_bf16_tn(8, 8, 8, fake, 4, fake, 8, fake, 8, None, None) == _lib.TTT_ERR_SHAPE
     assert lib.ttt_gemm_bf16_tn(8, 8, 8, fake, 12, fake, 8, fake, 8, None, None) == _lib.TTT_ERR_ALIGN
     assert lib.ttt_gemm_bf16_tn(8, 8, 8, None, 8, fake, 8, fake, 8, None, None) == _lib.TTT_ERR_NULL
+
+
+@pytest.mark.parametrize("use_gate,pos,start", ((False, "rope", 0), (True, "rope", 37), (True, "none", 0)))
+def test_fused_projections_match_gemm_then_prologue_and_the_restatement(use_gate, pos, start):
+    """`ttt_layer_projections` (GEMM with the head split, rotary rotation and learning-rate gate in its epilogue)
+    against the float64 restatement on the same bf16 operands, and against the two-launch path (GEMM, then
+    ttt_layer_prologue) it replaces."""
+    import ttt_rs_b200 as tb
+    from oracle import ttt_layer_oracle as LO
+    dev = torch.device("cuda:0")
+    B, T, H = 2, 256, 3
+    Cc = H * 64
+    g = torch.Generator().manual_seed(9)
+    x = (torch.randn(B, T, Cc, generator=g) * 0.5).to(torch.bfloat16)
+    blocks = {n: (torch.randn(Cc, Cc, generator=g) * Cc ** -0.5).to(torch.bfloat16) for n in ("q", "k", "v")}
+    if use_gate:
+        blocks["g"] = (torch.randn(Cc, Cc, generator=g) * Cc ** -0.5).to(torch.bfloat16)
+    lrw = (torch.randn(H, Cc, generator=g) * 0.02).to(torch.bfloat16)
+    lr_bias = (torch.randn(H, generator=g) * 0.1).to(torch.bfloat16)
+    cols, off, rows = {}, 0, []
+    for n, w in blocks.items():
+        cols[n] = off
+        off += Cc
+        rows.append(w)
+    cols["lr"] = off
+    rows += [lrw, torch.zeros((-(off + H)) % 8, Cc, dtype=torch.bfloat16)]
+    wcat = torch.cat(rows, dim=0).contiguous()
+    cfg = tb.TTTLayerConfig(hidden_size=Cc, num_heads=H, use_gate=use_gate, pos_encoding=pos)
+    xq, xk, xv, lr, gate = tb.layer_projections(x.to(dev), wcat.to(dev), cols, cfg, lr_bias.to(dev), start)
+    tb.check_status()
+
+    # float64 restatement on the bf16 operands
+    proj = x.double() @ wcat.double().t()
+    heads = lambda t: t.reshape(B, T, H, 64).permute(0, 2, 1, 3)  # noqa: E731
+    wq, wk, wv = (heads(proj[..., cols[n]:cols[n] + Cc]) for n in ("q", "k", "v"))
+    if pos == "rope":
+        posv = (start + torch.arange(T)) % 16
+        wq, wk = LO.rope_pairs(wq, posv, 10000.0), LO.rope_pairs(wk, posv, 10000.0)
+    wlr = torch.sigmoid(proj[..., cols["lr"]:cols["lr"] + H].permute(0, 2, 1) + lr_bias.double().reshape(1, H, 1)) / 64
+    for name, got, want in (("xq", xq, wq), ("xk", xk, wk), ("xv", xv, wv), ("ttt_lr_eta", lr, wlr)):
+        assert_close(got, want, 4e-3, f"fused projections: {name}")
+    if use_gate:
+        assert_close(gate.reshape(B, T, Cc), proj[..., cols["g"]:cols["g"] + Cc], 4e-3, "fused projections: gate")
+    else:
+        assert gate is None
+
+    # the two-launch path rounds the projection to bf16 before rotating: same values to bf16 rounding
+    p2 = tb.gemm_bf16_tn(x.reshape(B * T, Cc).to(dev), wcat.to(dev)).reshape(B, T, -1)
+    uq, uk, uv, ulr = tb.layer_prologue(p2, cfg, q_col=cols["q"], k_col=cols["k"], v_col=cols["v"], lr_col=cols["lr"],
+                                        lr_bias=lr_bias.to(dev), start_idx=start)
+    assert torch.equal(uv, xv), "v is a pure copy of the product in both paths"
+    assert_close(xq, uq.double(), 1.6e-2, "fused vs two-launch: xq")
+    assert_close(lr, ulr.double(), 1.6e-2, "fused vs two-launch: ttt_lr_eta")

@@ -25,4 +25,4 @@ from .fused import (  # noqa: F401
     fused_ttt_tile_forward_multi,
     packed_outer_grad_len,
 )
-from .layer import TTT, DecodeGraphs, TTTLayerConfig, gemm_bf16_tn, layer_epilogue, layer_prologue, new_inner  # noqa: F401,E402
+from .layer import TTT, DecodeGraphs, TTTLayerConfig, gemm_bf16_tn, layer_epilogue, layer_projections, layer_prologue, new_inner  # noqa: F401,E402

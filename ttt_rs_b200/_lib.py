@@ -72,6 +72,9 @@ SYMBOLS = {
                                               _P, _P, C.c_size_t, _P]),
     "ttt_layer_epilogue": (C.c_int, [_DP, _P, _P, C.c_int64, _P, _P, C.c_float, _P, _P]),
     "ttt_gemm_bf16_tn": (C.c_int, [C.c_int64, C.c_int64, C.c_int64, _P, C.c_int64, _P, C.c_int64, _P, C.c_int64, _P, _P]),
+    "ttt_layer_projections": (C.c_int, [_DP, _P, C.c_int64, C.c_int64, _P, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                        C.c_int64, C.c_int64, C.c_int64, _P, C.c_int, C.c_int, C.c_float, C.c_float,
+                                        _P, _P, _P, _P, _P, _P, _P]),
     "ttt_layer_qk_conv": (C.c_int, [_DP, _P, C.c_int64, _P, _P, _P, _P, _P, _P, _P]),
     "ttt_layer_qk_conv_backward_workspace_bytes": (C.c_size_t, [_DP]),
     "ttt_layer_qk_conv_backward": (C.c_int, [_DP, _P, _P, _P, C.c_int64, _P, _P, _P, _P, _P, _P, C.c_size_t, _P]),

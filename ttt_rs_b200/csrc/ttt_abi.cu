@@ -198,17 +198,80 @@ int ttt_gemm_bf16_tn(int64_t m, int64_t n, int64_t k, const void* a, int64_t lda
   const NamedPtr ptrs[] = {{"a", a}, {"b", b}, {"c", c}};
   int rc = check_ptrs(ptrs, 3);
   if (rc != TTT_OK) return rc;
-  CUtensorMap maps[3];
+  CUtensorMap maps[7];
   if ((rc = make_gemm_map(&maps[0], a, m, k, lda)) != TTT_OK) return rc;
   if ((rc = make_gemm_map(&maps[1], b, n, k, ldb)) != TTT_OK) return rc;
   if ((rc = make_gemm_map(&maps[2], c, m, n, ldc)) != TTT_OK) return rc;
-  ttt::GemmParams p;
+  for (int i = 3; i < 7; ++i) maps[i] = maps[2];
+  ttt::GemmParams p{};
   p.M = (int)m;
   p.N = (int)n;
   p.K = (int)k;
   p.status = static_cast<uint32_t*>(status);
-  cudaError_t e = ttt::launch_gemm_bf16_tn(maps, p, static_cast<cudaStream_t>(stream));
+  cudaError_t e = ttt::launch_gemm_bf16_tn(maps, p, false, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "GEMM launch failed: %s", cudaGetErrorString(e));
+  return TTT_OK;
+}
+
+int ttt_layer_projections(const ttt_dims* d, const void* x, int64_t x_ld, int64_t hidden, const void* weights,
+                          int64_t w_ld, int64_t w_rows, int64_t q_col, int64_t k_col, int64_t v_col, int64_t g_col,
+                          int64_t lr_col, const void* lr_bias, int start_idx, int rope_mode, float rope_theta,
+                          float base_lr, void* xq, void* xk, void* xv, void* gate, void* ttt_lr_eta, void* status,
+                          void* stream) {
+  if (d == nullptr) return fail(TTT_ERR_NULL, "dims is null");
+  if (d->batch <= 0 || d->heads <= 0 || d->seq_len <= 0) return fail(TTT_ERR_SHAPE, "batch, heads, seq_len must be positive");
+  if (d->dtype != TTT_BF16 || d->head_dim != 64)
+    return fail(TTT_ERR_UNSUPPORTED, "the fused projection is built for bf16 and head_dim 64");
+  if (d->seq_len % 128 != 0)
+    return fail(TTT_ERR_UNSUPPORTED, "the fused projection needs seq_len %% 128 == 0 (got %d): use ttt_gemm_bf16_tn + "
+                                     "ttt_layer_prologue", d->seq_len);
+  if (d->heads > 64) return fail(TTT_ERR_UNSUPPORTED, "at most 64 heads");
+  if (rope_mode != 0 && rope_mode != 1)
+    return fail(TTT_ERR_UNSUPPORTED, "the fused projection rotates with wrapped positions (rope_mode 1) or not at all");
+  if (rope_mode == 1 && (d->mini_batch < 1 || d->mini_batch > 16))
+    return fail(TTT_ERR_UNSUPPORTED, "wrapped rotary positions need 1 <= mini_batch <= 16 here (got %d)", d->mini_batch);
+  if (rope_mode == 1 && !(rope_theta > 0.f)) return fail(TTT_ERR_SHAPE, "rope_theta must be positive");
+  if (start_idx < 0) return fail(TTT_ERR_SHAPE, "start_idx must be >= 0");
+  const int64_t C = (int64_t)d->heads * 64, M = (int64_t)d->batch * d->seq_len;
+  if (hidden <= 0 || w_rows <= 0 || x_ld < hidden || w_ld < hidden || ((x_ld | w_ld) & 7) != 0)
+    return fail(TTT_ERR_SHAPE, "hidden, pitches: x_ld and w_ld must be >= hidden and multiples of 8");
+  const int64_t cols[5] = {q_col, k_col, v_col, g_col, lr_col};
+  for (int i = 0; i < 5; ++i) {
+    if (i == 3 && g_col < 0) continue;
+    if (cols[i] < 0 || (cols[i] & 63) != 0 || cols[i] + (i == 4 ? d->heads : C) > w_rows)
+      return fail(TTT_ERR_SHAPE, "column block %d starts at %lld: must be a multiple of 64 inside the %lld weight rows",
+                  i, (long long)cols[i], (long long)w_rows);
+  }
+  if ((g_col >= 0) != (gate != nullptr)) return fail(TTT_ERR_NULL, "gate buffer and g_col must be given together");
+  const NamedPtr ptrs[] = {{"x", x}, {"weights", weights}, {"xq", xq}, {"xk", xk}, {"xv", xv}, {"ttt_lr_eta", ttt_lr_eta}};
+  int rc = check_ptrs(ptrs, 6);
+  if (rc != TTT_OK) return rc;
+  const int64_t rows = (int64_t)d->batch * d->heads * d->seq_len;
+  if (rows >= ((int64_t)1 << 31) || M >= ((int64_t)1 << 31)) return fail(TTT_ERR_SHAPE, "batch*heads*seq_len must be below 2^31");
+  CUtensorMap maps[7];
+  if ((rc = make_gemm_map(&maps[0], x, M, hidden, x_ld)) != TTT_OK) return rc;
+  if ((rc = make_gemm_map(&maps[1], weights, w_rows, hidden, w_ld)) != TTT_OK) return rc;
+  if ((rc = make_gemm_map(&maps[3], xq, rows, 64, 64)) != TTT_OK) return rc;
+  if ((rc = make_gemm_map(&maps[4], xk, rows, 64, 64)) != TTT_OK) return rc;
+  if ((rc = make_gemm_map(&maps[5], xv, rows, 64, 64)) != TTT_OK) return rc;
+  if (gate != nullptr) {
+    if ((rc = make_gemm_map(&maps[6], gate, M, C, C)) != TTT_OK) return rc;
+  } else {
+    maps[6] = maps[5];
+  }
+  maps[2] = maps[3];
+  ttt::GemmParams p{};
+  p.M = (int)M;
+  p.N = (int)w_rows;
+  p.K = (int)hidden;
+  p.status = static_cast<uint32_t*>(status);
+  p.f.q_col = (int)q_col; p.f.k_col = (int)k_col; p.f.v_col = (int)v_col; p.f.g_col = (int)g_col; p.f.lr_col = (int)lr_col;
+  p.f.H = d->heads; p.f.T = d->seq_len;
+  p.f.start_idx = start_idx; p.f.pos_mod = rope_mode == 1 ? d->mini_batch : 1; p.f.rope_mode = rope_mode;
+  p.f.rope_theta = rope_mode == 1 ? rope_theta : 1.f; p.f.base_lr = base_lr;
+  p.f.lr_bias = lr_bias; p.f.lr_out = ttt_lr_eta;
+  cudaError_t e = ttt::launch_gemm_bf16_tn(maps, p, true, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "fused projection launch failed: %s", cudaGetErrorString(e));
   return TTT_OK;
 }
 

@@ -15,7 +15,16 @@
 //     tcgen05.ld, converts to bf16, writes a swizzled staging tile in the (by then idle) stage buffers, and one thread
 //     stores the tile with TMA (rows / columns beyond M / N are clipped by the tensor map).
 // Two CTAs fit on an SM (3 x 32 KB stages, 128 of 512 tensor-memory columns each), so one tile's epilogue overlaps the
-// other's main loop.  No thread-block cluster, no multicast.
+// other's main loop.  Every CTA is on its own: no thread-block cluster, each CTA loads its own operands.
+//
+// Fused form (ttt_layer_projections): the same main loop over the layer's stacked q | k | v | (g) | lr weights, with
+// the step that follows the projections in the layer folded into the epilogue -- what `get_qkv` / `get_lr` do with the
+// projection output (rust/layer/src/ttt.rs:152-227): every 64-column half of a tile is one head of q, k, v or the
+// gate, or the block of learning-rate logits.  q and k halves are rotated (rotary pairs are adjacent columns, so a
+// pair sits in one thread's registers, still in float32) and stored as XQ / XK [B,H,T,F]; v halves go to XV, gate
+// halves to a [B*T, H*F] buffer, logits become ttt_lr_eta[b,h,t] = base_lr / F * sigmoid(logit + bias).  The
+// [B*T, N] projection output is never written.  Needs seq_len % 128 == 0 (a tile's 128 tokens then belong to one
+// batch element and land in 128 consecutive rows of [B*H*T, F]).
 //
 // Every mbarrier wait is bounded: on expiry the role sets a flag, everybody falls through to the common exit, tensor
 // memory is freed and the status words get {TTT_ERR_TIMEOUT, where, block, k-block}.
@@ -33,7 +42,8 @@ struct GemmSmem {
   static constexpr uint32_t OFF_B = GEMM_STAGES * GEMM_TILE_BYTES;
   static constexpr uint32_t OFF_BAR = 2 * GEMM_STAGES * GEMM_TILE_BYTES;  // full[S], empty[S], acc
   static constexpr uint32_t OFF_TMEM = OFF_BAR + (2 * GEMM_STAGES + 1) * 8;
-  static constexpr uint32_t TOTAL = OFF_TMEM + 8;
+  static constexpr uint32_t OFF_ROPE = OFF_TMEM + 8;  // fused epilogue: (cos, sin) for 16 positions x 32 pairs
+  static constexpr uint32_t TOTAL = OFF_ROPE + 16 * 32 * 8;
   static constexpr uint32_t DYN_BYTES = TOTAL + 1024;
 };
 
@@ -76,9 +86,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// FUSED: tm_c is unused; tm_o0..3 are the stores of XQ, XK, XV ([B*H*T, 64] views) and of the gate buffer.
+template <bool FUSED>
 __global__ void __launch_bounds__(GEMM_THREADS, 2)
     ttt_gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                            const __grid_constant__ CUtensorMap tm_c, const GemmParams p) {
+                            const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_o0,
+                            const __grid_constant__ CUtensorMap tm_o1, const __grid_constant__ CUtensorMap tm_o2,
+                            const __grid_constant__ CUtensorMap tm_o3, const GemmParams p) {
   using SM = GemmSmem;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_u32 = smem_u32(smem_raw);
@@ -96,7 +110,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2)
   if (tid == 0) {
     prefetch_tmap(&tm_a);
     prefetch_tmap(&tm_b);
-    prefetch_tmap(&tm_c);
+    if (FUSED) {
+      prefetch_tmap(&tm_o0);
+      prefetch_tmap(&tm_o1);
+      prefetch_tmap(&tm_o2);
+      prefetch_tmap(&tm_o3);
+    } else {
+      prefetch_tmap(&tm_c);
+    }
     for (int i = 0; i < 2 * GEMM_STAGES + 1; ++i) mbar_init(bar_full + 8 * i, 1);
     fence_mbar_init();
     s_fail = 0;
@@ -153,6 +174,43 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2)
     // ---------------- epilogue: 4 warps, warp w reads the tensor-memory lanes of quarter w % 4
     const int q = warp & 3;
     const int row = 32 * q + lane;
+    // fused: what each 64-column half of this tile is (0 q, 1 k, 2 v, 3 gate, 4 learning-rate logits, -1 nothing)
+    int kind[2] = {-1, -1}, head[2] = {0, 0};
+    const float2* rope_tab = reinterpret_cast<const float2*>(gbase + SM::OFF_ROPE);
+    int pos = 0, tok = 0, bat = 0;
+    if (FUSED) {
+      const int C = p.f.H * 64;
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int col0 = n0 + 64 * hf;
+        if (col0 >= p.f.q_col && col0 < p.f.q_col + C) {
+          kind[hf] = 0; head[hf] = (col0 - p.f.q_col) >> 6;
+        } else if (col0 >= p.f.k_col && col0 < p.f.k_col + C) {
+          kind[hf] = 1; head[hf] = (col0 - p.f.k_col) >> 6;
+        } else if (col0 >= p.f.v_col && col0 < p.f.v_col + C) {
+          kind[hf] = 2; head[hf] = (col0 - p.f.v_col) >> 6;
+        } else if (p.f.g_col >= 0 && col0 >= p.f.g_col && col0 < p.f.g_col + C) {
+          kind[hf] = 3; head[hf] = (col0 - p.f.g_col) >> 6;
+        } else if (col0 == p.f.lr_col) {
+          kind[hf] = 4;
+        }
+      }
+      tok = (m0 + row) % p.f.T;
+      bat = (m0 + row) / p.f.T;
+      if (p.f.rope_mode == 1) {
+        // (cos, sin) of position x pair, positions taken modulo the mini-batch length (at most 16 here)
+        const float log2_theta = log2f(p.f.rope_theta);
+        float2* tab = reinterpret_cast<float2*>(gbase + SM::OFF_ROPE);
+        for (int e = tid - 64; e < p.f.pos_mod * 32; e += 128) {
+          const int ps = e >> 5, i = e & 31;
+          float sn, cs;
+          sincosf(ps * exp2f(-(2.f * i / 64.f) * log2_theta), &sn, &cs);
+          tab[e] = make_float2(cs, sn);
+        }
+        pos = (p.f.start_idx + tok) % p.f.pos_mod;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+    }
     const bool ok = mbar_wait_bounded(bar_acc, 0);
     if (!ok) {
       s_fail = 1;
@@ -164,6 +222,34 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2)
       for (int c = 0; c < GEMM_BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld32(tmem + ((uint32_t)(32 * q) << 16) + 32 * c, r);
+        if (FUSED) {
+          const int kd = kind[c >> 1];
+          if (kd < 0) continue;
+          if (kd == 4) {
+            // learning-rate logits: column j of this half is head j
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int h = 32 * (c & 1) + i;
+              if (h < p.f.H) {
+                float z = __uint_as_float(r[i]);
+                if (p.f.lr_bias != nullptr) z += __bfloat162float(static_cast<const __nv_bfloat16*>(p.f.lr_bias)[h]);
+                static_cast<__nv_bfloat16*>(p.f.lr_out)[((size_t)bat * p.f.H + h) * p.f.T + tok] =
+                    __float2bfloat16_rn(p.f.base_lr * (1.f / 64.f) / (1.f + expf(-z)));
+              }
+            }
+            continue;
+          }
+          if (kd <= 1 && p.f.rope_mode == 1) {
+            const float2* cs = rope_tab + pos * 32 + 16 * (c & 1);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float x0 = __uint_as_float(r[2 * j]), x1 = __uint_as_float(r[2 * j + 1]);
+              const float2 w = cs[j];
+              r[2 * j] = __float_as_uint(x0 * w.x - x1 * w.y);
+              r[2 * j + 1] = __float_as_uint(x1 * w.x + x0 * w.y);
+            }
+          }
+        }
         // staging: two [128 rows][64 columns] bf16 tiles in the swizzled layout the TMA store expects, in the first
         // two A stages (every product has completed, so the ring is idle)
         const uint32_t tile = base + SM::OFF_A + (c >> 1) * GEMM_TILE_BYTES;
@@ -183,8 +269,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2)
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
     if (warp == 2 && lane == 0 && s_fail == 0) {
-      tma_store_2d(&tm_c, n0, m0, base + SM::OFF_A);
-      if (n0 + 64 < p.N) tma_store_2d(&tm_c, n0 + 64, m0, base + SM::OFF_A + GEMM_TILE_BYTES);
+      if (FUSED) {
+        const int t0 = m0 % p.f.T, b0 = m0 / p.f.T;
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const uint32_t src = base + SM::OFF_A + hf * GEMM_TILE_BYTES;
+          const int y = (b0 * p.f.H + head[hf]) * p.f.T + t0;  // first of 128 consecutive rows of [B*H*T, 64]
+          if (kind[hf] == 0) tma_store_2d(&tm_o0, 0, y, src);
+          if (kind[hf] == 1) tma_store_2d(&tm_o1, 0, y, src);
+          if (kind[hf] == 2) tma_store_2d(&tm_o2, 0, y, src);
+          if (kind[hf] == 3) tma_store_2d(&tm_o3, 64 * head[hf], m0, src);
+        }
+      } else {
+        tma_store_2d(&tm_c, n0, m0, base + SM::OFF_A);
+        if (n0 + 64 < p.N) tma_store_2d(&tm_c, n0 + 64, m0, base + SM::OFF_A + GEMM_TILE_BYTES);
+      }
       bulk_commit();
       bulk_wait_all<0>();
     }
@@ -194,13 +293,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2)
   if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 128;" ::"r"(tmem) : "memory");
 }
 
-cudaError_t launch_gemm_bf16_tn(const CUtensorMap* maps, const GemmParams& p, cudaStream_t st) {
-  auto kfn = ttt_gemm_bf16_tn_kernel;
+template <bool FUSED>
+static cudaError_t launch_gemm_t(const CUtensorMap* m, const GemmParams& p, cudaStream_t st) {
+  auto kfn = ttt_gemm_bf16_tn_kernel<FUSED>;
   cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmSmem::DYN_BYTES);
   if (e != cudaSuccess) return e;
   dim3 grid((p.N + GEMM_BN - 1) / GEMM_BN, (p.M + GEMM_BM - 1) / GEMM_BM);
-  kfn<<<grid, GEMM_THREADS, GemmSmem::DYN_BYTES, st>>>(maps[0], maps[1], maps[2], p);
+  kfn<<<grid, GEMM_THREADS, GemmSmem::DYN_BYTES, st>>>(m[0], m[1], m[2], m[3], m[4], m[5], m[6], p);
   return cudaGetLastError();
+}
+
+// maps: A, B, C (plain) or A, B, -, XQ, XK, XV, gate (fused: p.f filled in)
+cudaError_t launch_gemm_bf16_tn(const CUtensorMap* maps, const GemmParams& p, bool fused, cudaStream_t st) {
+  return fused ? launch_gemm_t<true>(maps, p, st) : launch_gemm_t<false>(maps, p, st);
 }
 
 }  // namespace ttt

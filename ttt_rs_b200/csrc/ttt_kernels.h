@@ -261,11 +261,22 @@ size_t mlp_bwd_ws_stride_floats(int T);
 cudaError_t launch_mlp_bwd(const MlpBwdParams& p, int B, cudaStream_t st);
 
 // bf16 projection GEMM C[M,N] = A[M,K] . B[N,K]^T on tcgen05 (ttt_gemm.cu).  maps: A, B (loads, box 64 x 128), C (store).
+// Fused epilogue of the layer's stacked projection (ttt_layer_projections): where the column blocks of the product
+// start (multiples of 64; g_col < 0 = no gate) and where their results go.
+struct GemmFuse {
+  int q_col, k_col, v_col, g_col, lr_col;
+  int H, T;                 // heads, tokens per sequence (T % 128 == 0)
+  int start_idx, pos_mod, rope_mode;  // rope_mode 0 none, 1 positions (start_idx + t) mod pos_mod, pos_mod <= 16
+  float rope_theta, base_lr;
+  const void* lr_bias;      // [H] bf16 or null
+  void* lr_out;             // ttt_lr_eta [B,H,T] bf16
+};
 struct GemmParams {
   int M, N, K;
   uint32_t* status;  // optional 4 words
+  GemmFuse f;        // read by the fused kernel only
 };
-cudaError_t launch_gemm_bf16_tn(const CUtensorMap* maps, const GemmParams& p, cudaStream_t st);
+cudaError_t launch_gemm_bf16_tn(const CUtensorMap* maps, const GemmParams& p, bool fused, cudaStream_t st);
 
 // bf16 only.  maps: q, k, v, out.
 cudaError_t launch_mlp_fwd(const CUtensorMap* maps, const MlpFwdParams& p, int nstreams, cudaStream_t st);

@@ -139,6 +139,34 @@ def gemm_bf16_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return c
 
 
+def layer_projections(x: torch.Tensor, wcat: torch.Tensor, cols, cfg: TTTLayerConfig, lr_bias: Optional[torch.Tensor],
+                      start_idx: int = 0):
+    """All projections of the layer plus the prologue in ONE launch (`ttt_layer_projections`: the tcgen05 GEMM with the
+    head split, rotary rotation and learning-rate gate in its epilogue).  x [B, T, hidden] bf16, wcat the stacked
+    q | k | v | (g) | lr weight rows with their starts in `cols`.  Returns xq, xk, xv [B,H,T,F], ttt_lr_eta [B,H,T] and
+    the gate buffer [B*T, H*F] (None without a gate)."""
+    from .fused import device_status
+    lib = _lib.load()
+    B, T, hidden = x.shape
+    H, F = cfg.num_heads, cfg.head_dim
+    dev = x.device
+    x2 = x.reshape(B * T, hidden)
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    xq, xk, xv = (torch.empty(B, H, T, F, dtype=x.dtype, device=dev) for _ in range(3))
+    lr = torch.empty(B, H, T, dtype=x.dtype, device=dev)
+    gate = torch.empty(B * T, H * F, dtype=x.dtype, device=dev) if "g" in cols else None
+    d = TttDims(B, H, T, F, cfg.mini_batch_size, 1, 0.0, _dtype_code(x.dtype))
+    bias = None if lr_bias is None else lr_bias.detach().reshape(-1).to(x.dtype).contiguous()
+    stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    with torch.cuda.device(dev):
+        _lib.check(lib.ttt_layer_projections(
+            C.byref(d), _ptr(x2), x2.stride(0), hidden, _ptr(wcat), wcat.stride(0), wcat.shape[0], cols["q"], cols["k"],
+            cols["v"], cols.get("g", -1), cols["lr"], _ptr(bias), start_idx, _POS[cfg.pos_encoding], cfg.rope_theta,
+            cfg.base_lr, _ptr(xq), _ptr(xk), _ptr(xv), _ptr(gate), _ptr(lr), _ptr(device_status(dev)), stream))
+    return xq, xk, xv, lr, gate
+
+
 class _PrologueFn(torch.autograd.Function):
     """`ttt_layer_prologue` with its gradient `ttt_layer_prologue_backward` (layout q | k | v | lr logits | padding,
     no shared-QK convolutions)."""
@@ -354,35 +382,45 @@ class TTT(torch.nn.Module):
             return gemm_bf16_tn(x.reshape(-1, x.shape[-1]), weight).reshape(*x.shape[:-1], weight.shape[0])
         return torch.matmul(x, weight.t())
 
+    def _can_fuse_projections(self, x: torch.Tensor, cols) -> bool:
+        """The one-launch projection + prologue covers bf16, sequence lengths that are multiples of 128, separate q / k
+        projections, wrapped or no rotary positions with a mini-batch of at most 16 tokens, and column blocks that
+        start on multiples of 64."""
+        c = self.config
+        return (x.dtype == torch.bfloat16 and x.is_cuda and x.shape[1] % 128 == 0 and not c.share_qk
+                and c.head_dim == 64 and c.hidden_size % 8 == 0 and c.num_heads <= 64
+                and c.pos_encoding in ("none", "rope") and c.mini_batch_size <= 16
+                and all(v % 64 == 0 for v in cols.values()))
+
     def get_inner_loop_inputs(self, x: torch.Tensor, start_idx: int):
-        """Hidden states -> (TTTInputsInner, projection output, column map) (rust/layer/src/ttt.rs:250-267)."""
+        """Hidden states -> (TTTInputsInner, gate operand, gate pitch) (rust/layer/src/ttt.rs:250-267).  The gate
+        operand is a [B*T, pitch] view whose first H*F columns are x . g_proj^T (None without a gate)."""
         c = self.config
         B, T, _ = x.shape
         wcat, cols = self._fused_weight()
+        te = torch.clamp_min(self.token_idx + self.learnable_token_idx, 0.0)
+        token_eta = te.repeat((T + c.mini_batch_size - 1) // c.mini_batch_size)[:T].to(x.dtype)
+        if self._can_fuse_projections(x, cols):
+            xq, xk, xv, lr, gate = layer_projections(x, wcat, cols, c, self.learnable_ttt_lr_bias, start_idx)
+            return TTTInputsInner(Qkv(xq, xk, xv), token_eta, lr, start_idx), gate, c.num_heads * c.head_dim
         proj = self._project(x, wcat)  # [B, T, N]: every projection of the token in one product
         conv = None
         if c.share_qk:
             conv = (self.q_conv_weight, self.q_conv_bias, self.k_conv_weight, self.k_conv_bias)
         xq, xk, xv, lr = layer_prologue(proj, c, q_col=cols["q"], k_col=cols["k"], v_col=cols["v"], lr_col=cols["lr"],
                                         lr_bias=self.learnable_ttt_lr_bias, conv=conv, start_idx=start_idx)
-        te = torch.clamp_min(self.token_idx + self.learnable_token_idx, 0.0)
-        token_eta = te.repeat((T + c.mini_batch_size - 1) // c.mini_batch_size)[:T].to(x.dtype)
-        return TTTInputsInner(Qkv(xq, xk, xv), token_eta, lr, start_idx), proj, cols
+        gate = proj.reshape(B * T, -1)[:, cols["g"]:] if c.use_gate else None
+        return TTTInputsInner(Qkv(xq, xk, xv), token_eta, lr, start_idx), gate, proj.shape[-1]
 
     def forward(self, x: torch.Tensor, inner: FusedTileMultiTTTLinear, state: TTTLinearState,
                 start_idx: int = 0) -> torch.Tensor:
         """x [B, T, hidden] -> [B, T, hidden]; `state` is advanced in place (rust/layer/src/ttt.rs:269-299)."""
         if torch.is_grad_enabled():
             return self._forward_train(x, inner, state, start_idx)
-        c = self.config
-        B, T, _ = x.shape
-        inputs, proj, cols = self.get_inner_loop_inputs(x, start_idx)
+        inputs, gate, gate_ld = self.get_inner_loop_inputs(x, start_idx)
         out = inner.forward(state, inputs)  # [B, H, T, F]
-        gate, gate_ld = None, 0
-        if c.use_gate:
-            gate = proj.reshape(B * T, -1)[:, cols["g"]:]
-            gate_ld = proj.shape[-1]
-        y = layer_epilogue(out.contiguous(), self.post_norm_weight, self.post_norm_bias, 1e-6, gate, gate_ld)
+        y = layer_epilogue(out.contiguous(), self.post_norm_weight, self.post_norm_bias, 1e-6, gate,
+                           gate_ld if gate is not None else 0)
         return self._project(y, self.o_proj.detach())
 
 
