@@ -101,7 +101,9 @@ size_t ttt_linear_bias_ckpt_bytes(const ttt_dims* d);
  *   output          T [B,H,T,F]   (out)
  *   weight_out      T [B,H,F,F]   (out) final state
  *   bias_out        T [B,H,F]     (out)
- *   weight_ckpt, bias_ckpt        (out) opaque saved state, ttt_linear_*_ckpt_bytes bytes each
+ *   weight_ckpt, bias_ckpt        (out) opaque saved state, ttt_linear_*_ckpt_bytes bytes each; pass BOTH as NULL
+ *                                 for inference: nothing is then kept for a backward (no checkpoints, gradient tiles
+ *                                 or statistics are written -- about a third of the forward's HBM writes)
  */
 int ttt_linear_forward(const ttt_dims* d, const void* xq, const void* xk, const void* xv, const void* weight,
                        const void* bias, const void* token_eta, const void* ttt_lr_eta, const void* ln_weight,

@@ -125,3 +125,22 @@ def test_inner_model_interface_chains_state():
     assert_close(s2.weight, s1.weight, 2e-2, "chained weight")
     with pytest.raises(AssertionError):
         model.forward_mini_batch(model.init_state(2), mk(slice(0, 64)), range(0, 8))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_inference_forward_keeps_no_state_and_gives_the_same_bits(dtype):
+    """`save_state=False` (what `torch.no_grad()` selects): the kernel writes no checkpoints, gradient tiles or
+    statistics; output and final state are bit-identical to the training forward's."""
+    import ttt_rs_b200 as tb
+    dev = torch.device("cuda:0")
+    t = O.make_inputs(2, 3, 160, 64, 16, seed=12, dtype=dtype, with_grad_output=False)
+    cfg = tb.FusedTttConfig.new(16, 64, 1e-6, 128, 4)
+    ins = tb.TttInputs(*[t[k].to(dev) for k in LIN_IN])
+    a, saved = tb.TttTileMultiKernel.forward_launch(ins, cfg)
+    b, none = tb.TttTileMultiKernel.forward_launch(ins, cfg, save_state=False)
+    tb.check_status()
+    assert saved is not None and none is None
+    assert torch.equal(a.output, b.output) and torch.equal(a.weight, b.weight) and torch.equal(a.bias, b.bias)
+    with torch.no_grad():
+        out, w, _ = tb.fused_ttt_tile_forward_multi(*[t[k].to(dev) for k in LIN_IN], cfg)
+    assert torch.equal(out, a.output) and torch.equal(w, a.weight)

@@ -306,7 +306,9 @@ int ttt_linear_forward(const ttt_dims* d, const void* xq, const void* xk, const 
                            {"ln_bias", ln_bias}, {"output", output},
                            {"weight_out", weight_out}, {"bias_out", bias_out},
                            {"weight_ckpt", weight_ckpt}, {"bias_ckpt", bias_ckpt}};
-  rc = check_ptrs(ptrs, sizeof(ptrs) / sizeof(ptrs[0]));
+  // inference: both saved-state buffers null = nothing is kept for a backward
+  const bool save = weight_ckpt != nullptr || bias_ckpt != nullptr;
+  rc = check_ptrs(ptrs, (int)(sizeof(ptrs) / sizeof(ptrs[0])) - (save ? 0 : 2));
   if (rc != TTT_OK) return rc;
   if (status != nullptr && (reinterpret_cast<uintptr_t>(status) & 3u) != 0)
     return fail(TTT_ERR_ALIGN, "status is not 4-byte aligned");
@@ -315,7 +317,7 @@ int ttt_linear_forward(const ttt_dims* d, const void* xq, const void* xk, const 
   const AuxLayout al = aux_layout(d);
   uint8_t* aux = static_cast<uint8_t*>(bias_ckpt);
   CUtensorMap maps[5];
-  const void* bases[5] = {xq, xk, xv, output, aux + al.off_gp};
+  const void* bases[5] = {xq, xk, xv, output, save ? static_cast<const void*>(aux + al.off_gp) : output};
   for (int i = 0; i < 5; ++i) {
     rc = make_tile_map(&maps[i], bases[i], rows, d->dtype);
     if (rc != TTT_OK) return rc;
@@ -330,8 +332,8 @@ int ttt_linear_forward(const ttt_dims* d, const void* xq, const void* xk, const 
   p.w_out = weight_out;
   p.b_out = bias_out;
   p.w_ckpt = static_cast<float*>(weight_ckpt);
-  p.stats = reinterpret_cast<float4*>(aux + al.off_stats);
-  p.b_stage = reinterpret_cast<float*>(aux + al.off_bias);
+  p.stats = save ? reinterpret_cast<float4*>(aux + al.off_stats) : nullptr;
+  p.b_stage = save ? reinterpret_cast<float*>(aux + al.off_bias) : nullptr;
   p.status = static_cast<uint32_t*>(status);
   p.H = d->heads;
   p.T = d->seq_len;

@@ -42,8 +42,11 @@ struct GemmSmem {
   static constexpr uint32_t OFF_B = GEMM_STAGES * GEMM_TILE_BYTES;
   static constexpr uint32_t OFF_BAR = 2 * GEMM_STAGES * GEMM_TILE_BYTES;  // full[S], empty[S], acc
   static constexpr uint32_t OFF_TMEM = OFF_BAR + (2 * GEMM_STAGES + 1) * 8;
-  static constexpr uint32_t OFF_ROPE = OFF_TMEM + 8;  // fused epilogue: (cos, sin) for 16 positions x 32 pairs
-  static constexpr uint32_t TOTAL = OFF_ROPE + 16 * 32 * 8;
+  // fused epilogue: (cos, sin) for 16 positions x 32 pairs; rows padded to 33 entries so that the 16 rows the lanes
+  // of a warp read (consecutive tokens = consecutive positions) fall in distinct banks
+  static constexpr uint32_t OFF_ROPE = OFF_TMEM + 8;
+  static constexpr uint32_t ROPE_ROW = 33;
+  static constexpr uint32_t TOTAL = OFF_ROPE + 16 * ROPE_ROW * 8;
   static constexpr uint32_t DYN_BYTES = TOTAL + 1024;
 };
 
@@ -205,7 +208,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2)
           const int ps = e >> 5, i = e & 31;
           float sn, cs;
           sincosf(ps * exp2f(-(2.f * i / 64.f) * log2_theta), &sn, &cs);
-          tab[e] = make_float2(cs, sn);
+          tab[ps * SM::ROPE_ROW + i] = make_float2(cs, sn);
         }
         pos = (p.f.start_idx + tok) % p.f.pos_mod;
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -240,13 +243,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2)
             continue;
           }
           if (kd <= 1 && p.f.rope_mode == 1) {
-            const float2* cs = rope_tab + pos * 32 + 16 * (c & 1);
+            const float2* cs = rope_tab + pos * SM::ROPE_ROW + 16 * (c & 1);
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              const float x0 = __uint_as_float(r[2 * j]), x1 = __uint_as_float(r[2 * j + 1]);
+              // (x0, x1) -> (x0 c - x1 s, x1 c + x0 s) as two packed float32x2 operations
+              const F2 x = f2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
               const float2 w = cs[j];
-              r[2 * j] = __float_as_uint(x0 * w.x - x1 * w.y);
-              r[2 * j + 1] = __float_as_uint(x1 * w.x + x0 * w.y);
+              const F2 y = f2fma(f2(-x.y, x.x), f2(w.y), f2mul(x, f2(w.x)));
+              r[2 * j] = __float_as_uint(y.x);
+              r[2 * j + 1] = __float_as_uint(y.y);
             }
           }
         }
@@ -285,7 +290,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2)
         if (n0 + 64 < p.N) tma_store_2d(&tm_c, n0 + 64, m0, base + SM::OFF_A + GEMM_TILE_BYTES);
       }
       bulk_commit();
-      bulk_wait_all<0>();
+      bulk_wait_read<0>();  // the staging tiles must stay until the stores have read them; the writes finish on their own
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

@@ -61,6 +61,9 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
   const int head = stream % p.H;
   const int NS = p.NS;
   const int row_base = stream * p.T;  // first row of this stream in the [B*H*T, 64] view
+  // inference launches pass no saved-state buffers: nothing is kept for a backward (no checkpoints, gradient tiles,
+  // row statistics or per-stage biases are written)
+  const bool save = (p.w_ckpt != nullptr);
 
   if (tid == 0) {
     prefetch_tmap(&tm_q);
@@ -142,14 +145,14 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     }
 
     // ---- saved state: W before the update of every K-th stage, the bias before every stage
-    if (s % p.K == 0) {
+    if (save && s % p.K == 0) {
       float* wc = p.w_ckpt + ((size_t)stream * (p.NCK + 1) + s / p.K) * HD * HD;
 #pragma unroll
       for (int kt = 0; kt < 8; ++kt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) wc[(8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1)] = wt[kt][i] * wscale;
     }
-    if (g == 0) {
+    if (save && g == 0) {
       float* bs = p.b_stage + ((size_t)stream * (NS + 1) + s) * HD;
 #pragma unroll
       for (int j = 0; j < 4; ++j) bs[nb + 8 * (j >> 1) + 2 * t + (j & 1)] = bias[j];
@@ -230,10 +233,12 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
         const Pk<NP> pkd = split_pack<NP>(gp[nt][r].x, gp[nt][r].y);
-        if constexpr (NP == 1) {
-          asm volatile("st.shared.b32 [%0], %1;" ::"r"(sg + off_bf16(g + 8 * r, nb + 8 * nt + 2 * t)), "r"(pkd.p[0]) : "memory");
-        } else {
-          st_pair<T>(sg, g + 8 * r, nb + 8 * nt + 2 * t, gp[nt][r].x, gp[nt][r].y);
+        if (save) {
+          if constexpr (NP == 1) {
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(sg + off_bf16(g + 8 * r, nb + 8 * nt + 2 * t)), "r"(pkd.p[0]) : "memory");
+          } else {
+            st_pair<T>(sg, g + 8 * r, nb + 8 * nt + 2 * t, gp[nt][r].x, gp[nt][r].y);
+          }
         }
         gt[nt][r] = movm_t_np<NP>(pkd);
       }
@@ -285,7 +290,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     F2 zb[2][2];
     slab_pairs(zq, zb);
     ln_row_stats<TWO_PASS>(zb, xch, xsel, L, p.eps, mean, rstd, fl2);
-    if (L.warp == 0 && t == 0) {
+    if (save && L.warp == 0 && t == 0) {
       float4* sp = p.stats + ((size_t)row_base + (size_t)s * CS) * 2;
       sp[2 * g] = st1[0];
       sp[2 * g + 1] = make_float4(mean[0], rstd[0], 0.f, 0.f);
@@ -306,7 +311,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     __syncthreads();
     if (tid == 0) {
       tma_store_tile<T>(&tm_o, row_base + s * CS, so);
-      tma_store_tile<T>(&tm_g, row_base + s * CS, sg);
+      if (save) tma_store_tile<T>(&tm_g, row_base + s * CS, sg);
       bulk_commit();
       bulk_wait_read<1>();
       if (s + FWD_NST < NS) issue_loads(s + FWD_NST);
@@ -321,21 +326,21 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
 
   if (!failed) {
     // ---- final state (returned, and kept as the last checkpoint / last bias record for the backward)
-    float* wc = p.w_ckpt + ((size_t)stream * (p.NCK + 1) + p.NCK) * HD * HD;
+    float* wc = save ? p.w_ckpt + ((size_t)stream * (p.NCK + 1) + p.NCK) * HD * HD : nullptr;
 #pragma unroll
     for (int kt = 0; kt < 8; ++kt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int idx = (8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1);
         st_from_float<T>(p.w_out, (size_t)stream * HD * HD + idx, wt[kt][i] * wscale);
-        wc[idx] = wt[kt][i] * wscale;
+        if (save) wc[idx] = wt[kt][i] * wscale;
       }
     if (g == 0) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int c = nb + 8 * (j >> 1) + 2 * t + (j & 1);
         st_from_float<T>(p.b_out, (size_t)stream * HD + c, bias[j]);
-        p.b_stage[((size_t)stream * (NS + 1) + NS) * HD + c] = bias[j];
+        if (save) p.b_stage[((size_t)stream * (NS + 1) + NS) * HD + c] = bias[j];
       }
     }
   }

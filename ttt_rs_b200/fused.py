@@ -205,7 +205,9 @@ class TttTileMultiKernel:
     """The multi-stage tiled TTT-Linear operator: one launch walks every mini-batch of the sequence."""
 
     @staticmethod
-    def forward_launch(inputs: TttInputs, config: FusedTttConfig) -> Tuple[TttOutputs, TttSavedStateMulti]:
+    def forward_launch(inputs: TttInputs, config: FusedTttConfig,
+                       save_state: bool = True) -> Tuple[TttOutputs, Optional[TttSavedStateMulti]]:
+        """`save_state=False` (inference): nothing is kept for a backward and the second return value is None."""
         if config.mini_batch_len <= 0:
             raise TttError(_lib.TTT_ERR_SHAPE, "mini_batch_len must be set for TttTileMultiKernel")
         lib = _lib.load()
@@ -222,9 +224,11 @@ class TttTileMultiKernel:
         bias_out = torch.empty_like(inputs.bias)
         # opaque saved state, sized by the library: float32 W at every checkpoint (+ the final W), and one buffer
         # holding the per-stage lr-scaled LN gradient tiles, row statistics and biases
-        w_ck = torch.empty(lib.ttt_linear_weight_ckpt_bytes(C.byref(d)) // 4, dtype=torch.float32,
-                           device=dev).view(B * H * (nck + 1), F, F)
-        b_ck = torch.empty(lib.ttt_linear_bias_ckpt_bytes(C.byref(d)), dtype=torch.uint8, device=dev)
+        w_ck = b_ck = None
+        if save_state:
+            w_ck = torch.empty(lib.ttt_linear_weight_ckpt_bytes(C.byref(d)) // 4, dtype=torch.float32,
+                               device=dev).view(B * H * (nck + 1), F, F)
+            b_ck = torch.empty(lib.ttt_linear_bias_ckpt_bytes(C.byref(d)), dtype=torch.uint8, device=dev)
         status = device_status(dev)
         with torch.cuda.device(dev):
             rc = lib.ttt_linear_forward(
@@ -233,6 +237,8 @@ class TttTileMultiKernel:
                 _ptr(inputs.ln_bias), _ptr(output), _ptr(weight_out), _ptr(bias_out), _ptr(w_ck), _ptr(b_ck),
                 _ptr(status), _stream_ptr(dev))
         _lib.check(rc)
+        if not save_state:
+            return TttOutputs(output, weight_out, bias_out), None
         saved = TttSavedStateMulti(inputs.xq, inputs.xk, inputs.xv, inputs.weight, inputs.bias, inputs.token_eta,
                                    inputs.ttt_lr_eta, inputs.ln_weight, inputs.ln_bias, w_ck, b_ck, status)
         return TttOutputs(output, weight_out, bias_out), saved
@@ -334,7 +340,12 @@ class _FusedTttTileMultiFn(torch.autograd.Function):
 
 def fused_ttt_tile_forward_multi(xq, xk, xv, weight, bias, token_eta, ttt_lr_eta, ln_weight, ln_bias,
                                  config: FusedTttConfig):
-    """(output, weight_updated, bias_updated); differentiable w.r.t. the nine tensor inputs through `output`."""
+    """(output, weight_updated, bias_updated); differentiable w.r.t. the nine tensor inputs through `output`.
+    Under `torch.no_grad()` the forward keeps nothing for a backward."""
+    if not torch.is_grad_enabled():
+        outs, _ = TttTileMultiKernel.forward_launch(
+            TttInputs(xq, xk, xv, weight, bias, token_eta, ttt_lr_eta, ln_weight, ln_bias), config, save_state=False)
+        return outs.output, outs.weight, outs.bias
     return _FusedTttTileMultiFn.apply(xq, xk, xv, weight, bias, token_eta, ttt_lr_eta, ln_weight, ln_bias, config)
 
 
