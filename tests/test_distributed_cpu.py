@@ -79,3 +79,20 @@ def test_two_ranks_allreduce_matches_single_process():
     for r in range(world):
         # the packed buffer is float32 by definition
         assert torch.allclose(ret[r], full, rtol=1e-5, atol=1e-6 * full.abs().max().item()), f"rank {r}"
+
+
+def test_benchmark_shards_are_the_batch_rows_of_the_same_tensors():
+    """`bench.py --gpus N` (strong scaling) gives rank r the rows [r B/N, (r+1) B/N) of the seed-0 tensors: the shards
+    tile the batch, per-stream tensors are cut, shared parameters are passed whole."""
+    import sys
+    from pathlib import Path
+    sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+    import bench
+    t = O.make_inputs(8, 2, 32, 64, 16, seed=0, dtype=torch.float32)
+    world = 4
+    parts = [bench.shard_rows(t, *D.shard_batch(8, r, world)) for r in range(world)]
+    for k, v in t.items():
+        if v.dim() >= 3:
+            assert torch.equal(torch.cat([p[k] for p in parts], dim=0), v), k
+        else:
+            assert all(p[k] is v for p in parts), k
