@@ -4,18 +4,20 @@
 // This is the product behind the reference layer's `Linear` projections q/k/v/g, the per-head learning-rate weights
 // and o_proj (rust/layer/src/ttt.rs:152-227,289-299), which it gets from Burn's matmul.
 //
-// One CTA computes one 128 x 128 tile of C:
+// Persistent CTAs (one per SM) walk the 128 x 128 tiles of C, n fastest (the CTAs running at one time share a few
+// row blocks of A through L2; B stays L2-resident):
 //   * warp 0 (one lane) is the TMA producer: A and B tiles of 128 rows x 64 k (128-byte rows, 128-byte swizzle) into
-//     a ring of GEMM_STAGES shared-memory stages, completion counted in bytes on the stage's `full` mbarrier;
+//     a ring of GEMM_STAGES shared-memory stages that never drains between tiles, completion counted in bytes on the
+//     stage's `full` mbarrier;
 //   * warp 1 (one lane) issues tcgen05.mma (cta_group::1, kind::f16, M = 128, N = 128, K = 16): operands by
-//     shared-memory descriptor, accumulator 128 lanes x 128 columns of float32 in tensor memory; after the four
-//     k-steps of a stage a tcgen05.commit on the stage's `empty` mbarrier hands the stage back to the producer, and
-//     after the last stage a commit on `acc` releases the epilogue;
+//     shared-memory descriptor, accumulators in tensor memory -- TWO buffers of 128 lanes x 128 float32 columns, used
+//     alternately; after the four k-steps of a stage a tcgen05.commit on the stage's `empty` mbarrier hands the stage
+//     back to the producer, and after a tile's last stage a commit on `acc_full[buffer]` releases the epilogue;
 //   * warps 2-5 are the epilogue: each reads its quarter of the tensor-memory lanes (one row per thread) with
-//     tcgen05.ld, converts to bf16, writes a swizzled staging tile in the (by then idle) stage buffers, and one thread
-//     stores the tile with TMA (rows / columns beyond M / N are clipped by the tensor map).
-// Two CTAs fit on an SM (3 x 32 KB stages, 128 of 512 tensor-memory columns each), so one tile's epilogue overlaps the
-// other's main loop.  Every CTA is on its own: no thread-block cluster, each CTA loads its own operands.
+//     tcgen05.ld, converts to bf16, writes a swizzled staging tile and one thread stores it with TMA (rows / columns
+//     beyond M / N are clipped by the tensor map); `acc_empty[buffer]` then gives the accumulator back.  So the
+//     epilogue of tile i runs under the main loop of tile i + 1.
+// Every CTA is on its own: no thread-block cluster, each CTA loads its own operands.
 //
 // Fused form (ttt_layer_projections): the same main loop over the layer's stacked q | k | v | (g) | lr weights, with
 // the step that follows the projections in the layer folded into the epilogue -- what `get_qkv` / `get_lr` do with the
@@ -33,15 +35,16 @@
 
 namespace ttt {
 
-constexpr int GEMM_BM = 128, GEMM_BN = 128, GEMM_BK = 64, GEMM_STAGES = 3;
+constexpr int GEMM_BM = 128, GEMM_BN = 128, GEMM_BK = 64, GEMM_STAGES = 5;
 constexpr uint32_t GEMM_TILE_BYTES = GEMM_BM * GEMM_BK * 2;  // 16 KB: one operand tile of a stage
 constexpr int GEMM_THREADS = 192;
 
 struct GemmSmem {
   static constexpr uint32_t OFF_A = 0;
   static constexpr uint32_t OFF_B = GEMM_STAGES * GEMM_TILE_BYTES;
-  static constexpr uint32_t OFF_BAR = 2 * GEMM_STAGES * GEMM_TILE_BYTES;  // full[S], empty[S], acc
-  static constexpr uint32_t OFF_TMEM = OFF_BAR + (2 * GEMM_STAGES + 1) * 8;
+  static constexpr uint32_t OFF_STG = 2 * GEMM_STAGES * GEMM_TILE_BYTES;  // epilogue staging: two [128][64] bf16 tiles
+  static constexpr uint32_t OFF_BAR = OFF_STG + 2 * GEMM_TILE_BYTES;      // full[S], empty[S], acc_full[2], acc_empty[2]
+  static constexpr uint32_t OFF_TMEM = OFF_BAR + (2 * GEMM_STAGES + 4) * 8;
   // fused epilogue: (cos, sin) for 16 positions x 32 pairs; rows padded to 33 entries so that the 16 rows the lanes
   // of a warp read (consecutive tokens = consecutive positions) fall in distinct banks
   static constexpr uint32_t OFF_ROPE = OFF_TMEM + 8;
@@ -89,9 +92,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
 // FUSED: tm_c is unused; tm_o0..3 are the stores of XQ, XK, XV ([B*H*T, 64] views) and of the gate buffer.
 template <bool FUSED>
-__global__ void __launch_bounds__(GEMM_THREADS, 2)
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
     ttt_gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                             const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_o0,
                             const __grid_constant__ CUtensorMap tm_o1, const __grid_constant__ CUtensorMap tm_o2,
@@ -102,13 +109,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2)
   const uint32_t base = (raw_u32 + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (base - raw_u32);
   const uint32_t bar_full = base + SM::OFF_BAR, bar_empty = bar_full + 8 * GEMM_STAGES,
-                 bar_acc = bar_empty + 8 * GEMM_STAGES;
+                 bar_acc_full = bar_empty + 8 * GEMM_STAGES, bar_acc_empty = bar_acc_full + 16;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gbase + SM::OFF_TMEM);
   __shared__ int s_fail;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n0 = blockIdx.x * GEMM_BN, m0 = blockIdx.y * GEMM_BM;
   const int KB = (p.K + GEMM_BK - 1) / GEMM_BK;
+  const int tiles_n = (p.N + GEMM_BN - 1) / GEMM_BN, tiles_m = (p.M + GEMM_BM - 1) / GEMM_BM;
+  const int ntiles = tiles_n * tiles_m;
 
   if (tid == 0) {
     prefetch_tmap(&tm_a);
@@ -121,12 +129,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2)
     } else {
       prefetch_tmap(&tm_c);
     }
-    for (int i = 0; i < 2 * GEMM_STAGES + 1; ++i) mbar_init(bar_full + 8 * i, 1);
+    for (int i = 0; i < 2 * GEMM_STAGES + 4; ++i) mbar_init(bar_full + 8 * i, 1);
     fence_mbar_init();
     s_fail = 0;
   }
-  if (warp == 1) {  // tensor memory: 128 columns of float32 accumulators (the same warp frees them at the end)
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 128;" ::"r"(base + SM::OFF_TMEM)
+  if (warp == 1) {  // tensor memory: two accumulators of 128 float32 columns (the same warp frees them at the end)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(base + SM::OFF_TMEM)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -136,166 +144,209 @@ __global__ void __launch_bounds__(GEMM_THREADS, 2)
   const uint32_t tmem = *tmem_slot;
 
   if (warp == 0) {
-    // ---------------- TMA producer
+    // ---------------- TMA producer: one ring over all the tiles of this CTA
     if (lane == 0) {
-      for (int kb = 0; kb < KB; ++kb) {
-        const int st = kb % GEMM_STAGES;
-        if (kb >= GEMM_STAGES && !mbar_wait_bounded(bar_empty + 8 * st, ((kb / GEMM_STAGES) - 1) & 1)) {
-          s_fail = 1;
-          report_timeout(p.status, 31, kb);
-          break;
+      uint32_t it = 0;  // k-blocks issued so far
+      for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const int m0 = (tile / tiles_n) * GEMM_BM, n0 = (tile % tiles_n) * GEMM_BN;
+        bool ok = true;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const uint32_t st = it % GEMM_STAGES;
+          if (it >= GEMM_STAGES && !mbar_wait_bounded(bar_empty + 8 * st, ((it / GEMM_STAGES) - 1) & 1)) {
+            s_fail = 1;
+            report_timeout(p.status, 31, kb);
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(bar_full + 8 * st, 2 * GEMM_TILE_BYTES);
+          tma_load_2d(base + SM::OFF_A + st * GEMM_TILE_BYTES, &tm_a, kb * GEMM_BK, m0, bar_full + 8 * st);
+          tma_load_2d(base + SM::OFF_B + st * GEMM_TILE_BYTES, &tm_b, kb * GEMM_BK, n0, bar_full + 8 * st);
         }
-        mbar_expect_tx(bar_full + 8 * st, 2 * GEMM_TILE_BYTES);
-        tma_load_2d(base + SM::OFF_A + st * GEMM_TILE_BYTES, &tm_a, kb * GEMM_BK, m0, bar_full + 8 * st);
-        tma_load_2d(base + SM::OFF_B + st * GEMM_TILE_BYTES, &tm_b, kb * GEMM_BK, n0, bar_full + 8 * st);
+        if (!ok) break;
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_bf16(GEMM_BM, GEMM_BN);
-      bool ok = true;
-      for (int kb = 0; kb < KB && ok; ++kb) {
-        const int st = kb % GEMM_STAGES;
-        if (!mbar_wait_bounded(bar_full + 8 * st, (kb / GEMM_STAGES) & 1)) {
+      uint32_t it = 0, tl = 0;  // k-blocks consumed, tiles started
+      for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tl) {
+        const uint32_t buf = tl & 1;
+        bool ok = true;
+        // the epilogue must have drained this accumulator (its previous use was two tiles ago)
+        if (tl >= 2 && !mbar_wait_bounded(bar_acc_empty + 8 * buf, ((tl >> 1) - 1) & 1)) {
           s_fail = 1;
-          report_timeout(p.status, 32, kb);
-          ok = false;
+          report_timeout(p.status, 34, tl);
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = base + SM::OFF_A + st * GEMM_TILE_BYTES, b_addr = base + SM::OFF_B + st * GEMM_TILE_BYTES;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const uint32_t st = it % GEMM_STAGES;
+          if (!mbar_wait_bounded(bar_full + 8 * st, (it / GEMM_STAGES) & 1)) {
+            s_fail = 1;
+            report_timeout(p.status, 32, kb);
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = base + SM::OFF_A + st * GEMM_TILE_BYTES, b_addr = base + SM::OFF_B + st * GEMM_TILE_BYTES;
 #pragma unroll
-        for (int ks = 0; ks < GEMM_BK / 16; ++ks)  // 32 bytes per k-step inside the swizzled 128-byte rows
-          umma_bf16(tmem, umma_desc_sw128(a_addr + 32 * ks), umma_desc_sw128(b_addr + 32 * ks), idesc,
-                    (kb | ks) != 0 ? 1u : 0u);
-        umma_commit(bar_empty + 8 * st);  // the stage is free once these products have read it
+          for (int ks = 0; ks < GEMM_BK / 16; ++ks)  // 32 bytes per k-step inside the swizzled 128-byte rows
+            umma_bf16(tmem + buf * GEMM_BN, umma_desc_sw128(a_addr + 32 * ks), umma_desc_sw128(b_addr + 32 * ks), idesc,
+                      (kb | ks) != 0 ? 1u : 0u);
+          umma_commit(bar_empty + 8 * st);  // the stage is free once these products have read it
+        }
+        if (!ok) break;
+        umma_commit(bar_acc_full + 8 * buf);  // arrives when every product of this tile is complete
       }
-      umma_commit(bar_acc);  // arrives when every product issued above is complete (at once if none was issued)
     }
   } else {
     // ---------------- epilogue: 4 warps, warp w reads the tensor-memory lanes of quarter w % 4
     const int q = warp & 3;
     const int row = 32 * q + lane;
-    // fused: what each 64-column half of this tile is (0 q, 1 k, 2 v, 3 gate, 4 learning-rate logits, -1 nothing)
-    int kind[2] = {-1, -1}, head[2] = {0, 0};
     const float2* rope_tab = reinterpret_cast<const float2*>(gbase + SM::OFF_ROPE);
-    int pos = 0, tok = 0, bat = 0;
-    if (FUSED) {
-      const int C = p.f.H * 64;
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        const int col0 = n0 + 64 * hf;
-        if (col0 >= p.f.q_col && col0 < p.f.q_col + C) {
-          kind[hf] = 0; head[hf] = (col0 - p.f.q_col) >> 6;
-        } else if (col0 >= p.f.k_col && col0 < p.f.k_col + C) {
-          kind[hf] = 1; head[hf] = (col0 - p.f.k_col) >> 6;
-        } else if (col0 >= p.f.v_col && col0 < p.f.v_col + C) {
-          kind[hf] = 2; head[hf] = (col0 - p.f.v_col) >> 6;
-        } else if (p.f.g_col >= 0 && col0 >= p.f.g_col && col0 < p.f.g_col + C) {
-          kind[hf] = 3; head[hf] = (col0 - p.f.g_col) >> 6;
-        } else if (col0 == p.f.lr_col) {
-          kind[hf] = 4;
-        }
+    if (FUSED && p.f.rope_mode == 1) {
+      // (cos, sin) of position x pair, positions taken modulo the mini-batch length (at most 16 here)
+      const float log2_theta = log2f(p.f.rope_theta);
+      float2* tab = reinterpret_cast<float2*>(gbase + SM::OFF_ROPE);
+      for (int e = tid - 64; e < p.f.pos_mod * 32; e += 128) {
+        const int ps = e >> 5, i = e & 31;
+        float sn, cs;
+        sincosf(ps * exp2f(-(2.f * i / 64.f) * log2_theta), &sn, &cs);
+        tab[ps * SM::ROPE_ROW + i] = make_float2(cs, sn);
       }
-      tok = (m0 + row) % p.f.T;
-      bat = (m0 + row) / p.f.T;
-      if (p.f.rope_mode == 1) {
-        // (cos, sin) of position x pair, positions taken modulo the mini-batch length (at most 16 here)
-        const float log2_theta = log2f(p.f.rope_theta);
-        float2* tab = reinterpret_cast<float2*>(gbase + SM::OFF_ROPE);
-        for (int e = tid - 64; e < p.f.pos_mod * 32; e += 128) {
-          const int ps = e >> 5, i = e & 31;
-          float sn, cs;
-          sincosf(ps * exp2f(-(2.f * i / 64.f) * log2_theta), &sn, &cs);
-          tab[ps * SM::ROPE_ROW + i] = make_float2(cs, sn);
-        }
-        pos = (p.f.start_idx + tok) % p.f.pos_mod;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
     }
-    const bool ok = mbar_wait_bounded(bar_acc, 0);
-    if (!ok) {
-      s_fail = 1;
-      if (lane == 0) report_timeout(p.status, 33, 0);
-    }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok && s_fail == 0) {
-#pragma unroll
-      for (int c = 0; c < GEMM_BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tmem + ((uint32_t)(32 * q) << 16) + 32 * c, r);
-        if (FUSED) {
-          const int kd = kind[c >> 1];
-          if (kd < 0) continue;
-          if (kd == 4) {
-            // learning-rate logits: column j of this half is head j
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int h = 32 * (c & 1) + i;
-              if (h < p.f.H) {
-                float z = __uint_as_float(r[i]);
-                if (p.f.lr_bias != nullptr) z += __bfloat162float(static_cast<const __nv_bfloat16*>(p.f.lr_bias)[h]);
-                static_cast<__nv_bfloat16*>(p.f.lr_out)[((size_t)bat * p.f.H + h) * p.f.T + tok] =
-                    __float2bfloat16_rn(p.f.base_lr * (1.f / 64.f) / (1.f + expf(-z)));
-              }
-            }
-            continue;
-          }
-          if (kd <= 1 && p.f.rope_mode == 1) {
-            const float2* cs = rope_tab + pos * SM::ROPE_ROW + 16 * (c & 1);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              // (x0, x1) -> (x0 c - x1 s, x1 c + x0 s) as two packed float32x2 operations
-              const F2 x = f2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-              const float2 w = cs[j];
-              const F2 y = f2fma(f2(-x.y, x.x), f2(w.y), f2mul(x, f2(w.x)));
-              r[2 * j] = __float_as_uint(y.x);
-              r[2 * j + 1] = __float_as_uint(y.y);
-            }
-          }
-        }
-        // staging: two [128 rows][64 columns] bf16 tiles in the swizzled layout the TMA store expects, in the first
-        // two A stages (every product has completed, so the ring is idle)
-        const uint32_t tile = base + SM::OFF_A + (c >> 1) * GEMM_TILE_BYTES;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int chunk = (c & 1) * 4 + i;  // 16-byte chunk of the 128-byte row
-          const uint32_t v0 = pack_bf16(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
-          const uint32_t v1 = pack_bf16(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
-          const uint32_t v2 = pack_bf16(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
-          const uint32_t v3 = pack_bf16(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
-          asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(tile + row * 128 + ((chunk ^ (row & 7)) << 4)),
-                       "r"(v0), "r"(v1), "r"(v2), "r"(v3)
-                       : "memory");
-        }
-      }
-      fence_proxy_async_smem();
-    }
-    asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
-    if (warp == 2 && lane == 0 && s_fail == 0) {
+    uint32_t tl = 0;
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tl) {
+      const int m0 = (tile / tiles_n) * GEMM_BM, n0 = (tile % tiles_n) * GEMM_BN;
+      const uint32_t buf = tl & 1;
+      // fused: what each 64-column half of this tile is (0 q, 1 k, 2 v, 3 gate, 4 learning-rate logits, -1 nothing)
+      int kind[2] = {-1, -1}, head[2] = {0, 0};
+      int pos = 0, tok = 0, bat = 0;
       if (FUSED) {
-        const int t0 = m0 % p.f.T, b0 = m0 / p.f.T;
+        const int C = p.f.H * 64;
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
-          const uint32_t src = base + SM::OFF_A + hf * GEMM_TILE_BYTES;
-          const int y = (b0 * p.f.H + head[hf]) * p.f.T + t0;  // first of 128 consecutive rows of [B*H*T, 64]
-          if (kind[hf] == 0) tma_store_2d(&tm_o0, 0, y, src);
-          if (kind[hf] == 1) tma_store_2d(&tm_o1, 0, y, src);
-          if (kind[hf] == 2) tma_store_2d(&tm_o2, 0, y, src);
-          if (kind[hf] == 3) tma_store_2d(&tm_o3, 64 * head[hf], m0, src);
+          const int col0 = n0 + 64 * hf;
+          if (col0 >= p.f.q_col && col0 < p.f.q_col + C) {
+            kind[hf] = 0; head[hf] = (col0 - p.f.q_col) >> 6;
+          } else if (col0 >= p.f.k_col && col0 < p.f.k_col + C) {
+            kind[hf] = 1; head[hf] = (col0 - p.f.k_col) >> 6;
+          } else if (col0 >= p.f.v_col && col0 < p.f.v_col + C) {
+            kind[hf] = 2; head[hf] = (col0 - p.f.v_col) >> 6;
+          } else if (p.f.g_col >= 0 && col0 >= p.f.g_col && col0 < p.f.g_col + C) {
+            kind[hf] = 3; head[hf] = (col0 - p.f.g_col) >> 6;
+          } else if (col0 == p.f.lr_col) {
+            kind[hf] = 4;
+          }
         }
-      } else {
-        tma_store_2d(&tm_c, n0, m0, base + SM::OFF_A);
-        if (n0 + 64 < p.N) tma_store_2d(&tm_c, n0 + 64, m0, base + SM::OFF_A + GEMM_TILE_BYTES);
+        tok = (m0 + row) % p.f.T;
+        bat = (m0 + row) / p.f.T;
+        pos = (p.f.start_idx + tok) % p.f.pos_mod;
       }
-      bulk_commit();
-      bulk_wait_read<0>();  // the staging tiles must stay until the stores have read them; the writes finish on their own
+      bool ok = mbar_wait_bounded(bar_acc_full + 8 * buf, (tl >> 1) & 1);
+      if (!ok) {
+        s_fail = 1;
+        if (lane == 0) report_timeout(p.status, 33, tl);
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // the previous tile's stores must have read the staging tiles before they are overwritten
+      if (warp == 2 && lane == 0) bulk_wait_read<0>();
+      {
+        // barrier of the four epilogue warps that also agrees on failure: every thread leaves with the same verdict
+        const uint32_t mine = (!ok || s_fail != 0) ? 1u : 0u;
+        uint32_t any;
+        asm volatile(
+            "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.or.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+            : "=r"(any)
+            : "r"(mine)
+            : "memory");
+        ok = (any == 0);
+      }
+      if (ok) {
+#pragma unroll
+        for (int c = 0; c < GEMM_BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tmem + ((uint32_t)(32 * q) << 16) + buf * GEMM_BN + 32 * c, r);
+          if (FUSED) {
+            const int kd = kind[c >> 1];
+            if (kd < 0) continue;
+            if (kd == 4) {
+              // learning-rate logits: column j of this half is head j
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const int h = 32 * (c & 1) + i;
+                if (h < p.f.H) {
+                  float z = __uint_as_float(r[i]);
+                  if (p.f.lr_bias != nullptr) z += __bfloat162float(static_cast<const __nv_bfloat16*>(p.f.lr_bias)[h]);
+                  static_cast<__nv_bfloat16*>(p.f.lr_out)[((size_t)bat * p.f.H + h) * p.f.T + tok] =
+                      __float2bfloat16_rn(p.f.base_lr * (1.f / 64.f) / (1.f + expf(-z)));
+                }
+              }
+              continue;
+            }
+            if (kd <= 1 && p.f.rope_mode == 1) {
+              const float2* cs = rope_tab + pos * SM::ROPE_ROW + 16 * (c & 1);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                // (x0, x1) -> (x0 c - x1 s, x1 c + x0 s) as two packed float32x2 operations
+                const F2 x = f2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                const float2 w = cs[j];
+                const F2 y = f2fma(f2(-x.y, x.x), f2(w.y), f2mul(x, f2(w.x)));
+                r[2 * j] = __float_as_uint(y.x);
+                r[2 * j + 1] = __float_as_uint(y.y);
+              }
+            }
+          }
+          // staging: two [128 rows][64 columns] bf16 tiles in the swizzled layout the TMA store expects
+          const uint32_t stg = base + SM::OFF_STG + (c >> 1) * GEMM_TILE_BYTES;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int chunk = (c & 1) * 4 + i;  // 16-byte chunk of the 128-byte row
+            const uint32_t v0 = pack_bf16(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+            const uint32_t v1 = pack_bf16(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+            const uint32_t v2 = pack_bf16(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+            const uint32_t v3 = pack_bf16(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(stg + row * 128 + ((chunk ^ (row & 7)) << 4)),
+                         "r"(v0), "r"(v1), "r"(v2), "r"(v3)
+                         : "memory");
+          }
+        }
+        fence_proxy_async_smem();
+      }
+      // every tcgen05.ld of this accumulator has completed (wait::ld above): hand it back, then store the tile
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (warp == 2 && lane == 0) {
+        mbar_arrive(bar_acc_empty + 8 * buf);
+        if (ok) {
+          const uint32_t s0 = base + SM::OFF_STG, s1 = s0 + GEMM_TILE_BYTES;
+          if (FUSED) {
+            const int t0 = m0 % p.f.T, b0 = m0 / p.f.T;
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+              const uint32_t src = hf ? s1 : s0;
+              const int y = (b0 * p.f.H + head[hf]) * p.f.T + t0;  // first of 128 consecutive rows of [B*H*T, 64]
+              if (kind[hf] == 0) tma_store_2d(&tm_o0, 0, y, src);
+              if (kind[hf] == 1) tma_store_2d(&tm_o1, 0, y, src);
+              if (kind[hf] == 2) tma_store_2d(&tm_o2, 0, y, src);
+              if (kind[hf] == 3) tma_store_2d(&tm_o3, 64 * head[hf], m0, src);
+            }
+          } else {
+            tma_store_2d(&tm_c, n0, m0, s0);
+            if (n0 + 64 < p.N) tma_store_2d(&tm_c, n0 + 64, m0, s1);
+          }
+          bulk_commit();
+        }
+      }
+      if (!ok) break;
     }
+    if (warp == 2 && lane == 0) bulk_wait_read<0>();  // the staging tiles must outlive the last stores' reads
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 128;" ::"r"(tmem) : "memory");
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem) : "memory");
 }
 
 template <bool FUSED>
@@ -303,7 +354,11 @@ static cudaError_t launch_gemm_t(const CUtensorMap* m, const GemmParams& p, cuda
   auto kfn = ttt_gemm_bf16_tn_kernel<FUSED>;
   cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmSmem::DYN_BYTES);
   if (e != cudaSuccess) return e;
-  dim3 grid((p.N + GEMM_BN - 1) / GEMM_BN, (p.M + GEMM_BM - 1) / GEMM_BM);
+  int dev = 0, sms = 0;
+  if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+  if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+  const long ntiles = (long)((p.N + GEMM_BN - 1) / GEMM_BN) * ((p.M + GEMM_BM - 1) / GEMM_BM);
+  const int grid = (int)(ntiles < sms ? ntiles : sms);  // persistent: one CTA per SM walks the tiles
   kfn<<<grid, GEMM_THREADS, GemmSmem::DYN_BYTES, st>>>(m[0], m[1], m[2], m[3], m[4], m[5], m[6], p);
   return cudaGetLastError();
 }
