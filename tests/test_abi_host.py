@@ -161,7 +161,7 @@ def test_partial_and_layer_entry_points_validate_their_arguments(lib):
 
 
 def test_rust_declarations_in_the_integration_guide_match_the_header():
-    """INTEGRATION.md carries the Rust `extern "C"` block a maintainer would paste; it is generated from the header.
+    """The integration guide carries the Rust `extern "C"` block a maintainer would paste; it is generated from the header.
     The committed text must equal a fresh generation, and every declaration must have as many arguments as the
     ctypes table that the tests call through."""
     import sys

@@ -1,6 +1,6 @@
 """Long-context TTT-Linear at the 1.3B layer shape (32 heads x 64, bf16, checkpoint interval 16; sequence lengths
 8192 and 32768 = 512 and 2048 chained mini-batches).  The reference's own tests stop at T = 2048
-(rust/fused/src/linear_fused_tile/tests.rs:95-102), so at these lengths the float64 oracle is the only judge.  The
+(rust/fused/src/linear_fused_tile/tests.rs:95-102), so at these lengths the float64 oracle is the only yardstick.  The
 backward walks the state back from each checkpoint with the saved gradient tiles; these cases are the evidence that
 its rounding drift stays bounded by one checkpoint interval however long the chain is."""
 
