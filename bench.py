@@ -662,7 +662,11 @@ def bench_inner(tb, w, host, dev, world, rank, args, name):
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         ms, fwd_ms = tmax[0].item(), tmax[1].item()
         bwd_ms = tmax[2].item() if w["backward"] else None
-    return {"ms": ms, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "clocks": clocks, "cfg": cfg, "mlp": mlp}
+    # per-step device time (first launch of the step to its last), for the median / minimum the reference's own
+    # benchmark protocol reports (rust/cli/src/bench.rs:175-190)
+    per_step = sorted(e[0].elapsed_time(e[2] if w["backward"] else e[1]) for e in ev_pairs)
+    return {"ms": ms, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "clocks": clocks, "cfg": cfg, "mlp": mlp,
+            "median_ms": statistics.median(per_step), "min_ms": per_step[0]}
 
 
 def roofline_of(w, res, name):
@@ -827,6 +831,7 @@ def main():
                        "l2": "inputs exceed L2: each step streams %.0f MB of operands per GPU"
                              % (roof["step"].get("algorithmic_bytes", 0) / 1e6) if not mlp else
                              "inputs exceed L2 (%.0f MB of operands per step)" % (algorithmic_bytes(w_rank)[0] / 1e6)},
+            "ms_per_step_median": res["median_ms"], "ms_per_step_min": res["min_ms"],
             "clocks": res["clocks"], "e2e": e2e,
             "gpu_launches": args.steps * ((3 if mlp else 4) if w["backward"] else 1),
             "roofline": roof,

@@ -49,10 +49,25 @@ def test_checkpoint_and_workspace_sizes(lib):
         streams * 1 * 128 + streams * 80 + streams * (4096 + 64) + streams * (2 * 4096 + 64) + 8)
 
 
+def test_sizes_for_head_dim_32(lib):
+    """Two 32-wide heads share a 64-wide tile: saved state is sized per pair, per-head results per head."""
+    d = _dims(head_dim=32, heads=4, seq_len=80, checkpoint_interval=2)
+    pairs, heads_all, ns = 2 * 2, 2 * 4, 5
+    assert lib.ttt_linear_num_checkpoints(C.byref(d)) == 3
+    assert lib.ttt_linear_weight_ckpt_bytes(C.byref(d)) == pairs * (3 + 1) * 64 * 64 * 4
+    rows = pairs * 80
+    assert lib.ttt_linear_bias_ckpt_bytes(C.byref(d)) == rows * 64 * 2 + rows * 64 + pairs * (ns + 1) * 64 * 4
+    assert lib.ttt_linear_backward_workspace_bytes(C.byref(d)) == 4 * (
+        pairs * 1 * 128 + heads_all * 80 + heads_all * (1024 + 32) + pairs * (2 * 4096 + 64) + 8)
+    # the TTT-MLP kernels take head_dim 64 only
+    assert lib.ttt_mlp_backward_workspace_bytes(C.byref(d)) == 0
+
+
 @pytest.mark.parametrize("kw,code", [
     (dict(seq_len=70), _lib.TTT_ERR_SHAPE),              # not a multiple of the mini-batch
     (dict(mini_batch=8, seq_len=64), _lib.TTT_ERR_UNSUPPORTED),
-    (dict(head_dim=32), _lib.TTT_ERR_UNSUPPORTED),
+    (dict(head_dim=128), _lib.TTT_ERR_UNSUPPORTED),
+    (dict(head_dim=32, heads=3), _lib.TTT_ERR_UNSUPPORTED),   # head_dim 32 pairs heads: needs an even count
     (dict(checkpoint_interval=0), _lib.TTT_ERR_SHAPE),
     (dict(batch=0), _lib.TTT_ERR_SHAPE),
     (dict(dtype=7), _lib.TTT_ERR_UNSUPPORTED),

@@ -76,15 +76,72 @@ int make_gemm_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, 
   return TTT_OK;
 }
 
-int check_dims(const ttt_dims* d) {
+// Views of a [B,H,T,32] tensor for the kernels that take a PAIR of 32-wide heads per 64-wide tile.  bf16: 4-D
+// [B*H/2 pairs, T tokens, 2 heads, 32 features] with a box of one pair x 16 tokens x 2 heads x 32 features, which
+// lands in shared memory as 16 rows of 128 bytes, head 0's features then head 1's: the same image as a 64-wide tile.
+// float32: 2-D [B*H*T, 32], box = 16 tokens x 32 features = one half tile.
+int make_pair_map(CUtensorMap* m, const void* base, int64_t pairs, int64_t T, int dtype) {
+  EncodeFn enc = get_encode_fn();
+  if (enc == nullptr) return fail(TTT_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  CUresult r;
+  if (dtype == TTT_BF16) {
+    const cuuint64_t dims[4] = {32, 2, (cuuint64_t)T, (cuuint64_t)pairs};
+    const cuuint64_t strides[3] = {(cuuint64_t)(T * 32 * 2), 32 * 2, (cuuint64_t)(2 * T * 32 * 2)};
+    const cuuint32_t box[4] = {32, 2, 16, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    const cuuint64_t dims[2] = {32, (cuuint64_t)(2 * pairs * T)};
+    const cuuint64_t strides[1] = {32 * 4};
+    const cuuint32_t box[2] = {32, 16};
+    const cuuint32_t estr[2] = {1, 1};
+    r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
+  if (r != CUDA_SUCCESS) return fail(TTT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return TTT_OK;
+}
+
+// How the problem looks to the 64-wide kernels: head_dim 64 as it is; head_dim 32 (TTT-Linear only) as H/2 streams per
+// batch row, each a pair of heads side by side.
+struct Packing {
+  int seg;         // features per head: 64 or 32
+  int nh;          // heads per tile: 1 or 2
+  int heads;       // streams per batch row as the kernels count them
+  int64_t streams; // batch * heads
+  int64_t rows;    // streams * seq_len
+};
+Packing packing(const ttt_dims* d) {
+  Packing k;
+  k.seg = d->head_dim;
+  k.nh = 64 / d->head_dim;
+  k.heads = d->heads / k.nh;
+  k.streams = (int64_t)d->batch * k.heads;
+  k.rows = k.streams * d->seq_len;
+  return k;
+}
+// map of one [B,H,T,F] input or output of the caller
+int make_io_map(CUtensorMap* m, const void* base, const ttt_dims* d) {
+  const Packing k = packing(d);
+  if (k.seg == 64) return make_tile_map(m, base, k.rows, d->dtype);
+  return make_pair_map(m, base, k.streams, d->seq_len, d->dtype);
+}
+
+int check_dims(const ttt_dims* d, bool allow_head_dim_32 = false) {
   if (d == nullptr) return fail(TTT_ERR_NULL, "dims is null");
   if (d->batch <= 0 || d->heads <= 0 || d->seq_len <= 0 || d->head_dim <= 0 || d->mini_batch <= 0)
     return fail(TTT_ERR_SHAPE, "batch, heads, seq_len, head_dim and mini_batch must be positive");
   if (d->checkpoint_interval < 1) return fail(TTT_ERR_SHAPE, "checkpoint_interval must be >= 1");
   if (d->dtype != TTT_F32 && d->dtype != TTT_BF16) return fail(TTT_ERR_UNSUPPORTED, "unknown dtype %d", d->dtype);
-  if (d->mini_batch != 16 || d->head_dim != 64)
-    return fail(TTT_ERR_UNSUPPORTED, "Unsupported tile config: mini_batch_len=%d, head_dim=%d (supported: 16x64)",
-                d->mini_batch, d->head_dim);
+  if (d->mini_batch != 16 || (d->head_dim != 64 && !(allow_head_dim_32 && d->head_dim == 32)))
+    return fail(TTT_ERR_UNSUPPORTED, "Unsupported tile config: mini_batch_len=%d, head_dim=%d (supported: 16x64%s)",
+                d->mini_batch, d->head_dim, allow_head_dim_32 ? ", 16x32" : "");
+  if (d->head_dim == 32 && d->heads % 2 != 0)
+    return fail(TTT_ERR_UNSUPPORTED, "head_dim 32 runs two heads per tile and needs an even number of heads (got %d)",
+                d->heads);
   if (d->seq_len % d->mini_batch != 0)
     return fail(TTT_ERR_SHAPE, "seq_len (%d) must be divisible by mini_batch_len (%d)", d->seq_len, d->mini_batch);
   if ((int64_t)d->batch * d->heads * d->seq_len >= (int64_t)1 << 31)
@@ -118,13 +175,14 @@ struct AuxLayout {
   size_t off_gp, off_stats, off_bias, total_bytes;
 };
 AuxLayout aux_layout(const ttt_dims* d) {
-  const size_t rows = (size_t)d->batch * d->heads * d->seq_len;
-  const size_t streams = (size_t)d->batch * d->heads;
+  const Packing k = packing(d);
+  const size_t rows = (size_t)k.rows;
+  const size_t streams = (size_t)k.streams;
   const size_t ns = (size_t)d->seq_len / d->mini_batch;
   AuxLayout a;
   a.off_gp = 0;
   a.off_stats = a.off_gp + rows * 64 * (d->dtype == TTT_BF16 ? 2 : 4);
-  a.off_bias = a.off_stats + rows * 32;
+  a.off_bias = a.off_stats + rows * 32 * k.nh;  // one record of two float4 per (token, head)
   a.total_bytes = a.off_bias + streams * (ns + 1) * 64 * sizeof(float);
   return a;
 }
@@ -136,14 +194,17 @@ struct WsLayout {
   int nch;
 };
 WsLayout ws_layout(const ttt_dims* d) {
-  const size_t streams = (size_t)d->batch * d->heads;
+  const Packing k = packing(d);
+  const size_t streams = (size_t)k.streams;                    // as the kernel counts them
+  const size_t heads_all = (size_t)d->batch * d->heads;        // as the caller counts them
+  const size_t F = (size_t)d->head_dim;
   const int ns = d->seq_len / d->mini_batch;
   WsLayout w;
   w.nch = (ns + kBwdChunkStages - 1) / kBwdChunkStages;
   w.off_ln = 0;
   w.off_te = w.off_ln + streams * (size_t)w.nch * 2 * 64;
-  w.off_w = w.off_te + streams * (size_t)d->seq_len;
-  w.off_handoff = w.off_w + streams * (64 * 64 + 64);
+  w.off_w = w.off_te + heads_all * (size_t)d->seq_len;
+  w.off_handoff = w.off_w + heads_all * (F * F + F);
   w.off_sched = w.off_handoff + streams * (2 * 64 * 64 + 64);
   const size_t words = w.off_sched + ((1 + streams + 3) & ~(size_t)3);
   w.total_bytes = words * sizeof(float);
@@ -281,15 +342,15 @@ void ttt_b200_debug_handoff(uint32_t poll_limit, int32_t first_item) {
 }
 
 int64_t ttt_linear_num_checkpoints(const ttt_dims* d) {
-  if (check_dims(d) != TTT_OK) return -1;
+  if (check_dims(d, true) != TTT_OK) return -1;
   return num_ckpt(d);
 }
 size_t ttt_linear_weight_ckpt_bytes(const ttt_dims* d) {
-  if (check_dims(d) != TTT_OK) return 0;
-  return (size_t)d->batch * d->heads * (num_ckpt(d) + 1) * 64 * 64 * sizeof(float);
+  if (check_dims(d, true) != TTT_OK) return 0;
+  return (size_t)packing(d).streams * (num_ckpt(d) + 1) * 64 * 64 * sizeof(float);
 }
 size_t ttt_linear_bias_ckpt_bytes(const ttt_dims* d) {
-  if (check_dims(d) != TTT_OK) return 0;
+  if (check_dims(d, true) != TTT_OK) return 0;
   return aux_layout(d).total_bytes;
 }
 
@@ -297,7 +358,7 @@ int ttt_linear_forward(const ttt_dims* d, const void* xq, const void* xk, const 
                        const void* bias, const void* token_eta, const void* ttt_lr_eta, const void* ln_weight,
                        const void* ln_bias, void* output, void* weight_out, void* bias_out, void* weight_ckpt,
                        void* bias_ckpt, void* status, void* stream) {
-  int rc = check_dims(d);
+  int rc = check_dims(d, true);
   if (rc != TTT_OK) return rc;
   const NamedPtr ptrs[] = {{"xq", xq},           {"xk", xk},
                            {"xv", xv},           {"weight", weight},
@@ -313,15 +374,18 @@ int ttt_linear_forward(const ttt_dims* d, const void* xq, const void* xk, const 
   if (status != nullptr && (reinterpret_cast<uintptr_t>(status) & 3u) != 0)
     return fail(TTT_ERR_ALIGN, "status is not 4-byte aligned");
 
-  const int64_t rows = (int64_t)d->batch * d->heads * d->seq_len;
+  const Packing pk = packing(d);
   const AuxLayout al = aux_layout(d);
   uint8_t* aux = static_cast<uint8_t*>(bias_ckpt);
   CUtensorMap maps[5];
-  const void* bases[5] = {xq, xk, xv, output, save ? static_cast<const void*>(aux + al.off_gp) : output};
-  for (int i = 0; i < 5; ++i) {
-    rc = make_tile_map(&maps[i], bases[i], rows, d->dtype);
+  const void* bases[4] = {xq, xk, xv, output};
+  for (int i = 0; i < 4; ++i) {
+    rc = make_io_map(&maps[i], bases[i], d);
     if (rc != TTT_OK) return rc;
   }
+  // the saved Gp tiles are always kept 64 wide; without saved state the map is never used, but must be a valid one
+  rc = save ? make_tile_map(&maps[4], aux + al.off_gp, pk.rows, d->dtype) : make_io_map(&maps[4], output, d);
+  if (rc != TTT_OK) return rc;
   ttt::LinFwdParams p;
   p.w0 = weight;
   p.b0 = bias;
@@ -335,19 +399,20 @@ int ttt_linear_forward(const ttt_dims* d, const void* xq, const void* xk, const 
   p.stats = save ? reinterpret_cast<float4*>(aux + al.off_stats) : nullptr;
   p.b_stage = save ? reinterpret_cast<float*>(aux + al.off_bias) : nullptr;
   p.status = static_cast<uint32_t*>(status);
-  p.H = d->heads;
+  p.H = pk.heads;
   p.T = d->seq_len;
   p.NS = d->seq_len / d->mini_batch;
   p.K = d->checkpoint_interval;
   p.NCK = (int)num_ckpt(d);
   p.eps = d->epsilon;
-  cudaError_t e = ttt::launch_linear_fwd(d->dtype, maps, p, d->batch * d->heads, static_cast<cudaStream_t>(stream));
+  cudaError_t e =
+      ttt::launch_linear_fwd(d->dtype, pk.seg, maps, p, (int)pk.streams, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(e));
   return TTT_OK;
 }
 
 size_t ttt_linear_backward_workspace_bytes(const ttt_dims* d) {
-  if (check_dims(d) != TTT_OK) return 0;
+  if (check_dims(d, true) != TTT_OK) return 0;
   return ws_layout(d).total_bytes;
 }
 
@@ -374,7 +439,7 @@ int ttt_linear_backward_state_grads(const ttt_dims* d, const void* xq, const voi
                                     void* grad_ttt_lr_eta, float* grad_token_eta, float* grad_ln_weight,
                                     float* grad_ln_bias, float* outer_grad_packed, void* workspace,
                                     size_t workspace_bytes, void* status, void* stream) {
-  int rc = check_dims(d);
+  int rc = check_dims(d, true);
   if (rc != TTT_OK) return rc;
   const NamedPtr ptrs[] = {{"xq", xq},
                            {"xk", xk},
@@ -408,15 +473,17 @@ int ttt_linear_backward_state_grads(const ttt_dims* d, const void* xq, const voi
   if (workspace_bytes < wl.total_bytes)
     return fail(TTT_ERR_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes, wl.total_bytes);
 
-  const int64_t rows = (int64_t)d->batch * d->heads * d->seq_len;
+  const Packing pk = packing(d);
   const AuxLayout al = aux_layout(d);
   const uint8_t* aux = static_cast<const uint8_t*>(bias_ckpt);
   CUtensorMap maps[8];
-  const void* bases[8] = {xq, xk, xv, grad_output, grad_xq, grad_xk, grad_xv, aux + al.off_gp};
-  for (int i = 0; i < 8; ++i) {
-    rc = make_tile_map(&maps[i], bases[i], rows, d->dtype);
+  const void* bases[7] = {xq, xk, xv, grad_output, grad_xq, grad_xk, grad_xv};
+  for (int i = 0; i < 7; ++i) {
+    rc = make_io_map(&maps[i], bases[i], d);
     if (rc != TTT_OK) return rc;
   }
+  rc = make_tile_map(&maps[7], aux + al.off_gp, pk.rows, d->dtype);
+  if (rc != TTT_OK) return rc;
   float* ws = static_cast<float*>(workspace);
   ttt::LinBwdParams p;
   p.w0 = weight;
@@ -440,18 +507,18 @@ int ttt_linear_backward_state_grads(const ttt_dims* d, const void* xq, const voi
   p.sched = reinterpret_cast<int*>(ws + wl.off_sched);
   p.CH = kBwdChunkStages;
   p.NCH = wl.nch;
-  p.nstreams = d->batch * d->heads;
+  p.nstreams = (int)pk.streams;
   p.handoff_polls = g_handoff_polls.load();
   p.item_base = g_item_base.load();
   p.status = static_cast<uint32_t*>(status);
-  p.H = d->heads;
+  p.H = pk.heads;
   p.T = d->seq_len;
   p.NS = d->seq_len / d->mini_batch;
   p.K = d->checkpoint_interval;
   p.NCK = (int)num_ckpt(d);
   p.eps = d->epsilon;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  cudaError_t e = ttt::launch_linear_bwd(d->dtype, maps, p, d->batch * d->heads, st);
+  cudaError_t e = ttt::launch_linear_bwd(d->dtype, pk.seg, maps, p, (int)pk.streams, st);
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "backward launch failed: %s", cudaGetErrorString(e));
   ttt::ReduceParams r;
   r.part_ln = p.part_ln;
@@ -463,6 +530,7 @@ int ttt_linear_backward_state_grads(const ttt_dims* d, const void* xq, const voi
   r.packed = outer_grad_packed;
   r.B = d->batch;
   r.H = d->heads;
+  r.F = d->head_dim;
   r.T = d->seq_len;
   r.NCH = wl.nch;
   e = ttt::launch_linear_bwd_reduce(r, st);

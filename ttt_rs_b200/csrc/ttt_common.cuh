@@ -83,6 +83,18 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, int x, int y
                "r"(y), "r"(src)
                : "memory");
 }
+// 4-D tiled forms (two 32-wide heads gathered into one 64-wide tile: coordinates feature, head in pair, token, pair).
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm, int x, int y, int z, int w, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(tm), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* tm, int x, int y, int z, int w, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%1, %2, %3, %4}], [%5];" ::"l"(tm), "r"(x),
+               "r"(y), "r"(z), "r"(w), "r"(src)
+               : "memory");
+}
 // Untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16).
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),

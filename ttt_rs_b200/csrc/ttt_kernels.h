@@ -62,6 +62,7 @@ struct ReduceParams {
   float* d_ln_b;       // [H,F] f32
   float* packed;       // nullable: [H*F*F + 3*H*F + CS] f32
   int B, H, T, NCH;
+  int F;  // features per head: 64, or 32 (two heads per 64-wide tile in part_ln)
 };
 
 struct MlpFwdParams {
@@ -282,10 +283,10 @@ cudaError_t launch_gemm_bf16_tn(const CUtensorMap* maps, const GemmParams& p, bo
 cudaError_t launch_mlp_fwd(const CUtensorMap* maps, const MlpFwdParams& p, int nstreams, cudaStream_t st);
 
 // dtype: 0 = float32, 1 = bfloat16.  maps: q, k, v, out, gp (saved lr-scaled LN gradient, [B*H*T, 64] of T).
-cudaError_t launch_linear_fwd(int dtype, const CUtensorMap* maps, const LinFwdParams& p, int nstreams,
+cudaError_t launch_linear_fwd(int dtype, int seg, const CUtensorMap* maps, const LinFwdParams& p, int nstreams,
                               cudaStream_t st);
 // maps: q, k, v, d_out, d_q, d_k, d_v, gp.
-cudaError_t launch_linear_bwd(int dtype, const CUtensorMap* maps, const LinBwdParams& p, int nstreams,
+cudaError_t launch_linear_bwd(int dtype, int seg, const CUtensorMap* maps, const LinBwdParams& p, int nstreams,
                               cudaStream_t st);
 cudaError_t launch_linear_bwd_reduce(const ReduceParams& p, cudaStream_t st);
 

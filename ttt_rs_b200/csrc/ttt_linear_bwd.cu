@@ -22,6 +22,11 @@
 //   * The three gradients that the reference accumulates with float atomics (token_eta, LN weight/bias) are written as
 //     per-stream partials to a workspace and summed by a second kernel in a fixed order, so results are
 //     bitwise reproducible.
+//
+// head_dim 32 (SEG = 32): as in the forward, a CTA takes a pair of heads side by side in the 64-wide tiles with
+// block-diagonal W^T and dW^T; the row sums, Q.K^T, dZbar.Gp^T and the k-ranges of the rank-16 updates are restricted
+// to the head's own 32 columns, and everything written per head (ttt_lr_eta gradient, token_eta terms, state
+// gradients) goes to the head's own place in the caller's [B, H, ...] tensors.
 #include "ttt_kernels.h"
 #include "ttt_stage.cuh"
 
@@ -36,10 +41,10 @@ struct BwdSmem {
   // one slot = the tiles of one stage: q, k, gp (raw + operand planes), v, d_out (raw), then small records
   static constexpr uint32_t OFF_Q = 0, OFF_K = TF::BYTES, OFF_G = 2 * TF::BYTES, OFF_V = 3 * TF::BYTES;
   static constexpr uint32_t OFF_DO = OFF_V + TF::RAW_BYTES;
-  static constexpr uint32_t OFF_STAT = OFF_DO + TF::RAW_BYTES;  // 16 tokens x 2 float4
-  static constexpr uint32_t OFF_BS = OFF_STAT + 512;            // 64 floats: bias at the start of the stage
-  static constexpr uint32_t OFF_LR = OFF_BS + 256;              // 16 x element
-  static constexpr uint32_t SLOT = OFF_STAT + 1024;
+  static constexpr uint32_t OFF_STAT = OFF_DO + TF::RAW_BYTES;  // 16 tokens x 2 float4 (x 2 heads when paired)
+  static constexpr uint32_t OFF_BS = OFF_STAT + 1024;           // 64 floats: bias at the start of the stage
+  static constexpr uint32_t OFF_LR = OFF_BS + 256;              // 16 x element (x 2 heads when paired)
+  static constexpr uint32_t SLOT = OFF_STAT + 2048;
   static constexpr uint32_t OFF_W = NSLOT * SLOT;               // W_s^T, 4 sub-tiles [16 n][64 k]
   static constexpr uint32_t OFF_DW = OFF_W + 4 * PLANES;        // dW^T, same layout
   static constexpr uint32_t OFF_DZ = OFF_DW + 4 * PLANES;       // dZbar operand tile
@@ -55,7 +60,7 @@ struct BwdSmem {
 #define TTT_BWD_MINB_BF16 2  // resident blocks per SM the bf16 kernel is compiled for
 #endif
 
-template <typename T>
+template <typename T, int SEG>
 __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 : 1))
     ttt_linear_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                           const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -66,6 +71,8 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
   using SM = BwdSmem<T>;
   constexpr int NP = TF::NP;
   constexpr uint32_t PL = TILE_BF16_BYTES;  // plane stride
+  constexpr float INV_F = 1.f / SEG;        // features per head (LayerNorm row length)
+  constexpr int NH = (SEG == 32) ? 2 : 1;   // heads per tile
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_u32 = smem_u32(smem_raw);
@@ -77,6 +84,8 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
 
   const Lane L;
   const int tid = L.tid, lane = L.lane, g = L.g, t = L.t, nb = L.nb, warp = L.warp;
+  const int hsel = warp >> 1;                 // SEG = 32: which head of the pair this warp's columns belong to
+  const int khalf = (SEG == 32) ? hsel : -1;  // and the k-range of W^T / dW^T that is its own block
   const int NS = p.NS;
   // work item = (stream, chunk of CH stages); set per item below
   int stream = 0, row_base = 0;
@@ -102,15 +111,23 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
     const uint32_t bar = bar0 + 8 * slot;
     const uint32_t sl = base + slot * SM::SLOT;
     const int r0 = row_base + s * CS;
-    mbar_expect_tx(bar, 5u * TF::RAW_BYTES + 512u + 256u + CS * TF::ELT);
-    tma_load_tile<T>(sl + SM::OFF_K, &tm_k, r0, bar);
-    tma_load_tile<T>(sl + SM::OFF_G, &tm_g, r0, bar);
-    tma_load_tile<T>(sl + SM::OFF_Q, &tm_q, r0, bar);
-    tma_load_tile<T>(sl + SM::OFF_V, &tm_v, r0, bar);
-    tma_load_tile<T>(sl + SM::OFF_DO, &tm_do, r0, bar);
-    bulk_load_1d(sl + SM::OFF_STAT, p.stats + (size_t)r0 * 2, 512u, bar);
+    mbar_expect_tx(bar, 5u * TF::RAW_BYTES + NH * 512u + 256u + NH * CS * TF::ELT);
+    tma_load_x<T, SEG>(sl + SM::OFF_K, &tm_k, stream, s * CS, p.T, bar);
+    tma_load_tile<T>(sl + SM::OFF_G, &tm_g, r0, bar);  // saved tiles are kept in the packed 64-wide form
+    tma_load_x<T, SEG>(sl + SM::OFF_Q, &tm_q, stream, s * CS, p.T, bar);
+    tma_load_x<T, SEG>(sl + SM::OFF_V, &tm_v, stream, s * CS, p.T, bar);
+    tma_load_x<T, SEG>(sl + SM::OFF_DO, &tm_do, stream, s * CS, p.T, bar);
+    bulk_load_1d(sl + SM::OFF_STAT, p.stats + (size_t)r0 * 2 * NH, NH * 512u, bar);
     bulk_load_1d(sl + SM::OFF_BS, p.b_stage + ((size_t)stream * (NS + 1) + s) * HD, 256u, bar);
-    bulk_load_1d(sl + SM::OFF_LR, static_cast<const uint8_t*>(p.lr) + (size_t)r0 * TF::ELT, CS * TF::ELT, bar);
+    if constexpr (SEG == 64) {
+      bulk_load_1d(sl + SM::OFF_LR, static_cast<const uint8_t*>(p.lr) + (size_t)r0 * TF::ELT, CS * TF::ELT, bar);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        bulk_load_1d(sl + SM::OFF_LR + j * CS * TF::ELT,
+                     static_cast<const uint8_t*>(p.lr) + ((size_t)(2 * stream + j) * p.T + s * CS) * TF::ELT,
+                     CS * TF::ELT, bar);
+    }
   };
 
   // ---- per-thread constants and accumulators (column pairs nt = 0,1; rows g and g+8)
@@ -169,11 +186,18 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
 #pragma unroll
       for (int kt = 0; kt < 8; ++kt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-          dwt[kt][i] = (p.dw_in == nullptr)
-                           ? 0.f
-                           : ld_as_float<T>(p.dw_in, (size_t)stream * HD * HD + (8 * kt + 2 * t + (i & 1)) * HD + nb + g +
-                                                         8 * (i >> 1));
+        for (int i = 0; i < 4; ++i) {
+          const int k = 8 * kt + 2 * t + (i & 1), nn = nb + g + 8 * (i >> 1);
+          if (p.dw_in == nullptr) {
+            dwt[kt][i] = 0.f;
+          } else if constexpr (SEG == 64) {
+            dwt[kt][i] = ld_as_float<T>(p.dw_in, (size_t)stream * HD * HD + k * HD + nn);
+          } else {
+            dwt[kt][i] = ((kt >> 2) == hsel) ? ld_as_float<T>(p.dw_in, (size_t)(2 * stream + hsel) * 32 * 32 +
+                                                                         (k & 31) * 32 + (nn & 31))
+                                             : 0.f;
+          }
+        }
       if (p.db_in != nullptr) {
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
@@ -259,7 +283,8 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       }
       issue_next();
     }
-    const float lr_row[2] = {ld_as_float<T>(gsl + SM::OFF_LR, g), ld_as_float<T>(gsl + SM::OFF_LR, g + 8)};
+    const uint8_t* lrp = gsl + SM::OFF_LR + (SEG == 32 ? hsel * CS * TF::ELT : 0);
+    const float lr_row[2] = {ld_as_float<T>(lrp, g), ld_as_float<T>(lrp, g + 8)};
     const float4* stat = reinterpret_cast<const float4*>(gsl + SM::OFF_STAT);
     const float* bsv = reinterpret_cast<const float*>(gsl + SM::OFF_BS);
 
@@ -270,7 +295,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       if (w_moves) {
         ldsm_np<NP>(agt, pg + lane_off_B_nk(lane, nb), PL, true);
         const Pk<NP> ngt[4] = {neg_pk<NP>(agt[0]), neg_pk<NP>(agt[1]), neg_pk<NP>(agt[2]), neg_pk<NP>(agt[3])};
-        state_update_direct<NP>(wt, ngt, pk, lane);
+        state_update_direct<NP>(wt, ngt, pk, lane, khalf);
       }
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
@@ -309,8 +334,10 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       }
       // the A fragments of K are also the B fragments of Q K^T (the same four 8x8 blocks in another order)
       const Pk<NP> bj0[2] = {ak[0], ak[2]}, bj1[2] = {ak[1], ak[3]};
-      mma_np<NP>(at[0], aq, bj0);
-      mma_np<NP>(at[1], aq, bj1);
+      if (SEG == 64 || (ks >> 1) == hsel) {  // Q K^T contracts over the head's own features only
+        mma_np<NP>(at[0], aq, bj0);
+        mma_np<NP>(at[1], aq, bj1);
+      }
     }
     // products were taken with What: Z = wscale * acc + b
 #pragma unroll
@@ -324,7 +351,9 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
     float mean1[2], rstd1[2], Bv1[2], mean2[2], rstd2[2];
     F2 xh[2][2], gy[2][2], gx[2][2], G[2][2];
     {
-      const float4 sa0 = stat[2 * g], sb0 = stat[2 * g + 1], sa1 = stat[2 * (g + 8)], sb1 = stat[2 * (g + 8) + 1];
+      const int h_ = (SEG == 32) ? hsel : 0;  // record of (token, head): index NH * token + head
+      const float4 sa0 = stat[2 * (NH * g + h_)], sb0 = stat[2 * (NH * g + h_) + 1],
+                   sa1 = stat[2 * (NH * (g + 8) + h_)], sb1 = stat[2 * (NH * (g + 8) + h_) + 1];
       mean1[0] = sa0.x; rstd1[0] = sa0.y; mean1[1] = sa1.x; rstd1[1] = sa1.y;
       const float A[2] = {sa0.z, sa1.z};
       Bv1[0] = sa0.w; Bv1[1] = sa1.w;
@@ -375,7 +404,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
           p2[r] = f2fma(tv_, x, p2[r]);
         }
       float2 a0, a1;
-      xch_rows2(&xch[xsel], L, f2hsum(p1[0]), f2hsum(p2[0]), f2hsum(p1[1]), f2hsum(p2[1]), a0, a1, fail);
+      xch_rows2<SEG>(&xch[xsel], L, f2hsum(p1[0]), f2hsum(p2[0]), f2hsum(p1[1]), f2hsum(p2[1]), a0, a1, fail);
       xsel ^= 1;
       if (fail) {
         failed = true;
@@ -383,7 +412,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
         break;
       }
       issue_next();
-      const float c1[2] = {a0.x * (1.f / HD), a1.x * (1.f / HD)}, c2[2] = {a0.y * (1.f / HD), a1.y * (1.f / HD)};
+      const float c1[2] = {a0.x * INV_F, a1.x * INV_F}, c2[2] = {a0.y * INV_F, a1.y * INV_F};
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
@@ -412,7 +441,9 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       ldsm_np<NP>(bwt, tW + ks * SM::PLANES + lane_off_B_kn(lane, nb), PL, true);
       ldsm_np<NP>(ags, pg + lane_off_A(lane, 16 * ks), PL, false);
       ldsm_np<NP>(bdw, tDW + ks * SM::PLANES + lane_off_B_kn(lane, nb), PL, true);
-      {  // P' = dZbar Gp^T (16x16); the A fragments of Gp serve as its B fragments (same 8x8 blocks, other order)
+      if (SEG == 64 || (ks >> 1) == hsel) {
+        // P' = dZbar Gp^T (16x16, over the head's own columns); the A fragments of Gp serve as its B fragments (same
+        // 8x8 blocks, other order)
         const Pk<NP> b0[2] = {ags[0], ags[2]}, b1[2] = {ags[1], ags[3]};
         mma_np<NP>(pp[0], adz, b0);
         mma_np<NP>(pp[1], adz, b1);
@@ -469,6 +500,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       ldsm_np<NP>(adzt, tDZ + lane_off_B_nk(lane, nb), PL, true);
 #pragma unroll
       for (int kp = 0; kp < 4; ++kp) {
+        if (khalf >= 0 && (kp >> 1) != khalf) continue;  // paired heads: only the head's own block of dW^T
         Pk<NP> bq[4];
         ldsm_np<NP>(bq, pq + lane_off_B_kn(lane, 16 * kp), PL, true);
         const Pk<NP> b0[2] = {bq[0], bq[1]}, b1[2] = {bq[2], bq[3]};
@@ -503,14 +535,15 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
         }
       float4 o0, o1;
       int f2_ = 0;
-      xch_rows(&xch[xsel], L, make_float4(f2hsum(p1[0]), f2hsum(p2[0]), f2hsum(pdl[0]), f2hsum(prt[0])),
-               make_float4(f2hsum(p1[1]), f2hsum(p2[1]), f2hsum(pdl[1]), f2hsum(prt[1])), o0, o1, f2_);
+      xch_rows<SEG>(&xch[xsel], L, make_float4(f2hsum(p1[0]), f2hsum(p2[0]), f2hsum(pdl[0]), f2hsum(prt[0])),
+                    make_float4(f2hsum(p1[1]), f2hsum(p2[1]), f2hsum(pdl[1]), f2hsum(prt[1])), o0, o1, f2_);
       xsel ^= 1;
-      s1t[0] = o0.x * (1.f / HD); s2t[0] = o0.y * (1.f / HD);
-      s1t[1] = o1.x * (1.f / HD); s2t[1] = o1.y * (1.f / HD);
+      s1t[0] = o0.x * INV_F; s2t[0] = o0.y * INV_F;
+      s1t[1] = o1.x * INV_F; s2t[1] = o1.y * INV_F;
       const float rt_all = col_sum(o0.w + o1.w);  // sum over the 16 rows
-      if (warp == 0 && t == 0) {
-        const size_t o = (size_t)row_base + (size_t)s * CS;
+      if ((warp & 1) == 0 && t == 0 && (SEG == 32 || warp == 0)) {
+        // per (batch, head) stream of the caller's tensors: the pair's heads are streams 2 * stream and 2 * stream + 1
+        const size_t o = (SEG == 32 ? (size_t)(2 * stream + hsel) * p.T : (size_t)row_base) + (size_t)s * CS;
         st_from_float<T>(p.d_lr, o + g, o0.z);
         st_from_float<T>(p.d_lr, o + g + 8, o1.z);
         p.part_te[o + g] = dte_row[0];
@@ -539,9 +572,9 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
         }
       float2 a0, a1;
       int f2_ = 0;
-      xch_rows2(&xch[xsel], L, f2hsum(pd[0]), f2hsum(ps[0]), f2hsum(pd[1]), f2hsum(ps[1]), a0, a1, f2_);
+      xch_rows2<SEG>(&xch[xsel], L, f2hsum(pd[0]), f2hsum(ps[0]), f2hsum(pd[1]), f2hsum(ps[1]), a0, a1, f2_);
       xsel ^= 1;
-      const float D[2] = {a0.x * (1.f / HD), a1.x * (1.f / HD)}, S[2] = {a0.y * (1.f / HD), a1.y * (1.f / HD)};
+      const float D[2] = {a0.x * INV_F, a1.x * INV_F}, S[2] = {a0.y * INV_F, a1.y * INV_F};
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
@@ -570,6 +603,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       ldsm_np<NP>(adzt, tDZ1 + lane_off_B_nk(lane, nb), PL, true);
 #pragma unroll
       for (int kp = 0; kp < 4; ++kp) {
+        if (khalf >= 0 && (kp >> 1) != khalf) continue;
         Pk<NP> bk[4];
         ldsm_np<NP>(bk, pk + lane_off_B_kn(lane, 16 * kp), PL, true);
         const Pk<NP> b0[2] = {bk[0], bk[1]}, b1[2] = {bk[2], bk[3]};
@@ -598,10 +632,9 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       fence_proxy_async_smem();
       __syncthreads();
       if (tid == 0) {
-        const int r0 = row_base + s * CS;
-        tma_store_tile<T>(&tm_dq, r0, so_q);
-        tma_store_tile<T>(&tm_dk, r0, so_k);
-        tma_store_tile<T>(&tm_dv, r0, so_v);
+        tma_store_x<T, SEG>(&tm_dq, stream, s * CS, p.T, so_q);
+        tma_store_x<T, SEG>(&tm_dk, stream, s * CS, p.T, so_k);
+        tma_store_x<T, SEG>(&tm_dv, stream, s * CS, p.T, so_v);
         bulk_commit();
       }
     }
@@ -643,9 +676,18 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       for (int kt = 0; kt < 8; ++kt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int idx = (8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1);
-          st_from_float<T>(p.d_w, wo + idx, dwt[kt][i]);
-          if (p.part_w != nullptr) p.part_w[(size_t)stream * (HD * HD + HD) + idx] = dwt[kt][i];
+          const int k = 8 * kt + 2 * t + (i & 1), nn = nb + g + 8 * (i >> 1);
+          if constexpr (SEG == 64) {
+            const int idx = k * HD + nn;
+            st_from_float<T>(p.d_w, wo + idx, dwt[kt][i]);
+            if (p.part_w != nullptr) p.part_w[(size_t)stream * (HD * HD + HD) + idx] = dwt[kt][i];
+          } else if ((kt >> 2) == hsel) {
+            // the head's own 32 x 32 block, at the head's place in the caller's [B, H, 32, 32] layout
+            const size_t hs = (size_t)(2 * stream + hsel);
+            const int idx = (k & 31) * 32 + (nn & 31);
+            st_from_float<T>(p.d_w, hs * 32 * 32 + idx, dwt[kt][i]);
+            if (p.part_w != nullptr) p.part_w[hs * (32 * 32 + 32) + idx] = dwt[kt][i];
+          }
         }
       if (g == 0) {
 #pragma unroll
@@ -654,8 +696,11 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int c = nb + 8 * nt + 2 * t + e;
-            st_from_float<T>(p.d_b, (size_t)stream * HD + c, dbi[e]);
-            if (p.part_w != nullptr) p.part_w[(size_t)stream * (HD * HD + HD) + HD * HD + c] = dbi[e];
+            st_from_float<T>(p.d_b, (size_t)stream * HD + c, dbi[e]);  // [B, H, 32] flat = [B, H/2, 64] flat
+            if (p.part_w != nullptr) {
+              if constexpr (SEG == 64) p.part_w[(size_t)stream * (HD * HD + HD) + HD * HD + c] = dbi[e];
+              else p.part_w[(size_t)(2 * stream + hsel) * (32 * 32 + 32) + 32 * 32 + (c & 31)] = dbi[e];
+            }
           }
         }
       }
@@ -675,8 +720,10 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
 // reads), the eight partial sums meet in shared memory and are added in warp order: a fixed summation order.
 __global__ void __launch_bounds__(256) ttt_linear_bwd_reduce_kernel(const ReduceParams p) {
   __shared__ float part[8][32];
-  const int H = p.H, B = p.B, T = p.T, NCH = p.NCH;
-  const int n_te = T, n_ln = 2 * H * HD, n_w = (p.packed != nullptr) ? H * (HD * HD + HD) : 0;
+  // H heads of F features as the caller counts them; the partials of the LayerNorm gradients are in the kernel's
+  // 64-wide tiles, which hold NP = 64 / F heads side by side
+  const int H = p.H, B = p.B, T = p.T, NCH = p.NCH, F = p.F, NP = HD / F, HP = H / NP;
+  const int n_te = T, n_ln = 2 * H * F, n_w = (p.packed != nullptr) ? H * (F * F + F) : 0;
   const int total = n_te + n_ln + n_w;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int base = blockIdx.x * 32; base < total; base += gridDim.x * 32) {
@@ -685,17 +732,17 @@ __global__ void __launch_bounds__(256) ttt_linear_bwd_reduce_kernel(const Reduce
     if (i < n_te) {
       for (int st = warp; st < B * H; st += 8) acc += p.part_te[(size_t)st * T + i];
     } else if (i < n_te + n_ln) {
-      const int k = i - n_te, which = k / (H * HD), hf = k % (H * HD), h = hf / HD, f = hf % HD;
+      const int k = i - n_te, which = k / (H * F), hf = k % (H * F), h = hf / F, f = hf % F;
       for (int j = warp; j < B * NCH; j += 8) {
         const int b = j / NCH, ch = j - b * NCH;
-        acc += p.part_ln[(((size_t)(b * H + h) * NCH + ch) * 2 + which) * HD + f];
+        acc += p.part_ln[(((size_t)(b * HP + h / NP) * NCH + ch) * 2 + which) * HD + (h % NP) * F + f];
       }
     } else if (i < total) {
       const int k = i - n_te - n_ln;
-      const bool is_w = k < H * HD * HD;
-      const int h = is_w ? k / (HD * HD) : (k - H * HD * HD) / HD;
-      const int e = is_w ? k % (HD * HD) : HD * HD + (k - H * HD * HD) % HD;
-      for (int b = warp; b < B; b += 8) acc += p.part_w[(size_t)(b * H + h) * (HD * HD + HD) + e];
+      const bool is_w = k < H * F * F;
+      const int h = is_w ? k / (F * F) : (k - H * F * F) / F;
+      const int e = is_w ? k % (F * F) : F * F + (k - H * F * F) % F;
+      for (int b = warp; b < B; b += 8) acc += p.part_w[(size_t)(b * H + h) * (F * F + F) + e];
     }
     part[warp][lane] = acc;
     __syncthreads();
@@ -707,8 +754,8 @@ __global__ void __launch_bounds__(256) ttt_linear_bwd_reduce_kernel(const Reduce
         p.d_token_eta[i] = sum;
       } else if (i < n_te + n_ln) {
         const int k = i - n_te;
-        (k < H * HD ? p.d_ln_g : p.d_ln_b)[k % (H * HD)] = sum;
-        if (p.packed != nullptr) p.packed[(size_t)H * HD * HD + H * HD + k] = sum;
+        (k < H * F ? p.d_ln_g : p.d_ln_b)[k % (H * F)] = sum;
+        if (p.packed != nullptr) p.packed[(size_t)H * F * F + H * F + k] = sum;
       } else {
         p.packed[i - n_te - n_ln] = sum;
       }
@@ -725,12 +772,12 @@ __global__ void ttt_linear_bwd_fold_kernel(const ReduceParams p) {
   for (int s = lane; s < p.T / CS; s += 32) acc += p.d_token_eta[s * CS + c];
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) p.packed[(size_t)p.H * HD * HD + 3 * p.H * HD + c] = acc;
+  if (lane == 0) p.packed[(size_t)p.H * p.F * p.F + 3 * p.H * p.F + c] = acc;
 }
 
-template <typename T>
+template <typename T, int SEG>
 static cudaError_t launch_bwd_t(const CUtensorMap* m, const LinBwdParams& p, int nstreams, cudaStream_t st) {
-  auto kfn = ttt_linear_bwd_kernel<T>;
+  auto kfn = ttt_linear_bwd_kernel<T, SEG>;
   cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BwdSmem<T>::DYN_BYTES);
   if (e != cudaSuccess) return e;
   // persistent grid: as many blocks as can be resident at once (they wait on one another's hand-offs), never more
@@ -751,14 +798,18 @@ static cudaError_t launch_bwd_t(const CUtensorMap* m, const LinBwdParams& p, int
   return cudaLaunchCooperativeKernel((const void*)kfn, dim3(grid), dim3(NTHREADS), args, BwdSmem<T>::DYN_BYTES, st);
 }
 
-cudaError_t launch_linear_bwd(int dtype, const CUtensorMap* maps, const LinBwdParams& p, int nstreams,
+cudaError_t launch_linear_bwd(int dtype, int seg, const CUtensorMap* maps, const LinBwdParams& p, int nstreams,
                               cudaStream_t st) {
-  if (dtype == 1) return launch_bwd_t<__nv_bfloat16>(maps, p, nstreams, st);
-  return launch_bwd_t<float>(maps, p, nstreams, st);
+  if (seg == 32) {
+    if (dtype == 1) return launch_bwd_t<__nv_bfloat16, 32>(maps, p, nstreams, st);
+    return launch_bwd_t<float, 32>(maps, p, nstreams, st);
+  }
+  if (dtype == 1) return launch_bwd_t<__nv_bfloat16, 64>(maps, p, nstreams, st);
+  return launch_bwd_t<float, 64>(maps, p, nstreams, st);
 }
 
 cudaError_t launch_linear_bwd_reduce(const ReduceParams& p, cudaStream_t st) {
-  const int total = p.T + 2 * p.H * HD + (p.packed != nullptr ? p.H * (HD * HD + HD) : 0);
+  const int total = p.T + 2 * p.H * p.F + (p.packed != nullptr ? p.H * (p.F * p.F + p.F) : 0);
   int blocks = (total + 31) / 32;
   if (blocks > 148 * 8) blocks = 148 * 8;
   ttt_linear_bwd_reduce_kernel<<<blocks, 256, 0, st>>>(p);

@@ -16,6 +16,12 @@
 //   * Row statistics for the two LayerNorms are warp-shuffle reduced and exchanged across the 4 warps through
 //     512 bytes of shared memory; G reaches the tensor cores as an A/B operand through movmatrix.
 //   * Output tiles leave through a double-buffered staging tile and a TMA store.
+//
+// head_dim 32 (template parameter SEG = 32) runs on the same 64-wide tiling: a CTA takes a PAIR of heads of one batch
+// element, their 16 x 32 tiles side by side in the 16 x 64 tile (warps 0,1 = first head, warps 2,3 = second), and the
+// state as a block-diagonal 64 x 64 matrix whose off-diagonal blocks stay zero.  K.W and Q.W need no change (the zero
+// blocks contribute nothing); what is per head -- the LayerNorm row sums, Q.K^T and the k-range of the state update
+// -- is restricted to the head's own 32 columns.
 #include <type_traits>
 
 #include "ttt_kernels.h"
@@ -31,14 +37,15 @@ struct FwdSmem {
   using TF = TileFmt<T>;
   static constexpr uint32_t SLOT = 3 * TF::BYTES;                  // q, k, v
   static constexpr uint32_t OFF_OUT = FWD_NST * SLOT;              // staging (raw format): 2 x output, 2 x Gp
-  static constexpr uint32_t OFF_LR = OFF_OUT + 4 * TF::RAW_BYTES;  // FWD_NST x 64 bytes
-  static constexpr uint32_t OFF_XCH = OFF_LR + FWD_NST * 64;       // 2 x Xch4
+  static constexpr uint32_t LR_SLOT = 128;                         // lr of one stage: 16 elements (x 2 heads when paired)
+  static constexpr uint32_t OFF_LR = OFF_OUT + 4 * TF::RAW_BYTES;
+  static constexpr uint32_t OFF_XCH = OFF_LR + FWD_NST * LR_SLOT;  // 2 x Xch4
   static constexpr uint32_t OFF_BAR = OFF_XCH + 2 * sizeof(Xch4);
   static constexpr uint32_t TOTAL = OFF_BAR + FWD_NST * 8;
   static constexpr uint32_t DYN_BYTES = TOTAL + 1024;  // slack for manual 1024-byte alignment
 };
 
-template <typename T>
+template <typename T, int SEG>
 __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     ttt_linear_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                           const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -47,6 +54,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
   using SM = FwdSmem<T>;
   constexpr int NP = TF::NP;
   constexpr bool TWO_PASS = (sizeof(T) == 4);
+  constexpr float INV_F = 1.f / SEG;  // features per head (LayerNorm row length)
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_u32 = smem_u32(smem_raw);
@@ -57,7 +65,9 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
 
   const Lane L;
   const int tid = L.tid, lane = L.lane, g = L.g, t = L.t, nb = L.nb;
-  const int stream = blockIdx.x;
+  const int hsel = L.warp >> 1;              // SEG = 32: which head of the pair this warp's columns belong to
+  const int khalf = (SEG == 32) ? hsel : -1; // and the k-range of the state that is its own block
+  const int stream = blockIdx.x;             // (batch, head) stream, or (batch, pair of heads) when SEG = 32
   const int head = stream % p.H;
   const int NS = p.NS;
   const int row_base = stream * p.T;  // first row of this stream in the [B*H*T, 64] view
@@ -80,13 +90,20 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     const int slot = s % FWD_NST;
     const uint32_t bar = bar0 + 8 * slot;
     const uint32_t tq = base + slot * SM::SLOT;
-    mbar_expect_tx(bar, 3 * TF::RAW_BYTES + CS * TF::ELT);
-    const int r0 = row_base + s * CS;
-    tma_load_tile<T>(tq, &tm_q, r0, bar);
-    tma_load_tile<T>(tq + TF::BYTES, &tm_k, r0, bar);
-    tma_load_tile<T>(tq + 2 * TF::BYTES, &tm_v, r0, bar);
-    bulk_load_1d(base + SM::OFF_LR + slot * 64,
-                 static_cast<const uint8_t*>(p.lr) + (size_t)(row_base + s * CS) * TF::ELT, CS * TF::ELT, bar);
+    mbar_expect_tx(bar, 3 * TF::RAW_BYTES + (SEG == 32 ? 2 : 1) * CS * TF::ELT);
+    tma_load_x<T, SEG>(tq, &tm_q, stream, s * CS, p.T, bar);
+    tma_load_x<T, SEG>(tq + TF::BYTES, &tm_k, stream, s * CS, p.T, bar);
+    tma_load_x<T, SEG>(tq + 2 * TF::BYTES, &tm_v, stream, s * CS, p.T, bar);
+    if constexpr (SEG == 64) {
+      bulk_load_1d(base + SM::OFF_LR + slot * SM::LR_SLOT,
+                   static_cast<const uint8_t*>(p.lr) + (size_t)(row_base + s * CS) * TF::ELT, CS * TF::ELT, bar);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 2; ++j)  // ttt_lr_eta is [B, H, T]: the two heads of the pair are T elements apart
+        bulk_load_1d(base + SM::OFF_LR + slot * SM::LR_SLOT + j * CS * TF::ELT,
+                     static_cast<const uint8_t*>(p.lr) + ((size_t)(2 * stream + j) * p.T + s * CS) * TF::ELT,
+                     CS * TF::ELT, bar);
+    }
   };
   if (tid == 0) {
     for (int s = 0; s < FWD_NST && s < NS; ++s) issue_loads(s);
@@ -118,7 +135,14 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int k = 8 * kt + 2 * t + (i & 1), n = nb + g + 8 * (i >> 1);
-      wt[kt][i] = ld_as_float<T>(p.w0, (size_t)stream * HD * HD + k * HD + n) * winv;
+      if constexpr (SEG == 64) {
+        wt[kt][i] = ld_as_float<T>(p.w0, (size_t)stream * HD * HD + k * HD + n) * winv;
+      } else {
+        // block-diagonal: head hsel's 32 x 32 state at rows / columns [32 hsel, 32 hsel + 32); zero elsewhere
+        wt[kt][i] = ((kt >> 2) == hsel)
+                        ? ld_as_float<T>(p.w0, (size_t)(2 * stream + hsel) * 32 * 32 + (k & 31) * 32 + (n & 31)) * winv
+                        : 0.f;
+      }
     }
 
   int xsel = 0;
@@ -158,8 +182,8 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
       for (int j = 0; j < 4; ++j) bs[nb + 8 * (j >> 1) + 2 * t + (j & 1)] = bias[j];
     }
 
-    const float lr_row[2] = {ld_as_float<T>(gbase + SM::OFF_LR + slot * 64, g),
-                             ld_as_float<T>(gbase + SM::OFF_LR + slot * 64, g + 8)};
+    const uint8_t* lrp = gbase + SM::OFF_LR + slot * SM::LR_SLOT + (SEG == 32 ? hsel * CS * TF::ELT : 0);
+    const float lr_row[2] = {ld_as_float<T>(lrp, g), ld_as_float<T>(lrp, g + 8)};
 
     // ---- Z1 = K W + b, Zq = Q W + b (columns nb..nb+15), Attn = Q K^T (full 16x16, every warp)
     float z1[2][4], zq[2][4], at[2][4];
@@ -181,8 +205,10 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
       }
       // the A fragments of K are also the B fragments of Q K^T (the same four 8x8 blocks in another order)
       const Pk<NP> bj0[2] = {ak[0], ak[2]}, bj1[2] = {ak[1], ak[3]};
-      mma_np<NP>(at[0], aq, bj0);
-      mma_np<NP>(at[1], aq, bj1);
+      if (SEG == 64 || (ks >> 1) == hsel) {  // Q K^T contracts over the head's own features only
+        mma_np<NP>(at[0], aq, bj0);
+        mma_np<NP>(at[1], aq, bj1);
+      }
     }
     // products were taken with What: Z = wscale * acc + b
     F2 z1p[2][2], zqp[2][2];
@@ -201,7 +227,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
 
     // ---- LN statistics of Z1, then G = dL/dZ1 and Gp = lr[row] * G
     float mean[2], rstd[2];
-    ln_row_stats<TWO_PASS>(z1p, xch, xsel, L, p.eps, mean, rstd, fail);
+    ln_row_stats<TWO_PASS, SEG>(z1p, xch, xsel, L, p.eps, mean, rstd, fail);
     if (fail) {
       failed = true;
       if (tid == 0) report_timeout(p.status, 2, s);
@@ -215,9 +241,9 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
       ln_l2_pieces<T>(z1p, mean, rstd, gam, bet, tk, tv, L, xh, gy, gx, sa, sb);
       float2 a0, a1;
       int f2_ = 0;
-      xch_rows2(&xch[xsel], L, sa[0], sb[0], sa[1], sb[1], a0, a1, f2_);
+      xch_rows2<SEG>(&xch[xsel], L, sa[0], sb[0], sa[1], sb[1], a0, a1, f2_);
       xsel ^= 1;
-      const float A[2] = {a0.x * (1.f / HD), a1.x * (1.f / HD)}, Bv[2] = {a0.y * (1.f / HD), a1.y * (1.f / HD)};
+      const float A[2] = {a0.x * INV_F, a1.x * INV_F}, Bv[2] = {a0.y * INV_F, a1.y * INV_F};
       const float rs[2] = {rstd[0] * lr_row[0], rstd[1] * lr_row[1]};
       g_from_pieces(gx, xh, A, Bv, rs, gp);
       st1[0] = make_float4(mean[0], rstd[0], A[0], Bv[0]);
@@ -264,7 +290,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     // ---- state update: W^T[nb.., :] -= te15 * Gp^T K ; b -= te15 * colsum(Gp)
     {
       const Pk<NP> agt[4] = {gt[0][0], gt[1][0], gt[0][1], gt[1][1]};
-      if (w_moves) state_update_direct<NP>(wt, agt, pk, lane);
+      if (w_moves) state_update_direct<NP>(wt, agt, pk, lane, khalf);
       if constexpr (NP == 1) {
         // column sums of the bf16 Gp tile as a product with a tile of ones (every row of the result is the sum)
         constexpr uint32_t ONES = 0x3F803F80u;
@@ -289,13 +315,16 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     int fl2 = 0;
     F2 zb[2][2];
     slab_pairs(zq, zb);
-    ln_row_stats<TWO_PASS>(zb, xch, xsel, L, p.eps, mean, rstd, fl2);
-    if (save && L.warp == 0 && t == 0) {
-      float4* sp = p.stats + ((size_t)row_base + (size_t)s * CS) * 2;
-      sp[2 * g] = st1[0];
-      sp[2 * g + 1] = make_float4(mean[0], rstd[0], 0.f, 0.f);
-      sp[2 * (g + 8)] = st1[1];
-      sp[2 * (g + 8) + 1] = make_float4(mean[1], rstd[1], 0.f, 0.f);
+    ln_row_stats<TWO_PASS, SEG>(zb, xch, xsel, L, p.eps, mean, rstd, fl2);
+    if (save && (L.warp & 1) == 0 && t == 0 && (SEG == 32 || L.warp == 0)) {
+      // two float4 per token (and per head of the pair: record index 2 * token + head)
+      constexpr int NH = (SEG == 32) ? 2 : 1;
+      float4* sp = p.stats + ((size_t)row_base + (size_t)s * CS) * 2 * NH;
+      const int h = (SEG == 32) ? hsel : 0;
+      sp[2 * (NH * g + h)] = st1[0];
+      sp[2 * (NH * g + h) + 1] = make_float4(mean[0], rstd[0], 0.f, 0.f);
+      sp[2 * (NH * (g + 8) + h)] = st1[1];
+      sp[2 * (NH * (g + 8) + h) + 1] = make_float4(mean[1], rstd[1], 0.f, 0.f);
     }
     const uint32_t so = base + SM::OFF_OUT + (s & 1) * TF::RAW_BYTES;
 #pragma unroll
@@ -310,8 +339,8 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     fence_proxy_async_smem();
     __syncthreads();
     if (tid == 0) {
-      tma_store_tile<T>(&tm_o, row_base + s * CS, so);
-      if (save) tma_store_tile<T>(&tm_g, row_base + s * CS, sg);
+      tma_store_x<T, SEG>(&tm_o, stream, s * CS, p.T, so);
+      if (save) tma_store_tile<T>(&tm_g, row_base + s * CS, sg);  // saved tiles are kept in the packed 64-wide form
       bulk_commit();
       bulk_wait_read<1>();
       if (s + FWD_NST < NS) issue_loads(s + FWD_NST);
@@ -331,8 +360,13 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     for (int kt = 0; kt < 8; ++kt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int idx = (8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1);
-        st_from_float<T>(p.w_out, (size_t)stream * HD * HD + idx, wt[kt][i] * wscale);
+        const int k = 8 * kt + 2 * t + (i & 1), n = nb + g + 8 * (i >> 1);
+        const int idx = k * HD + n;
+        if constexpr (SEG == 64) {
+          st_from_float<T>(p.w_out, (size_t)stream * HD * HD + idx, wt[kt][i] * wscale);
+        } else if ((kt >> 2) == hsel) {
+          st_from_float<T>(p.w_out, (size_t)(2 * stream + hsel) * 32 * 32 + (k & 31) * 32 + (n & 31), wt[kt][i] * wscale);
+        }
         if (save) wc[idx] = wt[kt][i] * wscale;
       }
     if (g == 0) {
@@ -347,19 +381,23 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
   if (tid == 0) bulk_wait_all<0>();
 }
 
-template <typename T>
+template <typename T, int SEG>
 static cudaError_t launch_fwd_t(const CUtensorMap* m, const LinFwdParams& p, int nstreams, cudaStream_t st) {
-  auto kfn = ttt_linear_fwd_kernel<T>;
+  auto kfn = ttt_linear_fwd_kernel<T, SEG>;
   cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FwdSmem<T>::DYN_BYTES);
   if (e != cudaSuccess) return e;
   kfn<<<nstreams, NTHREADS, FwdSmem<T>::DYN_BYTES, st>>>(m[0], m[1], m[2], m[3], m[4], p);
   return cudaGetLastError();
 }
 
-cudaError_t launch_linear_fwd(int dtype, const CUtensorMap* maps, const LinFwdParams& p, int nstreams,
+cudaError_t launch_linear_fwd(int dtype, int seg, const CUtensorMap* maps, const LinFwdParams& p, int nstreams,
                               cudaStream_t st) {
-  if (dtype == 1) return launch_fwd_t<__nv_bfloat16>(maps, p, nstreams, st);
-  return launch_fwd_t<float>(maps, p, nstreams, st);
+  if (seg == 32) {
+    if (dtype == 1) return launch_fwd_t<__nv_bfloat16, 32>(maps, p, nstreams, st);
+    return launch_fwd_t<float, 32>(maps, p, nstreams, st);
+  }
+  if (dtype == 1) return launch_fwd_t<__nv_bfloat16, 64>(maps, p, nstreams, st);
+  return launch_fwd_t<float, 64>(maps, p, nstreams, st);
 }
 
 }  // namespace ttt

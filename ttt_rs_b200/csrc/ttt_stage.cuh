@@ -27,8 +27,10 @@ struct __align__(16) Xch4 {
   float4 v[CS][5];  // [row][warp] with the row padded to 80 bytes: the 8 rows a warp reads fall in distinct banks
 };
 
-// Every thread contributes its two rows (g, g+8); returns the CTA-wide sums for those rows.
+// Every thread contributes its two rows (g, g+8); returns the sums over the row's SEG columns: all four warps
+// (SEG = 64) or the warp pair that holds this thread's 32-wide head (SEG = 32: warps 0,1 / 2,3).
 // `flag` is OR-reduced over the CTA by the same barrier (used to spread a timed-out wait).
+template <int SEG = 64>
 __device__ __forceinline__ void xch_rows(Xch4* xb, const Lane& L, const float4 a0, const float4 a1, float4& o0,
                                          float4& o1, int& flag) {
   float4 p0, p1;
@@ -41,17 +43,28 @@ __device__ __forceinline__ void xch_rows(Xch4* xb, const Lane& L, const float4 a
   flag = __syncthreads_or(flag);
   const float4* r0 = &xb->v[L.g][0];
   const float4* r1 = &xb->v[L.g + 8][0];
-  // (w0 + w1) + (w2 + w3) per component, two components per packed add
-  auto sum4 = [](const float4* r) {
-    const float4 a = r[0], b = r[1], c = r[2], d = r[3];
-    const F2 lo = f2add(f2add(f2(a.x, a.y), f2(b.x, b.y)), f2add(f2(c.x, c.y), f2(d.x, d.y)));
-    const F2 hi = f2add(f2add(f2(a.z, a.w), f2(b.z, b.w)), f2add(f2(c.z, c.w), f2(d.z, d.w)));
-    return make_float4(lo.x, lo.y, hi.x, hi.y);
-  };
-  o0 = sum4(r0);
-  o1 = sum4(r1);
+  if constexpr (SEG == 64) {
+    // (w0 + w1) + (w2 + w3) per component, two components per packed add
+    auto sum4 = [](const float4* r) {
+      const float4 a = r[0], b = r[1], c = r[2], d = r[3];
+      const F2 lo = f2add(f2add(f2(a.x, a.y), f2(b.x, b.y)), f2add(f2(c.x, c.y), f2(d.x, d.y)));
+      const F2 hi = f2add(f2add(f2(a.z, a.w), f2(b.z, b.w)), f2add(f2(c.z, c.w), f2(d.z, d.w)));
+      return make_float4(lo.x, lo.y, hi.x, hi.y);
+    };
+    o0 = sum4(r0);
+    o1 = sum4(r1);
+  } else {
+    auto sum2 = [](const float4* r) {
+      const float4 a = r[0], b = r[1];
+      const F2 lo = f2add(f2(a.x, a.y), f2(b.x, b.y)), hi = f2add(f2(a.z, a.w), f2(b.z, b.w));
+      return make_float4(lo.x, lo.y, hi.x, hi.y);
+    };
+    o0 = sum2(r0 + (L.warp & 2));
+    o1 = sum2(r1 + (L.warp & 2));
+  }
 }
 // Two-value variant (same buffer type, half the shuffles).
+template <int SEG = 64>
 __device__ __forceinline__ void xch_rows2(Xch4* xb, const Lane& L, float a0x, float a0y, float a1x, float a1y,
                                           float2& o0, float2& o1, int& flag) {
   a0x = quad_sum(a0x); a0y = quad_sum(a0y); a1x = quad_sum(a1x); a1y = quad_sum(a1y);
@@ -66,17 +79,24 @@ __device__ __forceinline__ void xch_rows2(Xch4* xb, const Lane& L, float a0x, fl
   const float4 q = *reinterpret_cast<const float4*>(&base[L.g * 6 + 2]);
   const float4 p2 = *reinterpret_cast<const float4*>(&base[(L.g + 8) * 6]);
   const float4 q2 = *reinterpret_cast<const float4*>(&base[(L.g + 8) * 6 + 2]);
-  // (w0 + w1) + (w2 + w3) for both values of a row with packed adds
-  o0 = f2add(f2add(f2(p.x, p.y), f2(p.z, p.w)), f2add(f2(q.x, q.y), f2(q.z, q.w)));
-  o1 = f2add(f2add(f2(p2.x, p2.y), f2(p2.z, p2.w)), f2add(f2(q2.x, q2.y), f2(q2.z, q2.w)));
+  if constexpr (SEG == 64) {
+    // (w0 + w1) + (w2 + w3) for both values of a row with packed adds
+    o0 = f2add(f2add(f2(p.x, p.y), f2(p.z, p.w)), f2add(f2(q.x, q.y), f2(q.z, q.w)));
+    o1 = f2add(f2add(f2(p2.x, p2.y), f2(p2.z, p2.w)), f2add(f2(q2.x, q2.y), f2(q2.z, q2.w)));
+  } else {
+    const bool hi = (L.warp & 2) != 0;  // this thread's head: warps 0,1 or warps 2,3
+    o0 = hi ? f2add(f2(q.x, q.y), f2(q.z, q.w)) : f2add(f2(p.x, p.y), f2(p.z, p.w));
+    o1 = hi ? f2add(f2(q2.x, q2.y), f2(q2.z, q2.w)) : f2add(f2(p2.x, p2.y), f2(p2.z, p2.w));
+  }
 }
 
 // LayerNorm row statistics of a slab: mean and 1/sqrt(var + eps) for rows g and g+8.
 // bf16 I/O uses one exchange (sum, sum of squares); float32 I/O uses the two-pass variance of the reference.
 // Slabs here are column pairs: F2 z[nt][r] = columns (nb + 8nt + 2t, +1) of row g + 8r.
-template <bool TWO_PASS>
+template <bool TWO_PASS, int SEG = 64>
 __device__ __forceinline__ void ln_row_stats(const F2 (&z)[2][2], Xch4* xch, int& xsel, const Lane& L, float eps,
                                              float (&mean)[2], float (&rstd)[2], int& flag) {
+  constexpr float INV = 1.f / SEG;  // features per LayerNorm row
   float s1[2], s2[2] = {0.f, 0.f};
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -84,13 +104,13 @@ __device__ __forceinline__ void ln_row_stats(const F2 (&z)[2][2], Xch4* xch, int
     if constexpr (!TWO_PASS) s2[r] = f2hsum(f2fma(z[0][r], z[0][r], f2mul(z[1][r], z[1][r])));
   }
   float2 a0, a1;
-  xch_rows2(&xch[xsel], L, s1[0], s2[0], s1[1], s2[1], a0, a1, flag);
+  xch_rows2<SEG>(&xch[xsel], L, s1[0], s2[0], s1[1], s2[1], a0, a1, flag);
   xsel ^= 1;
-  mean[0] = a0.x * (1.f / HD);
-  mean[1] = a1.x * (1.f / HD);
+  mean[0] = a0.x * INV;
+  mean[1] = a1.x * INV;
   if constexpr (!TWO_PASS) {
-    rstd[0] = rsqrtf(fmaxf(a0.y * (1.f / HD) - mean[0] * mean[0], 0.f) + eps);
-    rstd[1] = rsqrtf(fmaxf(a1.y * (1.f / HD) - mean[1] * mean[1], 0.f) + eps);
+    rstd[0] = rsqrtf(fmaxf(a0.y * INV - mean[0] * mean[0], 0.f) + eps);
+    rstd[1] = rsqrtf(fmaxf(a1.y * INV - mean[1] * mean[1], 0.f) + eps);
   } else {
     float q2[2];
 #pragma unroll
@@ -99,10 +119,10 @@ __device__ __forceinline__ void ln_row_stats(const F2 (&z)[2][2], Xch4* xch, int
       q2[r] = f2hsum(f2fma(d0, d0, f2mul(d1, d1)));
     }
     int f2_ = 0;
-    xch_rows2(&xch[xsel], L, q2[0], 0.f, q2[1], 0.f, a0, a1, f2_);
+    xch_rows2<SEG>(&xch[xsel], L, q2[0], 0.f, q2[1], 0.f, a0, a1, f2_);
     xsel ^= 1;
-    rstd[0] = 1.0f / sqrtf(a0.x * (1.f / HD) + eps);
-    rstd[1] = 1.0f / sqrtf(a1.x * (1.f / HD) + eps);
+    rstd[0] = 1.0f / sqrtf(a0.x * INV + eps);
+    rstd[1] = 1.0f / sqrtf(a1.x * INV + eps);
   }
 }
 
@@ -191,11 +211,14 @@ __device__ __forceinline__ void state_update(float (&wt)[8][4], const Pk<NP> (&a
 // Same rank-16 update accumulated straight into the state registers: S^T += A^T-fragments x K.  Used with the state
 // kept as W / (-te15), so neither temporaries nor a scaling pass are needed; the backward's reversal passes the
 // fragments with their sign bits flipped.
+// `khalf`: -1 = all 64 k-columns; 0 / 1 = only k in [0,32) / [32,64) (a 32-wide head's own block when two heads share
+// the tile: the other block of the state stays zero).
 template <int NP>
 __device__ __forceinline__ void state_update_direct(float (&wt)[8][4], const Pk<NP> (&agt)[4], uint32_t k_planes,
-                                                    int lane) {
+                                                    int lane, int khalf = -1) {
 #pragma unroll
   for (int kp = 0; kp < 4; ++kp) {
+    if (khalf >= 0 && (kp >> 1) != khalf) continue;
     Pk<NP> bk[4];
     ldsm_np<NP>(bk, k_planes + lane_off_B_kn(lane, 16 * kp), TILE_BF16_BYTES, true);
     const Pk<NP> b0[2] = {bk[0], bk[1]}, b1[2] = {bk[2], bk[3]};

@@ -115,4 +115,39 @@ __device__ __forceinline__ void tma_store_tile(const CUtensorMap* tm, int row0, 
   }
 }
 
+// Tile of a PAIR of 32-wide heads (head_dim 32): the two heads' 16 x 32 blocks side by side in one 16 x 64 tile, so
+// that the 64-wide kernels serve two such streams at once.  bf16: one 4-D box {32 features, 2 heads, 16 tokens,
+// 1 pair} of the [B*H/2, 2, T, 32] view lands as 16 rows of 128 bytes; float32: each half tile is one 2-D box of the
+// [B*H*T, 32] view.  `pair` = index of the head pair (packed stream), `t0` = first token, seq = tokens per sequence.
+template <typename T>
+__device__ __forceinline__ void tma_load_pair_tile(uint32_t tile, const CUtensorMap* tm, int pair, int t0, int seq,
+                                                   uint32_t bar) {
+  if constexpr (sizeof(T) == 2) {
+    tma_load_4d(tile, tm, 0, 0, t0, pair, bar);
+  } else {
+    tma_load_2d(tile, tm, 0, (2 * pair) * seq + t0, bar);
+    tma_load_2d(tile + 2048, tm, 0, (2 * pair + 1) * seq + t0, bar);
+  }
+}
+template <typename T>
+__device__ __forceinline__ void tma_store_pair_tile(const CUtensorMap* tm, int pair, int t0, int seq, uint32_t tile) {
+  if constexpr (sizeof(T) == 2) {
+    tma_store_4d(tm, 0, 0, t0, pair, tile);
+  } else {
+    tma_store_2d(tm, 0, (2 * pair) * seq + t0, tile);
+    tma_store_2d(tm, 0, (2 * pair + 1) * seq + t0, tile + 2048);
+  }
+}
+// SEG = 64: one head per tile; SEG = 32: a pair of heads per tile.  `stream` is the (packed) stream index.
+template <typename T, int SEG>
+__device__ __forceinline__ void tma_load_x(uint32_t tile, const CUtensorMap* tm, int stream, int t0, int seq, uint32_t bar) {
+  if constexpr (SEG == 64) tma_load_tile<T>(tile, tm, stream * seq + t0, bar);
+  else tma_load_pair_tile<T>(tile, tm, stream, t0, seq, bar);
+}
+template <typename T, int SEG>
+__device__ __forceinline__ void tma_store_x(const CUtensorMap* tm, int stream, int t0, int seq, uint32_t tile) {
+  if constexpr (SEG == 64) tma_store_tile<T>(tm, stream * seq + t0, tile);
+  else tma_store_pair_tile<T>(tm, stream, t0, seq, tile);
+}
+
 }  // namespace ttt

@@ -227,7 +227,7 @@ class TttTileMultiKernel:
         w_ck = b_ck = None
         if save_state:
             w_ck = torch.empty(lib.ttt_linear_weight_ckpt_bytes(C.byref(d)) // 4, dtype=torch.float32,
-                               device=dev).view(B * H * (nck + 1), F, F)
+                               device=dev).view(-1, 64, 64)  # head_dim 32: a pair of heads per 64 x 64 block
             b_ck = torch.empty(lib.ttt_linear_bias_ckpt_bytes(C.byref(d)), dtype=torch.uint8, device=dev)
         status = device_status(dev)
         with torch.cuda.device(dev):
