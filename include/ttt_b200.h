@@ -44,7 +44,7 @@ enum ttt_status {
   TTT_OK = 0,
   TTT_ERR_NULL = 1,        /* a required pointer is null */
   TTT_ERR_SHAPE = 2,       /* non-positive dim, seq_len % mini_batch != 0, checkpoint_interval < 1 */
-  TTT_ERR_UNSUPPORTED = 3, /* (mini_batch, head_dim) other than (16, 64); unknown dtype */
+  TTT_ERR_UNSUPPORTED = 3, /* tile (mini_batch, head_dim) not built (see ttt_dims); unknown dtype */
   TTT_ERR_ALIGN = 4,       /* a tensor base is not 16-byte aligned */
   TTT_ERR_CUDA = 5,        /* a CUDA runtime/driver call failed (message in ttt_b200_last_error) */
   TTT_ERR_TIMEOUT = 6,     /* written by kernels into `status`, never returned by a launch call */
@@ -59,7 +59,7 @@ typedef struct ttt_dims {
   int32_t batch;               /* B */
   int32_t heads;               /* H */
   int32_t seq_len;             /* T, multiple of mini_batch */
-  int32_t head_dim;            /* F (64) */
+  int32_t head_dim;            /* F: 64; TTT-Linear forward/backward also take 32 with an even number of heads */
   int32_t mini_batch;          /* CS (16) */
   int32_t checkpoint_interval; /* K >= 1, in stages */
   float epsilon;               /* LayerNorm epsilon */
@@ -86,6 +86,10 @@ int64_t ttt_linear_num_checkpoints(const ttt_dims* d);
  *   weight_ckpt: float32 W before every K-th stage plus the final W, [B*H*(NCK+1), F, F];
  *   bias_ckpt:   per stage the lr-scaled LN gradient tile [B*H*T, F] of T, two float4 of row statistics per
  *                token, and the float32 bias at the start of every stage.
+ * (head_dim 32, the reference's 16x32 tile, rust/fused/src/linear_fused_tile/mod.rs:32-37: the kernels run heads
+ * 2j and 2j+1 of a batch element side by side in one 64-wide tile, so the saved state is laid out per PAIR of heads,
+ * 64 x 64 float32 per checkpoint with the two 32 x 32 states on the diagonal.  The sizes below account for it; all
+ * tensors of the caller keep the [B,H,...,32] layouts listed at the entry points.)
  * The backward walks W back from each checkpoint with the saved gradient tiles instead of re-simulating the
  * forward, so `checkpoint_interval` only sets how often W is re-read exactly. */
 size_t ttt_linear_weight_ckpt_bytes(const ttt_dims* d);

@@ -76,31 +76,22 @@ int make_gemm_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, 
   return TTT_OK;
 }
 
-// Views of a [B,H,T,32] tensor for the kernels that take a PAIR of 32-wide heads per 64-wide tile.  bf16: 4-D
-// [B*H/2 pairs, T tokens, 2 heads, 32 features] with a box of one pair x 16 tokens x 2 heads x 32 features, which
-// lands in shared memory as 16 rows of 128 bytes, head 0's features then head 1's: the same image as a 64-wide tile.
-// float32: 2-D [B*H*T, 32], box = 16 tokens x 32 features = one half tile.
+// View of a float32 [B,H,T,32] tensor for the kernels that take a PAIR of 32-wide heads per 64-wide tile: 2-D
+// [B*H*T, 32], box = 16 tokens x 32 features = 16 rows of 128 bytes = one half tile.  (In bf16 a half tile is 64 bytes
+// wide, narrower than the swizzle span; those tiles are gathered by the kernel from the plain pointer and the map is a
+// placeholder over the same memory.)
 int make_pair_map(CUtensorMap* m, const void* base, int64_t pairs, int64_t T, int dtype) {
   EncodeFn enc = get_encode_fn();
   if (enc == nullptr) return fail(TTT_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
-  CUresult r;
-  if (dtype == TTT_BF16) {
-    const cuuint64_t dims[4] = {32, 2, (cuuint64_t)T, (cuuint64_t)pairs};
-    const cuuint64_t strides[3] = {(cuuint64_t)(T * 32 * 2), 32 * 2, (cuuint64_t)(2 * T * 32 * 2)};
-    const cuuint32_t box[4] = {32, 2, 16, 1};
-    const cuuint32_t estr[4] = {1, 1, 1, 1};
-    r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  } else {
-    const cuuint64_t dims[2] = {32, (cuuint64_t)(2 * pairs * T)};
-    const cuuint64_t strides[1] = {32 * 4};
-    const cuuint32_t box[2] = {32, 16};
-    const cuuint32_t estr[2] = {1, 1};
-    r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  }
+  const bool bf = dtype == TTT_BF16;
+  const cuuint64_t dims[2] = {32, (cuuint64_t)(2 * pairs * T)};
+  const cuuint64_t strides[1] = {(cuuint64_t)(32 * (bf ? 2 : 4))};
+  const cuuint32_t box[2] = {32, 16};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   bf ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(TTT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return TTT_OK;
 }
@@ -399,6 +390,10 @@ int ttt_linear_forward(const ttt_dims* d, const void* xq, const void* xk, const 
   p.stats = save ? reinterpret_cast<float4*>(aux + al.off_stats) : nullptr;
   p.b_stage = save ? reinterpret_cast<float*>(aux + al.off_bias) : nullptr;
   p.status = static_cast<uint32_t*>(status);
+  p.xq = xq;
+  p.xk = xk;
+  p.xv = xv;
+  p.out = output;
   p.H = pk.heads;
   p.T = d->seq_len;
   p.NS = d->seq_len / d->mini_batch;
@@ -511,6 +506,13 @@ int ttt_linear_backward_state_grads(const ttt_dims* d, const void* xq, const voi
   p.handoff_polls = g_handoff_polls.load();
   p.item_base = g_item_base.load();
   p.status = static_cast<uint32_t*>(status);
+  p.xq = xq;
+  p.xk = xk;
+  p.xv = xv;
+  p.d_out = grad_output;
+  p.d_q = grad_xq;
+  p.d_k = grad_xk;
+  p.d_v = grad_xv;
   p.H = pk.heads;
   p.T = d->seq_len;
   p.NS = d->seq_len / d->mini_batch;

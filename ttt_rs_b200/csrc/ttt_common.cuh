@@ -83,18 +83,16 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, int x, int y
                "r"(y), "r"(src)
                : "memory");
 }
-// 4-D tiled forms (two 32-wide heads gathered into one 64-wide tile: coordinates feature, head in pair, token, pair).
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm, int x, int y, int z, int w, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
-      ::"r"(dst), "l"(tm), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
-      : "memory");
+// 16-byte asynchronous copy global -> shared by the executing thread (not the bulk / TMA path), and the arrival that
+// makes an mbarrier wait for all such copies the thread has issued so far.  `.noinc`: the arrival is one of the
+// arrivals the barrier was initialised to expect.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
-__device__ __forceinline__ void tma_store_4d(const CUtensorMap* tm, int x, int y, int z, int w, uint32_t src) {
-  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%1, %2, %3, %4}], [%5];" ::"l"(tm), "r"(x),
-               "r"(y), "r"(z), "r"(w), "r"(src)
-               : "memory");
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 // Untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16).
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),

@@ -20,6 +20,12 @@ struct LinFwdParams {
   float4* stats;          // [B*H*T][2]: (mean1, rstd1, A, Bv), (mean2, rstd2, 0, 0) per token
   float* b_stage;         // [B*H*(NS+1), F] float32: bias at the start of every stage, final bias last
   uint32_t* status;       // device uint32[4] or null
+  // the caller's tensors behind the q, k, v, out maps; read only where tiles are gathered instead of loaded by TMA
+  // (head_dim 32 in bf16)
+  const void* xq;
+  const void* xk;
+  const void* xv;
+  void* out;
   int H, T, NS, K, NCK;
   float eps;
 };
@@ -49,6 +55,14 @@ struct LinBwdParams {
   float* part_te;   // workspace: [B*H][T] per-stream token_eta gradient terms
   float* part_w;    // workspace: [B*H][F*F + F] float32 dW, db per stream (for the packed reduction)
   uint32_t* status;
+  // the caller's tensors behind the q, k, v, d_out, d_q, d_k, d_v maps (used where tiles are gathered: head_dim 32, bf16)
+  const void* xq;
+  const void* xk;
+  const void* xv;
+  const void* d_out;
+  void* d_q;
+  void* d_k;
+  void* d_v;
   int H, T, NS, K, NCK;
   float eps;
 };

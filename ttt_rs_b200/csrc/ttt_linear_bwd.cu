@@ -73,6 +73,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
   constexpr uint32_t PL = TILE_BF16_BYTES;  // plane stride
   constexpr float INV_F = 1.f / SEG;        // features per head (LayerNorm row length)
   constexpr int NH = (SEG == 32) ? 2 : 1;   // heads per tile
+  constexpr bool GATHER = PairIo<T, SEG>::GATHER;  // q, k, v, d_out, d_q, d_k, d_v tiles moved by the threads, not TMA
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_u32 = smem_u32(smem_raw);
@@ -100,33 +101,45 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
     prefetch_tmap(&tm_dq);
     prefetch_tmap(&tm_dk);
     prefetch_tmap(&tm_dv);
-    for (int i = 0; i < SM::NSLOT; ++i) mbar_init(bar0 + 8 * i, 1);
+    // arrivals per phase: thread 0's expect_tx, plus every thread's cp.async arrival where tiles are gathered
+    for (int i = 0; i < SM::NSLOT; ++i) mbar_init(bar0 + 8 * i, GATHER ? 1 + NTHREADS : 1);
     fence_mbar_init();
   }
   __syncthreads();
 
-  // everything stage s needs, into slot n % NSLOT
+  // everything stage s needs, into slot n % NSLOT; called by every thread, thread 0 issues the TMA / bulk copies
   auto issue_loads = [&](int n, int s) {
     const int slot = n % SM::NSLOT;
     const uint32_t bar = bar0 + 8 * slot;
     const uint32_t sl = base + slot * SM::SLOT;
     const int r0 = row_base + s * CS;
-    mbar_expect_tx(bar, 5u * TF::RAW_BYTES + NH * 512u + 256u + NH * CS * TF::ELT);
-    tma_load_x<T, SEG>(sl + SM::OFF_K, &tm_k, stream, s * CS, p.T, bar);
-    tma_load_tile<T>(sl + SM::OFF_G, &tm_g, r0, bar);  // saved tiles are kept in the packed 64-wide form
-    tma_load_x<T, SEG>(sl + SM::OFF_Q, &tm_q, stream, s * CS, p.T, bar);
-    tma_load_x<T, SEG>(sl + SM::OFF_V, &tm_v, stream, s * CS, p.T, bar);
-    tma_load_x<T, SEG>(sl + SM::OFF_DO, &tm_do, stream, s * CS, p.T, bar);
-    bulk_load_1d(sl + SM::OFF_STAT, p.stats + (size_t)r0 * 2 * NH, NH * 512u, bar);
-    bulk_load_1d(sl + SM::OFF_BS, p.b_stage + ((size_t)stream * (NS + 1) + s) * HD, 256u, bar);
-    if constexpr (SEG == 64) {
-      bulk_load_1d(sl + SM::OFF_LR, static_cast<const uint8_t*>(p.lr) + (size_t)r0 * TF::ELT, CS * TF::ELT, bar);
-    } else {
+    if (tid == 0) {
+      mbar_expect_tx(bar, (GATHER ? 1u : 5u) * TF::RAW_BYTES + NH * 512u + 256u + NH * CS * TF::ELT);
+      tma_load_tile<T>(sl + SM::OFF_G, &tm_g, r0, bar);  // saved tiles are kept in the packed 64-wide form
+      if constexpr (!GATHER) {
+        tma_load_x<T, SEG>(sl + SM::OFF_K, &tm_k, stream, s * CS, p.T, bar);
+        tma_load_x<T, SEG>(sl + SM::OFF_Q, &tm_q, stream, s * CS, p.T, bar);
+        tma_load_x<T, SEG>(sl + SM::OFF_V, &tm_v, stream, s * CS, p.T, bar);
+        tma_load_x<T, SEG>(sl + SM::OFF_DO, &tm_do, stream, s * CS, p.T, bar);
+      }
+      bulk_load_1d(sl + SM::OFF_STAT, p.stats + (size_t)r0 * 2 * NH, NH * 512u, bar);
+      bulk_load_1d(sl + SM::OFF_BS, p.b_stage + ((size_t)stream * (NS + 1) + s) * HD, 256u, bar);
+      if constexpr (SEG == 64) {
+        bulk_load_1d(sl + SM::OFF_LR, static_cast<const uint8_t*>(p.lr) + (size_t)r0 * TF::ELT, CS * TF::ELT, bar);
+      } else {
 #pragma unroll
-      for (int j = 0; j < 2; ++j)
-        bulk_load_1d(sl + SM::OFF_LR + j * CS * TF::ELT,
-                     static_cast<const uint8_t*>(p.lr) + ((size_t)(2 * stream + j) * p.T + s * CS) * TF::ELT,
-                     CS * TF::ELT, bar);
+        for (int j = 0; j < 2; ++j)
+          bulk_load_1d(sl + SM::OFF_LR + j * CS * TF::ELT,
+                       static_cast<const uint8_t*>(p.lr) + ((size_t)(2 * stream + j) * p.T + s * CS) * TF::ELT,
+                       CS * TF::ELT, bar);
+      }
+    }
+    if constexpr (GATHER) {
+      gather_pair_tile_bf16(sl + SM::OFF_K, p.xk, stream, s * CS, p.T, tid);
+      gather_pair_tile_bf16(sl + SM::OFF_Q, p.xq, stream, s * CS, p.T, tid);
+      gather_pair_tile_bf16(sl + SM::OFF_V, p.xv, stream, s * CS, p.T, tid);
+      gather_pair_tile_bf16(sl + SM::OFF_DO, p.d_out, stream, s * CS, p.T, tid);
+      cp_async_mbar_arrive_noinc(bar);
     }
   };
 
@@ -171,7 +184,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
     row_base = stream * p.T;
     const int head = stream % p.H;
     const int s_lo = chunk * p.CH, s_hi = min(s_lo + p.CH, NS) - 1;
-    if (tid == 0) issue_loads(n, s_hi);
+    issue_loads(n, s_hi);
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
       const int c = nb + 8 * nt + 2 * t;
@@ -266,7 +279,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       // so the other slot may be overwritten
       if (!next_issued) {
         next_issued = true;
-        if (tid == 0 && s > s_lo) issue_loads(n + 1, s - 1);
+        if (s > s_lo) issue_loads(n + 1, s - 1);
       }
     };
     if constexpr (NP == 3) {
@@ -631,7 +644,11 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
         }
       fence_proxy_async_smem();
       __syncthreads();
-      if (tid == 0) {
+      if constexpr (GATHER) {
+        scatter_pair_tile_bf16(p.d_q, stream, s * CS, p.T, so_q, tid);
+        scatter_pair_tile_bf16(p.d_k, stream, s * CS, p.T, so_k, tid);
+        scatter_pair_tile_bf16(p.d_v, stream, s * CS, p.T, so_v, tid);
+      } else if (tid == 0) {
         tma_store_x<T, SEG>(&tm_dq, stream, s * CS, p.T, so_q);
         tma_store_x<T, SEG>(&tm_dk, stream, s * CS, p.T, so_k);
         tma_store_x<T, SEG>(&tm_dv, stream, s * CS, p.T, so_v);
@@ -707,6 +724,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
     }
   }  // item loop
   if (tid == 0) bulk_wait_all<0>();
+  if constexpr (GATHER) cp_async_wait_all();  // (an item that gave up may leave gathers in flight)
 }
 
 // ----------------------------------------------------------------------------------------------------

@@ -55,6 +55,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
   constexpr int NP = TF::NP;
   constexpr bool TWO_PASS = (sizeof(T) == 4);
   constexpr float INV_F = 1.f / SEG;  // features per head (LayerNorm row length)
+  constexpr bool GATHER = PairIo<T, SEG>::GATHER;  // q, k, v, out tiles moved by the threads instead of TMA
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_u32 = smem_u32(smem_raw);
@@ -81,33 +82,43 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     prefetch_tmap(&tm_v);
     prefetch_tmap(&tm_o);
     prefetch_tmap(&tm_g);
-    for (int i = 0; i < FWD_NST; ++i) mbar_init(bar0 + 8 * i, 1);
+    // arrivals per phase: thread 0's expect_tx, plus every thread's cp.async arrival where tiles are gathered
+    for (int i = 0; i < FWD_NST; ++i) mbar_init(bar0 + 8 * i, GATHER ? 1 + NTHREADS : 1);
     fence_mbar_init();
   }
   __syncthreads();
 
+  // called by every thread; thread 0 issues the TMA / bulk copies
   auto issue_loads = [&](int s) {
     const int slot = s % FWD_NST;
     const uint32_t bar = bar0 + 8 * slot;
     const uint32_t tq = base + slot * SM::SLOT;
-    mbar_expect_tx(bar, 3 * TF::RAW_BYTES + (SEG == 32 ? 2 : 1) * CS * TF::ELT);
-    tma_load_x<T, SEG>(tq, &tm_q, stream, s * CS, p.T, bar);
-    tma_load_x<T, SEG>(tq + TF::BYTES, &tm_k, stream, s * CS, p.T, bar);
-    tma_load_x<T, SEG>(tq + 2 * TF::BYTES, &tm_v, stream, s * CS, p.T, bar);
-    if constexpr (SEG == 64) {
-      bulk_load_1d(base + SM::OFF_LR + slot * SM::LR_SLOT,
-                   static_cast<const uint8_t*>(p.lr) + (size_t)(row_base + s * CS) * TF::ELT, CS * TF::ELT, bar);
-    } else {
+    if (tid == 0) {
+      mbar_expect_tx(bar, (GATHER ? 0 : 3 * TF::RAW_BYTES) + (SEG == 32 ? 2 : 1) * CS * TF::ELT);
+      if constexpr (!GATHER) {
+        tma_load_x<T, SEG>(tq, &tm_q, stream, s * CS, p.T, bar);
+        tma_load_x<T, SEG>(tq + TF::BYTES, &tm_k, stream, s * CS, p.T, bar);
+        tma_load_x<T, SEG>(tq + 2 * TF::BYTES, &tm_v, stream, s * CS, p.T, bar);
+      }
+      if constexpr (SEG == 64) {
+        bulk_load_1d(base + SM::OFF_LR + slot * SM::LR_SLOT,
+                     static_cast<const uint8_t*>(p.lr) + (size_t)(row_base + s * CS) * TF::ELT, CS * TF::ELT, bar);
+      } else {
 #pragma unroll
-      for (int j = 0; j < 2; ++j)  // ttt_lr_eta is [B, H, T]: the two heads of the pair are T elements apart
-        bulk_load_1d(base + SM::OFF_LR + slot * SM::LR_SLOT + j * CS * TF::ELT,
-                     static_cast<const uint8_t*>(p.lr) + ((size_t)(2 * stream + j) * p.T + s * CS) * TF::ELT,
-                     CS * TF::ELT, bar);
+        for (int j = 0; j < 2; ++j)  // ttt_lr_eta is [B, H, T]: the two heads of the pair are T elements apart
+          bulk_load_1d(base + SM::OFF_LR + slot * SM::LR_SLOT + j * CS * TF::ELT,
+                       static_cast<const uint8_t*>(p.lr) + ((size_t)(2 * stream + j) * p.T + s * CS) * TF::ELT,
+                       CS * TF::ELT, bar);
+      }
+    }
+    if constexpr (GATHER) {
+      gather_pair_tile_bf16(tq, p.xq, stream, s * CS, p.T, tid);
+      gather_pair_tile_bf16(tq + TF::BYTES, p.xk, stream, s * CS, p.T, tid);
+      gather_pair_tile_bf16(tq + 2 * TF::BYTES, p.xv, stream, s * CS, p.T, tid);
+      cp_async_mbar_arrive_noinc(bar);
     }
   };
-  if (tid == 0) {
-    for (int s = 0; s < FWD_NST && s < NS; ++s) issue_loads(s);
-  }
+  for (int s = 0; s < FWD_NST && s < NS; ++s) issue_loads(s);
 
   // ---- per-thread constants: 4 owned columns c(nt,e) = nb + 8nt + 2t + e, rows g and g+8
   F2 gam[2], bet[2];
@@ -338,13 +349,14 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
       }
     fence_proxy_async_smem();
     __syncthreads();
+    if constexpr (GATHER) scatter_pair_tile_bf16(p.out, stream, s * CS, p.T, so, tid);
     if (tid == 0) {
-      tma_store_x<T, SEG>(&tm_o, stream, s * CS, p.T, so);
+      if constexpr (!GATHER) tma_store_x<T, SEG>(&tm_o, stream, s * CS, p.T, so);
       if (save) tma_store_tile<T>(&tm_g, row_base + s * CS, sg);  // saved tiles are kept in the packed 64-wide form
       bulk_commit();
       bulk_wait_read<1>();
-      if (s + FWD_NST < NS) issue_loads(s + FWD_NST);
     }
+    if (s + FWD_NST < NS) issue_loads(s + FWD_NST);
     return true;
   };
   for (int s0 = 0; s0 < NS; s0 += FWD_NST) {
@@ -379,6 +391,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     }
   }
   if (tid == 0) bulk_wait_all<0>();
+  if constexpr (GATHER) cp_async_wait_all();  // (a stage that gave up may leave gathers in flight)
 }
 
 template <typename T, int SEG>

@@ -116,38 +116,54 @@ __device__ __forceinline__ void tma_store_tile(const CUtensorMap* tm, int row0, 
 }
 
 // Tile of a PAIR of 32-wide heads (head_dim 32): the two heads' 16 x 32 blocks side by side in one 16 x 64 tile, so
-// that the 64-wide kernels serve two such streams at once.  bf16: one 4-D box {32 features, 2 heads, 16 tokens,
-// 1 pair} of the [B*H/2, 2, T, 32] view lands as 16 rows of 128 bytes; float32: each half tile is one 2-D box of the
-// [B*H*T, 32] view.  `pair` = index of the head pair (packed stream), `t0` = first token, seq = tokens per sequence.
-template <typename T>
-__device__ __forceinline__ void tma_load_pair_tile(uint32_t tile, const CUtensorMap* tm, int pair, int t0, int seq,
-                                                   uint32_t bar) {
-  if constexpr (sizeof(T) == 2) {
-    tma_load_4d(tile, tm, 0, 0, t0, pair, bar);
-  } else {
-    tma_load_2d(tile, tm, 0, (2 * pair) * seq + t0, bar);
-    tma_load_2d(tile + 2048, tm, 0, (2 * pair + 1) * seq + t0, bar);
-  }
+// that the 64-wide kernels serve two such streams at once.  `pair` = index of the head pair (packed stream), `t0` =
+// first token, `seq` = tokens per sequence; the caller's tensor is [B*H, seq, 32], heads 2 pair and 2 pair + 1.
+//
+// float32: a half tile is 16 rows of 128 bytes, exactly one 128-byte-swizzled TMA box of the 2-D view [B*H*seq, 32].
+// bf16: a half tile is only 64 bytes wide, and a swizzled TMA box row narrower than the swizzle span still occupies a
+// whole 128-byte row of shared memory, so TMA cannot put the two halves side by side.  The tile is gathered instead:
+// 128 chunks of 16 bytes, one cp.async per thread, written at the swizzled position TMA would have used; results leave
+// the same way (ld.shared + st.global per thread).
+template <typename T, int SEG>
+struct PairIo {
+  static constexpr bool GATHER = (SEG == 32 && sizeof(T) == 2);
+};
+__device__ __forceinline__ void gather_pair_tile_bf16(uint32_t tile, const void* base, int pair, int t0, int seq, int tid) {
+  const int row = tid >> 3, c = tid & 7;  // chunk c of the 128-byte row: head c >> 2, features 8 (c & 3) ..
+  const uint8_t* src = static_cast<const uint8_t*>(base) +
+                       (((size_t)(2 * pair + (c >> 2)) * seq + t0 + row) * 32 + (c & 3) * 8) * 2;
+  cp_async_16(tile + row * 128 + ((c ^ (row & 7)) << 4), src);
 }
-template <typename T>
-__device__ __forceinline__ void tma_store_pair_tile(const CUtensorMap* tm, int pair, int t0, int seq, uint32_t tile) {
-  if constexpr (sizeof(T) == 2) {
-    tma_store_4d(tm, 0, 0, t0, pair, tile);
-  } else {
-    tma_store_2d(tm, 0, (2 * pair) * seq + t0, tile);
-    tma_store_2d(tm, 0, (2 * pair + 1) * seq + t0, tile + 2048);
-  }
+__device__ __forceinline__ void scatter_pair_tile_bf16(void* base, int pair, int t0, int seq, uint32_t tile, int tid) {
+  const int row = tid >> 3, c = tid & 7;
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(tile + row * 128 + ((c ^ (row & 7)) << 4)));
+  uint8_t* dst = static_cast<uint8_t*>(base) + (((size_t)(2 * pair + (c >> 2)) * seq + t0 + row) * 32 + (c & 3) * 8) * 2;
+  *reinterpret_cast<uint4*>(dst) = v;
 }
-// SEG = 64: one head per tile; SEG = 32: a pair of heads per tile.  `stream` is the (packed) stream index.
+// TMA side.  SEG = 64: one head per tile, `stream` * seq + t0 is the tile's first row of the [B*H*seq, 64] view.
+// SEG = 32, float32: two boxes of the [B*H*seq, 32] view.  (SEG = 32, bf16 does not come here: PairIo::GATHER.)
 template <typename T, int SEG>
 __device__ __forceinline__ void tma_load_x(uint32_t tile, const CUtensorMap* tm, int stream, int t0, int seq, uint32_t bar) {
-  if constexpr (SEG == 64) tma_load_tile<T>(tile, tm, stream * seq + t0, bar);
-  else tma_load_pair_tile<T>(tile, tm, stream, t0, seq, bar);
+  static_assert(!PairIo<T, SEG>::GATHER, "bf16 pair tiles are gathered, not loaded by TMA");
+  if constexpr (SEG == 64) {
+    tma_load_tile<T>(tile, tm, stream * seq + t0, bar);
+  } else {
+    tma_load_2d(tile, tm, 0, (2 * stream) * seq + t0, bar);
+    tma_load_2d(tile + 2048, tm, 0, (2 * stream + 1) * seq + t0, bar);
+  }
 }
 template <typename T, int SEG>
 __device__ __forceinline__ void tma_store_x(const CUtensorMap* tm, int stream, int t0, int seq, uint32_t tile) {
-  if constexpr (SEG == 64) tma_store_tile<T>(tm, stream * seq + t0, tile);
-  else tma_store_pair_tile<T>(tm, stream, t0, seq, tile);
+  static_assert(!PairIo<T, SEG>::GATHER, "bf16 pair tiles are scattered, not stored by TMA");
+  if constexpr (SEG == 64) {
+    tma_store_tile<T>(tm, stream * seq + t0, tile);
+  } else {
+    tma_store_2d(tm, 0, (2 * stream) * seq + t0, tile);
+    tma_store_2d(tm, 0, (2 * stream + 1) * seq + t0, tile + 2048);
+  }
 }
 
 }  // namespace ttt
