@@ -52,6 +52,9 @@ WORKLOADS = {
                      desc="TTT-MLP inner loop fwd (64-256-64, GELU tanh), bf16, B=16 H=12 T=2048 d=64 mb=16"),
     "cfg2": dict(B=16, H=12, T=2048, dtype="bf16", K=1, backward=True, inner="mlp",
                  desc="TTT-MLP inner loop fwd+bwd (64-256-64, GELU tanh), bf16, B=16 H=12 T=2048 d=64 mb=16"),
+    # the reference's 125m-h32 preset: hidden 768 as 24 heads of 32 features (tile 16x32), two heads per kernel tile
+    "cfg1-d32": dict(B=32, H=24, T=2048, F=32, dtype="bf16", K=16, backward=True,
+                     desc="TTT-Linear inner loop fwd+bwd, bf16, B=32 H=24 T=2048 d=32 mb=16 ckpt=16"),
     "cfg4-8k": dict(B=8, H=32, T=8192, dtype="bf16", K=16, backward=True,
                     desc="TTT-Linear inner loop fwd+bwd, bf16, B=8 H=32 T=8192 d=64 mb=16 ckpt=16"),
     "cfg4-16k": dict(B=8, H=32, T=16384, dtype="bf16", K=16, backward=True,
@@ -90,6 +93,7 @@ def algorithmic_bytes(w, fwd=True, bwd=True):
     its share of the float32 checkpoints; backward reads q,k,v,d_out (4Fs) + lr, writes dq,dk,dv (3Fs) + dlr and
     re-reads the checkpoints; per-stream constants (W0,b0,W_T,b_T; dW,db) amortise over T."""
     s = 2 if w["dtype"] == "bf16" else 4
+    F = w.get("F", 64)
     tok_heads = w["B"] * w["H"] * w["T"]
     streams = w["B"] * w["H"]
     ck = (F * F + F) * s / (w["K"] * CS)  # counted at the element size; this build keeps them in float32
@@ -175,7 +179,7 @@ class ClockSampler:
 def make_host_inputs(w, seed):
     from ttt_rs_b200.synthetic import make_inputs
     dt = torch.bfloat16 if w["dtype"] == "bf16" else torch.float32
-    return make_inputs(w["B"], w["H"], w["T"], F, CS, seed=seed, dtype=dt, with_grad_output=True,
+    return make_inputs(w["B"], w["H"], w["T"], w.get("F", F), CS, seed=seed, dtype=dt, with_grad_output=True,
                        inner=w.get("inner", "linear"))
 
 
@@ -578,7 +582,7 @@ def bench_inner(tb, w, host, dev, world, rank, args, name):
     import torch.distributed as dist
     from ttt_rs_b200.distributed import allreduce_outer_grads
     mlp = w.get("inner") == "mlp"
-    cfg = tb.FusedTttConfig.new(CS, F, 1e-6, 128, w["K"])
+    cfg = tb.FusedTttConfig.new(CS, w.get("F", F), 1e-6, 128, w["K"])
     if mlp:
         md = {k: host[k].to(dev) for k in MLP_IN}
         mstate = tb.TTTMLPState(md["w1"], md["b1"], md["w2"], md["b2"])
@@ -587,7 +591,8 @@ def bench_inner(tb, w, host, dev, world, rank, args, name):
     go = host["grad_output"].to(dev)
     H = host["xq"].shape[1]
     # two packed outer-gradient buffers: the all-reduce of step i overlaps the forward of step i+1
-    packed = [torch.zeros(tb.packed_outer_grad_len(H), device=dev) for _ in range(2)] if w["backward"] else None
+    packed = ([torch.zeros(tb.packed_outer_grad_len(H, w.get("F", F)), device=dev) for _ in range(2)]
+              if w["backward"] else None)
     pending = [None, None]
     ev_pairs = []
     step_no = [0]
@@ -900,7 +905,7 @@ def run_e2e(tb, w, host, dev, cfg, world, args, tokens):
     names_in = ("xq", "xk", "xv", "ttt_lr_eta") + (("grad_output",) if w["backward"] else ())
     pinned = {k: host[k].pin_memory() for k in names_in}
     params = {k: host[k].to(dev) for k in ("weight", "bias", "token_eta", "ln_weight", "ln_bias")}
-    out_host = alloc_host_outputs(w["B"], w["H"], w["T"], F, host["xq"].dtype, w["backward"])
+    out_host = alloc_host_outputs(w["B"], w["H"], w["T"], w.get("F", F), host["xq"].dtype, w["backward"])
     runner = HostBatchRunner(cfg, dev, chunks=E2E_CHUNKS, backward=w["backward"])
 
     for _ in range(2):

@@ -390,10 +390,6 @@ int ttt_linear_forward(const ttt_dims* d, const void* xq, const void* xk, const 
   p.stats = save ? reinterpret_cast<float4*>(aux + al.off_stats) : nullptr;
   p.b_stage = save ? reinterpret_cast<float*>(aux + al.off_bias) : nullptr;
   p.status = static_cast<uint32_t*>(status);
-  p.xq = xq;
-  p.xk = xk;
-  p.xv = xv;
-  p.out = output;
   p.H = pk.heads;
   p.T = d->seq_len;
   p.NS = d->seq_len / d->mini_batch;
@@ -401,7 +397,7 @@ int ttt_linear_forward(const ttt_dims* d, const void* xq, const void* xk, const 
   p.NCK = (int)num_ckpt(d);
   p.eps = d->epsilon;
   cudaError_t e =
-      ttt::launch_linear_fwd(d->dtype, pk.seg, maps, p, (int)pk.streams, static_cast<cudaStream_t>(stream));
+      ttt::launch_linear_fwd(d->dtype, pk.seg, maps, bases, p, (int)pk.streams, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(e));
   return TTT_OK;
 }
@@ -506,13 +502,6 @@ int ttt_linear_backward_state_grads(const ttt_dims* d, const void* xq, const voi
   p.handoff_polls = g_handoff_polls.load();
   p.item_base = g_item_base.load();
   p.status = static_cast<uint32_t*>(status);
-  p.xq = xq;
-  p.xk = xk;
-  p.xv = xv;
-  p.d_out = grad_output;
-  p.d_q = grad_xq;
-  p.d_k = grad_xk;
-  p.d_v = grad_xv;
   p.H = pk.heads;
   p.T = d->seq_len;
   p.NS = d->seq_len / d->mini_batch;
@@ -520,7 +509,7 @@ int ttt_linear_backward_state_grads(const ttt_dims* d, const void* xq, const voi
   p.NCK = (int)num_ckpt(d);
   p.eps = d->epsilon;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  cudaError_t e = ttt::launch_linear_bwd(d->dtype, pk.seg, maps, p, (int)pk.streams, st);
+  cudaError_t e = ttt::launch_linear_bwd(d->dtype, pk.seg, maps, bases, p, (int)pk.streams, st);
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "backward launch failed: %s", cudaGetErrorString(e));
   ttt::ReduceParams r;
   r.part_ln = p.part_ln;

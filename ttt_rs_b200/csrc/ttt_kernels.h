@@ -20,12 +20,6 @@ struct LinFwdParams {
   float4* stats;          // [B*H*T][2]: (mean1, rstd1, A, Bv), (mean2, rstd2, 0, 0) per token
   float* b_stage;         // [B*H*(NS+1), F] float32: bias at the start of every stage, final bias last
   uint32_t* status;       // device uint32[4] or null
-  // the caller's tensors behind the q, k, v, out maps; read only where tiles are gathered instead of loaded by TMA
-  // (head_dim 32 in bf16)
-  const void* xq;
-  const void* xk;
-  const void* xv;
-  void* out;
   int H, T, NS, K, NCK;
   float eps;
 };
@@ -55,14 +49,6 @@ struct LinBwdParams {
   float* part_te;   // workspace: [B*H][T] per-stream token_eta gradient terms
   float* part_w;    // workspace: [B*H][F*F + F] float32 dW, db per stream (for the packed reduction)
   uint32_t* status;
-  // the caller's tensors behind the q, k, v, d_out, d_q, d_k, d_v maps (used where tiles are gathered: head_dim 32, bf16)
-  const void* xq;
-  const void* xk;
-  const void* xv;
-  const void* d_out;
-  void* d_q;
-  void* d_k;
-  void* d_v;
   int H, T, NS, K, NCK;
   float eps;
 };
@@ -296,12 +282,14 @@ cudaError_t launch_gemm_bf16_tn(const CUtensorMap* maps, const GemmParams& p, bo
 // bf16 only.  maps: q, k, v, out.
 cudaError_t launch_mlp_fwd(const CUtensorMap* maps, const MlpFwdParams& p, int nstreams, cudaStream_t st);
 
-// dtype: 0 = float32, 1 = bfloat16.  maps: q, k, v, out, gp (saved lr-scaled LN gradient, [B*H*T, 64] of T).
-cudaError_t launch_linear_fwd(int dtype, int seg, const CUtensorMap* maps, const LinFwdParams& p, int nstreams,
-                              cudaStream_t st);
-// maps: q, k, v, d_out, d_q, d_k, d_v, gp.
-cudaError_t launch_linear_bwd(int dtype, int seg, const CUtensorMap* maps, const LinBwdParams& p, int nstreams,
-                              cudaStream_t st);
+// dtype: 0 = float32, 1 = bfloat16.  seg: features per head, 64 or 32 (two heads per tile).
+// maps: q, k, v, out, gp (saved lr-scaled LN gradient, [B*H*T, 64] of T); io: the plain pointers behind the first
+// four maps, in the same order (used by the instantiation that gathers its tiles: seg 32 in bf16).
+cudaError_t launch_linear_fwd(int dtype, int seg, const CUtensorMap* maps, const void* const* io, const LinFwdParams& p,
+                              int nstreams, cudaStream_t st);
+// maps: q, k, v, d_out, d_q, d_k, d_v, gp; io: the plain pointers behind the first seven.
+cudaError_t launch_linear_bwd(int dtype, int seg, const CUtensorMap* maps, const void* const* io, const LinBwdParams& p,
+                              int nstreams, cudaStream_t st);
 cudaError_t launch_linear_bwd_reduce(const ReduceParams& p, cudaStream_t st);
 
 }  // namespace ttt

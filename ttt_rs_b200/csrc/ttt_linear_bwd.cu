@@ -32,7 +32,7 @@
 
 namespace ttt {
 
-template <typename T>
+template <typename T, int SEG>
 struct BwdSmem {
   using TF = TileFmt<T>;
   static constexpr int NP = TF::NP;
@@ -41,10 +41,11 @@ struct BwdSmem {
   // one slot = the tiles of one stage: q, k, gp (raw + operand planes), v, d_out (raw), then small records
   static constexpr uint32_t OFF_Q = 0, OFF_K = TF::BYTES, OFF_G = 2 * TF::BYTES, OFF_V = 3 * TF::BYTES;
   static constexpr uint32_t OFF_DO = OFF_V + TF::RAW_BYTES;
-  static constexpr uint32_t OFF_STAT = OFF_DO + TF::RAW_BYTES;  // 16 tokens x 2 float4 (x 2 heads when paired)
-  static constexpr uint32_t OFF_BS = OFF_STAT + 1024;           // 64 floats: bias at the start of the stage
+  static constexpr uint32_t STAT_BYTES = (SEG == 32) ? 1024 : 512;  // 16 tokens x 2 float4 (x 2 heads when paired)
+  static constexpr uint32_t OFF_STAT = OFF_DO + TF::RAW_BYTES;
+  static constexpr uint32_t OFF_BS = OFF_STAT + STAT_BYTES;     // 64 floats: bias at the start of the stage
   static constexpr uint32_t OFF_LR = OFF_BS + 256;              // 16 x element (x 2 heads when paired)
-  static constexpr uint32_t SLOT = OFF_STAT + 2048;
+  static constexpr uint32_t SLOT = OFF_STAT + 2 * STAT_BYTES;   // (keeps every tile 1024-byte aligned)
   static constexpr uint32_t OFF_W = NSLOT * SLOT;               // W_s^T, 4 sub-tiles [16 n][64 k]
   static constexpr uint32_t OFF_DW = OFF_W + 4 * PLANES;        // dW^T, same layout
   static constexpr uint32_t OFF_DZ = OFF_DW + 4 * PLANES;       // dZbar operand tile
@@ -62,13 +63,16 @@ struct BwdSmem {
 
 template <typename T, int SEG>
 __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 : 1))
-    ttt_linear_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                          const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                          const __grid_constant__ CUtensorMap tm_dq, const __grid_constant__ CUtensorMap tm_dk,
-                          const __grid_constant__ CUtensorMap tm_dv, const __grid_constant__ CUtensorMap tm_g,
-                          const LinBwdParams p) {
+    ttt_linear_bwd_kernel(const __grid_constant__ typename PairIo<T, SEG>::Ref tm_q,
+                          const __grid_constant__ typename PairIo<T, SEG>::Ref tm_k,
+                          const __grid_constant__ typename PairIo<T, SEG>::Ref tm_v,
+                          const __grid_constant__ typename PairIo<T, SEG>::Ref tm_do,
+                          const __grid_constant__ typename PairIo<T, SEG>::Ref tm_dq,
+                          const __grid_constant__ typename PairIo<T, SEG>::Ref tm_dk,
+                          const __grid_constant__ typename PairIo<T, SEG>::Ref tm_dv,
+                          const __grid_constant__ CUtensorMap tm_g, const LinBwdParams p) {
   using TF = TileFmt<T>;
-  using SM = BwdSmem<T>;
+  using SM = BwdSmem<T, SEG>;
   constexpr int NP = TF::NP;
   constexpr uint32_t PL = TILE_BF16_BYTES;  // plane stride
   constexpr float INV_F = 1.f / SEG;        // features per head (LayerNorm row length)
@@ -93,53 +97,68 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
   __shared__ int s_item;
 
   if (tid == 0) {
-    prefetch_tmap(&tm_q);
-    prefetch_tmap(&tm_k);
-    prefetch_tmap(&tm_v);
-    prefetch_tmap(&tm_do);
+    if constexpr (!GATHER) {
+      prefetch_tmap(&tm_q);
+      prefetch_tmap(&tm_k);
+      prefetch_tmap(&tm_v);
+      prefetch_tmap(&tm_do);
+    }
     prefetch_tmap(&tm_g);
-    prefetch_tmap(&tm_dq);
-    prefetch_tmap(&tm_dk);
-    prefetch_tmap(&tm_dv);
+    if constexpr (!GATHER) {
+      prefetch_tmap(&tm_dq);
+      prefetch_tmap(&tm_dk);
+      prefetch_tmap(&tm_dv);
+    }
     // arrivals per phase: thread 0's expect_tx, plus every thread's cp.async arrival where tiles are gathered
     for (int i = 0; i < SM::NSLOT; ++i) mbar_init(bar0 + 8 * i, GATHER ? 1 + NTHREADS : 1);
     fence_mbar_init();
   }
   __syncthreads();
 
-  // everything stage s needs, into slot n % NSLOT; called by every thread, thread 0 issues the TMA / bulk copies
+  // everything stage s needs, into slot n % NSLOT (thread 0: TMA / bulk copies)
   auto issue_loads = [&](int n, int s) {
     const int slot = n % SM::NSLOT;
     const uint32_t bar = bar0 + 8 * slot;
     const uint32_t sl = base + slot * SM::SLOT;
     const int r0 = row_base + s * CS;
-    if (tid == 0) {
-      mbar_expect_tx(bar, (GATHER ? 1u : 5u) * TF::RAW_BYTES + NH * 512u + 256u + NH * CS * TF::ELT);
+    if constexpr (SEG == 64) {
+      mbar_expect_tx(bar, 5u * TF::RAW_BYTES + 512u + 256u + CS * TF::ELT);
+      tma_load_tile<T>(sl + SM::OFF_K, &tm_k, r0, bar);
+      tma_load_tile<T>(sl + SM::OFF_G, &tm_g, r0, bar);
+      tma_load_tile<T>(sl + SM::OFF_Q, &tm_q, r0, bar);
+      tma_load_tile<T>(sl + SM::OFF_V, &tm_v, r0, bar);
+      tma_load_tile<T>(sl + SM::OFF_DO, &tm_do, r0, bar);
+      bulk_load_1d(sl + SM::OFF_STAT, p.stats + (size_t)r0 * 2, 512u, bar);
+      bulk_load_1d(sl + SM::OFF_BS, p.b_stage + ((size_t)stream * (NS + 1) + s) * HD, 256u, bar);
+      bulk_load_1d(sl + SM::OFF_LR, static_cast<const uint8_t*>(p.lr) + (size_t)r0 * TF::ELT, CS * TF::ELT, bar);
+    } else {
+      mbar_expect_tx(bar, (GATHER ? 1u : 5u) * TF::RAW_BYTES + 1024u + 256u + 2 * CS * TF::ELT);
       tma_load_tile<T>(sl + SM::OFF_G, &tm_g, r0, bar);  // saved tiles are kept in the packed 64-wide form
       if constexpr (!GATHER) {
-        tma_load_x<T, SEG>(sl + SM::OFF_K, &tm_k, stream, s * CS, p.T, bar);
-        tma_load_x<T, SEG>(sl + SM::OFF_Q, &tm_q, stream, s * CS, p.T, bar);
-        tma_load_x<T, SEG>(sl + SM::OFF_V, &tm_v, stream, s * CS, p.T, bar);
-        tma_load_x<T, SEG>(sl + SM::OFF_DO, &tm_do, stream, s * CS, p.T, bar);
+        tma_load_pair<T>(sl + SM::OFF_K, &tm_k, stream, s * CS, p.T, bar);
+        tma_load_pair<T>(sl + SM::OFF_Q, &tm_q, stream, s * CS, p.T, bar);
+        tma_load_pair<T>(sl + SM::OFF_V, &tm_v, stream, s * CS, p.T, bar);
+        tma_load_pair<T>(sl + SM::OFF_DO, &tm_do, stream, s * CS, p.T, bar);
       }
-      bulk_load_1d(sl + SM::OFF_STAT, p.stats + (size_t)r0 * 2 * NH, NH * 512u, bar);
+      bulk_load_1d(sl + SM::OFF_STAT, p.stats + (size_t)r0 * 4, 1024u, bar);
       bulk_load_1d(sl + SM::OFF_BS, p.b_stage + ((size_t)stream * (NS + 1) + s) * HD, 256u, bar);
-      if constexpr (SEG == 64) {
-        bulk_load_1d(sl + SM::OFF_LR, static_cast<const uint8_t*>(p.lr) + (size_t)r0 * TF::ELT, CS * TF::ELT, bar);
-      } else {
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
-          bulk_load_1d(sl + SM::OFF_LR + j * CS * TF::ELT,
-                       static_cast<const uint8_t*>(p.lr) + ((size_t)(2 * stream + j) * p.T + s * CS) * TF::ELT,
-                       CS * TF::ELT, bar);
-      }
+      for (int j = 0; j < 2; ++j)  // ttt_lr_eta is [B, H, T]: the two heads of the pair are T elements apart
+        bulk_load_1d(sl + SM::OFF_LR + j * CS * TF::ELT,
+                     static_cast<const uint8_t*>(p.lr) + ((size_t)(2 * stream + j) * p.T + s * CS) * TF::ELT,
+                     CS * TF::ELT, bar);
     }
+  };
+  // every thread, where tiles are gathered: its 16-byte chunk of the k, q, v, d_out tiles, then its arrival
+  auto issue_gather = [&](int n, int s) {
     if constexpr (GATHER) {
-      gather_pair_tile_bf16(sl + SM::OFF_K, p.xk, stream, s * CS, p.T, tid);
-      gather_pair_tile_bf16(sl + SM::OFF_Q, p.xq, stream, s * CS, p.T, tid);
-      gather_pair_tile_bf16(sl + SM::OFF_V, p.xv, stream, s * CS, p.T, tid);
-      gather_pair_tile_bf16(sl + SM::OFF_DO, p.d_out, stream, s * CS, p.T, tid);
-      cp_async_mbar_arrive_noinc(bar);
+      const int slot = n % SM::NSLOT;
+      const uint32_t sl = base + slot * SM::SLOT;
+      gather_pair_tile_bf16(sl + SM::OFF_K, tm_k.ptr, stream, s * CS, p.T, tid);
+      gather_pair_tile_bf16(sl + SM::OFF_Q, tm_q.ptr, stream, s * CS, p.T, tid);
+      gather_pair_tile_bf16(sl + SM::OFF_V, tm_v.ptr, stream, s * CS, p.T, tid);
+      gather_pair_tile_bf16(sl + SM::OFF_DO, tm_do.ptr, stream, s * CS, p.T, tid);
+      cp_async_mbar_arrive_noinc(bar0 + 8 * slot);
     }
   };
 
@@ -184,7 +203,8 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
     row_base = stream * p.T;
     const int head = stream % p.H;
     const int s_lo = chunk * p.CH, s_hi = min(s_lo + p.CH, NS) - 1;
-    issue_loads(n, s_hi);
+    if (tid == 0) issue_loads(n, s_hi);
+    issue_gather(n, s_hi);
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
       const int c = nb + 8 * nt + 2 * t;
@@ -200,15 +220,17 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       for (int kt = 0; kt < 8; ++kt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int k = 8 * kt + 2 * t + (i & 1), nn = nb + g + 8 * (i >> 1);
-          if (p.dw_in == nullptr) {
-            dwt[kt][i] = 0.f;
-          } else if constexpr (SEG == 64) {
-            dwt[kt][i] = ld_as_float<T>(p.dw_in, (size_t)stream * HD * HD + k * HD + nn);
+          if constexpr (SEG == 64) {
+            dwt[kt][i] = (p.dw_in == nullptr)
+                             ? 0.f
+                             : ld_as_float<T>(p.dw_in, (size_t)stream * HD * HD + (8 * kt + 2 * t + (i & 1)) * HD + nb +
+                                                           g + 8 * (i >> 1));
           } else {
-            dwt[kt][i] = ((kt >> 2) == hsel) ? ld_as_float<T>(p.dw_in, (size_t)(2 * stream + hsel) * 32 * 32 +
-                                                                         (k & 31) * 32 + (nn & 31))
-                                             : 0.f;
+            // the head's own 32 x 32 block of the pair's block-diagonal dW^T; zero elsewhere
+            const int k = 8 * kt + 2 * t + (i & 1), nn = nb + g + 8 * (i >> 1);
+            dwt[kt][i] = (p.dw_in == nullptr || (kt >> 2) != hsel)
+                             ? 0.f
+                             : ld_as_float<T>(p.dw_in, (size_t)(2 * stream + hsel) * 32 * 32 + (k & 31) * 32 + (nn & 31));
           }
         }
       if (p.db_in != nullptr) {
@@ -279,7 +301,8 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       // so the other slot may be overwritten
       if (!next_issued) {
         next_issued = true;
-        if (s > s_lo) issue_loads(n + 1, s - 1);
+        if (tid == 0 && s > s_lo) issue_loads(n + 1, s - 1);
+        if (GATHER && s > s_lo) issue_gather(n + 1, s - 1);
       }
     };
     if constexpr (NP == 3) {
@@ -296,8 +319,9 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       }
       issue_next();
     }
-    const uint8_t* lrp = gsl + SM::OFF_LR + (SEG == 32 ? hsel * CS * TF::ELT : 0);
-    const float lr_row[2] = {ld_as_float<T>(lrp, g), ld_as_float<T>(lrp, g + 8)};
+    // (SEG = 32: the pair's second head has its 16 values right after the first head's)
+    const float lr_row[2] = {ld_as_float<T>(gsl + SM::OFF_LR, (SEG == 32 ? hsel * CS : 0) + g),
+                             ld_as_float<T>(gsl + SM::OFF_LR, (SEG == 32 ? hsel * CS : 0) + g + 8)};
     const float4* stat = reinterpret_cast<const float4*>(gsl + SM::OFF_STAT);
     const float* bsv = reinterpret_cast<const float*>(gsl + SM::OFF_BS);
 
@@ -364,9 +388,9 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
     float mean1[2], rstd1[2], Bv1[2], mean2[2], rstd2[2];
     F2 xh[2][2], gy[2][2], gx[2][2], G[2][2];
     {
-      const int h_ = (SEG == 32) ? hsel : 0;  // record of (token, head): index NH * token + head
-      const float4 sa0 = stat[2 * (NH * g + h_)], sb0 = stat[2 * (NH * g + h_) + 1],
-                   sa1 = stat[2 * (NH * (g + 8) + h_)], sb1 = stat[2 * (NH * (g + 8) + h_) + 1];
+      // records of rows g and g + 8 (SEG = 32: of this warp's head; record index 2 * token + head)
+      const int rg = (SEG == 32) ? 2 * g + hsel : g, rg8 = (SEG == 32) ? 2 * (g + 8) + hsel : g + 8;
+      const float4 sa0 = stat[2 * rg], sb0 = stat[2 * rg + 1], sa1 = stat[2 * rg8], sb1 = stat[2 * rg8 + 1];
       mean1[0] = sa0.x; rstd1[0] = sa0.y; mean1[1] = sa1.x; rstd1[1] = sa1.y;
       const float A[2] = {sa0.z, sa1.z};
       Bv1[0] = sa0.w; Bv1[1] = sa1.w;
@@ -554,7 +578,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       s1t[0] = o0.x * INV_F; s2t[0] = o0.y * INV_F;
       s1t[1] = o1.x * INV_F; s2t[1] = o1.y * INV_F;
       const float rt_all = col_sum(o0.w + o1.w);  // sum over the 16 rows
-      if ((warp & 1) == 0 && t == 0 && (SEG == 32 || warp == 0)) {
+      if ((SEG == 32 ? (warp & 1) == 0 : warp == 0) && t == 0) {
         // per (batch, head) stream of the caller's tensors: the pair's heads are streams 2 * stream and 2 * stream + 1
         const size_t o = (SEG == 32 ? (size_t)(2 * stream + hsel) * p.T : (size_t)row_base) + (size_t)s * CS;
         st_from_float<T>(p.d_lr, o + g, o0.z);
@@ -645,13 +669,20 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       fence_proxy_async_smem();
       __syncthreads();
       if constexpr (GATHER) {
-        scatter_pair_tile_bf16(p.d_q, stream, s * CS, p.T, so_q, tid);
-        scatter_pair_tile_bf16(p.d_k, stream, s * CS, p.T, so_k, tid);
-        scatter_pair_tile_bf16(p.d_v, stream, s * CS, p.T, so_v, tid);
+        scatter_pair_tile_bf16(tm_dq.ptr, stream, s * CS, p.T, so_q, tid);
+        scatter_pair_tile_bf16(tm_dk.ptr, stream, s * CS, p.T, so_k, tid);
+        scatter_pair_tile_bf16(tm_dv.ptr, stream, s * CS, p.T, so_v, tid);
       } else if (tid == 0) {
-        tma_store_x<T, SEG>(&tm_dq, stream, s * CS, p.T, so_q);
-        tma_store_x<T, SEG>(&tm_dk, stream, s * CS, p.T, so_k);
-        tma_store_x<T, SEG>(&tm_dv, stream, s * CS, p.T, so_v);
+        if constexpr (SEG == 64) {
+          const int r0 = row_base + s * CS;
+          tma_store_tile<T>(&tm_dq, r0, so_q);
+          tma_store_tile<T>(&tm_dk, r0, so_k);
+          tma_store_tile<T>(&tm_dv, r0, so_v);
+        } else {
+          tma_store_pair<T>(&tm_dq, stream, s * CS, p.T, so_q);
+          tma_store_pair<T>(&tm_dk, stream, s * CS, p.T, so_k);
+          tma_store_pair<T>(&tm_dv, stream, s * CS, p.T, so_v);
+        }
         bulk_commit();
       }
     }
@@ -693,13 +724,13 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       for (int kt = 0; kt < 8; ++kt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int k = 8 * kt + 2 * t + (i & 1), nn = nb + g + 8 * (i >> 1);
           if constexpr (SEG == 64) {
-            const int idx = k * HD + nn;
+            const int idx = (8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1);
             st_from_float<T>(p.d_w, wo + idx, dwt[kt][i]);
             if (p.part_w != nullptr) p.part_w[(size_t)stream * (HD * HD + HD) + idx] = dwt[kt][i];
           } else if ((kt >> 2) == hsel) {
             // the head's own 32 x 32 block, at the head's place in the caller's [B, H, 32, 32] layout
+            const int k = 8 * kt + 2 * t + (i & 1), nn = nb + g + 8 * (i >> 1);
             const size_t hs = (size_t)(2 * stream + hsel);
             const int idx = (k & 31) * 32 + (nn & 31);
             st_from_float<T>(p.d_w, hs * 32 * 32 + idx, dwt[kt][i]);
@@ -736,11 +767,13 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
 // ----------------------------------------------------------------------------------------------------
 // Block = 32 consecutive outputs x 8 warps.  Warp w sums terms w, w+8, ... of each output (coalesced 128-byte
 // reads), the eight partial sums meet in shared memory and are added in warp order: a fixed summation order.
+template <int F>
 __global__ void __launch_bounds__(256) ttt_linear_bwd_reduce_kernel(const ReduceParams p) {
   __shared__ float part[8][32];
   // H heads of F features as the caller counts them; the partials of the LayerNorm gradients are in the kernel's
   // 64-wide tiles, which hold NP = 64 / F heads side by side
-  const int H = p.H, B = p.B, T = p.T, NCH = p.NCH, F = p.F, NP = HD / F, HP = H / NP;
+  constexpr int NP = HD / F;
+  const int H = p.H, B = p.B, T = p.T, NCH = p.NCH, HP = H / NP;
   const int n_te = T, n_ln = 2 * H * F, n_w = (p.packed != nullptr) ? H * (F * F + F) : 0;
   const int total = n_te + n_ln + n_w;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -794,16 +827,18 @@ __global__ void ttt_linear_bwd_fold_kernel(const ReduceParams p) {
 }
 
 template <typename T, int SEG>
-static cudaError_t launch_bwd_t(const CUtensorMap* m, const LinBwdParams& p, int nstreams, cudaStream_t st) {
+static cudaError_t launch_bwd_t(const CUtensorMap* m, const void* const* io, const LinBwdParams& p, int nstreams,
+                                cudaStream_t st) {
+  using SM = BwdSmem<T, SEG>;
   auto kfn = ttt_linear_bwd_kernel<T, SEG>;
-  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BwdSmem<T>::DYN_BYTES);
+  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM::DYN_BYTES);
   if (e != cudaSuccess) return e;
   // persistent grid: as many blocks as can be resident at once (they wait on one another's hand-offs), never more
   // than there are work items; launched cooperatively so that co-residency is guaranteed, not assumed
   int dev = 0, sms = 0, per_sm = 0;
   if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
   if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
-  if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kfn, NTHREADS, BwdSmem<T>::DYN_BYTES)) != cudaSuccess)
+  if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kfn, NTHREADS, SM::DYN_BYTES)) != cudaSuccess)
     return e;
   if (per_sm < 1) return cudaErrorLaunchOutOfResources;
   int grid = sms * per_sm;
@@ -811,26 +846,33 @@ static cudaError_t launch_bwd_t(const CUtensorMap* m, const LinBwdParams& p, int
   if (grid > nitems) grid = nitems;
   if ((e = cudaMemsetAsync(p.sched, 0, sizeof(int) * (size_t)(1 + nstreams), st)) != cudaSuccess) return e;
   LinBwdParams pp = p;
-  void* args[] = {(void*)&m[0], (void*)&m[1], (void*)&m[2], (void*)&m[3], (void*)&m[4],
-                  (void*)&m[5], (void*)&m[6], (void*)&m[7], (void*)&pp};
-  return cudaLaunchCooperativeKernel((const void*)kfn, dim3(grid), dim3(NTHREADS), args, BwdSmem<T>::DYN_BYTES, st);
+  RawTensor raw[7];
+  void* args[9];
+  for (int i = 0; i < 7; ++i) {
+    raw[i].ptr = const_cast<void*>(io[i]);
+    args[i] = PairIo<T, SEG>::GATHER ? (void*)&raw[i] : (void*)&m[i];
+  }
+  args[7] = (void*)&m[7];
+  args[8] = (void*)&pp;
+  return cudaLaunchCooperativeKernel((const void*)kfn, dim3(grid), dim3(NTHREADS), args, SM::DYN_BYTES, st);
 }
 
-cudaError_t launch_linear_bwd(int dtype, int seg, const CUtensorMap* maps, const LinBwdParams& p, int nstreams,
-                              cudaStream_t st) {
+cudaError_t launch_linear_bwd(int dtype, int seg, const CUtensorMap* maps, const void* const* io, const LinBwdParams& p,
+                              int nstreams, cudaStream_t st) {
   if (seg == 32) {
-    if (dtype == 1) return launch_bwd_t<__nv_bfloat16, 32>(maps, p, nstreams, st);
-    return launch_bwd_t<float, 32>(maps, p, nstreams, st);
+    if (dtype == 1) return launch_bwd_t<__nv_bfloat16, 32>(maps, io, p, nstreams, st);
+    return launch_bwd_t<float, 32>(maps, io, p, nstreams, st);
   }
-  if (dtype == 1) return launch_bwd_t<__nv_bfloat16, 64>(maps, p, nstreams, st);
-  return launch_bwd_t<float, 64>(maps, p, nstreams, st);
+  if (dtype == 1) return launch_bwd_t<__nv_bfloat16, 64>(maps, io, p, nstreams, st);
+  return launch_bwd_t<float, 64>(maps, io, p, nstreams, st);
 }
 
 cudaError_t launch_linear_bwd_reduce(const ReduceParams& p, cudaStream_t st) {
   const int total = p.T + 2 * p.H * p.F + (p.packed != nullptr ? p.H * (p.F * p.F + p.F) : 0);
   int blocks = (total + 31) / 32;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  ttt_linear_bwd_reduce_kernel<<<blocks, 256, 0, st>>>(p);
+  if (p.F == 32) ttt_linear_bwd_reduce_kernel<32><<<blocks, 256, 0, st>>>(p);
+  else ttt_linear_bwd_reduce_kernel<64><<<blocks, 256, 0, st>>>(p);
   if (p.packed != nullptr) ttt_linear_bwd_fold_kernel<<<1, CS * 32, 0, st>>>(p);
   return cudaGetLastError();
 }

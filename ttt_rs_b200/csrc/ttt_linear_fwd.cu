@@ -32,13 +32,13 @@ namespace ttt {
 constexpr int FWD_NST = 3;  // TMA pipeline depth (stages in flight); the stage loop is unrolled by it
 static_assert(FWD_NST == 3, "the stage loop below is written out for three slots");
 
-template <typename T>
+template <typename T, int SEG>
 struct FwdSmem {
   using TF = TileFmt<T>;
   static constexpr uint32_t SLOT = 3 * TF::BYTES;                  // q, k, v
   static constexpr uint32_t OFF_OUT = FWD_NST * SLOT;              // staging (raw format): 2 x output, 2 x Gp
-  static constexpr uint32_t LR_SLOT = 128;                         // lr of one stage: 16 elements (x 2 heads when paired)
-  static constexpr uint32_t OFF_LR = OFF_OUT + 4 * TF::RAW_BYTES;
+  static constexpr uint32_t LR_SLOT = (SEG == 32) ? 128 : 64;      // lr of one stage: 16 elements (x 2 heads when paired)
+  static constexpr uint32_t OFF_LR = OFF_OUT + 4 * TF::RAW_BYTES;  // FWD_NST x LR_SLOT
   static constexpr uint32_t OFF_XCH = OFF_LR + FWD_NST * LR_SLOT;  // 2 x Xch4
   static constexpr uint32_t OFF_BAR = OFF_XCH + 2 * sizeof(Xch4);
   static constexpr uint32_t TOTAL = OFF_BAR + FWD_NST * 8;
@@ -47,11 +47,13 @@ struct FwdSmem {
 
 template <typename T, int SEG>
 __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
-    ttt_linear_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                          const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+    ttt_linear_fwd_kernel(const __grid_constant__ typename PairIo<T, SEG>::Ref tm_q,
+                          const __grid_constant__ typename PairIo<T, SEG>::Ref tm_k,
+                          const __grid_constant__ typename PairIo<T, SEG>::Ref tm_v,
+                          const __grid_constant__ typename PairIo<T, SEG>::Ref tm_o,
                           const __grid_constant__ CUtensorMap tm_g, const LinFwdParams p) {
   using TF = TileFmt<T>;
-  using SM = FwdSmem<T>;
+  using SM = FwdSmem<T, SEG>;
   constexpr int NP = TF::NP;
   constexpr bool TWO_PASS = (sizeof(T) == 4);
   constexpr float INV_F = 1.f / SEG;  // features per head (LayerNorm row length)
@@ -77,10 +79,12 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
   const bool save = (p.w_ckpt != nullptr);
 
   if (tid == 0) {
-    prefetch_tmap(&tm_q);
-    prefetch_tmap(&tm_k);
-    prefetch_tmap(&tm_v);
-    prefetch_tmap(&tm_o);
+    if constexpr (!GATHER) {
+      prefetch_tmap(&tm_q);
+      prefetch_tmap(&tm_k);
+      prefetch_tmap(&tm_v);
+      prefetch_tmap(&tm_o);
+    }
     prefetch_tmap(&tm_g);
     // arrivals per phase: thread 0's expect_tx, plus every thread's cp.async arrival where tiles are gathered
     for (int i = 0; i < FWD_NST; ++i) mbar_init(bar0 + 8 * i, GATHER ? 1 + NTHREADS : 1);
@@ -88,37 +92,49 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
   }
   __syncthreads();
 
-  // called by every thread; thread 0 issues the TMA / bulk copies
+  // thread 0: TMA / bulk copies of one stage into its ring slot
   auto issue_loads = [&](int s) {
     const int slot = s % FWD_NST;
     const uint32_t bar = bar0 + 8 * slot;
     const uint32_t tq = base + slot * SM::SLOT;
-    if (tid == 0) {
-      mbar_expect_tx(bar, (GATHER ? 0 : 3 * TF::RAW_BYTES) + (SEG == 32 ? 2 : 1) * CS * TF::ELT);
+    if constexpr (SEG == 64) {
+      mbar_expect_tx(bar, 3 * TF::RAW_BYTES + CS * TF::ELT);
+      const int r0 = row_base + s * CS;
+      tma_load_tile<T>(tq, &tm_q, r0, bar);
+      tma_load_tile<T>(tq + TF::BYTES, &tm_k, r0, bar);
+      tma_load_tile<T>(tq + 2 * TF::BYTES, &tm_v, r0, bar);
+      bulk_load_1d(base + SM::OFF_LR + slot * 64,
+                   static_cast<const uint8_t*>(p.lr) + (size_t)(row_base + s * CS) * TF::ELT, CS * TF::ELT, bar);
+    } else {
+      mbar_expect_tx(bar, (GATHER ? 0 : 3 * TF::RAW_BYTES) + 2 * CS * TF::ELT);
       if constexpr (!GATHER) {
-        tma_load_x<T, SEG>(tq, &tm_q, stream, s * CS, p.T, bar);
-        tma_load_x<T, SEG>(tq + TF::BYTES, &tm_k, stream, s * CS, p.T, bar);
-        tma_load_x<T, SEG>(tq + 2 * TF::BYTES, &tm_v, stream, s * CS, p.T, bar);
+        tma_load_pair<T>(tq, &tm_q, stream, s * CS, p.T, bar);
+        tma_load_pair<T>(tq + TF::BYTES, &tm_k, stream, s * CS, p.T, bar);
+        tma_load_pair<T>(tq + 2 * TF::BYTES, &tm_v, stream, s * CS, p.T, bar);
       }
-      if constexpr (SEG == 64) {
-        bulk_load_1d(base + SM::OFF_LR + slot * SM::LR_SLOT,
-                     static_cast<const uint8_t*>(p.lr) + (size_t)(row_base + s * CS) * TF::ELT, CS * TF::ELT, bar);
-      } else {
 #pragma unroll
-        for (int j = 0; j < 2; ++j)  // ttt_lr_eta is [B, H, T]: the two heads of the pair are T elements apart
-          bulk_load_1d(base + SM::OFF_LR + slot * SM::LR_SLOT + j * CS * TF::ELT,
-                       static_cast<const uint8_t*>(p.lr) + ((size_t)(2 * stream + j) * p.T + s * CS) * TF::ELT,
-                       CS * TF::ELT, bar);
-      }
-    }
-    if constexpr (GATHER) {
-      gather_pair_tile_bf16(tq, p.xq, stream, s * CS, p.T, tid);
-      gather_pair_tile_bf16(tq + TF::BYTES, p.xk, stream, s * CS, p.T, tid);
-      gather_pair_tile_bf16(tq + 2 * TF::BYTES, p.xv, stream, s * CS, p.T, tid);
-      cp_async_mbar_arrive_noinc(bar);
+      for (int j = 0; j < 2; ++j)  // ttt_lr_eta is [B, H, T]: the two heads of the pair are T elements apart
+        bulk_load_1d(base + SM::OFF_LR + slot * SM::LR_SLOT + j * CS * TF::ELT,
+                     static_cast<const uint8_t*>(p.lr) + ((size_t)(2 * stream + j) * p.T + s * CS) * TF::ELT,
+                     CS * TF::ELT, bar);
     }
   };
-  for (int s = 0; s < FWD_NST && s < NS; ++s) issue_loads(s);
+  // every thread, where tiles are gathered: its 16-byte chunk of the q, k, v tiles, then its arrival on the barrier
+  auto issue_gather = [&](int s) {
+    if constexpr (GATHER) {
+      const int slot = s % FWD_NST;
+      const uint32_t tq = base + slot * SM::SLOT;
+      gather_pair_tile_bf16(tq, tm_q.ptr, stream, s * CS, p.T, tid);
+      gather_pair_tile_bf16(tq + TF::BYTES, tm_k.ptr, stream, s * CS, p.T, tid);
+      gather_pair_tile_bf16(tq + 2 * TF::BYTES, tm_v.ptr, stream, s * CS, p.T, tid);
+      cp_async_mbar_arrive_noinc(bar0 + 8 * slot);
+    }
+  };
+  if (tid == 0) {
+    for (int s = 0; s < FWD_NST && s < NS; ++s) issue_loads(s);
+  }
+  if constexpr (GATHER)
+    for (int s = 0; s < FWD_NST && s < NS; ++s) issue_gather(s);
 
   // ---- per-thread constants: 4 owned columns c(nt,e) = nb + 8nt + 2t + e, rows g and g+8
   F2 gam[2], bet[2];
@@ -193,8 +209,10 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
       for (int j = 0; j < 4; ++j) bs[nb + 8 * (j >> 1) + 2 * t + (j & 1)] = bias[j];
     }
 
-    const uint8_t* lrp = gbase + SM::OFF_LR + slot * SM::LR_SLOT + (SEG == 32 ? hsel * CS * TF::ELT : 0);
-    const float lr_row[2] = {ld_as_float<T>(lrp, g), ld_as_float<T>(lrp, g + 8)};
+    // (SEG = 32: the pair's second head has its 16 values right after the first head's)
+    const float lr_row[2] = {
+        ld_as_float<T>(gbase + SM::OFF_LR + slot * SM::LR_SLOT, (SEG == 32 ? hsel * CS : 0) + g),
+        ld_as_float<T>(gbase + SM::OFF_LR + slot * SM::LR_SLOT, (SEG == 32 ? hsel * CS : 0) + g + 8)};
 
     // ---- Z1 = K W + b, Zq = Q W + b (columns nb..nb+15), Attn = Q K^T (full 16x16, every warp)
     float z1[2][4], zq[2][4], at[2][4];
@@ -327,15 +345,21 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     F2 zb[2][2];
     slab_pairs(zq, zb);
     ln_row_stats<TWO_PASS, SEG>(zb, xch, xsel, L, p.eps, mean, rstd, fl2);
-    if (save && (L.warp & 1) == 0 && t == 0 && (SEG == 32 || L.warp == 0)) {
-      // two float4 per token (and per head of the pair: record index 2 * token + head)
-      constexpr int NH = (SEG == 32) ? 2 : 1;
-      float4* sp = p.stats + ((size_t)row_base + (size_t)s * CS) * 2 * NH;
-      const int h = (SEG == 32) ? hsel : 0;
-      sp[2 * (NH * g + h)] = st1[0];
-      sp[2 * (NH * g + h) + 1] = make_float4(mean[0], rstd[0], 0.f, 0.f);
-      sp[2 * (NH * (g + 8) + h)] = st1[1];
-      sp[2 * (NH * (g + 8) + h) + 1] = make_float4(mean[1], rstd[1], 0.f, 0.f);
+    if constexpr (SEG == 64) {
+      if (save && L.warp == 0 && t == 0) {
+        float4* sp = p.stats + ((size_t)row_base + (size_t)s * CS) * 2;
+        sp[2 * g] = st1[0];
+        sp[2 * g + 1] = make_float4(mean[0], rstd[0], 0.f, 0.f);
+        sp[2 * (g + 8)] = st1[1];
+        sp[2 * (g + 8) + 1] = make_float4(mean[1], rstd[1], 0.f, 0.f);
+      }
+    } else if (save && (L.warp & 1) == 0 && t == 0) {
+      // two float4 per (token, head): record index 2 * token + head of the pair
+      float4* sp = p.stats + ((size_t)row_base + (size_t)s * CS) * 4;
+      sp[2 * (2 * g + hsel)] = st1[0];
+      sp[2 * (2 * g + hsel) + 1] = make_float4(mean[0], rstd[0], 0.f, 0.f);
+      sp[2 * (2 * (g + 8) + hsel)] = st1[1];
+      sp[2 * (2 * (g + 8) + hsel) + 1] = make_float4(mean[1], rstd[1], 0.f, 0.f);
     }
     const uint32_t so = base + SM::OFF_OUT + (s & 1) * TF::RAW_BYTES;
 #pragma unroll
@@ -349,14 +373,17 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
       }
     fence_proxy_async_smem();
     __syncthreads();
-    if constexpr (GATHER) scatter_pair_tile_bf16(p.out, stream, s * CS, p.T, so, tid);
+    if constexpr (GATHER) scatter_pair_tile_bf16(tm_o.ptr, stream, s * CS, p.T, so, tid);
     if (tid == 0) {
-      if constexpr (!GATHER) tma_store_x<T, SEG>(&tm_o, stream, s * CS, p.T, so);
+      if constexpr (SEG == 64) tma_store_tile<T>(&tm_o, row_base + s * CS, so);
+      else if constexpr (!GATHER) tma_store_pair<T>(&tm_o, stream, s * CS, p.T, so);
       if (save) tma_store_tile<T>(&tm_g, row_base + s * CS, sg);  // saved tiles are kept in the packed 64-wide form
       bulk_commit();
       bulk_wait_read<1>();
+      if (s + FWD_NST < NS) issue_loads(s + FWD_NST);
     }
-    if (s + FWD_NST < NS) issue_loads(s + FWD_NST);
+    if constexpr (GATHER)
+      if (s + FWD_NST < NS) issue_gather(s + FWD_NST);
     return true;
   };
   for (int s0 = 0; s0 < NS; s0 += FWD_NST) {
@@ -372,12 +399,13 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     for (int kt = 0; kt < 8; ++kt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int k = 8 * kt + 2 * t + (i & 1), n = nb + g + 8 * (i >> 1);
-        const int idx = k * HD + n;
+        const int idx = (8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1);
         if constexpr (SEG == 64) {
           st_from_float<T>(p.w_out, (size_t)stream * HD * HD + idx, wt[kt][i] * wscale);
         } else if ((kt >> 2) == hsel) {
-          st_from_float<T>(p.w_out, (size_t)(2 * stream + hsel) * 32 * 32 + (k & 31) * 32 + (n & 31), wt[kt][i] * wscale);
+          // the head's own 32 x 32 block (rows and columns 32 hsel .. of the tile's state)
+          st_from_float<T>(p.w_out, (size_t)(2 * stream + hsel) * 32 * 32 + ((idx >> 6) & 31) * 32 + (idx & 31),
+                           wt[kt][i] * wscale);
         }
         if (save) wc[idx] = wt[kt][i] * wscale;
       }
@@ -395,22 +423,30 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
 }
 
 template <typename T, int SEG>
-static cudaError_t launch_fwd_t(const CUtensorMap* m, const LinFwdParams& p, int nstreams, cudaStream_t st) {
+static cudaError_t launch_fwd_t(const CUtensorMap* m, const void* const* io, const LinFwdParams& p, int nstreams,
+                                cudaStream_t st) {
+  using SM = FwdSmem<T, SEG>;
   auto kfn = ttt_linear_fwd_kernel<T, SEG>;
-  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FwdSmem<T>::DYN_BYTES);
+  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM::DYN_BYTES);
   if (e != cudaSuccess) return e;
-  kfn<<<nstreams, NTHREADS, FwdSmem<T>::DYN_BYTES, st>>>(m[0], m[1], m[2], m[3], m[4], p);
+  if constexpr (PairIo<T, SEG>::GATHER) {
+    kfn<<<nstreams, NTHREADS, SM::DYN_BYTES, st>>>(RawTensor{const_cast<void*>(io[0])}, RawTensor{const_cast<void*>(io[1])},
+                                                   RawTensor{const_cast<void*>(io[2])},
+                                                   RawTensor{const_cast<void*>(io[3])}, m[4], p);
+  } else {
+    kfn<<<nstreams, NTHREADS, SM::DYN_BYTES, st>>>(m[0], m[1], m[2], m[3], m[4], p);
+  }
   return cudaGetLastError();
 }
 
-cudaError_t launch_linear_fwd(int dtype, int seg, const CUtensorMap* maps, const LinFwdParams& p, int nstreams,
-                              cudaStream_t st) {
+cudaError_t launch_linear_fwd(int dtype, int seg, const CUtensorMap* maps, const void* const* io, const LinFwdParams& p,
+                              int nstreams, cudaStream_t st) {
   if (seg == 32) {
-    if (dtype == 1) return launch_fwd_t<__nv_bfloat16, 32>(maps, p, nstreams, st);
-    return launch_fwd_t<float, 32>(maps, p, nstreams, st);
+    if (dtype == 1) return launch_fwd_t<__nv_bfloat16, 32>(maps, io, p, nstreams, st);
+    return launch_fwd_t<float, 32>(maps, io, p, nstreams, st);
   }
-  if (dtype == 1) return launch_fwd_t<__nv_bfloat16, 64>(maps, p, nstreams, st);
-  return launch_fwd_t<float, 64>(maps, p, nstreams, st);
+  if (dtype == 1) return launch_fwd_t<__nv_bfloat16, 64>(maps, io, p, nstreams, st);
+  return launch_fwd_t<float, 64>(maps, io, p, nstreams, st);
 }
 
 }  // namespace ttt

@@ -6,6 +6,8 @@
 // three bf16 planes (see Pk<3>) that ldmatrix reads, while element-wise code reads the raw floats.
 #pragma once
 
+#include <type_traits>
+
 #include "ttt_common.cuh"
 
 namespace ttt {
@@ -124,9 +126,15 @@ __device__ __forceinline__ void tma_store_tile(const CUtensorMap* tm, int row0, 
 // whole 128-byte row of shared memory, so TMA cannot put the two halves side by side.  The tile is gathered instead:
 // 128 chunks of 16 bytes, one cp.async per thread, written at the swizzled position TMA would have used; results leave
 // the same way (ld.shared + st.global per thread).
+// How a kernel is handed one of the caller's [B,H,T,F] tensors: a TMA descriptor, or a plain pointer where the tiles
+// are gathered (the kernel's parameter list is unchanged for every other instantiation).
+struct alignas(64) RawTensor {
+  void* ptr;
+};
 template <typename T, int SEG>
 struct PairIo {
   static constexpr bool GATHER = (SEG == 32 && sizeof(T) == 2);
+  using Ref = std::conditional_t<GATHER, RawTensor, CUtensorMap>;
 };
 __device__ __forceinline__ void gather_pair_tile_bf16(uint32_t tile, const void* base, int pair, int t0, int seq, int tid) {
   const int row = tid >> 3, c = tid & 7;  // chunk c of the 128-byte row: head c >> 2, features 8 (c & 3) ..
@@ -143,27 +151,18 @@ __device__ __forceinline__ void scatter_pair_tile_bf16(void* base, int pair, int
   uint8_t* dst = static_cast<uint8_t*>(base) + (((size_t)(2 * pair + (c >> 2)) * seq + t0 + row) * 32 + (c & 3) * 8) * 2;
   *reinterpret_cast<uint4*>(dst) = v;
 }
-// TMA side.  SEG = 64: one head per tile, `stream` * seq + t0 is the tile's first row of the [B*H*seq, 64] view.
-// SEG = 32, float32: two boxes of the [B*H*seq, 32] view.  (SEG = 32, bf16 does not come here: PairIo::GATHER.)
-template <typename T, int SEG>
-__device__ __forceinline__ void tma_load_x(uint32_t tile, const CUtensorMap* tm, int stream, int t0, int seq, uint32_t bar) {
-  static_assert(!PairIo<T, SEG>::GATHER, "bf16 pair tiles are gathered, not loaded by TMA");
-  if constexpr (SEG == 64) {
-    tma_load_tile<T>(tile, tm, stream * seq + t0, bar);
-  } else {
-    tma_load_2d(tile, tm, 0, (2 * stream) * seq + t0, bar);
-    tma_load_2d(tile + 2048, tm, 0, (2 * stream + 1) * seq + t0, bar);
-  }
+// float32 pair tile by TMA: two boxes of the [B*H*seq, 32] view, one per head.
+template <typename T>
+__device__ __forceinline__ void tma_load_pair(uint32_t tile, const CUtensorMap* tm, int pair, int t0, int seq, uint32_t bar) {
+  static_assert(sizeof(T) == 4, "bf16 pair tiles are gathered, not loaded by TMA");
+  tma_load_2d(tile, tm, 0, (2 * pair) * seq + t0, bar);
+  tma_load_2d(tile + 2048, tm, 0, (2 * pair + 1) * seq + t0, bar);
 }
-template <typename T, int SEG>
-__device__ __forceinline__ void tma_store_x(const CUtensorMap* tm, int stream, int t0, int seq, uint32_t tile) {
-  static_assert(!PairIo<T, SEG>::GATHER, "bf16 pair tiles are scattered, not stored by TMA");
-  if constexpr (SEG == 64) {
-    tma_store_tile<T>(tm, stream * seq + t0, tile);
-  } else {
-    tma_store_2d(tm, 0, (2 * stream) * seq + t0, tile);
-    tma_store_2d(tm, 0, (2 * stream + 1) * seq + t0, tile + 2048);
-  }
+template <typename T>
+__device__ __forceinline__ void tma_store_pair(const CUtensorMap* tm, int pair, int t0, int seq, uint32_t tile) {
+  static_assert(sizeof(T) == 4, "bf16 pair tiles are scattered, not stored by TMA");
+  tma_store_2d(tm, 0, (2 * pair) * seq + t0, tile);
+  tma_store_2d(tm, 0, (2 * pair + 1) * seq + t0, tile + 2048);
 }
 
 }  // namespace ttt
