@@ -210,6 +210,7 @@ int ttt_mlp_backward(const ttt_dims* d, const void* xq, const void* xk, const vo
  *   d->seq_len = r, 1 <= r <= 16 (d->mini_batch and d->checkpoint_interval are not read); tensors as in
  *   ttt_linear_forward with T = r; token_eta holds the r coefficients of these positions.  Forward only: nothing is
  *   saved for a backward.  weight_out / bias_out may alias weight / bias (state advanced in place).
+ *   head_dim 64 or 32 (here any number of heads: this kernel works head by head).
  */
 int ttt_linear_forward_partial(const ttt_dims* d, const void* xq, const void* xk, const void* xv, const void* weight,
                                const void* bias, const void* token_eta, const void* ttt_lr_eta,

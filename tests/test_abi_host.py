@@ -134,10 +134,10 @@ def test_cpp_host_mirror_compiles(tmp_path):
 def test_partial_and_layer_entry_points_validate_their_arguments(lib):
     """Argument checks of the entry points around the main path; all fail before anything touches the device."""
     fake = C.c_void_p(0x1000)
-    # partial mini-batch: 1..16 tokens, head_dim 64
+    # partial mini-batch: 1..16 tokens, head_dim 64 or 32
     for seq, code in ((0, _lib.TTT_ERR_SHAPE), (17, _lib.TTT_ERR_SHAPE)):
         assert lib.ttt_linear_forward_partial(C.byref(_dims(seq_len=seq)), *([fake] * 12), None) == code
-    assert lib.ttt_linear_forward_partial(C.byref(_dims(seq_len=3, head_dim=32)), *([fake] * 12), None) == \
+    assert lib.ttt_linear_forward_partial(C.byref(_dims(seq_len=3, head_dim=48)), *([fake] * 12), None) == \
         _lib.TTT_ERR_UNSUPPORTED
     args = [fake] * 12
     args[9] = None

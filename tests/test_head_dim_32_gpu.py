@@ -110,6 +110,53 @@ def test_backward_with_final_state_gradients():
         assert_close(getattr(grads, name), ref["grad_" + name], 1e-4, f"grad_{name} (state grads, head_dim 32)")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("r", (1, 5, 16))
+def test_partial_mini_batch(dtype, r):
+    """Decode step / sequence tail (`ttt_linear_forward_partial`) at head_dim 32: one mini-batch of r tokens."""
+    import ttt_rs_b200 as tb
+    dev = torch.device("cuda:0")
+    t = _case(2, 3, 1, 60 + r, dtype)  # the partial kernel works head by head: odd head counts are fine
+    for k in ("xq", "xk", "xv"):
+        t[k] = t[k][:, :, :r].contiguous()
+    t["ttt_lr_eta"] = t["ttt_lr_eta"][:, :, :r].contiguous()
+    t["token_eta"] = t["token_eta"][:r].contiguous()
+    cfg = tb.FusedTttConfig.new(16, F, 1e-6, 128, 1)
+    outs = tb.TttTileMultiKernel.forward_partial(tb.TttInputs(*[t[k].to(dev) for k in LIN_IN]), cfg)
+    torch.cuda.synchronize()
+    want = O.ttt_linear_forward(*[t[k].double() for k in LIN_IN], mini_batch=r, eps=1e-6)
+    assert_close(outs.output, want["output"], RTOL[dtype], "partial output (head_dim 32)")
+    assert_close(outs.weight, want["weight"], RTOL[dtype], "partial weight (head_dim 32)")
+    assert_close(outs.bias, want["bias"], RTOL[dtype], "partial bias (head_dim 32)")
+
+
+def test_inner_model_interface_with_ragged_tail():
+    """`FusedTileMultiTTTLinear.forward` over 2 full mini-batches + a 7-token tail, 4 heads of 32."""
+    import ttt_rs_b200 as tb
+    dev = torch.device("cuda:0")
+    dtype = torch.float32
+    B, H, T = 2, 4, 39
+    t = _case(B, H, 3, 17, dtype)
+    for k in ("xq", "xk", "xv"):
+        t[k] = t[k][:, :, :T].contiguous()
+    t["ttt_lr_eta"] = t["ttt_lr_eta"][:, :, :T].contiguous()
+    t["token_eta"] = (1.0 / (torch.arange(T) % 16 + 1)).to(dtype)
+    inner = tb.TTTLinear(H, F, 16, 1e-6, 1, device=dev, dtype=dtype)
+    with torch.no_grad():
+        inner.ln_weight.copy_(t["ln_weight"]); inner.ln_bias.copy_(t["ln_bias"])
+    m = tb.FusedTileMultiTTTLinear(inner, allow_partial=True)
+    state = tb.TTTLinearState(t["weight"].to(dev), t["bias"].to(dev))
+    ins = tb.TTTInputsInner(tb.Qkv(t["xq"].to(dev), t["xk"].to(dev), t["xv"].to(dev)), t["token_eta"].to(dev),
+                            t["ttt_lr_eta"].to(dev))
+    with torch.no_grad():
+        out = m.forward(state, ins)
+    torch.cuda.synchronize()
+    want = O.ttt_linear_forward_any_length(*[t[k].double() for k in LIN_IN], mini_batch=16)
+    assert out.shape == (B, H, T, F)
+    assert_close(out, want["output"], 1e-4, "ragged output (head_dim 32)")
+    assert_close(state.weight, want["weight"], 1e-4, "ragged final weight (head_dim 32)")
+
+
 def test_odd_head_count_is_rejected():
     import ttt_rs_b200 as tb
     t = _case(1, 3, 2, 3, torch.bfloat16)

@@ -25,17 +25,17 @@ def _ptr(t):
     return None if t is None else C.c_void_p(t.data_ptr())
 
 
-def _backward_both_ways(seed, B, H, NS, K, dtype):
+def _backward_both_ways(seed, B, H, NS, K, dtype, F=64):
     import ttt_rs_b200 as tb
     from ttt_rs_b200 import _lib
     lib = _lib.load()
     dev = torch.device("cuda:0")
-    t = O.make_inputs(B, H, NS * 16, 64, 16, seed=seed, dtype=dtype)
-    cfg = tb.FusedTttConfig.new(16, 64, 1e-6, 128, K)
+    t = O.make_inputs(B, H, NS * 16, F, 16, seed=seed, dtype=dtype)
+    cfg = tb.FusedTttConfig.new(16, F, 1e-6, 128, K)
     ins = tb.TttInputs(*[t[k].to(dev) for k in LIN_IN])
     _, saved = tb.TttTileMultiKernel.forward_launch(ins, cfg)
     go = t["grad_output"].to(dev)
-    T, F = NS * 16, 64
+    T = NS * 16
     d = _lib.TttDims(B, H, T, F, 16, K, float(cfg.epsilon()), _lib.TTT_BF16 if dtype == torch.bfloat16 else _lib.TTT_F32)
     stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
 
@@ -44,7 +44,7 @@ def _backward_both_ways(seed, B, H, NS, K, dtype):
             xq=torch.empty_like(saved.xq), xk=torch.empty_like(saved.xq), xv=torch.empty_like(saved.xq),
             w=torch.empty_like(saved.weight_init), b=torch.empty_like(saved.bias), lr=torch.empty_like(saved.ttt_lr_eta),
             te=torch.empty(T, device=dev), lnw=torch.empty(H, F, device=dev), lnb=torch.empty(H, F, device=dev),
-            packed=torch.empty(tb.packed_outer_grad_len(H), device=dev))
+            packed=torch.empty(tb.packed_outer_grad_len(H, F), device=dev))
 
     common = [_ptr(saved.xq), _ptr(saved.xk), _ptr(saved.xv), _ptr(saved.weight_init), _ptr(saved.bias),
               _ptr(saved.token_eta), _ptr(saved.ttt_lr_eta), _ptr(saved.ln_weight), _ptr(saved.ln_bias),
@@ -67,10 +67,10 @@ def _backward_both_ways(seed, B, H, NS, K, dtype):
 @pytest.mark.gpu
 def test_noalloc_backward_matches_workspace_backward_twice_in_a_row():
     rtol = {torch.bfloat16: 2e-2, torch.float32: 1e-4}
-    # two calls back to back, different sizes and data; then a third in float32
-    for seed, (B, H, NS, K), dtype in ((1, (3, 2, 8, 4), torch.bfloat16), (2, (2, 4, 20, 16), torch.bfloat16),
-                                       (3, (1, 2, 5, 2), torch.float32)):
-        got, ref = _backward_both_ways(seed, B, H, NS, K, dtype)
+    # two calls back to back, different sizes and data; then a third in float32; then head_dim 32 (pairs of heads)
+    for seed, (B, H, NS, K), dtype, F in ((1, (3, 2, 8, 4), torch.bfloat16, 64), (2, (2, 4, 20, 16), torch.bfloat16, 64),
+                                          (3, (1, 2, 5, 2), torch.float32, 64), (4, (2, 4, 6, 4), torch.bfloat16, 32)):
+        got, ref = _backward_both_ways(seed, B, H, NS, K, dtype, F)
         for k in ref:
             assert_close(got[k], ref[k].double(), rtol[dtype], f"seed {seed}: {k}")
             # the kernels are deterministic, so the two entry points agree to the bit

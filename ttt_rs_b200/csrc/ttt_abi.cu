@@ -626,7 +626,7 @@ extern "C" int ttt_linear_backward_noalloc(const ttt_dims* d, const void* xq, co
                                            void* grad_bias, void* grad_ttt_lr_eta, float* grad_token_eta,
                                            float* grad_ln_weight, float* grad_ln_bias, float* outer_grad_packed,
                                            void* status, void* stream) {
-  int rc = check_dims(d);
+  int rc = check_dims(d, true);
   if (rc != TTT_OK) return rc;
   const size_t need = ws_layout(d).total_bytes;
   if (need > (size_t)TTT_NOALLOC_SCRATCH_BYTES)
@@ -752,7 +752,8 @@ extern "C" int ttt_linear_forward_partial(const ttt_dims* d, const void* xq, con
   if (d == nullptr) return fail(TTT_ERR_NULL, "dims is null");
   if (d->batch <= 0 || d->heads <= 0) return fail(TTT_ERR_SHAPE, "batch and heads must be positive");
   if (d->dtype != TTT_F32 && d->dtype != TTT_BF16) return fail(TTT_ERR_UNSUPPORTED, "unknown dtype %d", d->dtype);
-  if (d->head_dim != 64) return fail(TTT_ERR_UNSUPPORTED, "Unsupported head_dim=%d (supported: 64)", d->head_dim);
+  if (d->head_dim != 64 && d->head_dim != 32)
+    return fail(TTT_ERR_UNSUPPORTED, "Unsupported head_dim=%d (supported: 64, 32)", d->head_dim);
   if (d->seq_len < 1 || d->seq_len > 16)
     return fail(TTT_ERR_SHAPE, "a partial mini-batch has 1..16 tokens (got seq_len=%d)", d->seq_len);
   if (!(d->epsilon >= 0.f)) return fail(TTT_ERR_SHAPE, "epsilon must be >= 0");
@@ -778,7 +779,7 @@ extern "C" int ttt_linear_forward_partial(const ttt_dims* d, const void* xq, con
   p.H = d->heads;
   p.R = d->seq_len;
   p.eps = d->epsilon;
-  cudaError_t e = ttt::launch_linear_partial(d->dtype, p, d->batch * d->heads, static_cast<cudaStream_t>(stream));
+  cudaError_t e = ttt::launch_linear_partial(d->dtype, d->head_dim, p, d->batch * d->heads, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "partial forward launch failed: %s", cudaGetErrorString(e));
   return TTT_OK;
 }

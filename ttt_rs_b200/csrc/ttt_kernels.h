@@ -207,7 +207,7 @@ struct LinPartialParams {
   int H, R;
   float eps;
 };
-cudaError_t launch_linear_partial(int dtype, const LinPartialParams& p, int nstreams, cudaStream_t st);
+cudaError_t launch_linear_partial(int dtype, int head_dim, const LinPartialParams& p, int nstreams, cudaStream_t st);
 
 // TTT-MLP backward (ttt_mlp_bwd.cu), bf16 I/O.
 struct MlpBwdParams {

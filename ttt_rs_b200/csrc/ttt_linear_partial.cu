@@ -7,26 +7,25 @@
 // r = 1 (rust/layer/src/ttt.rs:253-256).  The reference's fused kernels refuse these shapes
 // (rust/fused/src/linear_fused_tile/wrapper.rs:152-172); only its unfused tensor-op path covers them.
 //
-// Work per stream is tiny (r <= 16 rows against a 64x64 state), so this is a CUDA-core kernel: one 64-thread CTA per
-// (batch, head) stream, thread n owns column n of W (64 float registers) and column n of every 16x64 tile; the
-// stream's state is read and written exactly once (the HBM traffic that bounds a decode step).
+// Work per stream is tiny (r <= 16 rows against an F x F state, F = 64 or 32), so this is a CUDA-core kernel: one
+// F-thread CTA per (batch, head) stream, thread n owns column n of W (F float registers) and column n of every 16 x F
+// tile; the stream's state is read and written exactly once (the HBM traffic that bounds a decode step).
 #include "ttt_kernels.h"
 #include "ttt_common.cuh"
 
 namespace ttt {
 
-constexpr int PT_THREADS = 64;
-
+template <int FD>
 struct PartialSmem {
-  float q[CS][HD], k[CS][HD], v[CS][HD];
+  float q[CS][FD], k[CS][FD], v[CS][FD];
   float attn[CS][CS];
   float lr[CS], te[CS];
   float red[2][CS][2];  // cross-warp partial sums
 };
 
-// Sums over the 64 columns (threads) of two values per row, for rows < r.  Every thread gets the totals.
-template <int RM>
-__device__ __forceinline__ void row_sums(PartialSmem& sm, int r, int tid, float (&a)[RM], float (&b)[RM]) {
+// Sums over the F columns (threads) of two values per row, for rows < r.  Every thread gets the totals.
+template <int RM, int FD>
+__device__ __forceinline__ void row_sums(PartialSmem<FD>& sm, int r, int tid, float (&a)[RM], float (&b)[RM]) {
   const int warp = tid >> 5, lane = tid & 31;
 #pragma unroll
   for (int i = 0; i < RM; ++i) {
@@ -46,8 +45,8 @@ __device__ __forceinline__ void row_sums(PartialSmem& sm, int r, int tid, float 
 #pragma unroll
   for (int i = 0; i < RM; ++i) {
     if (i < r) {
-      a[i] = sm.red[0][i][0] + sm.red[1][i][0];
-      b[i] = sm.red[0][i][1] + sm.red[1][i][1];
+      a[i] = (FD == 64) ? sm.red[0][i][0] + sm.red[1][i][0] : sm.red[0][i][0];
+      b[i] = (FD == 64) ? sm.red[0][i][1] + sm.red[1][i][1] : sm.red[0][i][1];
     }
   }
   __syncthreads();  // red may be reused
@@ -55,9 +54,11 @@ __device__ __forceinline__ void row_sums(PartialSmem& sm, int r, int tid, float 
 
 // RM: compile-time bound on the number of rows (1 for the decode step, 4, or 16), so that short mini-batches do not
 // pay for sixteen rows of predicated-off arithmetic.
-template <typename T, int RM>
-__global__ void __launch_bounds__(PT_THREADS) ttt_linear_partial_kernel(const LinPartialParams p) {
-  __shared__ PartialSmem sm;
+template <typename T, int RM, int FD>
+__global__ void __launch_bounds__(FD) ttt_linear_partial_kernel(const LinPartialParams p) {
+  constexpr int HD = FD;  // features per head in this instantiation (shadows the 64 of the tiled kernels)
+  constexpr int PT_THREADS = FD;
+  __shared__ PartialSmem<FD> sm;
   const int n = threadIdx.x;
   const int stream = blockIdx.x, head = stream % p.H, r = p.R;
   const size_t row0 = (size_t)stream * r;
@@ -112,7 +113,7 @@ __global__ void __launch_bounds__(PT_THREADS) ttt_linear_partial_kernel(const Li
     a[i] = z1[i];
     b2[i] = 0.f;
   }
-  row_sums<RM>(sm, r, n, a, b2);
+  row_sums<RM, FD>(sm, r, n, a, b2);
 #pragma unroll
   for (int i = 0; i < RM; ++i) {
     mean[i] = a[i] * (1.f / HD);
@@ -120,7 +121,7 @@ __global__ void __launch_bounds__(PT_THREADS) ttt_linear_partial_kernel(const Li
     a[i] = d * d;
     b2[i] = 0.f;
   }
-  row_sums<RM>(sm, r, n, a, b2);
+  row_sums<RM, FD>(sm, r, n, a, b2);
   float xh[RM], gx[RM], g[RM];
 #pragma unroll
   for (int i = 0; i < RM; ++i) {
@@ -131,7 +132,7 @@ __global__ void __launch_bounds__(PT_THREADS) ttt_linear_partial_kernel(const Li
     a[i] = gx[i];
     b2[i] = gx[i] * xh[i];
   }
-  row_sums<RM>(sm, r, n, a, b2);
+  row_sums<RM, FD>(sm, r, n, a, b2);
 #pragma unroll
   for (int i = 0; i < RM; ++i)
     g[i] = (i < r) ? (gx[i] - a[i] * (1.f / HD) - xh[i] * b2[i] * (1.f / HD)) * rstd[i] : 0.f;
@@ -149,7 +150,7 @@ __global__ void __launch_bounds__(PT_THREADS) ttt_linear_partial_kernel(const Li
     a[i] = zq[i];
     b2[i] = 0.f;
   }
-  row_sums<RM>(sm, r, n, a, b2);
+  row_sums<RM, FD>(sm, r, n, a, b2);
 #pragma unroll
   for (int i = 0; i < RM; ++i) {
     mean[i] = a[i] * (1.f / HD);
@@ -157,7 +158,7 @@ __global__ void __launch_bounds__(PT_THREADS) ttt_linear_partial_kernel(const Li
     a[i] = d * d;
     b2[i] = 0.f;
   }
-  row_sums<RM>(sm, r, n, a, b2);
+  row_sums<RM, FD>(sm, r, n, a, b2);
 #pragma unroll
   for (int i = 0; i < RM; ++i) {
     if (i < r) {
@@ -184,21 +185,23 @@ __global__ void __launch_bounds__(PT_THREADS) ttt_linear_partial_kernel(const Li
   st_from_float<T>(p.b_out, (size_t)stream * HD + n, bias);
 }
 
-cudaError_t launch_linear_partial(int dtype, const LinPartialParams& p, int nstreams, cudaStream_t st) {
-  if (dtype == 1) {
-    if (p.R == 1)
-      ttt_linear_partial_kernel<__nv_bfloat16, 1><<<nstreams, PT_THREADS, 0, st>>>(p);
-    else if (p.R <= 4)
-      ttt_linear_partial_kernel<__nv_bfloat16, 4><<<nstreams, PT_THREADS, 0, st>>>(p);
-    else
-      ttt_linear_partial_kernel<__nv_bfloat16, 16><<<nstreams, PT_THREADS, 0, st>>>(p);
+template <typename T, int FD>
+static void launch_partial_t(const LinPartialParams& p, int nstreams, cudaStream_t st) {
+  if (p.R == 1)
+    ttt_linear_partial_kernel<T, 1, FD><<<nstreams, FD, 0, st>>>(p);
+  else if (p.R <= 4)
+    ttt_linear_partial_kernel<T, 4, FD><<<nstreams, FD, 0, st>>>(p);
+  else
+    ttt_linear_partial_kernel<T, 16, FD><<<nstreams, FD, 0, st>>>(p);
+}
+
+cudaError_t launch_linear_partial(int dtype, int head_dim, const LinPartialParams& p, int nstreams, cudaStream_t st) {
+  if (head_dim == 32) {
+    if (dtype == 1) launch_partial_t<__nv_bfloat16, 32>(p, nstreams, st);
+    else launch_partial_t<float, 32>(p, nstreams, st);
   } else {
-    if (p.R == 1)
-      ttt_linear_partial_kernel<float, 1><<<nstreams, PT_THREADS, 0, st>>>(p);
-    else if (p.R <= 4)
-      ttt_linear_partial_kernel<float, 4><<<nstreams, PT_THREADS, 0, st>>>(p);
-    else
-      ttt_linear_partial_kernel<float, 16><<<nstreams, PT_THREADS, 0, st>>>(p);
+    if (dtype == 1) launch_partial_t<__nv_bfloat16, 64>(p, nstreams, st);
+    else launch_partial_t<float, 64>(p, nstreams, st);
   }
   return cudaGetLastError();
 }
