@@ -60,14 +60,14 @@ int make_tile_map(CUtensorMap* m, const void* base, int64_t rows, int dtype) {
   return TTT_OK;
 }
 
-// 2-D bf16 view [rows, cols] with a row pitch of `ld` elements, box = 64 columns x 128 rows, 128-byte swizzle
-// (operand and result tiles of the projection GEMM).
-int make_gemm_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld) {
+// 2-D bf16 view [rows, cols] with a row pitch of `ld` elements, box = 64 columns x `box_rows` rows (128: A operand
+// and result tiles of the projection GEMM; 256: its B operand), 128-byte swizzle.
+int make_gemm_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows = 128) {
   EncodeFn enc = get_encode_fn();
   if (enc == nullptr) return fail(TTT_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
   const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)(ld * 2)};
-  const cuuint32_t box[2] = {64, 128};
+  const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -252,7 +252,7 @@ int ttt_gemm_bf16_tn(int64_t m, int64_t n, int64_t k, const void* a, int64_t lda
   if (rc != TTT_OK) return rc;
   CUtensorMap maps[7];
   if ((rc = make_gemm_map(&maps[0], a, m, k, lda)) != TTT_OK) return rc;
-  if ((rc = make_gemm_map(&maps[1], b, n, k, ldb)) != TTT_OK) return rc;
+  if ((rc = make_gemm_map(&maps[1], b, n, k, ldb, 256)) != TTT_OK) return rc;
   if ((rc = make_gemm_map(&maps[2], c, m, n, ldc)) != TTT_OK) return rc;
   for (int i = 3; i < 7; ++i) maps[i] = maps[2];
   ttt::GemmParams p{};
@@ -302,7 +302,7 @@ int ttt_layer_projections(const ttt_dims* d, const void* x, int64_t x_ld, int64_
   if (rows >= ((int64_t)1 << 31) || M >= ((int64_t)1 << 31)) return fail(TTT_ERR_SHAPE, "batch*heads*seq_len must be below 2^31");
   CUtensorMap maps[7];
   if ((rc = make_gemm_map(&maps[0], x, M, hidden, x_ld)) != TTT_OK) return rc;
-  if ((rc = make_gemm_map(&maps[1], weights, w_rows, hidden, w_ld)) != TTT_OK) return rc;
+  if ((rc = make_gemm_map(&maps[1], weights, w_rows, hidden, w_ld, 256)) != TTT_OK) return rc;
   if ((rc = make_gemm_map(&maps[3], xq, rows, 64, 64)) != TTT_OK) return rc;
   if ((rc = make_gemm_map(&maps[4], xk, rows, 64, 64)) != TTT_OK) return rc;
   if ((rc = make_gemm_map(&maps[5], xv, rows, 64, 64)) != TTT_OK) return rc;

@@ -4,27 +4,32 @@
 // This is the product behind the reference layer's `Linear` projections q/k/v/g, the per-head learning-rate weights
 // and o_proj (rust/layer/src/ttt.rs:152-227,289-299), which it gets from Burn's matmul.
 //
-// Persistent CTAs (one per SM) walk the 128 x 128 tiles of C, n fastest (the CTAs running at one time share a few
-// row blocks of A through L2; B stays L2-resident):
-//   * warp 0 (one lane) is the TMA producer: A and B tiles of 128 rows x 64 k (128-byte rows, 128-byte swizzle) into
-//     a ring of GEMM_STAGES shared-memory stages that never drains between tiles, completion counted in bytes on the
-//     stage's `full` mbarrier;
-//   * warp 1 (one lane) issues tcgen05.mma (cta_group::1, kind::f16, M = 128, N = 128, K = 16): operands by
-//     shared-memory descriptor, accumulators in tensor memory -- TWO buffers of 128 lanes x 128 float32 columns, used
-//     alternately; after the four k-steps of a stage a tcgen05.commit on the stage's `empty` mbarrier hands the stage
-//     back to the producer, and after a tile's last stage a commit on `acc_full[buffer]` releases the epilogue;
+// Persistent CTAs (one per SM) walk the 128 x 256 tiles of C, n fastest (the CTAs running at one time share a few
+// row blocks of A through L2; B stays L2-resident).  The tile is 256 wide because a tcgen05.mma reads both operands
+// from shared memory for every instruction: at M = 128, N = 128, K = 16 that is 8 KB per 64 tensor-pipe cycles, the
+// whole 128 bytes per cycle of an SM's shared memory, which the TMA fill of the next stages needs as well -- such
+// tiles measured 39-47 % tensor-pipe activity whatever the pipeline depth; at N = 256 the same bytes of A serve twice
+// the columns (12 KB per 128 cycles).
+//   * warp 0 (one lane) is the TMA producer: an A tile of 128 rows x 64 k and a B tile of 256 rows x 64 k (128-byte
+//     rows, 128-byte swizzle) per stage into a ring of shared-memory stages that never drains between tiles,
+//     completion counted in bytes on the stage's `full` mbarrier;
+//   * warp 1 (one lane) issues tcgen05.mma (cta_group::1, kind::f16, M = 128, N = 256 -- less in the last tile column,
+//     any multiple of 16 -- K = 16): operands by shared-memory descriptor, accumulators in tensor memory -- TWO buffers
+//     of 128 lanes x 256 float32 columns (all 512 columns of the SM), used alternately; after the four k-steps of a
+//     stage a tcgen05.commit on the stage's `empty` mbarrier hands the stage back to the producer, and after a tile's
+//     last stage a commit on `acc_full[buffer]` releases the epilogue;
 //   * warps 2-5 are the epilogue: each reads its quarter of the tensor-memory lanes (one row per thread) with
-//     tcgen05.ld, converts to bf16, writes a swizzled staging tile and one thread stores it with TMA (rows / columns
-//     beyond M / N are clipped by the tensor map); `acc_empty[buffer]` then gives the accumulator back.  So the
-//     epilogue of tile i runs under the main loop of tile i + 1.
+//     tcgen05.ld, 64 columns at a time, converts to bf16, writes a swizzled staging tile (two, used alternately) and
+//     one thread stores it with TMA (rows / columns beyond M / N are clipped by the tensor map); after the last read
+//     `acc_empty[buffer]` gives the accumulator back.  So the epilogue of tile i runs under the main loop of tile i + 1.
 // Every CTA is on its own: no thread-block cluster, each CTA loads its own operands.
 //
 // Fused form (ttt_layer_projections): the same main loop over the layer's stacked q | k | v | (g) | lr weights, with
 // the step that follows the projections in the layer folded into the epilogue -- what `get_qkv` / `get_lr` do with the
-// projection output (rust/layer/src/ttt.rs:152-227): every 64-column half of a tile is one head of q, k, v or the
-// gate, or the block of learning-rate logits.  q and k halves are rotated (rotary pairs are adjacent columns, so a
-// pair sits in one thread's registers, still in float32) and stored as XQ / XK [B,H,T,F]; v halves go to XV, gate
-// halves to a [B*T, H*F] buffer, logits become ttt_lr_eta[b,h,t] = base_lr / F * sigmoid(logit + bias).  The
+// projection output (rust/layer/src/ttt.rs:152-227): every 64-column quarter of a tile is one head of q, k, v or the
+// gate, or the block of learning-rate logits.  q and k quarters are rotated (rotary pairs are adjacent columns, so a
+// pair sits in one thread's registers, still in float32) and stored as XQ / XK [B,H,T,F]; v quarters go to XV, gate
+// quarters to a [B*T, H*F] buffer, logits become ttt_lr_eta[b,h,t] = base_lr / F * sigmoid(logit + bias).  The
 // [B*T, N] projection output is never written.  Needs seq_len % 128 == 0 (a tile's 128 tokens then belong to one
 // batch element and land in 128 consecutive rows of [B*H*T, F]).
 //
@@ -35,21 +40,25 @@
 
 namespace ttt {
 
-constexpr int GEMM_BM = 128, GEMM_BN = 128, GEMM_BK = 64, GEMM_STAGES = 5;
-constexpr uint32_t GEMM_TILE_BYTES = GEMM_BM * GEMM_BK * 2;  // 16 KB: one operand tile of a stage
+constexpr int GEMM_BM = 128, GEMM_BN = 256, GEMM_BK = 64;
+constexpr uint32_t GEMM_A_BYTES = GEMM_BM * GEMM_BK * 2;  // 16 KB: the A tile of a stage
+constexpr uint32_t GEMM_B_BYTES = GEMM_BN * GEMM_BK * 2;  // 32 KB: the B tile of a stage
+constexpr uint32_t GEMM_STAGE_BYTES = GEMM_A_BYTES + GEMM_B_BYTES;
+constexpr uint32_t GEMM_STG_BYTES = GEMM_BM * 64 * 2;     // 16 KB: one [128][64] bf16 staging tile of the epilogue
 constexpr int GEMM_THREADS = 192;
 
+template <bool FUSED>
 struct GemmSmem {
-  static constexpr uint32_t OFF_A = 0;
-  static constexpr uint32_t OFF_B = GEMM_STAGES * GEMM_TILE_BYTES;
-  static constexpr uint32_t OFF_STG = 2 * GEMM_STAGES * GEMM_TILE_BYTES;  // epilogue staging: two [128][64] bf16 tiles
-  static constexpr uint32_t OFF_BAR = OFF_STG + 2 * GEMM_TILE_BYTES;      // full[S], empty[S], acc_full[2], acc_empty[2]
-  static constexpr uint32_t OFF_TMEM = OFF_BAR + (2 * GEMM_STAGES + 4) * 8;
+  // the fused form keeps a rotary table in shared memory and gives up one stage for it
+  static constexpr int STAGES = FUSED ? 3 : 4;
+  static constexpr uint32_t OFF_STG = STAGES * GEMM_STAGE_BYTES;    // epilogue staging: two [128][64] bf16 tiles
+  static constexpr uint32_t OFF_BAR = OFF_STG + 2 * GEMM_STG_BYTES; // full[S], empty[S], acc_full[2], acc_empty[2]
+  static constexpr uint32_t OFF_TMEM = OFF_BAR + (2 * STAGES + 4) * 8;
   // fused epilogue: (cos, sin) for 16 positions x 32 pairs; rows padded to 33 entries so that the 16 rows the lanes
   // of a warp read (consecutive tokens = consecutive positions) fall in distinct banks
   static constexpr uint32_t OFF_ROPE = OFF_TMEM + 8;
   static constexpr uint32_t ROPE_ROW = 33;
-  static constexpr uint32_t TOTAL = OFF_ROPE + 16 * ROPE_ROW * 8;
+  static constexpr uint32_t TOTAL = OFF_ROPE + (FUSED ? 16 * ROPE_ROW * 8 : 0);
   static constexpr uint32_t DYN_BYTES = TOTAL + 1024;
 };
 
@@ -61,7 +70,7 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
 }
 // instruction descriptor, kind::f16: D float32 (bit 4), A and B bf16 (bits 7, 10), both K-major, N >> 3 at bit 17,
 // M >> 4 at bit 24
-__host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {  // N: a multiple of 16, 16..256, at M = 128
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
@@ -103,7 +112,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                             const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_o0,
                             const __grid_constant__ CUtensorMap tm_o1, const __grid_constant__ CUtensorMap tm_o2,
                             const __grid_constant__ CUtensorMap tm_o3, const GemmParams p) {
-  using SM = GemmSmem;
+  using SM = GemmSmem<FUSED>;
+  constexpr int GEMM_STAGES = SM::STAGES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_u32 = smem_u32(smem_raw);
   const uint32_t base = (raw_u32 + 1023u) & ~1023u;
@@ -133,8 +143,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     fence_mbar_init();
     s_fail = 0;
   }
-  if (warp == 1) {  // tensor memory: two accumulators of 128 float32 columns (the same warp frees them at the end)
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(base + SM::OFF_TMEM)
+  if (warp == 1) {  // tensor memory: two accumulators of 256 float32 columns (the same warp frees them at the end)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(base + SM::OFF_TMEM)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -158,9 +168,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             ok = false;
             break;
           }
-          mbar_expect_tx(bar_full + 8 * st, 2 * GEMM_TILE_BYTES);
-          tma_load_2d(base + SM::OFF_A + st * GEMM_TILE_BYTES, &tm_a, kb * GEMM_BK, m0, bar_full + 8 * st);
-          tma_load_2d(base + SM::OFF_B + st * GEMM_TILE_BYTES, &tm_b, kb * GEMM_BK, n0, bar_full + 8 * st);
+          mbar_expect_tx(bar_full + 8 * st, GEMM_STAGE_BYTES);  // (rows beyond M / N arrive as zeros and count)
+          tma_load_2d(base + st * GEMM_STAGE_BYTES, &tm_a, kb * GEMM_BK, m0, bar_full + 8 * st);
+          tma_load_2d(base + st * GEMM_STAGE_BYTES + GEMM_A_BYTES, &tm_b, kb * GEMM_BK, n0, bar_full + 8 * st);
         }
         if (!ok) break;
       }
@@ -168,10 +178,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   } else if (warp == 1) {
     // ---------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(GEMM_BM, GEMM_BN);
       uint32_t it = 0, tl = 0;  // k-blocks consumed, tiles started
       for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tl) {
         const uint32_t buf = tl & 1;
+        // columns this tile really has, rounded up to the instruction's granule (the last tile column is narrower)
+        const int n_left = p.N - (tile % tiles_n) * GEMM_BN;
+        const uint32_t idesc = umma_idesc_bf16(GEMM_BM, n_left >= GEMM_BN ? GEMM_BN : ((n_left + 15) & ~15));
         bool ok = true;
         // the epilogue must have drained this accumulator (its previous use was two tiles ago)
         if (tl >= 2 && !mbar_wait_bounded(bar_acc_empty + 8 * buf, ((tl >> 1) - 1) & 1)) {
@@ -189,7 +201,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             break;
           }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_addr = base + SM::OFF_A + st * GEMM_TILE_BYTES, b_addr = base + SM::OFF_B + st * GEMM_TILE_BYTES;
+          const uint32_t a_addr = base + st * GEMM_STAGE_BYTES, b_addr = a_addr + GEMM_A_BYTES;
 #pragma unroll
           for (int ks = 0; ks < GEMM_BK / 16; ++ks)  // 32 bytes per k-step inside the swizzled 128-byte rows
             umma_bf16(tmem + buf * GEMM_BN, umma_desc_sw128(a_addr + 32 * ks), umma_desc_sw128(b_addr + 32 * ks), idesc,
@@ -221,25 +233,29 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tl) {
       const int m0 = (tile / tiles_n) * GEMM_BM, n0 = (tile % tiles_n) * GEMM_BN;
       const uint32_t buf = tl & 1;
-      // fused: what each 64-column half of this tile is (0 q, 1 k, 2 v, 3 gate, 4 learning-rate logits, -1 nothing)
-      int kind[2] = {-1, -1}, head[2] = {0, 0};
+      // fused: what each 64-column group of this tile is (0 q, 1 k, 2 v, 3 gate, 4 learning-rate logits, -1 nothing)
+      // (packed into two words, 8 bits per group, so that the group loop can index them without a local array)
+      uint32_t kind_w = 0, head_w = 0;
       int pos = 0, tok = 0, bat = 0;
       if (FUSED) {
         const int C = p.f.H * 64;
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          const int col0 = n0 + 64 * hf;
+        for (int j = 0; j < 4; ++j) {
+          const int col0 = n0 + 64 * j;
+          int kd = -1, hd = 0;
           if (col0 >= p.f.q_col && col0 < p.f.q_col + C) {
-            kind[hf] = 0; head[hf] = (col0 - p.f.q_col) >> 6;
+            kd = 0; hd = (col0 - p.f.q_col) >> 6;
           } else if (col0 >= p.f.k_col && col0 < p.f.k_col + C) {
-            kind[hf] = 1; head[hf] = (col0 - p.f.k_col) >> 6;
+            kd = 1; hd = (col0 - p.f.k_col) >> 6;
           } else if (col0 >= p.f.v_col && col0 < p.f.v_col + C) {
-            kind[hf] = 2; head[hf] = (col0 - p.f.v_col) >> 6;
+            kd = 2; hd = (col0 - p.f.v_col) >> 6;
           } else if (p.f.g_col >= 0 && col0 >= p.f.g_col && col0 < p.f.g_col + C) {
-            kind[hf] = 3; head[hf] = (col0 - p.f.g_col) >> 6;
+            kd = 3; hd = (col0 - p.f.g_col) >> 6;
           } else if (col0 == p.f.lr_col) {
-            kind[hf] = 4;
+            kd = 4;
           }
+          kind_w |= (uint32_t)(kd + 1) << (8 * j);
+          head_w |= (uint32_t)hd << (8 * j);
         }
         tok = (m0 + row) % p.f.T;
         bat = (m0 + row) / p.f.T;
@@ -251,8 +267,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         if (lane == 0) report_timeout(p.status, 33, tl);
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // the previous tile's stores must have read the staging tiles before they are overwritten
-      if (warp == 2 && lane == 0) bulk_wait_read<0>();
       {
         // barrier of the four epilogue warps that also agrees on failure: every thread leaves with the same verdict
         const uint32_t mine = (!ok || s_fail != 0) ? 1u : 0u;
@@ -264,80 +278,81 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             : "memory");
         ok = (any == 0);
       }
-      if (ok) {
+      const int t0 = FUSED ? m0 % p.f.T : 0, b0 = FUSED ? m0 / p.f.T : 0;
+#pragma unroll 1
+      for (int j = 0; j < 4; ++j) {  // 64 columns at a time through one of the two staging tiles
+        const int kd = (int)((kind_w >> (8 * j)) & 0xff) - 1, hd = (int)((head_w >> (8 * j)) & 0xff);
+        const bool live = ok && n0 + 64 * j < p.N && (!FUSED || kd >= 0);
+        const uint32_t stg = base + SM::OFF_STG + (j & 1) * GEMM_STG_BYTES;
+        // the store issued two groups ago must have read this staging tile before it is overwritten
+        if (warp == 2 && lane == 0) bulk_wait_read<1>();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (live) {
 #pragma unroll
-        for (int c = 0; c < GEMM_BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tmem + ((uint32_t)(32 * q) << 16) + buf * GEMM_BN + 32 * c, r);
-          if (FUSED) {
-            const int kd = kind[c >> 1];
-            if (kd < 0) continue;
-            if (kd == 4) {
-              // learning-rate logits: column j of this half is head j
+          for (int hc = 0; hc < 2; ++hc) {
+            const int c = 2 * j + hc;  // 32-column slice of the accumulator
+            uint32_t r[32];
+            tmem_ld32(tmem + ((uint32_t)(32 * q) << 16) + buf * GEMM_BN + 32 * c, r);
+            if (FUSED) {
+              if (kd == 4) {
+                // learning-rate logits: column i of this group is head i
 #pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                const int h = 32 * (c & 1) + i;
-                if (h < p.f.H) {
-                  float z = __uint_as_float(r[i]);
-                  if (p.f.lr_bias != nullptr) z += __bfloat162float(static_cast<const __nv_bfloat16*>(p.f.lr_bias)[h]);
-                  static_cast<__nv_bfloat16*>(p.f.lr_out)[((size_t)bat * p.f.H + h) * p.f.T + tok] =
-                      __float2bfloat16_rn(p.f.base_lr * (1.f / 64.f) / (1.f + expf(-z)));
+                for (int i = 0; i < 32; ++i) {
+                  const int h = 32 * hc + i;
+                  if (h < p.f.H) {
+                    float z = __uint_as_float(r[i]);
+                    if (p.f.lr_bias != nullptr) z += __bfloat162float(static_cast<const __nv_bfloat16*>(p.f.lr_bias)[h]);
+                    static_cast<__nv_bfloat16*>(p.f.lr_out)[((size_t)bat * p.f.H + h) * p.f.T + tok] =
+                        __float2bfloat16_rn(p.f.base_lr * (1.f / 64.f) / (1.f + expf(-z)));
+                  }
+                }
+                continue;
+              }
+              if (kd <= 1 && p.f.rope_mode == 1) {
+                const float2* cs = rope_tab + pos * SM::ROPE_ROW + 16 * hc;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  // (x0, x1) -> (x0 c - x1 s, x1 c + x0 s) as two packed float32x2 operations
+                  const F2 x = f2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                  const float2 w = cs[i];
+                  const F2 y = f2fma(f2(-x.y, x.x), f2(w.y), f2mul(x, f2(w.x)));
+                  r[2 * i] = __float_as_uint(y.x);
+                  r[2 * i + 1] = __float_as_uint(y.y);
                 }
               }
-              continue;
             }
-            if (kd <= 1 && p.f.rope_mode == 1) {
-              const float2* cs = rope_tab + pos * SM::ROPE_ROW + 16 * (c & 1);
+            // staging: [128 rows][64 columns] bf16 in the swizzled layout the TMA store expects
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                // (x0, x1) -> (x0 c - x1 s, x1 c + x0 s) as two packed float32x2 operations
-                const F2 x = f2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-                const float2 w = cs[j];
-                const F2 y = f2fma(f2(-x.y, x.x), f2(w.y), f2mul(x, f2(w.x)));
-                r[2 * j] = __float_as_uint(y.x);
-                r[2 * j + 1] = __float_as_uint(y.y);
-              }
+            for (int i = 0; i < 4; ++i) {
+              const int chunk = hc * 4 + i;  // 16-byte chunk of the 128-byte row
+              const uint32_t v0 = pack_bf16(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+              const uint32_t v1 = pack_bf16(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+              const uint32_t v2 = pack_bf16(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+              const uint32_t v3 = pack_bf16(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+              asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(stg + row * 128 + ((chunk ^ (row & 7)) << 4)),
+                           "r"(v0), "r"(v1), "r"(v2), "r"(v3)
+                           : "memory");
             }
           }
-          // staging: two [128 rows][64 columns] bf16 tiles in the swizzled layout the TMA store expects
-          const uint32_t stg = base + SM::OFF_STG + (c >> 1) * GEMM_TILE_BYTES;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int chunk = (c & 1) * 4 + i;  // 16-byte chunk of the 128-byte row
-            const uint32_t v0 = pack_bf16(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
-            const uint32_t v1 = pack_bf16(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
-            const uint32_t v2 = pack_bf16(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
-            const uint32_t v3 = pack_bf16(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
-            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(stg + row * 128 + ((chunk ^ (row & 7)) << 4)),
-                         "r"(v0), "r"(v1), "r"(v2), "r"(v3)
-                         : "memory");
-          }
+          fence_proxy_async_smem();
         }
-        fence_proxy_async_smem();
-      }
-      // every tcgen05.ld of this accumulator has completed (wait::ld above): hand it back, then store the tile
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (warp == 2 && lane == 0) {
-        mbar_arrive(bar_acc_empty + 8 * buf);
-        if (ok) {
-          const uint32_t s0 = base + SM::OFF_STG, s1 = s0 + GEMM_TILE_BYTES;
-          if (FUSED) {
-            const int t0 = m0 % p.f.T, b0 = m0 / p.f.T;
-#pragma unroll
-            for (int hf = 0; hf < 2; ++hf) {
-              const uint32_t src = hf ? s1 : s0;
-              const int y = (b0 * p.f.H + head[hf]) * p.f.T + t0;  // first of 128 consecutive rows of [B*H*T, 64]
-              if (kind[hf] == 0) tma_store_2d(&tm_o0, 0, y, src);
-              if (kind[hf] == 1) tma_store_2d(&tm_o1, 0, y, src);
-              if (kind[hf] == 2) tma_store_2d(&tm_o2, 0, y, src);
-              if (kind[hf] == 3) tma_store_2d(&tm_o3, 64 * head[hf], m0, src);
+        if (j == 3) asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          // after the last group every tcgen05.ld of this accumulator has completed (wait::ld): hand it back
+          if (j == 3) mbar_arrive(bar_acc_empty + 8 * buf);
+          if (live && !(FUSED && kd == 4)) {
+            if (FUSED) {
+              const int y = (b0 * p.f.H + hd) * p.f.T + t0;  // first of 128 consecutive rows of [B*H*T, 64]
+              if (kd == 0) tma_store_2d(&tm_o0, 0, y, stg);
+              if (kd == 1) tma_store_2d(&tm_o1, 0, y, stg);
+              if (kd == 2) tma_store_2d(&tm_o2, 0, y, stg);
+              if (kd == 3) tma_store_2d(&tm_o3, 64 * hd, m0, stg);
+            } else {
+              tma_store_2d(&tm_c, n0 + 64 * j, m0, stg);
             }
-          } else {
-            tma_store_2d(&tm_c, n0, m0, s0);
-            if (n0 + 64 < p.N) tma_store_2d(&tm_c, n0 + 64, m0, s1);
           }
-          bulk_commit();
+          bulk_commit();  // (an empty group when nothing was stored: keeps the two-buffer count in step)
         }
       }
       if (!ok) break;
@@ -346,20 +361,20 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem) : "memory");
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
 }
 
 template <bool FUSED>
 static cudaError_t launch_gemm_t(const CUtensorMap* m, const GemmParams& p, cudaStream_t st) {
   auto kfn = ttt_gemm_bf16_tn_kernel<FUSED>;
-  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmSmem::DYN_BYTES);
+  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmSmem<FUSED>::DYN_BYTES);
   if (e != cudaSuccess) return e;
   int dev = 0, sms = 0;
   if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
   if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
   const long ntiles = (long)((p.N + GEMM_BN - 1) / GEMM_BN) * ((p.M + GEMM_BM - 1) / GEMM_BM);
   const int grid = (int)(ntiles < sms ? ntiles : sms);  // persistent: one CTA per SM walks the tiles
-  kfn<<<grid, GEMM_THREADS, GemmSmem::DYN_BYTES, st>>>(m[0], m[1], m[2], m[3], m[4], m[5], m[6], p);
+  kfn<<<grid, GEMM_THREADS, GemmSmem<FUSED>::DYN_BYTES, st>>>(m[0], m[1], m[2], m[3], m[4], m[5], m[6], p);
   return cudaGetLastError();
 }
 
