@@ -17,6 +17,9 @@ pytestmark = pytest.mark.gpu
     (1000, 2320, 768),   # ragged M; the layer's fused projection width at 12 heads
     (300, 72, 104),      # ragged everything: K tail zero-filled by the tensor map, N < 128
     (4096, 768, 768),    # o_proj at the 125M layer shape
+    (640, 520, 256),     # CTA-pair form (M >= 512) with an odd number of 128-row blocks: the second CTA of the last
+                         # pair has no rows; last tile column 8 wide
+    (1152, 288, 64),     # pair form, one k-block, last tile column 32 wide (16 columns from each CTA of the pair)
 ])
 def test_gemm_matches_float64_product(M, N, K):
     import ttt_rs_b200 as tb
@@ -71,7 +74,7 @@ def test_fused_projections_match_gemm_then_prologue_and_the_restatement(use_gate
     import ttt_rs_b200 as tb
     from oracle import ttt_layer_oracle as LO
     dev = torch.device("cuda:0")
-    B, T, H = 2, 256, 3
+    B, T, H = (5, 128, 3) if start else (2, 256, 3)  # 5 x 128 rows: the pair form with an odd number of row blocks
     Cc = H * 64
     g = torch.Generator().manual_seed(9)
     x = (torch.randn(B, T, Cc, generator=g) * 0.5).to(torch.bfloat16)

@@ -4,6 +4,7 @@
 #include <cstdio>
 #include <atomic>
 #include <cstring>
+#include <cstdlib>
 #include <mutex>
 
 #include "../../include/ttt_b200.h"
@@ -119,6 +120,17 @@ int make_io_map(CUtensorMap* m, const void* base, const ttt_dims* d) {
   const Packing k = packing(d);
   if (k.seg == 64) return make_tile_map(m, base, k.rows, d->dtype);
   return make_pair_map(m, base, k.streams, d->seq_len, d->dtype);
+}
+
+// Which form of the projection GEMM runs: CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles) when the product has at
+// least two such rows of tiles, single CTAs (128 x 256 tiles) below that (decode steps, short prefills).
+// TTT_GEMM_PAIR=0 / 1 in the environment forces one form (measurements, tests).
+bool gemm_pair_form(int64_t m) {
+  static const int forced = [] {
+    const char* e = std::getenv("TTT_GEMM_PAIR");
+    return (e != nullptr && e[0] != '\0') ? (e[0] != '0' ? 1 : 0) : -1;
+  }();
+  return forced >= 0 ? forced != 0 : m >= 512;
 }
 
 int check_dims(const ttt_dims* d, bool allow_head_dim_32 = false) {
@@ -252,7 +264,8 @@ int ttt_gemm_bf16_tn(int64_t m, int64_t n, int64_t k, const void* a, int64_t lda
   if (rc != TTT_OK) return rc;
   CUtensorMap maps[7];
   if ((rc = make_gemm_map(&maps[0], a, m, k, lda)) != TTT_OK) return rc;
-  if ((rc = make_gemm_map(&maps[1], b, n, k, ldb, 256)) != TTT_OK) return rc;
+  const bool pair = gemm_pair_form(m);
+  if ((rc = make_gemm_map(&maps[1], b, n, k, ldb, pair ? 128 : 256)) != TTT_OK) return rc;
   if ((rc = make_gemm_map(&maps[2], c, m, n, ldc)) != TTT_OK) return rc;
   for (int i = 3; i < 7; ++i) maps[i] = maps[2];
   ttt::GemmParams p{};
@@ -260,7 +273,7 @@ int ttt_gemm_bf16_tn(int64_t m, int64_t n, int64_t k, const void* a, int64_t lda
   p.N = (int)n;
   p.K = (int)k;
   p.status = static_cast<uint32_t*>(status);
-  cudaError_t e = ttt::launch_gemm_bf16_tn(maps, p, false, static_cast<cudaStream_t>(stream));
+  cudaError_t e = ttt::launch_gemm_bf16_tn(maps, p, false, pair, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "GEMM launch failed: %s", cudaGetErrorString(e));
   return TTT_OK;
 }
@@ -302,7 +315,8 @@ int ttt_layer_projections(const ttt_dims* d, const void* x, int64_t x_ld, int64_
   if (rows >= ((int64_t)1 << 31) || M >= ((int64_t)1 << 31)) return fail(TTT_ERR_SHAPE, "batch*heads*seq_len must be below 2^31");
   CUtensorMap maps[7];
   if ((rc = make_gemm_map(&maps[0], x, M, hidden, x_ld)) != TTT_OK) return rc;
-  if ((rc = make_gemm_map(&maps[1], weights, w_rows, hidden, w_ld, 256)) != TTT_OK) return rc;
+  const bool pair = gemm_pair_form(M);
+  if ((rc = make_gemm_map(&maps[1], weights, w_rows, hidden, w_ld, pair ? 128 : 256)) != TTT_OK) return rc;
   if ((rc = make_gemm_map(&maps[3], xq, rows, 64, 64)) != TTT_OK) return rc;
   if ((rc = make_gemm_map(&maps[4], xk, rows, 64, 64)) != TTT_OK) return rc;
   if ((rc = make_gemm_map(&maps[5], xv, rows, 64, 64)) != TTT_OK) return rc;
@@ -322,7 +336,7 @@ int ttt_layer_projections(const ttt_dims* d, const void* x, int64_t x_ld, int64_
   p.f.start_idx = start_idx; p.f.pos_mod = rope_mode == 1 ? d->mini_batch : 1; p.f.rope_mode = rope_mode;
   p.f.rope_theta = rope_mode == 1 ? rope_theta : 1.f; p.f.base_lr = base_lr;
   p.f.lr_bias = lr_bias; p.f.lr_out = ttt_lr_eta;
-  cudaError_t e = ttt::launch_gemm_bf16_tn(maps, p, true, static_cast<cudaStream_t>(stream));
+  cudaError_t e = ttt::launch_gemm_bf16_tn(maps, p, true, pair, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "fused projection launch failed: %s", cudaGetErrorString(e));
   return TTT_OK;
 }

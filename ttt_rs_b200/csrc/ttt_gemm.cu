@@ -22,7 +22,19 @@
 //     tcgen05.ld, 64 columns at a time, converts to bf16, writes a swizzled staging tile (two, used alternately) and
 //     one thread stores it with TMA (rows / columns beyond M / N are clipped by the tensor map); after the last read
 //     `acc_empty[buffer]` gives the accumulator back.  So the epilogue of tile i runs under the main loop of tile i + 1.
-// Every CTA is on its own: no thread-block cluster, each CTA loads its own operands.
+// In this form every CTA is on its own: no thread-block cluster, each CTA loads its own operands.
+//
+// Pair form (PAIR = true; tcgen05 cta_group::2): two CTAs of a cluster, on neighbouring SMs, share one 256 x 256 tile.
+// CTA r of the pair loads rows [128 r, 128 r + 128) of the A tile and rows [128 r, ...) of the B tile into its own
+// shared memory only (TMA loads whose bytes are counted on the LEADER's `full` barrier, cta_group::2 form:
+// half the B bytes per CTA and per FLOP of the single form, and what a tcgen05.mma reads per cycle drops from 96 to 64
+// bytes per SM); the CTA of rank 0 issues tcgen05.mma.cta_group::2 (M = 256: 128 rows in each CTA's tensor memory;
+// N = 256: 128 rows of B from each CTA's shared memory at the same offset) once the stage is full in both CTAs, and
+// commits every hand-back twice, to its own barrier and to the peer's (mapa address).  Each CTA's epilogue drains its own 128 accumulator rows; the leader
+// reuses an accumulator when both epilogues have arrived on its `acc_empty` (count 2, the peer's arrival remote).
+// Before leaving, each producer waits for the last hand-backs of its stages and the leader for the last accumulator
+// releases, so that no remote arrival can land in the shared memory of a CTA that has exited; a cluster barrier then
+// precedes the release of tensor memory.
 //
 // Fused form (ttt_layer_projections): the same main loop over the layer's stacked q | k | v | (g) | lr weights, with
 // the step that follows the projections in the layer folded into the epilogue -- what `get_qkv` / `get_lr` do with the
@@ -35,6 +47,9 @@
 //
 // Every mbarrier wait is bounded: on expiry the role sets a flag, everybody falls through to the common exit, tensor
 // memory is freed and the status words get {TTT_ERR_TIMEOUT, where, block, k-block}.
+#include <cstdio>
+#include <cstdlib>
+
 #include "ttt_kernels.h"
 #include "ttt_stage.cuh"
 
@@ -47,13 +62,18 @@ constexpr uint32_t GEMM_STAGE_BYTES = GEMM_A_BYTES + GEMM_B_BYTES;
 constexpr uint32_t GEMM_STG_BYTES = GEMM_BM * 64 * 2;     // 16 KB: one [128][64] bf16 staging tile of the epilogue
 constexpr int GEMM_THREADS = 192;
 
-template <bool FUSED>
+template <bool FUSED, bool PAIR>
 struct GemmSmem {
-  // the fused form keeps a rotary table in shared memory and gives up one stage for it
-  static constexpr int STAGES = FUSED ? 3 : 4;
-  static constexpr uint32_t OFF_STG = STAGES * GEMM_STAGE_BYTES;    // epilogue staging: two [128][64] bf16 tiles
-  static constexpr uint32_t OFF_BAR = OFF_STG + 2 * GEMM_STG_BYTES; // full[S], empty[S], acc_full[2], acc_empty[2]
-  static constexpr uint32_t OFF_TMEM = OFF_BAR + (2 * STAGES + 4) * 8;
+  // a stage: the A tile, then this CTA's rows of the B tile (all 256, or 128 of them in the pair form); the fused
+  // form keeps a rotary table in shared memory and gives up one stage for it
+  static constexpr uint32_t B_BYTES = PAIR ? GEMM_B_BYTES / 2 : GEMM_B_BYTES;
+  static constexpr uint32_t STAGE_BYTES = GEMM_A_BYTES + B_BYTES;
+  static constexpr int STAGES = PAIR ? (FUSED ? 5 : 6) : (FUSED ? 3 : 4);
+  static constexpr uint32_t OFF_STG = STAGES * STAGE_BYTES;         // epilogue staging: two [128][64] bf16 tiles
+  // full[S], empty[S], acc_full[2], acc_empty[2]
+  static constexpr uint32_t OFF_BAR = OFF_STG + 2 * GEMM_STG_BYTES;
+  static constexpr int NBAR = 2 * STAGES + 4;
+  static constexpr uint32_t OFF_TMEM = OFF_BAR + NBAR * 8;
   // fused epilogue: (cos, sin) for 16 positions x 32 pairs; rows padded to 33 entries so that the 16 rows the lanes
   // of a warp read (consecutive tokens = consecutive positions) fall in distinct banks
   static constexpr uint32_t OFF_ROPE = OFF_TMEM + 8;
@@ -84,6 +104,64 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint6
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// cta_group::2 forms: issued by the leader CTA of a pair; `bar` of the commit may be a mapa address in the peer.
+__device__ __forceinline__ void umma2_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma2_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// address of `addr` (a shared-memory address of this CTA) in the CTA of rank `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_rank(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// bounded wait on a barrier of this CTA whose arrivals come from the other CTA of the cluster
+__device__ __forceinline__ bool mbar_wait_bounded_cluster(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+// 2-D tiled TMA load into this CTA's shared memory whose completion is counted on a barrier of the pair's leader
+// (`bar` is a shared::cluster address; the bytes go to the issuing CTA only)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* tm, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(tm), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -106,14 +184,17 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 
 // FUSED: tm_c is unused; tm_o0..3 are the stores of XQ, XK, XV ([B*H*T, 64] views) and of the gate buffer.
-template <bool FUSED>
+// PAIR: launched as clusters of two CTAs (see the head of the file); tm_b then has a box of 128 rows.
+template <bool FUSED, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     ttt_gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                             const __grid_constant__ CUtensorMap tm_c, const __grid_constant__ CUtensorMap tm_o0,
                             const __grid_constant__ CUtensorMap tm_o1, const __grid_constant__ CUtensorMap tm_o2,
                             const __grid_constant__ CUtensorMap tm_o3, const GemmParams p) {
-  using SM = GemmSmem<FUSED>;
+  using SM = GemmSmem<FUSED, PAIR>;
   constexpr int GEMM_STAGES = SM::STAGES;
+  constexpr uint32_t STAGE_BYTES = SM::STAGE_BYTES;
+  constexpr int TILE_M = PAIR ? 2 * GEMM_BM : GEMM_BM;  // rows of C per tile (128 per CTA)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_u32 = smem_u32(smem_raw);
   const uint32_t base = (raw_u32 + 1023u) & ~1023u;
@@ -124,9 +205,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   __shared__ int s_fail;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;  // 0 = the CTA that issues the pair's products
   const int KB = (p.K + GEMM_BK - 1) / GEMM_BK;
-  const int tiles_n = (p.N + GEMM_BN - 1) / GEMM_BN, tiles_m = (p.M + GEMM_BM - 1) / GEMM_BM;
+  const int tiles_n = (p.N + GEMM_BN - 1) / GEMM_BN, tiles_m = (p.M + TILE_M - 1) / TILE_M;
   const int ntiles = tiles_n * tiles_m;
+  // this CTA's (pair's) tiles: first, stride
+  const int tile0 = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int tstep = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  // columns a tile really has, rounded up to the instruction's granule (the last tile column is narrower); in the
+  // pair form each CTA supplies half of them, so the granule is 32
+  auto n_eff_of = [&](int tile) {
+    const int n_left = p.N - (tile % tiles_n) * GEMM_BN;
+    return n_left >= GEMM_BN ? GEMM_BN : (PAIR ? ((n_left + 31) & ~31) : ((n_left + 15) & ~15));
+  };
 
   if (tid == 0) {
     prefetch_tmap(&tm_a);
@@ -139,17 +230,29 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     } else {
       prefetch_tmap(&tm_c);
     }
-    for (int i = 0; i < 2 * GEMM_STAGES + 4; ++i) mbar_init(bar_full + 8 * i, 1);
+    for (int i = 0; i < SM::NBAR; ++i) {
+      // one arrival per phase, except (pair form) `acc_empty`: an accumulator is free when the epilogues of both CTAs
+      // have arrived, the peer's from the other CTA
+      const uint32_t b = bar_full + 8 * i;
+      mbar_init(b, (PAIR && (b == bar_acc_empty || b == bar_acc_empty + 8)) ? 2 : 1);
+    }
     fence_mbar_init();
     s_fail = 0;
   }
   if (warp == 1) {  // tensor memory: two accumulators of 256 float32 columns (the same warp frees them at the end)
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(base + SM::OFF_TMEM)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if constexpr (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(base + SM::OFF_TMEM)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(base + SM::OFF_TMEM)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();  // both CTAs' barriers are initialised and both hold their tensor memory
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
 
@@ -157,36 +260,61 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     // ---------------- TMA producer: one ring over all the tiles of this CTA
     if (lane == 0) {
       uint32_t it = 0;  // k-blocks issued so far
-      for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-        const int m0 = (tile / tiles_n) * GEMM_BM, n0 = (tile % tiles_n) * GEMM_BN;
-        bool ok = true;
+      bool ok = true;
+      const uint32_t leader_full = PAIR ? mapa_rank(bar_full, 0) : bar_full;
+      for (int tile = tile0; tile < ntiles && ok; tile += tstep) {
+        const int m0 = (tile / tiles_n) * TILE_M + GEMM_BM * (int)rank;
+        // rows of B: all of the tile's, or this CTA's half of the columns the products will use
+        const int n0 = (tile % tiles_n) * GEMM_BN + (PAIR ? (int)rank * (n_eff_of(tile) >> 1) : 0);
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const uint32_t st = it % GEMM_STAGES;
-          if (it >= GEMM_STAGES && !mbar_wait_bounded(bar_empty + 8 * st, ((it / GEMM_STAGES) - 1) & 1)) {
+          if (it >= GEMM_STAGES) {
+            if (!(PAIR && rank == 1 ? mbar_wait_bounded_cluster(bar_empty + 8 * st, ((it / GEMM_STAGES) - 1) & 1)
+                                    : mbar_wait_bounded(bar_empty + 8 * st, ((it / GEMM_STAGES) - 1) & 1))) {
+              s_fail = 1;
+              report_timeout(p.status, 31, kb);
+              ok = false;
+              break;
+            }
+          }
+          if constexpr (PAIR) {
+            // both CTAs' loads complete on the leader's barrier, which expects the bytes of both
+            if (rank == 0) mbar_expect_tx(bar_full + 8 * st, 2 * STAGE_BYTES);
+            tma_load_2d_pair(base + st * STAGE_BYTES, &tm_a, kb * GEMM_BK, m0, leader_full + 8 * st);
+            tma_load_2d_pair(base + st * STAGE_BYTES + GEMM_A_BYTES, &tm_b, kb * GEMM_BK, n0, leader_full + 8 * st);
+          } else {
+            mbar_expect_tx(bar_full + 8 * st, STAGE_BYTES);  // (rows beyond M / N arrive as zeros and count)
+            tma_load_2d(base + st * STAGE_BYTES, &tm_a, kb * GEMM_BK, m0, bar_full + 8 * st);
+            tma_load_2d(base + st * STAGE_BYTES + GEMM_A_BYTES, &tm_b, kb * GEMM_BK, n0, bar_full + 8 * st);
+          }
+        }
+      }
+      if (PAIR && ok) {
+        // the last hand-backs of the stages (the peer's arrive from the other CTA) must land before this CTA leaves
+        const uint32_t last = it < (uint32_t)GEMM_STAGES ? it : (uint32_t)GEMM_STAGES;
+        for (uint32_t j = 0; j < last; ++j) {
+          const uint32_t i2 = it - 1 - j;  // the last k-block issued into stage i2 % GEMM_STAGES
+          if (!(rank == 1 ? mbar_wait_bounded_cluster(bar_empty + 8 * (i2 % GEMM_STAGES), (i2 / GEMM_STAGES) & 1)
+                          : mbar_wait_bounded(bar_empty + 8 * (i2 % GEMM_STAGES), (i2 / GEMM_STAGES) & 1))) {
             s_fail = 1;
-            report_timeout(p.status, 31, kb);
-            ok = false;
+            report_timeout(p.status, 35, j);
             break;
           }
-          mbar_expect_tx(bar_full + 8 * st, GEMM_STAGE_BYTES);  // (rows beyond M / N arrive as zeros and count)
-          tma_load_2d(base + st * GEMM_STAGE_BYTES, &tm_a, kb * GEMM_BK, m0, bar_full + 8 * st);
-          tma_load_2d(base + st * GEMM_STAGE_BYTES + GEMM_A_BYTES, &tm_b, kb * GEMM_BK, n0, bar_full + 8 * st);
         }
-        if (!ok) break;
       }
     }
   } else if (warp == 1) {
-    // ---------------- MMA issuer
-    if (lane == 0) {
+    // ---------------- MMA issuer (the leader of a pair); the peer only reports its stages
+    if (lane == 0 && rank == 0) {
       uint32_t it = 0, tl = 0;  // k-blocks consumed, tiles started
-      for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tl) {
+      const uint32_t peer_empty = PAIR ? mapa_rank(bar_empty, 1) : 0u, peer_acc_full = PAIR ? mapa_rank(bar_acc_full, 1) : 0u;
+      bool ok = true;
+      for (int tile = tile0; tile < ntiles && ok; tile += tstep, ++tl) {
         const uint32_t buf = tl & 1;
-        // columns this tile really has, rounded up to the instruction's granule (the last tile column is narrower)
-        const int n_left = p.N - (tile % tiles_n) * GEMM_BN;
-        const uint32_t idesc = umma_idesc_bf16(GEMM_BM, n_left >= GEMM_BN ? GEMM_BN : ((n_left + 15) & ~15));
-        bool ok = true;
-        // the epilogue must have drained this accumulator (its previous use was two tiles ago)
-        if (tl >= 2 && !mbar_wait_bounded(bar_acc_empty + 8 * buf, ((tl >> 1) - 1) & 1)) {
+        const uint32_t idesc = umma_idesc_bf16(TILE_M, n_eff_of(tile));
+        // the epilogue(s) must have drained this accumulator (its previous use was two tiles ago)
+        if (tl >= 2 && !(PAIR ? mbar_wait_bounded_cluster(bar_acc_empty + 8 * buf, ((tl >> 1) - 1) & 1)
+                              : mbar_wait_bounded(bar_acc_empty + 8 * buf, ((tl >> 1) - 1) & 1))) {
           s_fail = 1;
           report_timeout(p.status, 34, tl);
           break;
@@ -194,22 +322,51 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const uint32_t st = it % GEMM_STAGES;
-          if (!mbar_wait_bounded(bar_full + 8 * st, (it / GEMM_STAGES) & 1)) {
+          if (!(PAIR ? mbar_wait_bounded_cluster(bar_full + 8 * st, (it / GEMM_STAGES) & 1)
+                     : mbar_wait_bounded(bar_full + 8 * st, (it / GEMM_STAGES) & 1))) {
             s_fail = 1;
             report_timeout(p.status, 32, kb);
             ok = false;
             break;
           }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_addr = base + st * GEMM_STAGE_BYTES, b_addr = a_addr + GEMM_A_BYTES;
+          const uint32_t a_addr = base + st * STAGE_BYTES, b_addr = a_addr + GEMM_A_BYTES;
 #pragma unroll
-          for (int ks = 0; ks < GEMM_BK / 16; ++ks)  // 32 bytes per k-step inside the swizzled 128-byte rows
-            umma_bf16(tmem + buf * GEMM_BN, umma_desc_sw128(a_addr + 32 * ks), umma_desc_sw128(b_addr + 32 * ks), idesc,
-                      (kb | ks) != 0 ? 1u : 0u);
-          umma_commit(bar_empty + 8 * st);  // the stage is free once these products have read it
+          for (int ks = 0; ks < GEMM_BK / 16; ++ks) {  // 32 bytes per k-step inside the swizzled 128-byte rows
+            if constexpr (PAIR)
+              umma2_bf16(tmem + buf * GEMM_BN, umma_desc_sw128(a_addr + 32 * ks), umma_desc_sw128(b_addr + 32 * ks),
+                         idesc, (kb | ks) != 0 ? 1u : 0u);
+            else
+              umma_bf16(tmem + buf * GEMM_BN, umma_desc_sw128(a_addr + 32 * ks), umma_desc_sw128(b_addr + 32 * ks),
+                        idesc, (kb | ks) != 0 ? 1u : 0u);
+          }
+          // the stage is free once these products have read it (in both CTAs)
+          if constexpr (PAIR) {
+            umma2_commit(bar_empty + 8 * st);
+            umma2_commit(peer_empty + 8 * st);
+          } else {
+            umma_commit(bar_empty + 8 * st);
+          }
         }
         if (!ok) break;
-        umma_commit(bar_acc_full + 8 * buf);  // arrives when every product of this tile is complete
+        // arrives when every product of this tile is complete
+        if constexpr (PAIR) {
+          umma2_commit(bar_acc_full + 8 * buf);
+          umma2_commit(peer_acc_full + 8 * buf);
+        } else {
+          umma_commit(bar_acc_full + 8 * buf);
+        }
+      }
+      if (PAIR && ok) {
+        // the peer's last accumulator releases arrive from the other CTA: let them land before this CTA leaves
+        for (uint32_t j = 0; j < 2 && j < tl; ++j) {
+          const uint32_t t2 = tl - 1 - j;
+          if (!mbar_wait_bounded_cluster(bar_acc_empty + 8 * (t2 & 1), (t2 >> 1) & 1)) {
+            s_fail = 1;
+            report_timeout(p.status, 36, t2);
+            break;
+          }
+        }
       }
     }
   } else {
@@ -230,8 +387,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       asm volatile("bar.sync 1, 128;" ::: "memory");
     }
     uint32_t tl = 0;
-    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++tl) {
-      const int m0 = (tile / tiles_n) * GEMM_BM, n0 = (tile % tiles_n) * GEMM_BN;
+    // where this CTA reports an accumulator drained: its own barrier, or the pair leader's
+    const uint32_t acc_empty_at = PAIR ? mapa_rank(bar_acc_empty, 0) : bar_acc_empty;
+    for (int tile = tile0; tile < ntiles; tile += tstep, ++tl) {
+      const int m0 = (tile / tiles_n) * TILE_M + GEMM_BM * (int)rank, n0 = (tile % tiles_n) * GEMM_BN;
       const uint32_t buf = tl & 1;
       // fused: what each 64-column group of this tile is (0 q, 1 k, 2 v, 3 gate, 4 learning-rate logits, -1 nothing)
       // (packed into two words, 8 bits per group, so that the group loop can index them without a local array)
@@ -299,7 +458,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                   const int h = 32 * hc + i;
-                  if (h < p.f.H) {
+                  if (h < p.f.H && m0 + row < p.M) {
                     float z = __uint_as_float(r[i]);
                     if (p.f.lr_bias != nullptr) z += __bfloat162float(static_cast<const __nv_bfloat16*>(p.f.lr_bias)[h]);
                     static_cast<__nv_bfloat16*>(p.f.lr_out)[((size_t)bat * p.f.H + h) * p.f.T + tok] =
@@ -340,7 +499,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (warp == 2 && lane == 0) {
           // after the last group every tcgen05.ld of this accumulator has completed (wait::ld): hand it back
-          if (j == 3) mbar_arrive(bar_acc_empty + 8 * buf);
+          if (j == 3) {
+            if constexpr (PAIR) mbar_arrive_cluster(acc_empty_at + 8 * buf);
+            else mbar_arrive(bar_acc_empty + 8 * buf);
+          }
           if (live && !(FUSED && kd == 4)) {
             if (FUSED) {
               const int y = (b0 * p.f.H + hd) * p.f.T + t0;  // first of 128 consecutive rows of [B*H*T, 64]
@@ -361,25 +523,65 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+  if constexpr (PAIR) {
+    cluster_sync_all();  // neither CTA releases tensor memory or leaves while the other may still use the pair's
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+  } else {
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+  }
 }
 
 template <bool FUSED>
 static cudaError_t launch_gemm_t(const CUtensorMap* m, const GemmParams& p, cudaStream_t st) {
-  auto kfn = ttt_gemm_bf16_tn_kernel<FUSED>;
-  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GemmSmem<FUSED>::DYN_BYTES);
+  using SM = GemmSmem<FUSED, false>;
+  auto kfn = ttt_gemm_bf16_tn_kernel<FUSED, false>;
+  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM::DYN_BYTES);
   if (e != cudaSuccess) return e;
   int dev = 0, sms = 0;
   if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
   if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
   const long ntiles = (long)((p.N + GEMM_BN - 1) / GEMM_BN) * ((p.M + GEMM_BM - 1) / GEMM_BM);
   const int grid = (int)(ntiles < sms ? ntiles : sms);  // persistent: one CTA per SM walks the tiles
-  kfn<<<grid, GEMM_THREADS, GemmSmem<FUSED>::DYN_BYTES, st>>>(m[0], m[1], m[2], m[3], m[4], m[5], m[6], p);
+  kfn<<<grid, GEMM_THREADS, SM::DYN_BYTES, st>>>(m[0], m[1], m[2], m[3], m[4], m[5], m[6], p);
   return cudaGetLastError();
 }
 
-// maps: A, B, C (plain) or A, B, -, XQ, XK, XV, gate (fused: p.f filled in)
-cudaError_t launch_gemm_bf16_tn(const CUtensorMap* maps, const GemmParams& p, bool fused, cudaStream_t st) {
+// pair form: clusters of two CTAs, as many as can be resident (a cluster waits on nothing outside itself)
+template <bool FUSED>
+static cudaError_t launch_gemm_pair_t(const CUtensorMap* m, const GemmParams& p, cudaStream_t st) {
+  using SM = GemmSmem<FUSED, true>;
+  auto kfn = ttt_gemm_bf16_tn_kernel<FUSED, true>;
+  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM::DYN_BYTES);
+  if (e != cudaSuccess) return e;
+  int dev = 0, sms = 0;
+  if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+  if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = SM::DYN_BYTES;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.gridDim = dim3(2 * (sms / 2));
+  int nclusters = 0;
+  if ((e = cudaOccupancyMaxActiveClusters(&nclusters, kfn, &cfg)) != cudaSuccess) return e;
+  if (nclusters < 1) return cudaErrorLaunchOutOfResources;
+  const long ntiles = (long)((p.N + GEMM_BN - 1) / GEMM_BN) * ((p.M + 2 * GEMM_BM - 1) / (2 * GEMM_BM));
+  if (nclusters > sms / 2) nclusters = sms / 2;
+  if (nclusters > ntiles) nclusters = (int)ntiles;
+  cfg.gridDim = dim3(2 * nclusters);
+  return cudaLaunchKernelEx(&cfg, kfn, m[0], m[1], m[2], m[3], m[4], m[5], m[6], p);
+}
+
+// maps: A, B, C (plain) or A, B, -, XQ, XK, XV, gate (fused: p.f filled in).  pair: the cluster form, whose B map has
+// a box of 128 rows.
+cudaError_t launch_gemm_bf16_tn(const CUtensorMap* maps, const GemmParams& p, bool fused, bool pair, cudaStream_t st) {
+  if (pair) return fused ? launch_gemm_pair_t<true>(maps, p, st) : launch_gemm_pair_t<false>(maps, p, st);
   return fused ? launch_gemm_t<true>(maps, p, st) : launch_gemm_t<false>(maps, p, st);
 }
 

@@ -277,7 +277,7 @@ struct GemmParams {
   uint32_t* status;  // optional 4 words
   GemmFuse f;        // read by the fused kernel only
 };
-cudaError_t launch_gemm_bf16_tn(const CUtensorMap* maps, const GemmParams& p, bool fused, cudaStream_t st);
+cudaError_t launch_gemm_bf16_tn(const CUtensorMap* maps, const GemmParams& p, bool fused, bool pair, cudaStream_t st);
 
 // bf16 only.  maps: q, k, v, out.
 cudaError_t launch_mlp_fwd(const CUtensorMap* maps, const MlpFwdParams& p, int nstreams, cudaStream_t st);
