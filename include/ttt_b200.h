@@ -83,7 +83,8 @@ void ttt_b200_debug_handoff(uint32_t poll_limit, int32_t first_item);
 int64_t ttt_linear_num_checkpoints(const ttt_dims* d);
 /* Bytes of the two saved-state buffers the forward fills and the backward reads back (the role of the reference's
  * weight_checkpoints / bias_checkpoints tensors, forward/launch.rs:221-226).  Both are opaque to the caller:
- *   weight_ckpt: float32 W before every K-th stage plus the final W, [B*H*(NCK+1), F, F];
+ *   weight_ckpt: float32 W before every K-th stage plus the final W, B*H*(NCK+1) blocks of 64*64 floats, each in
+ *                the order the kernels' threads hold the state (not row-major);
  *   bias_ckpt:   per stage the lr-scaled LN gradient tile [B*H*T, F] of T, two float4 of row statistics per
  *                token, and the float32 bias at the start of every stage.
  * (head_dim 32, the reference's 16x32 tile, rust/fused/src/linear_fused_tile/mod.rs:32-37: the kernels run heads

@@ -52,7 +52,8 @@ def test_forward_matches_oracle(dtype, B, H, NS, K):
     assert_close(outs.bias, ref["bias"], r, "final bias")
     # saved state: float32 W before every K-th stage, then the final W, per stream
     nck = (NS + K - 1) // K
-    ck = saved.weight_checkpoints.reshape(B * H, nck + 1, 64, 64)
+    import ttt_rs_b200 as tb
+    ck = tb.unpack_weight_checkpoints(saved.weight_checkpoints).reshape(B * H, nck + 1, 64, 64)
     assert_close(ck[:, :nck].reshape(-1, 64, 64), ref["weight_checkpoints"], r, "weight checkpoints")
     assert_close(ck[:, nck], ref["weight"].reshape(B * H, 64, 64), r, "final-state checkpoint")
 

@@ -24,5 +24,6 @@ from .fused import (  # noqa: F401
     fused_ttt_mlp_forward,
     fused_ttt_tile_forward_multi,
     packed_outer_grad_len,
+    unpack_weight_checkpoints,
 )
 from .layer import TTT, DecodeGraphs, TTTLayerConfig, gemm_bf16_tn, layer_epilogue, layer_projections, layer_prologue, new_inner  # noqa: F401,E402

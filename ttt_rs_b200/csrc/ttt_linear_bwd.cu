@@ -274,6 +274,14 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
         dbias[nt] = __ldcg(reinterpret_cast<const float2*>(ho + 2 * HD * HD + nb + 8 * nt + 2 * t));
     }
 
+  // the next stage (walking down) that ends a checkpoint interval, and the checkpoint that holds the state after it
+  // (kept from stage to stage: no division by the runtime interval on the chain)
+  int ck_idx = s_hi / p.K + 1;
+  int s_ck = min(ck_idx * p.K, NS) - 1;
+  if (s_ck != s_hi) {
+    --ck_idx;
+    s_ck = ck_idx * p.K - 1;
+  }
   for (int s = s_hi; s >= s_lo; --s, ++n) {
     const int slot = n % SM::NSLOT;
     const uint32_t sl = base + slot * SM::SLOT;
@@ -282,16 +290,17 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
     const uint8_t* gsl = gbase + slot * SM::SLOT;
 
     // ---- at the last stage of a checkpoint interval: exact state after the stage (= next checkpoint / final W)
-    {
-      const int gi = s / p.K;
-      const int g1 = min((gi + 1) * p.K, NS);
-      if (s == g1 - 1) {
-        const float* wc = p.w_ckpt + ((size_t)stream * (p.NCK + 1) + gi + 1) * HD * HD;
+    if (s == s_ck) {
+      // stored by the forward as its threads held it: float4 kt of thread tid at [kt][tid]
+      const float4* wc =
+          reinterpret_cast<const float4*>(p.w_ckpt + ((size_t)stream * (p.NCK + 1) + ck_idx) * HD * HD);
 #pragma unroll
-        for (int kt = 0; kt < 8; ++kt)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) wt[kt][i] = wc[(8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1)] * winv;
+      for (int kt = 0; kt < 8; ++kt) {
+        const float4 v = __ldcg(wc + kt * NTHREADS + tid);
+        wt[kt][0] = v.x * winv; wt[kt][1] = v.y * winv; wt[kt][2] = v.z * winv; wt[kt][3] = v.w * winv;
       }
+      --ck_idx;
+      s_ck = ck_idx * p.K - 1;  // (the last interval of the sequence may be shorter than the others)
     }
 
     int fail = mbar_wait_bounded(bar0 + 8 * slot, (n / SM::NSLOT) & 1) ? 0 : 1;

@@ -174,6 +174,10 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
 
   int xsel = 0;
   bool failed = false;
+  // where the next checkpoint and the next per-stage bias record go, and the stages left until the next checkpoint
+  float4* ck_ptr = save ? reinterpret_cast<float4*>(p.w_ckpt + (size_t)stream * (p.NCK + 1) * HD * HD) : nullptr;
+  float* bs_ptr = save ? p.b_stage + (size_t)stream * (NS + 1) * HD : nullptr;
+  int ck_left = 0;
 
   // One stage with its ring slot known at compile time, so every shared-memory address is a hoisted lane offset plus
   // an immediate.  Returns false after a timed-out wait.
@@ -193,20 +197,6 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
         if (tid == 0) report_timeout(p.status, 1, s);
         return false;
       }
-    }
-
-    // ---- saved state: W before the update of every K-th stage, the bias before every stage
-    if (save && s % p.K == 0) {
-      float* wc = p.w_ckpt + ((size_t)stream * (p.NCK + 1) + s / p.K) * HD * HD;
-#pragma unroll
-      for (int kt = 0; kt < 8; ++kt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) wc[(8 * kt + 2 * t + (i & 1)) * HD + nb + g + 8 * (i >> 1)] = wt[kt][i] * wscale;
-    }
-    if (save && g == 0) {
-      float* bs = p.b_stage + ((size_t)stream * (NS + 1) + s) * HD;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) bs[nb + 8 * (j >> 1) + 2 * t + (j & 1)] = bias[j];
     }
 
     // (SEG = 32: the pair's second head has its 16 values right after the first head's)
@@ -239,6 +229,28 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
         mma_np<NP>(at[1], aq, bj1);
       }
     }
+    // ---- saved state: W before the update of every K-th stage, the bias before every stage.  Issued behind the
+    // products so that the stores' address arithmetic runs under the tensor cores' latency; the places are advanced
+    // from stage to stage (no division by the runtime interval on the chain).
+    if (save) {
+      if (ck_left == 0) {
+        // kept as the threads hold it (float4 kt of thread tid at [kt][tid]): eight coalesced 16-byte stores per
+        // thread, read back the same way by the backward
+#pragma unroll
+        for (int kt = 0; kt < 8; ++kt)
+          ck_ptr[kt * NTHREADS + tid] =
+              make_float4(wt[kt][0] * wscale, wt[kt][1] * wscale, wt[kt][2] * wscale, wt[kt][3] * wscale);
+        ck_ptr += HD * HD / 4;
+        ck_left = p.K;
+      }
+      --ck_left;
+      if (g == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) bs_ptr[nb + 8 * (j >> 1) + 2 * t + (j & 1)] = bias[j];
+      }
+      bs_ptr += HD;
+    }
+
     // products were taken with What: Z = wscale * acc + b
     F2 z1p[2][2], zqp[2][2];
 #pragma unroll
@@ -394,7 +406,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
 
   if (!failed) {
     // ---- final state (returned, and kept as the last checkpoint / last bias record for the backward)
-    float* wc = save ? p.w_ckpt + ((size_t)stream * (p.NCK + 1) + p.NCK) * HD * HD : nullptr;
+    float4* wc = save ? reinterpret_cast<float4*>(p.w_ckpt + ((size_t)stream * (p.NCK + 1) + p.NCK) * HD * HD) : nullptr;
 #pragma unroll
     for (int kt = 0; kt < 8; ++kt)
 #pragma unroll
@@ -407,7 +419,9 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
           st_from_float<T>(p.w_out, (size_t)(2 * stream + hsel) * 32 * 32 + ((idx >> 6) & 31) * 32 + (idx & 31),
                            wt[kt][i] * wscale);
         }
-        if (save) wc[idx] = wt[kt][i] * wscale;
+        if (save && i == 3)
+          wc[kt * NTHREADS + tid] =
+              make_float4(wt[kt][0] * wscale, wt[kt][1] * wscale, wt[kt][2] * wscale, wt[kt][3] * wscale);
       }
     if (g == 0) {
 #pragma unroll

@@ -313,6 +313,22 @@ class TttTileMultiKernel:
         check_status(device)
 
 
+def unpack_weight_checkpoints(weight_checkpoints: torch.Tensor) -> torch.Tensor:
+    """The float32 state checkpoints of `TttSavedStateMulti` as plain [n, 64, 64] matrices W[k][n] (for inspection and
+    tests; the kernels never need this).  The buffer holds each 64 x 64 state the way the kernels' threads hold it:
+    float4 `kt` of thread `tid` at [kt][tid], whose element i is W[8 kt + 2 t + (i & 1)][16 warp + g + 8 (i >> 1)] with
+    tid = 32 warp + 4 g + t -- eight coalesced 16-byte accesses per thread instead of 32 scattered ones."""
+    v = weight_checkpoints.reshape(-1, 8, 4, 8, 4, 4)  # [n, kt, warp, g, t, i]
+    n = v.shape[0]
+    kt, warp, g, t, i = torch.meshgrid(torch.arange(8), torch.arange(4), torch.arange(8), torch.arange(4),
+                                       torch.arange(4), indexing="ij")
+    k = (8 * kt + 2 * t + (i & 1)).reshape(-1).to(v.device)
+    col = (16 * warp + g + 8 * (i >> 1)).reshape(-1).to(v.device)
+    out = torch.empty((n, 64, 64), dtype=v.dtype, device=v.device)
+    out[:, k, col] = v.reshape(n, -1)
+    return out
+
+
 def packed_outer_grad_len(heads: int, head_dim: int = 64, mini_batch: int = 16) -> int:
     """Length of the float32 buffer `outer_grad_packed`: dW0 [H,F,F], db0 [H,F], d ln_weight [H,F],
     d ln_bias [H,F], d token_eta [CS]."""
