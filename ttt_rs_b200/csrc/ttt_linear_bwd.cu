@@ -77,6 +77,9 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
   constexpr uint32_t PL = TILE_BF16_BYTES;  // plane stride
   constexpr float INV_F = 1.f / SEG;        // features per head (LayerNorm row length)
   constexpr int NH = (SEG == 32) ? 2 : 1;   // heads per tile
+  // The loads of the next stage are issued by the first thread of warp 1, the stores (and their bulk groups) by thread
+  // 0: one warp doing both arrives at the stage's barriers that much later than the other three.
+  constexpr int LOADER = 32;
   constexpr bool GATHER = PairIo<T, SEG>::GATHER;  // q, k, v, d_out, d_q, d_k, d_v tiles moved by the threads, not TMA
 
   extern __shared__ uint8_t smem_raw[];
@@ -203,7 +206,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
     row_base = stream * p.T;
     const int head = stream % p.H;
     const int s_lo = chunk * p.CH, s_hi = min(s_lo + p.CH, NS) - 1;
-    if (tid == 0) issue_loads(n, s_hi);
+    if (tid == LOADER) issue_loads(n, s_hi);
     issue_gather(n, s_hi);
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
@@ -310,7 +313,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       // so the other slot may be overwritten
       if (!next_issued) {
         next_issued = true;
-        if (tid == 0 && s > s_lo) issue_loads(n + 1, s - 1);
+        if (tid == LOADER && s > s_lo) issue_loads(n + 1, s - 1);
         if (GATHER && s > s_lo) issue_gather(n + 1, s - 1);
       }
     };
@@ -587,7 +590,8 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       s1t[0] = o0.x * INV_F; s2t[0] = o0.y * INV_F;
       s1t[1] = o1.x * INV_F; s2t[1] = o1.y * INV_F;
       const float rt_all = col_sum(o0.w + o1.w);  // sum over the 16 rows
-      if ((SEG == 32 ? (warp & 1) == 0 : warp == 0) && t == 0) {
+      // (every warp holds these row values; warp 2 writes them: warps 0 and 1 issue the stage's stores and loads)
+      if ((SEG == 32 ? (warp & 1) == 0 : warp == 2) && t == 0) {
         // per (batch, head) stream of the caller's tensors: the pair's heads are streams 2 * stream and 2 * stream + 1
         const size_t o = (SEG == 32 ? (size_t)(2 * stream + hsel) * p.T : (size_t)row_base) + (size_t)s * CS;
         st_from_float<T>(p.d_lr, o + g, o0.z);

@@ -392,8 +392,10 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
       if (save) tma_store_tile<T>(&tm_g, row_base + s * CS, sg);  // saved tiles are kept in the packed 64-wide form
       bulk_commit();
       bulk_wait_read<1>();
-      if (s + FWD_NST < NS) issue_loads(s + FWD_NST);
     }
+    // (the next loads by the first thread of warp 1: thread 0 is busy with the stores, and a warp that does both
+    // arrives at the next stage's first barrier that much later than the other three)
+    if (tid == 32 && s + FWD_NST < NS) issue_loads(s + FWD_NST);
     if constexpr (GATHER)
       if (s + FWD_NST < NS) issue_gather(s + FWD_NST);
     return true;
