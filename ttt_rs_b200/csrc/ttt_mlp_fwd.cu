@@ -349,7 +349,8 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
       if (tid == 0) report_timeout(p.status, 21, s);
       break;
     }
-    if (tid == 0 && s > s_lo && s < s_hi) issue_loads(n + 1, s + 1);
+    // (the first thread of warp 1: thread 0 issues the stage's stores, and a warp doing both reaches the barriers late)
+    if (tid == 32 && s > s_lo && s < s_hi) issue_loads(n + 1, s + 1);
 
     // B fragments of W2[:, fb..fb+7] for two k-steps (32 hidden rows) from the bf16 copy
     const int m_ = lane >> 3, r_ = lane & 7;
