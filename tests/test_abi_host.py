@@ -49,6 +49,17 @@ def test_checkpoint_and_workspace_sizes(lib):
         streams * 1 * 128 + streams * 80 + streams * (4096 + 64) + streams * (2 * 4096 + 64) + 8)
 
 
+def test_sizes_for_mini_batch_8(lib):
+    """8-token mini-batches: twice the stages, so twice the per-stage records; per-token records unchanged."""
+    d = _dims(mini_batch=8, seq_len=80, checkpoint_interval=4)  # 10 stages -> 3 checkpoints
+    assert lib.ttt_linear_num_checkpoints(C.byref(d)) == 3
+    assert lib.ttt_linear_weight_ckpt_bytes(C.byref(d)) == 2 * 2 * (3 + 1) * 64 * 64 * 4
+    rows, streams, ns = 2 * 2 * 80, 4, 10
+    assert lib.ttt_linear_bias_ckpt_bytes(C.byref(d)) == rows * 64 * 2 + rows * 32 + streams * (ns + 1) * 64 * 4
+    # the TTT-MLP kernels take 16-token mini-batches only
+    assert lib.ttt_mlp_backward_workspace_bytes(C.byref(d)) == 0
+
+
 def test_sizes_for_head_dim_32(lib):
     """Two 32-wide heads share a 64-wide tile: saved state is sized per pair, per-head results per head."""
     d = _dims(head_dim=32, heads=4, seq_len=80, checkpoint_interval=2)
@@ -65,7 +76,8 @@ def test_sizes_for_head_dim_32(lib):
 
 @pytest.mark.parametrize("kw,code", [
     (dict(seq_len=70), _lib.TTT_ERR_SHAPE),              # not a multiple of the mini-batch
-    (dict(mini_batch=8, seq_len=64), _lib.TTT_ERR_UNSUPPORTED),
+    (dict(mini_batch=32, seq_len=64), _lib.TTT_ERR_UNSUPPORTED),   # 32-token mini-batches are not built
+    (dict(mini_batch=4, seq_len=64), _lib.TTT_ERR_UNSUPPORTED),
     (dict(head_dim=128), _lib.TTT_ERR_UNSUPPORTED),
     (dict(head_dim=32, heads=3), _lib.TTT_ERR_UNSUPPORTED),   # head_dim 32 pairs heads: needs an even count
     (dict(checkpoint_interval=0), _lib.TTT_ERR_SHAPE),

@@ -46,13 +46,13 @@ EncodeFn get_encode_fn() {
 
 // 2-D view [rows, 64] of a [B,H,T,64] tensor, box = one 16-token tile (or half of it for float32),
 // 128-byte swizzle so that ldmatrix / element-wise shared-memory reads are bank-conflict free.
-int make_tile_map(CUtensorMap* m, const void* base, int64_t rows, int dtype) {
+int make_tile_map(CUtensorMap* m, const void* base, int64_t rows, int dtype, int box_rows = 16) {
   EncodeFn enc = get_encode_fn();
   if (enc == nullptr) return fail(TTT_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
   const bool bf = dtype == TTT_BF16;
   const cuuint64_t dims[2] = {64, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)(64 * (bf ? 2 : 4))};
-  const cuuint32_t box[2] = {(cuuint32_t)(bf ? 64 : 32), 16};
+  const cuuint32_t box[2] = {(cuuint32_t)(bf ? 64 : 32), (cuuint32_t)box_rows};  // (8 rows: mini-batches of 8 tokens)
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(m, bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -81,13 +81,13 @@ int make_gemm_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, 
 // [B*H*T, 32], box = 16 tokens x 32 features = 16 rows of 128 bytes = one half tile.  (In bf16 a half tile is 64 bytes
 // wide, narrower than the swizzle span; those tiles are gathered by the kernel from the plain pointer and the map is a
 // placeholder over the same memory.)
-int make_pair_map(CUtensorMap* m, const void* base, int64_t pairs, int64_t T, int dtype) {
+int make_pair_map(CUtensorMap* m, const void* base, int64_t pairs, int64_t T, int dtype, int box_rows = 16) {
   EncodeFn enc = get_encode_fn();
   if (enc == nullptr) return fail(TTT_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
   const bool bf = dtype == TTT_BF16;
   const cuuint64_t dims[2] = {32, (cuuint64_t)(2 * pairs * T)};
   const cuuint64_t strides[1] = {(cuuint64_t)(32 * (bf ? 2 : 4))};
-  const cuuint32_t box[2] = {32, 16};
+  const cuuint32_t box[2] = {32, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(m, bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -118,8 +118,8 @@ Packing packing(const ttt_dims* d) {
 // map of one [B,H,T,F] input or output of the caller
 int make_io_map(CUtensorMap* m, const void* base, const ttt_dims* d) {
   const Packing k = packing(d);
-  if (k.seg == 64) return make_tile_map(m, base, k.rows, d->dtype);
-  return make_pair_map(m, base, k.streams, d->seq_len, d->dtype);
+  if (k.seg == 64) return make_tile_map(m, base, k.rows, d->dtype, d->mini_batch);
+  return make_pair_map(m, base, k.streams, d->seq_len, d->dtype, d->mini_batch);
 }
 
 // Which form of the projection GEMM runs: CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles) when the product has at
@@ -133,15 +133,18 @@ bool gemm_pair_form(int64_t m) {
   return forced >= 0 ? forced != 0 : m >= 512;
 }
 
-int check_dims(const ttt_dims* d, bool allow_head_dim_32 = false) {
+int check_dims(const ttt_dims* d, bool linear_tiles = false) {
   if (d == nullptr) return fail(TTT_ERR_NULL, "dims is null");
   if (d->batch <= 0 || d->heads <= 0 || d->seq_len <= 0 || d->head_dim <= 0 || d->mini_batch <= 0)
     return fail(TTT_ERR_SHAPE, "batch, heads, seq_len, head_dim and mini_batch must be positive");
   if (d->checkpoint_interval < 1) return fail(TTT_ERR_SHAPE, "checkpoint_interval must be >= 1");
   if (d->dtype != TTT_F32 && d->dtype != TTT_BF16) return fail(TTT_ERR_UNSUPPORTED, "unknown dtype %d", d->dtype);
-  if (d->mini_batch != 16 || (d->head_dim != 64 && !(allow_head_dim_32 && d->head_dim == 32)))
+  // TTT-Linear forward / backward (`linear_tiles`): 16x64, 16x32, 8x64, 8x32; everything else: 16x64
+  const bool mb_ok = d->mini_batch == 16 || (linear_tiles && d->mini_batch == 8);
+  const bool hd_ok = d->head_dim == 64 || (linear_tiles && d->head_dim == 32);
+  if (!mb_ok || !hd_ok)
     return fail(TTT_ERR_UNSUPPORTED, "Unsupported tile config: mini_batch_len=%d, head_dim=%d (supported: 16x64%s)",
-                d->mini_batch, d->head_dim, allow_head_dim_32 ? ", 16x32" : "");
+                d->mini_batch, d->head_dim, linear_tiles ? ", 16x32, 8x64, 8x32" : "");
   if (d->head_dim == 32 && d->heads % 2 != 0)
     return fail(TTT_ERR_UNSUPPORTED, "head_dim 32 runs two heads per tile and needs an even number of heads (got %d)",
                 d->heads);
@@ -389,7 +392,7 @@ int ttt_linear_forward(const ttt_dims* d, const void* xq, const void* xk, const 
     if (rc != TTT_OK) return rc;
   }
   // the saved Gp tiles are always kept 64 wide; without saved state the map is never used, but must be a valid one
-  rc = save ? make_tile_map(&maps[4], aux + al.off_gp, pk.rows, d->dtype) : make_io_map(&maps[4], output, d);
+  rc = save ? make_tile_map(&maps[4], aux + al.off_gp, pk.rows, d->dtype, d->mini_batch) : make_io_map(&maps[4], output, d);
   if (rc != TTT_OK) return rc;
   ttt::LinFwdParams p;
   p.w0 = weight;
@@ -411,7 +414,8 @@ int ttt_linear_forward(const ttt_dims* d, const void* xq, const void* xk, const 
   p.NCK = (int)num_ckpt(d);
   p.eps = d->epsilon;
   cudaError_t e =
-      ttt::launch_linear_fwd(d->dtype, pk.seg, maps, bases, p, (int)pk.streams, static_cast<cudaStream_t>(stream));
+      ttt::launch_linear_fwd(d->dtype, pk.seg, d->mini_batch, maps, bases, p, (int)pk.streams,
+                             static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "forward launch failed: %s", cudaGetErrorString(e));
   return TTT_OK;
 }
@@ -487,7 +491,7 @@ int ttt_linear_backward_state_grads(const ttt_dims* d, const void* xq, const voi
     rc = make_io_map(&maps[i], bases[i], d);
     if (rc != TTT_OK) return rc;
   }
-  rc = make_tile_map(&maps[7], aux + al.off_gp, pk.rows, d->dtype);
+  rc = make_tile_map(&maps[7], aux + al.off_gp, pk.rows, d->dtype, d->mini_batch);
   if (rc != TTT_OK) return rc;
   float* ws = static_cast<float*>(workspace);
   ttt::LinBwdParams p;
@@ -523,7 +527,7 @@ int ttt_linear_backward_state_grads(const ttt_dims* d, const void* xq, const voi
   p.NCK = (int)num_ckpt(d);
   p.eps = d->epsilon;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  cudaError_t e = ttt::launch_linear_bwd(d->dtype, pk.seg, maps, bases, p, (int)pk.streams, st);
+  cudaError_t e = ttt::launch_linear_bwd(d->dtype, pk.seg, d->mini_batch, maps, bases, p, (int)pk.streams, st);
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "backward launch failed: %s", cudaGetErrorString(e));
   ttt::ReduceParams r;
   r.part_ln = p.part_ln;
@@ -536,6 +540,7 @@ int ttt_linear_backward_state_grads(const ttt_dims* d, const void* xq, const voi
   r.B = d->batch;
   r.H = d->heads;
   r.F = d->head_dim;
+  r.mb = d->mini_batch;
   r.T = d->seq_len;
   r.NCH = wl.nch;
   e = ttt::launch_linear_bwd_reduce(r, st);

@@ -62,7 +62,8 @@ struct ReduceParams {
   float* d_ln_b;       // [H,F] f32
   float* packed;       // nullable: [H*F*F + 3*H*F + CS] f32
   int B, H, T, NCH;
-  int F;  // features per head: 64, or 32 (two heads per 64-wide tile in part_ln)
+  int F;   // features per head: 64, or 32 (two heads per 64-wide tile in part_ln)
+  int mb;  // tokens per mini-batch (16 or 8): d_token_eta is folded to [mb]
 };
 
 struct MlpFwdParams {
@@ -282,14 +283,15 @@ cudaError_t launch_gemm_bf16_tn(const CUtensorMap* maps, const GemmParams& p, bo
 // bf16 only.  maps: q, k, v, out.
 cudaError_t launch_mlp_fwd(const CUtensorMap* maps, const MlpFwdParams& p, int nstreams, cudaStream_t st);
 
-// dtype: 0 = float32, 1 = bfloat16.  seg: features per head, 64 or 32 (two heads per tile).
+// dtype: 0 = float32, 1 = bfloat16.  seg: features per head, 64 or 32 (two heads per tile).  mb: tokens per
+// mini-batch, 16 or 8 (the tile maps then have boxes of 8 rows).
 // maps: q, k, v, out, gp (saved lr-scaled LN gradient, [B*H*T, 64] of T); io: the plain pointers behind the first
 // four maps, in the same order (used by the instantiation that gathers its tiles: seg 32 in bf16).
-cudaError_t launch_linear_fwd(int dtype, int seg, const CUtensorMap* maps, const void* const* io, const LinFwdParams& p,
-                              int nstreams, cudaStream_t st);
+cudaError_t launch_linear_fwd(int dtype, int seg, int mb, const CUtensorMap* maps, const void* const* io,
+                              const LinFwdParams& p, int nstreams, cudaStream_t st);
 // maps: q, k, v, d_out, d_q, d_k, d_v, gp; io: the plain pointers behind the first seven.
-cudaError_t launch_linear_bwd(int dtype, int seg, const CUtensorMap* maps, const void* const* io, const LinBwdParams& p,
-                              int nstreams, cudaStream_t st);
+cudaError_t launch_linear_bwd(int dtype, int seg, int mb, const CUtensorMap* maps, const void* const* io,
+                              const LinBwdParams& p, int nstreams, cudaStream_t st);
 cudaError_t launch_linear_bwd_reduce(const ReduceParams& p, cudaStream_t st);
 
 }  // namespace ttt

@@ -61,7 +61,7 @@ struct BwdSmem {
 #define TTT_BWD_MINB_BF16 2  // resident blocks per SM the bf16 kernel is compiled for
 #endif
 
-template <typename T, int SEG>
+template <typename T, int SEG, int MB>
 __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 : 1))
     ttt_linear_bwd_kernel(const __grid_constant__ typename PairIo<T, SEG>::Ref tm_q,
                           const __grid_constant__ typename PairIo<T, SEG>::Ref tm_k,
@@ -116,6 +116,25 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
     for (int i = 0; i < SM::NSLOT; ++i) mbar_init(bar0 + 8 * i, GATHER ? 1 + NTHREADS : 1);
     fence_mbar_init();
   }
+  if constexpr (MB < CS) {
+    // padding rows of every tile of both slots, and of the statistics and lr records: zero once; the copies only ever
+    // write the first MB rows / records
+    for (uint32_t e = tid * 4; e < SM::NSLOT * SM::SLOT; e += NTHREADS * 4) {
+      const uint32_t o = e % SM::SLOT;
+      bool pad = false;
+      if (o < 3 * TF::BYTES) {  // q, k, gp: raw tile, then operand planes derived from it
+        const uint32_t in_tile = o % TF::BYTES;
+        pad = in_tile >= TF::RAW_BYTES || (in_tile % 2048) >= MB * 128;
+      } else if (o < SM::OFF_STAT) {  // v, d_out: raw tiles
+        pad = ((o - 3 * TF::BYTES) % 2048) >= MB * 128;
+      } else if (o < SM::OFF_BS) {
+        pad = (o - SM::OFF_STAT) >= MB * 32 * NH;
+      } else if (o >= SM::OFF_LR) {
+        pad = ((o - SM::OFF_LR) % (CS * TF::ELT)) >= MB * TF::ELT;
+      }
+      if (pad) asm volatile("st.shared.b32 [%0], %1;" ::"r"(base + e), "r"(0u) : "memory");
+    }
+  }
   __syncthreads();
 
   // everything stage s needs, into slot n % NSLOT (thread 0: TMA / bulk copies)
@@ -123,33 +142,33 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
     const int slot = n % SM::NSLOT;
     const uint32_t bar = bar0 + 8 * slot;
     const uint32_t sl = base + slot * SM::SLOT;
-    const int r0 = row_base + s * CS;
+    const int r0 = row_base + s * MB;
     if constexpr (SEG == 64) {
-      mbar_expect_tx(bar, 5u * TF::RAW_BYTES + 512u + 256u + CS * TF::ELT);
+      mbar_expect_tx(bar, (5u * TF::RAW_BYTES + 512u + CS * TF::ELT) * MB / CS + 256u);
       tma_load_tile<T>(sl + SM::OFF_K, &tm_k, r0, bar);
       tma_load_tile<T>(sl + SM::OFF_G, &tm_g, r0, bar);
       tma_load_tile<T>(sl + SM::OFF_Q, &tm_q, r0, bar);
       tma_load_tile<T>(sl + SM::OFF_V, &tm_v, r0, bar);
       tma_load_tile<T>(sl + SM::OFF_DO, &tm_do, r0, bar);
-      bulk_load_1d(sl + SM::OFF_STAT, p.stats + (size_t)r0 * 2, 512u, bar);
+      bulk_load_1d(sl + SM::OFF_STAT, p.stats + (size_t)r0 * 2, 512u * MB / CS, bar);
       bulk_load_1d(sl + SM::OFF_BS, p.b_stage + ((size_t)stream * (NS + 1) + s) * HD, 256u, bar);
-      bulk_load_1d(sl + SM::OFF_LR, static_cast<const uint8_t*>(p.lr) + (size_t)r0 * TF::ELT, CS * TF::ELT, bar);
+      bulk_load_1d(sl + SM::OFF_LR, static_cast<const uint8_t*>(p.lr) + (size_t)r0 * TF::ELT, MB * TF::ELT, bar);
     } else {
-      mbar_expect_tx(bar, (GATHER ? 1u : 5u) * TF::RAW_BYTES + 1024u + 256u + 2 * CS * TF::ELT);
+      mbar_expect_tx(bar, ((GATHER ? 1u : 5u) * TF::RAW_BYTES + 1024u + 2 * CS * TF::ELT) * MB / CS + 256u);
       tma_load_tile<T>(sl + SM::OFF_G, &tm_g, r0, bar);  // saved tiles are kept in the packed 64-wide form
       if constexpr (!GATHER) {
-        tma_load_pair<T>(sl + SM::OFF_K, &tm_k, stream, s * CS, p.T, bar);
-        tma_load_pair<T>(sl + SM::OFF_Q, &tm_q, stream, s * CS, p.T, bar);
-        tma_load_pair<T>(sl + SM::OFF_V, &tm_v, stream, s * CS, p.T, bar);
-        tma_load_pair<T>(sl + SM::OFF_DO, &tm_do, stream, s * CS, p.T, bar);
+        tma_load_pair<T>(sl + SM::OFF_K, &tm_k, stream, s * MB, p.T, bar);
+        tma_load_pair<T>(sl + SM::OFF_Q, &tm_q, stream, s * MB, p.T, bar);
+        tma_load_pair<T>(sl + SM::OFF_V, &tm_v, stream, s * MB, p.T, bar);
+        tma_load_pair<T>(sl + SM::OFF_DO, &tm_do, stream, s * MB, p.T, bar);
       }
-      bulk_load_1d(sl + SM::OFF_STAT, p.stats + (size_t)r0 * 4, 1024u, bar);
+      bulk_load_1d(sl + SM::OFF_STAT, p.stats + (size_t)r0 * 4, 1024u * MB / CS, bar);
       bulk_load_1d(sl + SM::OFF_BS, p.b_stage + ((size_t)stream * (NS + 1) + s) * HD, 256u, bar);
 #pragma unroll
       for (int j = 0; j < 2; ++j)  // ttt_lr_eta is [B, H, T]: the two heads of the pair are T elements apart
         bulk_load_1d(sl + SM::OFF_LR + j * CS * TF::ELT,
-                     static_cast<const uint8_t*>(p.lr) + ((size_t)(2 * stream + j) * p.T + s * CS) * TF::ELT,
-                     CS * TF::ELT, bar);
+                     static_cast<const uint8_t*>(p.lr) + ((size_t)(2 * stream + j) * p.T + s * MB) * TF::ELT,
+                     MB * TF::ELT, bar);
     }
   };
   // every thread, where tiles are gathered: its 16-byte chunk of the k, q, v, d_out tiles, then its arrival
@@ -157,18 +176,20 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
     if constexpr (GATHER) {
       const int slot = n % SM::NSLOT;
       const uint32_t sl = base + slot * SM::SLOT;
-      gather_pair_tile_bf16(sl + SM::OFF_K, tm_k.ptr, stream, s * CS, p.T, tid);
-      gather_pair_tile_bf16(sl + SM::OFF_Q, tm_q.ptr, stream, s * CS, p.T, tid);
-      gather_pair_tile_bf16(sl + SM::OFF_V, tm_v.ptr, stream, s * CS, p.T, tid);
-      gather_pair_tile_bf16(sl + SM::OFF_DO, tm_do.ptr, stream, s * CS, p.T, tid);
+      gather_pair_tile_bf16<MB>(sl + SM::OFF_K, tm_k.ptr, stream, s * MB, p.T, tid);
+      gather_pair_tile_bf16<MB>(sl + SM::OFF_Q, tm_q.ptr, stream, s * MB, p.T, tid);
+      gather_pair_tile_bf16<MB>(sl + SM::OFF_V, tm_v.ptr, stream, s * MB, p.T, tid);
+      gather_pair_tile_bf16<MB>(sl + SM::OFF_DO, tm_do.ptr, stream, s * MB, p.T, tid);
       cp_async_mbar_arrive_noinc(bar0 + 8 * slot);
     }
   };
 
   // ---- per-thread constants and accumulators (column pairs nt = 0,1; rows g and g+8)
   F2 gam[2], bet[2];
-  const float te_row[2] = {ld_as_float<T>(p.token_eta, g), ld_as_float<T>(p.token_eta, g + 8)};
-  const float te15 = ld_as_float<T>(p.token_eta, CS - 1);
+  // (MB = 8: rows 8..15 of every tile are padding -- zero operands, statistics, lr and token_eta, so every value
+  // derived from them is finite and multiplies a zero; nothing of them is stored)
+  const float te_row[2] = {ld_as_float<T>(p.token_eta, g), MB == CS ? ld_as_float<T>(p.token_eta, g + 8) : 0.f};
+  const float te15 = ld_as_float<T>(p.token_eta, MB - 1);
   // as in the forward, the state is carried as What = W / wscale (wscale = -te15), which turns the reversal of a
   // stage's update into one tensor-core accumulation What -= Gp^T K
   const bool w_moves = (te15 != 0.f);
@@ -593,11 +614,15 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       // (every warp holds these row values; warp 2 writes them: warps 0 and 1 issue the stage's stores and loads)
       if ((SEG == 32 ? (warp & 1) == 0 : warp == 2) && t == 0) {
         // per (batch, head) stream of the caller's tensors: the pair's heads are streams 2 * stream and 2 * stream + 1
-        const size_t o = (SEG == 32 ? (size_t)(2 * stream + hsel) * p.T : (size_t)row_base) + (size_t)s * CS;
+        const size_t o = (SEG == 32 ? (size_t)(2 * stream + hsel) * p.T : (size_t)row_base) + (size_t)s * MB;
         st_from_float<T>(p.d_lr, o + g, o0.z);
-        st_from_float<T>(p.d_lr, o + g + 8, o1.z);
-        p.part_te[o + g] = dte_row[0];
-        p.part_te[o + g + 8] = dte_row[1] - (g == 7 ? rt_all : 0.f);
+        if constexpr (MB == CS) {
+          st_from_float<T>(p.d_lr, o + g + 8, o1.z);
+          p.part_te[o + g] = dte_row[0];
+          p.part_te[o + g + 8] = dte_row[1] - (g == 7 ? rt_all : 0.f);
+        } else {
+          p.part_te[o + g] = dte_row[0] - (g == 7 ? rt_all : 0.f);  // the last token of an 8-token mini-batch is row 7
+        }
       }
     }
     // ---- 11. second derivative through LN + L2 gradient -> dZ1, dT
@@ -682,19 +707,19 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       fence_proxy_async_smem();
       __syncthreads();
       if constexpr (GATHER) {
-        scatter_pair_tile_bf16(tm_dq.ptr, stream, s * CS, p.T, so_q, tid);
-        scatter_pair_tile_bf16(tm_dk.ptr, stream, s * CS, p.T, so_k, tid);
-        scatter_pair_tile_bf16(tm_dv.ptr, stream, s * CS, p.T, so_v, tid);
+        scatter_pair_tile_bf16<MB>(tm_dq.ptr, stream, s * MB, p.T, so_q, tid);
+        scatter_pair_tile_bf16<MB>(tm_dk.ptr, stream, s * MB, p.T, so_k, tid);
+        scatter_pair_tile_bf16<MB>(tm_dv.ptr, stream, s * MB, p.T, so_v, tid);
       } else if (tid == 0) {
         if constexpr (SEG == 64) {
-          const int r0 = row_base + s * CS;
+          const int r0 = row_base + s * MB;
           tma_store_tile<T>(&tm_dq, r0, so_q);
           tma_store_tile<T>(&tm_dk, r0, so_k);
           tma_store_tile<T>(&tm_dv, r0, so_v);
         } else {
-          tma_store_pair<T>(&tm_dq, stream, s * CS, p.T, so_q);
-          tma_store_pair<T>(&tm_dk, stream, s * CS, p.T, so_k);
-          tma_store_pair<T>(&tm_dv, stream, s * CS, p.T, so_v);
+          tma_store_pair<T>(&tm_dq, stream, s * MB, p.T, so_q);
+          tma_store_pair<T>(&tm_dk, stream, s * MB, p.T, so_k);
+          tma_store_pair<T>(&tm_dv, stream, s * MB, p.T, so_v);
         }
         bulk_commit();
       }
@@ -833,17 +858,17 @@ __global__ void __launch_bounds__(256) ttt_linear_bwd_reduce_kernel(const Reduce
 __global__ void ttt_linear_bwd_fold_kernel(const ReduceParams p) {
   const int c = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float acc = 0.f;
-  for (int s = lane; s < p.T / CS; s += 32) acc += p.d_token_eta[s * CS + c];
+  for (int s = lane; s < p.T / p.mb; s += 32) acc += p.d_token_eta[s * p.mb + c];
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
   if (lane == 0) p.packed[(size_t)p.H * p.F * p.F + 3 * p.H * p.F + c] = acc;
 }
 
-template <typename T, int SEG>
+template <typename T, int SEG, int MB>
 static cudaError_t launch_bwd_t(const CUtensorMap* m, const void* const* io, const LinBwdParams& p, int nstreams,
                                 cudaStream_t st) {
   using SM = BwdSmem<T, SEG>;
-  auto kfn = ttt_linear_bwd_kernel<T, SEG>;
+  auto kfn = ttt_linear_bwd_kernel<T, SEG, MB>;
   cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM::DYN_BYTES);
   if (e != cudaSuccess) return e;
   // persistent grid: as many blocks as can be resident at once (they wait on one another's hand-offs), never more
@@ -870,14 +895,21 @@ static cudaError_t launch_bwd_t(const CUtensorMap* m, const void* const* io, con
   return cudaLaunchCooperativeKernel((const void*)kfn, dim3(grid), dim3(NTHREADS), args, SM::DYN_BYTES, st);
 }
 
-cudaError_t launch_linear_bwd(int dtype, int seg, const CUtensorMap* maps, const void* const* io, const LinBwdParams& p,
-                              int nstreams, cudaStream_t st) {
+template <typename T, int SEG>
+static cudaError_t launch_bwd_mb(int mb, const CUtensorMap* m, const void* const* io, const LinBwdParams& p,
+                                 int nstreams, cudaStream_t st) {
+  return mb == 8 ? launch_bwd_t<T, SEG, 8>(m, io, p, nstreams, st) : launch_bwd_t<T, SEG, 16>(m, io, p, nstreams, st);
+}
+
+// mb: tokens per mini-batch, 16 or 8 (the maps' boxes then have 8 rows)
+cudaError_t launch_linear_bwd(int dtype, int seg, int mb, const CUtensorMap* maps, const void* const* io,
+                              const LinBwdParams& p, int nstreams, cudaStream_t st) {
   if (seg == 32) {
-    if (dtype == 1) return launch_bwd_t<__nv_bfloat16, 32>(maps, io, p, nstreams, st);
-    return launch_bwd_t<float, 32>(maps, io, p, nstreams, st);
+    if (dtype == 1) return launch_bwd_mb<__nv_bfloat16, 32>(mb, maps, io, p, nstreams, st);
+    return launch_bwd_mb<float, 32>(mb, maps, io, p, nstreams, st);
   }
-  if (dtype == 1) return launch_bwd_t<__nv_bfloat16, 64>(maps, io, p, nstreams, st);
-  return launch_bwd_t<float, 64>(maps, io, p, nstreams, st);
+  if (dtype == 1) return launch_bwd_mb<__nv_bfloat16, 64>(mb, maps, io, p, nstreams, st);
+  return launch_bwd_mb<float, 64>(mb, maps, io, p, nstreams, st);
 }
 
 cudaError_t launch_linear_bwd_reduce(const ReduceParams& p, cudaStream_t st) {
@@ -886,7 +918,7 @@ cudaError_t launch_linear_bwd_reduce(const ReduceParams& p, cudaStream_t st) {
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (p.F == 32) ttt_linear_bwd_reduce_kernel<32><<<blocks, 256, 0, st>>>(p);
   else ttt_linear_bwd_reduce_kernel<64><<<blocks, 256, 0, st>>>(p);
-  if (p.packed != nullptr) ttt_linear_bwd_fold_kernel<<<1, CS * 32, 0, st>>>(p);
+  if (p.packed != nullptr) ttt_linear_bwd_fold_kernel<<<1, p.mb * 32, 0, st>>>(p);
   return cudaGetLastError();
 }
 

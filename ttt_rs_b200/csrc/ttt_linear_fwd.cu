@@ -45,7 +45,7 @@ struct FwdSmem {
   static constexpr uint32_t DYN_BYTES = TOTAL + 1024;  // slack for manual 1024-byte alignment
 };
 
-template <typename T, int SEG>
+template <typename T, int SEG, int MB>
 __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     ttt_linear_fwd_kernel(const __grid_constant__ typename PairIo<T, SEG>::Ref tm_q,
                           const __grid_constant__ typename PairIo<T, SEG>::Ref tm_k,
@@ -90,6 +90,18 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     for (int i = 0; i < FWD_NST; ++i) mbar_init(bar0 + 8 * i, GATHER ? 1 + NTHREADS : 1);
     fence_mbar_init();
   }
+  if constexpr (MB < CS) {
+    // padding rows of every tile of the ring, and the lr slots: zero once; the copies only ever write the first MB rows
+    for (uint32_t e = tid * 16; e < FWD_NST * SM::SLOT; e += NTHREADS * 16) {
+      const uint32_t in_tile = e % TF::BYTES;
+      // raw tile: 16 rows of 128 bytes (bf16) or two halves of 16 rows of 128 bytes (f32); planes are derived from it
+      const bool raw = in_tile < TF::RAW_BYTES;
+      if (!raw || (in_tile % 2048) >= MB * 128)
+        asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(base + e), "r"(0u) : "memory");
+    }
+    for (uint32_t e = tid * 4; e < FWD_NST * SM::LR_SLOT; e += NTHREADS * 4)
+      asm volatile("st.shared.b32 [%0], %1;" ::"r"(base + SM::OFF_LR + e), "r"(0u) : "memory");
+  }
   __syncthreads();
 
   // thread 0: TMA / bulk copies of one stage into its ring slot
@@ -98,25 +110,25 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     const uint32_t bar = bar0 + 8 * slot;
     const uint32_t tq = base + slot * SM::SLOT;
     if constexpr (SEG == 64) {
-      mbar_expect_tx(bar, 3 * TF::RAW_BYTES + CS * TF::ELT);
-      const int r0 = row_base + s * CS;
+      mbar_expect_tx(bar, (3 * TF::RAW_BYTES + CS * TF::ELT) * MB / CS);
+      const int r0 = row_base + s * MB;
       tma_load_tile<T>(tq, &tm_q, r0, bar);
       tma_load_tile<T>(tq + TF::BYTES, &tm_k, r0, bar);
       tma_load_tile<T>(tq + 2 * TF::BYTES, &tm_v, r0, bar);
       bulk_load_1d(base + SM::OFF_LR + slot * 64,
-                   static_cast<const uint8_t*>(p.lr) + (size_t)(row_base + s * CS) * TF::ELT, CS * TF::ELT, bar);
+                   static_cast<const uint8_t*>(p.lr) + (size_t)(row_base + s * MB) * TF::ELT, MB * TF::ELT, bar);
     } else {
-      mbar_expect_tx(bar, (GATHER ? 0 : 3 * TF::RAW_BYTES) + 2 * CS * TF::ELT);
+      mbar_expect_tx(bar, ((GATHER ? 0 : 3 * TF::RAW_BYTES) + 2 * CS * TF::ELT) * MB / CS);
       if constexpr (!GATHER) {
-        tma_load_pair<T>(tq, &tm_q, stream, s * CS, p.T, bar);
-        tma_load_pair<T>(tq + TF::BYTES, &tm_k, stream, s * CS, p.T, bar);
-        tma_load_pair<T>(tq + 2 * TF::BYTES, &tm_v, stream, s * CS, p.T, bar);
+        tma_load_pair<T>(tq, &tm_q, stream, s * MB, p.T, bar);
+        tma_load_pair<T>(tq + TF::BYTES, &tm_k, stream, s * MB, p.T, bar);
+        tma_load_pair<T>(tq + 2 * TF::BYTES, &tm_v, stream, s * MB, p.T, bar);
       }
 #pragma unroll
       for (int j = 0; j < 2; ++j)  // ttt_lr_eta is [B, H, T]: the two heads of the pair are T elements apart
         bulk_load_1d(base + SM::OFF_LR + slot * SM::LR_SLOT + j * CS * TF::ELT,
-                     static_cast<const uint8_t*>(p.lr) + ((size_t)(2 * stream + j) * p.T + s * CS) * TF::ELT,
-                     CS * TF::ELT, bar);
+                     static_cast<const uint8_t*>(p.lr) + ((size_t)(2 * stream + j) * p.T + s * MB) * TF::ELT,
+                     MB * TF::ELT, bar);
     }
   };
   // every thread, where tiles are gathered: its 16-byte chunk of the q, k, v tiles, then its arrival on the barrier
@@ -124,9 +136,9 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     if constexpr (GATHER) {
       const int slot = s % FWD_NST;
       const uint32_t tq = base + slot * SM::SLOT;
-      gather_pair_tile_bf16(tq, tm_q.ptr, stream, s * CS, p.T, tid);
-      gather_pair_tile_bf16(tq + TF::BYTES, tm_k.ptr, stream, s * CS, p.T, tid);
-      gather_pair_tile_bf16(tq + 2 * TF::BYTES, tm_v.ptr, stream, s * CS, p.T, tid);
+      gather_pair_tile_bf16<MB>(tq, tm_q.ptr, stream, s * MB, p.T, tid);
+      gather_pair_tile_bf16<MB>(tq + TF::BYTES, tm_k.ptr, stream, s * MB, p.T, tid);
+      gather_pair_tile_bf16<MB>(tq + 2 * TF::BYTES, tm_v.ptr, stream, s * MB, p.T, tid);
       cp_async_mbar_arrive_noinc(bar0 + 8 * slot);
     }
   };
@@ -147,8 +159,10 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     bias[2 * nt] = ld_as_float<T>(p.b0, (size_t)stream * HD + c);
     bias[2 * nt + 1] = ld_as_float<T>(p.b0, (size_t)stream * HD + c + 1);
   }
-  const float te_row[2] = {ld_as_float<T>(p.token_eta, g), ld_as_float<T>(p.token_eta, g + 8)};
-  const float te15 = ld_as_float<T>(p.token_eta, CS - 1);
+  // (MB = 8: rows 8..15 of every tile are padding -- zero K, Q, V, lr and token_eta, so they neither move the state
+  // nor reach the output, and nothing of them is stored)
+  const float te_row[2] = {ld_as_float<T>(p.token_eta, g), MB == CS ? ld_as_float<T>(p.token_eta, g + 8) : 0.f};
+  const float te15 = ld_as_float<T>(p.token_eta, MB - 1);
   // The state is carried as What = W / wscale with wscale = -te15, so that the update W -= te15 Gp^T K becomes
   // What += Gp^T K, accumulated by the tensor cores straight into the registers.  (te15 == 0: W never changes.)
   const bool w_moves = (te15 != 0.f);
@@ -359,19 +373,23 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     ln_row_stats<TWO_PASS, SEG>(zb, xch, xsel, L, p.eps, mean, rstd, fl2);
     if constexpr (SEG == 64) {
       if (save && L.warp == 0 && t == 0) {
-        float4* sp = p.stats + ((size_t)row_base + (size_t)s * CS) * 2;
+        float4* sp = p.stats + ((size_t)row_base + (size_t)s * MB) * 2;
         sp[2 * g] = st1[0];
         sp[2 * g + 1] = make_float4(mean[0], rstd[0], 0.f, 0.f);
-        sp[2 * (g + 8)] = st1[1];
-        sp[2 * (g + 8) + 1] = make_float4(mean[1], rstd[1], 0.f, 0.f);
+        if constexpr (MB == CS) {
+          sp[2 * (g + 8)] = st1[1];
+          sp[2 * (g + 8) + 1] = make_float4(mean[1], rstd[1], 0.f, 0.f);
+        }
       }
     } else if (save && (L.warp & 1) == 0 && t == 0) {
       // two float4 per (token, head): record index 2 * token + head of the pair
-      float4* sp = p.stats + ((size_t)row_base + (size_t)s * CS) * 4;
+      float4* sp = p.stats + ((size_t)row_base + (size_t)s * MB) * 4;
       sp[2 * (2 * g + hsel)] = st1[0];
       sp[2 * (2 * g + hsel) + 1] = make_float4(mean[0], rstd[0], 0.f, 0.f);
-      sp[2 * (2 * (g + 8) + hsel)] = st1[1];
-      sp[2 * (2 * (g + 8) + hsel) + 1] = make_float4(mean[1], rstd[1], 0.f, 0.f);
+      if constexpr (MB == CS) {
+        sp[2 * (2 * (g + 8) + hsel)] = st1[1];
+        sp[2 * (2 * (g + 8) + hsel) + 1] = make_float4(mean[1], rstd[1], 0.f, 0.f);
+      }
     }
     const uint32_t so = base + SM::OFF_OUT + (s & 1) * TF::RAW_BYTES;
 #pragma unroll
@@ -385,11 +403,11 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
       }
     fence_proxy_async_smem();
     __syncthreads();
-    if constexpr (GATHER) scatter_pair_tile_bf16(tm_o.ptr, stream, s * CS, p.T, so, tid);
+    if constexpr (GATHER) scatter_pair_tile_bf16<MB>(tm_o.ptr, stream, s * MB, p.T, so, tid);
     if (tid == 0) {
-      if constexpr (SEG == 64) tma_store_tile<T>(&tm_o, row_base + s * CS, so);
-      else if constexpr (!GATHER) tma_store_pair<T>(&tm_o, stream, s * CS, p.T, so);
-      if (save) tma_store_tile<T>(&tm_g, row_base + s * CS, sg);  // saved tiles are kept in the packed 64-wide form
+      if constexpr (SEG == 64) tma_store_tile<T>(&tm_o, row_base + s * MB, so);
+      else if constexpr (!GATHER) tma_store_pair<T>(&tm_o, stream, s * MB, p.T, so);
+      if (save) tma_store_tile<T>(&tm_g, row_base + s * MB, sg);  // saved tiles are kept in the packed 64-wide form
       bulk_commit();
       bulk_wait_read<1>();
     }
@@ -438,11 +456,11 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
   if constexpr (GATHER) cp_async_wait_all();  // (a stage that gave up may leave gathers in flight)
 }
 
-template <typename T, int SEG>
+template <typename T, int SEG, int MB>
 static cudaError_t launch_fwd_t(const CUtensorMap* m, const void* const* io, const LinFwdParams& p, int nstreams,
                                 cudaStream_t st) {
   using SM = FwdSmem<T, SEG>;
-  auto kfn = ttt_linear_fwd_kernel<T, SEG>;
+  auto kfn = ttt_linear_fwd_kernel<T, SEG, MB>;
   cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM::DYN_BYTES);
   if (e != cudaSuccess) return e;
   if constexpr (PairIo<T, SEG>::GATHER) {
@@ -455,14 +473,21 @@ static cudaError_t launch_fwd_t(const CUtensorMap* m, const void* const* io, con
   return cudaGetLastError();
 }
 
-cudaError_t launch_linear_fwd(int dtype, int seg, const CUtensorMap* maps, const void* const* io, const LinFwdParams& p,
-                              int nstreams, cudaStream_t st) {
+template <typename T, int SEG>
+static cudaError_t launch_fwd_mb(int mb, const CUtensorMap* m, const void* const* io, const LinFwdParams& p,
+                                 int nstreams, cudaStream_t st) {
+  return mb == 8 ? launch_fwd_t<T, SEG, 8>(m, io, p, nstreams, st) : launch_fwd_t<T, SEG, 16>(m, io, p, nstreams, st);
+}
+
+// mb: tokens per mini-batch, 16 or 8 (the maps' boxes then have 8 rows)
+cudaError_t launch_linear_fwd(int dtype, int seg, int mb, const CUtensorMap* maps, const void* const* io,
+                              const LinFwdParams& p, int nstreams, cudaStream_t st) {
   if (seg == 32) {
-    if (dtype == 1) return launch_fwd_t<__nv_bfloat16, 32>(maps, io, p, nstreams, st);
-    return launch_fwd_t<float, 32>(maps, io, p, nstreams, st);
+    if (dtype == 1) return launch_fwd_mb<__nv_bfloat16, 32>(mb, maps, io, p, nstreams, st);
+    return launch_fwd_mb<float, 32>(mb, maps, io, p, nstreams, st);
   }
-  if (dtype == 1) return launch_fwd_t<__nv_bfloat16, 64>(maps, io, p, nstreams, st);
-  return launch_fwd_t<float, 64>(maps, io, p, nstreams, st);
+  if (dtype == 1) return launch_fwd_mb<__nv_bfloat16, 64>(mb, maps, io, p, nstreams, st);
+  return launch_fwd_mb<float, 64>(mb, maps, io, p, nstreams, st);
 }
 
 }  // namespace ttt

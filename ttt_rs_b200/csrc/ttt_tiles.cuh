@@ -136,14 +136,18 @@ struct PairIo {
   static constexpr bool GATHER = (SEG == 32 && sizeof(T) == 2);
   using Ref = std::conditional_t<GATHER, RawTensor, CUtensorMap>;
 };
+template <int ROWS = 16>  // rows of the tile that exist (a mini-batch of 8 fills the first 8)
 __device__ __forceinline__ void gather_pair_tile_bf16(uint32_t tile, const void* base, int pair, int t0, int seq, int tid) {
   const int row = tid >> 3, c = tid & 7;  // chunk c of the 128-byte row: head c >> 2, features 8 (c & 3) ..
+  if (ROWS < 16 && row >= ROWS) return;
   const uint8_t* src = static_cast<const uint8_t*>(base) +
                        (((size_t)(2 * pair + (c >> 2)) * seq + t0 + row) * 32 + (c & 3) * 8) * 2;
   cp_async_16(tile + row * 128 + ((c ^ (row & 7)) << 4), src);
 }
+template <int ROWS = 16>
 __device__ __forceinline__ void scatter_pair_tile_bf16(void* base, int pair, int t0, int seq, uint32_t tile, int tid) {
   const int row = tid >> 3, c = tid & 7;
+  if (ROWS < 16 && row >= ROWS) return;
   uint4 v;
   asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
