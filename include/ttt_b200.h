@@ -60,7 +60,7 @@ typedef struct ttt_dims {
   int32_t heads;               /* H */
   int32_t seq_len;             /* T, multiple of mini_batch */
   int32_t head_dim;            /* F: 64; TTT-Linear forward/backward also take 32 with an even number of heads */
-  int32_t mini_batch;          /* CS (16) */
+  int32_t mini_batch;          /* CS: 16; TTT-Linear forward/backward also take 8 */
   int32_t checkpoint_interval; /* K >= 1, in stages */
   float epsilon;               /* LayerNorm epsilon */
   int32_t dtype;               /* enum ttt_dtype */
@@ -101,6 +101,7 @@ size_t ttt_linear_bias_ckpt_bytes(const ttt_dims* d);
  *   weight          T [B,H,F,F]   initial state W (per batch element), W[k][n]: z = x @ W
  *   bias            T [B,H,F]
  *   token_eta       T [T]         only entries [0, CS) are read, in every stage (forward/kernel.rs:152-165)
+ *                                 (CS = d->mini_batch)
  *   ttt_lr_eta      T [B,H,T]
  *   ln_weight/bias  T [H,F]
  *   output          T [B,H,T,F]   (out)
