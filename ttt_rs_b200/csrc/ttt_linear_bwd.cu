@@ -605,7 +605,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
         }
       float4 o0, o1;
       int f2_ = 0;
-      xch_rows<SEG>(&xch[xsel], L, make_float4(f2hsum(p1[0]), f2hsum(p2[0]), f2hsum(pdl[0]), f2hsum(prt[0])),
+      xch_rows<SEG, false>(&xch[xsel], L, make_float4(f2hsum(p1[0]), f2hsum(p2[0]), f2hsum(pdl[0]), f2hsum(prt[0])),
                     make_float4(f2hsum(p1[1]), f2hsum(p2[1]), f2hsum(pdl[1]), f2hsum(prt[1])), o0, o1, f2_);
       xsel ^= 1;
       s1t[0] = o0.x * INV_F; s2t[0] = o0.y * INV_F;
@@ -647,7 +647,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
         }
       float2 a0, a1;
       int f2_ = 0;
-      xch_rows2<SEG>(&xch[xsel], L, f2hsum(pd[0]), f2hsum(ps[0]), f2hsum(pd[1]), f2hsum(ps[1]), a0, a1, f2_);
+      xch_rows2<SEG, false>(&xch[xsel], L, f2hsum(pd[0]), f2hsum(ps[0]), f2hsum(pd[1]), f2hsum(ps[1]), a0, a1, f2_);
       xsel ^= 1;
       const float D[2] = {a0.x * INV_F, a1.x * INV_F}, S[2] = {a0.y * INV_F, a1.y * INV_F};
 #pragma unroll

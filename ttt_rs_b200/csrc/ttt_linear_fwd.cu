@@ -296,7 +296,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
       ln_l2_pieces<T>(z1p, mean, rstd, gam, bet, tk, tv, L, xh, gy, gx, sa, sb);
       float2 a0, a1;
       int f2_ = 0;
-      xch_rows2<SEG>(&xch[xsel], L, sa[0], sb[0], sa[1], sb[1], a0, a1, f2_);
+      xch_rows2<SEG, false>(&xch[xsel], L, sa[0], sb[0], sa[1], sb[1], a0, a1, f2_);
       xsel ^= 1;
       const float A[2] = {a0.x * INV_F, a1.x * INV_F}, Bv[2] = {a0.y * INV_F, a1.y * INV_F};
       const float rs[2] = {rstd[0] * lr_row[0], rstd[1] * lr_row[1]};
@@ -370,7 +370,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? 3 : 1))
     int fl2 = 0;
     F2 zb[2][2];
     slab_pairs(zq, zb);
-    ln_row_stats<TWO_PASS, SEG>(zb, xch, xsel, L, p.eps, mean, rstd, fl2);
+    ln_row_stats<TWO_PASS, SEG, false>(zb, xch, xsel, L, p.eps, mean, rstd, fl2);
     if constexpr (SEG == 64) {
       if (save && L.warp == 0 && t == 0) {
         float4* sp = p.stats + ((size_t)row_base + (size_t)s * MB) * 2;

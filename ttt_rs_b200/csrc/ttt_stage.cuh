@@ -29,8 +29,9 @@ struct __align__(16) Xch4 {
 
 // Every thread contributes its two rows (g, g+8); returns the sums over the row's SEG columns: all four warps
 // (SEG = 64) or the warp pair that holds this thread's 32-wide head (SEG = 32: warps 0,1 / 2,3).
-// `flag` is OR-reduced over the CTA by the same barrier (used to spread a timed-out wait).
-template <int SEG = 64>
+// `flag` is OR-reduced over the CTA by the same barrier (used to spread a timed-out wait); with FLAG = false the
+// barrier is a plain one and `flag` is left alone (a barrier that reduces costs more than one that does not).
+template <int SEG = 64, bool FLAG = true>
 __device__ __forceinline__ void xch_rows(Xch4* xb, const Lane& L, const float4 a0, const float4 a1, float4& o0,
                                          float4& o1, int& flag) {
   float4 p0, p1;
@@ -40,7 +41,8 @@ __device__ __forceinline__ void xch_rows(Xch4* xb, const Lane& L, const float4 a
     xb->v[L.g][L.warp] = p0;
     xb->v[L.g + 8][L.warp] = p1;
   }
-  flag = __syncthreads_or(flag);
+  if constexpr (FLAG) flag = __syncthreads_or(flag);
+  else __syncthreads();
   const float4* r0 = &xb->v[L.g][0];
   const float4* r1 = &xb->v[L.g + 8][0];
   if constexpr (SEG == 64) {
@@ -64,7 +66,7 @@ __device__ __forceinline__ void xch_rows(Xch4* xb, const Lane& L, const float4 a
   }
 }
 // Two-value variant (same buffer type, half the shuffles).
-template <int SEG = 64>
+template <int SEG = 64, bool FLAG = true>
 __device__ __forceinline__ void xch_rows2(Xch4* xb, const Lane& L, float a0x, float a0y, float a1x, float a1y,
                                           float2& o0, float2& o1, int& flag) {
   a0x = quad_sum(a0x); a0y = quad_sum(a0y); a1x = quad_sum(a1x); a1y = quad_sum(a1y);
@@ -74,7 +76,8 @@ __device__ __forceinline__ void xch_rows2(Xch4* xb, const Lane& L, float a0x, fl
     base[L.g * 6 + L.warp] = make_float2(a0x, a0y);
     base[(L.g + 8) * 6 + L.warp] = make_float2(a1x, a1y);
   }
-  flag = __syncthreads_or(flag);
+  if constexpr (FLAG) flag = __syncthreads_or(flag);
+  else __syncthreads();
   const float4 p = *reinterpret_cast<const float4*>(&base[L.g * 6]);
   const float4 q = *reinterpret_cast<const float4*>(&base[L.g * 6 + 2]);
   const float4 p2 = *reinterpret_cast<const float4*>(&base[(L.g + 8) * 6]);
@@ -93,7 +96,7 @@ __device__ __forceinline__ void xch_rows2(Xch4* xb, const Lane& L, float a0x, fl
 // LayerNorm row statistics of a slab: mean and 1/sqrt(var + eps) for rows g and g+8.
 // bf16 I/O uses one exchange (sum, sum of squares); float32 I/O uses the two-pass variance of the reference.
 // Slabs here are column pairs: F2 z[nt][r] = columns (nb + 8nt + 2t, +1) of row g + 8r.
-template <bool TWO_PASS, int SEG = 64>
+template <bool TWO_PASS, int SEG = 64, bool FLAG = true>
 __device__ __forceinline__ void ln_row_stats(const F2 (&z)[2][2], Xch4* xch, int& xsel, const Lane& L, float eps,
                                              float (&mean)[2], float (&rstd)[2], int& flag) {
   constexpr float INV = 1.f / SEG;  // features per LayerNorm row
@@ -104,7 +107,7 @@ __device__ __forceinline__ void ln_row_stats(const F2 (&z)[2][2], Xch4* xch, int
     if constexpr (!TWO_PASS) s2[r] = f2hsum(f2fma(z[0][r], z[0][r], f2mul(z[1][r], z[1][r])));
   }
   float2 a0, a1;
-  xch_rows2<SEG>(&xch[xsel], L, s1[0], s2[0], s1[1], s2[1], a0, a1, flag);
+  xch_rows2<SEG, FLAG>(&xch[xsel], L, s1[0], s2[0], s1[1], s2[1], a0, a1, flag);
   xsel ^= 1;
   mean[0] = a0.x * INV;
   mean[1] = a1.x * INV;
@@ -119,7 +122,7 @@ __device__ __forceinline__ void ln_row_stats(const F2 (&z)[2][2], Xch4* xch, int
       q2[r] = f2hsum(f2fma(d0, d0, f2mul(d1, d1)));
     }
     int f2_ = 0;
-    xch_rows2<SEG>(&xch[xsel], L, q2[0], 0.f, q2[1], 0.f, a0, a1, f2_);
+    xch_rows2<SEG, false>(&xch[xsel], L, q2[0], 0.f, q2[1], 0.f, a0, a1, f2_);
     xsel ^= 1;
     rstd[0] = 1.0f / sqrtf(a0.x * INV + eps);
     rstd[1] = 1.0f / sqrtf(a1.x * INV + eps);
