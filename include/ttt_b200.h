@@ -257,7 +257,9 @@ int ttt_layer_epilogue(const ttt_dims* d, const void* inner_out, const void* gat
  * one output feature per row (pitch ldb) -- so q/k/v/g/lr weights stacked by rows give all projections of the token
  * in one call, and o_proj is the same call on the epilogue's output.  Replaces the `Linear` forwards of
  * rust/layer/src/ttt.rs:152-227,289-299 (Burn matmul).  All pointers 16-byte aligned, pitches multiples of 8
- * elements; any m, n, k > 0 (edges are clipped / zero-filled by the tensor maps).  `status`: optional 4 words. */
+ * elements; any m, n, k > 0 (edges are clipped / zero-filled by the tensor maps).  `status`: optional 4 words.
+ * Products of 512 rows and more run as pairs of thread blocks on 256 x 256 tiles (tcgen05 cta_group::2), smaller ones
+ * as single blocks on 128 x 256 tiles; TTT_GEMM_PAIR=0 / 1 in the environment forces one form (for measurements). */
 int ttt_gemm_bf16_tn(int64_t m, int64_t n, int64_t k, const void* a, int64_t lda, const void* b, int64_t ldb, void* c,
                      int64_t ldc, void* status, void* stream);
 
