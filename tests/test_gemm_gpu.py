@@ -20,6 +20,7 @@ pytestmark = pytest.mark.gpu
     (640, 520, 256),     # CTA-pair form (M >= 512) with an odd number of 128-row blocks: the second CTA of the last
                          # pair has no rows; last tile column 8 wide
     (1152, 288, 64),     # pair form, one k-block, last tile column 32 wide (16 columns from each CTA of the pair)
+    (1024, 72, 104),     # pair form with ragged N and a K tail that the tensor maps fill with zeros
 ])
 def test_gemm_matches_float64_product(M, N, K):
     import ttt_rs_b200 as tb
