@@ -99,3 +99,37 @@ def test_backward_packs_outer_grads_and_is_deterministic(F, dtype):
         # checked exactly in the float32 case above
         err = (p1[o:o + MB].double().cpu() - want.sum(0)).abs().max().item()
         assert err <= 2e-2 * want.abs().max().item(), err
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_outer_layer_with_8_token_mini_batches(dtype):
+    """The whole layer (projections, rotary positions modulo 8, inner loop on 8x64 tiles, post norm, o_proj) against
+    the layer restatement run with mini_batch = 8."""
+    import ttt_rs_b200 as tb
+    from oracle import ttt_layer_oracle as LO
+    from test_layer_gpu import _layer_from_params, _random_case
+    dev = torch.device("cuda:0")
+    B, T, H = 2, 128, 3
+    x, p = _random_case(B, T, H, 23, False, True, dtype)
+    p["token_idx"] = p["token_idx"][:MB].clone()
+    p["learnable_token_idx"] = p["learnable_token_idx"][:MB].clone()
+    cfg = tb.TTTLayerConfig(hidden_size=H * 64, num_heads=H, share_qk=False, use_gate=True, mini_batch_size=MB)
+    m = tb.TTT(cfg, device=dev, dtype=dtype)
+    inner = tb.new_inner(cfg, device=dev, dtype=dtype)
+    # same parameter hand-over as the 16-token layer tests
+    m16, inner16 = _layer_from_params(tb, {**p, "learnable_token_idx": torch.zeros(16).double()}, False, True, dtype, dev, H)
+    with torch.no_grad():
+        for name in ("q_proj", "k_proj", "v_proj", "o_proj", "g_proj", "learnable_ttt_lr_weight", "learnable_ttt_lr_bias",
+                     "post_norm_weight", "post_norm_bias"):
+            getattr(m, name).copy_(getattr(m16, name))
+        m.learnable_token_idx.copy_(p["learnable_token_idx"].to(dtype))
+        for name in ("weight_init", "bias_init", "ln_weight", "ln_bias"):
+            getattr(inner.inner, name).copy_(getattr(inner16.inner, name))
+    m.invalidate_fused_weight()
+    with torch.no_grad():
+        state = inner.init_state(B)
+        y = m(x.to(dtype).to(dev), inner, state)
+    tb.check_status()
+    want, _ = LO.ttt_layer_forward(x, p, num_heads=H, use_gate=True, mini_batch=MB)
+    assert_close(y, want, RTOL[dtype], "layer output (8-token mini-batches)",
+                 max_bad_frac=2e-4 if dtype == torch.bfloat16 else 0.0)
