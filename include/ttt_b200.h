@@ -225,8 +225,9 @@ int ttt_linear_forward_partial(const ttt_dims* d, const void* xq, const void* xk
  * `conv_qk` :228-246, rotary embedding with the permute/undo-permute convention, rust/core/src/util.rs:284-392),
  * `get_lr` :205-227, and in `forward` :285-296 the permute back, `post_norm` and the optional gelu(tanh) gate.  The
  * projections themselves (q/k/v/g/o_proj, the per-head lr weights) stay ordinary GEMMs in the caller.
- * Only `batch`, `heads`, `seq_len`, `head_dim` (64), `mini_batch` (rotary wrap) and `dtype` of `d` are read; seq_len
- * need not be a multiple of mini_batch here.
+ * Only `batch`, `heads`, `seq_len`, `head_dim` (64 or 32; any number of heads, heads*head_dim <= 2048 for the
+ * epilogue), `mini_batch` (rotary wrap) and `dtype` of `d` are read; seq_len need not be a multiple of mini_batch here.
+ * The gradient entry points further down take the same shapes.
  */
 
 /* Projection outputs -> inner-loop operands.

@@ -172,7 +172,7 @@ def test_partial_and_layer_entry_points_validate_their_arguments(lib):
     assert pro(conv=(fake, fake, fake, None), kc=4) == _lib.TTT_ERR_NULL
     assert pro(conv=(fake, fake, fake, fake), kc=5) == _lib.TTT_ERR_UNSUPPORTED
     assert pro(q=C.c_void_p(0x1004)) == _lib.TTT_ERR_ALIGN
-    assert lib.ttt_layer_prologue(C.byref(_dims(head_dim=32)), *([fake] * 3), 128, fake, 8, *([None] * 5), 0, 0, 1,
+    assert lib.ttt_layer_prologue(C.byref(_dims(head_dim=48)), *([fake] * 3), 128, fake, 8, *([None] * 5), 0, 0, 1,
                                   10000.0, 1.0, fake, fake, fake, fake, None) == _lib.TTT_ERR_UNSUPPORTED
 
     # layer epilogue

@@ -58,15 +58,15 @@ def test_layer_forward_float32_matches_reference_golden(golden_dir, tag, share_q
     assert_close(state.weight, want_state["weight"], 2e-4, f"{tag}: final inner weight")
 
 
-def _random_case(B, T, H, seed, share_qk, use_gate, dtype):
+def _random_case(B, T, H, seed, share_qk, use_gate, dtype, F=64):
     g = torch.Generator().manual_seed(seed)
-    C = H * 64
+    C = H * F
     r = lambda *s, sc=1.0: (torch.randn(*s, generator=g) * sc).to(dtype).double()  # noqa: E731
     p = {"q_proj": r(C, C, sc=C ** -0.5), "v_proj": r(C, C, sc=C ** -0.5), "o_proj": r(C, C, sc=C ** -0.5),
          "lr_weight": r(H, C, 1, sc=0.02), "lr_bias": r(H, 1, sc=0.1), "token_idx": 1.0 / torch.arange(1, 17).double(),
          "learnable_token_idx": r(16, sc=0.05), "post_norm_weight": 1 + r(C, sc=0.1), "post_norm_bias": r(C, sc=0.1),
-         "W1": r(H, 64, 64, sc=0.02), "b1": r(H, 1, 64, sc=0.05), "ttt_norm_weight": 1 + r(H, 64, sc=0.1),
-         "ttt_norm_bias": r(H, 64, sc=0.1)}
+         "W1": r(H, F, F, sc=0.02), "b1": r(H, 1, F, sc=0.05), "ttt_norm_weight": 1 + r(H, F, sc=0.1),
+         "ttt_norm_bias": r(H, F, sc=0.1)}
     if share_qk:
         p.update(conv_q_weight=r(C, 1, 4, sc=0.5), conv_q_bias=r(C, sc=0.1), conv_k_weight=r(C, 1, 4, sc=0.5),
                  conv_k_bias=r(C, sc=0.1))
@@ -80,16 +80,17 @@ def _random_case(B, T, H, seed, share_qk, use_gate, dtype):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", (torch.float32, torch.bfloat16))
+@pytest.mark.parametrize("F,H", ((64, 3), (32, 3), (32, 12)))
 @pytest.mark.parametrize("share_qk,use_gate,pos,start", ((False, False, "rope", 0), (True, True, "rope", 21),
                                                          (False, True, "rope_global", 5), (True, False, "none", 0)))
-def test_prologue_and_epilogue_kernels_match_the_restatement(dtype, share_qk, use_gate, pos, start):
+def test_prologue_and_epilogue_kernels_match_the_restatement(dtype, F, H, share_qk, use_gate, pos, start):
     """Kernel-level parity on ragged sizes (T not a multiple of the mini-batch or of the kernel's token chunk,
-    heads not a multiple of 4), fed with exactly the projection values the kernels see."""
+    heads not a multiple of the 4 or 8 a warp takes), fed with exactly the projection values the kernels see."""
     import ttt_rs_b200 as tb
     dev = torch.device("cuda:0")
-    B, T, H = 3, 83, 3
-    C = H * 64
-    x, p = _random_case(B, T, H, 11, share_qk, use_gate, dtype)
+    B, T = 3, 83
+    C = H * F
+    x, p = _random_case(B, T, H, 11, share_qk, use_gate, dtype, F)
     cfg = tb.TTTLayerConfig(hidden_size=C, num_heads=H, share_qk=share_qk, use_gate=use_gate, pos_encoding=pos)
     # projection output as the layer lays it out: q | (k) | v | (g) | lr, rounded to the I/O type
     blocks = [x @ p["q_proj"].T] + ([] if share_qk else [x @ p["k_proj"].T]) + [x @ p["v_proj"].T]
@@ -108,7 +109,7 @@ def test_prologue_and_epilogue_kernels_match_the_restatement(dtype, share_qk, us
     torch.cuda.synchronize()
     # the restatement on the same rounded projection values
     pd = proj.double()
-    heads = lambda t: t.reshape(B, T, H, 64).permute(0, 2, 1, 3)  # noqa: E731
+    heads = lambda t: t.reshape(B, T, H, F).permute(0, 2, 1, 3)  # noqa: E731
     qs, ks, vs = pd[..., :C], pd[..., cols["k"]:cols["k"] + C], pd[..., cols["v"]:cols["v"] + C]
     if share_qk:
         ks = LO.causal_depthwise_conv(qs, p["conv_k_weight"], p["conv_k_bias"])
@@ -118,7 +119,7 @@ def test_prologue_and_epilogue_kernels_match_the_restatement(dtype, share_qk, us
         posv = start + torch.arange(T)
         posv = posv % 16 if pos == "rope" else posv
         wq, wk = LO.rope_pairs(wq, posv, 10000.0), LO.rope_pairs(wk, posv, 10000.0)
-    wlr = torch.sigmoid(pd[..., cols["lr"]:cols["lr"] + H].permute(0, 2, 1) + p["lr_bias"].reshape(1, H, 1)) / 64
+    wlr = torch.sigmoid(pd[..., cols["lr"]:cols["lr"] + H].permute(0, 2, 1) + p["lr_bias"].reshape(1, H, 1)) / F
     rt = RTOL[dtype]
     assert_close(xq, wq, rt, "xq"); assert_close(xk, wk, rt, "xk"); assert_close(xv, wv, rt, "xv")
     assert_close(lr, wlr, rt, "ttt_lr_eta")
@@ -126,7 +127,7 @@ def test_prologue_and_epilogue_kernels_match_the_restatement(dtype, share_qk, us
         assert torch.equal(xv.cpu(), heads(proj[..., cols["v"]:cols["v"] + C]).contiguous()), "xv must be a pure copy"
 
     # epilogue
-    inner_out = (torch.randn(B, H, T, 64, generator=torch.Generator().manual_seed(3)) * 2 + 0.3).to(dtype)
+    inner_out = (torch.randn(B, H, T, F, generator=torch.Generator().manual_seed(3)) * 2 + 0.3).to(dtype)
     gate = gate_ld = None
     if use_gate:
         gate, gate_ld = proj.to(dev).reshape(B * T, -1)[:, cols["g"]:], proj.shape[-1]
@@ -142,11 +143,14 @@ def test_prologue_and_epilogue_kernels_match_the_restatement(dtype, share_qk, us
 
 
 @pytest.mark.gpu
-def test_layer_forward_bfloat16_at_a_wider_shape():
+@pytest.mark.parametrize("F,H", ((64, 12), (32, 24)))
+def test_layer_forward_bfloat16_at_a_wider_shape(F, H):
+    """768 hidden features as 12 heads of 64 (one launch for projections + prologue) and as 24 heads of 32 (the
+    reference's `125m-h32` split: the projection GEMM, then the prologue kernel; the inner loop packs head pairs)."""
     import ttt_rs_b200 as tb
     dev = torch.device("cuda:0")
-    B, T, H = 2, 128, 12
-    x, p = _random_case(B, T, H, 5, False, True, torch.bfloat16)
+    B, T = 2, 128
+    x, p = _random_case(B, T, H, 5, False, True, torch.bfloat16, F)
     m, inner = _layer_from_params(tb, p, False, True, torch.bfloat16, dev, H)
     with torch.no_grad():
         state = inner.init_state(B)
@@ -157,17 +161,18 @@ def test_layer_forward_bfloat16_at_a_wider_shape():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("F,H", ((64, 3), (32, 4)))
 @pytest.mark.parametrize("use_gate,share_qk", ((False, False), (True, False), (True, True)))
-def test_layer_training_gradients_match_autograd_of_the_restatement(use_gate, share_qk):
+def test_layer_training_gradients_match_autograd_of_the_restatement(use_gate, share_qk, F, H):
     """Whole-layer backward (projection GEMM gradients by torch, every other step by this repo's gradient kernels)
     against float64 autograd through the CPU restatement."""
     import ttt_rs_b200 as tb
     dev = torch.device("cuda:0")
-    B, T, H = 2, 80 if share_qk else 48, 3  # 80 tokens: two chunks of the convolution gradient kernel
-    x, p = _random_case(B, T, H, 31, share_qk, use_gate, torch.float32)
+    B, T = 2, 80 if share_qk else 48  # 80 tokens: two chunks of the convolution gradient kernel
+    x, p = _random_case(B, T, H, 31, share_qk, use_gate, torch.float32, F)
     m, inner = _layer_from_params(tb, p, share_qk, use_gate, torch.float32, dev, H)
     xg = x.float().to(dev).requires_grad_(True)
-    gy = torch.randn(B, T, H * 64, generator=torch.Generator().manual_seed(2)).double()
+    gy = torch.randn(B, T, H * F, generator=torch.Generator().manual_seed(2)).double()
     state = inner.init_state(B)
     y = m(xg, inner, state)
     y.backward(gy.float().to(dev))

@@ -668,7 +668,8 @@ int check_layer_dims(const ttt_dims* d) {
   if (d == nullptr) return fail(TTT_ERR_NULL, "dims is null");
   if (d->batch <= 0 || d->heads <= 0 || d->seq_len <= 0) return fail(TTT_ERR_SHAPE, "batch, heads and seq_len must be positive");
   if (d->dtype != TTT_F32 && d->dtype != TTT_BF16) return fail(TTT_ERR_UNSUPPORTED, "unknown dtype %d", d->dtype);
-  if (d->head_dim != 64) return fail(TTT_ERR_UNSUPPORTED, "Unsupported head_dim=%d (supported: 64)", d->head_dim);
+  if (d->head_dim != 64 && d->head_dim != 32)
+    return fail(TTT_ERR_UNSUPPORTED, "Unsupported head_dim=%d (supported: 64, 32)", d->head_dim);
   if ((int64_t)d->batch * d->heads * d->seq_len >= (int64_t)1 << 31)
     return fail(TTT_ERR_SHAPE, "batch*heads*seq_len must be below 2^31");
   return TTT_OK;
@@ -693,9 +694,9 @@ extern "C" int ttt_layer_prologue(const ttt_dims* d, const void* q_src, const vo
     return fail(TTT_ERR_UNSUPPORTED, "wrapped rotary positions need 1 <= mini_batch <= 64 (got %d)", d->mini_batch);
   if (rope_mode != 0 && !(rope_theta > 0.f)) return fail(TTT_ERR_SHAPE, "rope_theta must be positive");
   if (start_idx < 0) return fail(TTT_ERR_SHAPE, "start_idx must be >= 0");
-  const int64_t cols = (int64_t)d->heads * 64;
+  const int64_t cols = (int64_t)d->heads * d->head_dim;
   if (src_ld < cols || (src_ld & 7) != 0)
-    return fail(TTT_ERR_SHAPE, "src_ld (%lld) must be >= heads*64 and a multiple of 8", (long long)src_ld);
+    return fail(TTT_ERR_SHAPE, "src_ld (%lld) must be >= heads*head_dim and a multiple of 8", (long long)src_ld);
   if (lr_ld < d->heads) return fail(TTT_ERR_SHAPE, "lr_ld (%lld) must be >= heads", (long long)lr_ld);
   const NamedPtr ptrs[] = {{"q_src", q_src}, {"k_src", conv ? q_src : k_src}, {"v_src", v_src}, {"xq", xq},
                            {"xk", xk},       {"xv", xv}};
@@ -727,7 +728,7 @@ extern "C" int ttt_layer_prologue(const ttt_dims* d, const void* q_src, const vo
   p.rope_mode = rope_mode;
   p.rope_theta = rope_mode != 0 ? rope_theta : 1.f;
   p.base_lr = base_lr;
-  cudaError_t e = ttt::launch_layer_prologue(d->dtype, p, static_cast<cudaStream_t>(stream));
+  cudaError_t e = ttt::launch_layer_prologue(d->dtype, d->head_dim, p, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "layer prologue launch failed: %s", cudaGetErrorString(e));
   return TTT_OK;
 }
@@ -737,15 +738,16 @@ extern "C" int ttt_layer_epilogue(const ttt_dims* d, const void* inner_out, cons
                                   void* stream) {
   int rc = check_layer_dims(d);
   if (rc != TTT_OK) return rc;
-  if (d->heads > 32) return fail(TTT_ERR_UNSUPPORTED, "heads=%d (supported: up to 32)", d->heads);
+  if (d->heads * d->head_dim > 2048)
+    return fail(TTT_ERR_UNSUPPORTED, "heads*head_dim=%d (supported: up to 2048)", d->heads * d->head_dim);
   if (!(eps >= 0.f)) return fail(TTT_ERR_SHAPE, "eps must be >= 0");
   const NamedPtr ptrs[] = {{"inner_out", inner_out}, {"y", y}};
   rc = check_ptrs(ptrs, 2);
   if (rc != TTT_OK) return rc;
   if (post_norm_weight == nullptr || post_norm_bias == nullptr) return fail(TTT_ERR_NULL, "post_norm_weight / post_norm_bias is null");
   if (gate != nullptr) {
-    if (gate_ld < (int64_t)d->heads * 64 || (gate_ld & 3) != 0)
-      return fail(TTT_ERR_SHAPE, "gate_ld (%lld) must be >= heads*64 and a multiple of 4", (long long)gate_ld);
+    if (gate_ld < (int64_t)d->heads * d->head_dim || (gate_ld & 3) != 0)
+      return fail(TTT_ERR_SHAPE, "gate_ld (%lld) must be >= heads*head_dim and a multiple of 4", (long long)gate_ld);
     if ((reinterpret_cast<uintptr_t>(gate) & 7u) != 0) return fail(TTT_ERR_ALIGN, "gate is not 8-byte aligned");
   }
   ttt::LayerEpiParams p;
@@ -759,7 +761,7 @@ extern "C" int ttt_layer_epilogue(const ttt_dims* d, const void* inner_out, cons
   p.H = d->heads;
   p.T = d->seq_len;
   p.eps = eps;
-  cudaError_t e = ttt::launch_layer_epilogue(d->dtype, p, static_cast<cudaStream_t>(stream));
+  cudaError_t e = ttt::launch_layer_epilogue(d->dtype, d->head_dim, p, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "layer epilogue launch failed: %s", cudaGetErrorString(e));
   return TTT_OK;
 }
@@ -816,8 +818,8 @@ extern "C" int ttt_layer_prologue_backward(const ttt_dims* d, const void* grad_x
   if (rope_mode != 0 && !(rope_theta > 0.f)) return fail(TTT_ERR_SHAPE, "rope_theta must be positive");
   if (start_idx < 0) return fail(TTT_ERR_SHAPE, "start_idx must be >= 0");
   if (!(base_lr != 0.f)) return fail(TTT_ERR_SHAPE, "base_lr must be non-zero");
-  if (dst_ld < (int64_t)d->heads * 64 || (dst_ld & 7) != 0)
-    return fail(TTT_ERR_SHAPE, "dst_ld (%lld) must be >= heads*64 and a multiple of 8", (long long)dst_ld);
+  if (dst_ld < (int64_t)d->heads * d->head_dim || (dst_ld & 7) != 0)
+    return fail(TTT_ERR_SHAPE, "dst_ld (%lld) must be >= heads*head_dim and a multiple of 8", (long long)dst_ld);
   if (lr_cols < d->heads || lr_ld < lr_cols)
     return fail(TTT_ERR_SHAPE, "need heads <= lr_cols <= lr_ld (got lr_cols=%d, lr_ld=%lld)", lr_cols, (long long)lr_ld);
   const NamedPtr ptrs[] = {{"grad_xq", grad_xq},       {"grad_xk", grad_xk},       {"grad_xv", grad_xv},
@@ -847,7 +849,7 @@ extern "C" int ttt_layer_prologue_backward(const ttt_dims* d, const void* grad_x
   p.rope_mode = rope_mode;
   p.rope_theta = rope_mode != 0 ? rope_theta : 1.f;
   p.base_lr = base_lr;
-  cudaError_t e = ttt::launch_layer_prologue_bwd(d->dtype, p, static_cast<cudaStream_t>(stream));
+  cudaError_t e = ttt::launch_layer_prologue_bwd(d->dtype, d->head_dim, p, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "layer prologue backward launch failed: %s", cudaGetErrorString(e));
   return TTT_OK;
 }
@@ -857,8 +859,9 @@ extern "C" int ttt_layer_qk_conv(const ttt_dims* d, const void* x, int64_t x_ld,
                                  void* k, void* stream) {
   int rc = check_layer_dims(d);
   if (rc != TTT_OK) return rc;
-  const int64_t C = (int64_t)d->heads * 64;
-  if (x_ld < C || (x_ld & 7) != 0) return fail(TTT_ERR_SHAPE, "x_ld (%lld) must be >= heads*64 and a multiple of 8", (long long)x_ld);
+  const int64_t C = (int64_t)d->heads * d->head_dim;
+  if (x_ld < C || (x_ld & 7) != 0)
+    return fail(TTT_ERR_SHAPE, "x_ld (%lld) must be >= heads*head_dim and a multiple of 8", (long long)x_ld);
   const NamedPtr ptrs[] = {{"x", x}, {"q", q}, {"k", k}};
   rc = check_ptrs(ptrs, 3);
   if (rc != TTT_OK) return rc;
@@ -875,7 +878,7 @@ extern "C" int ttt_layer_qk_conv(const ttt_dims* d, const void* x, int64_t x_ld,
 extern "C" size_t ttt_layer_qk_conv_backward_workspace_bytes(const ttt_dims* d) {
   if (check_layer_dims(d) != TTT_OK) return 0;
   const size_t nch = ((size_t)d->seq_len + ttt::LAYER_CONV_CHUNK - 1) / ttt::LAYER_CONV_CHUNK;
-  return (size_t)d->batch * nch * 10 * (size_t)d->heads * 64 * sizeof(float);
+  return (size_t)d->batch * nch * 10 * (size_t)d->heads * d->head_dim * sizeof(float);
 }
 
 extern "C" int ttt_layer_qk_conv_backward(const ttt_dims* d, const void* grad_q, const void* grad_k, const void* x,
@@ -884,8 +887,9 @@ extern "C" int ttt_layer_qk_conv_backward(const ttt_dims* d, const void* grad_q,
                                           size_t workspace_bytes, void* stream) {
   int rc = check_layer_dims(d);
   if (rc != TTT_OK) return rc;
-  const int64_t C = (int64_t)d->heads * 64;
-  if (x_ld < C || (x_ld & 7) != 0) return fail(TTT_ERR_SHAPE, "x_ld (%lld) must be >= heads*64 and a multiple of 8", (long long)x_ld);
+  const int64_t C = (int64_t)d->heads * d->head_dim;
+  if (x_ld < C || (x_ld & 7) != 0)
+    return fail(TTT_ERR_SHAPE, "x_ld (%lld) must be >= heads*head_dim and a multiple of 8", (long long)x_ld);
   const NamedPtr ptrs[] = {{"grad_q", grad_q}, {"grad_k", grad_k}, {"x", x}, {"grad_x", grad_x}};
   rc = check_ptrs(ptrs, 4);
   if (rc != TTT_OK) return rc;
@@ -905,8 +909,8 @@ extern "C" int ttt_layer_qk_conv_backward(const ttt_dims* d, const void* grad_q,
 }
 
 extern "C" size_t ttt_layer_epilogue_backward_workspace_bytes(const ttt_dims* d) {
-  if (check_layer_dims(d) != TTT_OK || d->heads > 32) return 0;
-  return ttt::layer_epilogue_bwd_workspace_bytes(d->batch, d->heads, d->seq_len);
+  if (check_layer_dims(d) != TTT_OK || d->heads * d->head_dim > 2048) return 0;
+  return ttt::layer_epilogue_bwd_workspace_bytes(d->batch, d->heads, d->seq_len, d->head_dim);
 }
 
 extern "C" int ttt_layer_epilogue_backward(const ttt_dims* d, const void* grad_y, const void* inner_out,
@@ -917,7 +921,8 @@ extern "C" int ttt_layer_epilogue_backward(const ttt_dims* d, const void* grad_y
                                            void* stream) {
   int rc = check_layer_dims(d);
   if (rc != TTT_OK) return rc;
-  if (d->heads > 32) return fail(TTT_ERR_UNSUPPORTED, "heads=%d (supported: up to 32)", d->heads);
+  if (d->heads * d->head_dim > 2048)
+    return fail(TTT_ERR_UNSUPPORTED, "heads*head_dim=%d (supported: up to 2048)", d->heads * d->head_dim);
   if (!(eps >= 0.f)) return fail(TTT_ERR_SHAPE, "eps must be >= 0");
   const NamedPtr ptrs[] = {{"grad_y", grad_y}, {"inner_out", inner_out}, {"grad_inner_out", grad_inner_out}};
   rc = check_ptrs(ptrs, 3);
@@ -927,9 +932,9 @@ extern "C" int ttt_layer_epilogue_backward(const ttt_dims* d, const void* grad_y
     return fail(TTT_ERR_NULL, "post_norm_weight / post_norm_bias / their gradients must not be null");
   if (gate != nullptr) {
     if (grad_gate == nullptr) return fail(TTT_ERR_NULL, "grad_gate is null although a gate is given");
-    const int64_t cols = (int64_t)d->heads * 64;
+    const int64_t cols = (int64_t)d->heads * d->head_dim;
     if (gate_ld < cols || (gate_ld & 3) != 0 || grad_gate_ld < cols || (grad_gate_ld & 3) != 0)
-      return fail(TTT_ERR_SHAPE, "gate_ld / grad_gate_ld must be >= heads*64 and multiples of 4");
+      return fail(TTT_ERR_SHAPE, "gate_ld / grad_gate_ld must be >= heads*head_dim and multiples of 4");
     if ((reinterpret_cast<uintptr_t>(gate) & 7u) != 0 || (reinterpret_cast<uintptr_t>(grad_gate) & 7u) != 0)
       return fail(TTT_ERR_ALIGN, "gate / grad_gate is not 8-byte aligned");
   }
@@ -954,7 +959,7 @@ extern "C" int ttt_layer_epilogue_backward(const ttt_dims* d, const void* grad_y
   p.H = d->heads;
   p.T = d->seq_len;
   p.eps = eps;
-  cudaError_t e = ttt::launch_layer_epilogue_bwd(d->dtype, p, static_cast<cudaStream_t>(stream));
+  cudaError_t e = ttt::launch_layer_epilogue_bwd(d->dtype, d->head_dim, p, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(TTT_ERR_CUDA, "layer epilogue backward launch failed: %s", cudaGetErrorString(e));
   return TTT_OK;
 }

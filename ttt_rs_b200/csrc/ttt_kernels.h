@@ -185,11 +185,11 @@ struct LayerConvBwdParams {
 constexpr int LAYER_CONV_CHUNK = 64;  // tokens a thread walks
 cudaError_t launch_layer_conv(int dtype, const LayerConvParams& p, cudaStream_t st);
 cudaError_t launch_layer_conv_bwd(int dtype, const LayerConvBwdParams& p, cudaStream_t st);
-cudaError_t launch_layer_prologue(int dtype, const LayerProParams& p, cudaStream_t st);
-cudaError_t launch_layer_prologue_bwd(int dtype, const LayerProBwdParams& p, cudaStream_t st);
-cudaError_t launch_layer_epilogue_bwd(int dtype, const LayerEpiBwdParams& p, cudaStream_t st);
-size_t layer_epilogue_bwd_workspace_bytes(int B, int H, int T);
-cudaError_t launch_layer_epilogue(int dtype, const LayerEpiParams& p, cudaStream_t st);
+cudaError_t launch_layer_prologue(int dtype, int head_dim, const LayerProParams& p, cudaStream_t st);
+cudaError_t launch_layer_prologue_bwd(int dtype, int head_dim, const LayerProBwdParams& p, cudaStream_t st);
+cudaError_t launch_layer_epilogue_bwd(int dtype, int head_dim, const LayerEpiBwdParams& p, cudaStream_t st);
+size_t layer_epilogue_bwd_workspace_bytes(int B, int H, int T, int head_dim);
+cudaError_t launch_layer_epilogue(int dtype, int head_dim, const LayerEpiParams& p, cudaStream_t st);
 
 // One mini-batch of R <= 16 tokens per stream (decode step, sequence tail): ttt_linear_partial.cu.
 struct LinPartialParams {

@@ -11,7 +11,7 @@
 //   * ttt_layer_epilogue_kernel reads the inner loop's [B,H,T,F] output once and writes [B,T,H*F] with the post
 //     LayerNorm and the optional gelu(tanh) gate applied.
 // Every global access is a full 128-byte (bf16) or 256-byte (f32) row segment per 8 / 32 lanes; no shared-memory
-// staging is needed because a (token, head) row of 64 features is contiguous in both layouts.
+// staging is needed because a (token, head) row of F = 64 or 32 features is contiguous in both layouts.
 #include "ttt_kernels.h"
 #include "ttt_common.cuh"
 
@@ -64,16 +64,18 @@ constexpr int PRO_TCHUNK = 32;   // tokens per warp task
 constexpr int PRO_MAXK = 4;      // causal convolution taps supported
 constexpr int PRO_MAXPOS = 64;   // rotary table rows (positions modulo the mini-batch length)
 
-// One warp task = (batch b, group of 4 heads, chunk of PRO_TCHUNK tokens).  Lane = 8*hq + sub handles head
-// 4*hgroup + hq, features [8*sub, 8*sub+8) = rotary pairs 4*sub .. 4*sub+3, and walks the chunk's tokens in groups of
-// PRO_TG whose loads are all issued before any of them is used (memory-level parallelism).
+// One warp task = (batch b, group of HPW heads, chunk of PRO_TCHUNK tokens), HPW = 4 heads of 64 features or 8 heads of
+// 32.  Lane = SUBS*hq + sub (SUBS = F/8) handles head HPW*hgroup + hq, features [8*sub, 8*sub+8) = rotary pairs
+// 4*sub .. 4*sub+3, and walks the chunk's tokens in groups of PRO_TG whose loads are all issued before any of them is
+// used (memory-level parallelism).
 constexpr int PRO_TG = 4;
 
-template <typename T, bool CONV>
+template <typename T, bool CONV, int FD>
 __global__ void __launch_bounds__(PRO_THREADS, (CONV || sizeof(T) == 4) ? 1 : 3) ttt_layer_prologue_kernel(const LayerProParams p) {
-  __shared__ float2 rope_tab[PRO_MAXPOS][32];  // (cos, sin) per position and pair
+  __shared__ float2 rope_tab[PRO_MAXPOS][32];  // (cos, sin) per position and pair (the first FD/2 pairs are used)
+  constexpr int F = FD, SUBS = FD / 8, HPW = 32 / SUBS;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int F = HD, H = p.H, NT = p.T;
+  const int H = p.H, NT = p.T;
   const bool rope = p.rope_mode != 0;
   const bool rope_wrap = p.rope_mode == 1;
   const float log2_theta = log2f(p.rope_theta);
@@ -88,8 +90,8 @@ __global__ void __launch_bounds__(PRO_THREADS, (CONV || sizeof(T) == 4) ? 1 : 3)
   }
   __syncthreads();
 
-  const int hq = lane >> 3, sub = lane & 7;
-  const int hgroups = (H + 3) >> 2, tchunks = (NT + PRO_TCHUNK - 1) / PRO_TCHUNK;
+  const int hq = lane / SUBS, sub = lane % SUBS;
+  const int hgroups = (H + HPW - 1) / HPW, tchunks = (NT + PRO_TCHUNK - 1) / PRO_TCHUNK;
   const long ntasks = (long)p.B * hgroups * tchunks;
   const int KC = p.conv_k;
 
@@ -97,7 +99,7 @@ __global__ void __launch_bounds__(PRO_THREADS, (CONV || sizeof(T) == 4) ? 1 : 3)
     const int tc = (int)(task % tchunks);
     const int hg = (int)((task / tchunks) % hgroups);
     const int b = (int)(task / ((long)tchunks * hgroups));
-    const int h = 4 * hg + hq;
+    const int h = HPW * hg + hq;
     if (h >= H) continue;
     const int col = h * F + 8 * sub;  // first of this lane's 8 columns inside a projection block
     const int t0 = tc * PRO_TCHUNK, t1 = min(NT, t0 + PRO_TCHUNK);
@@ -220,14 +222,15 @@ constexpr int EPI_THREADS = 256;
 
 
 // One CTA per tile of TT consecutive tokens of one batch element.  Load phase: for every head the tile's TT rows of
-// 64 features are one contiguous segment of the [B,H,T,F] tensor; all threads fetch the segments with 16-byte loads
+// F features are one contiguous segment of the [B,H,T,F] tensor; all threads fetch the segments with 16-byte loads
 // (the whole tile is in flight at once) and scatter them into a [TT][H*F] tile in shared memory.  Row phase: each
 // warp takes whole rows from shared memory (three sweeps: sum, squared deviations, output), applies the norm and the
 // optional gate and writes the row to [B,T,H*F] with 16-byte stores.  Several CTAs per SM overlap the two phases.
 // MAXCH: 16-byte chunks of one row per lane (rows of up to 32 * MAXCH chunks = 512 * MAXCH bytes); the tile holds
 // TT = 64 / MAXCH tokens, so the [TT][H*F] staging tile stays at or below 32 KB and several CTAs share an SM.
-template <typename T, int MAXCH>
+template <typename T, int MAXCH, int FD>
 __global__ void __launch_bounds__(EPI_THREADS, (MAXCH <= 4 ? 4 : 2)) ttt_layer_epilogue_kernel(const LayerEpiParams p) {
+  constexpr int HD = FD;  // features per head in this instantiation
   constexpr int TT = 64 / MAXCH;
   constexpr int EPC = 16 / sizeof(T);  // elements per 16-byte chunk
   constexpr int NPAIR = EPC / 2;
@@ -376,32 +379,41 @@ static int sm_count() {
   return n;
 }
 
-cudaError_t launch_layer_prologue(int dtype, const LayerProParams& p, cudaStream_t st) {
-  const long ntasks = (long)p.B * ((p.H + 3) / 4) * ((p.T + PRO_TCHUNK - 1) / PRO_TCHUNK);
+// grid of the two prologue kernels: one warp per (batch, group of 256 / head_dim heads, token chunk), capped
+static int prologue_grid(int B, int H, int T, int head_dim) {
+  const int hpw = 256 / head_dim;
+  const long ntasks = (long)B * ((H + hpw - 1) / hpw) * ((T + PRO_TCHUNK - 1) / PRO_TCHUNK);
   const long want = (ntasks + PRO_THREADS / 32 - 1) / (PRO_THREADS / 32);
   const long cap = (long)sm_count() * 8;
-  const int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
-  const bool conv = p.conv_q_w != nullptr;
-  if (dtype == 1) {
-    if (conv)
-      ttt_layer_prologue_kernel<__nv_bfloat16, true><<<grid, PRO_THREADS, 0, st>>>(p);
-    else
-      ttt_layer_prologue_kernel<__nv_bfloat16, false><<<grid, PRO_THREADS, 0, st>>>(p);
+  return (int)(want < 1 ? 1 : (want > cap ? cap : want));
+}
+
+template <typename T, int FD>
+static void launch_pro_t(const LayerProParams& p, int grid, cudaStream_t st) {
+  if (p.conv_q_w != nullptr)
+    ttt_layer_prologue_kernel<T, true, FD><<<grid, PRO_THREADS, 0, st>>>(p);
+  else
+    ttt_layer_prologue_kernel<T, false, FD><<<grid, PRO_THREADS, 0, st>>>(p);
+}
+
+cudaError_t launch_layer_prologue(int dtype, int head_dim, const LayerProParams& p, cudaStream_t st) {
+  const int grid = prologue_grid(p.B, p.H, p.T, head_dim);
+  if (head_dim == 32) {
+    if (dtype == 1) launch_pro_t<__nv_bfloat16, 32>(p, grid, st);
+    else launch_pro_t<float, 32>(p, grid, st);
   } else {
-    if (conv)
-      ttt_layer_prologue_kernel<float, true><<<grid, PRO_THREADS, 0, st>>>(p);
-    else
-      ttt_layer_prologue_kernel<float, false><<<grid, PRO_THREADS, 0, st>>>(p);
+    if (dtype == 1) launch_pro_t<__nv_bfloat16, 64>(p, grid, st);
+    else launch_pro_t<float, 64>(p, grid, st);
   }
   return cudaGetLastError();
 }
 
-template <typename T, int MAXCH>
+template <typename T, int MAXCH, int FD>
 static cudaError_t launch_epi_t(const LayerEpiParams& p, cudaStream_t st) {
-  const int C = p.H * HD;
+  const int C = p.H * FD;
   constexpr int TT = 64 / MAXCH;
   const size_t smem = 2 * (size_t)TT * C * sizeof(T) + 2 * (size_t)C * sizeof(float);
-  auto kfn = ttt_layer_epilogue_kernel<T, MAXCH>;
+  auto kfn = ttt_layer_epilogue_kernel<T, MAXCH, FD>;
   cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   const long ntiles = (long)p.B * ((p.T + TT - 1) / TT);
@@ -414,11 +426,17 @@ static cudaError_t launch_epi_t(const LayerEpiParams& p, cudaStream_t st) {
   return cudaGetLastError();
 }
 
-cudaError_t launch_layer_epilogue(int dtype, const LayerEpiParams& p, cudaStream_t st) {
-  // chunks of one row per lane: H*64 elements / (elements per 16 bytes) / 32 lanes
-  if (dtype == 1) return p.H <= 16 ? launch_epi_t<__nv_bfloat16, 4>(p, st) : launch_epi_t<__nv_bfloat16, 8>(p, st);
-  if (p.H <= 8) return launch_epi_t<float, 4>(p, st);
-  return p.H <= 16 ? launch_epi_t<float, 8>(p, st) : launch_epi_t<float, 16>(p, st);
+template <int FD>
+static cudaError_t launch_epi_f(int dtype, const LayerEpiParams& p, cudaStream_t st) {
+  // chunks of one row per lane: H*F elements / (elements per 16 bytes) / 32 lanes
+  const int C = p.H * FD;
+  if (dtype == 1) return C <= 1024 ? launch_epi_t<__nv_bfloat16, 4, FD>(p, st) : launch_epi_t<__nv_bfloat16, 8, FD>(p, st);
+  if (C <= 512) return launch_epi_t<float, 4, FD>(p, st);
+  return C <= 1024 ? launch_epi_t<float, 8, FD>(p, st) : launch_epi_t<float, 16, FD>(p, st);
+}
+
+cudaError_t launch_layer_epilogue(int dtype, int head_dim, const LayerEpiParams& p, cudaStream_t st) {
+  return head_dim == 32 ? launch_epi_f<32>(dtype, p, st) : launch_epi_f<64>(dtype, p, st);
 }
 
 }  // namespace ttt
@@ -433,11 +451,12 @@ namespace ttt {
 // to the projection layout [B*T, ld] with the inverse rotation applied to q and k; the gradient of ttt_lr_eta goes
 // back through the sigmoid to the logits' columns (lr = c sigma(z), c = base_lr / F  =>  dz = dlr * lr * (1 - lr/c));
 // padding columns after the H logit columns are zeroed.
-template <typename T>
+template <typename T, int FD>
 __global__ void __launch_bounds__(PRO_THREADS, sizeof(T) == 2 ? 3 : 1) ttt_layer_prologue_bwd_kernel(const LayerProBwdParams p) {
   __shared__ float2 rope_tab[PRO_MAXPOS][32];
+  constexpr int F = FD, SUBS = FD / 8, HPW = 32 / SUBS;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int F = HD, H = p.H, NT = p.T;
+  const int H = p.H, NT = p.T;
   const bool rope = p.rope_mode != 0, rope_wrap = p.rope_mode == 1;
   const float log2_theta = log2f(p.rope_theta);
   if (rope && rope_wrap) {
@@ -449,14 +468,14 @@ __global__ void __launch_bounds__(PRO_THREADS, sizeof(T) == 2 ? 3 : 1) ttt_layer
     }
   }
   __syncthreads();
-  const int hq = lane >> 3, sub = lane & 7;
-  const int hgroups = (H + 3) >> 2, tchunks = (NT + PRO_TCHUNK - 1) / PRO_TCHUNK;
+  const int hq = lane / SUBS, sub = lane % SUBS;
+  const int hgroups = (H + HPW - 1) / HPW, tchunks = (NT + PRO_TCHUNK - 1) / PRO_TCHUNK;
   const long ntasks = (long)p.B * hgroups * tchunks;
   for (long task = (long)blockIdx.x * (PRO_THREADS / 32) + warp; task < ntasks; task += (long)gridDim.x * (PRO_THREADS / 32)) {
     const int tc = (int)(task % tchunks);
     const int hg = (int)((task / tchunks) % hgroups);
     const int b = (int)(task / ((long)tchunks * hgroups));
-    const int h = 4 * hg + hq;
+    const int h = HPW * hg + hq;
     if (h >= H) continue;
     const int col = h * F + 8 * sub;
     const int t0 = tc * PRO_TCHUNK, t1 = min(NT, t0 + PRO_TCHUNK);
@@ -528,8 +547,9 @@ __global__ void __launch_bounds__(PRO_THREADS, sizeof(T) == 2 ? 3 : 1) ttt_layer
 //   dz = rstd * (dx - mean(dx) - x_hat * mean(dx * x_hat)),  dx = dn * gamma,
 // writes dz back into the tile (then scattered to [B,H,T,F] per head segment) and leaves (mean, rstd) of every row in
 // `row_stats` for the parameter-gradient kernel below.
-template <typename T, int MAXCH>
+template <typename T, int MAXCH, int FD>
 __global__ void __launch_bounds__(EPI_THREADS, (MAXCH <= 4 ? 2 : 1)) ttt_layer_epilogue_bwd_kernel(const LayerEpiBwdParams p) {
+  constexpr int HD = FD;  // features per head in this instantiation
   constexpr int TT = 64 / MAXCH;
   constexpr int EPC = 16 / sizeof(T);
   constexpr int CPR = HD / EPC;
@@ -719,8 +739,9 @@ __global__ void __launch_bounds__(EPI_THREADS, (MAXCH <= 4 ? 2 : 1)) ttt_layer_e
 // Parameter gradients of the post norm: d weight[c] = sum over tokens of dn * x_hat, d bias[c] = sum of dn.  One CTA
 // per slab of PARAM_SLAB tokens, one thread per column pair, rows walked in order; the slab's sums go to `partials`.
 constexpr int PARAM_SLAB = 128;
-template <typename T>
+template <typename T, int FD>
 __global__ void ttt_layer_epilogue_bwd_param_kernel(const LayerEpiBwdParams p) {
+  constexpr int HD = FD;  // features per head in this instantiation
   const int H = p.H, NT = p.T, C = H * HD;
   const int pair = threadIdx.x;          // columns 2*pair, 2*pair+1
   const int c = 2 * pair, h = c / HD, f = c % HD;
@@ -793,29 +814,29 @@ __global__ void __launch_bounds__(256) ttt_layer_epilogue_bwd_reduce_kernel(cons
   }
 }
 
-cudaError_t launch_layer_prologue_bwd(int dtype, const LayerProBwdParams& p, cudaStream_t st) {
-  const long ntasks = (long)p.B * ((p.H + 3) / 4) * ((p.T + PRO_TCHUNK - 1) / PRO_TCHUNK);
-  const long want = (ntasks + PRO_THREADS / 32 - 1) / (PRO_THREADS / 32);
-  const long cap = (long)sm_count() * 8;
-  const int grid = (int)(want < 1 ? 1 : (want > cap ? cap : want));
-  if (dtype == 1)
-    ttt_layer_prologue_bwd_kernel<__nv_bfloat16><<<grid, PRO_THREADS, 0, st>>>(p);
-  else
-    ttt_layer_prologue_bwd_kernel<float><<<grid, PRO_THREADS, 0, st>>>(p);
+cudaError_t launch_layer_prologue_bwd(int dtype, int head_dim, const LayerProBwdParams& p, cudaStream_t st) {
+  const int grid = prologue_grid(p.B, p.H, p.T, head_dim);
+  if (head_dim == 32) {
+    if (dtype == 1) ttt_layer_prologue_bwd_kernel<__nv_bfloat16, 32><<<grid, PRO_THREADS, 0, st>>>(p);
+    else ttt_layer_prologue_bwd_kernel<float, 32><<<grid, PRO_THREADS, 0, st>>>(p);
+  } else {
+    if (dtype == 1) ttt_layer_prologue_bwd_kernel<__nv_bfloat16, 64><<<grid, PRO_THREADS, 0, st>>>(p);
+    else ttt_layer_prologue_bwd_kernel<float, 64><<<grid, PRO_THREADS, 0, st>>>(p);
+  }
   return cudaGetLastError();
 }
 
-size_t layer_epilogue_bwd_workspace_bytes(int B, int H, int T) {
+size_t layer_epilogue_bwd_workspace_bytes(int B, int H, int T, int head_dim) {
   const size_t ntok = (size_t)B * T, nslab = (ntok + PARAM_SLAB - 1) / PARAM_SLAB;
-  return ntok * sizeof(float2) + nslab * 2 * (size_t)H * HD * sizeof(float);
+  return ntok * sizeof(float2) + nslab * 2 * (size_t)H * head_dim * sizeof(float);
 }
 
-template <typename T, int MAXCH>
+template <typename T, int MAXCH, int FD>
 static cudaError_t launch_epi_bwd_t(LayerEpiBwdParams p, cudaStream_t st) {
-  const int C = p.H * HD;
+  const int C = p.H * FD;
   constexpr int TT = 64 / MAXCH;
   const size_t smem = 2 * (size_t)TT * C * sizeof(T) + 2 * (size_t)C * sizeof(float);
-  auto kfn = ttt_layer_epilogue_bwd_kernel<T, MAXCH>;
+  auto kfn = ttt_layer_epilogue_bwd_kernel<T, MAXCH, FD>;
   cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   const long ntiles = (long)p.B * ((p.T + TT - 1) / TT);
@@ -830,21 +851,27 @@ static cudaError_t launch_epi_bwd_t(LayerEpiBwdParams p, cudaStream_t st) {
   if (e != cudaSuccess) return e;
   const long ntok = (long)p.B * p.T;
   const int nslab = (int)((ntok + PARAM_SLAB - 1) / PARAM_SLAB);
-  ttt_layer_epilogue_bwd_param_kernel<T><<<nslab, C / 2, 0, st>>>(p);
+  ttt_layer_epilogue_bwd_param_kernel<T, FD><<<nslab, C / 2, 0, st>>>(p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   ttt_layer_epilogue_bwd_reduce_kernel<<<(2 * C + 31) / 32, 256, 0, st>>>(p.partials, nslab, C, p.d_ln_w, p.d_ln_b);
   return cudaGetLastError();
 }
 
-cudaError_t launch_layer_epilogue_bwd(int dtype, const LayerEpiBwdParams& p0, cudaStream_t st) {
+template <int FD>
+static cudaError_t launch_epi_bwd_f(int dtype, const LayerEpiBwdParams& p, cudaStream_t st) {
+  const int C = p.H * FD;
+  if (dtype == 1) return C <= 1024 ? launch_epi_bwd_t<__nv_bfloat16, 4, FD>(p, st) : launch_epi_bwd_t<__nv_bfloat16, 8, FD>(p, st);
+  if (C <= 512) return launch_epi_bwd_t<float, 4, FD>(p, st);
+  return C <= 1024 ? launch_epi_bwd_t<float, 8, FD>(p, st) : launch_epi_bwd_t<float, 16, FD>(p, st);
+}
+
+cudaError_t launch_layer_epilogue_bwd(int dtype, int head_dim, const LayerEpiBwdParams& p0, cudaStream_t st) {
   // workspace: (mean, rstd) per token, then the slabs' partial parameter gradients
   LayerEpiBwdParams p = p0;
   p.row_stats = reinterpret_cast<float2*>(p0.partials);
   p.partials = p0.partials + 2 * (size_t)p0.B * p0.T;
-  if (dtype == 1) return p.H <= 16 ? launch_epi_bwd_t<__nv_bfloat16, 4>(p, st) : launch_epi_bwd_t<__nv_bfloat16, 8>(p, st);
-  if (p.H <= 8) return launch_epi_bwd_t<float, 4>(p, st);
-  return p.H <= 16 ? launch_epi_bwd_t<float, 8>(p, st) : launch_epi_bwd_t<float, 16>(p, st);
+  return head_dim == 32 ? launch_epi_bwd_f<32>(dtype, p, st) : launch_epi_bwd_f<64>(dtype, p, st);
 }
 
 // ----------------------------------------------------------------------------------------------------
