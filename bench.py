@@ -85,7 +85,7 @@ WORKLOADS = {
                           desc="dependent tensor-core step round trip, tcgen05 vs mma.sync (csrc/probe_chain_latency.cu)"),
 }
 F, CS = 64, 16
-E2E_CHUNKS = int(os.environ.get("TTT_E2E_CHUNKS", "10"))
+E2E_CHUNKS = int(os.environ.get("TTT_E2E_CHUNKS", "0")) or None  # None: chosen from the shapes (host_io.auto_chunks)
 
 
 def algorithmic_bytes(w, fwd=True, bwd=True):
@@ -935,7 +935,8 @@ def run_e2e(tb, w, host, dev, cfg, world, args, tokens):
             "copy_ceiling_note": "the same H2D and D2H byte counts as plain pinned cudaMemcpyAsync on two streams, all "
                                  "ranks at once, no kernels: the step is bound by the host link when ms_per_step is "
                                  "close to it (bytes are per rank)",
-            "how": f"pinned host buffers, {E2E_CHUNKS} tapered batch chunks pipelined over copy-in / compute / copy-out streams",
+            "how": f"pinned host buffers, {len(runner.last_bounds) - 1} equal batch chunks pipelined over copy-in / compute / "
+                   "copy-out streams; the small per-row tensors cross the link once per step",
             "host_numa_node": numa_node}
 
 
