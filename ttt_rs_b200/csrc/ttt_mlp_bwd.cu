@@ -70,6 +70,65 @@ struct MatG {
 template <int R, int C, bool TR>
 __device__ __forceinline__ MatG<R, C, !TR> tr(const MatG<R, C, TR> m) { return MatG<R, C, !TR>{m.p}; }
 
+// bf16 copy of a float32 matrix [R][C] of the workspace, read as the B operand of a product in either orientation
+// (the state gradients dW1, dW2 enter four products per stage, two of them transposed).  Stored in 8 x 8 supertiles
+// of 128 bytes; inside a supertile in 2 x 2 blocks of 8 bytes, rows of a block one after the other: element (r, c)
+// sits at mlp_shadow_at(r, c, C).  A B-fragment register is then one 32-bit load (pair along a row) or one 64-bit
+// load and a byte permute (pair along a column), every warp-wide load is one 128-byte line in both orientations, and
+// the writer's accumulator pair (r, c), (r, c + 1) is one 32-bit store (a warp's half tile = one line).
+__host__ __device__ inline int mlp_shadow_at(int r, int c, int C) {
+  return (((r >> 3) * (C >> 3) + (c >> 3)) << 6) + (((((r >> 1) & 3) << 2) + ((c >> 1) & 3)) << 2) + ((r & 1) << 1) + (c & 1);
+}
+template <int R, int C, bool TR>
+struct MatH {
+  bf* p;
+};
+template <int R, int C, bool TR>
+__device__ __forceinline__ MatH<R, C, !TR> tr(const MatH<R, C, TR> m) { return MatH<R, C, !TR>{m.p}; }
+
+// float32 master of a state matrix in tensor memory, used as a scratchpad that no tensor-core instruction touches:
+// tile_mma deals the 16 x 8 output tiles of a 64 x 256 (or 256 x 64) matrix to the 16 warps, eight tiles each, always
+// the same ones, so a thread only ever reads and writes its own 32 floats of a matrix -- and a warp can only address
+// its own quarter of the 128 tensor-memory lanes anyway.  Thread (warp w, lane l) owns lane 32 (w % 4) + l; the four
+// warps that share a lane quarter take 128 of the 512 columns each (w / 4), 32 columns per matrix (W1, W2, dW1, dW2):
+// 4 matrices x 64 KB = the SM's whole 256 KB.  Column 4 u + 2 h + e of a matrix holds element (g + 8 h, 2 t + e) of the
+// warp's u-th tile (g = l / 4, t = l % 4): the order of the accumulator registers.  A read-modify-write of a matrix is
+// one tcgen05.ld and one tcgen05.st of 32 columns per thread instead of a round trip to L2.
+template <int R, int C>
+struct MatM {
+  uint32_t taddr;  // lane quarter and first column of this warp's 32 columns of the matrix
+};
+template <class X>
+struct is_tmem : std::false_type {};
+template <int R, int C>
+struct is_tmem<MatM<R, C>> : std::true_type {};
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
+      "%30,%31}, [%32];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7]), "=f"(r[8]),
+        "=f"(r[9]), "=f"(r[10]), "=f"(r[11]), "=f"(r[12]), "=f"(r[13]), "=f"(r[14]), "=f"(r[15]), "=f"(r[16]),
+        "=f"(r[17]), "=f"(r[18]), "=f"(r[19]), "=f"(r[20]), "=f"(r[21]), "=f"(r[22]), "=f"(r[23]), "=f"(r[24]),
+        "=f"(r[25]), "=f"(r[26]), "=f"(r[27]), "=f"(r[28]), "=f"(r[29]), "=f"(r[30]), "=f"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
+      "%30,%31};\n\t"
+      "tcgen05.wait::st.sync.aligned;"
+      ::"f"(r[0]), "f"(r[1]), "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7]), "f"(r[8]), "f"(r[9]),
+        "f"(r[10]), "f"(r[11]), "f"(r[12]), "f"(r[13]), "f"(r[14]), "f"(r[15]), "f"(r[16]), "f"(r[17]), "f"(r[18]),
+        "f"(r[19]), "f"(r[20]), "f"(r[21]), "f"(r[22]), "f"(r[23]), "f"(r[24]), "f"(r[25]), "f"(r[26]), "f"(r[27]),
+        "f"(r[28]), "f"(r[29]), "f"(r[30]), "f"(r[31]), "r"(taddr)
+      : "memory");
+}
+
 __device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
 }
@@ -152,6 +211,22 @@ __device__ __forceinline__ void load_B(const MatG<R, C, TR> B, int k0, int j0, i
     r[1] = pack_bf16(__ldcg(s + 64), __ldcg(s + 72));
   }
 }
+template <int R, int C, bool TR>
+__device__ __forceinline__ void load_B(const MatH<R, C, TR> B, int k0, int j0, int lane, uint32_t (&r)[2]) {
+  const int g = lane >> 2, t = lane & 3;
+  if constexpr (TR) {  // stored [j][k]: the pair (k, k + 1) is adjacent
+#pragma unroll
+    for (int q = 0; q < 2; ++q)
+      r[q] = __ldcg(reinterpret_cast<const uint32_t*>(B.p + mlp_shadow_at(j0 + g, k0 + 2 * t + 8 * q, C)));
+  } else {  // stored [k][j]: rows k, k + 1 of the 2 x 2 block that holds column j
+    const uint32_t sel = (g & 1) ? 0x7632u : 0x5410u;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const uint2 w = __ldcg(reinterpret_cast<const uint2*>(B.p + mlp_shadow_at(k0 + 2 * t + 8 * q, (j0 + g) & ~1, C)));
+      r[q] = __byte_perm(w.x, w.y, sel);
+    }
+  }
+}
 template <int R, int C>
 __device__ __forceinline__ float2 c_load(const MatG<R, C, false> M, int i, int j) {
   return __ldcg(reinterpret_cast<const float2*>(M.p + M.at(i, j)));
@@ -194,6 +269,8 @@ template <class X>
 struct is_global_operand : std::false_type {};
 template <int R, int C, bool TR>
 struct is_global_operand<MatG<R, C, TR>> : std::true_type {};
+template <int R, int C, bool TR>
+struct is_global_operand<MatH<R, C, TR>> : std::true_type {};
 
 // C[M x N] = (ACC ? C : 0) + alpha * sum over the given products of A[M x K] . B[K x N];  M % 16 == 0, N % 8 == 0,
 // K % 16 == 0; every extent and stride is a compile-time constant.  With an epilogue functor the finished pair
@@ -213,6 +290,8 @@ __device__ __forceinline__ void tile_mma(const MC C, const float alpha, EPI epi,
   constexpr int TG = TG1 < GA ? GA : TG1 / GA * GA;
   constexpr int NA = TG / GA, NB = SHARE_B ? 1 : TG;
   static_assert(TG % GA == 0 && GA <= 4, "tile grouping");
+  constexpr bool TM = is_tmem<MC>::value;  // C lives in tensor memory: all eight tiles of the warp in one pass
+  static_assert(!TM || (ACC && per_warp == 8 && TG == 8 && total == NW * TG), "tensor-memory accumulators: 8 tiles per warp");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 #pragma unroll 1
   for (int tile0 = warp; tile0 < total; tile0 += NW * TG) {
@@ -220,6 +299,8 @@ __device__ __forceinline__ void tile_mma(const MC C, const float alpha, EPI epi,
     bool on[TG];
     float acc[TG][4];
     float2 cin[TG][2];
+    float tm[TM ? 32 : 1];
+    if constexpr (TM) tmem_ld32(C.taddr, tm);
 #pragma unroll
     for (int u = 0; u < TG; ++u) {
       const int tile = tile0 + u * NW;
@@ -232,7 +313,8 @@ __device__ __forceinline__ void tile_mma(const MC C, const float alpha, EPI epi,
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         cin[u][h] = make_float2(0.f, 0.f);
-        if constexpr (ACC)
+        if constexpr (TM) cin[u][h] = make_float2(tm[4 * u + 2 * h], tm[4 * u + 2 * h + 1]);
+        else if constexpr (ACC)
           if (on[u]) cin[u][h] = c_load(C, i0[u] + g + 8 * h, j0[u] + 2 * t);
       }
     }
@@ -265,10 +347,17 @@ __device__ __forceinline__ void tile_mma(const MC C, const float alpha, EPI epi,
         for (int h = 0; h < 2; ++h) {
           const int i = i0[u] + g + 8 * h, j = j0[u] + 2 * t;
           const float x = cin[u][h].x + alpha * acc[u][2 * h], y = cin[u][h].y + alpha * acc[u][2 * h + 1];
-          if constexpr (std::is_same<EPI, NoEpi>::value) c_store(C, i, j, x, y);
-          else epi(i, j, x, y);
+          if constexpr (TM) {  // the master goes back to tensor memory below; an epilogue only adds its copies
+            tm[4 * u + 2 * h] = x;
+            tm[4 * u + 2 * h + 1] = y;
+            if constexpr (!std::is_same<EPI, NoEpi>::value) epi(i, j, x, y);
+          } else {
+            if constexpr (std::is_same<EPI, NoEpi>::value) c_store(C, i, j, x, y);
+            else epi(i, j, x, y);
+          }
         }
       }
+    if constexpr (TM) tmem_st32(C.taddr, tm);
   }
 }
 
@@ -385,6 +474,43 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
   float* const db1 = S.db1;
   float* const db2 = S.db2;
   __shared__ int s_item;
+  __shared__ uint32_t s_tmem;
+  // Tensor memory, all 512 columns (shared memory keeps the block alone on its SM): the float32 masters of the state
+  // and of its gradient while a work item runs (see MatM).  The warp that allocates frees it at the end of the kernel;
+  // every way out of the item loop below leads there.
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&s_tmem)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_mine = s_tmem + ((32u * (uint32_t)(warp & 3)) << 16) + 128u * (uint32_t)(warp >> 2);
+  // workspace <-> tensor memory, this thread's 32 floats of one matrix (MatG stores a 16 x 8 tile as 128 consecutive
+  // floats in the order of the accumulator registers: tile index = the index tile_mma deals by)
+  auto master_in = [&](const float* M, const uint32_t taddr) {
+    float v[32];
+    const float* src = M + warp * 128 + 8 * (lane >> 2) + 2 * (lane & 3);
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const float2 f = __ldcg(reinterpret_cast<const float2*>(src + u * (MB_NW * 128) + 64 * h));
+        v[4 * u + 2 * h] = f.x;
+        v[4 * u + 2 * h + 1] = f.y;
+      }
+    tmem_st32(taddr, v);
+  };
+  auto master_out = [&](float* M, const uint32_t taddr) {
+    float v[32];
+    tmem_ld32(taddr, v);
+    float* dst = M + warp * 128 + 8 * (lane >> 2) + 2 * (lane & 3);
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+        *reinterpret_cast<float2*>(dst + u * (MB_NW * 128) + 64 * h) = make_float2(v[4 * u + 2 * h], v[4 * u + 2 * h + 1]);
+  };
 
   // Persistent block.  A stream is a chain of 2 NCH work items: its chunks of CH stages in pass 1 (ranks 0 ..
   // NCH-1, forward), then in pass 2 (ranks NCH .. 2 NCH-1, backward).  Items are handed out rank by rank over all
@@ -411,7 +537,8 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     const size_t row_base = (size_t)stream * p.T;
 
   // per-stream workspace: W1 [F][E], W2 [E][F], dW1, dW2 (float32, in the tile order of MatG), the hand-off record,
-  // then g1p [NS][16][E], g2p [NS][16][F] (bf16), then b1 | b2 at the start of every stage [NS][E + F] (float32)
+  // then g1p [NS][16][E], g2p [NS][16][F] (bf16), then b1 | b2 at the start of every stage [NS][E + F] (float32),
+  // then the bf16 operand copies of dW1 and dW2
   float* ws = p.workspace + (size_t)stream * p.ws_stride;
   float* W1 = ws;
   float* W2 = W1 + F * E;
@@ -421,6 +548,8 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
   bf* g1p_all = reinterpret_cast<bf*>(ho + MLP_BWD_HANDOFF_FLOATS);
   bf* g2p_all = g1p_all + (size_t)NS * CS * E;
   float* bst = reinterpret_cast<float*>(g2p_all + (size_t)NS * CS * F);  // [NS][E + F]: b1, b2 at the start of a stage
+  bf* dW1h = reinterpret_cast<bf*>(bst + (size_t)NS * (E + F));            // bf16 operand copies of dW1, dW2 (MatH)
+  bf* dW2h = dW1h + F * E;
 
   if (rel > 0) {
     // wait (bounded) until the previous item of this stream has published its state
@@ -482,11 +611,21 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
       for (int e = tid; e < F * E; e += MB_THREADS) {
         dW1[e] = 0.f;
         dW2[e] = 0.f;
+        reinterpret_cast<uint32_t*>(dW1h)[e] = 0u;  // both bf16 copies: 2 F E elements = F E words
       }
     for (int e = tid; e < E; e += MB_THREADS) db1[e] = fresh ? 0.f : __ldcg(ho + HO_DB1 + e);
     if (tid < F) db2[tid] = fresh ? 0.f : __ldcg(ho + HO_DB2 + tid);
   }
   __syncthreads();
+  // the masters of this item: W1, W2 (and in pass 2 dW1, dW2) from the workspace, where the previous item of the
+  // stream (or the forward kernel, or the lines above) left them
+  const uint32_t tW1a = tmem_mine, tW2a = tmem_mine + 32, tdW1a = tmem_mine + 64, tdW2a = tmem_mine + 96;
+  master_in(W1, tW1a);
+  master_in(W2, tW2a);
+  if (!pass1) {
+    master_in(dW1, tdW1a);
+    master_in(dW2, tdW2a);
+  }
   const float te_last = S.te[CS - 1];
 // per-phase cycle counts of block 0 (instrumented builds only; written to the status words after the walk)
 #ifdef TTT_MLP_TRACE
@@ -497,8 +636,10 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
 #endif
 
   // ---- operand / output views
-  const MatG<F, E, false> mW1{W1}, mdW1{dW1};
-  const MatG<E, F, false> mW2{W2}, mdW2{dW2};
+  const MatM<F, E> mW1{tW1a}, mdW1{tdW1a};
+  const MatM<E, F> mW2{tW2a}, mdW2{tdW2a};
+  const MatH<F, E, false> hdW1{dW1h};
+  const MatH<E, F, false> hdW2{dW2h};
   const MatT<1, 1> none{nullptr};
   typedef SB<EB, false> TE;
   typedef SB<FB, false> TF_;
@@ -514,19 +655,15 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
   const MatT<CP, 1> ma1{&S.a1[0][0]}, ma2{&S.a2[0][0]}, mdm{&S.dm[0][0]};
   const NoEpi noepi;
 
-  // W += sign * A^T B with the float32 master in the workspace and its bf16 shadow refreshed together
+  // W += sign * A^T B with the float32 master in tensor memory and its bf16 shadow refreshed together
   // (t1 / g2p hold lr o g1 / lr o g2, the operands of the forward's update; its scale te[15] is applied here)
   auto update_w1 = [&](const float sign) {  // W1 += sign * te[15] * K^T t1
-    tile_mma<true, F, E, 8>(mW1, sign * te_last, [&](int i, int j, float x, float y) {
-      c_store(mW1, i, j, x, y);
-      stb2(&S.w1[i][j], x, y);
-    }, prod<CS>(tr(sk), st1));
+    tile_mma<true, F, E, 8>(mW1, sign * te_last, [&](int i, int j, float x, float y) { stb2(&S.w1[i][j], x, y); },
+                            prod<CS>(tr(sk), st1));
   };
   auto update_w2 = [&](const float sign) {  // W2 += sign * te[15] * X2^T g2p
-    tile_mma<true, E, F, 8>(mW2, sign * te_last, [&](int i, int j, float x, float y) {
-      c_store(mW2, i, j, x, y);
-      stb2(&S.w2[i][j], x, y);
-    }, prod<CS>(tr(sx2), sg2p));
+    tile_mma<true, E, F, 8>(mW2, sign * te_last, [&](int i, int j, float x, float y) { stb2(&S.w2[i][j], x, y); },
+                            prod<CS>(tr(sx2), sg2p));
   };
   // z1 = K W1 + b1, x2 = gelu(z1); z1 itself is only needed through gelu'(z1) and (pass 2) gelu''(z1)
   auto forward_first_layer = [&](auto d2_tag) {
@@ -755,14 +892,14 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     tile_mma<false, CS, F>(mdk, 1.f, noepi, prod<CS>(tr(sda1), sq));               // dk = dA1^T Q
     TRM(9)
     // ---- 5. the four state updates; dW1, db1, dW2, db2 still hold the gradients w.r.t. the next stage's state
-    tile_mma<false, CS, F>(mgl1, 1.f, noepi, prod<E>(sg1, tr(mdW1)));              // gl1 = g1 dW1^T
-    tile_mma<false, CS, E>(st3, 1.f, noepi, prod<F>(sg2, tr(mdW2)));               // gl2 = g2 dW2^T
+    tile_mma<false, CS, F>(mgl1, 1.f, noepi, prod<E>(sg1, tr(hdW1)));              // gl1 = g1 dW1^T
+    tile_mma<false, CS, E>(st3, 1.f, noepi, prod<F>(sg2, tr(hdW2)));               // gl2 = g2 dW2^T
     tile_mma<false, CS, E>(none, -1.f, [&](int i, int j, float x, float y) {         // dg1 = -M1^T dz1b - (l o K) dW1 - l (x) db1
       stb2(&S.t2[i][j], x - S.ell[i] * db1[j], y - S.ell[i] * db1[j + 1]);
-    }, prod<CS>(tr(sm1), st1), prod<F>(sdz2, mdW1));
+    }, prod<CS>(tr(sm1), st1), prod<F>(sdz2, hdW1));
     tile_mma<true, CS, F>(mdg2, -1.f, [&](int i, int j, float x, float y) {         // dg2 -= (l o x2) dW2 + l (x) db2
       *reinterpret_cast<float2*>(&S.dg2[i][j]) = make_float2(x - S.ell[i] * db2[j], y - S.ell[i] * db2[j + 1]);
-    }, prod<E>(sz1b, mdW2));
+    }, prod<E>(sz1b, hdW2));
     __syncthreads();
     // dell[j] = -( gl1[j].K[j] + g1[j].db1 + gl2[j].x2[j] + g2[j].db2 )   (one row per warp)
     {
@@ -865,8 +1002,12 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     TRM(13)
     // ---- gradients w.r.t. this stage's state (all reads of the next-stage gradients are done): one pass over each
     //      float32 master, the contraction running over the tokens of all the tile pairs
-    tile_mma<true, E, F, 8>(mdW2, 1.f, noepi, prod<CS>(tr(st2), sg2), prod<CS>(tr(sx2b), sdz2b), prod<CS>(tr(sx2), sdz2));
-    tile_mma<true, F, E, 8>(mdW1, 1.f, noepi, prod<CS>(tr(sq), st1), prod<CS>(tr(sk), st4));
+    tile_mma<true, E, F, 8>(mdW2, 1.f, [&](int i, int j, float x, float y) {
+      *reinterpret_cast<uint32_t*>(dW2h + mlp_shadow_at(i, j, F)) = pack_bf16(x, y);
+    }, prod<CS>(tr(st2), sg2), prod<CS>(tr(sx2b), sdz2b), prod<CS>(tr(sx2), sdz2));
+    tile_mma<true, F, E, 8>(mdW1, 1.f, [&](int i, int j, float x, float y) {
+      *reinterpret_cast<uint32_t*>(dW1h + mlp_shadow_at(i, j, E)) = pack_bf16(x, y);
+    }, prod<CS>(tr(sq), st1), prod<CS>(tr(sk), st4));
     add_colsum(db2, &S.dz2b[0][0], F, FB, 1.f);
     add_colsum(db1, &S.t1[0][0], E, EB, 1.f);
     TRM(14)
@@ -900,6 +1041,15 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     TRM(15)
   }
   __syncthreads();
+  // the masters go back to the workspace: for the stream's next item, or (last item) for the output loop below
+  if (rank < 2 * p.NCH - 1) {
+    master_out(W1, tW1a);
+    master_out(W2, tW2a);
+  }
+  if (!pass1) {
+    master_out(dW1, tdW1a);
+    master_out(dW2, tdW2a);
+  }
   if (rank < 2 * p.NCH - 1) {
     // hand the stream to its next item
     for (int e = tid; e < E; e += MB_THREADS) {
@@ -917,6 +1067,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     if (tid == 0) *reinterpret_cast<volatile int*>(p.sched + 1 + stream) = rel + 1;
   } else {
     // ---- gradients w.r.t. the initial state, per-stream LayerNorm parameter gradients
+    __syncthreads();  // dW1, dW2 are in the workspace for every thread
     for (int e = tid; e < F * E; e += MB_THREADS) {
       st_from_float<T>(p.d_w1, (size_t)stream * F * E + e, __ldcg(dW1 + MatG<F, E, false>::at(e / E, e % E)));
       st_from_float<T>(p.d_w2, (size_t)stream * F * E + e, __ldcg(dW2 + MatG<E, F, false>::at(e / F, e % F)));
@@ -929,6 +1080,9 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     }
   }
   }  // item loop
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(s_tmem) : "memory");
 #ifdef TTT_MLP_TRACE
   if (tid == 0 && blockIdx.x == 0 && p.trace != nullptr)
     for (int i = 0; i < 16; ++i) p.trace[i] = (unsigned int)(tr_acc[i] / NS);
@@ -953,10 +1107,10 @@ __global__ void ttt_mlp_bwd_reduce_kernel(const float* part_te, const float* par
 }
 
 // floats of workspace per stream: the four float32 state matrices, the hand-off record, the bf16 g1p / g2p tiles of
-// every stage, the float32 biases at the start of every stage
+// every stage, the float32 biases at the start of every stage, the bf16 operand copies of dW1 and dW2
 size_t mlp_bwd_ws_stride_floats(int T) {
   const size_t ns = (size_t)T / CS;
-  return 4 * (size_t)HD * MB_E + MLP_BWD_HANDOFF_FLOATS + ns * CS * (MB_E + HD) / 2 + ns * (MB_E + HD);
+  return 4 * (size_t)HD * MB_E + MLP_BWD_HANDOFF_FLOATS + ns * CS * (MB_E + HD) / 2 + ns * (MB_E + HD) + (size_t)HD * MB_E;
 }
 
 cudaError_t launch_mlp_bwd(const MlpBwdParams& p0, int B, cudaStream_t st) {
