@@ -250,7 +250,8 @@ struct MlpBwdParams {
 // Per-stream block of the TTT-MLP backward's workspace, in floats: W1 [64][256], W2 [256][64], dW1, dW2 (float32, each
 // stored tile by tile in accumulator-fragment order, see mlp_state_at), the hand-off record between work items
 // (b1, b2, db1, db2, d ln_weight, d ln_bias), then per stage the bf16 tiles lr o g1 [NS][16][256] and lr o g2
-// [NS][16][64], then the float32 biases b1 | b2 at the start of every stage [NS][256 + 64].
+// [NS][16][64], then the float32 biases b1 | b2 at the start of every stage [NS][256 + 64], then bf16 copies of dW1 and
+// dW2 (64 KB) that the backward reads as product operands.
 constexpr int MLP_BWD_HANDOFF_FLOATS = 2 * 256 + 4 * 64;
 constexpr int MLP_HO_B1 = 0, MLP_HO_B2 = 256, MLP_HO_DB1 = 320, MLP_HO_DB2 = 576, MLP_HO_DG = 640, MLP_HO_DB = 704;
 // element (r, c) of a float32 matrix with C columns stored in accumulator-fragment order: the 16 x 8 tile

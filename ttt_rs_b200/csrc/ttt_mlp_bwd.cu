@@ -12,12 +12,13 @@
 //          kernel can do this instead while it runs (it then also leaves the final state in the workspace);
 //   pass 2 walks backward: W1_s = W1_{s+1} + K^T g1p, W2_s = W2_{s+1} + X2^T g2p recover the state of the stage,
 //          the stage's forward intermediates are recomputed from it, and the gradient steps follow.
-// Where things live: the float32 masters of W1, W2, dW1, dW2 (256 KB per stream) stay in the workspace (L2-resident
-// across the stage loop) and are only read-modified-written there; every matrix that is an operand of a product
-// sits in shared memory as a padded row-major bf16 tile that ldmatrix reads directly (the 16 x 256 and 16 x 64
-// working tiles, and bf16 shadows of W1 and W2 refreshed by the same epilogue that updates the masters).  Tiles
-// that only accumulate or feed a LayerNorm (z2, z2b, dg2, dk, ...) are float32.  Operand precision is the forward
-// kernel's: bf16 operands, float32 accumulation.
+// Where things live: the float32 masters of W1, W2, dW1, dW2 (256 KB per stream) sit in the SM's tensor memory while a
+// work item runs (each thread owns the 128 floats its accumulator fragments update, see MatM) and in the workspace
+// between work items; every matrix that is an operand of a product sits in shared memory as a padded row-major bf16
+// tile that ldmatrix reads directly (the 16 x 256 and 16 x 64 working tiles, and bf16 shadows of W1 and W2 refreshed
+// by the same epilogue that updates the masters) -- except dW1 and dW2, for whose bf16 copies shared memory has no
+// room: those are in the workspace (MatH).  Tiles that only accumulate or feed a LayerNorm (z2, z2b, dg2, dk, ...)
+// are float32.  Operand precision is the forward kernel's: bf16 operands, float32 accumulation.
 #include <type_traits>
 
 #include "ttt_kernels.h"
