@@ -291,8 +291,6 @@ __device__ __forceinline__ void tile_mma(const MC C, const float alpha, EPI epi,
   constexpr int TG = TG1 < GA ? GA : TG1 / GA * GA;
   constexpr int NA = TG / GA, NB = SHARE_B ? 1 : TG;
   static_assert(TG % GA == 0 && GA <= 4, "tile grouping");
-  constexpr bool TM = is_tmem<MC>::value;  // C lives in tensor memory: all eight tiles of the warp in one pass
-  static_assert(!TM || (ACC && per_warp == 8 && TG == 8 && total == NW * TG), "tensor-memory accumulators: 8 tiles per warp");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 #pragma unroll 1
   for (int tile0 = warp; tile0 < total; tile0 += NW * TG) {
@@ -300,8 +298,6 @@ __device__ __forceinline__ void tile_mma(const MC C, const float alpha, EPI epi,
     bool on[TG];
     float acc[TG][4];
     float2 cin[TG][2];
-    float tm[TM ? 32 : 1];
-    if constexpr (TM) tmem_ld32(C.taddr, tm);
 #pragma unroll
     for (int u = 0; u < TG; ++u) {
       const int tile = tile0 + u * NW;
@@ -314,8 +310,7 @@ __device__ __forceinline__ void tile_mma(const MC C, const float alpha, EPI epi,
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         cin[u][h] = make_float2(0.f, 0.f);
-        if constexpr (TM) cin[u][h] = make_float2(tm[4 * u + 2 * h], tm[4 * u + 2 * h + 1]);
-        else if constexpr (ACC)
+        if constexpr (ACC)
           if (on[u]) cin[u][h] = c_load(C, i0[u] + g + 8 * h, j0[u] + 2 * t);
       }
     }
@@ -348,18 +343,66 @@ __device__ __forceinline__ void tile_mma(const MC C, const float alpha, EPI epi,
         for (int h = 0; h < 2; ++h) {
           const int i = i0[u] + g + 8 * h, j = j0[u] + 2 * t;
           const float x = cin[u][h].x + alpha * acc[u][2 * h], y = cin[u][h].y + alpha * acc[u][2 * h + 1];
-          if constexpr (TM) {  // the master goes back to tensor memory below; an epilogue only adds its copies
-            tm[4 * u + 2 * h] = x;
-            tm[4 * u + 2 * h + 1] = y;
-            if constexpr (!std::is_same<EPI, NoEpi>::value) epi(i, j, x, y);
-          } else {
-            if constexpr (std::is_same<EPI, NoEpi>::value) c_store(C, i, j, x, y);
-            else epi(i, j, x, y);
-          }
+          if constexpr (std::is_same<EPI, NoEpi>::value) c_store(C, i, j, x, y);
+          else epi(i, j, x, y);
         }
       }
-    if constexpr (TM) tmem_st32(C.taddr, tm);
   }
+}
+
+// M[R][C] (float32 master in tensor memory) += alpha * sum over p of A_p^T B_p for token tiles A_p [16][R] and
+// B_p [16][C] (bf16, shared memory, rows of LDA / LDB elements): the rank-16 updates of the state and of its gradient.
+// The warp's eight output tiles are the ones tile_mma would deal it (tile w + 16 u: for the 64 x 256 matrices row tile
+// u / 2 and column tile w + 16 (u % 2), for the 256 x 64 ones row tile 2 u + w / 8 and column tile w % 8), so that the
+// operand copies written by the epilogue line up with what the other products read; every shared-memory address is a
+// per-thread base plus a compile-time offset.  epi(u, h, x, y) receives the finished pair (row g + 8 h of tile u,
+// columns 2 t, 2 t + 1) for the copies it keeps (u and h are compile-time constants after unrolling).
+template <int R, int C, int LDA, int LDB, int NP, class EPI>
+__device__ __forceinline__ void rank16_update(const MatM<R, C> M, const float alpha, EPI epi,
+                                              const uint32_t (&a_tiles)[NP], const uint32_t (&b_tiles)[NP]) {
+  static_assert((R == HD && C == MB_E) || (R == MB_E && C == HD), "the two shapes of the state matrices");
+  constexpr bool WIDE = C == MB_E;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // A^T fragment of rows i0 .. i0 + 15: the four 8 x 8 blocks of the stored [token][row] tile, read transposed
+  const uint32_t a_off = ((((lane & 7) + 8 * (lane >> 4)) * LDA + 8 * ((lane >> 3) & 1) + (WIDE ? 0 : 16 * (warp >> 3))) * 2);
+  const uint32_t b_off = (((lane & 15) * LDB + (WIDE ? 8 * warp : 8 * (warp & 7))) * 2);
+  float acc[8][4];
+#pragma unroll
+  for (int u = 0; u < 8; ++u)
+#pragma unroll
+    for (int q = 0; q < 4; ++q) acc[u][q] = 0.f;
+#pragma unroll
+  for (int pi = 0; pi < NP; ++pi) {
+    if constexpr (WIDE) {
+      uint32_t fa[4][4], fb[2][2];
+#pragma unroll
+      for (int m = 0; m < 4; ++m) ldsm_x4_t(fa[m], a_tiles[pi] + a_off + 16 * m * 2);
+#pragma unroll
+      for (int n = 0; n < 2; ++n) ldsm_x2_t(fb[n], b_tiles[pi] + b_off + 128 * n * 2);
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        mma_bf16(acc[u], fa[u >> 1][0], fa[u >> 1][1], fa[u >> 1][2], fa[u >> 1][3], fb[u & 1][0], fb[u & 1][1]);
+    } else {
+      uint32_t fa[8][4], fb[2];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) ldsm_x4_t(fa[u], a_tiles[pi] + a_off + 32 * u * 2);
+      ldsm_x2_t(fb, b_tiles[pi] + b_off);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) mma_bf16(acc[u], fa[u][0], fa[u][1], fa[u][2], fa[u][3], fb[0], fb[1]);
+    }
+  }
+  float tm[32];
+  tmem_ld32(M.taddr, tm);
+#pragma unroll
+  for (int u = 0; u < 8; ++u)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const float x = tm[4 * u + 2 * h] + alpha * acc[u][2 * h], y = tm[4 * u + 2 * h + 1] + alpha * acc[u][2 * h + 1];
+      tm[4 * u + 2 * h] = x;
+      tm[4 * u + 2 * h + 1] = y;
+      epi(u, h, x, y);
+    }
+  tmem_st32(M.taddr, tm);
 }
 
 // ---- element-wise helpers --------------------------------------------------------------------------------------
@@ -658,13 +701,26 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
 
   // W += sign * A^T B with the float32 master in tensor memory and its bf16 shadow refreshed together
   // (t1 / g2p hold lr o g1 / lr o g2, the operands of the forward's update; its scale te[15] is applied here)
+  // where this thread's pairs of a 64 x 256 / 256 x 64 matrix go (see rank16_update for the tiles of a warp): in the
+  // bf16 shadows in shared memory and in the bf16 operand copies in the workspace (MatH), as element offsets of the
+  // pair (tile u = 0, half h = 0); the other pairs follow at compile-time distances
+  const int fg = lane >> 2, ft = lane & 3;
+  const uint32_t w1_at = smem_u32(S.w1) + 2 * (fg * EB + 8 * warp + 2 * ft);
+  const uint32_t w2_at = smem_u32(S.w2) + 2 * ((16 * (warp >> 3) + fg) * FB + 8 * (warp & 7) + 2 * ft);
+  const int h_sub = ((((fg >> 1) & 3) * 4 + ft) * 4) + (fg & 1) * 2;
+  bf* const dW1h_at = dW1h + warp * 64 + h_sub;
+  bf* const dW2h_at = dW2h + (16 * (warp >> 3) + (warp & 7)) * 64 + h_sub;
   auto update_w1 = [&](const float sign) {  // W1 += sign * te[15] * K^T t1
-    tile_mma<true, F, E, 8>(mW1, sign * te_last, [&](int i, int j, float x, float y) { stb2(&S.w1[i][j], x, y); },
-                            prod<CS>(tr(sk), st1));
+    const uint32_t a[1] = {sk.a}, b[1] = {st1.a};
+    rank16_update<F, E, FB, EB, 1>(mW1, sign * te_last, [&](int u, int h, float x, float y) {
+      asm volatile("st.shared.b32 [%0], %1;" ::"r"(w1_at + 2 * ((16 * (u >> 1) + 8 * h) * EB + 128 * (u & 1))), "r"(pack_bf16(x, y)) : "memory");
+    }, a, b);
   };
   auto update_w2 = [&](const float sign) {  // W2 += sign * te[15] * X2^T g2p
-    tile_mma<true, E, F, 8>(mW2, sign * te_last, [&](int i, int j, float x, float y) { stb2(&S.w2[i][j], x, y); },
-                            prod<CS>(tr(sx2), sg2p));
+    const uint32_t a[1] = {sx2.a}, b[1] = {sg2p.a};
+    rank16_update<E, F, EB, FB, 1>(mW2, sign * te_last, [&](int u, int h, float x, float y) {
+      asm volatile("st.shared.b32 [%0], %1;" ::"r"(w2_at + 2 * ((32 * u + 8 * h) * FB)), "r"(pack_bf16(x, y)) : "memory");
+    }, a, b);
   };
   // z1 = K W1 + b1, x2 = gelu(z1); z1 itself is only needed through gelu'(z1) and (pass 2) gelu''(z1)
   auto forward_first_layer = [&](auto d2_tag) {
@@ -1003,12 +1059,18 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     TRM(13)
     // ---- gradients w.r.t. this stage's state (all reads of the next-stage gradients are done): one pass over each
     //      float32 master, the contraction running over the tokens of all the tile pairs
-    tile_mma<true, E, F, 8>(mdW2, 1.f, [&](int i, int j, float x, float y) {
-      *reinterpret_cast<uint32_t*>(dW2h + mlp_shadow_at(i, j, F)) = pack_bf16(x, y);
-    }, prod<CS>(tr(st2), sg2), prod<CS>(tr(sx2b), sdz2b), prod<CS>(tr(sx2), sdz2));
-    tile_mma<true, F, E, 8>(mdW1, 1.f, [&](int i, int j, float x, float y) {
-      *reinterpret_cast<uint32_t*>(dW1h + mlp_shadow_at(i, j, E)) = pack_bf16(x, y);
-    }, prod<CS>(tr(sq), st1), prod<CS>(tr(sk), st4));
+    {
+      const uint32_t a[3] = {st2.a, sx2b.a, sx2.a}, b[3] = {sg2.a, sdz2b.a, sdz2.a};
+      rank16_update<E, F, EB, FB, 3>(mdW2, 1.f, [&](int u, int h, float x, float y) {
+        *reinterpret_cast<uint32_t*>(dW2h_at + (4 * u + h) * 512) = pack_bf16(x, y);
+      }, a, b);
+    }
+    {
+      const uint32_t a[2] = {sq.a, sk.a}, b[2] = {st1.a, st4.a};
+      rank16_update<F, E, FB, EB, 2>(mdW1, 1.f, [&](int u, int h, float x, float y) {
+        *reinterpret_cast<uint32_t*>(dW1h_at + ((2 * (u >> 1) + h) * 32 + 16 * (u & 1)) * 64) = pack_bf16(x, y);
+      }, a, b);
+    }
     add_colsum(db2, &S.dz2b[0][0], F, FB, 1.f);
     add_colsum(db1, &S.t1[0][0], E, EB, 1.f);
     TRM(14)
