@@ -276,13 +276,13 @@ struct is_global_operand<MatH<R, C, TR>> : std::true_type {};
 // C[M x N] = (ACC ? C : 0) + alpha * sum over the given products of A[M x K] . B[K x N];  M % 16 == 0, N % 8 == 0,
 // K % 16 == 0; every extent and stride is a compile-time constant.  With an epilogue functor the finished pair
 // (i, j), (i, j + 1) goes to epi(i, j, x, y) instead of being stored to C.
-// Output tiles of 16 x 8 are dealt to the warps round-robin (the same tile always goes to the same warp, so
-// successive accumulations into one matrix need no barrier between them).  A warp works on up to TGMAX of its tiles
+// Output tiles of 16 x 8 are dealt to the warps round-robin (for one WOFF the same tile always goes to the same warp,
+// so successive accumulations into one matrix with the same WOFF need no barrier between them).  A warp works on up to TGMAX of its tiles
 // at a time: tile0 + u * NW, u < TG, so that their loads (for an accumulation into the float32 state in the
 // workspace: a round trip to L2) are in flight together.  When a row of output tiles goes round the warps GA times,
 // GA consecutive tiles of a warp share their rows (one A fragment serves them); when NW is a multiple of the tiles
 // per row all tiles of a warp share their columns (one B fragment).
-template <bool ACC, int M, int N, int TGMAX = 4, class MC, class EPI, class... PR>
+template <bool ACC, int M, int N, int TGMAX = 4, int WOFF = 0, class MC, class EPI, class... PR>
 __device__ __forceinline__ void tile_mma(const MC C, const float alpha, EPI epi, const PR... pr) {
   constexpr int NW = MB_NW, ntn = N / 8, total = (M / 16) * ntn, per_warp = (total + NW - 1) / NW;
   constexpr int GA = (ntn % NW == 0) ? ntn / NW : 1;
@@ -291,7 +291,9 @@ __device__ __forceinline__ void tile_mma(const MC C, const float alpha, EPI epi,
   constexpr int TG = TG1 < GA ? GA : TG1 / GA * GA;
   constexpr int NA = TG / GA, NB = SHARE_B ? 1 : TG;
   static_assert(TG % GA == 0 && GA <= 4, "tile grouping");
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  // WOFF: the tiles go round the warps starting at warp WOFF -- a product of 8 tiles that shares its phase with
+  // another one is given to the upper eight warps, so that no warp walks both contractions one after the other
+  const int warp = ((threadIdx.x >> 5) + (NW - WOFF)) & (NW - 1), lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
 #pragma unroll 1
   for (int tile0 = warp; tile0 < total; tile0 += NW * TG) {
     int i0[TG], j0[TG];
@@ -868,7 +870,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     }, prod<F>(sq, sw1), prod<CS>(sm1n, sg1));
     __syncthreads();
     tile_mma<false, CS, CS>(ma2, 1.f, noepi, prod<E>(sx2b, tr(sx2)));              // a2 = x2b x2^T
-    tile_mma<false, CS, F>(mdq, 1.f, noepi, prod<E>(sx2b, sw2));                   // z2b = x2b W2 ... (float32 tile)
+    tile_mma<false, CS, F, 4, 8>(mdq, 1.f, noepi, prod<E>(sx2b, sw2));             // z2b = x2b W2 ... (float32 tile)
     __syncthreads();
     for_c([&](int i, int j) {
       const float a = (j <= i) ? S.a2[i][j] : 0.f, m = S.eta[i][j] * (1.f + a);
@@ -912,7 +914,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     TRM(7)
     // ---- 2. z2b = x2b W2 + b2 - M2 g2
     tile_mma<false, CS, CS>(mdm, -1.f, noepi, prod<F>(sdz2b, tr(sg2)));            // dM2 = -tril(dz2b g2^T)
-    tile_mma<false, CS, F>(mdg2, 1.f, noepi, prod<CS>(tr(sm2n), sdz2b));           // dg2 = -M2^T dz2b
+    tile_mma<false, CS, F, 4, 8>(mdg2, 1.f, noepi, prod<CS>(tr(sm2n), sdz2b));     // dg2 = -M2^T dz2b
     __syncthreads();
     for_c([&](int i, int j) {
       const float d = (j <= i) ? S.dm[i][j] : 0.f;
@@ -946,7 +948,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     });
     __syncthreads();
     tile_mma<false, CS, F>(mdq, 1.f, noepi, prod<E>(st1, tr(sw1)), prod<CS>(sda1, sk));   // dq = dz1b W1^T + dA1 K
-    tile_mma<false, CS, F>(mdk, 1.f, noepi, prod<CS>(tr(sda1), sq));               // dk = dA1^T Q
+    tile_mma<false, CS, F, 4, 8>(mdk, 1.f, noepi, prod<CS>(tr(sda1), sq));         // dk = dA1^T Q
     TRM(9)
     // ---- 5. the four state updates; dW1, db1, dW2, db2 still hold the gradients w.r.t. the next stage's state
     tile_mma<false, CS, F>(mgl1, 1.f, noepi, prod<E>(sg1, tr(hdW1)));              // gl1 = g1 dW1^T
@@ -954,7 +956,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     tile_mma<false, CS, E>(none, -1.f, [&](int i, int j, float x, float y) {         // dg1 = -M1^T dz1b - (l o K) dW1 - l (x) db1
       stb2(&S.t2[i][j], x - S.ell[i] * db1[j], y - S.ell[i] * db1[j + 1]);
     }, prod<CS>(tr(sm1), st1), prod<F>(sdz2, hdW1));
-    tile_mma<true, CS, F>(mdg2, -1.f, [&](int i, int j, float x, float y) {         // dg2 -= (l o x2) dW2 + l (x) db2
+    tile_mma<true, CS, F, 4, 8>(mdg2, -1.f, [&](int i, int j, float x, float y) {   // dg2 -= (l o x2) dW2 + l (x) db2
       *reinterpret_cast<float2*>(&S.dg2[i][j]) = make_float2(x - S.ell[i] * db2[j], y - S.ell[i] * db2[j + 1]);
     }, prod<E>(sz1b, hdW2));
     __syncthreads();
