@@ -11,6 +11,10 @@
 //       (M = 64, N = 64, K = 16);
 //   (b) on the warp-level path the kernels use: four dependent mma.sync.m16n8k16 k-steps whose accumulator is
 //       packed to bf16 and fed back as the next A operand through registers [or through shared memory + ldmatrix].
+//   (c) tensor memory used as a per-thread scratchpad, with no tcgen05.mma at all: tcgen05.ld of a thread's own 32
+//       columns, an update (an add, or eight mma.sync accumulations), tcgen05.st back -- what a read-modify-write of
+//       float32 state that does not fit the register budget costs there (the TTT-MLP backward keeps its float32
+//       masters this way), alone and with three blocks per SM.
 // Cycles per step come from clock64 over CHAIN dependent steps.  The first tcgen05 step is checked against a host
 // product so that a mis-encoded descriptor cannot pass as a fast result.
 //
@@ -244,13 +248,71 @@ __global__ void __launch_bounds__(32, 1) mma_sync_chain(Result* out) {
   }
 }
 
+// Tensor memory as a per-thread scratchpad (no tcgen05.mma involved): a warp addresses the 32 lanes of its quarter, so
+// with the 32x32b shape N columns are N private 32-bit words of a thread.  One step = load 32 columns, update them,
+// store them back (a read-modify-write of float32 state that does not fit the register budget); MODE 1 updates them
+// with eight mma.sync accumulations (the rank-16 state update of the TTT-MLP backward), MODE 2 is those eight
+// mma.sync alone, for the difference.  Run with one block and with several blocks per SM (grid > 1).
+#define TTT_L32 "%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31"
+#define TTT_O8(r, b) "=f"(r[b]), "=f"(r[b + 1]), "=f"(r[b + 2]), "=f"(r[b + 3]), "=f"(r[b + 4]), "=f"(r[b + 5]), "=f"(r[b + 6]), "=f"(r[b + 7])
+#define TTT_I8(r, b) "f"(r[b]), "f"(r[b + 1]), "f"(r[b + 2]), "f"(r[b + 3]), "f"(r[b + 4]), "f"(r[b + 5]), "f"(r[b + 6]), "f"(r[b + 7])
+template <int MODE>
+__global__ void __launch_bounds__(128) tmem_scratch(Result* out) {
+  __shared__ uint32_t s_tmem;
+  const int warp = threadIdx.x >> 5;
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 64;" ::"r"(smem_u32(&s_tmem)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t ta = s_tmem + ((32u * (uint32_t)warp) << 16);
+  float r[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) r[i] = (float)(threadIdx.x + i);
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], {" TTT_L32 "};\n\ttcgen05.wait::st.sync.aligned;"
+               ::TTT_I8(r, 0), TTT_I8(r, 8), TTT_I8(r, 16), TTT_I8(r, 24), "r"(ta) : "memory");
+  __syncthreads();
+  unsigned long long t0 = 0;
+  for (int it = 0; it < CHAIN + 1; ++it) {
+    if (it == 1) t0 = clock64();
+    if (MODE != 2)
+      asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {" TTT_L32 "}, [%32];\n\ttcgen05.wait::ld.sync.aligned;"
+                   : TTT_O8(r, 0), TTT_O8(r, 8), TTT_O8(r, 16), TTT_O8(r, 24) : "r"(ta) : "memory");
+    if (MODE == 0) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) r[i] += 1.f;
+    } else {
+      const uint32_t a0 = 0x3c003c00u + it, b0 = 0x3a003a00u;
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(r[4 * u]), "+f"(r[4 * u + 1]), "+f"(r[4 * u + 2]), "+f"(r[4 * u + 3])
+                     : "r"(a0), "r"(a0), "r"(a0), "r"(a0), "r"(b0), "r"(b0));
+    }
+    if (MODE != 2)
+      asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], {" TTT_L32 "};\n\ttcgen05.wait::st.sync.aligned;"
+                   ::TTT_I8(r, 0), TTT_I8(r, 8), TTT_I8(r, 16), TTT_I8(r, 24), "r"(ta) : "memory");
+  }
+  const unsigned long long t1 = clock64();
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    out->cycles = t1 - t0;
+    out->error = 0;
+    out->first[0] = r[0];
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 64;" ::"r"(s_tmem) : "memory");
+}
+
 template <typename K>
-Result run(K kernel, int threads) {
+Result run(K kernel, int threads, int grid = 1) {
   Result* d;
   Result h{};
   cudaMalloc(&d, sizeof(Result));
   cudaMemset(d, 0, sizeof(Result));
-  kernel<<<1, threads>>>(d);
+  kernel<<<grid, threads>>>(d);
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) {
     fprintf(stderr, "kernel failed: %s\n", cudaGetErrorString(e));
@@ -294,6 +356,13 @@ int main() {
   rows.push_back({"tcgen05 M=64 N=64 K=16 (state update shape): mma -> commit -> mbarrier -> tcgen05.ld", run(tc5_chain<64, 1, false>, 128), false});
   rows.push_back({"mma.sync m16n8k16 x4 dependent k-steps -> cvt -> next A fragment in registers", run(mma_sync_chain<false>, 32), false});
   rows.push_back({"mma.sync m16n8k16 x4 dependent k-steps -> cvt -> st.shared -> ldmatrix -> next A fragment", run(mma_sync_chain<true>, 32), false});
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+  rows.push_back({"tensor-memory scratchpad: tcgen05.ld 32 columns -> add -> tcgen05.st (one block)", run(tmem_scratch<0>, 128), false});
+  rows.push_back({"8 x mma.sync m16n8k16 into 32 accumulator registers (one block)", run(tmem_scratch<2>, 128), false});
+  rows.push_back({"tcgen05.ld 32 columns -> 8 x mma.sync into them -> tcgen05.st (one block)", run(tmem_scratch<1>, 128), false});
+  rows.push_back({"8 x mma.sync m16n8k16 into 32 accumulator registers (3 blocks per SM)", run(tmem_scratch<2>, 128, 3 * sms), false});
+  rows.push_back({"tcgen05.ld 32 columns -> 8 x mma.sync into them -> tcgen05.st (3 blocks per SM)", run(tmem_scratch<1>, 128, 3 * sms), false});
   printf("{\"chain_steps\": %d, \"rows\": [", CHAIN);
   for (size_t i = 0; i < rows.size(); ++i) {
     const Row& w = rows[i];
