@@ -819,6 +819,19 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
     v.lr = tid < CS ? ld_as_float<T>(p.lr, row_base + (size_t)s * CS + tid) : 0.f;
     return v;
   };
+  // the lines fetch(s) will read, asked into L2 a whole stage ahead (the q / k / v / d_out rows come from HBM, and
+  // the fetch sits at the end of a stage with only the output stores between it and the commit that needs its data)
+  auto prefetch_l2 = [&](const int s) {
+    const size_t r0 = (row_base + (size_t)s * CS) * HD;
+    int r, c;
+    tile_piece(tid & 127, r, c);
+    const int which = tid >> 7;
+    const T* src = static_cast<const T*>(which == 0 ? p.xq : which == 1 ? p.xk : which == 2 ? p.xv : p.d_out) + r0;
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(src + r * HD + c));
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint4*>(g1p_all + (size_t)s * CS * E) + tid));
+    if (tid < 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint4*>(g2p_all + (size_t)s * CS * F) + tid));
+    if (tid < E + F) asm volatile("prefetch.global.L2 [%0];" ::"l"(bst + (size_t)s * (E + F) + tid));
+  };
   auto commit = [&](const StageIn& v) {
     int r, c;
     tile_piece(tid & 127, r, c);
@@ -840,6 +853,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
   for (int s = s_hi - 1; s >= s_lo; --s) {
     const size_t r0 = (row_base + (size_t)s * CS) * HD;
     commit(nxt);
+    if (s > s_lo) prefetch_l2(s - 1);
     __syncthreads();
     TRM(3)
     // ---- state at the start of this stage: undo the stage's updates (W1 first: X2 depends on it)
