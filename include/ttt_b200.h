@@ -188,11 +188,13 @@ int ttt_mlp_forward(const ttt_dims* d, const void* xq, const void* xk, const voi
  *   grad_xq, grad_xk, grad_xv [B,H,T,F]; grad_w1 [B,H,F,4F], grad_b1 [B,H,4F], grad_w2 [B,H,4F,F], grad_b2 [B,H,F]
  *   (per batch element); grad_ttt_lr_eta [B,H,T]; float32 grad_token_eta [T] (per stage position, summed over B, H),
  *   float32 grad_ln_weight / grad_ln_bias [H,F] (summed over B).  All written, never accumulated into.
- * `workspace`: ttt_mlp_backward_workspace_bytes(d) bytes, 16-byte aligned (float32 state and state gradients, the
- * hand-off records and the saved bf16 per-stage inner gradients of every stream: about B*H*(259 KB + 10 KB per
- * mini-batch), plus the scheduler words).  The kernel is persistent: blocks take (stream, chunk of 8 mini-batches)
- * work items and hand a stream's state to one another through the workspace; it is launched cooperatively (all
- * blocks co-resident) and every hand-off wait is bounded.  `status` (optional, 16 device words, zeroed by the
+ * `workspace`: ttt_mlp_backward_workspace_bytes(d) bytes, 16-byte aligned (float32 state and state gradients, a bf16
+ * copy of the state gradients, the hand-off records and the saved bf16 per-stage inner gradients of every stream:
+ * about B*H*(323 KB + 11 KB per mini-batch), plus the scheduler words).  The kernel is persistent: blocks take (stream,
+ * chunk of 8 mini-batches) work items and hand a stream's state to one another through the workspace; it is launched
+ * cooperatively (all blocks co-resident), one block per SM, and every hand-off wait is bounded.  A block allocates the
+ * SM's whole tensor memory (512 columns) for the float32 state while it runs and frees it before it exits, so a kernel
+ * of another stream that wants tensor memory on the same SM waits for it.  `status` (optional, 16 device words, zeroed by the
  * caller): {TTT_ERR_TIMEOUT, 1, block, item} if such a wait ran out; builds instrumented for tuning write per-phase
  * cycle counts of one block to the 16 words instead.
  */
