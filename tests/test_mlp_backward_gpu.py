@@ -126,3 +126,33 @@ def test_mlp_autograd_node():
     for k in ("xq", "xk", "xv", "w1", "b1", "w2", "b2", "ttt_lr_eta"):
         assert torch.equal(leaves[k].grad, g["grad_" + k]), k
     assert torch.equal(leaves["ln_weight"].grad, g["grad_ln_weight"].to(torch.bfloat16))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("from_forward", (False, True))
+def test_mlp_backward_is_bitwise_reproducible(from_forward):
+    """More streams than persistent blocks (B=16 H=12: 192 streams, 4 work items each), so a stream's items run on
+    different SMs and its float32 state travels tensor memory -> workspace -> tensor memory between them; a dirty
+    workspace the second time round.  Any race in those hand-offs, or a read of tensor memory or of the bf16 operand
+    copies that the run did not write itself, shows up as a difference between two runs."""
+    import ttt_rs_b200 as tb
+    dev = torch.device("cuda:0")
+    B, H, T = 16, 12, 512
+    t = O.make_inputs(B, H, T, 64, 16, seed=3, dtype=torch.bfloat16, inner="mlp")
+    cfg = tb.FusedTttConfig.new(16, 64, 1e-6, 128, 1)
+    d = {k: v.to(dev) for k, v in t.items()}
+    st = tb.TTTMLPState(d["w1"], d["b1"], d["w2"], d["b2"])
+    ws = tb.mlp_backward_workspace(d["xq"], cfg) if from_forward else None
+    runs = []
+    for _ in range(2):
+        if from_forward:
+            tb.fused_ttt_mlp_forward(d["xq"], d["xk"], d["xv"], st, d["token_eta"], d["ttt_lr_eta"], d["ln_weight"],
+                                     d["ln_bias"], cfg, backward_workspace=ws)
+        g = tb.fused_ttt_mlp_backward(d["xq"], d["xk"], d["xv"], st, d["token_eta"], d["ttt_lr_eta"], d["ln_weight"],
+                                      d["ln_bias"], d["grad_output"], cfg, workspace_from_forward=ws)
+        torch.cuda.synchronize()
+        tb.check_mlp_status(g)
+        runs.append({k: v.clone() for k, v in g.items() if isinstance(v, torch.Tensor)})
+    for k in runs[0]:
+        assert torch.equal(runs[0][k], runs[1][k]), f"{k} differs between two runs"
+    assert all(bool(torch.isfinite(v.float()).all()) for v in runs[0].values())
