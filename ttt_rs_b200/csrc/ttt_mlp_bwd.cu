@@ -88,9 +88,9 @@ template <int R, int C, bool TR>
 __device__ __forceinline__ MatH<R, C, !TR> tr(const MatH<R, C, TR> m) { return MatH<R, C, !TR>{m.p}; }
 
 // float32 master of a state matrix in tensor memory, used as a scratchpad that no tensor-core instruction touches:
-// tile_mma deals the 16 x 8 output tiles of a 64 x 256 (or 256 x 64) matrix to the 16 warps, eight tiles each, always
-// the same ones, so a thread only ever reads and writes its own 32 floats of a matrix -- and a warp can only address
-// its own quarter of the 128 tensor-memory lanes anyway.  Thread (warp w, lane l) owns lane 32 (w % 4) + l; the four
+// rank16_update gives the 16 x 8 output tiles of a 64 x 256 (or 256 x 64) matrix to the 16 warps, eight tiles each,
+// always the same ones, so a thread only ever reads and writes its own 32 floats of a matrix -- and a warp can only
+// address its own quarter of the 128 tensor-memory lanes anyway.  Thread (warp w, lane l) owns lane 32 (w % 4) + l; the four
 // warps that share a lane quarter take 128 of the 512 columns each (w / 4), 32 columns per matrix (W1, W2, dW1, dW2):
 // 4 matrices x 64 KB = the SM's whole 256 KB.  Column 4 u + 2 h + e of a matrix holds element (g + 8 h, 2 t + e) of the
 // warp's u-th tile (g = l / 4, t = l % 4): the order of the accumulator registers.  A read-modify-write of a matrix is
@@ -99,10 +99,6 @@ template <int R, int C>
 struct MatM {
   uint32_t taddr;  // lane quarter and first column of this warp's 32 columns of the matrix
 };
-template <class X>
-struct is_tmem : std::false_type {};
-template <int R, int C>
-struct is_tmem<MatM<R, C>> : std::true_type {};
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&r)[32]) {
   asm volatile(
@@ -533,7 +529,7 @@ __global__ void __launch_bounds__(MB_THREADS, 1) ttt_mlp_bwd_kernel(const MlpBwd
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_mine = s_tmem + ((32u * (uint32_t)(warp & 3)) << 16) + 128u * (uint32_t)(warp >> 2);
   // workspace <-> tensor memory, this thread's 32 floats of one matrix (MatG stores a 16 x 8 tile as 128 consecutive
-  // floats in the order of the accumulator registers: tile index = the index tile_mma deals by)
+  // floats in the order of the accumulator registers: tile index = the index rank16_update deals by)
   auto master_in = [&](const float* M, const uint32_t taddr) {
     float v[32];
     const float* src = M + warp * 128 + 8 * (lane >> 2) + 2 * (lane & 3);
