@@ -306,4 +306,38 @@ __device__ __forceinline__ void st_from_float<__nv_bfloat16>(void* base, size_t 
   static_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16_rn(v);
 }
 
+
+// ---- tensor memory as a per-thread scratchpad (no tensor-core instruction touches it) ---------------------------
+// A warp can address the 32 tensor-memory lanes of its quarter (warp index % 4) only, and with the 32x32b shape lane l
+// of the warp gets lane 32 (warp % 4) + l: N consecutive columns of that lane are N private 32-bit words of the
+// thread.  A kernel whose per-thread float32 state crowds its registers keeps it there between the places that use
+// it: a load + store round trip of 32 columns costs about 100 cycles (measured by probe_chain_latency.cu).
+// taddr = allocation base + (first lane of the quarter << 16) + column.
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, int columns) {  // one whole warp; a power of 2 >= 32
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_slot), "r"(columns) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, int columns) {  // the warp that allocated
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tmem_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// 32 columns <-> an [8][4] register array (the accumulator fragments of eight 16 x 8 tiles).  The load waits for its
+// data; the store does not wait: tmem_wait_st() before the next load of the same columns.
+__device__ __forceinline__ void tmem_ld_8x4(uint32_t taddr, float (&r)[8][4]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=f"(r[0][0]), "=f"(r[0][1]), "=f"(r[0][2]), "=f"(r[0][3]), "=f"(r[1][0]), "=f"(r[1][1]), "=f"(r[1][2]), "=f"(r[1][3]), "=f"(r[2][0]), "=f"(r[2][1]), "=f"(r[2][2]), "=f"(r[2][3]), "=f"(r[3][0]), "=f"(r[3][1]), "=f"(r[3][2]), "=f"(r[3][3]), "=f"(r[4][0]), "=f"(r[4][1]), "=f"(r[4][2]), "=f"(r[4][3]), "=f"(r[5][0]), "=f"(r[5][1]), "=f"(r[5][2]), "=f"(r[5][3]), "=f"(r[6][0]), "=f"(r[6][1]), "=f"(r[6][2]), "=f"(r[6][3]), "=f"(r[7][0]), "=f"(r[7][1]), "=f"(r[7][2]), "=f"(r[7][3])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_8x4(uint32_t taddr, const float (&r)[8][4]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31};"
+      ::"f"(r[0][0]), "f"(r[0][1]), "f"(r[0][2]), "f"(r[0][3]), "f"(r[1][0]), "f"(r[1][1]), "f"(r[1][2]), "f"(r[1][3]), "f"(r[2][0]), "f"(r[2][1]), "f"(r[2][2]), "f"(r[2][3]), "f"(r[3][0]), "f"(r[3][1]), "f"(r[3][2]), "f"(r[3][3]), "f"(r[4][0]), "f"(r[4][1]), "f"(r[4][2]), "f"(r[4][3]), "f"(r[5][0]), "f"(r[5][1]), "f"(r[5][2]), "f"(r[5][3]), "f"(r[6][0]), "f"(r[6][1]), "f"(r[6][2]), "f"(r[6][3]), "f"(r[7][0]), "f"(r[7][1]), "f"(r[7][2]), "f"(r[7][3]), "r"(taddr)
+      : "memory");
+}
+
 }  // namespace ttt

@@ -98,6 +98,15 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
   // work item = (stream, chunk of CH stages); set per item below
   int stream = 0, row_base = 0;
   __shared__ int s_item;
+  // W^T and dW^T (32 + 32 float32 words per thread) are parked in tensor memory between the places of a stage that use
+  // them (see tmem_ld_8x4), so that they do not occupy 64 registers through the middle of the stage.  64 columns per
+  // block, freed by the warp that allocated them after the item loop, where every way out of the loop ends.
+  __shared__ uint32_t s_tmem;
+  if (warp == 0) tmem_alloc(smem_u32(&s_tmem), 64);
+  tmem_fence_before_sync();
+  __syncthreads();
+  tmem_fence_after_sync();
+  const uint32_t tm_w = s_tmem + ((32u * (uint32_t)warp) << 16), tm_dw = tm_w + 32u;
 
   if (tid == 0) {
     if constexpr (!GATHER) {
@@ -213,8 +222,9 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
   const size_t HOFF = 2 * HD * HD + HD;
 
   // Persistent block: items are handed out in increasing order, last chunks of all streams first.  An item only
-  // waits for an item with a smaller index (the later chunk of the same stream), which a resident block already
-  // holds, so the launch cannot deadlock as long as all blocks are co-resident (cooperative launch).
+  // waits for an item with a smaller index (the later chunk of the same stream), which was taken by a block that runs
+  // or has finished (a block takes an item only once it runs), so the wait graph has no cycle and the launch cannot
+  // deadlock, whether or not every block of the grid is resident.
   while (!failed) {
     if (tid == 0) s_item = atomicAdd(&p.sched[0], 1);
     __syncthreads();
@@ -298,6 +308,9 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
         dbias[nt] = __ldcg(reinterpret_cast<const float2*>(ho + 2 * HD * HD + nb + 8 * nt + 2 * t));
     }
 
+  tmem_st_8x4(tm_w, wt);
+  tmem_st_8x4(tm_dw, dwt);
+
   // the next stage (walking down) that ends a checkpoint interval, and the checkpoint that holds the state after it
   // (kept from stage to stage: no division by the runtime interval on the chain)
   int ck_idx = s_hi / p.K + 1;
@@ -313,6 +326,10 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
     const uint32_t pq = tq + TF::PLANE_OFF, pk = tk + TF::PLANE_OFF, pg = tg + TF::PLANE_OFF;
     const uint8_t* gsl = gbase + slot * SM::SLOT;
 
+    // ---- the state after this stage, out of tensor memory
+    tmem_wait_st();
+    tmem_ld_8x4(tm_dw, dwt);
+    if (s != s_ck) tmem_ld_8x4(tm_w, wt);
     // ---- at the last stage of a checkpoint interval: exact state after the stage (= next checkpoint / final W)
     if (s == s_ck) {
       // stored by the forward as its threads held it: float4 kt of thread tid at [kt][tid]
@@ -409,6 +426,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
         mma_np<NP>(at[1], aq, bj1);
       }
     }
+    tmem_st_8x4(tm_w, wt);  // W_s^T: next used by the stage below (dW^T is unchanged so far: nothing to store)
     // products were taken with What: Z = wscale * acc + b
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
@@ -564,20 +582,6 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       mma_np<NP>(dgp[0], amt, z0);  // dGp = -M'^T dZbar
       mma_np<NP>(dgp[1], amt, zz1);
     }
-    // dW^T += dZbar^T Q
-    {
-      Pk<NP> adzt[4];
-      ldsm_np<NP>(adzt, tDZ + lane_off_B_nk(lane, nb), PL, true);
-#pragma unroll
-      for (int kp = 0; kp < 4; ++kp) {
-        if (khalf >= 0 && (kp >> 1) != khalf) continue;  // paired heads: only the head's own block of dW^T
-        Pk<NP> bq[4];
-        ldsm_np<NP>(bq, pq + lane_off_B_kn(lane, 16 * kp), PL, true);
-        const Pk<NP> b0[2] = {bq[0], bq[1]}, b1[2] = {bq[2], bq[3]};
-        mma_np<NP>(dwt[2 * kp], adzt, b0);
-        mma_np<NP>(dwt[2 * kp + 1], adzt, b1);
-      }
-    }
     // ---- 10. gradient reaching Gp, the lr / token_eta terms, and the first pair of second-derivative sums
     F2 u[2][2], v[2][2];
     float s1t[2], s2t[2];
@@ -673,6 +677,22 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
       mma_np<NP>(dk[0], adz1, b0);
       mma_np<NP>(dk[1], adz1, b1);
     }
+    // dW^T += dZbar^T Q, then dW^T += dZ1^T K: both here (the dZbar tile and this stage's Q tile are still in place), so
+    // that dW^T is in registers for this one stretch of the stage
+    tmem_ld_8x4(tm_dw, dwt);
+    {
+      Pk<NP> adzt[4];
+      ldsm_np<NP>(adzt, tDZ + lane_off_B_nk(lane, nb), PL, true);
+#pragma unroll
+      for (int kp = 0; kp < 4; ++kp) {
+        if (khalf >= 0 && (kp >> 1) != khalf) continue;  // paired heads: only the head's own block of dW^T
+        Pk<NP> bq[4];
+        ldsm_np<NP>(bq, pq + lane_off_B_kn(lane, 16 * kp), PL, true);
+        const Pk<NP> b0[2] = {bq[0], bq[1]}, b1[2] = {bq[2], bq[3]};
+        mma_np<NP>(dwt[2 * kp], adzt, b0);
+        mma_np<NP>(dwt[2 * kp + 1], adzt, b1);
+      }
+    }
     {
       Pk<NP> adzt[4];
       ldsm_np<NP>(adzt, tDZ1 + lane_off_B_nk(lane, nb), PL, true);
@@ -686,6 +706,7 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
         mma_np<NP>(dwt[2 * kp + 1], adzt, b1);
       }
     }
+    tmem_st_8x4(tm_dw, dwt);
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
       const F2 cs = f2add(dzsum[nt], f2add(dz1[nt][0], dz1[nt][1]));
@@ -727,6 +748,9 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
   }
 
     if (failed) break;
+    tmem_wait_st();
+    tmem_ld_8x4(tm_w, wt);
+    tmem_ld_8x4(tm_dw, dwt);
     // ---- end of the item: LN partials of this (stream, chunk); then either hand the state to the earlier chunk
     // or, for the first chunk of the sequence, write the gradients w.r.t. the initial state
 #pragma unroll
@@ -794,6 +818,10 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
   }  // item loop
   if (tid == 0) bulk_wait_all<0>();
   if constexpr (GATHER) cp_async_wait_all();  // (an item that gave up may leave gathers in flight)
+  tmem_wait_st();
+  tmem_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(s_tmem, 64);
 }
 
 // ----------------------------------------------------------------------------------------------------
@@ -871,13 +899,25 @@ static cudaError_t launch_bwd_t(const CUtensorMap* m, const void* const* io, con
   auto kfn = ttt_linear_bwd_kernel<T, SEG, MB>;
   cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SM::DYN_BYTES);
   if (e != cudaSuccess) return e;
-  // persistent grid: as many blocks as can be resident at once (they wait on one another's hand-offs), never more
-  // than there are work items; launched cooperatively so that co-residency is guaranteed, not assumed
-  int dev = 0, sms = 0, per_sm = 0;
+  // Persistent grid: as many blocks as fit on the device at once, never more than there are work items.  The count
+  // comes from the kernel's registers and shared memory: the occupancy calculator answers one block per SM for any
+  // kernel that allocates tensor memory, whatever it allocates (which also rules out a cooperative launch of more).
+  // Co-residency is not needed for progress: a block takes an item only once it runs, and the item it may wait for
+  // has a smaller index, so it was taken by a block that runs or has finished; a block that is not resident yet holds
+  // nothing anybody waits for.
+  int dev = 0, sms = 0, regs_sm = 0, smem_sm = 0, smem_rsv = 0;
   if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
   if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
-  if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kfn, NTHREADS, SM::DYN_BYTES)) != cudaSuccess)
-    return e;
+  if ((e = cudaDeviceGetAttribute(&regs_sm, cudaDevAttrMaxRegistersPerMultiprocessor, dev)) != cudaSuccess) return e;
+  if ((e = cudaDeviceGetAttribute(&smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev)) != cudaSuccess) return e;
+  if ((e = cudaDeviceGetAttribute(&smem_rsv, cudaDevAttrReservedSharedMemoryPerBlock, dev)) != cudaSuccess) return e;
+  cudaFuncAttributes fa;
+  if ((e = cudaFuncGetAttributes(&fa, kfn)) != cudaSuccess) return e;
+  const int regs_block = ((fa.numRegs + 7) & ~7) * NTHREADS;  // registers are allocated in units of 8 per thread
+  const int smem_block = (int)SM::DYN_BYTES + (int)fa.sharedSizeBytes + smem_rsv;
+  int per_sm = regs_sm / regs_block;
+  if (smem_sm / smem_block < per_sm) per_sm = smem_sm / smem_block;
+  if (per_sm > 512 / 64) per_sm = 512 / 64;  // tensor-memory columns
   if (per_sm < 1) return cudaErrorLaunchOutOfResources;
   int grid = sms * per_sm;
   const int nitems = nstreams * p.NCH;
@@ -892,7 +932,7 @@ static cudaError_t launch_bwd_t(const CUtensorMap* m, const void* const* io, con
   }
   args[7] = (void*)&m[7];
   args[8] = (void*)&pp;
-  return cudaLaunchCooperativeKernel((const void*)kfn, dim3(grid), dim3(NTHREADS), args, SM::DYN_BYTES, st);
+  return cudaLaunchKernel((const void*)kfn, dim3(grid), dim3(NTHREADS), args, SM::DYN_BYTES, st);
 }
 
 template <typename T, int SEG>
