@@ -522,11 +522,19 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) pp[nt][i] = gl[nt][i] = dk[nt][i] = dgp[nt][i] = 0.f;
+    // (bf16: the B fragments of W^T read here serve step 13 as well -- there are registers for them now that the state
+    // is parked in tensor memory)
+    constexpr bool KEEP_W = (NP == 1);
+    Pk<NP> bw_keep[KEEP_W ? 4 : 1][4];
 #pragma unroll
     for (int ks = 0; ks < 4; ++ks) {
       Pk<NP> adz[4], bwt[4], ags[4], bdw[4];
       ldsm_np<NP>(adz, tDZ + lane_off_A(lane, 16 * ks), PL, false);
       ldsm_np<NP>(bwt, tW + ks * SM::PLANES + lane_off_B_kn(lane, nb), PL, true);
+      if constexpr (KEEP_W) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) bw_keep[ks][i] = bwt[i];
+      }
       ldsm_np<NP>(ags, pg + lane_off_A(lane, 16 * ks), PL, false);
       ldsm_np<NP>(bdw, tDW + ks * SM::PLANES + lane_off_B_kn(lane, nb), PL, true);
       if (SEG == 64 || (ks >> 1) == hsel) {
@@ -672,7 +680,12 @@ __global__ void __launch_bounds__(NTHREADS, (sizeof(T) == 2 ? TTT_BWD_MINB_BF16 
     for (int ks = 0; ks < 4; ++ks) {
       Pk<NP> adz1[4], bwt[4];
       ldsm_np<NP>(adz1, tDZ1 + lane_off_A(lane, 16 * ks), PL, false);
-      ldsm_np<NP>(bwt, tW + ks * SM::PLANES + lane_off_B_kn(lane, nb), PL, true);
+      if constexpr (KEEP_W) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) bwt[i] = bw_keep[ks][i];
+      } else {
+        ldsm_np<NP>(bwt, tW + ks * SM::PLANES + lane_off_B_kn(lane, nb), PL, true);
+      }
       const Pk<NP> b0[2] = {bwt[0], bwt[1]}, b1[2] = {bwt[2], bwt[3]};
       mma_np<NP>(dk[0], adz1, b0);
       mma_np<NP>(dk[1], adz1, b1);
