@@ -134,6 +134,9 @@ size_t ttt_linear_backward_workspace_bytes(const ttt_dims* d);
  *                   d token_eta folded to [CS]} summed over this call's batch: one buffer for one all-reduce
  *   workspace       at least ttt_linear_backward_workspace_bytes(d) bytes
  * The three float32 outputs are written (not accumulated into); the caller need not zero them.
+ * The kernel is persistent (blocks take (stream, chunk of 16 mini-batches) work items; every hand-off wait is bounded,
+ * see `status`) and each of its blocks holds 64 columns of the SM's tensor memory while it runs: a kernel of another
+ * stream that wants more tensor memory than is left on an SM waits there until these blocks exit.
  */
 int ttt_linear_backward(const ttt_dims* d, const void* xq, const void* xk, const void* xv, const void* weight,
                         const void* bias, const void* token_eta, const void* ttt_lr_eta, const void* ln_weight,
