@@ -126,6 +126,15 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
   const int nitems = persistent ? p.nstreams * NCH : (int)gridDim.x;
   __shared__ int s_item;
   int stream = 0, head = 0, row_base = 0;
+  // W1^T and W2 (64 + 64 float32 words per thread) are parked in tensor memory between the places of a stage that use
+  // them (see tmem_ld_8x4): 256 columns per block -- two warps share a lane quarter and take 128 columns each --
+  // freed by the warp that allocated them after the work-item loop, where every way out of the loop ends.
+  __shared__ uint32_t s_tmem;
+  if (warp == 0) tmem_alloc(smem_u32(&s_tmem), 256);
+  tmem_fence_before_sync();
+  __syncthreads();
+  tmem_fence_after_sync();
+  const uint32_t tm_w1 = s_tmem + ((32u * (uint32_t)(warp & 3)) << 16) + 128u * (uint32_t)(warp >> 2), tm_w2 = tm_w1 + 64u;
 
   if (tid == 0) {
     prefetch_tmap(&tm_q);
@@ -269,6 +278,10 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
       for (int s = s_lo; s < s_lo + MLP_NST && s <= s_hi; ++s) issue_loads(n + (s - s_lo), s);
     }
     publish_w2();
+    tmem_st_8x4(tm_w1, w1t[0]);
+    tmem_st_8x4(tm_w1 + 32u, w1t[1]);
+    tmem_st_8x4(tm_w2, w2[0]);
+    tmem_st_8x4(tm_w2 + 32u, w2[1]);
 
   for (int s = s_lo; s <= s_hi; ++s, ++n) {
     const int slot = n % MLP_NST;
@@ -296,6 +309,9 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
     };
 
     // ---- S1. Z1 = K W1 + b1, Zq = Q W1 + b1 (columns eb..eb+31), A1 = Q K^T
+    tmem_wait_st();
+    tmem_ld_8x4(tm_w1, w1t[0]);
+    tmem_ld_8x4(tm_w1 + 32u, w1t[1]);
     float z1[4][4], zq[4][4], at[2][4];
 #pragma unroll
     for (int j = 0; j < 4; ++j)
@@ -400,6 +416,8 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
     }
     __syncthreads();  // B2: G2p tile visible
     // ---- S5. G1p = (G2p W2^T) o gelu'(Z1)  (columns eb..eb+31; W2 straight from registers)
+    tmem_ld_8x4(tm_w2, w2[0]);
+    tmem_ld_8x4(tm_w2 + 32u, w2[1]);
     F2 g1p[4][2];
     {
       float h[4][4];
@@ -529,11 +547,15 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
       }
     }
     // ---- S11. state updates (every warp its own rows), then refresh the bf16 copy of W2
+    tmem_ld_8x4(tm_w1, w1t[0]);
+    tmem_ld_8x4(tm_w1 + 32u, w1t[1]);
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt) {
       const Pk<1> agt[4] = {gt1[2 * mt][0], gt1[2 * mt + 1][0], gt1[2 * mt][1], gt1[2 * mt + 1][1]};
       if (w_moves) state_update_direct<1>(w1t[mt], agt, tk, lane);
     }
+    tmem_st_8x4(tm_w1, w1t[0]);
+    tmem_st_8x4(tm_w1 + 32u, w1t[1]);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       // float32 column sums, like the reference; the backward's reverse walk subtracts the sums of the bf16 operand
@@ -547,6 +569,8 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
       for (int j = 0; j < 4; ++j)
 #pragma unroll
         for (int r = 0; r < 2; ++r) xt[j][r] = movm_t_np<1>(split_pack<1>(x2[j][r].x, x2[j][r].y));
+      tmem_ld_8x4(tm_w2, w2[0]);
+      tmem_ld_8x4(tm_w2 + 32u, w2[1]);
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
         const Pk<1> ax[4] = {xt[2 * mt][0], xt[2 * mt + 1][0], xt[2 * mt][1], xt[2 * mt + 1][1]};
@@ -556,8 +580,15 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
       b2v = f2fma(f2(col_sum(cs.x), col_sum(cs.y)), f2(-te15), b2v);
     }
     if (s < s_hi) publish_w2();
+    tmem_st_8x4(tm_w2, w2[0]);
+    tmem_st_8x4(tm_w2 + 32u, w2[1]);
   }
   if (failed) break;
+  tmem_wait_st();
+  tmem_ld_8x4(tm_w1, w1t[0]);
+  tmem_ld_8x4(tm_w1 + 32u, w1t[1]);
+  tmem_ld_8x4(tm_w2, w2[0]);
+  tmem_ld_8x4(tm_w2 + 32u, w2[1]);
   if (chunk < NCH - 1) {
     // ---- park the state for the next chunk of this stream: register images into the stream's workspace block
     float4* h1 = reinterpret_cast<float4*>(bws);
@@ -622,6 +653,10 @@ __global__ void __launch_bounds__(MLP_THREADS, 1)
     }
   }
   }  // work items
+  tmem_wait_st();
+  tmem_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(s_tmem, 256);
   if (tid == 0) bulk_wait_all<0>();
 }
 
