@@ -176,6 +176,8 @@ int ttt_linear_backward_state_grads(const ttt_dims* d, const void* xq, const voi
  *                   forward leaves there the float32 final state and the bf16 operands of every state update, which
  *                   is all the backward's own first pass would compute: pass the buffer on to ttt_mlp_backward
  *                   with workspace_from_forward = 1.  NULL (with 0 bytes) for inference.
+ * One block per SM; a block holds 256 columns of the SM's tensor memory (the float32 state between its uses) while it
+ * runs.
  */
 int ttt_mlp_forward(const ttt_dims* d, const void* xq, const void* xk, const void* xv, const void* w1, const void* b1,
                     const void* w2, const void* b2, const void* token_eta, const void* ttt_lr_eta,
